@@ -1,0 +1,694 @@
+"""TEST INFRASTRUCTURE, NOT PRODUCT CODE.
+
+ctypes front of the CPU oracle (``libhl_oracle.so``, built from the C files beside
+this one) plus the small amount of host protocol logic the reference keeps around
+the primitives: hash tags, the hiding commitment's draw order, claim grouping and
+the opening of ``zkp-core/src/pcs.rs``.  Only the tests, the smoke check and the
+bench's CPU baseline import this module.
+
+Field elements travel as ``numpy.uint64``; an Fp2 is two consecutive words
+``(c0, c1)``, so an Fp2 vector of length n is a ``(n, 2)`` uint64 array.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence, Tuple
+
+import numpy as np
+
+P = 0xFFFFFFFF00000001
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "libhl_oracle.so")
+
+
+def build(force: bool = False) -> str:
+    """Compile the oracle with the system gcc (the Makefile beside this file)."""
+    srcs = [os.path.join(_HERE, f) for f in ("blake3.c", "ntt.c", "transcript.c", "sumcheck.c", "logup.c", "hl_oracle.h", "field.h")]
+    if force or not os.path.exists(_SO) or any(os.path.getmtime(s) > os.path.getmtime(_SO) for s in srcs):
+        subprocess.check_call(["make", "-C", _HERE, "-s"])
+    return _SO
+
+
+def _load():
+    if not os.path.exists(_SO):
+        build()
+    lib = C.CDLL(_SO)
+    u64, sz, vp, i32, i64 = C.c_uint64, C.c_size_t, C.c_void_p, C.c_int, C.c_int64
+    for name in ("or_fp_add", "or_fp_sub", "or_fp_mul", "or_fp_pow", "or_fp_from_u128"):
+        getattr(lib, name).restype = u64
+        getattr(lib, name).argtypes = [u64, u64]
+    for name in ("or_fp_neg", "or_fp_inv", "or_fp_new"):
+        getattr(lib, name).restype = u64
+        getattr(lib, name).argtypes = [u64]
+    lib.or_fp_from_i64.restype = u64
+    lib.or_fp_from_i64.argtypes = [i64]
+    lib.or_two_adic_root.restype = u64
+    lib.or_two_adic_root.argtypes = [C.c_uint32]
+    lib.or_tr_challenge_fp.restype = u64
+    lib.or_rng_next_u64.restype = u64
+    lib.or_rng_fp.restype = u64
+    lib.or_num_threads.restype = i32
+    return lib
+
+
+_lib = _load()
+
+
+def _p(a) -> C.c_void_p:
+    if a is None:
+        return C.c_void_p(0)
+    if isinstance(a, (bytes, bytearray)):
+        return bytes(a)
+    assert a.flags["C_CONTIGUOUS"]
+    return C.c_void_p(a.ctypes.data)
+
+
+def _u64(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.uint64)
+
+
+def num_threads() -> int:
+    return int(_lib.or_num_threads())
+
+
+# ----------------------------------------------------------------------------- field
+def fp_add(a, b): return int(_lib.or_fp_add(a, b))
+def fp_sub(a, b): return int(_lib.or_fp_sub(a, b))
+def fp_mul(a, b): return int(_lib.or_fp_mul(a, b))
+def fp_neg(a): return int(_lib.or_fp_neg(a))
+def fp_inv(a): return int(_lib.or_fp_inv(a))
+def fp_pow(a, e): return int(_lib.or_fp_pow(a, e))
+def fp_new(a): return int(_lib.or_fp_new(a))
+def fp_from_u128(v): return int(_lib.or_fp_from_u128((v >> 64) & (2**64 - 1), v & (2**64 - 1)))
+def fp_from_i64(v): return int(_lib.or_fp_from_i64(v))
+def two_adic_root(k): return int(_lib.or_two_adic_root(k))
+
+
+def fp2_add(a, b): return (fp_add(a[0], b[0]), fp_add(a[1], b[1]))
+def fp2_sub(a, b): return (fp_sub(a[0], b[0]), fp_sub(a[1], b[1]))
+def fp2_neg(a): return (fp_neg(a[0]), fp_neg(a[1]))
+def fp2_mul_base(a, b): return (fp_mul(a[0], b), fp_mul(a[1], b))
+def fp2_is_zero(a): return a[0] == 0 and a[1] == 0
+
+
+def fp2_mul(a, b):
+    x, y, o = (C.c_uint64 * 2)(*a), (C.c_uint64 * 2)(*b), (C.c_uint64 * 2)()
+    _lib.or_fp2_mul(x, y, o)
+    return (int(o[0]), int(o[1]))
+
+
+def fp2_inv(a):
+    x, o = (C.c_uint64 * 2)(*a), (C.c_uint64 * 2)()
+    _lib.or_fp2_inv(x, o)
+    return (int(o[0]), int(o[1]))
+
+
+def batch_inverse2(vals: np.ndarray) -> np.ndarray:
+    v = _u64(vals).copy()
+    _lib.or_batch_inverse2(_p(v), C.c_size_t(v.shape[0]))
+    return v
+
+
+# ----------------------------------------------------------------------------- blake3
+def blake3(data: bytes, key: Optional[bytes] = None, outlen: int = 32) -> bytes:
+    out = C.create_string_buffer(outlen)
+    _lib.or_blake3(_p(key) if key else None, data, C.c_size_t(len(data)), out, C.c_size_t(outlen))
+    return out.raw
+
+
+def derive_key(context: bytes, material: bytes) -> bytes:
+    out = C.create_string_buffer(32)
+    _lib.or_blake3_derive_key(context, C.c_size_t(len(context)), material, C.c_size_t(len(material)), out)
+    return out.raw
+
+
+# hashtag.rs:47-53
+CTX_TRANSCRIPT = b"hashline-zk-mr1 2026-09-20 fiat-shamir transcript"
+CTX_COLUMN = b"hashline-zk-mr1 2026-09-20 pcs column digest"
+CTX_LEAF = b"hashline-zk-mr1 2026-09-20 pcs salted merkle leaf"
+CTX_NODE = b"hashline-zk-mr1 2026-09-20 pcs merkle inner node"
+
+
+@dataclass(frozen=True)
+class HashTag:
+    """hashtag.rs:75-150: the legacy rule (no key anywhere) or one profile's four keys."""
+    transcript: Optional[bytes] = None
+    column: Optional[bytes] = None
+    leaf: Optional[bytes] = None
+    node: Optional[bytes] = None
+
+    @staticmethod
+    def legacy() -> "HashTag":
+        return HashTag()
+
+    @staticmethod
+    def for_profile(profile: str) -> "HashTag":
+        p = profile.encode()
+        return HashTag(derive_key(CTX_TRANSCRIPT, p), derive_key(CTX_COLUMN, p), derive_key(CTX_LEAF, p), derive_key(CTX_NODE, p))
+
+
+# ----------------------------------------------------------------------------- ntt / pcs primitives
+def ntt_forward(a: np.ndarray, max_log: int) -> np.ndarray:
+    a = _u64(a).copy()
+    _lib.or_ntt_forward(_p(a), C.c_uint32(int(a.size).bit_length() - 1), C.c_uint32(max_log))
+    return a
+
+
+def ntt_inverse(a: np.ndarray, max_log: int) -> np.ndarray:
+    a = _u64(a).copy()
+    _lib.or_ntt_inverse(_p(a), C.c_uint32(int(a.size).bit_length() - 1), C.c_uint32(max_log))
+    return a
+
+
+def coset_powers(h: int, nn: int) -> np.ndarray:
+    out = np.empty(nn, dtype=np.uint64)
+    _lib.or_coset_powers(C.c_uint64(h), C.c_size_t(nn), _p(out))
+    return out
+
+
+def encode_row_zk(msg, pad, pows, max_log: int) -> np.ndarray:
+    msg, pad, pows = _u64(msg), _u64(pad), _u64(pows)
+    out = np.empty(pows.size, dtype=np.uint64)
+    _lib.or_encode_row_zk(_p(msg), C.c_size_t(msg.size), _p(pad), C.c_size_t(pad.size), _p(pows), C.c_size_t(pows.size), C.c_uint32(max_log), _p(out))
+    return out
+
+
+def encode_rows_zk(data, rows: int, n: int, pads, q: int, pows, max_log: int) -> np.ndarray:
+    data, pads, pows = _u64(data), _u64(pads), _u64(pows)
+    nn = pows.size
+    enc = np.empty(rows * nn, dtype=np.uint64)
+    _lib.or_encode_rows_zk(_p(data), C.c_size_t(rows), C.c_size_t(n), _p(pads), C.c_size_t(q), _p(pows), C.c_size_t(nn), C.c_uint32(max_log), _p(enc))
+    return enc
+
+
+def encode_rows_plain(data, rows: int, n: int, nn: int, max_log: int) -> np.ndarray:
+    data = _u64(data)
+    enc = np.empty(rows * nn, dtype=np.uint64)
+    _lib.or_encode_rows_plain(_p(data), C.c_size_t(rows), C.c_size_t(n), C.c_size_t(nn), C.c_uint32(max_log), _p(enc))
+    return enc
+
+
+def hash_columns(encoded, rows: int, nn: int, key: Optional[bytes] = None) -> np.ndarray:
+    encoded = _u64(encoded)
+    leaves = np.empty((nn, 32), dtype=np.uint8)
+    _lib.or_hash_columns(_p(encoded), C.c_size_t(rows), C.c_size_t(nn), _p(key) if key else None, _p(leaves))
+    return leaves
+
+
+def salt_leaves(leaves: np.ndarray, salts: np.ndarray, leaf_key: Optional[bytes] = None) -> np.ndarray:
+    leaves, salts = np.ascontiguousarray(leaves, np.uint8), np.ascontiguousarray(salts, np.uint8)
+    out = np.empty_like(leaves)
+    _lib.or_salt_leaves(_p(leaves), _p(salts), C.c_size_t(leaves.shape[0]), _p(leaf_key) if leaf_key else None, _p(out))
+    return out
+
+
+def merkle_build(leaves: np.ndarray, node_key: Optional[bytes] = None) -> np.ndarray:
+    """All levels, flattened: nn leaves, nn/2, ..., the root last ((2 nn - 1) x 32 bytes)."""
+    leaves = np.ascontiguousarray(leaves, np.uint8)
+    nn = leaves.shape[0]
+    out = np.empty((2 * nn - 1, 32), dtype=np.uint8)
+    _lib.or_merkle_build(_p(leaves), C.c_size_t(nn), _p(node_key) if node_key else None, _p(out))
+    return out
+
+
+def merkle_path(levels: np.ndarray, nn: int, j: int) -> List[bytes]:
+    """merkle.rs:91-100: siblings from the leaf level up."""
+    out, off, w = [], 0, nn
+    while w > 1:
+        out.append(bytes(levels[off + (j ^ 1)]))
+        off += w
+        w //= 2
+        j >>= 1
+    return out
+
+
+def merkle_verify_path(root: bytes, idx: int, leaf: bytes, path: Sequence[bytes], node_key: Optional[bytes] = None) -> bool:
+    """merkle.rs:102-127."""
+    cur = leaf
+    for sib in path:
+        cur = blake3(cur + sib if idx & 1 == 0 else sib + cur, node_key)
+        idx >>= 1
+    return cur == root
+
+
+def fold_rows(src, rows: int, n: int, nn: int, ir: int, rhos: np.ndarray) -> np.ndarray:
+    src, rhos = _u64(src), _u64(rhos)
+    k = rhos.shape[0]
+    out = np.empty((k, n, 2), dtype=np.uint64)
+    _lib.or_fold_rows(_p(src), C.c_size_t(rows), C.c_size_t(n), C.c_size_t(nn), C.c_size_t(ir), _p(rhos), C.c_size_t(k), _p(out))
+    return out
+
+
+def gather_columns(encoded, rows: int, nn: int, idx) -> np.ndarray:
+    encoded, idx = _u64(encoded), _u64(idx)
+    out = np.empty((idx.size, rows), dtype=np.uint64)
+    _lib.or_gather_columns(_p(encoded), C.c_size_t(rows), C.c_size_t(nn), _p(idx), C.c_size_t(idx.size), _p(out))
+    return out
+
+
+# ----------------------------------------------------------------------------- transcript / rng
+class _TrStruct(C.Structure):
+    _fields_ = [("state", C.c_uint8 * 32), ("counter", C.c_uint64), ("key", C.c_uint8 * 32), ("keyed", C.c_int)]
+
+
+class Transcript:
+    """transcript.rs:17-167 without the masker plumbing (see `sc_prove` for masked rounds)."""
+
+    def __init__(self, domain: bytes, key: Optional[bytes] = None):
+        self._t = _TrStruct()
+        self.key = key
+        _lib.or_tr_new(C.byref(self._t), domain, C.c_size_t(len(domain)), _p(key) if key else None)
+
+    def clone(self) -> "Transcript":
+        t = Transcript.__new__(Transcript)
+        t._t = _TrStruct()
+        C.memmove(C.byref(t._t), C.byref(self._t), C.sizeof(_TrStruct))
+        t.key = self.key
+        return t
+
+    @property
+    def state(self) -> bytes:
+        return bytes(self._t.state)
+
+    @property
+    def counter(self) -> int:
+        return int(self._t.counter)
+
+    def absorb(self, label: bytes, data: bytes) -> None:
+        _lib.or_tr_absorb(C.byref(self._t), label, C.c_size_t(len(label)), data, C.c_size_t(len(data)))
+
+    def absorb_u64(self, label: bytes, v: int) -> None:
+        self.absorb(label, int(v).to_bytes(8, "little"))
+
+    def absorb_fp(self, label: bytes, vals) -> None:
+        self.absorb(label, _u64(vals).tobytes())
+
+    def absorb_fp2(self, label: bytes, vals) -> None:
+        self.absorb(label, _u64(vals).tobytes())
+
+    def squeeze(self) -> bytes:
+        out = C.create_string_buffer(32)
+        _lib.or_tr_squeeze(C.byref(self._t), out)
+        return out.raw
+
+    def challenge_fp(self) -> int:
+        return int(_lib.or_tr_challenge_fp(C.byref(self._t)))
+
+    def challenge_fp2(self) -> Tuple[int, int]:
+        o = (C.c_uint64 * 2)()
+        _lib.or_tr_challenge_fp2(C.byref(self._t), o)
+        return (int(o[0]), int(o[1]))
+
+    def challenge_fp2_vec(self, n: int) -> np.ndarray:
+        out = np.empty((n, 2), dtype=np.uint64)
+        for i in range(n):
+            out[i] = self.challenge_fp2()
+        return out
+
+    def challenge_indices(self, n: int, bound: int) -> np.ndarray:
+        out = np.empty(n, dtype=np.uint64)
+        _lib.or_tr_challenge_indices(C.byref(self._t), C.c_size_t(n), C.c_uint64(bound), _p(out))
+        return out
+
+
+class _RngStruct(C.Structure):
+    _fields_ = [("key", C.c_uint8 * 32), ("counter", C.c_uint64), ("buf", C.c_uint8 * 8192), ("pos", C.c_size_t)]
+
+
+class ZkRng:
+    """rng.rs:279-417: BLAKE3-XOF counter mode, 8 KiB blocks."""
+
+    def __init__(self, seed: int, domain: bytes):
+        self._r = _RngStruct()
+        _lib.or_rng_new(C.byref(self._r), C.c_uint64(seed), domain, C.c_size_t(len(domain)))
+
+    def next_u64(self) -> int:
+        return int(_lib.or_rng_next_u64(C.byref(self._r)))
+
+    def fp(self) -> int:
+        return int(_lib.or_rng_fp(C.byref(self._r)))
+
+    def fp2(self) -> Tuple[int, int]:
+        a = self.fp()
+        return (a, self.fp())
+
+    def fp_vec(self, n: int) -> np.ndarray:
+        out = np.empty(n, dtype=np.uint64)
+        _lib.or_rng_fill_fp(C.byref(self._r), _p(out), C.c_size_t(n))
+        return out
+
+    def fp2_vec(self, n: int) -> np.ndarray:
+        return self.fp_vec(2 * n).reshape(n, 2)
+
+    def bytes32(self) -> bytes:
+        out = C.create_string_buffer(32)
+        _lib.or_rng_bytes32(C.byref(self._r), out)
+        return out.raw
+
+    def salts(self, nn: int) -> np.ndarray:
+        return np.frombuffer(b"".join(self.bytes32() for _ in range(nn)), dtype=np.uint8).reshape(nn, 32).copy()
+
+
+# ----------------------------------------------------------------------------- mle / sumcheck
+def eq_table(r: np.ndarray) -> np.ndarray:
+    r = _u64(r).reshape(-1, 2)
+    out = np.empty((1 << r.shape[0], 2), dtype=np.uint64)
+    _lib.or_eq_table(_p(r), C.c_size_t(r.shape[0]), _p(out))
+    return out
+
+
+def eq_table_msb(r: np.ndarray) -> np.ndarray:
+    r = _u64(r).reshape(-1, 2)
+    out = np.empty((1 << r.shape[0], 2), dtype=np.uint64)
+    _lib.or_eq_table_msb(_p(r), C.c_size_t(r.shape[0]), _p(out))
+    return out
+
+
+def interpolate_eval(vals: np.ndarray, x) -> Tuple[int, int]:
+    vals = _u64(vals).reshape(-1, 2)
+    xx, o = (C.c_uint64 * 2)(*x), (C.c_uint64 * 2)()
+    _lib.or_interpolate_eval(_p(vals), C.c_size_t(vals.shape[0]), xx, o)
+    return (int(o[0]), int(o[1]))
+
+
+def eval_mle_ext(v: np.ndarray, r: np.ndarray) -> Tuple[int, int]:
+    """mle.rs:82-86."""
+    eq = eq_table_msb(r)
+    acc = (0, 0)
+    for a, e in zip(_u64(v).reshape(-1, 2), eq):
+        acc = fp2_add(acc, fp2_mul((int(e[0]), int(e[1])), (int(a[0]), int(a[1]))))
+    return acc
+
+
+def eval_mle_base(v: np.ndarray, r: np.ndarray) -> Tuple[int, int]:
+    """mle.rs:76-80."""
+    eq = eq_table_msb(r)
+    acc = (0, 0)
+    for a, e in zip(_u64(v), eq):
+        acc = fp2_add(acc, fp2_mul_base((int(e[0]), int(e[1])), int(a)))
+    return acc
+
+
+def fold_rows_i8(m: np.ndarray, w: np.ndarray) -> np.ndarray:
+    m = np.ascontiguousarray(m, dtype=np.int8)
+    w = _u64(w)
+    out = np.empty((m.shape[1], 2), dtype=np.uint64)
+    _lib.or_fold_rows_i8(_p(m), C.c_size_t(m.shape[0]), C.c_size_t(m.shape[1]), _p(w), _p(out))
+    return out
+
+
+def fold_cols_i8(m: np.ndarray, c: np.ndarray) -> np.ndarray:
+    m = np.ascontiguousarray(m, dtype=np.int8)
+    c = _u64(c)
+    out = np.empty((m.shape[0], 2), dtype=np.uint64)
+    _lib.or_fold_cols_i8(_p(m), C.c_size_t(m.shape[0]), C.c_size_t(m.shape[1]), _p(c), _p(out))
+    return out
+
+
+POLY_PROD, POLY_ZC, POLY_LOGUP_Q, POLY_LOGUP_T = 0, 1, 2, 3
+
+
+def poly_eval(poly: int, vals, coefs=None) -> Tuple[int, int]:
+    vals = _u64(vals).reshape(-1, 2)
+    o = (C.c_uint64 * 2)()
+    cf = _u64(coefs) if coefs is not None else None
+    _lib.or_poly_eval(C.c_int(poly), _p(vals), C.c_size_t(vals.shape[0]), _p(cf), o)
+    return (int(o[0]), int(o[1]))
+
+
+def sc_round(poly: int, tables: np.ndarray, degree: int, coefs=None, eval_one: bool = True) -> np.ndarray:
+    """tables: (k, len, 2); returns (degree + 1, 2)."""
+    tables = _u64(tables)
+    k, ln = tables.shape[0], tables.shape[1]
+    out = np.zeros((degree + 1, 2), dtype=np.uint64)
+    cf = _u64(coefs) if coefs is not None else None
+    _lib.or_sc_round(C.c_int(poly), _p(tables), C.c_size_t(k), C.c_size_t(ln), C.c_size_t(degree), _p(cf), C.c_int(1 if eval_one else 0), _p(out))
+    return out
+
+
+def cfs_round(coeffs: np.ndarray, n_vars: int, degree: int, j: int, prev: np.ndarray) -> np.ndarray:
+    coeffs = _u64(coeffs)
+    prev = _u64(prev).reshape(-1, 2) if j else np.zeros((1, 2), dtype=np.uint64)
+    out = np.empty((degree + 1, 2), dtype=np.uint64)
+    _lib.or_cfs_round(_p(coeffs), C.c_size_t(n_vars), C.c_size_t(degree), C.c_size_t(j), _p(prev), _p(out))
+    return out
+
+
+def cfs_total(coeffs: np.ndarray, n_vars: int, degree: int) -> Tuple[int, int]:
+    coeffs, o = _u64(coeffs), (C.c_uint64 * 2)()
+    _lib.or_cfs_total(_p(coeffs), C.c_size_t(n_vars), C.c_size_t(degree), o)
+    return (int(o[0]), int(o[1]))
+
+
+def cfs_eval(coeffs: np.ndarray, n_vars: int, degree: int, rho: np.ndarray) -> Tuple[int, int]:
+    coeffs, rho, o = _u64(coeffs), _u64(rho), (C.c_uint64 * 2)()
+    _lib.or_cfs_eval(_p(coeffs), C.c_size_t(n_vars), C.c_size_t(degree), _p(rho), o)
+    return (int(o[0]), int(o[1]))
+
+
+@dataclass
+class ScOutput:
+    rounds: np.ndarray      # (n, degree+1, 2) unmasked
+    masked: np.ndarray      # (n, degree+1, 2) what the transcript absorbed
+    challenges: np.ndarray  # (n, 2)
+    finals: np.ndarray      # (k, 2)
+
+
+def sc_prove(poly: int, tables: np.ndarray, degree: int, tr: Transcript, coefs=None, mask: Optional[np.ndarray] = None,
+             mask_c=None, mask_vars: Optional[int] = None, recover_one: bool = False, claim=None) -> ScOutput:
+    """sumcheck/rounds.rs:33-48 driver (with sumcheck.rs:282-299 masking when `mask` is given)."""
+    tables = _u64(tables).copy()
+    k, ln = tables.shape[0], tables.shape[1]
+    n = ln.bit_length() - 1
+    w = degree + 1
+    rounds = np.zeros((max(n, 1), w, 2), dtype=np.uint64)
+    masked = np.zeros((max(n, 1), w, 2), dtype=np.uint64)
+    chal = np.zeros((max(n, 1), 2), dtype=np.uint64)
+    finals = np.zeros((k, 2), dtype=np.uint64)
+    cf = _u64(coefs) if coefs is not None else None
+    mk = _u64(mask) if mask is not None else None
+    mc = (C.c_uint64 * 2)(*(mask_c if mask_c is not None else (0, 0)))
+    cl = (C.c_uint64 * 2)(*claim) if claim is not None else None
+    _lib.or_sc_prove(C.c_int(poly), _p(tables), C.c_size_t(k), C.c_size_t(n), C.c_size_t(degree), _p(cf), _p(mk), mc,
+                     C.c_size_t(mask_vars if mask_vars is not None else n), C.c_int(1 if recover_one else 0), cl, C.byref(tr._t),
+                     _p(rounds), _p(masked), _p(chal), _p(finals))
+    return ScOutput(rounds[:n], masked[:n], chal[:n], finals)
+
+
+def extension_round(poly: int, finals: np.ndarray, exts: np.ndarray, degree: int, coefs=None) -> np.ndarray:
+    """sumcheck.rs:302-314: s_k(X) = poly((1 - X) fin_t + X ext_t) at X = 0..=degree."""
+    out = np.empty((degree + 1, 2), dtype=np.uint64)
+    for x in range(degree + 1):
+        v = [fp2_add(tuple(map(int, f)), fp2_mul((x, 0), fp2_sub(tuple(map(int, e)), tuple(map(int, f))))) for f, e in zip(finals, exts)]
+        out[x] = poly_eval(poly, np.array(v, dtype=np.uint64), coefs)
+    return out
+
+
+def sc_verify(claimed, degree: int, n_rounds: int, rounds: Sequence[np.ndarray], tr: Transcript):
+    """sumcheck.rs:140-165.  Returns ((final claim, challenges), None) or (None, error text)."""
+    if len(rounds) != n_rounds:
+        return None, f"sumcheck: expected {n_rounds} rounds, got {len(rounds)}"
+    claim, chal = tuple(claimed), []
+    for j, s in enumerate(rounds):
+        s = _u64(s).reshape(-1, 2)
+        if s.shape[0] != degree + 1:
+            return None, f"sumcheck round {j}: expected degree {degree}, got {s.shape[0]} values"
+        if fp2_add(tuple(map(int, s[0])), tuple(map(int, s[1]))) != claim:
+            return None, f"sumcheck round {j}: s(0) + s(1) != claim"
+        tr.absorb_fp2(b"sc-round", s)
+        r = tr.challenge_fp2()
+        chal.append(r)
+        claim = interpolate_eval(s, r)
+    return (claim, chal), None
+
+
+# ----------------------------------------------------------------------------- logup
+def logup_histogram(idx: np.ndarray, table_len: int) -> np.ndarray:
+    idx = np.ascontiguousarray(idx, dtype=np.int32)
+    out = np.empty(table_len, dtype=np.uint64)
+    _lib.or_logup_histogram(_p(idx), C.c_size_t(idx.size), C.c_size_t(table_len), _p(out))
+    return out
+
+
+def logup_helpers(idx, outv, alpha, beta, tag, idx_off: int = 0) -> np.ndarray:
+    idx, outv = np.ascontiguousarray(idx, np.int32), np.ascontiguousarray(outv, np.int32)
+    h = np.empty((idx.size, 2), dtype=np.uint64)
+    _lib.or_logup_helpers(_p(idx), _p(outv), C.c_size_t(idx.size), (C.c_uint64 * 2)(*alpha), (C.c_uint64 * 2)(*beta),
+                          (C.c_uint64 * 2)(*tag), C.c_int64(idx_off), _p(h))
+    return h
+
+
+def logup_table_helper(table_out, mult, alpha, beta, tag) -> np.ndarray:
+    table_out, mult = np.ascontiguousarray(table_out, np.int32), _u64(mult)
+    ht = np.empty((table_out.size, 2), dtype=np.uint64)
+    _lib.or_logup_table_helper(_p(table_out), _p(mult), C.c_size_t(table_out.size), (C.c_uint64 * 2)(*alpha),
+                               (C.c_uint64 * 2)(*beta), (C.c_uint64 * 2)(*tag), _p(ht))
+    return ht
+
+
+# ----------------------------------------------------------------------------- the hiding commitment and its opening
+@dataclass
+class PcsParams:
+    log_cols: int
+    inv_rate: int
+    num_col_checks: int
+
+    @property
+    def cols(self) -> int:
+        return 1 << self.log_cols
+
+    @property
+    def enc_cols(self) -> int:
+        return self.cols * self.inv_rate
+
+
+@dataclass
+class CommittedZk:
+    """pcs.rs:607-620 (CommittedZk) with a host store."""
+    params: PcsParams
+    rows: int
+    q: int
+    data: np.ndarray       # rows*n
+    pads: np.ndarray       # rows*q
+    salts: np.ndarray      # nn x 32
+    encoded: np.ndarray    # rows*nn
+    leaves: np.ndarray     # nn x 32, unsalted
+    levels: np.ndarray     # (2nn-1) x 32
+    mask_rows: List[int] = field(default_factory=list)
+    prox_mask_row: Optional[int] = None
+
+    @property
+    def root(self) -> bytes:
+        return bytes(self.levels[-1])
+
+
+def commit_zk(params: PcsParams, data: np.ndarray, max_log: int, q: int, rng: ZkRng, tag: HashTag, coset: int = 7) -> CommittedZk:
+    """pcs.rs:782-817: pads (rows*q) then salts (nn) drawn in that order, then encode, hash, salt, tree."""
+    data = _u64(data)
+    n, nn = params.cols, params.enc_cols
+    rows = data.size // n
+    pads = rng.fp_vec(rows * q)
+    salts = rng.salts(nn)
+    pows = coset_powers(coset, nn)
+    enc = encode_rows_zk(data, rows, n, pads, q, pows, max_log)
+    leaves = hash_columns(enc, rows, nn, tag.column)
+    levels = merkle_build(salt_leaves(leaves, salts, tag.leaf), tag.node)
+    return CommittedZk(params, rows, q, data, pads, salts, enc, leaves, levels)
+
+
+@dataclass
+class ZPart:
+    offset: int
+    log_size: int
+    coef: Tuple[int, int]
+    point: np.ndarray  # (m, 2), possibly empty
+
+
+@dataclass
+class ZClaim:
+    parts: List[ZPart]
+    value: Tuple[int, int]
+
+
+def _zpart_weights(p: ZPart, rows: int, log_cols: int):
+    """pcs.rs:851-891."""
+    n = 1 << log_cols
+    row_w = [(0, 0)] * rows
+    ls = p.log_size
+    pt = _u64(p.point).reshape(-1, 2)
+    if pt.shape[0] == 0:
+        if ls >= log_cols:
+            r0 = p.offset // n
+            for i in range(1 << (ls - log_cols)):
+                row_w[r0 + i] = fp2_add(row_w[r0 + i], p.coef)
+            key = (b"", 0, n)
+        else:
+            r0, c0 = p.offset // n, p.offset % n
+            row_w[r0] = fp2_add(row_w[r0], p.coef)
+            key = (b"", c0, 1 << ls)
+    else:
+        assert pt.shape[0] == ls
+        if ls >= log_cols:
+            lr = ls - log_cols
+            r0 = p.offset // n
+            eq_r = eq_table_msb(pt[:lr])
+            for i, e in enumerate(eq_r):
+                row_w[r0 + i] = fp2_add(row_w[r0 + i], fp2_mul(p.coef, (int(e[0]), int(e[1]))))
+            key = (pt[lr:].tobytes(), 0, n)
+        else:
+            r0, c0 = p.offset // n, p.offset % n
+            row_w[r0] = fp2_add(row_w[r0], p.coef)
+            key = (pt.tobytes(), c0, 1 << ls)
+    return row_w, key
+
+
+def group_zclaims(claims: Sequence[ZClaim], rows: int, log_cols: int):
+    """pcs.rs:926-948: groups in first-seen order of the column key; returns [(key, [(row_w, value)])]."""
+    keys, groups = [], []
+    for c in claims:
+        rw, key = _zpart_weights(c.parts[0], rows, log_cols)
+        for p in c.parts[1:]:
+            rw2, key2 = _zpart_weights(p, rows, log_cols)
+            assert key2 == key
+            rw = [fp2_add(a, b) for a, b in zip(rw, rw2)]
+        if key in keys:
+            groups[keys.index(key)][1].append((rw, c.value))
+        else:
+            keys.append(key)
+            groups.append((key, [(rw, c.value)]))
+    return groups
+
+
+def zk_rhos(groups, rows: int, tr: Transcript) -> np.ndarray:
+    """pcs.rs:952-973: lambdas per group, then `rows` proximity challenges.  Returns (G+1, rows, 2)."""
+    out = np.zeros((len(groups) + 1, rows, 2), dtype=np.uint64)
+    for g, (_, members) in enumerate(groups):
+        lambdas = tr.challenge_fp2_vec(len(members))
+        rho = [(0, 0)] * rows
+        for (rw, _val), lam in zip(members, lambdas):
+            lam = (int(lam[0]), int(lam[1]))
+            for i in range(rows):
+                if not fp2_is_zero(rw[i]):
+                    rho[i] = fp2_add(rho[i], fp2_mul(lam, rw[i]))
+        out[g] = np.array(rho, dtype=np.uint64)
+    out[-1] = tr.challenge_fp2_vec(rows)
+    return out
+
+
+@dataclass
+class OpeningZk:
+    group_vecs: np.ndarray                        # (G, n+q, 2)
+    prox_vec: np.ndarray                          # (n+q, 2)
+    columns: List[Tuple[int, np.ndarray, bytes, List[bytes]]]
+
+    def to_bytes(self) -> bytes:
+        """pcs.rs:638-657 (OpeningZk::write_bytes)."""
+        out = [self.group_vecs.tobytes(), self.prox_vec.tobytes()]
+        for j, col, salt, path in self.columns:
+            out.append(int(j).to_bytes(8, "little") + _u64(col).tobytes() + salt + b"".join(path))
+        return b"".join(out)
+
+
+def open_zk(cmz: CommittedZk, claims: Sequence[ZClaim], tr: Transcript, fold=None, columns=None) -> OpeningZk:
+    """pcs.rs:1040-1069.  `fold(rhos) -> (G+1, n+q, 2)` and `columns(idx) -> (len(idx), rows)` default to the
+    host store; a device store under test is plugged in through them."""
+    p, rows, q = cmz.params, cmz.rows, cmz.q
+    n, nn = p.cols, p.enc_cols
+    groups = group_zclaims(claims, rows, p.log_cols)
+    rhos = zk_rhos(groups, rows, tr)
+    if fold is None:
+        msg = fold_rows(cmz.data, rows, n, n, 1, rhos)
+        padf = fold_rows(cmz.pads, rows, q, q, 1, rhos)
+        vecs = np.concatenate([msg, padf], axis=1)
+    else:
+        vecs = fold(rhos)
+    for v in vecs[:-1]:
+        tr.absorb_fp2(b"pcs-vec", v)
+    tr.absorb_fp2(b"pcs-prox", vecs[-1])
+    idx = tr.challenge_indices(p.num_col_checks, nn)
+    cols = gather_columns(cmz.encoded, rows, nn, idx) if columns is None else columns(idx)
+    out = [(int(j), cols[c], bytes(cmz.salts[int(j)]), merkle_path(cmz.levels, nn, int(j))) for c, j in enumerate(idx)]
+    return OpeningZk(vecs[:-1], vecs[-1], out)

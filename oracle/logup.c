@@ -1,0 +1,58 @@
+/*
+ * TEST INFRASTRUCTURE, NOT PRODUCT CODE.
+ * CPU restatement of the reference's LogUp helper arithmetic
+ * (hashline/src/private_block/protocol.rs:993-1011 `inverses`, :1928-1933
+ * `table_helper`; accuracy_act.rs:55-117 `histogram`, `query_values`,
+ * `denominators`) for a single-group lookup of (index, output) pairs:
+ *
+ *   query tuple   q_i = (idx_i + idx_off) + beta * out_i + tag
+ *   helper        h_i = 1 / (alpha - q_i)
+ *   table tuple   t_v = v + beta * table_out[v] + tag        (v = 0 .. table_len-1)
+ *   table helper  h_t[v] = mult[v] / (alpha - t_v)
+ *
+ * All sums are formed in the field (Fp2::from_i64 of each term), never through
+ * wrapping signed arithmetic, as accuracy_act.rs:91-99 requires.
+ */
+#include "hl_oracle.h"
+#include <stdlib.h>
+#include <string.h>
+
+static inline fp2_t from_i64(int64_t v) { return fp2_new(fp_from_i64(v), 0); }
+
+/* accuracy_act.rs:55-73: every query counted (padding included) */
+void or_logup_histogram(const int32_t *idx, size_t nq, size_t table_len, uint64_t *mult) {
+    memset(mult, 0, table_len * 8);
+    for (size_t i = 0; i < nq; i++) mult[(size_t)idx[i]]++;
+}
+
+/* protocol.rs:993-1011: denominators inverted in chunks of 2^14 by Montgomery's
+ * trick (field.rs:212-227); inverses are unique, so chunking moves no word. */
+void or_logup_helpers(const int32_t *idx, const int32_t *outv, size_t nq, const uint64_t alpha[2],
+                      const uint64_t beta[2], const uint64_t gamma_tag[2], int64_t idx_off, uint64_t *h) {
+    fp2_t a = fp2_new(alpha[0], alpha[1]), b = fp2_new(beta[0], beta[1]), tag = fp2_new(gamma_tag[0], gamma_tag[1]);
+    fp2_t *den = (fp2_t *)h;
+    const size_t CH = (size_t)1 << 14;
+    size_t nch = (nq + CH - 1) / CH;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (size_t c = 0; c < nch; c++) {
+        size_t lo = c * CH, hi = lo + CH < nq ? lo + CH : nq;
+        for (size_t i = lo; i < hi; i++) {
+            fp2_t q = fp2_add(fp2_add(fp2_add(from_i64(idx[i]), from_i64(idx_off)), fp2_mul(b, from_i64(outv[i]))), tag);
+            den[i] = fp2_sub(a, q);
+        }
+        or_batch_inverse2((uint64_t *)(den + lo), hi - lo);
+    }
+}
+
+/* protocol.rs:1928-1933 with the table tuple of accuracy_act.rs:28-31 */
+void or_logup_table_helper(const int32_t *table_out, const uint64_t *mult, size_t table_len, const uint64_t alpha[2],
+                           const uint64_t beta[2], const uint64_t gamma_tag[2], uint64_t *ht) {
+    fp2_t a = fp2_new(alpha[0], alpha[1]), b = fp2_new(beta[0], beta[1]), tag = fp2_new(gamma_tag[0], gamma_tag[1]);
+    fp2_t *den = (fp2_t *)ht;
+    for (size_t v = 0; v < table_len; v++) {
+        fp2_t t = fp2_add(fp2_add(from_i64((int64_t)v), fp2_mul(b, from_i64(table_out[v]))), tag);
+        den[v] = fp2_sub(a, t);
+    }
+    or_batch_inverse2(ht, table_len);
+    for (size_t v = 0; v < table_len; v++) den[v] = fp2_mul_base(den[v], fp_new(mult[v]));
+}

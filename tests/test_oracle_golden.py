@@ -1,0 +1,470 @@
+"""Pins the CPU oracle against the reference's own golden data (no GPU needed).
+
+Sources of the fixtures: ``tests/golden/make_golden.py``.  Record grammars:
+``zkp-core/tests/lean_l5_export.rs`` and ``lean_l6_export.rs`` of the reference;
+encode vectors: ``zkp-core/src/pcs/encode_conformance_tests.rs``.
+"""
+import hashlib
+import json
+import os
+
+import numpy as np
+import pytest
+
+P = 0xFFFFFFFF00000001
+M64 = (1 << 64) - 1
+
+
+def _records(path):
+    with open(path) as f:
+        for line in f:
+            if line.startswith("#") or not line.strip():
+                continue
+            yield line.rstrip("\n").split(" ")
+
+
+@pytest.fixture(scope="module")
+def l5(golden_dir):
+    return list(_records(os.path.join(golden_dir, "l5_corpus.txt")))
+
+
+@pytest.fixture(scope="module")
+def l6(golden_dir):
+    return list(_records(os.path.join(golden_dir, "l6_corpus.txt")))
+
+
+def unhex(s):
+    return b"" if s == "-" else bytes.fromhex(s)
+
+
+def gen_bytes(seed, n):
+    """`gen:<seed>:<len>` of lean_l5_export.rs:51-53."""
+    i = np.arange(n, dtype=np.uint64)
+    with np.errstate(over="ignore"):
+        v = i * np.uint64(0x9E3779B97F4A7C15) + np.uint64((seed * 0xD1B54A32D192ED03) & M64)
+    return (v >> np.uint64(56)).astype(np.uint8).tobytes()
+
+
+def gen_fp2(n):
+    """`fgen:<n>` of lean_l5_export.rs:56-58 (Fp::new of each word)."""
+    i = np.arange(n, dtype=np.uint64)
+    with np.errstate(over="ignore"):
+        a = i * np.uint64(0x9E3779B97F4A7C15)
+    a = np.where(a >= np.uint64(P), a - np.uint64(P), a)
+    b = i ^ np.uint64(0xDEADBEEF)
+    return np.stack([a, b], axis=1).astype(np.uint64)
+
+
+def data_spec(s):
+    if s.startswith("gen:"):
+        _, seed, n = s.split(":")
+        return gen_bytes(int(seed), int(n))
+    if s.startswith("h:"):
+        return bytes.fromhex(s[2:])
+    raise ValueError(s)
+
+
+def fp2v(s):
+    if s == "-":
+        return np.zeros((0, 2), dtype=np.uint64)
+    return np.array([int(x) for x in s.split(",")], dtype=np.uint64).reshape(-1, 2)
+
+
+def fpv(s):
+    if s == "-":
+        return np.zeros(0, dtype=np.uint64)
+    return np.array([int(x) for x in s.split(",")], dtype=np.uint64)
+
+
+def f2(s):
+    a, b = s.split(",")
+    return (int(a), int(b))
+
+
+# --------------------------------------------------------------------------- L5: field
+def test_l5_field_records(oracle, l5):
+    o, n = oracle, 0
+    for r in l5:
+        if r[0] == "FP":
+            op, a = r[1], [int(x) for x in r[2:]]
+            got = {
+                "add": lambda: o.fp_add(a[0], a[1]), "sub": lambda: o.fp_sub(a[0], a[1]), "mul": lambda: o.fp_mul(a[0], a[1]),
+                "neg": lambda: o.fp_neg(a[0]), "inv": lambda: o.fp_inv(a[0]), "pow": lambda: o.fp_pow(a[0], a[1]),
+                "new": lambda: o.fp_new(a[0]), "u128": lambda: o.fp_from_u128((a[0] << 64) | a[1]),
+            }[op]()
+            assert got == a[-1], r
+            n += 1
+        elif r[0] == "F2":
+            op, a = r[1], [int(x) for x in r[2:]]
+            if op == "add": got, want = o.fp2_add(a[0:2], a[2:4]), a[4:6]
+            elif op == "sub": got, want = o.fp2_sub(a[0:2], a[2:4]), a[4:6]
+            elif op == "mul": got, want = o.fp2_mul(a[0:2], a[2:4]), a[4:6]
+            elif op == "neg": got, want = o.fp2_neg(a[0:2]), a[2:4]
+            elif op == "mulbase": got, want = o.fp2_mul_base(a[0:2], a[2]), a[3:5]
+            elif op == "inv": got, want = o.fp2_inv(a[0:2]), a[2:4]
+            else: raise AssertionError(op)
+            assert list(got) == want, r
+            n += 1
+        elif r[0] == "BY":
+            if r[1] == "fp":
+                assert int(r[2]).to_bytes(8, "little").hex() == r[3]
+            elif r[1] == "fp2":
+                assert (int(r[2]).to_bytes(8, "little") + int(r[3]).to_bytes(8, "little")).hex() == r[4]
+            elif r[1] == "fp2from":
+                b = bytes.fromhex(r[2])
+                assert o.fp_new(int.from_bytes(b[:8], "little")) == int(r[3]) and o.fp_new(int.from_bytes(b[8:], "little")) == int(r[4])
+            n += 1
+    assert n > 4000
+    assert o.two_adic_root(32) == 1753635133440165772  # field.rs:339
+
+
+# --------------------------------------------------------------------------- L5: BLAKE3
+def test_l5_blake3_records_and_python_module(oracle, l5):
+    n = 0
+    for r in l5:
+        if r[0] != "B3":
+            continue
+        data = data_spec(r[3])
+        if r[1] == "hash":
+            got = oracle.blake3(data)
+        elif r[1] == "keyed":
+            got = oracle.blake3(data, bytes.fromhex(r[2]))
+        else:
+            got = oracle.derive_key(bytes.fromhex(r[2]), data)
+        assert got.hex() == r[4], r[:4]
+        n += 1
+    assert n == 119
+    # a second, independent check where the `blake3` wheel is importable (XOF lengths included)
+    b3 = pytest.importorskip("blake3")
+    key = bytes(range(32))
+    for ln in (0, 1, 63, 64, 65, 1023, 1024, 1025, 2048, 3073, 7000, 20032, 32768):
+        d = gen_bytes(ln + 3, ln)
+        assert oracle.blake3(d) == b3.blake3(d).digest()
+        assert oracle.blake3(d, key) == b3.blake3(d, key=key).digest()
+        assert oracle.blake3(d, None, 8192) == b3.blake3(d).digest(length=8192)
+
+
+def test_hash_tag_key_pins(oracle):
+    """hashtag.rs:188-198."""
+    g = oracle.HashTag.for_profile("hashline-zk-mr1/private-block-rung-g-t24-dev/1")
+    assert g.transcript.hex() == "51b7d0b0171d54b5bb45fd42c3f9369cad87894b625e0569b89fac0036d20dbe"
+    assert g.column.hex() == "2295498fd6fd5e41320da717e9da89462e5c90a5b3b2d72ac496bcc157c2cd2c"
+    assert g.leaf.hex() == "fe211417895c73c4a70430cb9bfb7081289ec7532f2716d2a86f609b0de54032"
+    assert g.node.hex() == "8c4d2cfe7b8528d350f20dece1250c8d81596eb25d26bffda1247238f0f71fcc"
+    m = oracle.HashTag.for_profile("hashline-zk-mr1/private-block-m125/1")
+    assert m.transcript.hex() == "125f9b4d44ac3c46712a35419cdeda6c1428db443ccaf58da67f35b15b37291c"
+    assert m.column.hex() == "d5fc391cc58eed85631b4c3dabc7d377477eb1a0a725aeccaec0f4d10061b135"
+    assert m.leaf.hex() == "1dc6f7146ad501ede6d90b3071da2f3251d38137303ffcc0a6a48b7f89effe83"
+    assert m.node.hex() == "798eb64ff187f6f3e8e889ac4c4742607ac71a71fa09e2944a0ecc5e8a42026b"
+
+
+# --------------------------------------------------------------------------- L5: transcript
+def test_l5_transcript_replay(oracle, l5):
+    t, n = None, 0
+    for r in l5:
+        k = r[0]
+        if k == "TR":
+            t = oracle.Transcript(unhex(r[2])) if r[1] == "new" else oracle.Transcript(unhex(r[2]), bytes.fromhex(r[3]))
+            continue
+        if k == "TS":
+            assert t.state.hex() == r[1]
+        elif k == "TA":
+            t.absorb(unhex(r[1]), data_spec(r[2]))
+            assert t.state.hex() == r[3], r[:3]
+        elif k == "TU":
+            t.absorb_u64(unhex(r[1]), int(r[2]))
+            assert t.state.hex() == r[3]
+        elif k == "TF":
+            t.absorb_fp(unhex(r[1]), fpv(r[2]))
+            assert t.state.hex() == r[3]
+        elif k == "TF2":
+            v = gen_fp2(int(r[2][5:])) if r[2].startswith("fgen:") else fp2v(r[2][2:])
+            t.absorb_fp2(unhex(r[1]), v)
+            assert t.state.hex() == r[3], r[:3]
+        elif k == "TCF":
+            assert t.challenge_fp() == int(r[1]) and t.state.hex() == r[2]
+        elif k == "TCF2":
+            assert t.challenge_fp2() == (int(r[1]), int(r[2])) and t.state.hex() == r[3]
+        elif k == "TCV":
+            v = t.challenge_fp2_vec(int(r[1]))
+            assert (v == fp2v(r[2])).all() and t.state.hex() == r[3]
+        elif k == "TCI":
+            idx = t.challenge_indices(int(r[1]), int(r[2]))
+            assert (idx == fpv(r[3])).all() and t.state.hex() == r[4]
+        else:
+            continue
+        n += 1
+    assert n > 220
+
+
+# --------------------------------------------------------------------------- L5: Merkle
+def test_l5_merkle_records(oracle, l5):
+    tags, n = {}, 0
+    for r in l5:
+        if r[0] == "MTAG":
+            tags[r[1]] = [None if x == "-" else bytes.fromhex(x) for x in r[2:6]]
+    assert tags["legacy"] == [None] * 4
+    for name, prof in (("rungg", "hashline-zk-mr1/private-block-rung-g-t24-dev/1"), ("m125", "hashline-zk-mr1/private-block-m125/1")):
+        t = oracle.HashTag.for_profile(prof)
+        assert tags[name] == [t.transcript, t.column, t.leaf, t.node]
+    for r in l5:
+        if r[0] == "MB":
+            nl = int(r[2])
+            leaves = np.frombuffer(b"".join(oracle.blake3(i.to_bytes(8, "little")) for i in range(nl)), dtype=np.uint8).reshape(nl, 32)
+            levels = oracle.merkle_build(leaves, tags[r[1]][3])
+            assert bytes(levels[-1]).hex() == r[3]
+            n += 1
+        elif r[0] == "MP":
+            path = [bytes.fromhex(x) for x in r[5].split(",")] if r[5] != "-" else []
+            ok = oracle.merkle_verify_path(bytes.fromhex(r[2]), int(r[3]), bytes.fromhex(r[4]), path, tags[r[1]][3])
+            assert int(ok) == int(r[6])
+            n += 1
+        elif r[0] == "MLEAF":
+            a, b = np.frombuffer(bytes.fromhex(r[2]), np.uint8).reshape(1, 32), np.frombuffer(bytes.fromhex(r[3]), np.uint8).reshape(1, 32)
+            assert bytes(oracle.salt_leaves(a, b, tags[r[1]][2])[0]).hex() == r[4]
+            n += 1
+        elif r[0] == "MNODE":
+            assert oracle.blake3(bytes.fromhex(r[2]) + bytes.fromhex(r[3]), tags[r[1]][3]).hex() == r[4]
+            n += 1
+        elif r[0] == "MCOL":
+            col = fpv(r[2])
+            assert bytes(oracle.hash_columns(col, col.size, 1, tags[r[1]][1])[0]).hex() == r[3]
+            n += 1
+    assert n == 27 + 528 + 3 + 3 + 12
+
+
+# --------------------------------------------------------------------------- L5: whole seeded tagged openings
+def test_l5_whole_pcs_openings(oracle, l5):
+    """lean_l5_export.rs:342-427: commit_zk_owned_with_tag + open_zk from ZkRng::new(seed, ..)."""
+    o = oracle
+    cases = {"rungg": ("hashline-zk-mr1/private-block-rung-g-t24-dev/1", 4, 4, 12, 31), "m125": ("hashline-zk-mr1/private-block-m125/1", 5, 2, 20, 32),
+             "legacy": (None, 4, 4, 12, 33)}
+    it = iter(l5)
+    done = 0
+    for r in it:
+        if r[0] != "PCS":
+            continue
+        name = r[1]
+        profile, log_cols, inv_rate, q, seed = cases[name]
+        tag = o.HashTag.for_profile(profile) if profile else o.HashTag.legacy()
+        p = o.PcsParams(log_cols, inv_rate, q)
+        n, nn, rows = p.cols, p.enc_cols, 3
+        rng = o.ZkRng(seed, b"lean-l5 pcs corpus")
+        d = np.array([o.fp_from_i64(((i * 37) % 256) - 128) for i in range(rows * n)], dtype=np.uint64)
+        for rr in (1, 2):
+            for j in range(n):
+                d[rr * n + j] = rng.fp()
+        cmz = o.commit_zk(p, d, log_cols + 4, q, rng, tag)
+        cmz.mask_rows, cmz.prox_mask_row = [1], 2
+        assert cmz.root.hex() == r[3], name
+        assert (int(r[4]), int(r[5]), int(r[6])) == (rows, nn, q)
+        pt = np.array([[3000 + i * 7 + 3, 3 + i * 11 + 5] for i in range(log_cols)], dtype=np.uint64)
+        e = (99991, 7)
+        vp, vr = o.eval_mle_base(d[0:n], pt), o.eval_mle_base(d[n:2 * n], pt)
+        one_e = o.fp2_sub((1, 0), e)
+        claims = [o.ZClaim([o.ZPart(0, log_cols, one_e, pt), o.ZPart(n, log_cols, e, pt)], o.fp2_add(o.fp2_mul(one_e, vp), o.fp2_mul(e, vr)))]
+        tr = o.Transcript(unhex(r[2]), tag.transcript)
+        tr.absorb(b"root", cmz.root)
+        op = o.open_zk(cmz, claims, tr)
+        ng = int(r[7])
+        assert op.group_vecs.shape[0] == ng == 1
+        for g in range(ng):
+            rec = next(it)
+            assert rec[0] == "PCSG" and (op.group_vecs[g] == fp2v(rec[1])).all()
+        rec = next(it)
+        assert rec[0] == "PCSP" and (op.prox_vec == fp2v(rec[1])).all()
+        for (j, col, salt, path) in op.columns:
+            rec = next(it)
+            assert rec[0] == "PCSC" and int(rec[1]) == j
+            assert (col == fpv(rec[2])).all() and salt.hex() == rec[3]
+            assert [x.hex() for x in path] == rec[4].split(",")
+        rec = next(it)
+        assert rec[0] == "PCSEND" and tr.state.hex() == rec[1]
+        done += 1
+    assert done == 3
+
+
+# --------------------------------------------------------------------------- encode conformance vectors
+def splitmix_fp(seed, n):
+    out, s = [], seed
+    for _ in range(n):
+        s = (s + 0x9E3779B97F4A7C15) & M64
+        z = s
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & M64
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & M64
+        out.append((z ^ (z >> 31)) % P)
+    return np.array(out, dtype=np.uint64)
+
+
+def vector_inputs(v):
+    """encode_conformance_tests.rs:49-84."""
+    n, q, kind = int(v["n"]), int(v["q_pad"]), v["name"].split("-", 1)[1]
+    msg, pad = np.zeros(n, dtype=np.uint64), np.zeros(q, dtype=np.uint64)
+    if kind == "zero_msg_seeded_pad":
+        pad = splitmix_fp(int(v["pad_seed"]), q)
+    elif kind == "delta0":
+        msg[0] = 1
+    elif kind == "delta_last":
+        msg[n - 1] = 1
+    elif kind == "seeded":
+        msg, pad = splitmix_fp(int(v["msg_seed"]), n), splitmix_fp(int(v["pad_seed"]), q)
+    return msg, pad
+
+
+def test_encode_conformance_vectors(oracle, golden_dir):
+    g = json.load(open(os.path.join(golden_dir, "encode_vectors.json")))
+    assert len(g["vectors"]) == 35
+    for v in g["vectors"]:
+        msg, pad = vector_inputs(v)
+        assert hashlib.sha256(msg.tobytes()).hexdigest() == v["msg_sha256"]
+        assert hashlib.sha256(pad.tobytes()).hexdigest() == v["pad_sha256"]
+        nn = int(v["nn"])
+        pows = oracle.coset_powers(7, nn)
+        for max_log in {nn.bit_length() - 1, 18}:
+            row = oracle.encode_row_zk(msg, pad, pows, max_log)
+            assert hashlib.sha256(row.tobytes()).hexdigest() == v["encoded_sha256"], (v["name"], max_log)
+        assert [int(x) for x in row[:8]] == v["encoded_first8"] and [int(x) for x in row[-8:]] == v["encoded_last8"]
+        for k, want in v["encoded_probes"].items():
+            assert int(row[int(k)]) == want
+        if v["name"] in g["full_rows"]:
+            assert [int(x) for x in row] == g["full_rows"][v["name"]]
+    bad = {c["sha256"] for e in g["negative_controls"] for c in e["controls"]}
+    good = {v["encoded_sha256"] for v in g["vectors"]}
+    assert len(bad) == 15 and not (bad & good)
+
+
+# --------------------------------------------------------------------------- L6: mle / cfs
+def test_l6_mle_and_cfs_records(oracle, l6):
+    o, n, mask = oracle, 0, None
+    zr = o.ZkRng(61, b"lean-l6 cfs corpus")
+    for r in l6:
+        k = r[0]
+        if k == "IE":
+            assert o.interpolate_eval(fp2v(r[1]), f2(r[2])) == f2(r[3])
+        elif k == "EQT":
+            pt = fp2v(r[1])
+            assert (o.eq_table(pt) == fp2v(r[2])).all() and (o.eq_table_msb(pt) == fp2v(r[3])).all()
+        elif k == "EQP":
+            pt, s = fp2v(r[1]), fp2v(r[2])
+            acc = (1, 0)  # mle.rs:62-72
+            for a, b in zip(pt, s):
+                a, b = tuple(map(int, a)), tuple(map(int, b))
+                t = o.fp2_add(o.fp2_mul(a, b), o.fp2_mul(o.fp2_sub((1, 0), a), o.fp2_sub((1, 0), b)))
+                acc = o.fp2_mul(acc, t)
+            assert acc == f2(r[3])
+        elif k == "MLX":
+            assert o.eval_mle_ext(fp2v(r[1]), fp2v(r[2])) == f2(r[3])
+        elif k == "MLB":
+            assert o.eval_mle_base(fpv(r[1]), fp2v(r[2])) == f2(r[3])
+        elif k == "CFSM":
+            nv, d = int(r[1]), int(r[2])
+            mask = (zr.fp2_vec(nv * d + 2), nv, d)  # CfsMask::random draws from the same stream in order
+            assert (mask[0] == fp2v(r[3])).all()
+            assert o.cfs_total(*mask) == f2(r[4])
+            rho = None
+        elif k == "CFSV":
+            rho = fp2v(r[1])
+            assert o.cfs_eval(mask[0], mask[1], mask[2], rho) == f2(r[2])
+        elif k == "CFSR":
+            j = int(r[1])
+            assert (o.cfs_round(mask[0], mask[1], mask[2], j, fp2v(r[2])) == fp2v(r[3])).all()
+        elif k == "MT":
+            fin, ext, rho_k = f2(r[1]), f2(r[2]), f2(r[3])
+            assert o.fp2_add(fin, o.fp2_mul(rho_k, o.fp2_sub(ext, fin))) == f2(r[4])
+        elif k == "EXR":
+            poly = {"prod": o.POLY_PROD, "zc": o.POLY_ZC}[r[1]]
+            assert (o.extension_round(poly, fp2v(r[3]), fp2v(r[4]), int(r[2])) == fp2v(r[5])).all()
+        else:
+            continue
+        n += 1
+    assert n > 300
+
+
+# --------------------------------------------------------------------------- L6: whole sumchecks
+def _blocks(l6):
+    cur = None
+    for r in l6:
+        if r[0] == "SCNEW":
+            if cur:
+                yield cur
+            cur = []
+        elif cur is not None and r[0].startswith("SC"):
+            cur.append(r)
+    if cur:
+        yield cur
+
+
+def test_l6_whole_sumchecks_prover_and_verifier(oracle, l6):
+    o = oracle
+    honest = verdicts = 0
+    for blk in _blocks(l6):
+        tables = np.stack([fp2v(r[1]) for r in blk if r[0] == "SCTAB"])
+        mask = next((r for r in blk if r[0] == "SCMASK"), None)
+        polyname = next(r[1] for r in blk if r[0] in ("SCFIN", "SCMFIN", "SCEXT", "SCXTERM"))
+        poly = {"prod": o.POLY_PROD, "zc": o.POLY_ZC}[polyname]
+        # every SC ... SCEND run in the block: the verifier's verdict and transcript state
+        runs, cur = [], None
+        for r in blk:
+            if r[0] == "SC":
+                cur = {"hdr": r, "pre": None, "rounds": []}
+            elif r[0] == "SCPRE":
+                cur["pre"] = f2(r[1])
+            elif r[0] == "SCR":
+                cur["rounds"].append(fp2v(r[1]))
+            elif r[0] == "SCEND":
+                cur["end"] = r
+                runs.append(cur)
+        for run in runs:
+            h = run["hdr"]
+            domain, key, deg, nr, claimed = unhex(h[2]), (None if h[3] == "-" else bytes.fromhex(h[3])), int(h[4]), int(h[5]), f2(h[6])
+            tv = o.Transcript(domain, key)
+            if run["pre"] is not None:
+                assert tv.challenge_fp2() == run["pre"]
+            res, err = o.sc_verify(claimed, deg, nr, run["rounds"], tv)
+            e = run["end"]
+            if e[1] == "ok":
+                assert res is not None and res[0] == f2(e[2])
+                assert (np.array(res[1], dtype=np.uint64).reshape(-1, 2) == fp2v(e[3])).all() and tv.state.hex() == e[4]
+            else:
+                assert res is None and err.encode().hex() == e[2] and tv.state.hex() == e[3]
+            verdicts += 1
+        # the honest run, re-PROVED by the oracle from the tables (the corpus's second copy of an
+        # extended run only replays the verifier on a tampered terminal: nothing to re-prove there)
+        if mask is not None and not any(r[0] == "SCUNM" for r in blk):
+            continue
+        run = runs[0]
+        h = run["hdr"]
+        domain, key, deg, nr = unhex(h[2]), (None if h[3] == "-" else bytes.fromhex(h[3])), int(h[4]), int(h[5])
+        n = tables.shape[1].bit_length() - 1
+        tp = o.Transcript(domain, key)
+        if mask is None:
+            out = o.sc_prove(poly, tables, deg, tp)
+            assert nr == n
+        else:
+            cc = tp.challenge_fp2()
+            assert cc == run["pre"]
+            mv, md, mco = int(mask[1]), int(mask[2]), fp2v(mask[3])
+            assert md == deg
+            out = o.sc_prove(poly, tables, deg, tp, mask=mco, mask_c=cc, mask_vars=mv)
+            unm = [fp2v(r[2]) for r in blk if r[0] == "SCUNM"]
+            assert len(unm) == n and all((out.rounds[j] == unm[j]).all() for j in range(n))
+        for j in range(n):
+            assert (out.masked[j] == run["rounds"][j]).all(), (h[1], j)
+        fin = next(r for r in blk if r[0] in ("SCFIN", "SCMFIN", "SCEXT"))
+        assert (out.finals == fp2v(fin[2])).all()
+        if fin[0] == "SCEXT":  # masked + one extension round (argument.rs private slot form)
+            exts = fp2v(fin[3])
+            sk = o.extension_round(poly, out.finals, exts, deg)
+            gk = o.cfs_round(mco, mv, md, n, out.challenges)
+            sk = np.array([o.fp2_add(tuple(map(int, s)), o.fp2_mul(cc, tuple(map(int, g)))) for s, g in zip(sk, gk)], dtype=np.uint64)
+            assert nr == n + 1 and (sk == run["rounds"][n]).all()
+            tp.absorb_fp2(b"sc-round", sk)
+            tp.challenge_fp2()
+        assert tp.state.hex() == run["end"][-1], h[1]
+        # s(1) recovery gives the same messages (sumcheck/rounds.rs:94-147)
+        if mask is None and n >= 1 and deg >= 1:
+            t2 = o.Transcript(domain, key)
+            out2 = o.sc_prove(poly, tables, deg, t2, recover_one=True)
+            assert (out2.rounds == out.rounds).all() and t2.state == tp.state
+        honest += 1
+    assert honest == 15 and verdicts >= 171
