@@ -1,0 +1,127 @@
+/*
+ * hl_b200 - the B200 (sm_100a) backend of the Hashline prover's data-parallel hot path,
+ * as a C-ABI shared library.
+ *
+ * The reference prover (Rust) reaches an accelerator through two seams:
+ *   zkp-core/src/pcs/backend.rs:30-100      trait EncodedStore, trait Backend
+ *   zkp-core/src/sumcheck/rounds.rs:22-28   trait SumcheckRounds
+ * and the adapter in hashline/src/gpu/mod.rs:687-859 plugs a device into them.  Every
+ * entry point below is what an `impl Backend / EncodedStore / SumcheckRounds` for this
+ * backend binds over FFI; each comment names the reference item it stands for.
+ * (paths are relative to the reference's ops/zkp-mvp/gpu-metal tree)
+ *
+ * Conventions
+ *  - Field elements are canonical Goldilocks words (uint64_t < p, p = 2^64 - 2^32 + 1);
+ *    an Fp2 is two consecutive words (c0, c1) (field.rs:139-203).  Digests are 32 bytes.
+ *  - Every pointer is HOST memory unless its name starts with d_.  Inputs are read during
+ *    the call only; outputs are complete when the call returns (the *_dev calls are
+ *    asynchronous on the context's stream and say so).
+ *  - Every call returns 0 (HL_B200_OK) or a negative HL_B200_ERR_*; hl_b200_last_error
+ *    gives the text.  A non-zero status is the seam's "decline" (backend.rs:66-71); there
+ *    is no CPU fallback inside the library and nothing aborts.
+ *  - Results are the reference CPU backend's bytes: the library draws no randomness and
+ *    touches no transcript except the replayable round batch of hl_b200_rounds_batched.
+ *  - A context serialises its calls with a mutex; use one context per host thread for
+ *    concurrent forks (run_fork.rs:1677-1779).
+ */
+#ifndef HL_B200_H
+#define HL_B200_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct hl_ctx hl_ctx;
+typedef struct hl_store hl_store;
+typedef struct hl_rounds hl_rounds;
+
+enum {
+    HL_B200_OK = 0,
+    HL_B200_ERR_ARG = -1,         /* a shape or pointer the call cannot take */
+    HL_B200_ERR_OOM = -2,         /* device allocation failed */
+    HL_B200_ERR_DEVICE = -3,      /* a CUDA call failed; see hl_b200_last_error */
+    HL_B200_ERR_TIMEOUT = -4,     /* a bounded device wait ran out */
+    HL_B200_ERR_MISMATCH = -5,    /* a self-check failed */
+    HL_B200_ERR_ZERO = -6,        /* zero denominator or zero challenge: "discard attempt" (protocol.rs:1059) */
+    HL_B200_ERR_UNSUPPORTED = -7  /* a size outside the kernels' range; the caller keeps its own path */
+};
+
+/* ---- context: hashline/src/gpu/mod.rs:25-58 (enabled, label), metal.rs:75-95 (lazy context) ---- */
+int hl_b200_init(int device, hl_ctx** out);
+void hl_b200_shutdown(hl_ctx* ctx);
+const char* hl_b200_label(hl_ctx* ctx);
+const char* hl_b200_last_error(hl_ctx* ctx);
+/* Run the context's work on the caller's CUDA stream (a cudaStream_t); NULL restores its own. */
+int hl_b200_set_stream(hl_ctx* ctx, void* cuda_stream);
+int hl_b200_sync(hl_ctx* ctx);
+/* Which encoder runs: 0 = radix-2 shared-memory stages (any n <= 2^14), 1 = the 16-point
+ * register passes when 2^8 <= n <= 2^14 (default).  Same words either way. */
+int hl_b200_set_encoder(hl_ctx* ctx, int fast);
+
+/* ---- field self-test: metal_probe_field (tests/zk60_metal_commit.rs:69-89), k_probe ----
+ * out3n[3i..3i+2] = (a_i + b_i, a_i - b_i, a_i * b_i) */
+int hl_b200_probe_field(hl_ctx* ctx, const uint64_t* a, const uint64_t* b, size_t n, uint64_t* out3n);
+
+/* ---- Backend::try_commit (pcs/backend.rs:79-82; CPU body pcs.rs:230-250) ----
+ * data: rows x 2^log_cols.  Systematic Reed-Solomon rows to nn = inv_rate 2^log_cols columns,
+ * column leaves (unkeyed BLAKE3 when key32 is NULL) into leaves32 (nn x 32 bytes).
+ * max_log is the caller's NttTables::max_log (ntt.rs:9-43); it must cover log2 nn and does
+ * not change any value.  The store keeps the encoding resident until hl_b200_store_free. */
+int hl_b200_commit(hl_ctx* ctx, uint32_t log_cols, uint32_t inv_rate, const uint64_t* data, size_t rows,
+                   uint32_t max_log, const uint8_t* key32, hl_store** store, uint8_t* leaves32);
+
+/* ---- Backend::try_commit_zk / try_commit_zk_keyed (pcs/backend.rs:84-99; CPU body
+ * pcs.rs:674-693, 782-817 and pcs/encode_buffer.rs:10-71) ----
+ * pads: rows x q, pows: nn coset powers.  Returns the UNSALTED leaves; the caller salts and
+ * builds the tree (or calls hl_b200_merkle).  The store keeps data, pads and encoding. */
+int hl_b200_commit_zk(hl_ctx* ctx, uint32_t log_cols, uint32_t inv_rate, const uint64_t* data, size_t rows,
+                      const uint64_t* pads, size_t q, const uint64_t* pows, uint32_t max_log, const uint8_t* key32,
+                      hl_store** store, uint8_t* leaves32);
+
+/* The same commitment for inputs that already live in device memory (the reference's
+ * device-buffer commitment, pcs.rs:801-803 / metal.rs:3105 resident rows).  Asynchronous on
+ * the context's stream; d_leaves32 (nn x 32 bytes, device) is ready when the stream reaches
+ * this point.  The store BORROWS d_data and d_pads: keep them alive until it is freed. */
+int hl_b200_commit_zk_dev(hl_ctx* ctx, uint32_t log_cols, uint32_t inv_rate, const uint64_t* d_data, size_t rows,
+                          const uint64_t* d_pads, size_t q, const uint64_t* d_pows, const uint8_t* key32,
+                          hl_store** store, uint8_t* d_leaves32);
+
+/* ---- salt_leaf_keyed + MerkleTree::build_keyed (pcs.rs:696-715, merkle.rs:48-81) ----
+ * levels_out: (2 nn - 1) x 32 bytes: the nn salted leaves, then each level up, the root last.
+ * salts32 NULL: the leaves are used as level 0 unchanged (the plain commitment's tree). */
+int hl_b200_merkle(hl_ctx* ctx, const uint8_t* leaves32, const uint8_t* salts32, size_t nn, const uint8_t* leaf_key32,
+                   const uint8_t* node_key32, uint8_t* levels_out);
+/* The same on the leaves a commit left on the device (no leaf round trip). */
+int hl_b200_store_merkle(hl_store* store, const uint8_t* salts32, const uint8_t* leaf_key32, const uint8_t* node_key32,
+                         uint8_t* levels_out);
+
+/* ---- EncodedStore::fold_rows / fold_rows_with_pads (pcs/backend.rs:33-59; CPU body
+ * pcs.rs:342-378, 976-1000) ----
+ * rhos: k x rows Fp2.  out: k vectors of n Fp2 (with_pads == 0) or n + q Fp2 (with_pads != 0,
+ * hiding stores only: the n message entries then rho^T pads). */
+int hl_b200_store_fold(hl_store* store, const uint64_t* rhos, size_t k, int with_pads, uint64_t* out);
+/* ---- EncodedStore::columns (pcs/backend.rs:37-39; pcs.rs:1055-1067) ----
+ * out: nidx x rows words, in the order of idx, duplicates repeated. */
+int hl_b200_store_columns(hl_store* store, const uint64_t* idx, size_t nidx, uint64_t* out);
+/* rows, n, nn, q of a store (q = 0 for the plain form) */
+int hl_b200_store_shape(hl_store* store, size_t* rows, size_t* n, size_t* nn, size_t* q);
+/* device address of the encoding (rows x nn words) and of the leaves; for device-side callers */
+const uint64_t* hl_b200_store_encoded_dev(hl_store* store);
+const uint8_t* hl_b200_store_leaves_dev(hl_store* store);
+void hl_b200_store_free(hl_store* store);
+
+/* ---- counters: GpuStats / dev_stats (hashline/src/gpu/mod.rs:890-908) ---- */
+typedef struct {
+    uint64_t commits, folds, gathers, merkles, round_batches;
+    uint64_t kernel_launches;   /* kernels this context has launched */
+    uint64_t bytes_h2d, bytes_d2h;
+    uint64_t declines;          /* calls that returned an error */
+} hl_stats;
+int hl_b200_stats(hl_ctx* ctx, hl_stats* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

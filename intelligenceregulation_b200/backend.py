@@ -1,0 +1,218 @@
+"""Host-side mirror of the prover's accelerator seam over the C ABI.
+
+The reference reaches a device through ``trait Backend`` / ``trait EncodedStore``
+(zkp-core/src/pcs/backend.rs:30-100) and hashline's adapter
+(hashline/src/gpu/mod.rs:687-859: ``backend()``, ``enabled()``, ``label()``, ``DevStore``).
+The names, argument meaning and error behaviour here follow those: a hook returns
+``None`` when the device declines (the error is counted and kept in ``declined``),
+and raises instead when ``HL_GPU_REQUIRED=1`` (mod.rs:76-102).  Arrays are numpy
+``uint64`` (canonical Goldilocks words; an Fp2 is two consecutive words).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import List, Optional, Tuple
+
+import numpy as np
+
+from . import _lib
+
+
+def _ptr(a) -> C.c_void_p:
+    if a is None:
+        return C.c_void_p(0)
+    if isinstance(a, (bytes, bytearray)):
+        return C.cast(C.create_string_buffer(bytes(a), len(a)), C.c_void_p)
+    if isinstance(a, int):
+        return C.c_void_p(a)
+    assert a.flags["C_CONTIGUOUS"]
+    return C.c_void_p(a.ctypes.data)
+
+
+def _u64(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.uint64)
+
+
+def required() -> bool:
+    """hashline/src/gpu/mod.rs:76-78."""
+    return os.environ.get("HL_GPU_REQUIRED") == "1"
+
+
+class DeviceError(RuntimeError):
+    def __init__(self, code: int, text: str):
+        super().__init__(f"hl_b200 error {code}: {text}")
+        self.code = code
+
+
+class Context:
+    """One device context (hashline/src/gpu/metal.rs:75-95 keeps one per process)."""
+
+    def __init__(self, device: int = 0):
+        self.lib = _lib.load()
+        h = C.c_void_p()
+        rc = self.lib.hl_b200_init(device, C.byref(h))
+        if rc != 0:
+            raise DeviceError(rc, "no usable CUDA device")
+        self.h = h
+        self.declines: List[Tuple[str, str]] = []
+
+    def close(self) -> None:
+        if self.h:
+            self.lib.hl_b200_shutdown(self.h)
+            self.h = None
+
+    def label(self) -> str:
+        return self.lib.hl_b200_label(self.h).decode()
+
+    def last_error(self) -> str:
+        return self.lib.hl_b200_last_error(self.h).decode()
+
+    def check(self, rc: int) -> None:
+        if rc != 0:
+            raise DeviceError(rc, self.last_error())
+
+    def declined(self, site: str, rc: int) -> None:
+        """mod.rs:80-94: log and count a decline; under HL_GPU_REQUIRED=1 a decline is fatal."""
+        text = self.last_error()
+        self.declines.append((site, text))
+        if required():
+            raise DeviceError(rc, f"{site}: {text} (HL_GPU_REQUIRED=1)")
+
+    def set_stream(self, cuda_stream: int) -> None:
+        self.check(self.lib.hl_b200_set_stream(self.h, C.c_void_p(cuda_stream)))
+
+    def set_encoder(self, fast: bool) -> None:
+        self.check(self.lib.hl_b200_set_encoder(self.h, 1 if fast else 0))
+
+    def sync(self) -> None:
+        self.check(self.lib.hl_b200_sync(self.h))
+
+    def stats(self) -> dict:
+        s = _lib.Stats()
+        self.check(self.lib.hl_b200_stats(self.h, C.byref(s)))
+        return {n: int(getattr(s, n)) for n, _ in s._fields_}
+
+    def probe_field(self, a, b) -> np.ndarray:
+        """metal_probe_field: (a+b, a-b, a*b) per pair, shape (n, 3)."""
+        a, b = _u64(a), _u64(b)
+        out = np.empty((a.size, 3), dtype=np.uint64)
+        self.check(self.lib.hl_b200_probe_field(self.h, _ptr(a), _ptr(b), a.size, _ptr(out)))
+        return out
+
+    def merkle(self, leaves: np.ndarray, salts: Optional[np.ndarray], leaf_key: Optional[bytes], node_key: Optional[bytes]) -> np.ndarray:
+        """salt_leaf_keyed + MerkleTree::build_keyed: all levels, (2 nn - 1, 32) bytes, root last."""
+        leaves = np.ascontiguousarray(leaves, dtype=np.uint8)
+        nn = leaves.shape[0]
+        out = np.empty((2 * nn - 1, 32), dtype=np.uint8)
+        s = np.ascontiguousarray(salts, dtype=np.uint8) if salts is not None else None
+        self.check(self.lib.hl_b200_merkle(self.h, _ptr(leaves), _ptr(s), nn, _ptr(leaf_key), _ptr(node_key), _ptr(out)))
+        return out
+
+
+class B200Commit:
+    """The store of a device commitment: ``impl EncodedStore`` (pcs/backend.rs:30-60)."""
+
+    def __init__(self, ctx: Context, handle: C.c_void_p):
+        self.ctx, self.h = ctx, handle
+        r, n, nn, q = C.c_size_t(), C.c_size_t(), C.c_size_t(), C.c_size_t()
+        ctx.lib.hl_b200_store_shape(handle, C.byref(r), C.byref(n), C.byref(nn), C.byref(q))
+        self.rows, self.n, self.nn, self.q = r.value, n.value, nn.value, q.value
+
+    def fold_batch(self) -> int:
+        """backend.rs:45-47: every vector in one call (the device folds in batches itself)."""
+        return 1 << 30
+
+    def fold_rows(self, rhos: np.ndarray) -> np.ndarray:
+        """rho^T M over the message columns: (k, rows, 2) -> (k, n, 2)."""
+        rhos = _u64(rhos)
+        k = rhos.shape[0]
+        out = np.empty((k, self.n, 2), dtype=np.uint64)
+        self.ctx.check(self.ctx.lib.hl_b200_store_fold(self.h, _ptr(rhos), k, 0, _ptr(out)))
+        return out
+
+    def fold_rows_with_pads(self, rhos: np.ndarray) -> np.ndarray:
+        """backend.rs:56-59 ([A8]): rho^T [M | pads], (k, n + q, 2); the pads are the commit's, resident."""
+        rhos = _u64(rhos)
+        k = rhos.shape[0]
+        out = np.empty((k, self.n + self.q, 2), dtype=np.uint64)
+        self.ctx.check(self.ctx.lib.hl_b200_store_fold(self.h, _ptr(rhos), k, 1, _ptr(out)))
+        return out
+
+    def columns(self, idx) -> np.ndarray:
+        """The encoded columns at idx, (len(idx), rows), order of idx, duplicates repeated."""
+        idx = _u64(idx)
+        out = np.empty((idx.size, self.rows), dtype=np.uint64)
+        self.ctx.check(self.ctx.lib.hl_b200_store_columns(self.h, _ptr(idx), idx.size, _ptr(out)))
+        return out
+
+    def merkle(self, salts: Optional[np.ndarray], leaf_key: Optional[bytes], node_key: Optional[bytes]) -> np.ndarray:
+        out = np.empty((2 * self.nn - 1, 32), dtype=np.uint8)
+        s = np.ascontiguousarray(salts, dtype=np.uint8) if salts is not None else None
+        self.ctx.check(self.ctx.lib.hl_b200_store_merkle(self.h, _ptr(s), _ptr(leaf_key), _ptr(node_key), _ptr(out)))
+        return out
+
+    def encoded_dev(self) -> int:
+        return int(self.ctx.lib.hl_b200_store_encoded_dev(self.h) or 0)
+
+    def leaves_dev(self) -> int:
+        return int(self.ctx.lib.hl_b200_store_leaves_dev(self.h) or 0)
+
+    def free(self) -> None:
+        if self.h:
+            self.ctx.lib.hl_b200_store_free(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class B200Backend:
+    """``impl Backend`` (pcs/backend.rs:66-100) for this device; the adapter's ``backend()``."""
+
+    def __init__(self, ctx: Optional[Context] = None, device: int = 0):
+        self.ctx = ctx or Context(device)
+
+    def enabled(self) -> bool:
+        return True
+
+    def label(self) -> str:
+        return self.ctx.label()
+
+    def try_commit(self, log_cols: int, inv_rate: int, data, max_log: int, key: Optional[bytes] = None):
+        data = _u64(data)
+        rows = data.size >> log_cols
+        leaves = np.empty((inv_rate << log_cols, 32), dtype=np.uint8)
+        h = C.c_void_p()
+        rc = self.ctx.lib.hl_b200_commit(self.ctx.h, log_cols, inv_rate, _ptr(data), rows, max_log, _ptr(key), C.byref(h), _ptr(leaves))
+        if rc != 0:
+            self.ctx.declined("b200 commit", rc)
+            return None
+        return B200Commit(self.ctx, h), leaves
+
+    def try_commit_zk(self, log_cols: int, inv_rate: int, data, pads, pows, max_log: int):
+        return self.try_commit_zk_keyed(log_cols, inv_rate, data, pads, pows, max_log, None)
+
+    def try_commit_zk_keyed(self, log_cols: int, inv_rate: int, data, pads, pows, max_log: int, key: Optional[bytes]):
+        data, pads, pows = _u64(data), _u64(pads), _u64(pows)
+        rows = data.size >> log_cols
+        q = pads.size // rows if rows else 0
+        leaves = np.empty((inv_rate << log_cols, 32), dtype=np.uint8)
+        h = C.c_void_p()
+        rc = self.ctx.lib.hl_b200_commit_zk(self.ctx.h, log_cols, inv_rate, _ptr(data), rows, _ptr(pads), q, _ptr(pows), max_log,
+                                             _ptr(key), C.byref(h), _ptr(leaves))
+        if rc != 0:
+            self.ctx.declined("b200 zk commit", rc)
+            return None
+        return B200Commit(self.ctx, h), leaves
+
+    def commit_zk_dev(self, log_cols: int, inv_rate: int, d_data: int, rows: int, d_pads: int, q: int, d_pows: int,
+                      key: Optional[bytes], d_leaves: int = 0) -> B200Commit:
+        """The device-buffer commitment: inputs are device addresses, asynchronous on the context's stream."""
+        h = C.c_void_p()
+        self.ctx.check(self.ctx.lib.hl_b200_commit_zk_dev(self.ctx.h, log_cols, inv_rate, C.c_void_p(d_data), rows, C.c_void_p(d_pads), q,
+                                                            C.c_void_p(d_pows), _ptr(key), C.byref(h), C.c_void_p(d_leaves)))
+        return B200Commit(self.ctx, h)

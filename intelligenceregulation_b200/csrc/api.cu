@@ -1,0 +1,196 @@
+// The C ABI of the backend (include/hl_b200.h): context, commitments, stores, Merkle trees.
+// Host runtime only; the kernels live in encode.cu, hash.cu, store.cu, misc.cu.
+#include "api_internal.h"
+
+#include <cstdio>
+#include <cstring>
+
+using namespace hlapi;
+
+namespace hlapi {
+
+int fail(hl_ctx* c, int code, const char* what, cudaError_t e) {
+    if (c) {
+        char buf[512];
+        if (e != cudaSuccess) snprintf(buf, sizeof buf, "%s: %s", what, cudaGetErrorString(e));
+        else snprintf(buf, sizeof buf, "%s", what);
+        c->last_error = buf;
+        c->stats.declines++;
+    }
+    return code;
+}
+
+// Stream-ordered allocation from the device's default pool, whose release threshold is
+// lifted at init so that freed blocks are reused instead of returned to the driver.
+int dev_alloc(hl_ctx* c, void** p, size_t bytes) {
+    *p = nullptr;
+    if (bytes == 0) bytes = 16;
+    if (c->alloc_cap && c->alloc_live + bytes > c->alloc_cap) return fail(c, HL_B200_ERR_OOM, "allocation cap reached (test hook)");
+    cudaError_t e = cudaMallocAsync(p, bytes, c->stream);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(c, HL_B200_ERR_OOM, "cudaMallocAsync", e);
+    }
+    c->alloc_live += bytes;
+    return HL_B200_OK;
+}
+
+void dev_free(hl_ctx* c, void* p, size_t bytes) {
+    if (!p) return;
+    cudaFreeAsync(p, c->stream);
+    if (bytes == 0) bytes = 16;
+    c->alloc_live = c->alloc_live >= bytes ? c->alloc_live - bytes : 0;
+}
+
+int h2d(hl_ctx* c, void* d, const void* h, size_t bytes) {
+    if (!bytes) return HL_B200_OK;
+    cudaError_t e = cudaMemcpyAsync(d, h, bytes, cudaMemcpyHostToDevice, c->stream);
+    if (e != cudaSuccess) return fail(c, HL_B200_ERR_DEVICE, "copy to device", e);
+    c->stats.bytes_h2d += bytes;
+    return HL_B200_OK;
+}
+
+int d2h(hl_ctx* c, void* h, const void* d, size_t bytes) {
+    if (!bytes) return HL_B200_OK;
+    cudaError_t e = cudaMemcpyAsync(h, d, bytes, cudaMemcpyDeviceToHost, c->stream);
+    if (e != cudaSuccess) return fail(c, HL_B200_ERR_DEVICE, "copy from device", e);
+    c->stats.bytes_d2h += bytes;
+    return HL_B200_OK;
+}
+
+int sync(hl_ctx* c, const char* what) {
+    cudaError_t e = cudaStreamSynchronize(c->stream);
+    if (e != cudaSuccess) return fail(c, HL_B200_ERR_DEVICE, what, e);
+    return HL_B200_OK;
+}
+
+// w_nn^j for j < nn, w_nn = 7^((p-1)/2^32)^(2^(32-log nn)) (field.rs:86-91, ntt.rs:29-43);
+// built once per size on the host and kept on the device.
+int root_powers(hl_ctx* c, u32 lognn, const u64** out) {
+    auto it = c->tw.find(lognn);
+    if (it != c->tw.end()) { *out = it->second; return HL_B200_OK; }
+    if (lognn > 26) return fail(c, HL_B200_ERR_UNSUPPORTED, "transform size above 2^26");
+    size_t nn = (size_t)1 << lognn;
+    std::vector<u64> h(nn);
+    u64 r32 = gl_pow(7, (GL_P - 1) >> 32), w = gl_pow(r32, 1ULL << (32 - lognn)), cur = 1;
+    for (size_t j = 0; j < nn; j++) { h[j] = cur; cur = gl_mul(cur, w); }
+    void* d = nullptr;
+    cudaError_t e = cudaMalloc(&d, nn * 8);
+    if (e != cudaSuccess) return fail(c, HL_B200_ERR_OOM, "twiddle table", e);
+    e = cudaMemcpyAsync(d, h.data(), nn * 8, cudaMemcpyHostToDevice, c->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);  // h dies at return
+    if (e != cudaSuccess) { cudaFree(d); return fail(c, HL_B200_ERR_DEVICE, "twiddle upload", e); }
+    c->tw[lognn] = (u64*)d;
+    *out = (u64*)d;
+    return HL_B200_OK;
+}
+
+// a 32-byte key as eight device words; NULL stays NULL (unkeyed)
+int upload_key(hl_ctx* c, const uint8_t* key32, uint32_t** d_key) {
+    *d_key = nullptr;
+    if (!key32) return HL_B200_OK;
+    int rc = dev_alloc(c, (void**)d_key, 32);
+    if (rc) return rc;
+    return h2d(c, *d_key, key32, 32);  // little-endian host: the bytes are the words
+}
+
+int log2_exact(size_t v) {
+    if (v == 0 || (v & (v - 1))) return -1;
+    int l = 0;
+    while (((size_t)1 << l) < v) l++;
+    return l;
+}
+
+}  // namespace hlapi
+
+extern "C" {
+
+int hl_b200_init(int device, hl_ctx** out) {
+    if (!out) return HL_B200_ERR_ARG;
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || device < 0 || device >= count) return HL_B200_ERR_DEVICE;
+    if (cudaSetDevice(device) != cudaSuccess) return HL_B200_ERR_DEVICE;
+    hl_ctx* c = new hl_ctx();
+    c->device = device;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) { delete c; return HL_B200_ERR_DEVICE; }
+    c->sm_count = prop.multiProcessorCount;
+    if (cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking) != cudaSuccess) { delete c; return HL_B200_ERR_DEVICE; }
+    c->stream = c->own_stream;
+    cudaMemPool_t pool;
+    if (cudaDeviceGetDefaultMemPool(&pool, device) == cudaSuccess) {
+        unsigned long long keep = ~0ULL;
+        cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+    }
+    char buf[256];
+    snprintf(buf, sizeof buf, "hl_b200: %s (sm_%d%d, %d SMs, %.0f GB), device %d", prop.name, prop.major, prop.minor,
+             prop.multiProcessorCount, (double)prop.totalGlobalMem / 1e9, device);
+    c->label = buf;
+    *out = c;
+    return HL_B200_OK;
+}
+
+void hl_b200_shutdown(hl_ctx* c) {
+    if (!c) return;
+    cudaSetDevice(c->device);
+    cudaStreamSynchronize(c->stream);
+    for (auto& kv : c->tw) cudaFree(kv.second);
+    cudaStreamDestroy(c->own_stream);
+    delete c;
+}
+
+const char* hl_b200_label(hl_ctx* c) { return c ? c->label.c_str() : "hl_b200: no context"; }
+const char* hl_b200_last_error(hl_ctx* c) { return c ? c->last_error.c_str() : "no context"; }
+
+int hl_b200_set_stream(hl_ctx* c, void* s) {
+    if (!c) return HL_B200_ERR_ARG;
+    std::lock_guard<std::mutex> g(c->mu);
+    cudaStreamSynchronize(c->stream);
+    c->stream = s ? (cudaStream_t)s : c->own_stream;
+    return HL_B200_OK;
+}
+
+int hl_b200_sync(hl_ctx* c) {
+    if (!c) return HL_B200_ERR_ARG;
+    std::lock_guard<std::mutex> g(c->mu);
+    cudaSetDevice(c->device);
+    return sync(c, "synchronize");
+}
+
+int hl_b200_set_encoder(hl_ctx* c, int fast) {
+    if (!c) return HL_B200_ERR_ARG;
+    c->fast_encoder = fast != 0;
+    return HL_B200_OK;
+}
+
+int hl_b200_stats(hl_ctx* c, hl_stats* out) {
+    if (!c || !out) return HL_B200_ERR_ARG;
+    std::lock_guard<std::mutex> g(c->mu);
+    *out = c->stats;
+    return HL_B200_OK;
+}
+
+int hl_b200_probe_field(hl_ctx* c, const uint64_t* a, const uint64_t* b, size_t n, uint64_t* out3n) {
+    if (!c || (n && (!a || !b || !out3n))) return fail(c, HL_B200_ERR_ARG, "probe_field: null argument");
+    std::lock_guard<std::mutex> g(c->mu);
+    cudaSetDevice(c->device);
+    u64 *da = nullptr, *db = nullptr, *dout = nullptr;
+    int rc = dev_alloc(c, (void**)&da, n * 8);
+    if (!rc) rc = dev_alloc(c, (void**)&db, n * 8);
+    if (!rc) rc = dev_alloc(c, (void**)&dout, n * 24);
+    if (!rc) rc = h2d(c, da, a, n * 8);
+    if (!rc) rc = h2d(c, db, b, n * 8);
+    if (!rc) {
+        cudaError_t e = hlk::probe_field(da, db, n, dout, c->stream);
+        c->stats.kernel_launches += n ? 1 : 0;
+        if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "probe_field launch", e);
+    }
+    if (!rc) rc = d2h(c, out3n, dout, n * 24);
+    if (!rc) rc = sync(c, "probe_field");
+    dev_free(c, da, n * 8); dev_free(c, db, n * 8); dev_free(c, dout, n * 24);
+    return rc;
+}
+
+}  // extern "C"

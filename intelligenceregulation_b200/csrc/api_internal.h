@@ -1,0 +1,51 @@
+// Host-side objects behind the opaque handles of include/hl_b200.h.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/hl_b200.h"
+#include "kernels.h"
+
+struct hl_ctx {
+    int device = 0;
+    int sm_count = 0;
+    cudaStream_t own_stream = nullptr;
+    cudaStream_t stream = nullptr;
+    bool fast_encoder = true;
+    std::mutex mu;
+    std::map<u32, u64*> tw;  // log2 nn -> nn powers of the nn-th root
+    std::string label, last_error;
+    hl_stats stats{};
+    size_t alloc_live = 0;   // bytes handed out and not yet returned
+    size_t alloc_cap = 0;    // 0 = none; a host-side failure-injection cap (mod.rs:121 set_alloc_cap_for_test)
+};
+
+struct hl_store {
+    hl_ctx* ctx = nullptr;
+    u32 rows = 0, logn = 0, logr = 0, q = 0;
+    bool zk = false;
+    bool owns_inputs = true;      // false: d_data / d_pads belong to the caller
+    u64* d_data = nullptr;        // rows x n
+    u64* d_pads = nullptr;        // rows x q
+    u64* d_enc = nullptr;         // rows x nn
+    uint32_t* d_leaves = nullptr; // nn x 8 words, unsalted
+    int encoder_path = -1;
+    size_t n() const { return (size_t)1 << logn; }
+    size_t nn() const { return (size_t)1 << (logn + logr); }
+};
+
+namespace hlapi {
+int fail(hl_ctx* c, int code, const char* what, cudaError_t e = cudaSuccess);
+int dev_alloc(hl_ctx* c, void** p, size_t bytes);
+void dev_free(hl_ctx* c, void* p, size_t bytes);
+int h2d(hl_ctx* c, void* d, const void* h, size_t bytes);
+int d2h(hl_ctx* c, void* h, const void* d, size_t bytes);
+int sync(hl_ctx* c, const char* what);
+int root_powers(hl_ctx* c, u32 lognn, const u64** out);
+int upload_key(hl_ctx* c, const uint8_t* key32, uint32_t** d_key);
+int log2_exact(size_t v);
+}  // namespace hlapi

@@ -1,0 +1,294 @@
+// C ABI: commitments (Backend::try_commit*), stores (EncodedStore), Merkle trees.
+#include "api_internal.h"
+
+using namespace hlapi;
+
+namespace {
+
+struct Shape {
+    u32 logn, logr, rows, q;
+    bool zk;
+};
+
+// Encode + column-hash on device memory that is already in place.  Leaves stay in st->d_leaves.
+int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* key32) {
+    const u32 logn = st->logn, lognn = st->logn + st->logr;
+    const size_t n = st->n(), nn = st->nn();
+    const u32 T = st->zk ? (u32)((n + st->q + n - 1) / n) : 1u;
+    const u64* tw = nullptr;
+    int rc = root_powers(c, lognn, &tw);
+    if (rc) return rc;
+    uint32_t* d_key = nullptr;
+    u64* scratch = nullptr;
+    uint32_t* cvs = nullptr;
+    const size_t scratch_words = hlk::encode_scratch_words(logn, T, c->sm_count, st->rows);
+    const u32 nchunks = hlk::hash_chunks(st->rows);
+    const size_t cvs_bytes = nchunks > 1 ? (size_t)nchunks * nn * 32 : 0;
+    rc = upload_key(c, key32, &d_key);
+    if (!rc) rc = dev_alloc(c, (void**)&scratch, scratch_words * 8);
+    if (!rc && cvs_bytes) rc = dev_alloc(c, (void**)&cvs, cvs_bytes);
+    if (!rc) {
+        enc::RowArgs a;
+        a.data = st->d_data; a.pads = st->d_pads; a.pows = d_pows; a.tw_nn = tw; a.enc = st->d_enc; a.scratch = scratch;
+        a.rows = st->rows; a.q = st->zk ? st->q : 0; a.T = T; a.logr = st->logr; a.zk = st->zk ? 1 : 0;
+        a.ninv = gl_inv((u64)n);
+        cudaError_t e = hlk::encode_rows(a, logn, c->fast_encoder, c->sm_count, scratch_words, c->stream, &st->encoder_path);
+        c->stats.kernel_launches += 1;
+        if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "row encoder launch", e);
+    }
+    if (!rc) {
+        cudaError_t e = hlk::hash_columns(st->d_enc, st->rows, (u32)nn, d_key, cvs, st->d_leaves, c->stream);
+        c->stats.kernel_launches += nchunks > 1 ? 2 : 1;
+        if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "column hash launch", e);
+    }
+    dev_free(c, scratch, scratch_words * 8);
+    if (cvs) dev_free(c, cvs, cvs_bytes);
+    if (d_key) dev_free(c, d_key, 32);
+    return rc;
+}
+
+int check_shape(hl_ctx* c, uint32_t log_cols, uint32_t inv_rate, size_t rows, size_t q, bool zk, uint32_t max_log, Shape* s) {
+    int logr = log2_exact(inv_rate);
+    if (logr < 0 || rows == 0 || rows > 0x7FFFFFFFu) return fail(c, HL_B200_ERR_ARG, "commit: rows or inv_rate");
+    if (log_cols < 1) return fail(c, HL_B200_ERR_UNSUPPORTED, "commit: fewer than 2 columns");
+    if (log_cols > 14) return fail(c, HL_B200_ERR_UNSUPPORTED, "commit: more than 2^14 columns per row");
+    if (max_log && log_cols + (uint32_t)logr > max_log) return fail(c, HL_B200_ERR_ARG, "commit: transform exceeds the caller's NTT tables");
+    size_t n = (size_t)1 << log_cols, nn = n << logr;
+    if (zk && (q == 0 || n + q > nn)) return fail(c, HL_B200_ERR_ARG, "commit_zk: pad count (need 0 < q and n + q <= nn)");
+    if (rows * nn > ((size_t)1 << 36)) return fail(c, HL_B200_ERR_UNSUPPORTED, "commit: encoding above 512 GiB");
+    s->logn = log_cols; s->logr = (u32)logr; s->rows = (u32)rows; s->q = zk ? (u32)q : 0; s->zk = zk;
+    return HL_B200_OK;
+}
+
+void free_store(hl_store* st) {
+    hl_ctx* c = st->ctx;
+    if (st->owns_inputs) {
+        dev_free(c, st->d_data, (size_t)st->rows * st->n() * 8);
+        dev_free(c, st->d_pads, (size_t)st->rows * st->q * 8);
+    }
+    dev_free(c, st->d_enc, (size_t)st->rows * st->nn() * 8);
+    dev_free(c, st->d_leaves, st->nn() * 32);
+    delete st;
+}
+
+int commit_host(hl_ctx* c, const Shape& s, const uint64_t* data, const uint64_t* pads, const uint64_t* pows,
+                const uint8_t* key32, hl_store** store, uint8_t* leaves32) {
+    hl_store* st = new hl_store();
+    st->ctx = c; st->rows = s.rows; st->logn = s.logn; st->logr = s.logr; st->q = s.q; st->zk = s.zk;
+    const size_t n = st->n(), nn = st->nn();
+    u64* d_pows = nullptr;
+    int rc = dev_alloc(c, (void**)&st->d_data, (size_t)s.rows * n * 8);
+    if (!rc && s.zk) rc = dev_alloc(c, (void**)&st->d_pads, (size_t)s.rows * s.q * 8);
+    if (!rc && s.zk) rc = dev_alloc(c, (void**)&d_pows, nn * 8);
+    if (!rc) rc = dev_alloc(c, (void**)&st->d_enc, (size_t)s.rows * nn * 8);
+    if (!rc) rc = dev_alloc(c, (void**)&st->d_leaves, nn * 32);
+    if (!rc) rc = h2d(c, st->d_data, data, (size_t)s.rows * n * 8);
+    if (!rc && s.zk) rc = h2d(c, st->d_pads, pads, (size_t)s.rows * s.q * 8);
+    if (!rc && s.zk) rc = h2d(c, d_pows, pows, nn * 8);
+    if (!rc) rc = commit_on_device(c, st, d_pows, key32);
+    if (!rc) rc = d2h(c, leaves32, st->d_leaves, nn * 32);
+    if (!rc) rc = sync(c, "commit");
+    if (d_pows) dev_free(c, d_pows, nn * 8);
+    if (rc) { cudaStreamSynchronize(c->stream); free_store(st); return rc; }
+    c->stats.commits++;
+    *store = st;
+    return HL_B200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int hl_b200_commit(hl_ctx* c, uint32_t log_cols, uint32_t inv_rate, const uint64_t* data, size_t rows, uint32_t max_log,
+                   const uint8_t* key32, hl_store** store, uint8_t* leaves32) {
+    if (!c || !data || !store || !leaves32) return fail(c, HL_B200_ERR_ARG, "commit: null argument");
+    std::lock_guard<std::mutex> g(c->mu);
+    cudaSetDevice(c->device);
+    Shape s;
+    int rc = check_shape(c, log_cols, inv_rate, rows, 0, false, max_log, &s);
+    if (rc) return rc;
+    return commit_host(c, s, data, nullptr, nullptr, key32, store, leaves32);
+}
+
+int hl_b200_commit_zk(hl_ctx* c, uint32_t log_cols, uint32_t inv_rate, const uint64_t* data, size_t rows,
+                      const uint64_t* pads, size_t q, const uint64_t* pows, uint32_t max_log, const uint8_t* key32,
+                      hl_store** store, uint8_t* leaves32) {
+    if (!c || !data || !pads || !pows || !store || !leaves32) return fail(c, HL_B200_ERR_ARG, "commit_zk: null argument");
+    std::lock_guard<std::mutex> g(c->mu);
+    cudaSetDevice(c->device);
+    Shape s;
+    int rc = check_shape(c, log_cols, inv_rate, rows, q, true, max_log, &s);
+    if (rc) return rc;
+    return commit_host(c, s, data, pads, pows, key32, store, leaves32);
+}
+
+int hl_b200_commit_zk_dev(hl_ctx* c, uint32_t log_cols, uint32_t inv_rate, const uint64_t* d_data, size_t rows,
+                          const uint64_t* d_pads, size_t q, const uint64_t* d_pows, const uint8_t* key32,
+                          hl_store** store, uint8_t* d_leaves32) {
+    if (!c || !d_data || !d_pads || !d_pows || !store) return fail(c, HL_B200_ERR_ARG, "commit_zk_dev: null argument");
+    std::lock_guard<std::mutex> g(c->mu);
+    cudaSetDevice(c->device);
+    Shape s;
+    int rc = check_shape(c, log_cols, inv_rate, rows, q, true, 0, &s);
+    if (rc) return rc;
+    hl_store* st = new hl_store();
+    st->ctx = c; st->rows = s.rows; st->logn = s.logn; st->logr = s.logr; st->q = s.q; st->zk = true;
+    st->owns_inputs = false;
+    st->d_data = const_cast<u64*>((const u64*)d_data);
+    st->d_pads = const_cast<u64*>((const u64*)d_pads);
+    const size_t nn = st->nn();
+    rc = dev_alloc(c, (void**)&st->d_enc, (size_t)s.rows * nn * 8);
+    if (!rc) rc = dev_alloc(c, (void**)&st->d_leaves, nn * 32);
+    if (!rc) rc = commit_on_device(c, st, (const u64*)d_pows, key32);
+    if (!rc && d_leaves32) {
+        cudaError_t e = cudaMemcpyAsync(d_leaves32, st->d_leaves, nn * 32, cudaMemcpyDeviceToDevice, c->stream);
+        if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "leaf copy", e);
+    }
+    if (rc) { cudaStreamSynchronize(c->stream); free_store(st); return rc; }
+    c->stats.commits++;
+    *store = st;
+    return HL_B200_OK;
+}
+
+int hl_b200_store_shape(hl_store* st, size_t* rows, size_t* n, size_t* nn, size_t* q) {
+    if (!st) return HL_B200_ERR_ARG;
+    if (rows) *rows = st->rows;
+    if (n) *n = st->n();
+    if (nn) *nn = st->nn();
+    if (q) *q = st->q;
+    return HL_B200_OK;
+}
+
+const uint64_t* hl_b200_store_encoded_dev(hl_store* st) { return st ? (const uint64_t*)st->d_enc : nullptr; }
+const uint8_t* hl_b200_store_leaves_dev(hl_store* st) { return st ? (const uint8_t*)st->d_leaves : nullptr; }
+
+void hl_b200_store_free(hl_store* st) {
+    if (!st) return;
+    hl_ctx* c = st->ctx;
+    std::lock_guard<std::mutex> g(c->mu);
+    cudaSetDevice(c->device);
+    free_store(st);
+}
+
+int hl_b200_store_fold(hl_store* st, const uint64_t* rhos, size_t k, int with_pads, uint64_t* out) {
+    if (!st) return HL_B200_ERR_ARG;
+    hl_ctx* c = st->ctx;
+    if (k && (!rhos || !out)) return fail(c, HL_B200_ERR_ARG, "store_fold: null argument");
+    if (with_pads && !st->zk) return fail(c, HL_B200_ERR_ARG, "store_fold: pads asked of a plain store");
+    if (k == 0) return HL_B200_OK;
+    if (k > 0xFFFFu * 8u) return fail(c, HL_B200_ERR_ARG, "store_fold: too many vectors");
+    std::lock_guard<std::mutex> g(c->mu);
+    cudaSetDevice(c->device);
+    const u32 n = (u32)st->n(), q = with_pads ? st->q : 0, w = n + q;
+    u64 *d_rhos = nullptr, *d_out = nullptr;
+    const size_t rb = k * (size_t)st->rows * 16, ob = k * (size_t)w * 16;
+    int rc = dev_alloc(c, (void**)&d_rhos, rb);
+    if (!rc) rc = dev_alloc(c, (void**)&d_out, ob);
+    if (!rc) rc = h2d(c, d_rhos, rhos, rb);
+    if (!rc) {
+        // hiding form: the message is the resident data (the encoding is not systematic, pcs.rs:985-987);
+        // plain form: the systematic positions of the encoding (pcs.rs:332-340)
+        cudaError_t e = st->zk ? hlk::fold_rows(st->d_data, st->rows, n, n, 1, d_rhos, (u32)k, d_out, w, 0, c->stream)
+                               : hlk::fold_rows(st->d_enc, st->rows, n, st->nn(), 1u << st->logr, d_rhos, (u32)k, d_out, w, 0, c->stream);
+        c->stats.kernel_launches++;
+        if (e == cudaSuccess && q) {
+            e = hlk::fold_rows(st->d_pads, st->rows, q, q, 1, d_rhos, (u32)k, d_out, w, n, c->stream);
+            c->stats.kernel_launches++;
+        }
+        if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "fold launch", e);
+    }
+    if (!rc) rc = d2h(c, out, d_out, ob);
+    if (!rc) rc = sync(c, "store_fold");
+    dev_free(c, d_rhos, rb); dev_free(c, d_out, ob);
+    if (!rc) c->stats.folds++;
+    return rc;
+}
+
+int hl_b200_store_columns(hl_store* st, const uint64_t* idx, size_t nidx, uint64_t* out) {
+    if (!st) return HL_B200_ERR_ARG;
+    hl_ctx* c = st->ctx;
+    if (nidx && (!idx || !out)) return fail(c, HL_B200_ERR_ARG, "store_columns: null argument");
+    if (nidx == 0) return HL_B200_OK;
+    if (nidx > 65535) return fail(c, HL_B200_ERR_ARG, "store_columns: more than 65535 columns in one call");
+    for (size_t i = 0; i < nidx; i++)
+        if (idx[i] >= st->nn()) return fail(c, HL_B200_ERR_ARG, "store_columns: index out of range");
+    std::lock_guard<std::mutex> g(c->mu);
+    cudaSetDevice(c->device);
+    u64 *d_idx = nullptr, *d_out = nullptr;
+    const size_t ob = nidx * (size_t)st->rows * 8;
+    int rc = dev_alloc(c, (void**)&d_idx, nidx * 8);
+    if (!rc) rc = dev_alloc(c, (void**)&d_out, ob);
+    if (!rc) rc = h2d(c, d_idx, idx, nidx * 8);
+    if (!rc) {
+        cudaError_t e = hlk::gather_columns(st->d_enc, st->rows, st->nn(), d_idx, (u32)nidx, d_out, c->stream);
+        c->stats.kernel_launches++;
+        if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "gather launch", e);
+    }
+    if (!rc) rc = d2h(c, out, d_out, ob);
+    if (!rc) rc = sync(c, "store_columns");
+    dev_free(c, d_idx, nidx * 8); dev_free(c, d_out, ob);
+    if (!rc) c->stats.gathers++;
+    return rc;
+}
+
+static int merkle_common(hl_ctx* c, const uint32_t* d_leaves_in, const uint8_t* h_leaves, const uint8_t* salts32, size_t nn,
+                         const uint8_t* leaf_key32, const uint8_t* node_key32, uint8_t* levels_out) {
+    if (log2_exact(nn) < 0 || nn > ((size_t)1 << 26)) return fail(c, HL_B200_ERR_ARG, "merkle: leaf count must be a power of two");
+    const size_t lv_bytes = (2 * nn - 1) * 32;
+    uint32_t *d_levels = nullptr, *d_in = nullptr, *d_salts = nullptr, *d_lk = nullptr, *d_nk = nullptr;
+    int rc = dev_alloc(c, (void**)&d_levels, lv_bytes);
+    if (!rc) rc = upload_key(c, leaf_key32, &d_lk);
+    if (!rc) rc = upload_key(c, node_key32, &d_nk);
+    const uint32_t* leaves = d_leaves_in;
+    if (!rc && !leaves) {
+        rc = dev_alloc(c, (void**)&d_in, nn * 32);
+        if (!rc) rc = h2d(c, d_in, h_leaves, nn * 32);
+        leaves = d_in;
+    }
+    if (!rc && salts32) {
+        rc = dev_alloc(c, (void**)&d_salts, nn * 32);
+        if (!rc) rc = h2d(c, d_salts, salts32, nn * 32);
+        if (!rc) {
+            cudaError_t e = hlk::salt_leaves(leaves, d_salts, (u32)nn, d_lk, d_levels, c->stream);
+            c->stats.kernel_launches++;
+            if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "salt launch", e);
+        }
+    } else if (!rc) {
+        cudaError_t e = cudaMemcpyAsync(d_levels, leaves, nn * 32, cudaMemcpyDeviceToDevice, c->stream);
+        if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "leaf copy", e);
+    }
+    if (!rc) {
+        cudaError_t e = hlk::merkle_levels(d_levels, (u32)nn, d_nk, c->stream);
+        for (size_t w = nn; w > 2048; w >>= 1) c->stats.kernel_launches++;
+        if (nn > 1) c->stats.kernel_launches++;
+        if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "merkle launch", e);
+    }
+    if (!rc) rc = d2h(c, levels_out, d_levels, lv_bytes);
+    if (!rc) rc = sync(c, "merkle");
+    dev_free(c, d_levels, lv_bytes);
+    if (d_in) dev_free(c, d_in, nn * 32);
+    if (d_salts) dev_free(c, d_salts, nn * 32);
+    if (d_lk) dev_free(c, d_lk, 32);
+    if (d_nk) dev_free(c, d_nk, 32);
+    if (!rc) c->stats.merkles++;
+    return rc;
+}
+
+int hl_b200_merkle(hl_ctx* c, const uint8_t* leaves32, const uint8_t* salts32, size_t nn, const uint8_t* leaf_key32,
+                   const uint8_t* node_key32, uint8_t* levels_out) {
+    if (!c || !leaves32 || !levels_out) return fail(c, HL_B200_ERR_ARG, "merkle: null argument");
+    std::lock_guard<std::mutex> g(c->mu);
+    cudaSetDevice(c->device);
+    return merkle_common(c, nullptr, leaves32, salts32, nn, leaf_key32, node_key32, levels_out);
+}
+
+int hl_b200_store_merkle(hl_store* st, const uint8_t* salts32, const uint8_t* leaf_key32, const uint8_t* node_key32,
+                         uint8_t* levels_out) {
+    if (!st || !levels_out) return HL_B200_ERR_ARG;
+    hl_ctx* c = st->ctx;
+    std::lock_guard<std::mutex> g(c->mu);
+    cudaSetDevice(c->device);
+    return merkle_common(c, st->d_leaves, nullptr, salts32, st->nn(), leaf_key32, node_key32, levels_out);
+}
+
+}  // extern "C"

@@ -1,0 +1,115 @@
+// Goldilocks field arithmetic for device (and host) code.
+//
+// p = 2^64 - 2^32 + 1.  Every value handed to or returned from these functions
+// is canonical (< p), which is the representation the reference prover keeps
+// (zkp-core/src/field.rs:10-116).  The extension is Fp2 = Fp[u]/(u^2 - 7),
+// stored as two consecutive words (c0, c1) (field.rs:139-203).
+//
+// The reduction uses 2^64 = 2^32 - 1 and 2^96 = -1 (mod p): a 128-bit product
+// lo + 2^64 (hh 2^32 + hl) equals lo - hh + hl (2^32 - 1).  No division, no
+// Montgomery form: canonical words go straight to the BLAKE3 column hash.
+#pragma once
+#include <stdint.h>
+
+#ifdef __CUDACC__
+#define GL_HD __host__ __device__ __forceinline__
+#else
+#define GL_HD inline
+#endif
+
+typedef unsigned long long u64;
+typedef unsigned int u32;
+
+#define GL_P 0xFFFFFFFF00000001ULL
+#define GL_EPS 0xFFFFFFFFULL
+
+struct fp2 {
+    u64 c0, c1;
+};
+
+GL_HD u64 gl_canon(u64 v) { return v >= GL_P ? v - GL_P : v; }
+
+GL_HD u64 gl_add(u64 a, u64 b) {
+    u64 r = a + b;
+    if (r < a) r += GL_EPS;  // wrapped past 2^64: 2^64 = EPS (mod p); the sum is then already < p
+    return gl_canon(r);
+}
+
+GL_HD u64 gl_sub(u64 a, u64 b) {
+    u64 r = a - b;
+    if (a < b) r -= GL_EPS;  // borrowed 2^64: give back EPS, i.e. add p
+    return r;
+}
+
+GL_HD u64 gl_neg(u64 a) { return a ? GL_P - a : 0; }
+
+GL_HD u64 gl_reduce128(u64 lo, u64 hi) {
+    u64 hh = hi >> 32, hl = hi & GL_EPS;
+    u64 t0 = lo - hh;
+    if (lo < hh) t0 -= GL_EPS;
+    u64 t1 = (hl << 32) - hl;  // hl * (2^32 - 1), below 2^64
+    u64 r = t0 + t1;
+    if (r < t0) r += GL_EPS;
+    return gl_canon(r);
+}
+
+GL_HD u64 gl_mul(u64 a, u64 b) {
+#ifdef __CUDA_ARCH__
+    return gl_reduce128(a * b, __umul64hi(a, b));
+#else
+    unsigned __int128 x = (unsigned __int128)a * b;
+    return gl_reduce128((u64)x, (u64)(x >> 64));
+#endif
+}
+
+// Signed small integer to field (field.rs:32-34).
+GL_HD u64 gl_from_i64(long long v) {
+    if (v >= 0) return gl_canon((u64)v);
+    u64 m = (u64)(-(v + 1)) + 1;
+    return gl_canon(GL_P - m % GL_P);
+}
+
+GL_HD u64 gl_pow(u64 b, u64 e) {
+    u64 acc = 1;
+    while (e) {
+        if (e & 1) acc = gl_mul(acc, b);
+        b = gl_mul(b, b);
+        e >>= 1;
+    }
+    return acc;
+}
+GL_HD u64 gl_inv(u64 a) { return gl_pow(a, GL_P - 2); }
+
+GL_HD fp2 f2(u64 a, u64 b) {
+    fp2 r;
+    r.c0 = a;
+    r.c1 = b;
+    return r;
+}
+GL_HD fp2 f2_add(fp2 a, fp2 b) { return f2(gl_add(a.c0, b.c0), gl_add(a.c1, b.c1)); }
+GL_HD fp2 f2_sub(fp2 a, fp2 b) { return f2(gl_sub(a.c0, b.c0), gl_sub(a.c1, b.c1)); }
+GL_HD fp2 f2_mul_base(fp2 a, u64 b) { return f2(gl_mul(a.c0, b), gl_mul(a.c1, b)); }
+// (a0 + a1 u)(b0 + b1 u) with u^2 = 7 (field.rs:163-169)
+GL_HD fp2 f2_mul(fp2 a, fp2 b) {
+    u64 ac = gl_mul(a.c0, b.c0), bd = gl_mul(a.c1, b.c1);
+    u64 ad = gl_mul(a.c0, b.c1), bc = gl_mul(a.c1, b.c0);
+    u64 bd7 = gl_sub(gl_reduce128(bd << 3, bd >> 61), bd);  // 7 bd = 8 bd - bd
+    return f2(gl_add(ac, bd7), gl_add(ad, bc));
+}
+GL_HD bool f2_is_zero(fp2 a) { return (a.c0 | a.c1) == 0; }
+// conj(a) / (a0^2 - 7 a1^2) (field.rs:180-185)
+GL_HD fp2 f2_inv(fp2 a) {
+    u64 norm = gl_sub(gl_mul(a.c0, a.c0), gl_mul(gl_mul(a.c1, a.c1), 7));
+    u64 ni = gl_inv(norm);
+    return f2(gl_mul(a.c0, ni), gl_mul(gl_neg(a.c1), ni));
+}
+
+GL_HD u32 gl_brev(u32 x, int bits) {
+#ifdef __CUDA_ARCH__
+    return bits ? (__brev(x) >> (32 - bits)) : 0;
+#else
+    u32 r = 0;
+    for (int i = 0; i < bits; i++) r = (r << 1) | ((x >> i) & 1);
+    return r;
+#endif
+}

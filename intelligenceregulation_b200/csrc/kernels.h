@@ -1,0 +1,30 @@
+// Launch wrappers of the device kernels (one .cu file per family).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "encode_core.cuh"
+
+namespace hlk {
+
+// encode.cu
+size_t encode_scratch_words(u32 logn, u32 T, int sm_count, u32 rows);
+cudaError_t encode_rows(const enc::RowArgs& a, u32 logn, bool allow_fast, int sm_count, size_t scratch_words,
+                        cudaStream_t st, int* path_out);
+
+// hash.cu
+u32 hash_chunks(u32 rows);
+cudaError_t hash_columns(const u64* enc, u32 rows, u32 nn, const uint32_t* d_key, uint32_t* d_cvs, uint32_t* d_leaves,
+                         cudaStream_t st);
+cudaError_t salt_leaves(const uint32_t* d_leaves, const uint32_t* d_salts, u32 nn, const uint32_t* d_leaf_key,
+                        uint32_t* d_out, cudaStream_t st);
+cudaError_t merkle_levels(uint32_t* d_levels, u32 nn, const uint32_t* d_node_key, cudaStream_t st);
+
+// store.cu
+cudaError_t fold_rows(const u64* src, u32 rows, u32 ncols, size_t ld, u32 ir, const u64* d_rhos, u32 k, u64* d_out,
+                      u32 out_ld, u32 out_off, cudaStream_t st);
+cudaError_t gather_columns(const u64* enc, u32 rows, size_t nn, const u64* d_idx, u32 nidx, u64* d_out, cudaStream_t st);
+
+// misc.cu
+cudaError_t probe_field(const u64* d_a, const u64* d_b, size_t n, u64* d_out3, cudaStream_t st);
+
+}  // namespace hlk
