@@ -1,0 +1,327 @@
+"""Ligero-commit throughput of the B200 backend (and of the CPU restatement beside it).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+One step = one hiding commitment of one transformer block's `A` matrix at the Llama-3-8B block
+shape the reference registers (W16R2_8B_T128_H24: 2,504 rows x 2^14 -> 2^15 columns, Q = 280 pads
+per row, keyed column hash), through to its salted Merkle root: inverse NTT, pad + coset scaling,
+forward NTT, BLAKE3 column leaves, salted leaves, tree.  Metric: encoded bytes (rows * nn * 8)
+per second, the reference's own accounting for "commit GB/s".
+
+`value`  - inputs already resident in HBM, timed with CUDA events on the library's stream.
+`e2e`    - the same commitment through the host-pointer C-ABI call a prover makes
+           (hl_b200_commit_zk + hl_b200_store_merkle), pinned host inputs, H2D and D2H inside the clock.
+With N > 1 every rank commits its own blocks (D55 sharding: block k belongs to rank k mod N; no
+data-path collective) and the 32-byte roots are all-gathered over NCCL, as the join needs them.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORK = {"log_cols": 14, "inv_rate": 2, "q": 280, "rows": 2504, "profile": "hashline-zk-mr1/b200-bench/1"}
+P = 0xFFFFFFFF00000001
+PUBLISHED_GBPS = 26.0  # the reference's Metal backend on an M3 Ultra at this exact shape
+
+
+def splitmix_fp(seed: int, n: int) -> np.ndarray:
+    """Seeded uniform field elements: SplitMix64 words reduced mod p (the generator of the reference's
+    encode vectors, zkp-core/src/pcs/encode_conformance_tests.rs:28-47)."""
+    i = np.arange(1, n + 1, dtype=np.uint64)
+    with np.errstate(over="ignore"):
+        z = np.uint64(seed) + i * np.uint64(0x9E3779B97F4A7C15)
+        z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+        z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+        z = z ^ (z >> np.uint64(31))
+    return z % np.uint64(P)
+
+
+def coset_powers(nn: int) -> np.ndarray:
+    out, x = np.empty(nn, dtype=np.uint64), 1
+    for i in range(nn):
+        out[i] = x
+        x = x * 7 % P
+    return out
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown," \
+        "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, gpu_index: int):
+        self.idx, self.rows, self.proc = gpu_index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.idx)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        self.t.join(timeout=2)
+        sm = [float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        reasons = set()
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_commit_sample(o, rows_s: int, threads_note: str):
+    """One hiding commitment of `rows_s` rows at the workload's n / nn / q on the host cores (the CPU
+    restatement of pcs.rs:782-817); returns seconds."""
+    w = WORK
+    n, nn, q = 1 << w["log_cols"], (1 << w["log_cols"]) * w["inv_rate"], w["q"]
+    tag = o.HashTag.for_profile(w["profile"])
+    data, pads = splitmix_fp(11, rows_s * n), splitmix_fp(12, rows_s * q)
+    salts = np.frombuffer(o.blake3(b"bench-salts", None, nn * 32), dtype=np.uint8).reshape(nn, 32)
+    pows = o.coset_powers(7, nn)
+    t0 = time.perf_counter()
+    enc = o.encode_rows_zk(data, rows_s, n, pads, q, pows, w["log_cols"] + 1)
+    leaves = o.hash_columns(enc, rows_s, nn, tag.column)
+    o.merkle_build(o.salt_leaves(leaves, salts, tag.leaf), tag.node)
+    return time.perf_counter() - t0
+
+
+def run_reference(args, rank: int) -> None:
+    """The reference arm: the prover's CPU path on this box's host cores.  The reference's own binary is
+    Rust and cannot be built here (no cargo in this image), so this times the C restatement of it
+    (oracle/, OpenMP over rows / column tiles, the reference's task grains) and says so."""
+    if rank != 0:
+        return
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import hl_oracle as o
+
+    w = WORK
+    nn = (1 << w["log_cols"]) * w["inv_rate"]
+    rows_s = 128
+    for _ in range(args.warmup):
+        cpu_commit_sample(o, rows_s, "")
+    t = [cpu_commit_sample(o, rows_s, "") for _ in range(args.steps)]
+    sec = sum(t) / len(t)
+    gbps = rows_s * nn * 8 / sec / 1e9
+    cores = o.num_threads()
+    line = {
+        "impl": "reference", "metric": "ligero_commit_GBps", "value": gbps, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u64",
+        "data": "synthetic", "config": workload_config(1) | {"sample_rows": rows_s},
+        "cpu_baseline": {"value": gbps, "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": f"{rows_s} of {w['rows']} rows per step at the same n/nn/q: encode + column hash + salt + tree; "
+                                   "C restatement of the reference's Rust CPU path (no Rust toolchain in this image)"},
+        "e2e": {"value": gbps, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def workload_config(world: int) -> dict:
+    w = WORK
+    return {"workload": "Ligero hiding commit of the Llama-3-8B block's A matrix (W16R2_8B_T128_H24): "
+                        f"{w['rows']} rows x 2^{w['log_cols']} -> 2^{w['log_cols'] + 1} (rate 1/2), Q = {w['q']}, keyed BLAKE3 leaves, salted tree to the root",
+            "rows": w["rows"], "log_cols": w["log_cols"], "inv_rate": w["inv_rate"], "q_pad": w["q"],
+            "parallelism": f"d55-block-sharding x{world}" if world > 1 else "single",
+            "l2": "inputs (328 MB) and encoding (656 MB) exceed the 126 MB L2; no flush needed",
+            "published_baseline": "26.0 GB/s, reference Metal backend on Apple M3 Ultra, same shape"}
+
+
+def run_b200(args, rank: int, local_rank: int, world: int) -> None:
+    import torch
+    import torch.distributed as dist
+    from intelligenceregulation_b200 import backend
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; this backend has no CPU path")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    w = WORK
+    log_cols, ir, q, rows = w["log_cols"], w["inv_rate"], w["q"], w["rows"]
+    n, nn = 1 << log_cols, (1 << log_cols) * ir
+    # the bench profile's hash-tag keys (hashtag.rs:47-53,92-100): derive_key is the caller's host logic
+    import blake3 as b3
+
+    prof = w["profile"].encode()
+    col_key = b3.blake3(prof, derive_key_context="hashline-zk-mr1 2026-09-20 pcs column digest").digest()
+    leaf_key = b3.blake3(prof, derive_key_context="hashline-zk-mr1 2026-09-20 pcs salted merkle leaf").digest()
+    node_key = b3.blake3(prof, derive_key_context="hashline-zk-mr1 2026-09-20 pcs merkle inner node").digest()
+
+    # this rank's block (D55: block k -> rank k mod world); seeded synthetic witness words uniform in [0, p)
+    block = rank
+    h_data = torch.from_numpy(splitmix_fp(0xB2000100 + block, rows * n).view(np.int64)).pin_memory()
+    h_pads = torch.from_numpy(splitmix_fp(0xB2000200 + block, rows * q).view(np.int64)).pin_memory()
+    h_pows = torch.from_numpy(coset_powers(nn).view(np.int64)).pin_memory()
+    h_salts = torch.from_numpy(np.frombuffer(b3.blake3(b"bench-salts-%d" % block).digest(length=nn * 32), dtype=np.uint8).copy()).pin_memory()
+
+    dev = backend.B200Backend(device=local_rank)
+    stream = torch.cuda.current_stream()
+    dev.ctx.set_stream(stream.cuda_stream)
+    d_data, d_pads, d_pows, d_salts = (t.cuda(non_blocking=True) for t in (h_data, h_pads, h_pows, h_salts))
+    d_levels = torch.empty((2 * nn - 1) * 32, dtype=torch.uint8, device="cuda")
+    roots = torch.empty(world * 32, dtype=torch.uint8, device="cuda")
+    torch.cuda.synchronize()
+
+    def step_resident():
+        st = dev.commit_zk_dev(log_cols, ir, d_data.data_ptr(), rows, d_pads.data_ptr(), q, d_pows.data_ptr(), col_key)
+        st.merkle_dev(d_salts.data_ptr(), leaf_key, node_key, d_levels.data_ptr())
+        st.free()
+        if world > 1:
+            dist.all_gather_into_tensor(roots, d_levels[-32:])
+
+    np_data, np_pads, np_pows, np_salts = (t.numpy().view(np.uint64) if t.dtype == torch.int64 else t.numpy() for t in (h_data, h_pads, h_pows, h_salts))
+
+    def step_e2e():
+        st, leaves = dev.try_commit_zk_keyed(log_cols, ir, np_data, np_pads, np_pows, log_cols + 1, col_key)
+        levels = st.merkle(np_salts.reshape(nn, 32), leaf_key, node_key)
+        st.free()
+        if world > 1:
+            dist.all_gather_into_tensor(roots, torch.from_numpy(levels[-1].copy()).cuda())
+        return leaves, levels
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- resident-input leg ----
+    for _ in range(args.warmup):
+        step_resident()
+    barrier()
+    dev.ctx.timing_read(reset=True)
+    dev.ctx.timing_enable(True)
+    launches0 = dev.ctx.stats()["kernel_launches"]
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        step_resident()
+    e1.record(stream)
+    barrier()
+    ms = max_over_ranks(e0.elapsed_time(e1))
+    tim = dev.ctx.timing_read(reset=True)
+    dev.ctx.timing_enable(False)
+    launches = dev.ctx.stats()["kernel_launches"] - launches0
+    root_resident = bytes(d_levels[-32:].cpu().numpy())
+
+    if args.profile:
+        sampler.stop()
+        if rank == 0:
+            print(json.dumps({"profile_run": True, "ms_per_step": ms / args.steps, "kernel_ms": {k: v[0] / max(1, v[1]) for k, v in tim.items()}, "gpu_launches": launches}))
+        dev.ctx.close()
+        return
+
+    # ---- end-to-end leg: host pointers in, leaves + tree out ----
+    for _ in range(max(1, args.warmup // 2)):
+        step_e2e()
+    barrier()
+    s0 = dev.ctx.stats()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        leaves, levels = step_e2e()
+    barrier()
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    clocks = sampler.stop()
+    s1 = dev.ctx.stats()
+    assert bytes(levels[-1]) == root_resident, "the two legs disagree on the root"
+
+    enc_bytes = rows * nn * 8
+    value = world * enc_bytes * args.steps / (ms * 1e-3) / 1e9
+    e2e_v = world * enc_bytes * args.steps / e2e_s / 1e9
+    enc_ms = tim["encode"][0] / max(1, tim["encode"][1])
+    hash_ms = tim["hash"][0] / max(1, tim["hash"][1])
+    mer_ms = tim["merkle"][0] / max(1, tim["merkle"][1])
+    alg_bytes = 8 * rows * (n + q) + 8 * rows * nn
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except OSError:
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    achieved = alg_bytes / (enc_ms * 1e-3) / 1e9
+
+    cpu = None
+    if world == 1 and rank == 0:
+        sys.path.insert(0, os.path.join(ROOT, "oracle"))
+        import hl_oracle as o
+
+        rows_s = 32
+        sec = cpu_commit_sample(o, rows_s, "")
+        rows_s = int(min(rows, max(32, rows_s * 10.0 / max(sec, 1e-3)) // 8 * 8))  # about ten seconds of CPU work
+        sec = cpu_commit_sample(o, rows_s, "")
+        cpu = {"value": rows_s * nn * 8 / sec / 1e9, "unit": "GB/s", "cores": o.num_threads(), "kind": "port",
+               "sample": f"{rows_s} of {rows} rows at the same n/nn/q, {sec:.1f} s: encode + column hash + salt + tree; C restatement "
+                         "(OpenMP) of the reference's Rust CPU path, which cannot be built in this image"}
+
+    if rank == 0:
+        line = {
+            "metric": "ligero_commit_GBps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": value / world / PUBLISHED_GBPS if world == 1 else None,
+            "dtype": "u64", "data": "synthetic", "config": workload_config(world),
+            "e2e": {"value": e2e_v, "unit": "GB/s", "h2d_bytes_per_step": (s1["bytes_h2d"] - s0["bytes_h2d"]) // args.steps,
+                    "d2h_bytes_per_step": (s1["bytes_d2h"] - s0["bytes_d2h"]) // args.steps, "ms_per_step": e2e_s * 1e3 / args.steps},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "kernel": "k_encode_fast<14,512>", "achieved": achieved, "peak": peak,
+                         "peak_source": "MEASURED_PEAKS.json hbm_gbs" if peaks else "fallback 6650 GB/s", "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "algorithmic_bytes_per_launch": alg_bytes, "ms_per_launch": enc_ms,
+                         "note": "integer-issue bound kernel (64-bit modular multiplies on the IMAD pipe); HBM fraction reported as the contract asks"},
+            "kernel_ms_per_step": {"encode": enc_ms, "column_hash": hash_ms, "salt_and_tree": mer_ms},
+            "cpu_baseline": cpu,
+            "root": root_resident.hex(),
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    dev.ctx.close()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--profile", action="store_true", help="resident-input leg only (for a run under a profiler)")
+    args = ap.parse_args()
+    rank, local_rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    if args.impl == "reference":
+        run_reference(args, rank)
+    else:
+        run_b200(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

@@ -97,6 +97,11 @@ int hl_b200_merkle(hl_ctx* ctx, const uint8_t* leaves32, const uint8_t* salts32,
 int hl_b200_store_merkle(hl_store* store, const uint8_t* salts32, const uint8_t* leaf_key32, const uint8_t* node_key32,
                          uint8_t* levels_out);
 
+/* The same, device to device and asynchronous on the context's stream: d_salts32 (nn x 32 bytes, or
+ * NULL) and d_levels_out ((2 nn - 1) x 32 bytes) are device memory; the root is the last 32 bytes. */
+int hl_b200_store_merkle_dev(hl_store* store, const uint8_t* d_salts32, const uint8_t* leaf_key32, const uint8_t* node_key32,
+                             uint8_t* d_levels_out);
+
 /* ---- EncodedStore::fold_rows / fold_rows_with_pads (pcs/backend.rs:33-59; CPU body
  * pcs.rs:342-378, 976-1000) ----
  * rhos: k x rows Fp2.  out: k vectors of n Fp2 (with_pads == 0) or n + q Fp2 (with_pads != 0,
@@ -120,6 +125,17 @@ typedef struct {
     uint64_t declines;          /* calls that returned an error */
 } hl_stats;
 int hl_b200_stats(hl_ctx* ctx, hl_stats* out);
+
+/* ---- per-kernel-family device time: the phase clock of timing.rs:1-130 / HL_METAL_TIMING
+ * (metal.rs:2148-2179), taken with CUDA events on the context's stream.  Off by default. ---- */
+enum { HL_T_ENCODE = 0, HL_T_HASH = 1, HL_T_MERKLE = 2, HL_T_FOLD = 3, HL_T_GATHER = 4, HL_T_ROUNDS = 5, HL_T_LOGUP = 6, HL_T_COUNT = 8 };
+typedef struct {
+    double ms[HL_T_COUNT];        /* summed device time per family since the last reset */
+    uint64_t spans[HL_T_COUNT];   /* timed spans per family (one span = the family's launches of one call) */
+} hl_timing;
+int hl_b200_timing_enable(hl_ctx* ctx, int on);
+/* Waits for the stream, then reports (and with reset != 0 clears) the accumulated spans. */
+int hl_b200_timing_read(hl_ctx* ctx, hl_timing* out, int reset);
 
 #ifdef __cplusplus
 }

@@ -37,6 +37,7 @@ SIGNATURES = {
     "hl_b200_commit_zk_dev": (_int, [_vp, _u32, _u32, _vp, _sz, _vp, _sz, _vp, _vp, _pp, _vp]),
     "hl_b200_merkle": (_int, [_vp, _vp, _vp, _sz, _vp, _vp, _vp]),
     "hl_b200_store_merkle": (_int, [_vp, _vp, _vp, _vp, _vp]),
+    "hl_b200_store_merkle_dev": (_int, [_vp, _vp, _vp, _vp, _vp]),
     "hl_b200_store_fold": (_int, [_vp, _vp, _sz, _int, _vp]),
     "hl_b200_store_columns": (_int, [_vp, _vp, _sz, _vp]),
     "hl_b200_store_shape": (_int, [_vp, C.POINTER(_sz), C.POINTER(_sz), C.POINTER(_sz), C.POINTER(_sz)]),
@@ -45,6 +46,16 @@ SIGNATURES = {
     "hl_b200_store_free": (None, [_vp]),
     "hl_b200_stats": (_int, [_vp, C.POINTER(Stats)]),
 }
+
+T_NAMES = ("encode", "hash", "merkle", "fold", "gather", "rounds", "logup")
+
+
+class Timing(C.Structure):
+    _fields_ = [("ms", C.c_double * 8), ("spans", C.c_uint64 * 8)]
+
+
+SIGNATURES["hl_b200_timing_enable"] = (_int, [_vp, _int])
+SIGNATURES["hl_b200_timing_read"] = (_int, [_vp, C.POINTER(Timing), _int])
 
 _lib = None
 

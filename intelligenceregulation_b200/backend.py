@@ -93,6 +93,15 @@ class Context:
         self.check(self.lib.hl_b200_stats(self.h, C.byref(s)))
         return {n: int(getattr(s, n)) for n, _ in s._fields_}
 
+    def timing_enable(self, on: bool = True) -> None:
+        self.check(self.lib.hl_b200_timing_enable(self.h, 1 if on else 0))
+
+    def timing_read(self, reset: bool = True) -> dict:
+        """Device milliseconds and span counts per kernel family since the last reset (waits for the stream)."""
+        t = _lib.Timing()
+        self.check(self.lib.hl_b200_timing_read(self.h, C.byref(t), 1 if reset else 0))
+        return {n: (float(t.ms[i]), int(t.spans[i])) for i, n in enumerate(_lib.T_NAMES)}
+
     def probe_field(self, a, b) -> np.ndarray:
         """metal_probe_field: (a+b, a-b, a*b) per pair, shape (n, 3)."""
         a, b = _u64(a), _u64(b)
@@ -151,6 +160,10 @@ class B200Commit:
         s = np.ascontiguousarray(salts, dtype=np.uint8) if salts is not None else None
         self.ctx.check(self.ctx.lib.hl_b200_store_merkle(self.h, _ptr(s), _ptr(leaf_key), _ptr(node_key), _ptr(out)))
         return out
+
+    def merkle_dev(self, d_salts: int, leaf_key: Optional[bytes], node_key: Optional[bytes], d_levels: int) -> None:
+        """Salted leaves and tree, device to device, asynchronous on the context's stream."""
+        self.ctx.check(self.ctx.lib.hl_b200_store_merkle_dev(self.h, C.c_void_p(d_salts), _ptr(leaf_key), _ptr(node_key), C.c_void_p(d_levels)))
 
     def encoded_dev(self) -> int:
         return int(self.ctx.lib.hl_b200_store_encoded_dev(self.h) or 0)

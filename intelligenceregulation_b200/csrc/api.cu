@@ -101,9 +101,51 @@ int log2_exact(size_t v) {
     return l;
 }
 
+static cudaEvent_t take_event(hl_ctx* c) {
+    if (!c->ev_pool.empty()) { cudaEvent_t e = c->ev_pool.back(); c->ev_pool.pop_back(); return e; }
+    cudaEvent_t e = nullptr;
+    cudaEventCreate(&e);
+    return e;
+}
+
+Timed::Timed(hl_ctx* ctx, int cls) : c(ctx), on(ctx->timing) {
+    if (!on) return;
+    s.a = take_event(c); s.b = take_event(c); s.cls = cls;
+    cudaEventRecord(s.a, c->stream);
+}
+Timed::~Timed() {
+    if (!on) return;
+    cudaEventRecord(s.b, c->stream);
+    c->spans.push_back(s);
+}
+
 }  // namespace hlapi
 
 extern "C" {
+
+int hl_b200_timing_enable(hl_ctx* c, int on) {
+    if (!c) return HL_B200_ERR_ARG;
+    std::lock_guard<std::mutex> g(c->mu);
+    c->timing = on != 0;
+    return HL_B200_OK;
+}
+
+int hl_b200_timing_read(hl_ctx* c, hl_timing* out, int reset) {
+    if (!c || !out) return HL_B200_ERR_ARG;
+    std::lock_guard<std::mutex> g(c->mu);
+    cudaSetDevice(c->device);
+    int rc = sync(c, "timing_read");
+    if (rc) return rc;
+    for (auto& s : c->spans) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, s.a, s.b) == cudaSuccess) { c->timing_acc.ms[s.cls] += ms; c->timing_acc.spans[s.cls]++; }
+        c->ev_pool.push_back(s.a); c->ev_pool.push_back(s.b);
+    }
+    c->spans.clear();
+    *out = c->timing_acc;
+    if (reset) c->timing_acc = hl_timing{};
+    return HL_B200_OK;
+}
 
 int hl_b200_init(int device, hl_ctx** out) {
     if (!out) return HL_B200_ERR_ARG;
@@ -137,6 +179,8 @@ void hl_b200_shutdown(hl_ctx* c) {
     cudaSetDevice(c->device);
     cudaStreamSynchronize(c->stream);
     for (auto& kv : c->tw) cudaFree(kv.second);
+    for (auto& s : c->spans) { cudaEventDestroy(s.a); cudaEventDestroy(s.b); }
+    for (auto e : c->ev_pool) cudaEventDestroy(e);
     cudaStreamDestroy(c->own_stream);
     delete c;
 }

@@ -20,6 +20,11 @@ struct hl_ctx {
     std::map<u32, u64*> tw;  // log2 nn -> nn powers of the nn-th root
     std::string label, last_error;
     hl_stats stats{};
+    bool timing = false;
+    struct Span { cudaEvent_t a, b; int cls; };
+    std::vector<Span> spans;          // recorded, not yet read
+    std::vector<cudaEvent_t> ev_pool;  // events ready for reuse
+    hl_timing timing_acc{};
     size_t alloc_live = 0;   // bytes handed out and not yet returned
     size_t alloc_cap = 0;    // 0 = none; a host-side failure-injection cap (mod.rs:121 set_alloc_cap_for_test)
 };
@@ -48,4 +53,13 @@ int sync(hl_ctx* c, const char* what);
 int root_powers(hl_ctx* c, u32 lognn, const u64** out);
 int upload_key(hl_ctx* c, const uint8_t* key32, uint32_t** d_key);
 int log2_exact(size_t v);
+
+// Brackets the launches of one kernel family with two events when the context's timing is on.
+struct Timed {
+    hl_ctx* c;
+    hl_ctx::Span s;
+    bool on;
+    Timed(hl_ctx* c, int cls);
+    ~Timed();
+};
 }  // namespace hlapi

@@ -32,11 +32,13 @@ int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* 
         a.data = st->d_data; a.pads = st->d_pads; a.pows = d_pows; a.tw_nn = tw; a.enc = st->d_enc; a.scratch = scratch;
         a.rows = st->rows; a.q = st->zk ? st->q : 0; a.T = T; a.logr = st->logr; a.zk = st->zk ? 1 : 0;
         a.ninv = gl_inv((u64)n);
+        Timed t(c, HL_T_ENCODE);
         cudaError_t e = hlk::encode_rows(a, logn, c->fast_encoder, c->sm_count, scratch_words, c->stream, &st->encoder_path);
         c->stats.kernel_launches += 1;
         if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "row encoder launch", e);
     }
     if (!rc) {
+        Timed t(c, HL_T_HASH);
         cudaError_t e = hlk::hash_columns(st->d_enc, st->rows, (u32)nn, d_key, cvs, st->d_leaves, c->stream);
         c->stats.kernel_launches += nchunks > 1 ? 2 : 1;
         if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "column hash launch", e);
@@ -186,6 +188,7 @@ int hl_b200_store_fold(hl_store* st, const uint64_t* rhos, size_t k, int with_pa
     if (!rc) rc = dev_alloc(c, (void**)&d_out, ob);
     if (!rc) rc = h2d(c, d_rhos, rhos, rb);
     if (!rc) {
+        Timed t(c, HL_T_FOLD);
         // hiding form: the message is the resident data (the encoding is not systematic, pcs.rs:985-987);
         // plain form: the systematic positions of the encoding (pcs.rs:332-340)
         cudaError_t e = st->zk ? hlk::fold_rows(st->d_data, st->rows, n, n, 1, d_rhos, (u32)k, d_out, w, 0, c->stream)
@@ -220,6 +223,7 @@ int hl_b200_store_columns(hl_store* st, const uint64_t* idx, size_t nidx, uint64
     if (!rc) rc = dev_alloc(c, (void**)&d_out, ob);
     if (!rc) rc = h2d(c, d_idx, idx, nidx * 8);
     if (!rc) {
+        Timed t(c, HL_T_GATHER);
         cudaError_t e = hlk::gather_columns(st->d_enc, st->rows, st->nn(), d_idx, (u32)nidx, d_out, c->stream);
         c->stats.kernel_launches++;
         if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "gather launch", e);
@@ -231,14 +235,39 @@ int hl_b200_store_columns(hl_store* st, const uint64_t* idx, size_t nidx, uint64
     return rc;
 }
 
+// salted leaves + all levels into d_levels, from device leaves (and device salts, or none)
+static int merkle_on_device(hl_ctx* c, const uint32_t* d_leaves, const uint32_t* d_salts, size_t nn, const uint8_t* leaf_key32,
+                            const uint8_t* node_key32, uint32_t* d_levels) {
+    uint32_t *d_lk = nullptr, *d_nk = nullptr;
+    int rc = upload_key(c, leaf_key32, &d_lk);
+    if (!rc) rc = upload_key(c, node_key32, &d_nk);
+    if (!rc) {
+        Timed t(c, HL_T_MERKLE);
+        cudaError_t e;
+        if (d_salts) {
+            e = hlk::salt_leaves(d_leaves, d_salts, (u32)nn, d_lk, d_levels, c->stream);
+            c->stats.kernel_launches++;
+        } else {
+            e = cudaMemcpyAsync(d_levels, d_leaves, nn * 32, cudaMemcpyDeviceToDevice, c->stream);
+        }
+        if (e == cudaSuccess) {
+            e = hlk::merkle_levels(d_levels, (u32)nn, d_nk, c->stream);
+            for (size_t w = nn; w > 2048; w >>= 1) c->stats.kernel_launches++;
+            if (nn > 1) c->stats.kernel_launches++;
+        }
+        if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "merkle launch", e);
+    }
+    if (d_lk) dev_free(c, d_lk, 32);
+    if (d_nk) dev_free(c, d_nk, 32);
+    return rc;
+}
+
 static int merkle_common(hl_ctx* c, const uint32_t* d_leaves_in, const uint8_t* h_leaves, const uint8_t* salts32, size_t nn,
                          const uint8_t* leaf_key32, const uint8_t* node_key32, uint8_t* levels_out) {
     if (log2_exact(nn) < 0 || nn > ((size_t)1 << 26)) return fail(c, HL_B200_ERR_ARG, "merkle: leaf count must be a power of two");
     const size_t lv_bytes = (2 * nn - 1) * 32;
-    uint32_t *d_levels = nullptr, *d_in = nullptr, *d_salts = nullptr, *d_lk = nullptr, *d_nk = nullptr;
+    uint32_t *d_levels = nullptr, *d_in = nullptr, *d_salts = nullptr;
     int rc = dev_alloc(c, (void**)&d_levels, lv_bytes);
-    if (!rc) rc = upload_key(c, leaf_key32, &d_lk);
-    if (!rc) rc = upload_key(c, node_key32, &d_nk);
     const uint32_t* leaves = d_leaves_in;
     if (!rc && !leaves) {
         rc = dev_alloc(c, (void**)&d_in, nn * 32);
@@ -248,28 +277,13 @@ static int merkle_common(hl_ctx* c, const uint32_t* d_leaves_in, const uint8_t* 
     if (!rc && salts32) {
         rc = dev_alloc(c, (void**)&d_salts, nn * 32);
         if (!rc) rc = h2d(c, d_salts, salts32, nn * 32);
-        if (!rc) {
-            cudaError_t e = hlk::salt_leaves(leaves, d_salts, (u32)nn, d_lk, d_levels, c->stream);
-            c->stats.kernel_launches++;
-            if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "salt launch", e);
-        }
-    } else if (!rc) {
-        cudaError_t e = cudaMemcpyAsync(d_levels, leaves, nn * 32, cudaMemcpyDeviceToDevice, c->stream);
-        if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "leaf copy", e);
     }
-    if (!rc) {
-        cudaError_t e = hlk::merkle_levels(d_levels, (u32)nn, d_nk, c->stream);
-        for (size_t w = nn; w > 2048; w >>= 1) c->stats.kernel_launches++;
-        if (nn > 1) c->stats.kernel_launches++;
-        if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "merkle launch", e);
-    }
+    if (!rc) rc = merkle_on_device(c, leaves, d_salts, nn, leaf_key32, node_key32, d_levels);
     if (!rc) rc = d2h(c, levels_out, d_levels, lv_bytes);
     if (!rc) rc = sync(c, "merkle");
     dev_free(c, d_levels, lv_bytes);
     if (d_in) dev_free(c, d_in, nn * 32);
     if (d_salts) dev_free(c, d_salts, nn * 32);
-    if (d_lk) dev_free(c, d_lk, 32);
-    if (d_nk) dev_free(c, d_nk, 32);
     if (!rc) c->stats.merkles++;
     return rc;
 }
@@ -289,6 +303,17 @@ int hl_b200_store_merkle(hl_store* st, const uint8_t* salts32, const uint8_t* le
     std::lock_guard<std::mutex> g(c->mu);
     cudaSetDevice(c->device);
     return merkle_common(c, st->d_leaves, nullptr, salts32, st->nn(), leaf_key32, node_key32, levels_out);
+}
+
+int hl_b200_store_merkle_dev(hl_store* st, const uint8_t* d_salts32, const uint8_t* leaf_key32, const uint8_t* node_key32,
+                             uint8_t* d_levels_out) {
+    if (!st || !d_levels_out) return HL_B200_ERR_ARG;
+    hl_ctx* c = st->ctx;
+    std::lock_guard<std::mutex> g(c->mu);
+    cudaSetDevice(c->device);
+    int rc = merkle_on_device(c, st->d_leaves, (const uint32_t*)d_salts32, st->nn(), leaf_key32, node_key32, (uint32_t*)d_levels_out);
+    if (!rc) c->stats.merkles++;
+    return rc;
 }
 
 }  // extern "C"
