@@ -179,7 +179,8 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     h_salts = torch.from_numpy(np.frombuffer(b3.blake3(b"bench-salts-%d" % block).digest(length=nn * 32), dtype=np.uint8).copy()).pin_memory()
 
     dev = backend.B200Backend(device=local_rank)
-    stream = torch.cuda.current_stream()
+    stream = torch.cuda.Stream()  # the library, torch's copies and the timing events all use this one stream
+    torch.cuda.set_stream(stream)
     dev.ctx.set_stream(stream.cuda_stream)
     d_data, d_pads, d_pows, d_salts = (t.cuda(non_blocking=True) for t in (h_data, h_pads, h_pows, h_salts))
     d_levels = torch.empty((2 * nn - 1) * 32, dtype=torch.uint8, device="cuda")
@@ -216,14 +217,15 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
         return float(t.item())
 
     # ---- resident-input leg ----
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     for _ in range(args.warmup):
         step_resident()
     barrier()
     dev.ctx.timing_read(reset=True)
     dev.ctx.timing_enable(True)
     launches0 = dev.ctx.stats()["kernel_launches"]
-    sampler = ClockSampler(local_rank)
-    sampler.start()
+    sampler.rows.clear()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     for _ in range(args.steps):
@@ -311,7 +313,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--profile", action="store_true", help="resident-input leg only (for a run under a profiler)")

@@ -117,6 +117,48 @@ const uint64_t* hl_b200_store_encoded_dev(hl_store* store);
 const uint8_t* hl_b200_store_leaves_dev(hl_store* store);
 void hl_b200_store_free(hl_store* store);
 
+/* ---- SumcheckRounds (sumcheck/rounds.rs:22-28; CPU evaluator ClosureRounds :52-167) ----
+ * k tables of 2^n_vars Fp2 (table-major, variable 0 = most significant index bit) and a slot polynomial
+ * from a fixed family; round j returns the UNMASKED values at 0..=degree of
+ * sum_i poly(T(i) + d (T(i + half) - T(i))), fold applies T[i] += r (T[i + half] - T[i]).
+ *   HL_POLY_PROD     product of the k tables, degree = k <= 6 (matmul slots v0*v1: argument.rs:2174-2203)
+ *   HL_POLY_ZC       t0 * (t1 * t2 - t3), k = 4, degree 3 (zero-check with an eq table)
+ *   HL_POLY_LOGUP_Q  t0 * (t1 * (alpha - t2) - 1), k = 3, degree 3, coefs[0] = alpha (LogUp helper constraint)
+ *   HL_POLY_LOGUP_T  t0 * (t1 * (alpha - t2) - t3), k = 4, degree 3 (table helper, layout.rs slot 19) */
+enum { HL_POLY_PROD = 0, HL_POLY_ZC = 1, HL_POLY_LOGUP_Q = 2, HL_POLY_LOGUP_T = 3 };
+int hl_b200_rounds_new(hl_ctx* ctx, int poly, size_t k, uint32_t n_vars, uint32_t degree, const uint64_t* tables,
+                       const uint64_t* coefs, size_t ncoefs, hl_rounds** out);
+/* SumcheckRounds::round: sums = degree + 1 Fp2.  eval_one == 0 skips the point 1 (left zero): the caller
+ * recovers s(1) = claim - s(0) (rounds.rs:94-99,137-140). */
+int hl_b200_rounds_round(hl_rounds* r, uint32_t j, int eval_one, uint64_t* sums);
+/* SumcheckRounds::fold */
+int hl_b200_rounds_fold(hl_rounds* r, const uint64_t challenge[2]);
+/* SumcheckRounds::finals: k Fp2, the caller's table order */
+int hl_b200_rounds_finals(hl_rounds* r, uint64_t* out);
+void hl_b200_rounds_free(hl_rounds* r);
+
+/* The transcript position a device batch starts from and ends at (transcript.rs:226-243: state(),
+ * counter(), fs_key()), with the running unmasked claim of the s(1) recovery. */
+typedef struct {
+    uint8_t state[32];
+    uint64_t counter;
+    uint8_t key[32];
+    int32_t keyed;         /* 0: legacy unkeyed transcript */
+    int32_t recover_one;   /* rounds.rs:81-86 */
+    int32_t have_claim;    /* claim[] holds the exact unmasked sum for the first round of the batch */
+    int32_t reserved;
+    uint64_t claim[2];
+} hl_fs_state;
+/* `nd` consecutive rounds entirely on the device, as prove_rounds (rounds.rs:33-48) drives them under
+ * a CfsMasker (sumcheck.rs:282-299): round sums, s(1) recovery, masked message s + c g_j, absorb
+ * "sc-round", squeeze r_j, fold.  mask_coeffs NULL = no mask; otherwise mask_vars * degree + 2 Fp2 in
+ * the layout of sumcheck.rs:199-200 and the batch must start at round 0.
+ * out: per round (degree+1) unmasked sums, (degree+1) absorbed (masked) values, then r_j  (Fp2 each).
+ * fs is updated to the position after the batch.  The caller replays the batch through its own
+ * transcript and compares (metal.rs:4156-4171); nothing here is trusted blind. */
+int hl_b200_rounds_batched(hl_rounds* r, uint32_t nd, hl_fs_state* fs, const uint64_t* mask_coeffs, uint32_t mask_vars,
+                           const uint64_t mask_c[2], uint64_t* out);
+
 /* ---- counters: GpuStats / dev_stats (hashline/src/gpu/mod.rs:890-908) ---- */
 typedef struct {
     uint64_t commits, folds, gathers, merkles, round_batches;

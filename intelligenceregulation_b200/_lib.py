@@ -47,6 +47,20 @@ SIGNATURES = {
     "hl_b200_stats": (_int, [_vp, C.POINTER(Stats)]),
 }
 
+class FsState(C.Structure):
+    _fields_ = [("state", C.c_uint8 * 32), ("counter", C.c_uint64), ("key", C.c_uint8 * 32), ("keyed", C.c_int32),
+                ("recover_one", C.c_int32), ("have_claim", C.c_int32), ("reserved", C.c_int32), ("claim", C.c_uint64 * 2)]
+
+
+SIGNATURES.update({
+    "hl_b200_rounds_new": (_int, [_vp, _int, _sz, _u32, _u32, _vp, _vp, _sz, _pp]),
+    "hl_b200_rounds_round": (_int, [_vp, _u32, _int, _vp]),
+    "hl_b200_rounds_fold": (_int, [_vp, _vp]),
+    "hl_b200_rounds_finals": (_int, [_vp, _vp]),
+    "hl_b200_rounds_free": (None, [_vp]),
+    "hl_b200_rounds_batched": (_int, [_vp, _u32, C.POINTER(FsState), _vp, _u32, _vp, _vp]),
+})
+
 T_NAMES = ("encode", "hash", "merkle", "fold", "gather", "rounds", "logup")
 
 

@@ -229,3 +229,76 @@ class B200Backend:
         self.ctx.check(self.ctx.lib.hl_b200_commit_zk_dev(self.ctx.h, log_cols, inv_rate, C.c_void_p(d_data), rows, C.c_void_p(d_pads), q,
                                                             C.c_void_p(d_pows), _ptr(key), C.byref(h), C.c_void_p(d_leaves)))
         return B200Commit(self.ctx, h)
+
+
+POLY_PROD, POLY_ZC, POLY_LOGUP_Q, POLY_LOGUP_T = 0, 1, 2, 3
+
+
+class B200Rounds:
+    """``impl SumcheckRounds`` (sumcheck/rounds.rs:22-28) with the tables resident on the device, plus the
+    device-side batch of rounds the reference's Metal evaluator runs (metal.rs:4141 ``masked_prove``)."""
+
+    def __init__(self, ctx: Context, poly: int, tables: np.ndarray, degree: int, coefs=None):
+        tables = _u64(tables)
+        assert tables.ndim == 3 and tables.shape[2] == 2
+        self.ctx, self.k = ctx, tables.shape[0]
+        self._n_vars = int(tables.shape[1]).bit_length() - 1
+        assert tables.shape[1] == 1 << self._n_vars
+        self._degree = degree
+        cf = _u64(coefs).reshape(-1, 2) if coefs is not None else None
+        h = C.c_void_p()
+        ctx.check(ctx.lib.hl_b200_rounds_new(ctx.h, poly, self.k, self._n_vars, degree, _ptr(tables), _ptr(cf),
+                                             0 if cf is None else cf.shape[0], C.byref(h)))
+        self.h = h
+
+    def n_vars(self) -> int:
+        return self._n_vars
+
+    def degree(self) -> int:
+        return self._degree
+
+    def round(self, j: int, eval_one: bool = True) -> np.ndarray:
+        out = np.zeros((self._degree + 1, 2), dtype=np.uint64)
+        self.ctx.check(self.ctx.lib.hl_b200_rounds_round(self.h, j, 1 if eval_one else 0, _ptr(out)))
+        return out
+
+    def fold(self, r) -> None:
+        rr = np.array([int(r[0]), int(r[1])], dtype=np.uint64)
+        self.ctx.check(self.ctx.lib.hl_b200_rounds_fold(self.h, _ptr(rr)))
+
+    def finals(self) -> np.ndarray:
+        out = np.zeros((self.k, 2), dtype=np.uint64)
+        self.ctx.check(self.ctx.lib.hl_b200_rounds_finals(self.h, _ptr(out)))
+        return out
+
+    def batched(self, nd: int, state: bytes, counter: int, key: Optional[bytes] = None, mask: Optional[np.ndarray] = None,
+                mask_vars: int = 0, mask_c=(0, 0), recover_one: bool = False, claim=None):
+        """`nd` rounds on the device from transcript position (state, counter).  Returns
+        (sums (nd, D+1, 2), absorbed (nd, D+1, 2), challenges (nd, 2), new state, new counter, running claim)."""
+        fs = _lib.FsState()
+        C.memmove(fs.state, state, 32)
+        fs.counter = counter
+        if key:
+            C.memmove(fs.key, key, 32)
+        fs.keyed = 1 if key else 0
+        fs.recover_one = 1 if recover_one else 0
+        fs.have_claim = 1 if claim is not None else 0
+        if claim is not None:
+            fs.claim[0], fs.claim[1] = int(claim[0]), int(claim[1])
+        np_ = self._degree + 1
+        out = np.zeros((nd, 2 * np_ + 1, 2), dtype=np.uint64)
+        mk = _u64(mask).reshape(-1, 2) if mask is not None else None
+        mc = np.array([int(mask_c[0]), int(mask_c[1])], dtype=np.uint64)
+        self.ctx.check(self.ctx.lib.hl_b200_rounds_batched(self.h, nd, C.byref(fs), _ptr(mk), mask_vars, _ptr(mc), _ptr(out)))
+        return out[:, :np_], out[:, np_:2 * np_], out[:, 2 * np_], bytes(fs.state), int(fs.counter), (int(fs.claim[0]), int(fs.claim[1]))
+
+    def free(self) -> None:
+        if self.h:
+            self.ctx.lib.hl_b200_rounds_free(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass

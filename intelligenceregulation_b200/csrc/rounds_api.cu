@@ -1,0 +1,226 @@
+// C ABI: the sumcheck evaluator (`impl SumcheckRounds`, sumcheck/rounds.rs:22-28) and its
+// device-side batch of rounds with the Fiat-Shamir step (the reference's Metal form:
+// metal.rs:3509-3669 MetalRounds, :4141-4192 TailedRounds::masked_prove).
+#include <cstring>
+
+#include "api_internal.h"
+#include "sumcheck.h"
+
+using namespace hlapi;
+
+struct hl_rounds {
+    hl_ctx* ctx = nullptr;
+    int poly = 0;
+    u32 k = 0, n_vars = 0, degree = 0, next = 0;
+    size_t stride = 0, len = 0, ncoefs = 0;
+    u32 max_blocks = 0;
+    u64* d_tables = nullptr;
+    u64* d_coefs = nullptr;
+    u64* d_partials = nullptr;
+    u64* d_out = nullptr;      // n_vars rows of (2 (degree+1) + 1) Fp2
+    u64* d_inv_den = nullptr;
+    hlk::ScState* d_state = nullptr;
+    size_t out_row() const { return (2 * ((size_t)degree + 1) + 1) * 2; }
+};
+
+namespace {
+
+void free_rounds(hl_rounds* r) {
+    hl_ctx* c = r->ctx;
+    dev_free(c, r->d_tables, r->k * r->stride * 16);
+    dev_free(c, r->d_coefs, (r->ncoefs ? r->ncoefs : 1) * 16);
+    dev_free(c, r->d_partials, (size_t)r->max_blocks * (r->degree + 1) * 16);
+    dev_free(c, r->d_out, (r->n_vars ? r->n_vars : 1) * r->out_row() * 8);
+    dev_free(c, r->d_inv_den, ((size_t)r->degree + 1) * 8);
+    dev_free(c, r->d_state, sizeof(hlk::ScState));
+    delete r;
+}
+
+// launches round j's kernels; the caller holds the context lock
+int launch_round(hl_rounds* r, int eval_one, int fs, int use_claim, int recover, const u64* d_mask, const u64* d_hs, int mask_vars) {
+    hl_ctx* c = r->ctx;
+    const u32 half = (u32)(r->len / 2);
+    const u32 nb = hlk::sc_round_blocks(half, c->sm_count);
+    cudaError_t e = hlk::sc_round(r->poly, (int)r->k, r->d_tables, r->stride, half, r->d_coefs, eval_one, r->d_partials, nb, c->stream);
+    c->stats.kernel_launches++;
+    if (e != cudaSuccess) return fail(c, HL_B200_ERR_DEVICE, "round launch", e);
+    hlk::ScStep a;
+    a.partials = r->d_partials; a.nblocks = nb; a.degree = (int)r->degree; a.round = (int)r->next;
+    a.use_claim = use_claim; a.recover = recover; a.fs = fs; a.mask = d_mask; a.mask_half_suffix = d_hs; a.mask_vars = mask_vars;
+    a.inv_den = r->d_inv_den; a.state = r->d_state; a.out = r->d_out;
+    e = hlk::sc_step(a, c->stream);
+    c->stats.kernel_launches++;
+    if (e != cudaSuccess) return fail(c, HL_B200_ERR_DEVICE, "round step launch", e);
+    return HL_B200_OK;
+}
+
+int launch_fold(hl_rounds* r) {
+    hl_ctx* c = r->ctx;
+    cudaError_t e = hlk::sc_fold(r->d_tables, r->stride, (u32)(r->len / 2), r->k, r->d_state, c->stream);
+    c->stats.kernel_launches++;
+    if (e != cudaSuccess) return fail(c, HL_B200_ERR_DEVICE, "fold launch", e);
+    r->len /= 2;
+    r->next++;
+    return HL_B200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int hl_b200_rounds_new(hl_ctx* c, int poly, size_t k, uint32_t n_vars, uint32_t degree, const uint64_t* tables,
+                       const uint64_t* coefs, size_t ncoefs, hl_rounds** out) {
+    if (!c || !tables || !out) return fail(c, HL_B200_ERR_ARG, "rounds_new: null argument");
+    if (n_vars > 30) return fail(c, HL_B200_ERR_UNSUPPORTED, "rounds_new: more than 30 variables");
+    if (!hlk::sc_supported(poly, (int)k, (int)degree)) return fail(c, HL_B200_ERR_UNSUPPORTED, "rounds_new: polynomial family / table count / degree");
+    if ((poly == hlk::POLY_LOGUP_Q || poly == hlk::POLY_LOGUP_T) && (!coefs || ncoefs < 1)) return fail(c, HL_B200_ERR_ARG, "rounds_new: alpha missing");
+    std::lock_guard<std::mutex> g(c->mu);
+    cudaSetDevice(c->device);
+    hl_rounds* r = new hl_rounds();
+    r->ctx = c; r->poly = poly; r->k = (u32)k; r->n_vars = n_vars; r->degree = degree; r->ncoefs = ncoefs;
+    r->stride = r->len = (size_t)1 << n_vars;
+    r->max_blocks = hlk::sc_round_blocks((u32)(r->len / 2), c->sm_count);
+    u64 inv_den[hlk::SC_MAX_POINTS];
+    for (u32 i = 0; i <= degree; i++) {
+        u64 den = 1;
+        for (u32 j = 0; j <= degree; j++)
+            if (j != i) den = gl_mul(den, gl_from_i64((long long)i - (long long)j));
+        inv_den[i] = gl_inv(den);
+    }
+    int rc = dev_alloc(c, (void**)&r->d_tables, k * r->stride * 16);
+    if (!rc) rc = dev_alloc(c, (void**)&r->d_coefs, (ncoefs ? ncoefs : 1) * 16);
+    if (!rc) rc = dev_alloc(c, (void**)&r->d_partials, (size_t)r->max_blocks * (degree + 1) * 16);
+    if (!rc) rc = dev_alloc(c, (void**)&r->d_out, (n_vars ? n_vars : 1) * r->out_row() * 8);
+    if (!rc) rc = dev_alloc(c, (void**)&r->d_inv_den, ((size_t)degree + 1) * 8);
+    if (!rc) rc = dev_alloc(c, (void**)&r->d_state, sizeof(hlk::ScState));
+    if (!rc) rc = h2d(c, r->d_tables, tables, k * r->stride * 16);
+    if (!rc && ncoefs) rc = h2d(c, r->d_coefs, coefs, ncoefs * 16);
+    if (!rc) rc = h2d(c, r->d_inv_den, inv_den, ((size_t)degree + 1) * 8);
+    if (!rc) {
+        cudaError_t e = cudaMemsetAsync(r->d_state, 0, sizeof(hlk::ScState), c->stream);
+        if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "state clear", e);
+    }
+    if (!rc) rc = sync(c, "rounds_new");
+    if (rc) { cudaStreamSynchronize(c->stream); free_rounds(r); return rc; }
+    *out = r;
+    return HL_B200_OK;
+}
+
+void hl_b200_rounds_free(hl_rounds* r) {
+    if (!r) return;
+    hl_ctx* c = r->ctx;
+    std::lock_guard<std::mutex> g(c->mu);
+    cudaSetDevice(c->device);
+    free_rounds(r);
+}
+
+int hl_b200_rounds_round(hl_rounds* r, uint32_t j, int eval_one, uint64_t* sums) {
+    if (!r || !sums) return HL_B200_ERR_ARG;
+    hl_ctx* c = r->ctx;
+    if (j != r->next || j >= r->n_vars) return fail(c, HL_B200_ERR_ARG, "rounds_round: round order (a round needs the preceding fold)");
+    std::lock_guard<std::mutex> g(c->mu);
+    cudaSetDevice(c->device);
+    int rc;
+    {
+        Timed t(c, HL_T_ROUNDS);
+        rc = launch_round(r, eval_one, 0, 0, 0, nullptr, nullptr, 0);
+    }
+    if (!rc) rc = d2h(c, sums, r->d_out + (size_t)j * r->out_row(), ((size_t)r->degree + 1) * 16);
+    if (!rc) rc = sync(c, "rounds_round");
+    return rc;
+}
+
+int hl_b200_rounds_fold(hl_rounds* r, const uint64_t rr[2]) {
+    if (!r || !rr) return HL_B200_ERR_ARG;
+    hl_ctx* c = r->ctx;
+    if (r->next >= r->n_vars) return fail(c, HL_B200_ERR_ARG, "rounds_fold: every variable is already folded");
+    std::lock_guard<std::mutex> g(c->mu);
+    cudaSetDevice(c->device);
+    int rc = h2d(c, (char*)r->d_state + offsetof(hlk::ScState, r), rr, 16);
+    if (!rc) {
+        Timed t(c, HL_T_ROUNDS);
+        rc = launch_fold(r);
+    }
+    if (!rc) rc = sync(c, "rounds_fold");
+    return rc;
+}
+
+int hl_b200_rounds_finals(hl_rounds* r, uint64_t* out) {
+    if (!r || !out) return HL_B200_ERR_ARG;
+    hl_ctx* c = r->ctx;
+    if (r->next != r->n_vars) return fail(c, HL_B200_ERR_ARG, "rounds_finals: finals need all folds");
+    std::lock_guard<std::mutex> g(c->mu);
+    cudaSetDevice(c->device);
+    int rc = HL_B200_OK;
+    for (u32 t = 0; t < r->k && !rc; t++) rc = d2h(c, out + 2 * t, r->d_tables + 2 * (size_t)t * r->stride, 16);
+    if (!rc) rc = sync(c, "rounds_finals");
+    return rc;
+}
+
+int hl_b200_rounds_batched(hl_rounds* r, uint32_t nd, hl_fs_state* fs, const uint64_t* mask_coeffs, uint32_t mask_vars,
+                           const uint64_t mask_c[2], uint64_t* out) {
+    if (!r || !fs || !out) return HL_B200_ERR_ARG;
+    hl_ctx* c = r->ctx;
+    if (nd == 0) return HL_B200_OK;
+    if (r->next + nd > r->n_vars) return fail(c, HL_B200_ERR_ARG, "rounds_batched: more rounds than variables left");
+    if (mask_coeffs && (r->next != 0 || !mask_c || mask_vars < r->n_vars || mask_vars > 63))
+        return fail(c, HL_B200_ERR_ARG, "rounds_batched: a masked batch starts at round 0 and its mask covers every variable");
+    if (fs->recover_one && r->degree < 1) return fail(c, HL_B200_ERR_ARG, "rounds_batched: claim recovery requires degree >= 1");
+    std::lock_guard<std::mutex> g(c->mu);
+    cudaSetDevice(c->device);
+    hlk::ScState st;
+    memset(&st, 0, sizeof st);
+    memcpy(st.state, fs->state, 32);
+    memcpy(st.key, fs->key, 32);
+    st.counter = fs->counter;
+    st.keyed = fs->keyed;
+    st.claim = f2(fs->claim[0], fs->claim[1]);
+    st.prod_prev = f2(1, 0);
+    u64 *d_mask = nullptr, *d_hs = nullptr;
+    const size_t mlen = mask_coeffs ? (size_t)mask_vars * r->degree + 2 : 0;
+    std::vector<u64> hs;
+    int rc = HL_B200_OK;
+    if (mask_coeffs) {
+        st.mask_c = f2(mask_c[0], mask_c[1]);
+        // per round j: sum_{i>j} u_i(1) / 2 (sumcheck.rs:266-268)
+        const fp2* co = reinterpret_cast<const fp2*>(mask_coeffs);
+        const u64 half = gl_inv(2);
+        hs.assign((size_t)mask_vars * 2, 0);
+        fp2 run = f2(0, 0);
+        for (int i = (int)mask_vars - 1; i >= 0; i--) {
+            hs[2 * i] = run.c0; hs[2 * i + 1] = run.c1;
+            fp2 u1 = f2(0, 0);
+            for (u32 e = 0; e < r->degree; e++) u1 = f2_add(u1, co[2 + (size_t)i * r->degree + e]);
+            run = f2_add(run, f2_mul_base(u1, half));
+        }
+        rc = dev_alloc(c, (void**)&d_mask, mlen * 16);
+        if (!rc) rc = dev_alloc(c, (void**)&d_hs, (size_t)mask_vars * 16);
+        if (!rc) rc = h2d(c, d_mask, mask_coeffs, mlen * 16);
+        if (!rc) rc = h2d(c, d_hs, hs.data(), (size_t)mask_vars * 16);
+    }
+    if (!rc) rc = h2d(c, r->d_state, &st, sizeof st);
+    const u32 first = r->next;
+    bool have_claim = fs->recover_one && fs->have_claim;
+    {
+        Timed t(c, HL_T_ROUNDS);
+        for (u32 i = 0; i < nd && !rc; i++) {
+            rc = launch_round(r, have_claim ? 0 : 1, 1, have_claim ? 1 : 0, fs->recover_one ? 1 : 0, d_mask, d_hs, (int)mask_vars);
+            if (!rc) rc = launch_fold(r);
+            have_claim = fs->recover_one != 0;
+        }
+    }
+    if (!rc) rc = d2h(c, out, r->d_out + (size_t)first * r->out_row(), (size_t)nd * r->out_row() * 8);
+    if (!rc) rc = d2h(c, &st, r->d_state, sizeof st);
+    if (!rc) rc = sync(c, "rounds_batched");
+    if (d_mask) dev_free(c, d_mask, mlen * 16);
+    if (d_hs) dev_free(c, d_hs, (size_t)mask_vars * 16);
+    if (rc) return rc;
+    memcpy(fs->state, st.state, 32);
+    fs->counter = st.counter;
+    fs->claim[0] = st.claim.c0; fs->claim[1] = st.claim.c1;
+    fs->have_claim = fs->recover_one ? 1 : fs->have_claim;
+    c->stats.round_batches++;
+    return HL_B200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,272 @@
+// Sumcheck kernels: round polynomial, Fiat-Shamir step, table fold (sumcheck/rounds.rs:94-160).
+//
+// Tables are k arrays of `stride` Fp2 (16 bytes each); the live part of a table is its first
+// `len` entries.  Variable 0 is the most significant index bit, so round j pairs entry i with
+// entry i + len/2, and the fold writes the first half in place.
+//
+// k_sc_round   one grid pass over the pairs: each thread evaluates the slot polynomial at the
+//              points 0..D by repeated addition of (T(i+half) - T(i)) and keeps D+1 running sums;
+//              warp-shuffle tree, then a shared-memory tree across warps, one partial per CTA.
+// k_sc_step    one warp: sums the CTA partials, recovers s(1) from the running claim, adds the
+//              CFS mask c*g_j, absorbs "sc-round" into the transcript state, squeezes the
+//              challenge, updates the claim and the mask's running terms (transcript.rs:67-148,
+//              sumcheck.rs:260-299).  The host replays these rounds through its own transcript.
+// k_sc_fold    T[i] += r (T[i+half] - T[i]) for every table, r read from device memory.
+#include "b3.cuh"
+#include "gl_field.cuh"
+#include "kernels.h"
+#include "sumcheck.h"
+
+namespace {
+
+using hlk::ScStep;
+
+__device__ __forceinline__ fp2 ld2(const u64* p) {
+    ulonglong2 v = *reinterpret_cast<const ulonglong2*>(p);
+    return f2(v.x, v.y);
+}
+__device__ __forceinline__ void st2(u64* p, fp2 v) { *reinterpret_cast<ulonglong2*>(p) = make_ulonglong2(v.c0, v.c1); }
+
+__device__ __forceinline__ fp2 f2_one() { return f2(1, 0); }
+
+// The slot polynomial families (ids in sumcheck.h).
+template <int POLY, int K>
+__device__ __forceinline__ fp2 poly_eval(const fp2 (&v)[K], const fp2* __restrict__ coefs) {
+    if constexpr (POLY == hlk::POLY_PROD) {
+        fp2 a = v[0];
+#pragma unroll
+        for (int t = 1; t < K; t++) a = f2_mul(a, v[t]);
+        return a;
+    } else if constexpr (POLY == hlk::POLY_ZC) {
+        return f2_mul(v[0], f2_sub(f2_mul(v[1], v[2]), v[3]));
+    } else if constexpr (POLY == hlk::POLY_LOGUP_Q) {
+        return f2_mul(v[0], f2_sub(f2_mul(v[1], f2_sub(coefs[0], v[2])), f2_one()));
+    } else {
+        return f2_mul(v[0], f2_sub(f2_mul(v[1], f2_sub(coefs[0], v[2])), v[3]));
+    }
+}
+
+__device__ __forceinline__ u64 shfl_down64(u64 v, int d) {
+    u32 lo = __shfl_down_sync(0xffffffffu, (u32)v, d), hi = __shfl_down_sync(0xffffffffu, (u32)(v >> 32), d);
+    return ((u64)hi << 32) | lo;
+}
+
+constexpr int RT = 256;  // threads of a round CTA
+
+template <int POLY, int K, int D>
+__global__ void __launch_bounds__(RT) k_sc_round(const u64* __restrict__ tables, size_t stride, u32 half, const u64* __restrict__ coefs,
+                                                 int eval_one, u64* __restrict__ partials) {
+    fp2 acc[D + 1];
+#pragma unroll
+    for (int d = 0; d <= D; d++) acc[d] = f2(0, 0);
+    const fp2* cf = reinterpret_cast<const fp2*>(coefs);
+    for (u32 i = blockIdx.x * RT + threadIdx.x; i < half; i += gridDim.x * RT) {
+        fp2 cur[K], dif[K];
+#pragma unroll
+        for (int t = 0; t < K; t++) {
+            const u64* tb = tables + 2 * (size_t)t * stride;
+            cur[t] = ld2(tb + 2 * (size_t)i);
+            dif[t] = f2_sub(ld2(tb + 2 * ((size_t)i + half)), cur[t]);
+        }
+        acc[0] = f2_add(acc[0], poly_eval<POLY, K>(cur, cf));
+#pragma unroll
+        for (int d = 1; d <= D; d++) {
+#pragma unroll
+            for (int t = 0; t < K; t++) cur[t] = f2_add(cur[t], dif[t]);
+            if (d != 1 || eval_one) acc[d] = f2_add(acc[d], poly_eval<POLY, K>(cur, cf));
+        }
+    }
+    // warp tree
+#pragma unroll
+    for (int d = 0; d <= D; d++) {
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+            acc[d].c0 = gl_add(acc[d].c0, shfl_down64(acc[d].c0, off));
+            acc[d].c1 = gl_add(acc[d].c1, shfl_down64(acc[d].c1, off));
+        }
+    }
+    __shared__ u64 wsum[RT / 32][2 * (D + 1)];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) {
+#pragma unroll
+        for (int d = 0; d <= D; d++) { wsum[warp][2 * d] = acc[d].c0; wsum[warp][2 * d + 1] = acc[d].c1; }
+    }
+    __syncthreads();
+    if (threadIdx.x < 2 * (D + 1)) {
+        u64 s = 0;
+#pragma unroll
+        for (int w = 0; w < RT / 32; w++) s = gl_add(s, wsum[w][threadIdx.x]);
+        partials[(size_t)blockIdx.x * 2 * (D + 1) + threadIdx.x] = s;
+    }
+}
+
+// ---- transcript pieces on the device: one chunk, at most 1024 bytes ----
+__device__ void hash_small(const uint32_t* key, const uint32_t* words, u32 len, uint32_t (&out)[8]) {
+    b3::init_cv(out, key);
+    const u32 nb = len ? (len + 63) / 64 : 1;
+    for (u32 b = 0; b < nb; b++) {
+        uint32_t m[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) m[i] = words[16 * b + i];
+        uint32_t flags = (key ? b3::KEYED : 0u) | (b == 0 ? b3::CHUNK_START : 0u) | (b == nb - 1 ? (b3::CHUNK_END | b3::ROOT) : 0u);
+        b3::compress(out, m, 0, b == nb - 1 ? len - 64 * b : 64, flags);
+    }
+}
+
+__device__ __forceinline__ u64 reduce_le16(const uint32_t* w) {  // 128-bit little-endian draw mod p (transcript.rs:133-148)
+    return gl_reduce128(((u64)w[1] << 32) | w[0], ((u64)w[3] << 32) | w[2]);
+}
+
+// One warp.  Lanes share the partial sums; lane 0 runs the serial Fiat-Shamir step.
+__global__ void __launch_bounds__(32) k_sc_step(ScStep a) {
+    __shared__ u64 sums[2 * hlk::SC_MAX_POINTS];
+    __shared__ __align__(16) uint32_t msg[64];  // 256 bytes
+    const int lane = threadIdx.x, W = 2 * (a.degree + 1);
+    for (int w = 0; w < W; w++) {
+        u64 s = 0;
+        for (u32 b = lane; b < a.nblocks; b += 32) s = gl_add(s, a.partials[(size_t)b * W + w]);
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) s = gl_add(s, shfl_down64(s, off));
+        if (lane == 0) sums[w] = s;
+    }
+    __syncwarp();
+    if (lane != 0) return;
+    hlk::ScState* st = a.state;
+    fp2* s = reinterpret_cast<fp2*>(sums);
+    const int np = a.degree + 1;
+    if (a.use_claim) s[1] = f2_sub(st->claim, s[0]);          // s(1) = claim - s(0) (rounds.rs:137-140)
+    u64* orow = a.out + (size_t)a.round * (2 * (size_t)np + 1) * 2;
+    for (int d = 0; d < np; d++) st2(orow + 2 * d, s[d]);
+    if (!a.fs) return;                                          // plain round(): the host drives the transcript
+    // masked message s + c g_j (sumcheck.rs:260-295)
+    fp2 masked[hlk::SC_MAX_POINTS];
+    for (int d = 0; d < np; d++) masked[d] = s[d];
+    const fp2* mk = reinterpret_cast<const fp2*>(a.mask);
+    const int j = a.round;
+    if (mk) {
+        const fp2* aj = mk + 2 + (size_t)j * a.degree;
+        fp2 base = f2_add(f2_add(mk[0], st->acc_prev), reinterpret_cast<const fp2*>(a.mask_half_suffix)[j]);
+        fp2 ap = f2_mul(mk[1], st->prod_prev);
+        u64 scale = gl_pow(2, a.mask_vars - 1 - j);
+        for (int x = 0; x < np; x++) {
+            fp2 u = f2(0, 0);
+            u64 xp = 1;
+            for (int e = 1; e <= a.degree; e++) { xp = gl_mul(xp, (u64)x); u = f2_add(u, f2_mul_base(aj[e - 1], xp)); }
+            fp2 g = f2_add(f2_mul_base(f2_add(base, u), scale), f2_mul_base(ap, (u64)x));
+            masked[x] = f2_add(s[x], f2_mul(st->mask_c, g));
+        }
+    }
+    for (int d = 0; d < np; d++) st2(orow + 2 * (np + d), masked[d]);
+    // absorb: state' = H(state || LE64(8) || "sc-round" || LE64(16 np) || bytes) (transcript.rs:67-74)
+    const uint32_t* key = st->keyed ? st->key : nullptr;
+    for (int i = 0; i < 64; i++) msg[i] = 0;
+    for (int i = 0; i < 8; i++) msg[i] = st->state[i];
+    msg[8] = 8; msg[9] = 0;
+    msg[10] = 0x722d6373u; msg[11] = 0x646e756fu;              // "sc-r" "ound", little-endian words
+    msg[12] = 16u * np; msg[13] = 0;
+    for (int d = 0; d < np; d++) {
+        msg[14 + 4 * d] = (uint32_t)masked[d].c0; msg[15 + 4 * d] = (uint32_t)(masked[d].c0 >> 32);
+        msg[16 + 4 * d] = (uint32_t)masked[d].c1; msg[17 + 4 * d] = (uint32_t)(masked[d].c1 >> 32);
+    }
+    uint32_t h[8];
+    hash_small(key, msg, 56 + 16 * np, h);
+    // squeeze: out = H(state || "squeeze" || LE64(counter)); counter++; state = out (transcript.rs:120-130)
+    for (int i = 0; i < 16; i++) msg[i] = 0;
+    for (int i = 0; i < 8; i++) msg[i] = h[i];
+    const u64 ctr = st->counter;
+    msg[8] = 0x65757173u;                                       // "sque"
+    msg[9] = 0x00657a65u | ((uint32_t)(ctr & 0xff) << 24);      // "eze" then counter byte 0
+    msg[10] = (uint32_t)(ctr >> 8);
+    msg[11] = (uint32_t)(ctr >> 40);                            // bytes 5..7 (top byte of the word is zero)
+    hash_small(key, msg, 47, h);
+    st->counter = ctr + 1;
+    for (int i = 0; i < 8; i++) st->state[i] = h[i];
+    fp2 r = f2(reduce_le16(h), reduce_le16(h + 4));
+    st2(orow + 4 * np, r);
+    st->r = r;
+    // next claim = the UNMASKED round polynomial at r (rounds.rs:145-147; mle.rs:338-351)
+    if (a.recover) {
+        fp2 accv = f2(0, 0);
+        for (int i = 0; i < np; i++) {
+            fp2 num = f2_one();
+            for (int jj = 0; jj < np; jj++)
+                if (jj != i) num = f2_mul(num, f2(gl_sub(r.c0, (u64)jj), r.c1));
+            accv = f2_add(accv, f2_mul_base(f2_mul(s[i], num), a.inv_den[i]));
+        }
+        st->claim = accv;
+    }
+    if (mk) {  // the mask's running terms: sum_i u_i(r_i) and prod r_i
+        const fp2* aj = mk + 2 + (size_t)j * a.degree;
+        fp2 u = f2(0, 0), xp = f2_one();
+        for (int e = 1; e <= a.degree; e++) { xp = f2_mul(xp, r); u = f2_add(u, f2_mul(aj[e - 1], xp)); }
+        st->acc_prev = f2_add(st->acc_prev, u);
+        st->prod_prev = f2_mul(st->prod_prev, r);
+    }
+}
+
+__global__ void __launch_bounds__(256) k_sc_fold(u64* __restrict__ tables, size_t stride, u32 half, u32 k, const hlk::ScState* __restrict__ st) {
+    const u32 i = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
+    if (i >= half || t >= k) return;
+    const fp2 r = st->r;
+    u64* tb = tables + 2 * (size_t)t * stride;
+    fp2 a = ld2(tb + 2 * (size_t)i), b = ld2(tb + 2 * ((size_t)i + half));
+    st2(tb + 2 * (size_t)i, f2_add(a, f2_mul(r, f2_sub(b, a))));
+}
+
+template <int POLY, int K, int D>
+cudaError_t launch_round(const u64* tables, size_t stride, u32 half, const u64* coefs, int eval_one, u64* partials, u32 nblocks, cudaStream_t s) {
+    k_sc_round<POLY, K, D><<<nblocks, RT, 0, s>>>(tables, stride, half, coefs, eval_one, partials);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+namespace hlk {
+
+u32 sc_round_blocks(u32 half, int sm_count) {
+    u32 b = (half + RT - 1) / RT, cap = (u32)sm_count * 4;
+    if (b < 1) b = 1;
+    return b > cap ? cap : b;
+}
+
+bool sc_supported(int poly, int k, int degree) {
+    if (poly == POLY_PROD) return k >= 1 && k <= 6 && degree == k;
+    if (poly == POLY_ZC || poly == POLY_LOGUP_T) return k == 4 && degree == 3;
+    if (poly == POLY_LOGUP_Q) return k == 3 && degree == 3;
+    return false;
+}
+
+cudaError_t sc_round(int poly, int k, const u64* tables, size_t stride, u32 half, const u64* coefs, int eval_one, u64* partials,
+                     u32 nblocks, cudaStream_t s) {
+#define R(P, K, D) return launch_round<P, K, D>(tables, stride, half, coefs, eval_one, partials, nblocks, s)
+    switch (poly) {
+        case POLY_PROD:
+            switch (k) {
+                case 1: R(POLY_PROD, 1, 1);
+                case 2: R(POLY_PROD, 2, 2);
+                case 3: R(POLY_PROD, 3, 3);
+                case 4: R(POLY_PROD, 4, 4);
+                case 5: R(POLY_PROD, 5, 5);
+                case 6: R(POLY_PROD, 6, 6);
+            }
+            break;
+        case POLY_ZC: R(POLY_ZC, 4, 3);
+        case POLY_LOGUP_Q: R(POLY_LOGUP_Q, 3, 3);
+        case POLY_LOGUP_T: R(POLY_LOGUP_T, 4, 3);
+    }
+#undef R
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t sc_step(const ScStep& a, cudaStream_t s) {
+    k_sc_step<<<1, 32, 0, s>>>(a);
+    return cudaGetLastError();
+}
+
+cudaError_t sc_fold(u64* tables, size_t stride, u32 half, u32 k, const ScState* st, cudaStream_t s) {
+    dim3 grid((half + 255) / 256, k);
+    k_sc_fold<<<grid, 256, 0, s>>>(tables, stride, half, k, st);
+    return cudaGetLastError();
+}
+
+}  // namespace hlk

@@ -1,0 +1,48 @@
+// Shared declarations of the sumcheck kernels and their C-ABI wrapper.
+#pragma once
+#include <cuda_runtime.h>
+#include "gl_field.cuh"
+
+namespace hlk {
+
+enum { POLY_PROD = 0, POLY_ZC = 1, POLY_LOGUP_Q = 2, POLY_LOGUP_T = 3 };
+constexpr int SC_MAX_POINTS = 8;  // degree <= 7
+
+// Device-resident state of one evaluator: the transcript (state, counter, key), the running
+// unmasked claim, the last challenge, and the CFS mask's running terms.
+struct ScState {
+    uint32_t state[8];
+    uint32_t key[8];
+    u64 counter;
+    int keyed;
+    int pad_;
+    fp2 claim;
+    fp2 r;
+    fp2 mask_c;
+    fp2 acc_prev;   // sum_{i<j} u_i(r_i)
+    fp2 prod_prev;  // prod_{i<j} r_i
+};
+
+struct ScStep {
+    const u64* partials;        // nblocks x (degree+1) Fp2
+    u32 nblocks;
+    int degree, round;
+    int use_claim;              // s(1) := claim - s(0)
+    int recover;                // keep the running claim (rounds.rs recover_one)
+    int fs;                     // 0: only reduce and write the sums (host-driven round())
+    const u64* mask;            // CFS coefficients [a0, a', a_{j,e}] or NULL
+    const u64* mask_half_suffix;  // per round j: sum_{i>j} u_i(1)/2
+    int mask_vars;
+    const u64* inv_den;         // degree+1 inverse Lagrange denominators
+    ScState* state;
+    u64* out;                   // per round: (degree+1) sums, (degree+1) masked, r  (Fp2 each)
+};
+
+u32 sc_round_blocks(u32 half, int sm_count);
+bool sc_supported(int poly, int k, int degree);
+cudaError_t sc_round(int poly, int k, const u64* tables, size_t stride, u32 half, const u64* coefs, int eval_one, u64* partials,
+                     u32 nblocks, cudaStream_t s);
+cudaError_t sc_step(const ScStep& a, cudaStream_t s);
+cudaError_t sc_fold(u64* tables, size_t stride, u32 half, u32 k, const ScState* st, cudaStream_t s);
+
+}  // namespace hlk
