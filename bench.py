@@ -31,6 +31,9 @@ sys.path.insert(0, ROOT)
 
 WORK = {"log_cols": 14, "inv_rate": 2, "q": 280, "rows": 2504, "profile": "hashline-zk-mr1/b200-bench/1"}
 P = 0xFFFFFFFF00000001
+# dram__bytes_read.sum + dram__bytes_write.sum of one k_encode_fast<14,512> launch at this workload (ncu capture summarised in
+# profiles/k_encode_fast_8b_A.md); the kernel's shape is fixed, so the figure is per launch of the timed kernel
+ENCODE_DRAM_TRAFFIC = 756_425_984 + 1_137_284_000
 PUBLISHED_GBPS = 26.0  # the reference's Metal backend on an M3 Ultra at this exact shape
 
 
@@ -298,7 +301,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             "clocks": clocks,
             "roofline": {"bound": "hbm", "kernel": "k_encode_fast<14,512>", "achieved": achieved, "peak": peak,
                          "peak_source": "MEASURED_PEAKS.json hbm_gbs" if peaks else "fallback 6650 GB/s", "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "algorithmic_bytes_per_launch": alg_bytes, "ms_per_launch": enc_ms,
+                         "traffic": ENCODE_DRAM_TRAFFIC, "algorithmic_bytes_per_launch": alg_bytes, "ms_per_launch": enc_ms,
                          "note": "integer-issue bound kernel (64-bit modular multiplies on the IMAD pipe); HBM fraction reported as the contract asks"},
             "kernel_ms_per_step": {"encode": enc_ms, "column_hash": hash_ms, "salt_and_tree": mer_ms},
             "cpu_baseline": cpu,
