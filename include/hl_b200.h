@@ -102,6 +102,23 @@ int hl_b200_store_merkle(hl_store* store, const uint8_t* salts32, const uint8_t*
 int hl_b200_store_merkle_dev(hl_store* store, const uint8_t* d_salts32, const uint8_t* leaf_key32, const uint8_t* node_key32,
                              uint8_t* d_levels_out);
 
+/* ---- no counterpart in the reference: the column-leaf hash for callers that cannot allocate ----
+ * Some callers hold device buffers but may not allocate device memory themselves: a serving loop
+ * whose memory was reserved up front, a plug-in inside a process that owns the CUDA pools, a prover
+ * thread whose allocation cap is spent.  This call hashes the columns of a rows x nn row-major matrix
+ * that is already on the device (d_encoded) into nn 32-byte leaves (d_leaves32, device), keyed when
+ * key32 (host) is not NULL, exactly as the commitment's column hash does, and allocates nothing: its
+ * scratch (one 32-byte chaining value per column and 128-row chunk) lives in a 24 MiB array inside the
+ * library, held by every GPU that loads the library until the process exits.
+ * Limits: ceil(rows / 128) * nn * 32 bytes must fit in 24 MiB, else HL_B200_ERR_UNSUPPORTED.
+ * It works on the CURRENT device and launches on cuda_stream (a cudaStream_t, NULL = default stream)
+ * without waiting for it.  The first call on a device resolves the array's address
+ * (cudaGetSymbolAddress); make that call before any stream capture.  Every call on a device shares the
+ * array, which keeps the previous call's contents (none of it needs clearing: each call overwrites what
+ * it reads); calls that overlap on one GPU race on it and must be serialised by the caller. */
+int hl_b200_hash_columns_static(const uint64_t* d_encoded, size_t rows, size_t nn, const uint8_t* key32,
+                                uint8_t* d_leaves32, void* cuda_stream);
+
 /* ---- EncodedStore::fold_rows / fold_rows_with_pads (pcs/backend.rs:33-59; CPU body
  * pcs.rs:342-378, 976-1000) ----
  * rhos: k x rows Fp2.  out: k vectors of n Fp2 (with_pads == 0) or n + q Fp2 (with_pads != 0,

@@ -61,6 +61,8 @@ SIGNATURES.update({
     "hl_b200_rounds_batched": (_int, [_vp, _u32, C.POINTER(FsState), _vp, _u32, _vp, _vp]),
 })
 
+SIGNATURES["hl_b200_hash_columns_static"] = (_int, [_vp, _sz, _sz, _vp, _vp, _vp])
+
 T_NAMES = ("encode", "hash", "merkle", "fold", "gather", "rounds", "logup")
 
 

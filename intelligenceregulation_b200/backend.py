@@ -302,3 +302,15 @@ class B200Rounds:
             self.free()
         except Exception:
             pass
+
+
+def hash_columns_static(d_encoded: int, rows: int, nn: int, key: Optional[bytes], d_leaves: int, cuda_stream: int = 0) -> None:
+    """Column leaves of a device-resident rows x nn matrix into a device buffer, for callers that must not
+    allocate device memory (a pre-carved serving loop, a plug-in inside someone else's process).  The scratch
+    is a fixed 24 MiB array inside the library, so shapes with ceil(rows/128) * nn * 32 bytes above that are
+    refused; the call works on the current device, is asynchronous on `cuda_stream`, and must not overlap
+    another call of itself on the same GPU."""
+    lib = _lib.load()
+    rc = lib.hl_b200_hash_columns_static(C.c_void_p(d_encoded), rows, nn, _ptr(key), C.c_void_p(d_leaves), C.c_void_p(cuda_stream))
+    if rc != 0:
+        raise DeviceError(rc, "hash_columns_static: " + {-1: "bad argument", -7: "shape exceeds the 24 MiB static scratch"}.get(rc, "device error"))
