@@ -176,6 +176,23 @@ typedef struct {
 int hl_b200_rounds_batched(hl_rounds* r, uint32_t nd, hl_fs_state* fs, const uint64_t* mask_coeffs, uint32_t mask_vars,
                            const uint64_t mask_c[2], uint64_t* out);
 
+/* ---- LogUp (hashline/src/private_block/protocol.rs:993-1011 inverses, :1928-1933 table_helper;
+ * accuracy_act.rs:55-117 histogram / query_values / denominators) ----
+ * Multiplicities: mult[v] = number of queries with idx == v, idx in [0, table_len). */
+int hl_b200_logup_histogram(hl_ctx* ctx, const int32_t* idx, size_t nq, size_t table_len, uint64_t* mult);
+/* Helper column h[i] = s_i / (alpha - ((idx_i + idx_off) + beta * out_i + tag)), an Fp2 per entry, with
+ * s_i = 1 (mult NULL: the query side) or s_i = mult[i] (the table side m_v / (alpha - t_v); pass idx NULL
+ * for idx_i = i).  Every term is formed in the field.  HL_B200_ERR_ZERO if ANY denominator is zero
+ * ("zero LogUp denominator; discard attempt", protocol.rs:1005-1006); nothing is written then. */
+int hl_b200_logup_helpers(hl_ctx* ctx, const int32_t* idx, const int32_t* outv, size_t n, const uint64_t alpha[2],
+                          const uint64_t beta[2], const uint64_t tag[2], int64_t idx_off, const uint64_t* mult, uint64_t* h);
+
+/* ---- weight folds (zkp-core/src/mle.rs:157-205 fold_rows_i8 / fold_cols_i8, deferred forms :256-319) ----
+ * m: rows x cols int8, row-major.  fold_rows: out[j] = sum_i w[i] m[i][j] (w: rows Fp2, out: cols Fp2);
+ * fold_cols: out[i] = sum_j c[j] m[i][j] (c: cols Fp2, out: rows Fp2).  Exact integer sums, one reduction. */
+int hl_b200_fold_rows_i8(hl_ctx* ctx, const int8_t* m, size_t rows, size_t cols, const uint64_t* w, uint64_t* out);
+int hl_b200_fold_cols_i8(hl_ctx* ctx, const int8_t* m, size_t rows, size_t cols, const uint64_t* c, uint64_t* out);
+
 /* ---- counters: GpuStats / dev_stats (hashline/src/gpu/mod.rs:890-908) ---- */
 typedef struct {
     uint64_t commits, folds, gathers, merkles, round_batches;

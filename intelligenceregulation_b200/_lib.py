@@ -63,6 +63,13 @@ SIGNATURES.update({
 
 SIGNATURES["hl_b200_hash_columns_static"] = (_int, [_vp, _sz, _sz, _vp, _vp, _vp])
 
+SIGNATURES.update({
+    "hl_b200_logup_histogram": (_int, [_vp, _vp, _sz, _sz, _vp]),
+    "hl_b200_logup_helpers": (_int, [_vp, _vp, _vp, _sz, _vp, _vp, _vp, C.c_int64, _vp, _vp]),
+    "hl_b200_fold_rows_i8": (_int, [_vp, _vp, _sz, _sz, _vp, _vp]),
+    "hl_b200_fold_cols_i8": (_int, [_vp, _vp, _sz, _sz, _vp, _vp]),
+})
+
 T_NAMES = ("encode", "hash", "merkle", "fold", "gather", "rounds", "logup")
 
 

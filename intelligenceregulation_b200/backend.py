@@ -109,6 +109,38 @@ class Context:
         self.check(self.lib.hl_b200_probe_field(self.h, _ptr(a), _ptr(b), a.size, _ptr(out)))
         return out
 
+    def logup_histogram(self, idx, table_len: int) -> np.ndarray:
+        """accuracy_act.rs:55-73: multiplicity of every table entry over all queries (padding included)."""
+        idx = np.ascontiguousarray(idx, dtype=np.int32)
+        out = np.empty(table_len, dtype=np.uint64)
+        self.check(self.lib.hl_b200_logup_histogram(self.h, _ptr(idx), idx.size, table_len, _ptr(out)))
+        return out
+
+    def logup_helpers(self, idx, outv, alpha, beta, tag, idx_off: int = 0, mult=None) -> np.ndarray:
+        """protocol.rs:993-1011 / :1928: 1 / (alpha - q_i) per entry (times mult[i] when given); raises
+        DeviceError with code ERR_ZERO on a zero denominator (the attempt is to be discarded)."""
+        outv = np.ascontiguousarray(outv, dtype=np.int32)
+        ix = np.ascontiguousarray(idx, dtype=np.int32) if idx is not None else None
+        mu = _u64(mult) if mult is not None else None
+        h = np.empty((outv.size, 2), dtype=np.uint64)
+        a, b, t = (np.array([int(x[0]), int(x[1])], dtype=np.uint64) for x in (alpha, beta, tag))
+        self.check(self.lib.hl_b200_logup_helpers(self.h, _ptr(ix), _ptr(outv), outv.size, _ptr(a), _ptr(b), _ptr(t), idx_off, _ptr(mu), _ptr(h)))
+        return h
+
+    def fold_rows_i8(self, m: np.ndarray, w: np.ndarray) -> np.ndarray:
+        """mle.rs:157-185: w^T M for an int8 matrix, (cols, 2)."""
+        m, w = np.ascontiguousarray(m, dtype=np.int8), _u64(w)
+        out = np.empty((m.shape[1], 2), dtype=np.uint64)
+        self.check(self.lib.hl_b200_fold_rows_i8(self.h, _ptr(m), m.shape[0], m.shape[1], _ptr(w), _ptr(out)))
+        return out
+
+    def fold_cols_i8(self, m: np.ndarray, c: np.ndarray) -> np.ndarray:
+        """mle.rs:187-205: M c for an int8 matrix, (rows, 2)."""
+        m, c = np.ascontiguousarray(m, dtype=np.int8), _u64(c)
+        out = np.empty((m.shape[0], 2), dtype=np.uint64)
+        self.check(self.lib.hl_b200_fold_cols_i8(self.h, _ptr(m), m.shape[0], m.shape[1], _ptr(c), _ptr(out)))
+        return out
+
     def merkle(self, leaves: np.ndarray, salts: Optional[np.ndarray], leaf_key: Optional[bytes], node_key: Optional[bytes]) -> np.ndarray:
         """salt_leaf_keyed + MerkleTree::build_keyed: all levels, (2 nn - 1, 32) bytes, root last."""
         leaves = np.ascontiguousarray(leaves, dtype=np.uint8)

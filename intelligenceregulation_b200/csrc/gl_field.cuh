@@ -78,7 +78,25 @@ GL_HD u64 gl_pow(u64 b, u64 e) {
     }
     return acc;
 }
-GL_HD u64 gl_inv(u64 a) { return gl_pow(a, GL_P - 2); }
+GL_HD u64 gl_sqn(u64 a, int n) {
+    for (int i = 0; i < n; i++) a = gl_mul(a, a);
+    return a;
+}
+// a^(p-2) by an addition chain: p - 2 = (2^32 - 2) 2^32 + (2^32 - 1); 64 squarings, 10 multiplies.
+// The inverse is unique, so this is the word Fp::inv (field.rs:80-83) returns.
+GL_HD u64 gl_inv(u64 a) {
+    u64 a2 = gl_mul(gl_sqn(a, 1), a);         // a^(2^2 - 1)
+    u64 a4 = gl_mul(gl_sqn(a2, 2), a2);       // a^(2^4 - 1)
+    u64 a8 = gl_mul(gl_sqn(a4, 4), a4);
+    u64 a16 = gl_mul(gl_sqn(a8, 8), a8);
+    u64 a24 = gl_mul(gl_sqn(a16, 8), a8);
+    u64 a28 = gl_mul(gl_sqn(a24, 4), a4);
+    u64 a30 = gl_mul(gl_sqn(a28, 2), a2);
+    u64 a31 = gl_mul(gl_sqn(a30, 1), a);      // a^(2^31 - 1)
+    u64 b = gl_sqn(a31, 1);                   // a^(2^32 - 2)
+    u64 a32 = gl_mul(b, a);                   // a^(2^32 - 1)
+    return gl_mul(gl_sqn(b, 32), a32);
+}
 
 GL_HD fp2 f2(u64 a, u64 b) {
     fp2 r;

@@ -105,6 +105,10 @@ void or_logup_helpers(const int32_t *idx, const int32_t *outv, size_t nq, const 
 void or_logup_table_helper(const int32_t *table_out, const uint64_t *mult, size_t table_len, const uint64_t alpha[2],
                            const uint64_t beta[2], const uint64_t gamma_tag[2], uint64_t *ht /* table_len x 2 */);
 
+void or_logup_query_values(const int32_t *idx, const int32_t *outv, size_t n, const uint64_t beta[2],
+                           const uint64_t gamma_tag[2], int64_t idx_off, uint64_t *q);
+void or_fp2_sum(const uint64_t *v, size_t n, uint64_t out[2]);
+
 int or_num_threads(void);
 
 #ifdef __cplusplus

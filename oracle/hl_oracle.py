@@ -529,6 +529,21 @@ def logup_table_helper(table_out, mult, alpha, beta, tag) -> np.ndarray:
     return ht
 
 
+def logup_query_values(idx, outv, beta, tag, idx_off: int = 0) -> np.ndarray:
+    """accuracy_act.rs:91-99; idx None means idx_i = i (the table side)."""
+    outv = np.ascontiguousarray(outv, np.int32)
+    ix = np.ascontiguousarray(idx, np.int32) if idx is not None else None
+    q = np.empty((outv.size, 2), dtype=np.uint64)
+    _lib.or_logup_query_values(_p(ix), _p(outv), C.c_size_t(outv.size), (C.c_uint64 * 2)(*beta), (C.c_uint64 * 2)(*tag), C.c_int64(idx_off), _p(q))
+    return q
+
+
+def fp2_sum(v) -> Tuple[int, int]:
+    v, o = _u64(v), (C.c_uint64 * 2)()
+    _lib.or_fp2_sum(_p(v), C.c_size_t(v.size // 2), o)
+    return (int(o[0]), int(o[1]))
+
+
 # ----------------------------------------------------------------------------- the hiding commitment and its opening
 @dataclass
 class PcsParams:

@@ -56,3 +56,22 @@ void or_logup_table_helper(const int32_t *table_out, const uint64_t *mult, size_
     or_batch_inverse2(ht, table_len);
     for (size_t v = 0; v < table_len; v++) den[v] = fp2_mul_base(den[v], fp_new(mult[v]));
 }
+
+/* accuracy_act.rs:91-99 (query_values): q_i = (idx_i + off) + beta * out_i + tag; idx NULL means idx_i = i */
+void or_logup_query_values(const int32_t *idx, const int32_t *outv, size_t n, const uint64_t beta[2],
+                           const uint64_t gamma_tag[2], int64_t idx_off, uint64_t *q) {
+    fp2_t b = fp2_new(beta[0], beta[1]), tag = fp2_new(gamma_tag[0], gamma_tag[1]);
+    fp2_t *o = (fp2_t *)q;
+#pragma omp parallel for
+    for (size_t i = 0; i < n; i++) {
+        int64_t a = idx ? (int64_t)idx[i] : (int64_t)i;
+        o[i] = fp2_add(fp2_add(fp2_add(from_i64(a), from_i64(idx_off)), fp2_mul(b, from_i64(outv[i]))), tag);
+    }
+}
+
+/* sum of an Fp2 vector */
+void or_fp2_sum(const uint64_t *v, size_t n, uint64_t out[2]) {
+    fp2_t acc = FP2_ZERO;
+    for (size_t i = 0; i < n; i++) acc = fp2_add(acc, fp2_new(v[2 * i], v[2 * i + 1]));
+    out[0] = acc.c0; out[1] = acc.c1;
+}
