@@ -1,0 +1,202 @@
+"""Host logic of the D55 commit-fork-join run over several GPUs.
+
+The reference proves one request's transformer blocks as independent forks of one transcript
+(hashline/src/private_block/run_fork.rs:1617-1860): a commit phase absorbs the L - 1 boundary roots into
+S0, every block k is proved from ``fork(S0, k)``, and the join absorbs each fork's end state and IO claims
+in block order into S1.  There the forks are threads of one process; here a rank is a GPU, block k belongs
+to rank ``k mod world``, and the only data that crosses ranks are the small records below:
+
+* before the forks: the L - 1 boundary roots (32 bytes each), broadcast from rank 0;
+* after the forks: one fixed-size join record per block (index, 32-byte state, squeeze counter, two claim
+  lists), all-gathered; rank 0 (or every rank) replays the join.
+
+The transcript here is the caller's host transcript (transcript.rs:29-167) over the ``blake3`` package; the
+absorbed bytes and labels are those of run_fork.rs:907-1045 (`D55_LABELS` :156-166).
+"""
+from __future__ import annotations
+
+import struct
+from dataclasses import dataclass
+from typing import Callable, List, Optional, Sequence, Tuple
+
+import blake3 as _b3
+
+P = 0xFFFFFFFF00000001
+
+
+class HostTranscript:
+    """transcript.rs:29-167 (no masker): 32-byte state, labelled absorbs, counter-mode squeezes."""
+
+    def __init__(self, domain: bytes, key: Optional[bytes] = None):
+        self.key = key
+        self.state = self._h(b"hashline-v1/" + domain)
+        self.counter = 0
+
+    def _h(self, data: bytes) -> bytes:
+        return (_b3.blake3(data, key=self.key) if self.key else _b3.blake3(data)).digest()
+
+    def clone(self) -> "HostTranscript":
+        t = HostTranscript.__new__(HostTranscript)
+        t.key, t.state, t.counter = self.key, self.state, self.counter
+        return t
+
+    def absorb(self, label: bytes, data: bytes) -> None:
+        self.state = self._h(self.state + struct.pack("<Q", len(label)) + label + struct.pack("<Q", len(data)) + data)
+
+    def absorb_u64(self, label: bytes, v: int) -> None:
+        self.absorb(label, struct.pack("<Q", v))
+
+    def squeeze(self) -> bytes:
+        out = self._h(self.state + b"squeeze" + struct.pack("<Q", self.counter))
+        self.counter += 1
+        self.state = out
+        return out
+
+    def challenge_fp2(self) -> Tuple[int, int]:
+        b = self.squeeze()
+        return (int.from_bytes(b[:16], "little") % P, int.from_bytes(b[16:], "little") % P)
+
+
+@dataclass
+class RunHeader:
+    """The public header of a fork run (run_fork.rs:907-922)."""
+    profile: bytes
+    key: Optional[bytes]
+    blocks: int                       # L
+    shape: Tuple[int, int, int, int, int, int]  # tokens, width, hidden, q_heads, kv_heads, head_dim
+    expected_io: bytes
+    public_statement: bytes
+    parameter_line: bytes
+    calibration: bytes
+    schedule_digest: bytes
+
+    def transcript(self) -> HostTranscript:
+        tr = HostTranscript(self.profile, self.key)
+        tr.absorb(b"run-shape", b"".join(struct.pack("<Q", v) for v in (self.blocks, *self.shape)))
+        tr.absorb(b"expected-IO", self.expected_io)
+        tr.absorb(b"public-statement", self.public_statement)
+        tr.absorb(b"parameters", self.parameter_line)
+        tr.absorb(b"calibration", self.calibration)
+        tr.absorb(b"schedule", self.schedule_digest)
+        return tr
+
+
+def absorb_commit(tr: HostTranscript, blocks: int, roots: Sequence[bytes], rows: Sequence[int], log_cols: Sequence[int]) -> None:
+    """run_fork.rs:975-994 with protocol.rs:154-158: the L - 1 boundary roots in order, then `pb-fork-s0`."""
+    if len(roots) + 1 != blocks:
+        raise ValueError(f"D55: an {blocks}-block run has {blocks - 1} boundary roots, not {len(roots)}")
+    for k, root in enumerate(roots):
+        tr.absorb_u64(b"pb-fork-commit-root", k)
+        tr.absorb(b"B", root)
+        tr.absorb_u64(b"rows", rows[k])
+        tr.absorb_u64(b"log-cols", log_cols[k])
+    tr.absorb_u64(b"pb-fork-s0", blocks)
+
+
+def fork(s0: HostTranscript, idx: int, block_digest: bytes) -> HostTranscript:
+    """run_fork.rs:996-1009: fork(S0, idx)."""
+    t = s0.clone()
+    t.absorb_u64(b"pb-run-fork", idx)
+    t.absorb(b"pb-run-fork-block", block_digest)
+    return t
+
+
+@dataclass
+class JoinRecord:
+    """What one fork hands to the join (run_fork.rs:1034-1041)."""
+    k: int
+    state: bytes
+    counter: int
+    in_claims: bytes    # claim_bytes() of the slot-21 claims
+    out_claims: bytes   # claim_bytes() of the slot-22 claims
+
+    def pack(self, claim_cap: int) -> bytes:
+        """Fixed-size wire form for an all-gather: lengths first, claim lists zero-padded to claim_cap."""
+        if len(self.in_claims) > claim_cap or len(self.out_claims) > claim_cap or len(self.state) != 32:
+            raise ValueError("D55: join record does not fit its slot")
+        return (struct.pack("<QQQQ", self.k, self.counter, len(self.in_claims), len(self.out_claims)) + self.state
+                + self.in_claims.ljust(claim_cap, b"\0") + self.out_claims.ljust(claim_cap, b"\0"))
+
+    @staticmethod
+    def size(claim_cap: int) -> int:
+        return 32 + 32 + 2 * claim_cap
+
+    @staticmethod
+    def unpack(buf: bytes, claim_cap: int) -> "JoinRecord":
+        k, counter, li, lo = struct.unpack_from("<QQQQ", buf, 0)
+        if li > claim_cap or lo > claim_cap:
+            raise ValueError("D55: corrupt join record")
+        state = bytes(buf[32:64])
+        ic = bytes(buf[64:64 + li])
+        oc = bytes(buf[64 + claim_cap:64 + claim_cap + lo])
+        return JoinRecord(k, state, counter, ic, oc)
+
+
+def claim_bytes(claims) -> bytes:
+    """run_fork.rs:1011-1030: count, then per claim its value, part count and every part's public words.
+    A claim is (value, [(offset, log_size, coef, [point...])]) with Fp2 as (c0, c1)."""
+    b = [struct.pack("<Q", len(claims))]
+    for value, parts in claims:
+        b.append(struct.pack("<QQQ", value[0], value[1], len(parts)))
+        for off, log_size, coef, point in parts:
+            b.append(struct.pack("<QQQQQ", off, log_size, coef[0], coef[1], len(point)))
+            b.extend(struct.pack("<QQ", x[0], x[1]) for x in point)
+    return b"".join(b)
+
+
+def io_claim_list_len(log_plane: int, log_endpoint: int) -> int:
+    """run_fork.rs:176-182: the byte length of one IO slot's claim list at a shape."""
+    logm = min(log_plane, log_endpoint)
+    part = lambda coords: 8 + 8 + 16 + 8 + 16 * coords  # noqa: E731
+    return 8 + 16 + 8 + part(log_plane) + 2 * part(logm)
+
+
+def absorb_join(tr: HostTranscript, rec: JoinRecord) -> None:
+    tr.absorb_u64(b"pb-join-fork", rec.k)
+    tr.absorb(b"pb-join-state", rec.state + struct.pack("<Q", rec.counter))
+    tr.absorb(b"pb-join-in-claims", rec.in_claims)
+    tr.absorb(b"pb-join-out-claims", rec.out_claims)
+
+
+def close_join(tr: HostTranscript, blocks: int) -> None:
+    tr.absorb_u64(b"pb-fork-s1", blocks)
+
+
+def block_owner(k: int, world: int) -> int:
+    return k % world
+
+
+def blocks_of(rank: int, world: int, blocks: int) -> List[int]:
+    return [k for k in range(blocks) if block_owner(k, world) == rank]
+
+
+def join(s0: HostTranscript, records: Sequence[JoinRecord], blocks: int) -> HostTranscript:
+    """run_fork.rs:1819-1827: every block exactly once, in block order, then `pb-fork-s1`."""
+    by_k = {r.k: r for r in records}
+    if len(by_k) != blocks or sorted(by_k) != list(range(blocks)) or len(records) != blocks:
+        raise ValueError("D55: the join needs exactly one record per block")
+    tr = s0.clone()
+    for k in range(blocks):
+        absorb_join(tr, by_k[k])
+    close_join(tr, blocks)
+    return tr
+
+
+def run_forks(header: RunHeader, roots: Sequence[bytes], rows: Sequence[int], log_cols: Sequence[int], block_digests: Sequence[bytes],
+              prove_fork: Callable[[int, HostTranscript], JoinRecord], rank: int = 0, world: int = 1,
+              all_gather: Optional[Callable[[bytes], List[bytes]]] = None, claim_cap: int = 4096) -> HostTranscript:
+    """Phase 2 and 3 of a fork run on this rank: prove the blocks this rank owns from fork(S0, k), exchange the
+    join records (one fixed-size buffer per rank through `all_gather`), replay the join.  Returns S1.
+    A fork that fails raises here, before the gather, so no rank waits on a dead peer's kernels."""
+    s0 = header.transcript()
+    absorb_commit(s0, header.blocks, roots, rows, log_cols)
+    mine = [prove_fork(k, fork(s0, k, block_digests[k])) for k in blocks_of(rank, world, header.blocks)]
+    per_rank = -(-header.blocks // world)
+    size = JoinRecord.size(claim_cap)
+    buf = b"".join(r.pack(claim_cap) for r in mine).ljust(per_rank * size, b"\xff")
+    bufs = [buf] if world == 1 or all_gather is None else all_gather(buf)
+    records = []
+    for r, b in enumerate(bufs):
+        for i in range(len(blocks_of(r, world, header.blocks))):
+            records.append(JoinRecord.unpack(b[i * size:(i + 1) * size], claim_cap))
+    return join(s0, records, header.blocks)
