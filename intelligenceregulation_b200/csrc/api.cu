@@ -161,6 +161,8 @@ int hl_b200_init(int device, hl_ctx** out) {
     c->sm_count = prop.multiProcessorCount;
     if (cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking) != cudaSuccess) { delete c; return HL_B200_ERR_DEVICE; }
     c->stream = c->own_stream;
+    if (cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&c->ev_main, cudaEventDisableTiming) != cudaSuccess) { delete c; return HL_B200_ERR_DEVICE; }
     cudaMemPool_t pool;
     if (cudaDeviceGetDefaultMemPool(&pool, device) == cudaSuccess) {
         unsigned long long keep = ~0ULL;
@@ -181,6 +183,10 @@ void hl_b200_shutdown(hl_ctx* c) {
     for (auto& kv : c->tw) cudaFree(kv.second);
     for (auto& s : c->spans) { cudaEventDestroy(s.a); cudaEventDestroy(s.b); }
     for (auto e : c->ev_pool) cudaEventDestroy(e);
+    for (auto e : c->ev_chunks) cudaEventDestroy(e);
+    cudaEventDestroy(c->ev_main);
+    cudaStreamSynchronize(c->copy_stream);
+    cudaStreamDestroy(c->copy_stream);
     cudaStreamDestroy(c->own_stream);
     delete c;
 }

@@ -15,6 +15,9 @@ struct hl_ctx {
     int sm_count = 0;
     cudaStream_t own_stream = nullptr;
     cudaStream_t stream = nullptr;
+    cudaStream_t copy_stream = nullptr;     // uploads that overlap the encoder
+    cudaEvent_t ev_main = nullptr;
+    std::vector<cudaEvent_t> ev_chunks;
     bool fast_encoder = true;
     std::mutex mu;
     std::map<u32, u64*> tw;  // log2 nn -> nn powers of the nn-th root

@@ -10,8 +10,11 @@ struct Shape {
     bool zk;
 };
 
-// Encode + column-hash on device memory that is already in place.  Leaves stay in st->d_leaves.
-int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* key32) {
+// Encode + column-hash.  With `h_data` NULL the data rows are already in st->d_data; otherwise they are
+// uploaded here in row chunks on the context's copy stream while the encoder works on the chunks that
+// have arrived (the upload of a block-sized matrix takes longer than its encoding).  Leaves stay in
+// st->d_leaves.
+int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* key32, const uint64_t* h_data) {
     const u32 logn = st->logn, lognn = st->logn + st->logr;
     const size_t n = st->n(), nn = st->nn();
     const u32 T = st->zk ? (u32)((n + st->q + n - 1) / n) : 1u;
@@ -27,15 +30,47 @@ int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* 
     rc = upload_key(c, key32, &d_key);
     if (!rc) rc = dev_alloc(c, (void**)&scratch, scratch_words * 8);
     if (!rc && cvs_bytes) rc = dev_alloc(c, (void**)&cvs, cvs_bytes);
+    // row chunks: two rows per SM per chunk keeps every encoder launch a whole number of waves
+    const size_t row_bytes = n * 8;
+    u32 chunk = st->rows;
+    if (h_data && (size_t)st->rows * row_bytes >= ((size_t)32 << 20) && st->rows > 4u * (u32)c->sm_count) chunk = 2u * (u32)c->sm_count;
+    if (!rc && h_data && chunk < st->rows) {
+        // the copy stream may touch the fresh allocations only after the main stream has made them
+        cudaError_t e = cudaEventRecord(c->ev_main, c->stream);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(c->copy_stream, c->ev_main, 0);
+        if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "stream ordering", e);
+    }
     if (!rc) {
-        enc::RowArgs a;
-        a.data = st->d_data; a.pads = st->d_pads; a.pows = d_pows; a.tw_nn = tw; a.enc = st->d_enc; a.scratch = scratch;
-        a.rows = st->rows; a.q = st->zk ? st->q : 0; a.T = T; a.logr = st->logr; a.zk = st->zk ? 1 : 0;
-        a.ninv = gl_inv((u64)n);
         Timed t(c, HL_T_ENCODE);
-        cudaError_t e = hlk::encode_rows(a, logn, c->fast_encoder, c->sm_count, scratch_words, c->stream, &st->encoder_path);
-        c->stats.kernel_launches += 1;
-        if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "row encoder launch", e);
+        size_t ev_i = 0;
+        for (u32 r0 = 0; r0 < st->rows && !rc; r0 += chunk) {
+            const u32 nr = st->rows - r0 < chunk ? st->rows - r0 : chunk;
+            if (h_data) {
+                cudaStream_t cs = chunk < st->rows ? c->copy_stream : c->stream;
+                cudaError_t e = cudaMemcpyAsync(st->d_data + (size_t)r0 * n, h_data + (size_t)r0 * n, (size_t)nr * row_bytes, cudaMemcpyHostToDevice, cs);
+                c->stats.bytes_h2d += (size_t)nr * row_bytes;
+                if (e == cudaSuccess && cs != c->stream) {
+                    if (ev_i == c->ev_chunks.size()) {
+                        cudaEvent_t ev = nullptr;
+                        e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+                        if (e == cudaSuccess) c->ev_chunks.push_back(ev);
+                    }
+                    if (e == cudaSuccess) e = cudaEventRecord(c->ev_chunks[ev_i], cs);
+                    if (e == cudaSuccess) e = cudaStreamWaitEvent(c->stream, c->ev_chunks[ev_i], 0);
+                    ev_i++;
+                }
+                if (e != cudaSuccess) { rc = fail(c, HL_B200_ERR_DEVICE, "row upload", e); break; }
+            }
+            enc::RowArgs a;
+            a.data = st->d_data + (size_t)r0 * n;
+            a.pads = st->d_pads ? st->d_pads + (size_t)r0 * st->q : nullptr;
+            a.pows = d_pows; a.tw_nn = tw; a.enc = st->d_enc + (size_t)r0 * nn; a.scratch = scratch;
+            a.rows = nr; a.q = st->zk ? st->q : 0; a.T = T; a.logr = st->logr; a.zk = st->zk ? 1 : 0;
+            a.ninv = gl_inv((u64)n);
+            cudaError_t e = hlk::encode_rows(a, logn, c->fast_encoder, c->sm_count, scratch_words, c->stream, &st->encoder_path);
+            c->stats.kernel_launches += 1;
+            if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "row encoder launch", e);
+        }
     }
     if (!rc) {
         Timed t(c, HL_T_HASH);
@@ -84,14 +119,13 @@ int commit_host(hl_ctx* c, const Shape& s, const uint64_t* data, const uint64_t*
     if (!rc && s.zk) rc = dev_alloc(c, (void**)&d_pows, nn * 8);
     if (!rc) rc = dev_alloc(c, (void**)&st->d_enc, (size_t)s.rows * nn * 8);
     if (!rc) rc = dev_alloc(c, (void**)&st->d_leaves, nn * 32);
-    if (!rc) rc = h2d(c, st->d_data, data, (size_t)s.rows * n * 8);
     if (!rc && s.zk) rc = h2d(c, st->d_pads, pads, (size_t)s.rows * s.q * 8);
     if (!rc && s.zk) rc = h2d(c, d_pows, pows, nn * 8);
-    if (!rc) rc = commit_on_device(c, st, d_pows, key32);
+    if (!rc) rc = commit_on_device(c, st, d_pows, key32, data);
     if (!rc) rc = d2h(c, leaves32, st->d_leaves, nn * 32);
     if (!rc) rc = sync(c, "commit");
     if (d_pows) dev_free(c, d_pows, nn * 8);
-    if (rc) { cudaStreamSynchronize(c->stream); free_store(st); return rc; }
+    if (rc) { cudaStreamSynchronize(c->copy_stream); cudaStreamSynchronize(c->stream); free_store(st); return rc; }
     c->stats.commits++;
     *store = st;
     return HL_B200_OK;
@@ -141,7 +175,7 @@ int hl_b200_commit_zk_dev(hl_ctx* c, uint32_t log_cols, uint32_t inv_rate, const
     const size_t nn = st->nn();
     rc = dev_alloc(c, (void**)&st->d_enc, (size_t)s.rows * nn * 8);
     if (!rc) rc = dev_alloc(c, (void**)&st->d_leaves, nn * 32);
-    if (!rc) rc = commit_on_device(c, st, (const u64*)d_pows, key32);
+    if (!rc) rc = commit_on_device(c, st, (const u64*)d_pows, key32, nullptr);
     if (!rc && d_leaves32) {
         cudaError_t e = cudaMemcpyAsync(d_leaves32, st->d_leaves, nn * 32, cudaMemcpyDeviceToDevice, c->stream);
         if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "leaf copy", e);

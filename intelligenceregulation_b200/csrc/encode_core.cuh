@@ -158,9 +158,9 @@ struct Fast {
                     if (j & (1 << lb)) continue;
                     u32 k = k0 + (((u32)j & ((1u << lb) - 1u)) << W);
                     u64 w = TW[swz(k << (LOGN - st))];
-                    u64 u = e[j], v = gl_mul(e[j | (1 << lb)], w);
-                    e[j] = gl_add(u, v);
-                    e[j | (1 << lb)] = gl_sub(u, v);
+                    u64 u = e[j], v = gl_canon_fast(gl_mul_lazy(e[j | (1 << lb)], w));
+                    e[j] = gl_add_lazy(u, v);
+                    e[j | (1 << lb)] = gl_sub_lazy(u, v);
                 }
             }
 #pragma unroll
@@ -182,10 +182,10 @@ struct Fast {
                 for (int j = 0; j < 16; j++) {
                     if (j & (1 << lb)) continue;
                     u32 k = k0 + (((u32)j & ((1u << lb) - 1u)) << W);
-                    u64 w = TW[swz(N / 2 - (k << (LOGN - st)))];  // -w^-k
-                    u64 u = e[j], v = e[j | (1 << lb)];
-                    e[j] = gl_add(u, v);
-                    e[j | (1 << lb)] = gl_mul(gl_sub(v, u), w);
+                    u64 w = GL_P - TW[swz(N / 2 - (k << (LOGN - st)))];  // w^-k = -w^(n/2 - k)
+                    u64 u = e[j], v = gl_canon_fast(e[j | (1 << lb)]);
+                    e[j] = gl_add_lazy(u, v);
+                    e[j | (1 << lb)] = gl_mul_lazy(gl_sub_lazy(u, v), w);
                 }
             }
 #pragma unroll
@@ -244,7 +244,7 @@ struct Fast {
 
     GL_HD static void store(const RowArgs& a, u32 row, u32 s, const u64* S, u32 tid, u32 nt) {
         u64* dst = a.enc + ((size_t)row * N << a.logr) + s;
-        for (u32 k = tid; k < N; k += nt) dst[(size_t)k << a.logr] = S[swz(k)];
+        for (u32 k = tid; k < N; k += nt) dst[(size_t)k << a.logr] = gl_canon_fast(S[swz(k)]);  // the passes keep lazy words
     }
 };
 

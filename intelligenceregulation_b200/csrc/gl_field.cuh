@@ -62,6 +62,100 @@ GL_HD u64 gl_mul(u64 a, u64 b) {
 #endif
 }
 
+// ---- lazy forms for butterfly chains -------------------------------------------------------------
+// A "lazy" word is any u64 congruent to the value mod p (canonical or not).  Inside the NTT passes the
+// elements stay lazy and only products are brought back to canonical form, which is what lets every
+// add / sub get by with ONE conditional correction:
+//   gl_mul_lazy(a, b)   any a, b            -> lazy product
+//   gl_add_lazy(u, v)   u lazy, v CANONICAL -> lazy sum        (u + v < 2^65 - 2^32 + 1: one wrap at most)
+//   gl_sub_lazy(u, v)   u lazy, v CANONICAL -> lazy difference (u - v + 2^64 >= 2^32 - 1: one borrow at most)
+// On the device they are PTX carry chains over 32-bit limbs (the 64-bit C forms cost ~1.5x the ALU-pipe
+// instructions); the multiply builds the 128-bit product with four 32x32 multiply-adds.
+#ifdef __CUDA_ARCH__
+__device__ __forceinline__ u64 gl_mul_lazy(u64 a, u64 b) {
+    const u32 a0 = (u32)a, a1 = (u32)(a >> 32), b0 = (u32)b, b1 = (u32)(b >> 32);
+    const u64 x = (u64)a0 * b0;
+    const u64 y = (u64)a0 * b1 + (x >> 32);
+    const u64 z = (u64)a1 * b0 + (u32)y;
+    const u64 w = (u64)a1 * b1 + (y >> 32) + (z >> 32);
+    const u32 p0 = (u32)x, p1 = (u32)z, p2 = (u32)w, p3 = (u32)(w >> 32);
+    u32 r0, r1;
+    // (p1:p0) - p3 [borrow: - EPS]  + p2 * EPS [carry: + EPS]
+    asm("{\n\t"
+        ".reg .u32 t0,t1,m,q0,q1;\n\t"
+        ".reg .u64 q;\n\t"
+        "sub.cc.u32 t0, %2, %5;\n\t"
+        "subc.cc.u32 t1, %3, 0;\n\t"
+        "subc.u32 m, 0, 0;\n\t"
+        "sub.cc.u32 t0, t0, m;\n\t"
+        "subc.u32 t1, t1, 0;\n\t"
+        "mul.wide.u32 q, %4, 0xFFFFFFFF;\n\t"
+        "mov.b64 {q0,q1}, q;\n\t"
+        "add.cc.u32 t0, t0, q0;\n\t"
+        "addc.cc.u32 t1, t1, q1;\n\t"
+        "addc.u32 m, 0, 0;\n\t"
+        "mov.b64 q, {t0,t1};\n\t"
+        "mad.wide.u32 q, m, 0xFFFFFFFF, q;\n\t"
+        "mov.b64 {%0,%1}, q;\n\t"
+        "}"
+        : "=r"(r0), "=r"(r1)
+        : "r"(p0), "r"(p1), "r"(p2), "r"(p3));
+    return ((u64)r1 << 32) | r0;
+}
+// r >= p  <=>  high limb all ones and low limb non-zero; then r - p = low limb - 1
+__device__ __forceinline__ u64 gl_canon_fast(u64 r) {
+    const u32 r0 = (u32)r, r1 = (u32)(r >> 32);
+    return (r1 == 0xFFFFFFFFu && r0 != 0) ? (u64)(r0 - 1) : r;
+}
+__device__ __forceinline__ u64 gl_add_lazy(u64 u, u64 v) {
+    const u32 u0 = (u32)u, u1 = (u32)(u >> 32), v0 = (u32)v, v1 = (u32)(v >> 32);
+    u32 r0, r1;
+    asm("{\n\t.reg .u32 m;\n\t.reg .u64 q;\n\t"
+        "add.cc.u32 %0, %2, %4;\n\t"
+        "addc.cc.u32 %1, %3, %5;\n\t"
+        "addc.u32 m, 0, 0;\n\t"
+        "mov.b64 q, {%0,%1};\n\t"
+        "mad.wide.u32 q, m, 0xFFFFFFFF, q;\n\t"
+        "mov.b64 {%0,%1}, q;\n\t}"
+        : "=&r"(r0), "=&r"(r1) : "r"(u0), "r"(u1), "r"(v0), "r"(v1));
+    return ((u64)r1 << 32) | r0;
+}
+__device__ __forceinline__ u64 gl_sub_lazy(u64 u, u64 v) {
+    const u32 u0 = (u32)u, u1 = (u32)(u >> 32), v0 = (u32)v, v1 = (u32)(v >> 32);
+    u32 r0, r1;
+    asm("{\n\t.reg .u32 m;\n\t"
+        "sub.cc.u32 %0, %2, %4;\n\t"
+        "subc.cc.u32 %1, %3, %5;\n\t"
+        "subc.u32 m, 0, 0;\n\t"
+        "sub.cc.u32 %0, %0, m;\n\t"
+        "subc.u32 %1, %1, 0;\n\t}"
+        : "=&r"(r0), "=&r"(r1) : "r"(u0), "r"(u1), "r"(v0), "r"(v1));
+    return ((u64)r1 << 32) | r0;
+}
+#else
+// host forms with the same contracts (the phase emulation on the CPU runs these)
+inline u64 gl_mul_lazy(u64 a, u64 b) {
+    unsigned __int128 x = (unsigned __int128)a * b;
+    u64 lo = (u64)x, hi = (u64)(x >> 64), hh = hi >> 32, hl = hi & GL_EPS;
+    u64 t0 = lo - hh;
+    if (lo < hh) t0 -= GL_EPS;
+    u64 t1 = (hl << 32) - hl, r = t0 + t1;
+    if (r < t0) r += GL_EPS;
+    return r;  // not canonicalised
+}
+inline u64 gl_canon_fast(u64 r) { return gl_canon(r); }
+inline u64 gl_add_lazy(u64 u, u64 v) {
+    u64 r = u + v;
+    if (r < u) r += GL_EPS;
+    return r;
+}
+inline u64 gl_sub_lazy(u64 u, u64 v) {
+    u64 r = u - v;
+    if (u < v) r -= GL_EPS;
+    return r;
+}
+#endif
+
 // Signed small integer to field (field.rs:32-34).
 GL_HD u64 gl_from_i64(long long v) {
     if (v >= 0) return gl_canon((u64)v);
