@@ -40,7 +40,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     objs = []
     obj_dir = os.path.join(HERE, "build")
     os.makedirs(obj_dir, exist_ok=True)
-    common = [nvcc_path(), "-std=c++17", "-O3", "-lineinfo", "-ccbin", "/usr/bin/g++", "-Xcompiler", "-fPIC", *ARCH]
+    common = [nvcc_path(), "-std=c++17", "-O3", "-lineinfo", "-ccbin", "/usr/bin/g++", "-Xcompiler", "-fPIC", "-Werror", "all-warnings", *ARCH]
     if verbose:
         common += ["-Xptxas", "-v"]
     procs = []

@@ -168,7 +168,7 @@ int hl_b200_init(int device, hl_ctx** out) {
         unsigned long long keep = ~0ULL;
         cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
     }
-    char buf[256];
+    char buf[512];
     snprintf(buf, sizeof buf, "hl_b200: %s (sm_%d%d, %d SMs, %.0f GB), device %d", prop.name, prop.major, prop.minor,
              prop.multiProcessorCount, (double)prop.totalGlobalMem / 1e9, device);
     c->label = buf;

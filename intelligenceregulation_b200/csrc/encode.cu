@@ -44,17 +44,12 @@ __global__ void __launch_bounds__(THREADS) k_encode_fast(enc::RowArgs a) {
     const u32 tid = threadIdx.x;
     u64* X = a.scratch + (size_t)blockIdx.x * a.T * F::N;
     F::load_twiddles(a, TW, tid, THREADS);
+    __syncthreads();
     for (u32 row = blockIdx.x; row < a.rows; row += gridDim.x) {
-        F::load(a, row, S, tid, THREADS);
-        __syncthreads();
-        F::inverse(S, TW, tid, THREADS, CtaSync());
-        F::coeffs(a, row, S, X, tid, THREADS);
-        __syncthreads();
+        F::row_coeffs(a, row, S, TW, X, tid, THREADS, CtaSync());
+        __syncthreads();  // the scratch slot is complete and shared memory is free again
         for (u32 s = 0; s < (1u << a.logr); s++) {
-            F::twist(a, s, X, S, tid, THREADS);
-            __syncthreads();
-            F::forward(S, TW, tid, THREADS, CtaSync());
-            F::store(a, row, s, S, tid, THREADS);
+            F::row_residue(a, row, s, S, TW, X, tid, THREADS, CtaSync());
             __syncthreads();
         }
     }
@@ -63,7 +58,7 @@ __global__ void __launch_bounds__(THREADS) k_encode_fast(enc::RowArgs a) {
 template <int LOGN>
 constexpr int fast_threads() {
     constexpr int g = (1 << LOGN) / 16;
-    return g < 32 ? 32 : (g > 512 ? 512 : g);
+    return g < 32 ? 32 : (g > 1024 ? 1024 : g);
 }
 
 template <int LOGN>

@@ -119,132 +119,158 @@ struct Generic {
 
 // ---------------------------------------------------------------------------------------------
 // Fast path, 2^8 <= n <= 2^14: sixteen elements per thread per pass, four stages per pass in
-// registers, swizzled shared memory, twiddles w_n^j (j <= n/2) in shared memory.
+// registers, swizzled shared memory, twiddles w_n^j (j < n/2) in shared memory.
+//
+// Both directions run the SAME forward decimation-in-time passes: the inverse transform of msg is
+// c[i] = X[(n - i) mod n] / n with X the forward transform of msg, so the coefficient step just
+// reads the forward output at the negated index.  A transform is
+//     first pass   source(i) -> registers (16 values of stride n/16, coalesced over the lanes)
+//                  -> stages 1..4 -> shared memory at bit-reversed positions
+//     middle       shared -> stages -> shared, one 4-bit window of the position index per pass
+//     last pass    shared -> the remaining stages -> sink(k, value) straight from registers
+// so a row's words cross shared memory (passes - 1) times, and neither the input permutation nor
+// the output store is a pass of its own.  Words are "lazy" (any u64 congruent mod p) between passes;
+// the sinks canonicalise.
 // ---------------------------------------------------------------------------------------------
 template <int LOGN>
 struct Fast {
+    static_assert(LOGN >= 8 && LOGN <= 14, "fast path sizes");
     static constexpr u32 N = 1u << LOGN;
     static constexpr u32 GROUPS = N / 16;   // 16-element groups per pass
-    static constexpr u32 TW_WORDS = N / 2 + 16;
+    static constexpr u32 TW_WORDS = N / 2;
+    static constexpr int R4 = LOGN % 4;
+    static constexpr int LASTW = LOGN - 4;  // window of the last pass
+    static constexpr int LASTLO = R4 ? LOGN - R4 : LOGN - 4;
 
-    // TW[swz(j)] = w_n^j for j <= n/2 (entry n/2 is -1, so that w^-k = -w^(n/2-k) needs no branch)
+    // swz is linear over XOR, so swz(base | c) = swz(base) ^ swz(c) whenever base and c share no bit:
+    // one swizzle per group, compile-time constants per element.
+    static GL_HDC u32 swzc(u32 p) { return p ^ (((p >> 4) ^ (p >> 8) ^ (p >> 12)) & 15u); }
+    static GL_HDC u32 brev4(u32 j) { return ((j & 1) << 3) | ((j & 2) << 1) | ((j & 4) >> 1) | ((j & 8) >> 3); }
+
+    // TW[swz(j)] = w_n^j, j < n/2
     GL_HD static void load_twiddles(const RowArgs& a, u64* TW, u32 tid, u32 nt) {
-        for (u32 j = tid; j <= N / 2; j += nt) TW[swz(j)] = j == N / 2 ? GL_P - 1 : a.tw_nn[(size_t)j << a.logr];
+        for (u32 j = tid; j < N / 2; j += nt) TW[swz(j)] = a.tw_nn[(size_t)j << a.logr];
     }
 
-    GL_HD static void load(const RowArgs& a, u32 row, u64* S, u32 tid, u32 nt) {
-        const u64* src = a.data + (size_t)row * N;
-        for (u32 i = tid; i < N; i += nt) S[swz(i)] = src[i];
-    }
-
-    // A pass works on the 4-bit window [W, W+4) of the position index: the thread's 16 elements
-    // sit at base + j 2^W.  Of the window's bits, only stages LO+1 .. HI (1-based, stage st pairs
-    // positions that differ in bit st-1) are executed; W <= LO and HI <= W + 4.
     template <int W>
     GL_HD static u32 group_base(u32 g) { return ((g >> W) << (W + 4)) | (g & ((1u << W) - 1u)); }
 
+    // Stages LO+1 .. HI (1-based; stage st pairs positions that differ in bit st-1) on the 16 elements of the
+    // window [W, W+4); k0 = the group's position bits below the window.  Lazy in, lazy out.
     template <int W, int LO, int HI>
-    GL_HD static void dit_pass(u64* S, const u64* TW, u32 tid, u32 nt) {
-        for (u32 g = tid; g < GROUPS; g += nt) {
-            u32 base = group_base<W>(g), k0 = base & ((1u << W) - 1u);
-            u64 e[16];
+    GL_HD static void stages(u64 (&e)[16], const u64* TW, u32 k0) {
 #pragma unroll
-            for (int j = 0; j < 16; j++) e[j] = S[swz(base + ((u32)j << W))];
+        for (int st = LO + 1; st <= HI; st++) {
+            const int lb = st - 1 - W;  // bit of j this stage pairs
+            const u32 tbase = W > 0 ? swz(k0 << (LOGN - st)) : 0u;
 #pragma unroll
-            for (int st = LO + 1; st <= HI; st++) {
-                const int lb = st - 1 - W;  // bit of j this stage pairs
-#pragma unroll
-                for (int j = 0; j < 16; j++) {
-                    if (j & (1 << lb)) continue;
-                    u32 k = k0 + (((u32)j & ((1u << lb) - 1u)) << W);
-                    u64 w = TW[swz(k << (LOGN - st))];
-                    u64 u = e[j], v = gl_canon_fast(gl_mul_lazy(e[j | (1 << lb)], w));
-                    e[j] = gl_add_lazy(u, v);
-                    e[j | (1 << lb)] = gl_sub_lazy(u, v);
+            for (int j = 0; j < 16; j++) {
+                if (j & (1 << lb)) continue;
+                const u32 jm = (u32)j & ((1u << lb) - 1u);
+                u64 u = e[j], v;
+                if (W == 0 && jm == 0) {
+                    v = gl_canon_fast(e[j | (1 << lb)]);  // twiddle 1
+                } else {
+                    const u64 w = TW[tbase ^ swzc((jm << W) << (LOGN - st))];
+                    v = gl_canon_fast(gl_mul_lazy(e[j | (1 << lb)], w));
                 }
+                e[j] = gl_add_lazy(u, v);
+                e[j | (1 << lb)] = gl_sub_lazy(u, v);
             }
-#pragma unroll
-            for (int j = 0; j < 16; j++) S[swz(base + ((u32)j << W))] = e[j];
         }
     }
 
-    template <int W, int LO, int HI>
-    GL_HD static void dif_pass(u64* S, const u64* TW, u32 tid, u32 nt) {
-        for (u32 g = tid; g < GROUPS; g += nt) {
-            u32 base = group_base<W>(g), k0 = base & ((1u << W) - 1u);
+    // first pass: element i of the transform's input comes from source(i); lanes take neighbouring i
+    template <class Source>
+    GL_HD static void first_pass(u64* S, const u64* TW, u32 tid, u32 nt, Source source) {
+        for (u32 t = tid; t < GROUPS; t += nt) {
             u64 e[16];
 #pragma unroll
-            for (int j = 0; j < 16; j++) e[j] = S[swz(base + ((u32)j << W))];
+            for (int j = 0; j < 16; j++) e[j] = source(t + brev4((u32)j) * GROUPS);  // position 16 g + j holds index brev(16 g + j)
+            stages<0, 0, 4>(e, TW, 0);
+            const u32 sb = swz(gl_brev(t, LOGN - 4) << 4);
 #pragma unroll
-            for (int st = HI; st >= LO + 1; st--) {
-                const int lb = st - 1 - W;
-#pragma unroll
-                for (int j = 0; j < 16; j++) {
-                    if (j & (1 << lb)) continue;
-                    u32 k = k0 + (((u32)j & ((1u << lb) - 1u)) << W);
-                    u64 w = GL_P - TW[swz(N / 2 - (k << (LOGN - st)))];  // w^-k = -w^(n/2 - k)
-                    u64 u = e[j], v = gl_canon_fast(e[j | (1 << lb)]);
-                    e[j] = gl_add_lazy(u, v);
-                    e[j | (1 << lb)] = gl_mul_lazy(gl_sub_lazy(u, v), w);
-                }
-            }
-#pragma unroll
-            for (int j = 0; j < 16; j++) S[swz(base + ((u32)j << W))] = e[j];
+            for (int j = 0; j < 16; j++) S[sb ^ swzc((u32)j)] = e[j];
         }
     }
 
-    // the whole transforms as pass lists; `sync` is the barrier between passes
-    template <class Sync>
-    GL_HD static void inverse(u64* S, const u64* TW, u32 tid, u32 nt, Sync sync) {
-        constexpr int R4 = LOGN % 4;
-        // windows from the top: [LOGN-4, LOGN), ..., then the remaining low R4 stages in window [0,4)
-        if constexpr (LOGN >= 4) { dif_pass<LOGN - 4, LOGN - 4, LOGN>(S, TW, tid, nt); sync(); }
-        if constexpr (LOGN >= 8) { dif_pass<LOGN - 8, LOGN - 8, LOGN - 4>(S, TW, tid, nt); sync(); }
-        if constexpr (LOGN >= 12) { dif_pass<LOGN - 12, LOGN - 12, LOGN - 8>(S, TW, tid, nt); sync(); }
-        if constexpr (R4 > 0) { dif_pass<0, 0, R4>(S, TW, tid, nt); sync(); }
-    }
-    template <class Sync>
-    GL_HD static void forward(u64* S, const u64* TW, u32 tid, u32 nt, Sync sync) {
-        constexpr int R4 = LOGN % 4;
-        if constexpr (LOGN >= 4) { dit_pass<0, 0, 4>(S, TW, tid, nt); sync(); }
-        if constexpr (LOGN >= 8) { dit_pass<4, 4, 8>(S, TW, tid, nt); sync(); }
-        if constexpr (LOGN >= 12) { dit_pass<8, 8, 12>(S, TW, tid, nt); sync(); }
-        if constexpr (R4 > 0) { dit_pass<LOGN - 4, LOGN - R4, LOGN>(S, TW, tid, nt); sync(); }
+    template <int W>
+    GL_HD static void mid_pass(u64* S, const u64* TW, u32 tid, u32 nt) {
+        for (u32 g = tid; g < GROUPS; g += nt) {
+            const u32 base = group_base<W>(g), sb = swz(base);
+            u64 e[16];
+#pragma unroll
+            for (int j = 0; j < 16; j++) e[j] = S[sb ^ swzc((u32)j << W)];
+            stages<W, W, W + 4>(e, TW, base & ((1u << W) - 1u));
+#pragma unroll
+            for (int j = 0; j < 16; j++) S[sb ^ swzc((u32)j << W)] = e[j];
+        }
     }
 
-    GL_HD static void coeffs(const RowArgs& a, u32 row, const u64* S, u64* X, u32 tid, u32 nt) {
+    // last pass: output k = g + j n/16 goes to sink(k, lazy value)
+    template <class Sink>
+    GL_HD static void last_pass(const u64* S, const u64* TW, u32 tid, u32 nt, Sink sink) {
+        for (u32 g = tid; g < GROUPS; g += nt) {
+            const u32 sb = swz(g);
+            u64 e[16];
+#pragma unroll
+            for (int j = 0; j < 16; j++) e[j] = S[sb ^ swzc((u32)j << LASTW)];
+            stages<LASTW, LASTLO, LOGN>(e, TW, g);
+#pragma unroll
+            for (int j = 0; j < 16; j++) sink(g + ((u32)j << LASTW), e[j]);
+        }
+    }
+
+    template <class Source, class Sink, class Sync>
+    GL_HD static void transform(u64* S, const u64* TW, u32 tid, u32 nt, Source source, Sink sink, Sync sync) {
+        first_pass(S, TW, tid, nt, source);
+        sync();
+        // full 4-stage windows below the last pass's first stage: [4,8) when LASTLO >= 8, [8,12) when LASTLO >= 12
+        if constexpr (LASTLO >= 8) { mid_pass<4>(S, TW, tid, nt); sync(); }
+        if constexpr (LASTLO >= 12) { mid_pass<8>(S, TW, tid, nt); sync(); }
+        last_pass(S, TW, tid, nt, sink);
+    }
+
+    // ---- the row pipeline ----
+    // inverse transform of the message row, then the coefficient blocks x[t n + i] into the scratch slot
+    template <class Sync>
+    GL_HD static void row_coeffs(const RowArgs& a, u32 row, u64* S, const u64* TW, u64* X, u32 tid, u32 nt, Sync sync) {
+        const u64* src = a.data + (size_t)row * N;
         const u64* pad = a.pads + (size_t)row * a.q;
-        for (u32 i = tid; i < N; i += nt) {
-            u64 c = gl_mul(S[swz(gl_brev(i, LOGN))], a.ninv);
-            for (u32 t = 0; t < a.T; t++) {
-                u32 idx = i + t * N;
-                u64 v = t == 0 ? c : 0;
-                if (a.zk) {
-                    if (idx < a.q) v = gl_sub(v, pad[idx]);
-                    if (idx >= N && idx - N < a.q) v = gl_add(v, pad[idx - N]);
-                    if (idx >= N + a.q) break;
-                    v = gl_mul(v, a.pows[idx]);
-                }
-                X[(size_t)t * N + i] = v;
-            }
-        }
+        transform(S, TW, tid, nt, [&](u32 i) { return src[i]; },
+                  [&](u32 k, u64 v) {
+                      const u32 i = (N - k) & (N - 1);  // c[i] = X[(n - i) mod n] / n
+                      const u64 c = gl_mul(v, a.ninv);
+                      for (u32 t = 0; t < a.T; t++) {
+                          const u32 idx = i + t * N;
+                          u64 x = t == 0 ? c : 0;
+                          if (a.zk) {
+                              if (idx >= N + a.q) break;
+                              if (idx < a.q) x = gl_sub(x, pad[idx]);
+                              if (idx >= N && idx - N < a.q) x = gl_add(x, pad[idx - N]);
+                              x = gl_mul(x, a.pows[idx]);
+                          }
+                          X[(size_t)t * N + i] = x;
+                      }
+                  },
+                  sync);
     }
 
-    GL_HD static void twist(const RowArgs& a, u32 s, const u64* X, u64* S, u32 tid, u32 nt) {
+    // output residue s: the size-n transform of the twisted coefficients, stored at out[R k + s]
+    template <class Sync>
+    GL_HD static void row_residue(const RowArgs& a, u32 row, u32 s, u64* S, const u64* TW, const u64* X, u32 tid, u32 nt, Sync sync) {
         const u32 nn = N << a.logr;
-        for (u32 i = tid; i < N; i += nt) {
-            u64 y = ENC_LDCG(X + i);
-            // x[i + t n] is zero from i + t n >= n + q on, and those scratch words are never written
-            for (u32 t = 1; t < a.T && i + t * N < N + a.q; t++)
-                y = gl_add(y, gl_mul(ENC_LDCG(X + (size_t)t * N + i), a.tw_nn[(t * s * N) & (nn - 1)]));
-            if (s) y = gl_mul(y, a.tw_nn[(i * s) & (nn - 1)]);
-            S[swz(gl_brev(i, LOGN))] = y;
-        }
-    }
-
-    GL_HD static void store(const RowArgs& a, u32 row, u32 s, const u64* S, u32 tid, u32 nt) {
         u64* dst = a.enc + ((size_t)row * N << a.logr) + s;
-        for (u32 k = tid; k < N; k += nt) dst[(size_t)k << a.logr] = gl_canon_fast(S[swz(k)]);  // the passes keep lazy words
+        transform(S, TW, tid, nt,
+                  [&](u32 i) {
+                      u64 y = ENC_LDCG(X + i);
+                      // x[i + t n] is zero from i + t n >= n + q on, and those scratch words are never written
+                      for (u32 t = 1; t < a.T && i + t * N < N + a.q; t++)
+                          y = gl_add(y, gl_mul(ENC_LDCG(X + (size_t)t * N + i), a.tw_nn[(t * s * N) & (nn - 1)]));
+                      if (s) y = gl_mul(y, a.tw_nn[(i * s) & (nn - 1)]);
+                      return y;
+                  },
+                  [&](u32 k, u64 v) { dst[(size_t)k << a.logr] = gl_canon_fast(v); }, sync);
     }
 };
 

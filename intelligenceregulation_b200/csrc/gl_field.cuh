@@ -13,8 +13,10 @@
 
 #ifdef __CUDACC__
 #define GL_HD __host__ __device__ __forceinline__
+#define GL_HDC __host__ __device__ constexpr
 #else
 #define GL_HD inline
+#define GL_HDC constexpr
 #endif
 
 typedef unsigned long long u64;

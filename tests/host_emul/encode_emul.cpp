@@ -22,18 +22,12 @@ struct NoSync { void operator()() const {} };
 template <int LOGN>
 static void run_fast(RowArgs a, u32 nt) {
     using F = Fast<LOGN>;
-    std::vector<u64> S(F::N + 16), TW(F::TW_WORDS);
+    std::vector<u64> S(F::N + 16), TW(F::TW_WORDS + 16);
     for (u32 t = 0; t < nt; t++) F::load_twiddles(a, TW.data(), t, nt);
+    // one emulated thread owning every group keeps the pass order of the device code
     for (u32 row = 0; row < a.rows; row++) {
-        for (u32 t = 0; t < nt; t++) F::load(a, row, S.data(), t, nt);
-        // one emulated thread owning every group keeps the pass order of the device code
-        F::inverse(S.data(), TW.data(), 0, 1, NoSync());
-        for (u32 t = 0; t < nt; t++) F::coeffs(a, row, S.data(), a.scratch, t, nt);
-        for (u32 s = 0; s < (1u << a.logr); s++) {
-            for (u32 t = 0; t < nt; t++) F::twist(a, s, a.scratch, S.data(), t, nt);
-            F::forward(S.data(), TW.data(), 0, 1, NoSync());
-            for (u32 t = 0; t < nt; t++) F::store(a, row, s, S.data(), t, nt);
-        }
+        F::row_coeffs(a, row, S.data(), TW.data(), a.scratch, 0, 1, NoSync());
+        for (u32 s = 0; s < (1u << a.logr); s++) F::row_residue(a, row, s, S.data(), TW.data(), a.scratch, 0, 1, NoSync());
     }
 }
 
