@@ -225,13 +225,9 @@ int hl_b200_store_fold(hl_store* st, const uint64_t* rhos, size_t k, int with_pa
         Timed t(c, HL_T_FOLD);
         // hiding form: the message is the resident data (the encoding is not systematic, pcs.rs:985-987);
         // plain form: the systematic positions of the encoding (pcs.rs:332-340)
-        cudaError_t e = st->zk ? hlk::fold_rows(st->d_data, st->rows, n, n, 1, d_rhos, (u32)k, d_out, w, 0, c->stream)
-                               : hlk::fold_rows(st->d_enc, st->rows, n, st->nn(), 1u << st->logr, d_rhos, (u32)k, d_out, w, 0, c->stream);
+        cudaError_t e = st->zk ? hlk::fold_rows(st->d_data, st->rows, n, n, 1, q ? st->d_pads : nullptr, q, q, d_rhos, (u32)k, d_out, w, c->stream)
+                               : hlk::fold_rows(st->d_enc, st->rows, n, st->nn(), 1u << st->logr, nullptr, 0, 0, d_rhos, (u32)k, d_out, w, c->stream);
         c->stats.kernel_launches++;
-        if (e == cudaSuccess && q) {
-            e = hlk::fold_rows(st->d_pads, st->rows, q, q, 1, d_rhos, (u32)k, d_out, w, n, c->stream);
-            c->stats.kernel_launches++;
-        }
         if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "fold launch", e);
     }
     if (!rc) rc = d2h(c, out, d_out, ob);

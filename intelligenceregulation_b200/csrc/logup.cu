@@ -61,48 +61,68 @@ __global__ void __launch_bounds__(128) k_logup_helpers(const int* __restrict__ i
     }
 }
 
-// 128-bit accumulate of a 64 x 8 bit unsigned product
-__device__ __forceinline__ void mac128(u64& lo, u64& hi, u64 w, u32 v) {
-    u64 pl = w * v, ph = __umul64hi(w, (u64)v);
-    lo += pl;
-    hi += ph + (lo < pl ? 1ull : 0ull);
-}
-__device__ __forceinline__ void add128(u64& lo, u64& hi, u64 l2, u64 h2) {
-    lo += l2;
-    hi += h2 + (lo < l2 ? 1ull : 0ull);
-}
-// (sum - 128 * wsum) mod p from the two 128-bit unsigned sums
-__device__ __forceinline__ u64 unbias(u64 lo, u64 hi, u64 wlo, u64 whi) {
-    u64 s = gl_reduce128(lo, hi), w = gl_reduce128(wlo, whi);
+// ---- int8 weight folds -----------------------------------------------------------------------
+// sum_i w_i * m_i with w_i a canonical u64 and m_i an int8: bias m by +128 so that it is unsigned, split w into
+// 32-bit halves, and the two half-sums  S0 = sum lo(w_i) (m_i + 128),  S1 = sum hi(w_i) (m_i + 128)  are plain
+// 64-bit accumulations of 32x8-bit products (below 2^40 each): no carries, no reduction, as long as fewer than
+// 2^16 terms go into one accumulator before it is folded into the running field value
+//   S0 + 2^32 S1 - 128 (W0 + 2^32 W1),   W0 = sum lo(w_i), W1 = sum hi(w_i).
+constexpr u32 I8_BLOCK = 1u << 15;
+
+__device__ __forceinline__ u64 i8_fold(u64 s0, u64 s1, u64 w0, u64 w1) {
+    // each argument is below 2^56: canonical; the result is the exact signed sum mod p
+    const u64 W32 = 1ull << 32;
+    u64 s = gl_add(s0, gl_mul(s1, W32)), w = gl_add(w0, gl_mul(w1, W32));
     return gl_sub(s, gl_mul(w, 128));
 }
 
 constexpr int FR_ROWS = 128;
-// out[j] = sum_i w[i] * M[i][j]; one thread per 4 neighbouring columns, rows staged 128 at a time
+// out[j] = sum_i w[i] * M[i][j]; one thread per 4 neighbouring columns (one 32-bit load per row), rows staged
+// FR_ROWS at a time in shared memory as (low, high) halves of both components
 __global__ void __launch_bounds__(128) k_fold_rows_i8(const signed char* __restrict__ m, u32 rows, u32 cols, const u64* __restrict__ w,
                                                       u64* __restrict__ out) {
-    __shared__ u64 ws[FR_ROWS][2];
+    __shared__ uint4 ws[FR_ROWS];  // (lo c0, hi c0, lo c1, hi c1)
     const u32 j4 = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
-    u64 lo[4][2] = {}, hi[4][2] = {}, wl[2] = {}, wh[2] = {};
+    const bool vec = (cols & 3u) == 0;
+    u64 run[4][2] = {}, s[4][4] = {}, wsum[4] = {};
+    u32 since = 0;
     for (u32 r0 = 0; r0 < rows; r0 += FR_ROWS) {
         const u32 nr = min((u32)FR_ROWS, rows - r0);
         __syncthreads();
-        for (u32 t = threadIdx.x; t < nr * 2; t += blockDim.x) ws[t >> 1][t & 1] = w[(size_t)(r0 + (t >> 1)) * 2 + (t & 1)];
+        for (u32 t = threadIdx.x; t < nr; t += blockDim.x) {
+            const u64 a = w[(size_t)(r0 + t) * 2], b = w[(size_t)(r0 + t) * 2 + 1];
+            ws[t] = make_uint4((u32)a, (u32)(a >> 32), (u32)b, (u32)(b >> 32));
+        }
         __syncthreads();
         if (j4 < cols) {
             for (u32 i = 0; i < nr; i++) {
                 const signed char* p = m + (size_t)(r0 + i) * cols + j4;
-                const u64 w0 = ws[i][0], w1 = ws[i][1];
-                add128(wl[0], wh[0], w0, 0);
-                add128(wl[1], wh[1], w1, 0);
+                u32 packed;
+                if (vec) {
+                    packed = *reinterpret_cast<const u32*>(p) ^ 0x80808080u;  // +128 on every byte
+                } else {
+                    packed = 0;
+                    for (u32 c = 0; c < 4 && j4 + c < cols; c++) packed |= (u32)((int)p[c] + 128) << (8 * c);
+                }
+                const uint4 wv = ws[i];
+                wsum[0] += wv.x; wsum[1] += wv.y; wsum[2] += wv.z; wsum[3] += wv.w;
 #pragma unroll
                 for (int c = 0; c < 4; c++) {
-                    if (j4 + c < cols) {
-                        u32 v = (u32)((int)p[c] + 128);
-                        mac128(lo[c][0], hi[c][0], w0, v);
-                        mac128(lo[c][1], hi[c][1], w1, v);
-                    }
+                    const u32 v = (packed >> (8 * c)) & 0xFFu;
+                    s[c][0] += (u64)wv.x * v; s[c][1] += (u64)wv.y * v;
+                    s[c][2] += (u64)wv.z * v; s[c][3] += (u64)wv.w * v;
                 }
+            }
+            since += nr;
+            if (since + FR_ROWS > I8_BLOCK || r0 + FR_ROWS >= rows) {
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    run[c][0] = gl_add(run[c][0], i8_fold(s[c][0], s[c][1], wsum[0], wsum[1]));
+                    run[c][1] = gl_add(run[c][1], i8_fold(s[c][2], s[c][3], wsum[2], wsum[3]));
+                    s[c][0] = s[c][1] = s[c][2] = s[c][3] = 0;
+                }
+                wsum[0] = wsum[1] = wsum[2] = wsum[3] = 0;
+                since = 0;
             }
         }
     }
@@ -110,8 +130,8 @@ __global__ void __launch_bounds__(128) k_fold_rows_i8(const signed char* __restr
 #pragma unroll
         for (int c = 0; c < 4; c++)
             if (j4 + c < cols) {
-                out[2 * (size_t)(j4 + c)] = unbias(lo[c][0], hi[c][0], wl[0], wh[0]);
-                out[2 * (size_t)(j4 + c) + 1] = unbias(lo[c][1], hi[c][1], wl[1], wh[1]);
+                out[2 * (size_t)(j4 + c)] = run[c][0];
+                out[2 * (size_t)(j4 + c) + 1] = run[c][1];
             }
     }
 }
@@ -121,32 +141,58 @@ __device__ __forceinline__ u64 shfl_xor64(u64 v, int m) {
     return ((u64)hi << 32) | lo;
 }
 
-// out[i] = sum_j c[j] * M[i][j]; one warp per row, lanes stride over the columns, warp tree on the 128-bit sums
-__global__ void __launch_bounds__(256) k_fold_cols_i8(const signed char* __restrict__ m, u32 rows, u32 cols, const u64* __restrict__ c,
-                                                      u64* __restrict__ out) {
-    const u32 row = blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (row >= rows) return;
-    const signed char* p = m + (size_t)row * cols;
-    u64 lo[2] = {}, hi[2] = {}, wl[2] = {}, wh[2] = {};
-    for (u32 j = lane; j < cols; j += 32) {
+// out[i] = sum_j c[j] * M[i][j]; one CTA per FC_ROWS rows, its eight warps interleaved over the columns: a lane loads
+// c[j] once (coalesced over the lanes) and multiplies it into the bytes of the FC_ROWS rows at column j; warp tree,
+// then a shared-memory sum over the warps
+constexpr int FC_ROWS = 4;
+constexpr int FC_WARPS = 8;
+__global__ void __launch_bounds__(32 * FC_WARPS) k_fold_cols_i8(const signed char* __restrict__ m, u32 rows, u32 cols, const u64* __restrict__ c,
+                                                                u64* __restrict__ out) {
+    __shared__ u64 part[FC_WARPS][FC_ROWS][2];
+    const u32 row0 = blockIdx.x * FC_ROWS, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const u32 nr = min((u32)FC_ROWS, rows - row0);
+    u64 s[FC_ROWS][4] = {}, ws[4] = {}, run[FC_ROWS][2] = {};
+    u32 since = 0;
+#pragma unroll 4
+    for (u32 j = threadIdx.x; j < cols; j += 32 * FC_WARPS) {
         const ulonglong2 cw = *reinterpret_cast<const ulonglong2*>(c + 2 * (size_t)j);
-        u32 v = (u32)((int)p[j] + 128);
-        mac128(lo[0], hi[0], cw.x, v);
-        mac128(lo[1], hi[1], cw.y, v);
-        add128(wl[0], wh[0], cw.x, 0);
-        add128(wl[1], wh[1], cw.y, 0);
-    }
+        const u32 a0 = (u32)cw.x, a1 = (u32)(cw.x >> 32), b0 = (u32)cw.y, b1 = (u32)(cw.y >> 32);
+        ws[0] += a0; ws[1] += a1; ws[2] += b0; ws[3] += b1;
 #pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) {
+        for (int r = 0; r < FC_ROWS; r++) {
+            if ((u32)r < nr) {
+                const u32 v = (u32)((int)m[(size_t)(row0 + r) * cols + j] + 128);
+                s[r][0] += (u64)a0 * v; s[r][1] += (u64)a1 * v; s[r][2] += (u64)b0 * v; s[r][3] += (u64)b1 * v;
+            }
+        }
+        if (++since == I8_BLOCK) {
 #pragma unroll
-        for (int k = 0; k < 2; k++) {
-            add128(lo[k], hi[k], shfl_xor64(lo[k], off), shfl_xor64(hi[k], off));
-            add128(wl[k], wh[k], shfl_xor64(wl[k], off), shfl_xor64(wh[k], off));
+            for (int r = 0; r < FC_ROWS; r++) {
+                run[r][0] = gl_add(run[r][0], i8_fold(s[r][0], s[r][1], ws[0], ws[1]));
+                run[r][1] = gl_add(run[r][1], i8_fold(s[r][2], s[r][3], ws[2], ws[3]));
+                s[r][0] = s[r][1] = s[r][2] = s[r][3] = 0;
+            }
+            ws[0] = ws[1] = ws[2] = ws[3] = 0;
+            since = 0;
         }
     }
-    if (lane == 0) {
-        out[2 * (size_t)row] = unbias(lo[0], hi[0], wl[0], wh[0]);
-        out[2 * (size_t)row + 1] = unbias(lo[1], hi[1], wl[1], wh[1]);
+#pragma unroll
+    for (int r = 0; r < FC_ROWS; r++) {
+        u64 x0 = gl_add(run[r][0], i8_fold(s[r][0], s[r][1], ws[0], ws[1]));
+        u64 x1 = gl_add(run[r][1], i8_fold(s[r][2], s[r][3], ws[2], ws[3]));
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+            x0 = gl_add(x0, shfl_xor64(x0, off));
+            x1 = gl_add(x1, shfl_xor64(x1, off));
+        }
+        if (lane == 0) { part[warp][r][0] = x0; part[warp][r][1] = x1; }
+    }
+    __syncthreads();
+    if (threadIdx.x < FC_ROWS * 2 && threadIdx.x / 2 < nr) {
+        u64 x = 0;
+#pragma unroll
+        for (int w = 0; w < FC_WARPS; w++) x = gl_add(x, part[w][threadIdx.x / 2][threadIdx.x & 1]);
+        out[2 * (size_t)(row0 + threadIdx.x / 2) + (threadIdx.x & 1)] = x;
     }
 }
 
@@ -176,7 +222,7 @@ cudaError_t fold_rows_i8(const signed char* d_m, u32 rows, u32 cols, const u64* 
 }
 
 cudaError_t fold_cols_i8(const signed char* d_m, u32 rows, u32 cols, const u64* d_c, u64* d_out, cudaStream_t st) {
-    k_fold_cols_i8<<<(rows + 7) / 8, 256, 0, st>>>(d_m, rows, cols, d_c, d_out);
+    k_fold_cols_i8<<<(rows + FC_ROWS - 1) / FC_ROWS, 32 * FC_WARPS, 0, st>>>(d_m, rows, cols, d_c, d_out);
     return cudaGetLastError();
 }
 

@@ -5,52 +5,128 @@
 
 namespace {
 
-constexpr int FOLD_G = 8;        // rho vectors per pass over the matrix
-constexpr int FOLD_ROWS = 64;    // rows of rho staged in shared memory at a time
-constexpr int FOLD_THREADS = 128;
+// ---------------------------------------------------------------------------------------------
+// out[g][out_off + j] = sum_i rho_g[i] * src[i * ld + j * ir]   (pcs.rs:342-378, 976-1000)
+//
+// A dense (2k x rows) by (rows x ncols) product over the field: 3.2 G multiply-adds for the 8B block's
+// opening (38 vectors, 2,504 rows, 16,664 columns).  Reducing every product would cost ~27 instructions
+// each, so products are accumulated as plain integers and reduced once per block of rows:
+// a matrix word is cut into limbs of 22 + 22 + 20 bits, a rho component into two 32-bit halves, and the
+// six limb products (each < 2^54) are summed in six 64-bit accumulators with 32x32+64 multiply-adds and
+// no carry handling at all.  After FOLD_BLOCK = 256 rows (sums < 2^62) the six accumulators are folded
+// into the running field value with their weights 2^(22a + 32b).  Field addition is exact, so the words
+// are those of the reference's per-element loop (its zero skips only save work).
+//
+// One thread owns one column and FOLD_RPT rho vectors (2 x FOLD_RPT base-field components); a CTA is
+// 128 columns x FOLD_GROUPS groups of vectors, so that the groups' reads of the same matrix words are
+// served by L1.  Grid: (column tiles, batches of FOLD_RPT * FOLD_GROUPS vectors).
+// ---------------------------------------------------------------------------------------------
+constexpr int FOLD_COLS = 128;
+constexpr int FOLD_GROUPS = 4;
+constexpr int FOLD_RPT = 2;                           // rho vectors per thread
+constexpr int FOLD_G = FOLD_RPT * FOLD_GROUPS;        // rho vectors per CTA
+constexpr int FOLD_BLOCK = 256;                       // rows between reductions
+constexpr int FOLD_THREADS = FOLD_COLS * FOLD_GROUPS;
 
-// out[g][out_off + j] = sum_i rho_g[i] * src[i * ld + j * ir]   (pcs.rs:342-378)
-// One thread per column j, up to FOLD_G combinations at once; the matrix is read once per
-// batch of FOLD_G vectors, coalesced along j.  Grid: (column tiles, batches of FOLD_G).
-__global__ void __launch_bounds__(FOLD_THREADS) k_fold_rows(const u64* __restrict__ src, u32 rows, u32 ncols, size_t ld, u32 ir,
+// Two column segments in one launch (the message columns and the pad columns of a hiding opening), so that
+// the narrow pad segment's few CTAs run beside the wide segment's instead of as a tail of their own.
+struct FoldSeg {
+    const u64* src;
+    size_t ld;
+    u32 ncols, ir, out_off, tiles;
+};
+
+__global__ void __launch_bounds__(FOLD_THREADS) k_fold_rows(FoldSeg seg0, FoldSeg seg1, u32 rows,
                                                             const u64* __restrict__ rhos /* k x rows x 2 */, u32 k,
-                                                            u64* __restrict__ out, u32 out_ld, u32 out_off) {
-    __shared__ u64 rho_s[FOLD_G][FOLD_ROWS][2];
-    const u32 j = blockIdx.x * blockDim.x + threadIdx.x;
+                                                            u64* __restrict__ out, u32 out_ld) {
+    __shared__ uint2 rho_s[FOLD_BLOCK][FOLD_G * 2];  // [row][vector * 2 + component] = (low half, high half)
+    const bool second = blockIdx.x >= seg0.tiles;
+    const u64* __restrict__ src = second ? seg1.src : seg0.src;
+    const size_t ld = second ? seg1.ld : seg0.ld;
+    const u32 ncols = second ? seg1.ncols : seg0.ncols, ir = second ? seg1.ir : seg0.ir, out_off = second ? seg1.out_off : seg0.out_off;
+    const u32 tile = second ? blockIdx.x - seg0.tiles : blockIdx.x;
+    const u32 col = tile * FOLD_COLS + (threadIdx.x % FOLD_COLS), grp = threadIdx.x / FOLD_COLS;
     const u32 g0 = blockIdx.y * FOLD_G;
     const u32 ng = min((u32)FOLD_G, k - g0);
-    fp2 acc[FOLD_G];
+    constexpr int NC = FOLD_RPT * 2;  // components per thread
+    u64 run[NC];
 #pragma unroll
-    for (int g = 0; g < FOLD_G; g++) acc[g] = f2(0, 0);
-    for (u32 r0 = 0; r0 < rows; r0 += FOLD_ROWS) {
-        const u32 nr = min((u32)FOLD_ROWS, rows - r0);
+    for (int c = 0; c < NC; c++) run[c] = 0;
+    // weights of the six limb products: 2^(22 a + 32 b), a = 0..2, b = 0..1
+    const u64 W22 = 1ull << 22, W44 = 1ull << 44, W32 = 1ull << 32, W54 = 1ull << 54;
+    const u64 W76 = gl_reduce128(0, 1ull << 12);  // 2^76 mod p
+    for (u32 r0 = 0; r0 < rows; r0 += FOLD_BLOCK) {
+        const u32 nr = min((u32)FOLD_BLOCK, rows - r0);
         __syncthreads();
-        for (u32 t = threadIdx.x; t < ng * nr * 2; t += blockDim.x) {
-            u32 g = t / (nr * 2), rem = t % (nr * 2);
-            rho_s[g][rem >> 1][rem & 1] = rhos[((size_t)(g0 + g) * rows + r0) * 2 + rem];
+        for (u32 t = threadIdx.x; t < nr * FOLD_G * 2; t += FOLD_THREADS) {
+            const u32 i = t / (FOLD_G * 2), gc = t % (FOLD_G * 2), g = gc >> 1;
+            u64 w = g < ng ? rhos[((size_t)(g0 + g) * rows + r0 + i) * 2 + (gc & 1)] : 0ull;
+            rho_s[i][gc] = make_uint2((u32)w, (u32)(w >> 32));
         }
         __syncthreads();
-        if (j < ncols) {
-            for (u32 i = 0; i < nr; i++) {
-                const u64 v = src[(size_t)(r0 + i) * ld + (size_t)j * ir];
+        if (col < ncols && grp * FOLD_RPT < ng) {
+            u64 acc[NC][6];
 #pragma unroll
-                for (int g = 0; g < FOLD_G; g++) {
-                    if (g < (int)ng) {
-                        acc[g].c0 = gl_add(acc[g].c0, gl_mul(rho_s[g][i][0], v));
-                        acc[g].c1 = gl_add(acc[g].c1, gl_mul(rho_s[g][i][1], v));
+            for (int c = 0; c < NC; c++)
+#pragma unroll
+                for (int x = 0; x < 6; x++) acc[c][x] = 0;
+            const u64* p = src + (size_t)r0 * ld + (size_t)col * ir;
+            constexpr int PF = 8;  // rows fetched ahead: eight independent loads in flight per thread
+            u64 nxt[PF];
+#pragma unroll
+            for (int x = 0; x < PF; x++) nxt[x] = (u32)x < nr ? p[(size_t)x * ld] : 0ull;
+            for (u32 i0 = 0; i0 < nr; i0 += PF) {
+                u64 cur[PF];
+#pragma unroll
+                for (int x = 0; x < PF; x++) cur[x] = nxt[x];
+#pragma unroll
+                for (int x = 0; x < PF; x++) nxt[x] = i0 + PF + x < nr ? p[(size_t)(i0 + PF + x) * ld] : 0ull;
+#pragma unroll
+                for (int x = 0; x < PF; x++) {
+                    if (i0 + x < nr) {
+                        const u64 v = cur[x];
+                        const u32 v0 = (u32)v & 0x3FFFFFu, v1 = (u32)(v >> 22) & 0x3FFFFFu, v2 = (u32)(v >> 44);
+                        // an opening's group weights are zero outside their claims' rows (pcs.rs:851-891): skip those
+                        // rows for this thread's vectors; the test is uniform over the warp
+                        u32 any = 0;
+#pragma unroll
+                        for (int c = 0; c < NC; c++) any |= rho_s[i0 + x][grp * NC + c].x | rho_s[i0 + x][grp * NC + c].y;
+                        if (any == 0) continue;
+#pragma unroll
+                        for (int c = 0; c < NC; c++) {
+                            const uint2 r = rho_s[i0 + x][grp * NC + c];
+                            acc[c][0] += (u64)v0 * r.x;
+                            acc[c][1] += (u64)v1 * r.x;
+                            acc[c][2] += (u64)v2 * r.x;
+                            acc[c][3] += (u64)v0 * r.y;
+                            acc[c][4] += (u64)v1 * r.y;
+                            acc[c][5] += (u64)v2 * r.y;
+                        }
                     }
                 }
             }
+#pragma unroll
+            for (int c = 0; c < NC; c++) {  // every accumulator is below 2^62 < p: already a canonical word
+                u64 s = acc[c][0];
+                s = gl_add(s, gl_mul(acc[c][1], W22));
+                s = gl_add(s, gl_mul(acc[c][2], W44));
+                s = gl_add(s, gl_mul(acc[c][3], W32));
+                s = gl_add(s, gl_mul(acc[c][4], W54));
+                s = gl_add(s, gl_mul(acc[c][5], W76));
+                run[c] = gl_add(run[c], s);
+            }
         }
     }
-    if (j < ncols) {
+    if (col < ncols) {
 #pragma unroll
-        for (int g = 0; g < FOLD_G; g++)
-            if (g < (int)ng) {
-                u64* o = out + ((size_t)(g0 + g) * out_ld + out_off + j) * 2;
-                o[0] = acc[g].c0;
-                o[1] = acc[g].c1;
+        for (int v = 0; v < FOLD_RPT; v++) {
+            const u32 g = grp * FOLD_RPT + v;
+            if (g < ng) {
+                u64* o = out + ((size_t)(g0 + g) * out_ld + out_off + col) * 2;
+                o[0] = run[2 * v];
+                o[1] = run[2 * v + 1];
             }
+        }
     }
 }
 
@@ -66,11 +142,13 @@ __global__ void k_gather_cols(const u64* __restrict__ enc, u32 rows, size_t nn, 
 
 namespace hlk {
 
-cudaError_t fold_rows(const u64* src, u32 rows, u32 ncols, size_t ld, u32 ir, const u64* d_rhos, u32 k, u64* d_out,
-                      u32 out_ld, u32 out_off, cudaStream_t st) {
+cudaError_t fold_rows(const u64* src, u32 rows, u32 ncols, size_t ld, u32 ir, const u64* src2, u32 ncols2, size_t ld2,
+                      const u64* d_rhos, u32 k, u64* d_out, u32 out_ld, cudaStream_t st) {
     if (k == 0 || ncols == 0) return cudaSuccess;
-    dim3 grid((ncols + FOLD_THREADS - 1) / FOLD_THREADS, (k + FOLD_G - 1) / FOLD_G);
-    k_fold_rows<<<grid, FOLD_THREADS, 0, st>>>(src, rows, ncols, ld, ir, d_rhos, k, d_out, out_ld, out_off);
+    FoldSeg a{src, ld, ncols, ir, 0u, (ncols + FOLD_COLS - 1) / FOLD_COLS};
+    FoldSeg b{src2, ld2, src2 ? ncols2 : 0u, 1u, ncols, src2 ? (ncols2 + FOLD_COLS - 1) / FOLD_COLS : 0u};
+    dim3 grid(a.tiles + b.tiles, (k + FOLD_G - 1) / FOLD_G);
+    k_fold_rows<<<grid, FOLD_THREADS, 0, st>>>(a, b, rows, d_rhos, k, d_out, out_ld);
     return cudaGetLastError();
 }
 
