@@ -56,9 +56,18 @@ const char* hl_b200_last_error(hl_ctx* ctx);
 /* Run the context's work on the caller's CUDA stream (a cudaStream_t); NULL restores its own. */
 int hl_b200_set_stream(hl_ctx* ctx, void* cuda_stream);
 int hl_b200_sync(hl_ctx* ctx);
+/* Failure injection on the HOST side (hashline/src/gpu/mod.rs:121 set_alloc_cap_for_test): with a cap, a device
+ * allocation that would bring the context's live bytes above `bytes` fails with HL_B200_ERR_OOM before the
+ * runtime is asked; 0 removes the cap.  Nothing on the device is made to fault. */
+int hl_b200_set_alloc_cap(hl_ctx* ctx, size_t bytes);
 /* Which encoder runs: 0 = radix-2 shared-memory stages (any n <= 2^14), 1 = the 16-point
  * register passes when 2^8 <= n <= 2^14 (default).  Same words either way. */
 int hl_b200_set_encoder(hl_ctx* ctx, int fast);
+
+/* ---- integer-issue ceiling (no counterpart in the reference; a measurement aid) ----
+ * Runs the encoder's butterfly arithmetic on registers only, on every SM, and reports radix-2 Goldilocks
+ * butterflies per second: the denominator for the encoder's integer-pipe utilisation. */
+int hl_b200_butterfly_peak(hl_ctx* ctx, uint32_t iters, double* butterflies_per_second);
 
 /* ---- field self-test: metal_probe_field (tests/zk60_metal_commit.rs:69-89), k_probe ----
  * out3n[3i..3i+2] = (a_i + b_i, a_i - b_i, a_i * b_i) */

@@ -70,6 +70,10 @@ SIGNATURES.update({
     "hl_b200_fold_cols_i8": (_int, [_vp, _vp, _sz, _sz, _vp, _vp]),
 })
 
+SIGNATURES["hl_b200_butterfly_peak"] = (_int, [_vp, _u32, C.POINTER(C.c_double)])
+
+SIGNATURES["hl_b200_set_alloc_cap"] = (_int, [_vp, _sz])
+
 T_NAMES = ("encode", "hash", "merkle", "fold", "gather", "rounds", "logup")
 
 

@@ -85,6 +85,10 @@ class Context:
     def set_encoder(self, fast: bool) -> None:
         self.check(self.lib.hl_b200_set_encoder(self.h, 1 if fast else 0))
 
+    def set_alloc_cap(self, nbytes: int) -> None:
+        """Host-side allocation-failure injection (0 = no cap)."""
+        self.check(self.lib.hl_b200_set_alloc_cap(self.h, nbytes))
+
     def sync(self) -> None:
         self.check(self.lib.hl_b200_sync(self.h))
 
@@ -101,6 +105,12 @@ class Context:
         t = _lib.Timing()
         self.check(self.lib.hl_b200_timing_read(self.h, C.byref(t), 1 if reset else 0))
         return {n: (float(t.ms[i]), int(t.spans[i])) for i, n in enumerate(_lib.T_NAMES)}
+
+    def butterfly_peak(self, iters: int = 400) -> float:
+        """Register-resident radix-2 butterflies per second on this device (the encoder's integer ceiling)."""
+        v = C.c_double()
+        self.check(self.lib.hl_b200_butterfly_peak(self.h, iters, C.byref(v)))
+        return float(v.value)
 
     def probe_field(self, a, b) -> np.ndarray:
         """metal_probe_field: (a+b, a-b, a*b) per pair, shape (n, 3)."""

@@ -209,6 +209,13 @@ int hl_b200_sync(hl_ctx* c) {
     return sync(c, "synchronize");
 }
 
+int hl_b200_set_alloc_cap(hl_ctx* c, size_t bytes) {
+    if (!c) return HL_B200_ERR_ARG;
+    std::lock_guard<std::mutex> g(c->mu);
+    c->alloc_cap = bytes;
+    return HL_B200_OK;
+}
+
 int hl_b200_set_encoder(hl_ctx* c, int fast) {
     if (!c) return HL_B200_ERR_ARG;
     c->fast_encoder = fast != 0;
@@ -240,6 +247,38 @@ int hl_b200_probe_field(hl_ctx* c, const uint64_t* a, const uint64_t* b, size_t 
     if (!rc) rc = d2h(c, out3n, dout, n * 24);
     if (!rc) rc = sync(c, "probe_field");
     dev_free(c, da, n * 8); dev_free(c, db, n * 8); dev_free(c, dout, n * 24);
+    return rc;
+}
+
+int hl_b200_butterfly_peak(hl_ctx* c, uint32_t iters, double* butterflies_per_second) {
+    if (!c || !butterflies_per_second || iters == 0) return fail(c, HL_B200_ERR_ARG, "butterfly_peak: argument");
+    std::lock_guard<std::mutex> g(c->mu);
+    cudaSetDevice(c->device);
+    std::vector<u64> seed(4096);
+    u64 x = 88172645463325252ULL;
+    for (auto& v : seed) { x ^= x << 13; x ^= x >> 7; x ^= x << 17; v = gl_canon(x); }
+    u64 *d_seed = nullptr, *d_sink = nullptr;
+    int rc = dev_alloc(c, (void**)&d_seed, 4096 * 8);
+    if (!rc) rc = dev_alloc(c, (void**)&d_sink, 8);
+    if (!rc) rc = h2d(c, d_seed, seed.data(), 4096 * 8);
+    cudaEvent_t a = nullptr, b = nullptr;
+    float ms = 0.f;
+    const int blocks = c->sm_count * 8;
+    if (!rc) {
+        cudaEventCreate(&a); cudaEventCreate(&b);
+        cudaError_t e = hlk::butterfly_peak(d_seed, d_sink, 8, blocks, c->stream);  // warm-up
+        cudaEventRecord(a, c->stream);
+        if (e == cudaSuccess) e = hlk::butterfly_peak(d_seed, d_sink, iters, blocks, c->stream);
+        cudaEventRecord(b, c->stream);
+        c->stats.kernel_launches += 2;
+        if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "butterfly_peak launch", e);
+    }
+    if (!rc) rc = sync(c, "butterfly_peak");
+    if (!rc && cudaEventElapsedTime(&ms, a, b) != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "butterfly_peak timing");
+    if (a) cudaEventDestroy(a);
+    if (b) cudaEventDestroy(b);
+    dev_free(c, d_seed, 4096 * 8); dev_free(c, d_sink, 8);
+    if (!rc) *butterflies_per_second = (double)blocks * 256.0 * 32.0 * iters / (ms * 1e-3);
     return rc;
 }
 

@@ -203,10 +203,24 @@ int hl_b200_rounds_batched(hl_rounds* r, uint32_t nd, hl_fs_state* fs, const uin
     bool have_claim = fs->recover_one && fs->have_claim;
     {
         Timed t(c, HL_T_ROUNDS);
-        for (u32 i = 0; i < nd && !rc; i++) {
+        u32 i = 0;
+        for (; i < nd && !rc && r->len > hlk::SC_TAIL_LEN; i++) {
             rc = launch_round(r, have_claim ? 0 : 1, 1, have_claim ? 1 : 0, fs->recover_one ? 1 : 0, d_mask, d_hs, (int)mask_vars);
             if (!rc) rc = launch_fold(r);
             have_claim = fs->recover_one != 0;
+        }
+        if (!rc && i < nd) {  // the short rounds: one CTA, no launches in between
+            hlk::ScStep a;
+            a.partials = r->d_partials; a.nblocks = 1; a.degree = (int)r->degree; a.round = (int)r->next;
+            a.use_claim = 0; a.recover = fs->recover_one ? 1 : 0; a.fs = 1; a.mask = d_mask; a.mask_half_suffix = d_hs; a.mask_vars = (int)mask_vars;
+            a.inv_den = r->d_inv_den; a.state = r->d_state; a.out = r->d_out;
+            const u32 left = nd - i;
+            cudaError_t e = hlk::sc_tail(r->poly, (int)r->k, r->d_tables, r->stride, (u32)r->len, r->d_coefs, a, (int)left, have_claim ? 1 : 0,
+                                         r->d_partials, c->stream);
+            c->stats.kernel_launches++;
+            if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "tail rounds launch", e);
+            r->len >>= left;
+            r->next += left;
         }
     }
     if (!rc) rc = d2h(c, out, r->d_out + (size_t)first * r->out_row(), (size_t)nd * r->out_row() * 8);

@@ -104,6 +104,7 @@ __global__ void __launch_bounds__(RT) k_sc_round(const u64* __restrict__ tables,
 __device__ void hash_small(const uint32_t* key, const uint32_t* words, u32 len, uint32_t (&out)[8]) {
     b3::init_cv(out, key);
     const u32 nb = len ? (len + 63) / 64 : 1;
+#pragma unroll 1
     for (u32 b = 0; b < nb; b++) {
         uint32_t m[16];
 #pragma unroll
@@ -117,90 +118,219 @@ __device__ __forceinline__ u64 reduce_le16(const uint32_t* w) {  // 128-bit litt
     return gl_reduce128(((u64)w[1] << 32) | w[0], ((u64)w[3] << 32) | w[2]);
 }
 
-// One warp.  Lanes share the partial sums; lane 0 runs the serial Fiat-Shamir step.
-__global__ void __launch_bounds__(32) k_sc_step(ScStep a) {
-    __shared__ u64 sums[2 * hlk::SC_MAX_POINTS];
-    __shared__ __align__(16) uint32_t msg[64];  // 256 bytes
-    const int lane = threadIdx.x, W = 2 * (a.degree + 1);
-    for (int w = 0; w < W; w++) {
-        u64 s = 0;
-        for (u32 b = lane; b < a.nblocks; b += 32) s = gl_add(s, a.partials[(size_t)b * W + w]);
-#pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) s = gl_add(s, shfl_down64(s, off));
-        if (lane == 0) sums[w] = s;
-    }
-    __syncwarp();
-    if (lane != 0) return;
+__device__ __forceinline__ fp2 shfl_down_f2(fp2 v, int d) { return f2(shfl_down64(v.c0, d), shfl_down64(v.c1, d)); }
+
+// One warp.  The field work is spread over the lanes (one evaluation point per lane); only the two transcript
+// hashes run on lane 0.
+struct StepSmem {
+    u64 sums[2 * hlk::SC_MAX_POINTS];
+    u64 mskd[2 * hlk::SC_MAX_POINTS];
+    u64 chal[2];
+    __align__(16) uint32_t msg[64];  // 256 bytes
+};
+
+// One warp; sm.sums already holds the round's D+1 sums.
+__device__ void step_body(const ScStep& a, StepSmem& sm, int lane) {
+    u64* sums = sm.sums;
+    u64* mskd = sm.mskd;
+    u64* chal = sm.chal;
+    uint32_t* msg = sm.msg;
+    const int np = a.degree + 1, W = 2 * np, j = a.round;
     hlk::ScState* st = a.state;
     fp2* s = reinterpret_cast<fp2*>(sums);
-    const int np = a.degree + 1;
-    if (a.use_claim) s[1] = f2_sub(st->claim, s[0]);          // s(1) = claim - s(0) (rounds.rs:137-140)
-    u64* orow = a.out + (size_t)a.round * (2 * (size_t)np + 1) * 2;
-    for (int d = 0; d < np; d++) st2(orow + 2 * d, s[d]);
-    if (!a.fs) return;                                          // plain round(): the host drives the transcript
-    // masked message s + c g_j (sumcheck.rs:260-295)
-    fp2 masked[hlk::SC_MAX_POINTS];
-    for (int d = 0; d < np; d++) masked[d] = s[d];
+    if (lane == 0 && a.use_claim) s[1] = f2_sub(st->claim, s[0]);  // s(1) = claim - s(0) (rounds.rs:137-140)
+    __syncwarp();
+    u64* orow = a.out + (size_t)j * (2 * (size_t)np + 1) * 2;
+    if (lane < np) st2(orow + 2 * lane, s[lane]);
+    if (!a.fs) return;  // plain round(): the host drives the transcript
     const fp2* mk = reinterpret_cast<const fp2*>(a.mask);
-    const int j = a.round;
-    if (mk) {
-        const fp2* aj = mk + 2 + (size_t)j * a.degree;
-        fp2 base = f2_add(f2_add(mk[0], st->acc_prev), reinterpret_cast<const fp2*>(a.mask_half_suffix)[j]);
-        fp2 ap = f2_mul(mk[1], st->prod_prev);
-        u64 scale = gl_pow(2, a.mask_vars - 1 - j);
-        for (int x = 0; x < np; x++) {
+    // masked message s + c g_j, one point x per lane (sumcheck.rs:260-295):
+    //   g_j(x) = 2^(N-1-j) (a0 + sum_{i<j} u_i(r_i) + sum_{i>j} u_i(1)/2 + u_j(x)) + a' (prod_{i<j} r_i) x
+    if (lane < np) {
+        fp2 m = s[lane];
+        if (mk) {
+            const fp2* aj = mk + 2 + (size_t)j * a.degree;
+            const fp2 base = f2_add(f2_add(mk[0], st->acc_prev), reinterpret_cast<const fp2*>(a.mask_half_suffix)[j]);
+            const u64 scale = 1ull << (a.mask_vars - 1 - j);  // mask_vars <= 63: the power of two is its own canonical word
+            const u64 x = (u64)lane;
             fp2 u = f2(0, 0);
             u64 xp = 1;
-            for (int e = 1; e <= a.degree; e++) { xp = gl_mul(xp, (u64)x); u = f2_add(u, f2_mul_base(aj[e - 1], xp)); }
-            fp2 g = f2_add(f2_mul_base(f2_add(base, u), scale), f2_mul_base(ap, (u64)x));
-            masked[x] = f2_add(s[x], f2_mul(st->mask_c, g));
+            for (int e = 1; e <= a.degree; e++) { xp = gl_mul(xp, x); u = f2_add(u, f2_mul_base(aj[e - 1], xp)); }
+            const fp2 g = f2_add(f2_mul_base(f2_add(base, u), scale), f2_mul_base(f2_mul(mk[1], st->prod_prev), x));
+            m = f2_add(m, f2_mul(st->mask_c, g));
         }
+        st2(mskd + 2 * lane, m);
+        st2(orow + 2 * (np + lane), m);
     }
-    for (int d = 0; d < np; d++) st2(orow + 2 * (np + d), masked[d]);
-    // absorb: state' = H(state || LE64(8) || "sc-round" || LE64(16 np) || bytes) (transcript.rs:67-74)
-    const uint32_t* key = st->keyed ? st->key : nullptr;
-    for (int i = 0; i < 64; i++) msg[i] = 0;
-    for (int i = 0; i < 8; i++) msg[i] = st->state[i];
-    msg[8] = 8; msg[9] = 0;
-    msg[10] = 0x722d6373u; msg[11] = 0x646e756fu;              // "sc-r" "ound", little-endian words
-    msg[12] = 16u * np; msg[13] = 0;
-    for (int d = 0; d < np; d++) {
-        msg[14 + 4 * d] = (uint32_t)masked[d].c0; msg[15 + 4 * d] = (uint32_t)(masked[d].c0 >> 32);
-        msg[16 + 4 * d] = (uint32_t)masked[d].c1; msg[17 + 4 * d] = (uint32_t)(masked[d].c1 >> 32);
+    __syncwarp();
+    if (lane == 0) {
+        // absorb: state' = H(state || LE64(8) || "sc-round" || LE64(16 np) || bytes) (transcript.rs:67-74)
+        const uint32_t* key = st->keyed ? st->key : nullptr;
+        for (int i = 0; i < 64; i++) msg[i] = 0;
+        for (int i = 0; i < 8; i++) msg[i] = st->state[i];
+        msg[8] = 8; msg[9] = 0;
+        msg[10] = 0x722d6373u; msg[11] = 0x646e756fu;  // "sc-r" "ound", little-endian words
+        msg[12] = 16u * np; msg[13] = 0;
+        for (int d = 0; d < W; d++) { msg[14 + 2 * d] = (uint32_t)mskd[d]; msg[15 + 2 * d] = (uint32_t)(mskd[d] >> 32); }
+        uint32_t h[8];
+        hash_small(key, msg, 56 + 16 * np, h);
+        // squeeze: out = H(state || "squeeze" || LE64(counter)); counter++; state = out (transcript.rs:120-130)
+        for (int i = 0; i < 16; i++) msg[i] = 0;
+        for (int i = 0; i < 8; i++) msg[i] = h[i];
+        const u64 ctr = st->counter;
+        msg[8] = 0x65757173u;                                   // "sque"
+        msg[9] = 0x00657a65u | ((uint32_t)(ctr & 0xff) << 24);  // "eze" then counter byte 0
+        msg[10] = (uint32_t)(ctr >> 8);
+        msg[11] = (uint32_t)(ctr >> 40);                        // counter bytes 5..7; the message ends there
+        hash_small(key, msg, 47, h);
+        st->counter = ctr + 1;
+        for (int i = 0; i < 8; i++) st->state[i] = h[i];
+        const fp2 r = f2(reduce_le16(h), reduce_le16(h + 4));
+        chal[0] = r.c0; chal[1] = r.c1;
+        st2(orow + 4 * np, r);
+        st->r = r;
     }
-    uint32_t h[8];
-    hash_small(key, msg, 56 + 16 * np, h);
-    // squeeze: out = H(state || "squeeze" || LE64(counter)); counter++; state = out (transcript.rs:120-130)
-    for (int i = 0; i < 16; i++) msg[i] = 0;
-    for (int i = 0; i < 8; i++) msg[i] = h[i];
-    const u64 ctr = st->counter;
-    msg[8] = 0x65757173u;                                       // "sque"
-    msg[9] = 0x00657a65u | ((uint32_t)(ctr & 0xff) << 24);      // "eze" then counter byte 0
-    msg[10] = (uint32_t)(ctr >> 8);
-    msg[11] = (uint32_t)(ctr >> 40);                            // bytes 5..7 (top byte of the word is zero)
-    hash_small(key, msg, 47, h);
-    st->counter = ctr + 1;
-    for (int i = 0; i < 8; i++) st->state[i] = h[i];
-    fp2 r = f2(reduce_le16(h), reduce_le16(h + 4));
-    st2(orow + 4 * np, r);
-    st->r = r;
-    // next claim = the UNMASKED round polynomial at r (rounds.rs:145-147; mle.rs:338-351)
+    __syncwarp();
+    const fp2 r = f2(chal[0], chal[1]);
+    // next claim = the UNMASKED round polynomial at r, one Lagrange term per lane (rounds.rs:145-147; mle.rs:338-351)
     if (a.recover) {
-        fp2 accv = f2(0, 0);
-        for (int i = 0; i < np; i++) {
+        fp2 term = f2(0, 0);
+        if (lane < np) {
             fp2 num = f2_one();
             for (int jj = 0; jj < np; jj++)
-                if (jj != i) num = f2_mul(num, f2(gl_sub(r.c0, (u64)jj), r.c1));
-            accv = f2_add(accv, f2_mul_base(f2_mul(s[i], num), a.inv_den[i]));
+                if (jj != lane) num = f2_mul(num, f2(gl_sub(r.c0, (u64)jj), r.c1));
+            term = f2_mul_base(f2_mul(s[lane], num), a.inv_den[lane]);
         }
-        st->claim = accv;
+#pragma unroll
+        for (int off = 4; off >= 1; off >>= 1) term = f2_add(term, shfl_down_f2(term, off));  // np <= 8
+        if (lane == 0) st->claim = term;
     }
-    if (mk) {  // the mask's running terms: sum_i u_i(r_i) and prod r_i
+    if (mk && lane == 8) {  // the mask's running terms: sum_i u_i(r_i) and prod r_i
         const fp2* aj = mk + 2 + (size_t)j * a.degree;
         fp2 u = f2(0, 0), xp = f2_one();
         for (int e = 1; e <= a.degree; e++) { xp = f2_mul(xp, r); u = f2_add(u, f2_mul(aj[e - 1], xp)); }
         st->acc_prev = f2_add(st->acc_prev, u);
         st->prod_prev = f2_mul(st->prod_prev, r);
+    }
+}
+
+// The CTA partials of a round are summed by all STEP_T threads (independent loads, shared-memory tree);
+// warp 0 then runs the Fiat-Shamir step.
+constexpr int STEP_T = 512;
+__global__ void __launch_bounds__(STEP_T) k_sc_step(ScStep a) {
+    __shared__ StepSmem sm;
+    __shared__ u64 red[STEP_T];
+    const int W = 2 * (a.degree + 1);              // <= 16 words per partial row
+    const int w = threadIdx.x & 15, grp = threadIdx.x >> 4;  // STEP_T / 16 groups stride over the rows
+    u64 s = 0;
+    if (w < W) {
+#pragma unroll 4
+        for (u32 b = grp; b < a.nblocks; b += STEP_T / 16) s = gl_add(s, a.partials[(size_t)b * W + w]);
+    }
+    red[threadIdx.x] = s;
+    __syncthreads();
+    for (int stride = STEP_T / 2; stride >= 16; stride >>= 1) {
+        if (threadIdx.x < stride) red[threadIdx.x] = gl_add(red[threadIdx.x], red[threadIdx.x + stride]);
+        __syncthreads();
+    }
+    if (threadIdx.x < W) sm.sums[threadIdx.x] = red[threadIdx.x];
+    __syncthreads();
+    if (threadIdx.x < 32) step_body(a, sm, threadIdx.x);
+}
+
+// The tail of a sumcheck in ONE CTA: once a round has at most TAIL_HALF pairs, the remaining rounds (round sums,
+// Fiat-Shamir step, fold) run back to back behind block barriers instead of three launches per round.
+constexpr int TAIL_T = 1024;
+template <int POLY, int K, int D>
+__global__ void __launch_bounds__(TAIL_T) k_sc_tail(u64* __restrict__ tables, size_t stride, u32 len, const u64* __restrict__ coefs,
+                                                    ScStep a, int nrounds, int first_has_claim, u64* __restrict__ scratch) {
+    __shared__ StepSmem sm;
+    __shared__ u64 wsum[TAIL_T / 32][2 * (D + 1)];
+    // the evaluator state, the mask and the Lagrange denominators stay in shared memory for the whole tail:
+    // the serial step then waits on no global load
+    __shared__ hlk::ScState st_s;
+    __shared__ u64 mask_s[2 * (63 * D + 2)];
+    __shared__ u64 hs_s[2 * 63];
+    __shared__ u64 invden_s[hlk::SC_MAX_POINTS];
+    const fp2* cf = reinterpret_cast<const fp2*>(coefs);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    {
+        const u32* src = reinterpret_cast<const u32*>(a.state);
+        u32* dst = reinterpret_cast<u32*>(&st_s);
+        for (u32 i = threadIdx.x; i < sizeof(hlk::ScState) / 4; i += TAIL_T) dst[i] = src[i];
+        if (a.mask) {
+            for (u32 i = threadIdx.x; i < 2u * (a.mask_vars * D + 2); i += TAIL_T) mask_s[i] = a.mask[i];
+            for (u32 i = threadIdx.x; i < 2u * a.mask_vars; i += TAIL_T) hs_s[i] = a.mask_half_suffix[i];
+        }
+        if (threadIdx.x <= D) invden_s[threadIdx.x] = a.inv_den[threadIdx.x];
+    }
+    hlk::ScState* const st_global = a.state;
+    if (a.mask) { a.mask = mask_s; a.mask_half_suffix = hs_s; }
+    a.inv_den = invden_s;
+    a.state = &st_s;
+    __syncthreads();
+    for (int rd = 0; rd < nrounds; rd++) {
+        const u32 half = len >> 1;
+        const bool have_claim = a.recover && (rd > 0 || first_has_claim);
+        fp2 acc[D + 1];
+#pragma unroll
+        for (int d = 0; d <= D; d++) acc[d] = f2(0, 0);
+        for (u32 i = threadIdx.x; i < half; i += TAIL_T) {
+            fp2 cur[K], dif[K];
+#pragma unroll
+            for (int t = 0; t < K; t++) {
+                const u64* tb = tables + 2 * (size_t)t * stride;
+                cur[t] = ld2(tb + 2 * (size_t)i);
+                dif[t] = f2_sub(ld2(tb + 2 * ((size_t)i + half)), cur[t]);
+            }
+            acc[0] = f2_add(acc[0], poly_eval<POLY, K>(cur, cf));
+#pragma unroll
+            for (int d = 1; d <= D; d++) {
+#pragma unroll
+                for (int t = 0; t < K; t++) cur[t] = f2_add(cur[t], dif[t]);
+                if (d != 1 || !have_claim) acc[d] = f2_add(acc[d], poly_eval<POLY, K>(cur, cf));
+            }
+        }
+#pragma unroll
+        for (int d = 0; d <= D; d++) {
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) {
+                acc[d].c0 = gl_add(acc[d].c0, shfl_down64(acc[d].c0, off));
+                acc[d].c1 = gl_add(acc[d].c1, shfl_down64(acc[d].c1, off));
+            }
+        }
+        if (lane == 0) {
+#pragma unroll
+            for (int d = 0; d <= D; d++) { wsum[warp][2 * d] = acc[d].c0; wsum[warp][2 * d + 1] = acc[d].c1; }
+        }
+        __syncthreads();
+        if (threadIdx.x < 2 * (D + 1)) {
+            u64 s = 0;
+#pragma unroll
+            for (int w = 0; w < TAIL_T / 32; w++) s = gl_add(s, wsum[w][threadIdx.x]);
+            sm.sums[threadIdx.x] = s;
+        }
+        __syncthreads();
+        if (warp == 0) {
+            ScStep b = a;
+            b.round = a.round + rd; b.use_claim = have_claim ? 1 : 0; b.fs = 1;
+            step_body(b, sm, lane);
+        }
+        __syncthreads();
+        const fp2 r = a.state->r;
+        for (u32 x = threadIdx.x; x < half * K; x += TAIL_T) {
+            const u32 t = x / half, i = x - t * half;
+            u64* tb = tables + 2 * (size_t)t * stride;
+            fp2 p = ld2(tb + 2 * (size_t)i), q = ld2(tb + 2 * ((size_t)i + half));
+            st2(tb + 2 * (size_t)i, f2_add(p, f2_mul(r, f2_sub(q, p))));
+        }
+        __syncthreads();
+        len = half;
+    }
+    {
+        const u32* src = reinterpret_cast<const u32*>(&st_s);
+        u32* dst = reinterpret_cast<u32*>(st_global);
+        for (u32 i = threadIdx.x; i < sizeof(hlk::ScState) / 4; i += TAIL_T) dst[i] = src[i];
     }
 }
 
@@ -258,8 +388,37 @@ cudaError_t sc_round(int poly, int k, const u64* tables, size_t stride, u32 half
     return cudaErrorInvalidValue;
 }
 
+template <int POLY, int K, int D>
+static cudaError_t launch_tail(u64* tables, size_t stride, u32 len, const u64* coefs, const ScStep& a, int nrounds, int first_has_claim,
+                               u64* scratch, cudaStream_t s) {
+    k_sc_tail<POLY, K, D><<<1, TAIL_T, 0, s>>>(tables, stride, len, coefs, a, nrounds, first_has_claim, scratch);
+    return cudaGetLastError();
+}
+
+cudaError_t sc_tail(int poly, int k, u64* tables, size_t stride, u32 len, const u64* coefs, const ScStep& a, int nrounds,
+                    int first_has_claim, u64* scratch, cudaStream_t s) {
+#define R(P, K, D) return launch_tail<P, K, D>(tables, stride, len, coefs, a, nrounds, first_has_claim, scratch, s)
+    switch (poly) {
+        case POLY_PROD:
+            switch (k) {
+                case 1: R(POLY_PROD, 1, 1);
+                case 2: R(POLY_PROD, 2, 2);
+                case 3: R(POLY_PROD, 3, 3);
+                case 4: R(POLY_PROD, 4, 4);
+                case 5: R(POLY_PROD, 5, 5);
+                case 6: R(POLY_PROD, 6, 6);
+            }
+            break;
+        case POLY_ZC: R(POLY_ZC, 4, 3);
+        case POLY_LOGUP_Q: R(POLY_LOGUP_Q, 3, 3);
+        case POLY_LOGUP_T: R(POLY_LOGUP_T, 4, 3);
+    }
+#undef R
+    return cudaErrorInvalidValue;
+}
+
 cudaError_t sc_step(const ScStep& a, cudaStream_t s) {
-    k_sc_step<<<1, 32, 0, s>>>(a);
+    k_sc_step<<<1, STEP_T, 0, s>>>(a);
     return cudaGetLastError();
 }
 
