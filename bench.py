@@ -33,7 +33,7 @@ WORK = {"log_cols": 14, "inv_rate": 2, "q": 280, "rows": 2504, "profile": "hashl
 P = 0xFFFFFFFF00000001
 # dram__bytes_read.sum + dram__bytes_write.sum of one k_encode_fast<14,512> launch at this workload (ncu capture summarised in
 # profiles/k_encode_fast_8b_A.md); the kernel's shape is fixed, so the figure is per launch of the timed kernel
-ENCODE_DRAM_TRAFFIC = 756_425_984 + 1_137_284_000
+ENCODE_DRAM_TRAFFIC = 783_464_960 + 1_224_247_000
 PUBLISHED_GBPS = 26.0  # the reference's Metal backend on an M3 Ultra at this exact shape
 
 

@@ -154,6 +154,24 @@ void hl_b200_store_free(hl_store* store);
 enum { HL_POLY_PROD = 0, HL_POLY_ZC = 1, HL_POLY_LOGUP_Q = 2, HL_POLY_LOGUP_T = 3 };
 int hl_b200_rounds_new(hl_ctx* ctx, int poly, size_t k, uint32_t n_vars, uint32_t degree, const uint64_t* tables,
                        const uint64_t* coefs, size_t ncoefs, hl_rounds** out);
+/* The same evaluator for ANY slot polynomial, given as data: the expression graph of
+ * private_block/slot_ir.rs:57-345 (tables, affine and sum nodes, top-level terms), which the reference turns
+ * into a generated Metal kernel per slot (metal_slot.rs, metal.rs:2627 metal_rounds); here one kernel interprets it.
+ * The value at a cube point is that of the reference's interpreter (slot_ir.rs:352-377).
+ * `words` (32-bit) = the node records in order, then the term records:
+ *     affine node   [0 | count << 8] [konst coef] count x ([coef] [table id])     konst + sum coef_i * table_i
+ *     sum node      [1 | count << 8] count x ([coef] [nf] nf x [factor])          sum coef * prod(factors)
+ *     term          [coef] [nf] nf x [factor]                                     wrapper tables, then inner factors
+ *     factor        table id, or 0x80000000 | node id (a node refers only to earlier nodes)
+ *     coef          index into `coefs` (Fp2 each), or HL_IR_ONE / HL_IR_NEG_ONE / HL_IR_ZERO
+ * Limits: k <= 64 tables, 128 nodes, 4096 words, 512 coefficients, degree <= 7.  A malformed stream is
+ * HL_B200_ERR_ARG and reaches no kernel.  `degree` is the slot's DECLARED degree (the message length). */
+#define HL_IR_NODE 0x80000000u
+#define HL_IR_ONE 0xFFFFFFFFu
+#define HL_IR_NEG_ONE 0xFFFFFFFEu
+#define HL_IR_ZERO 0xFFFFFFFDu
+int hl_b200_rounds_new_ir(hl_ctx* ctx, size_t k, uint32_t n_vars, uint32_t degree, const uint64_t* tables, const uint32_t* words,
+                          size_t n_words, uint32_t n_nodes, uint32_t n_terms, const uint64_t* coefs, size_t ncoefs, hl_rounds** out);
 /* SumcheckRounds::round: sums = degree + 1 Fp2.  eval_one == 0 skips the point 1 (left zero): the caller
  * recovers s(1) = claim - s(0) (rounds.rs:94-99,137-140). */
 int hl_b200_rounds_round(hl_rounds* r, uint32_t j, int eval_one, uint64_t* sums);

@@ -54,6 +54,7 @@ class FsState(C.Structure):
 
 SIGNATURES.update({
     "hl_b200_rounds_new": (_int, [_vp, _int, _sz, _u32, _u32, _vp, _vp, _sz, _pp]),
+    "hl_b200_rounds_new_ir": (_int, [_vp, _sz, _u32, _u32, _vp, _vp, _sz, _u32, _u32, _vp, _sz, _pp]),
     "hl_b200_rounds_round": (_int, [_vp, _u32, _int, _vp]),
     "hl_b200_rounds_fold": (_int, [_vp, _vp]),
     "hl_b200_rounds_finals": (_int, [_vp, _vp]),

@@ -276,21 +276,93 @@ class B200Backend:
 POLY_PROD, POLY_ZC, POLY_LOGUP_Q, POLY_LOGUP_T = 0, 1, 2, 3
 
 
+class SlotProgram:
+    """A slot polynomial as data: the grammar of the reference's slot expression graph (private_block/slot_ir.rs:57-345:
+    `TableRef`, `Node` with `NodeBody::{Affine, Sum}`, `SlotTerm`), flattened into the word stream the C ABI takes
+    (include/hl_b200.h, `hl_b200_rounds_new_ir`).  Build it in the reference's order: nodes first (each refers only to
+    earlier nodes), then the top-level terms.  A coefficient is `ONE`, `NEG_ONE`, `ZERO` or an Fp2 `(c0, c1)`."""
+
+    ONE, NEG_ONE, ZERO = "one", "neg-one", "zero"
+    _SPECIAL = {"one": 0xFFFFFFFF, "neg-one": 0xFFFFFFFE, "zero": 0xFFFFFFFD}
+    NODE_FLAG = 0x80000000
+
+    def __init__(self, n_tables: int):
+        self.n_tables = n_tables
+        self.coefs: List[Tuple[int, int]] = []
+        self._coef_index = {}
+        self._words: List[int] = []
+        self.n_nodes = 0
+        self.n_terms = 0
+
+    @staticmethod
+    def node(node_id: int) -> int:
+        """the factor word of node `node_id` (a table's factor word is its id)"""
+        return SlotProgram.NODE_FLAG | node_id
+
+    def _coef(self, c) -> int:
+        if isinstance(c, str):
+            return self._SPECIAL[c]
+        key = (int(c[0]), int(c[1]))
+        if key not in self._coef_index:
+            self._coef_index[key] = len(self.coefs)
+            self.coefs.append(key)
+        return self._coef_index[key]
+
+    def _product(self, coef, factors) -> None:
+        self._words += [self._coef(coef), len(factors)] + [int(f) for f in factors]
+
+    def affine(self, konst, terms) -> int:
+        """`NodeBody::Affine`: konst + sum coef_i * table_i; `terms` = [(coef, table id)].  Returns the node id."""
+        assert self.n_terms == 0, "nodes come before terms"
+        self._words += [0 | (len(terms) << 8), self._coef(konst)]
+        for c, t in terms:
+            self._words += [self._coef(c), int(t)]
+        self.n_nodes += 1
+        return self.n_nodes - 1
+
+    def sum(self, subterms) -> int:
+        """`NodeBody::Sum`: sum coef * prod(factors); `subterms` = [(coef, [factor words])].  Returns the node id."""
+        assert self.n_terms == 0, "nodes come before terms"
+        self._words.append(1 | (len(subterms) << 8))
+        for c, fs in subterms:
+            self._product(c, fs)
+        self.n_nodes += 1
+        return self.n_nodes - 1
+
+    def term(self, coef, wrapper, inner) -> None:
+        """`SlotTerm`: coef * prod(wrapper tables) * prod(inner factors)"""
+        self._product(coef, list(wrapper) + list(inner))
+        self.n_terms += 1
+
+    def words(self) -> np.ndarray:
+        return np.array(self._words, dtype=np.uint32)
+
+    def coef_array(self) -> np.ndarray:
+        return np.array(self.coefs, dtype=np.uint64).reshape(-1, 2)
+
+
 class B200Rounds:
     """``impl SumcheckRounds`` (sumcheck/rounds.rs:22-28) with the tables resident on the device, plus the
     device-side batch of rounds the reference's Metal evaluator runs (metal.rs:4141 ``masked_prove``)."""
 
-    def __init__(self, ctx: Context, poly: int, tables: np.ndarray, degree: int, coefs=None):
+    def __init__(self, ctx: Context, poly, tables: np.ndarray, degree: int, coefs=None):
+        """`poly`: one of the POLY_* families, or a `SlotProgram` (any slot polynomial, as data)."""
         tables = _u64(tables)
         assert tables.ndim == 3 and tables.shape[2] == 2
         self.ctx, self.k = ctx, tables.shape[0]
         self._n_vars = int(tables.shape[1]).bit_length() - 1
         assert tables.shape[1] == 1 << self._n_vars
         self._degree = degree
-        cf = _u64(coefs).reshape(-1, 2) if coefs is not None else None
         h = C.c_void_p()
-        ctx.check(ctx.lib.hl_b200_rounds_new(ctx.h, poly, self.k, self._n_vars, degree, _ptr(tables), _ptr(cf),
-                                             0 if cf is None else cf.shape[0], C.byref(h)))
+        if isinstance(poly, SlotProgram):
+            assert poly.n_tables == self.k
+            w, cf = poly.words(), poly.coef_array()
+            ctx.check(ctx.lib.hl_b200_rounds_new_ir(ctx.h, self.k, self._n_vars, degree, _ptr(tables), w.ctypes.data_as(C.c_void_p), w.size,
+                                                    poly.n_nodes, poly.n_terms, _ptr(cf) if cf.size else None, cf.shape[0], C.byref(h)))
+        else:
+            cf = _u64(coefs).reshape(-1, 2) if coefs is not None else None
+            ctx.check(ctx.lib.hl_b200_rounds_new(ctx.h, poly, self.k, self._n_vars, degree, _ptr(tables), _ptr(cf),
+                                                 0 if cf is None else cf.shape[0], C.byref(h)))
         self.h = h
 
     def n_vars(self) -> int:

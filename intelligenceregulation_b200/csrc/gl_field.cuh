@@ -202,6 +202,7 @@ GL_HD fp2 f2(u64 a, u64 b) {
 }
 GL_HD fp2 f2_add(fp2 a, fp2 b) { return f2(gl_add(a.c0, b.c0), gl_add(a.c1, b.c1)); }
 GL_HD fp2 f2_sub(fp2 a, fp2 b) { return f2(gl_sub(a.c0, b.c0), gl_sub(a.c1, b.c1)); }
+GL_HD fp2 f2_neg(fp2 a) { return f2(gl_neg(a.c0), gl_neg(a.c1)); }
 GL_HD fp2 f2_mul_base(fp2 a, u64 b) { return f2(gl_mul(a.c0, b), gl_mul(a.c1, b)); }
 // (a0 + a1 u)(b0 + b1 u) with u^2 = 7 (field.rs:163-169)
 GL_HD fp2 f2_mul(fp2 a, fp2 b) {

@@ -20,6 +20,8 @@ struct hl_rounds {
     u64* d_out = nullptr;      // n_vars rows of (2 (degree+1) + 1) Fp2
     u64* d_inv_den = nullptr;
     hlk::ScState* d_state = nullptr;
+    hlk::IrDev ir{};           // poly == POLY_IR: the polynomial as data
+    u32 tail_len = hlk::SC_TAIL_LEN;
     size_t out_row() const { return (2 * ((size_t)degree + 1) + 1) * 2; }
 };
 
@@ -33,6 +35,8 @@ void free_rounds(hl_rounds* r) {
     dev_free(c, r->d_out, (r->n_vars ? r->n_vars : 1) * r->out_row() * 8);
     dev_free(c, r->d_inv_den, ((size_t)r->degree + 1) * 8);
     dev_free(c, r->d_state, sizeof(hlk::ScState));
+    if (r->ir.words) dev_free(c, (void*)r->ir.words, (size_t)r->ir.shape.n_words * 4);
+    if (r->ir.coefs) dev_free(c, (void*)r->ir.coefs, (size_t)(r->ir.shape.n_coefs ? r->ir.shape.n_coefs : 1) * 16);
     delete r;
 }
 
@@ -40,8 +44,10 @@ void free_rounds(hl_rounds* r) {
 int launch_round(hl_rounds* r, int eval_one, int fs, int use_claim, int recover, const u64* d_mask, const u64* d_hs, int mask_vars) {
     hl_ctx* c = r->ctx;
     const u32 half = (u32)(r->len / 2);
-    const u32 nb = hlk::sc_round_blocks(half, c->sm_count);
-    cudaError_t e = hlk::sc_round(r->poly, (int)r->k, r->d_tables, r->stride, half, r->d_coefs, eval_one, r->d_partials, nb, c->stream);
+    const bool is_ir = r->poly == hlk::POLY_IR;
+    const u32 nb = is_ir ? hlk::sc_ir_blocks(half, c->sm_count) : hlk::sc_round_blocks(half, c->sm_count);
+    cudaError_t e = is_ir ? hlk::sc_round_ir(r->ir, (int)r->k, r->d_tables, r->stride, half, (int)r->degree, eval_one, r->d_partials, nb, c->stream)
+                          : hlk::sc_round(r->poly, (int)r->k, r->d_tables, r->stride, half, r->d_coefs, eval_one, r->d_partials, nb, c->stream);
     c->stats.kernel_launches++;
     if (e != cudaSuccess) return fail(c, HL_B200_ERR_DEVICE, "round launch", e);
     hlk::ScStep a;
@@ -68,18 +74,24 @@ int launch_fold(hl_rounds* r) {
 
 extern "C" {
 
-int hl_b200_rounds_new(hl_ctx* c, int poly, size_t k, uint32_t n_vars, uint32_t degree, const uint64_t* tables,
-                       const uint64_t* coefs, size_t ncoefs, hl_rounds** out) {
-    if (!c || !tables || !out) return fail(c, HL_B200_ERR_ARG, "rounds_new: null argument");
-    if (n_vars > 30) return fail(c, HL_B200_ERR_UNSUPPORTED, "rounds_new: more than 30 variables");
-    if (!hlk::sc_supported(poly, (int)k, (int)degree)) return fail(c, HL_B200_ERR_UNSUPPORTED, "rounds_new: polynomial family / table count / degree");
-    if ((poly == hlk::POLY_LOGUP_Q || poly == hlk::POLY_LOGUP_T) && (!coefs || ncoefs < 1)) return fail(c, HL_B200_ERR_ARG, "rounds_new: alpha missing");
+}  // extern "C"
+
+namespace {
+
+// the evaluator of either kind; `words` is the data form of the polynomial when poly == POLY_IR
+int rounds_build(hl_ctx* c, int poly, size_t k, uint32_t n_vars, uint32_t degree, const uint64_t* tables, const uint64_t* coefs,
+                 size_t ncoefs, const uint32_t* words, const ir::Shape* shape, hl_rounds** out) {
     std::lock_guard<std::mutex> g(c->mu);
     cudaSetDevice(c->device);
     hl_rounds* r = new hl_rounds();
     r->ctx = c; r->poly = poly; r->k = (u32)k; r->n_vars = n_vars; r->degree = degree; r->ncoefs = ncoefs;
     r->stride = r->len = (size_t)1 << n_vars;
     r->max_blocks = hlk::sc_round_blocks((u32)(r->len / 2), c->sm_count);
+    if (poly == hlk::POLY_IR) {
+        r->max_blocks = hlk::sc_ir_blocks((u32)(r->len / 2), c->sm_count);
+        r->tail_len = hlk::sc_ir_tail_len(*shape, (int)degree);
+        r->ir.shape = *shape;
+    }
     u64 inv_den[hlk::SC_MAX_POINTS];
     for (u32 i = 0; i <= degree; i++) {
         u64 den = 1;
@@ -96,6 +108,12 @@ int hl_b200_rounds_new(hl_ctx* c, int poly, size_t k, uint32_t n_vars, uint32_t 
     if (!rc) rc = h2d(c, r->d_tables, tables, k * r->stride * 16);
     if (!rc && ncoefs) rc = h2d(c, r->d_coefs, coefs, ncoefs * 16);
     if (!rc) rc = h2d(c, r->d_inv_den, inv_den, ((size_t)degree + 1) * 8);
+    if (!rc && poly == hlk::POLY_IR) {
+        rc = dev_alloc(c, (void**)&r->ir.words, (size_t)shape->n_words * 4);
+        if (!rc) rc = dev_alloc(c, (void**)&r->ir.coefs, (size_t)(shape->n_coefs ? shape->n_coefs : 1) * 16);
+        if (!rc) rc = h2d(c, (void*)r->ir.words, words, (size_t)shape->n_words * 4);
+        if (!rc && shape->n_coefs) rc = h2d(c, (void*)r->ir.coefs, coefs, (size_t)shape->n_coefs * 16);
+    }
     if (!rc) {
         cudaError_t e = cudaMemsetAsync(r->d_state, 0, sizeof(hlk::ScState), c->stream);
         if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "state clear", e);
@@ -104,6 +122,35 @@ int hl_b200_rounds_new(hl_ctx* c, int poly, size_t k, uint32_t n_vars, uint32_t 
     if (rc) { cudaStreamSynchronize(c->stream); free_rounds(r); return rc; }
     *out = r;
     return HL_B200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int hl_b200_rounds_new(hl_ctx* c, int poly, size_t k, uint32_t n_vars, uint32_t degree, const uint64_t* tables,
+                       const uint64_t* coefs, size_t ncoefs, hl_rounds** out) {
+    if (!c || !tables || !out) return fail(c, HL_B200_ERR_ARG, "rounds_new: null argument");
+    if (n_vars > 30) return fail(c, HL_B200_ERR_UNSUPPORTED, "rounds_new: more than 30 variables");
+    if (poly == hlk::POLY_IR) return fail(c, HL_B200_ERR_ARG, "rounds_new: a data-form polynomial goes through rounds_new_ir");
+    if (!hlk::sc_supported(poly, (int)k, (int)degree)) return fail(c, HL_B200_ERR_UNSUPPORTED, "rounds_new: polynomial family / table count / degree");
+    if ((poly == hlk::POLY_LOGUP_Q || poly == hlk::POLY_LOGUP_T) && (!coefs || ncoefs < 1)) return fail(c, HL_B200_ERR_ARG, "rounds_new: alpha missing");
+    return rounds_build(c, poly, k, n_vars, degree, tables, coefs, ncoefs, nullptr, nullptr, out);
+}
+
+int hl_b200_rounds_new_ir(hl_ctx* c, size_t k, uint32_t n_vars, uint32_t degree, const uint64_t* tables, const uint32_t* words,
+                          size_t n_words, uint32_t n_nodes, uint32_t n_terms, const uint64_t* coefs, size_t ncoefs, hl_rounds** out) {
+    if (!c || !tables || !words || !out || (ncoefs && !coefs)) return fail(c, HL_B200_ERR_ARG, "rounds_new_ir: null argument");
+    if (n_vars > 30) return fail(c, HL_B200_ERR_UNSUPPORTED, "rounds_new_ir: more than 30 variables");
+    if (!hlk::sc_supported(hlk::POLY_IR, (int)k, (int)degree) || n_words > ir::MAX_WORDS || n_nodes > ir::MAX_NODES || ncoefs > ir::MAX_COEFS)
+        return fail(c, HL_B200_ERR_UNSUPPORTED, "rounds_new_ir: table count, degree or program size beyond the evaluator's limits");
+    ir::Shape sh{(u32)k, n_nodes, n_terms, (u32)ncoefs, (u32)n_words};
+    if (int why = ir::validate(sh, words)) {
+        char buf[96];
+        snprintf(buf, sizeof buf, "rounds_new_ir: malformed program (check %d)", why);
+        return fail(c, HL_B200_ERR_ARG, buf);
+    }
+    return rounds_build(c, hlk::POLY_IR, k, n_vars, degree, tables, coefs, ncoefs, words, &sh, out);
 }
 
 void hl_b200_rounds_free(hl_rounds* r) {
@@ -204,7 +251,7 @@ int hl_b200_rounds_batched(hl_rounds* r, uint32_t nd, hl_fs_state* fs, const uin
     {
         Timed t(c, HL_T_ROUNDS);
         u32 i = 0;
-        for (; i < nd && !rc && r->len > hlk::SC_TAIL_LEN; i++) {
+        for (; i < nd && !rc && r->len > r->tail_len; i++) {
             rc = launch_round(r, have_claim ? 0 : 1, 1, have_claim ? 1 : 0, fs->recover_one ? 1 : 0, d_mask, d_hs, (int)mask_vars);
             if (!rc) rc = launch_fold(r);
             have_claim = fs->recover_one != 0;
@@ -215,8 +262,10 @@ int hl_b200_rounds_batched(hl_rounds* r, uint32_t nd, hl_fs_state* fs, const uin
             a.use_claim = 0; a.recover = fs->recover_one ? 1 : 0; a.fs = 1; a.mask = d_mask; a.mask_half_suffix = d_hs; a.mask_vars = (int)mask_vars;
             a.inv_den = r->d_inv_den; a.state = r->d_state; a.out = r->d_out;
             const u32 left = nd - i;
-            cudaError_t e = hlk::sc_tail(r->poly, (int)r->k, r->d_tables, r->stride, (u32)r->len, r->d_coefs, a, (int)left, have_claim ? 1 : 0,
-                                         r->d_partials, c->stream);
+            cudaError_t e = r->poly == hlk::POLY_IR
+                                ? hlk::sc_tail_ir(r->ir, (int)r->k, r->d_tables, r->stride, (u32)r->len, (int)r->degree, a, (int)left, have_claim ? 1 : 0, c->stream)
+                                : hlk::sc_tail(r->poly, (int)r->k, r->d_tables, r->stride, (u32)r->len, r->d_coefs, a, (int)left, have_claim ? 1 : 0,
+                                               r->d_partials, c->stream);
             c->stats.kernel_launches++;
             if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "tail rounds launch", e);
             r->len >>= left;

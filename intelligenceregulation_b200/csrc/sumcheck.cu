@@ -343,6 +343,159 @@ __global__ void __launch_bounds__(256) k_sc_fold(u64* __restrict__ tables, size_
     st2(tb + 2 * (size_t)i, f2_add(a, f2_mul(r, f2_sub(b, a))));
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Slot polynomials given as data (slot_ir.cuh): the same round / tail structure with the polynomial
+// interpreted from a word stream held in shared memory.  A work item is one (pair, evaluation point):
+// the table values at point d are T(i) + d (T(i+half) - T(i)), so the points of a pair are independent
+// and a heavy polynomial (60 tables, 70 nodes) still fills the machine in the short rounds.
+// The per-thread table and node values live in local memory (L1 / L2 resident).
+// ---------------------------------------------------------------------------------------------
+constexpr int IRT = 128;
+
+__device__ __forceinline__ void ir_stage(const hlk::IrDev& p, u32* w_s, fp2*& cf_s, int nthreads) {
+    for (u32 x = threadIdx.x; x < p.shape.n_words; x += nthreads) w_s[x] = p.words[x];
+    cf_s = reinterpret_cast<fp2*>(w_s + ((p.shape.n_words + 3u) & ~3u));
+    for (u32 x = threadIdx.x; x < p.shape.n_coefs; x += nthreads) cf_s[x] = ld2(p.coefs + 2 * (size_t)x);
+}
+
+// the polynomial at point d of pair i
+__device__ __forceinline__ fp2 ir_point(const ir::Shape& sh, const u32* w_s, const fp2* cf_s, const u64* __restrict__ tables, size_t stride,
+                                        u32 i, u32 half, u32 d, fp2* tv, fp2* nv) {
+    for (u32 t = 0; t < sh.n_tables; t++) {
+        const u64* tb = tables + 2 * (size_t)t * stride;
+        if (d == 0) {
+            tv[t] = ld2(tb + 2 * (size_t)i);
+        } else if (d == 1) {
+            tv[t] = ld2(tb + 2 * ((size_t)i + half));
+        } else {
+            const fp2 lo = ld2(tb + 2 * (size_t)i), hi = ld2(tb + 2 * ((size_t)i + half));
+            tv[t] = f2_add(lo, f2_mul_base(f2_sub(hi, lo), (u64)d));
+        }
+    }
+    return ir::eval(sh, w_s, cf_s, tv, nv);
+}
+
+// grid (blocks, degree + 1): row y evaluates point y; partials[block][point] as in k_sc_round
+__global__ void __launch_bounds__(IRT) k_sc_round_ir(const u64* __restrict__ tables, size_t stride, u32 half, hlk::IrDev p, int degree,
+                                                     int eval_one, u64* __restrict__ partials) {
+    extern __shared__ __align__(16) u32 ir_smem[];
+    __shared__ u64 wsum[IRT / 32][2];
+    fp2* cf_s;
+    const u32 d = blockIdx.y;
+    u64* dst = partials + ((size_t)blockIdx.x * (degree + 1) + d) * 2;
+    if (d == 1 && !eval_one) {  // s(1) comes from the running claim
+        if (threadIdx.x < 2) dst[threadIdx.x] = 0;
+        return;
+    }
+    ir_stage(p, ir_smem, cf_s, IRT);
+    __syncthreads();
+    fp2 tv[ir::MAX_TABLES], nv[ir::MAX_NODES];
+    fp2 acc = f2(0, 0);
+    for (u32 i = blockIdx.x * IRT + threadIdx.x; i < half; i += gridDim.x * IRT)
+        acc = f2_add(acc, ir_point(p.shape, ir_smem, cf_s, tables, stride, i, half, d, tv, nv));
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+        acc.c0 = gl_add(acc.c0, shfl_down64(acc.c0, off));
+        acc.c1 = gl_add(acc.c1, shfl_down64(acc.c1, off));
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { wsum[warp][0] = acc.c0; wsum[warp][1] = acc.c1; }
+    __syncthreads();
+    if (threadIdx.x < 2) {
+        u64 s = 0;
+#pragma unroll
+        for (int w = 0; w < IRT / 32; w++) s = gl_add(s, wsum[w][threadIdx.x]);
+        dst[threadIdx.x] = s;
+    }
+}
+
+constexpr int IR_TAIL_T = 1024;
+__global__ void __launch_bounds__(IR_TAIL_T) k_sc_tail_ir(u64* __restrict__ tables, size_t stride, u32 len, hlk::IrDev p, int degree, int k,
+                                                          ScStep a, int nrounds, int first_has_claim) {
+    extern __shared__ __align__(16) u32 ir_smem[];
+    __shared__ StepSmem sm;
+    __shared__ u64 wsum[IR_TAIL_T / 32][2 * hlk::SC_MAX_POINTS];
+    __shared__ hlk::ScState st_s;
+    __shared__ u64 mask_s[2 * (63 * (hlk::SC_MAX_POINTS - 1) + 2)];
+    __shared__ u64 hs_s[2 * 63];
+    __shared__ u64 invden_s[hlk::SC_MAX_POINTS];
+    fp2* cf_s;
+    ir_stage(p, ir_smem, cf_s, IR_TAIL_T);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, np = degree + 1;
+    {
+        const u32* src = reinterpret_cast<const u32*>(a.state);
+        u32* dst = reinterpret_cast<u32*>(&st_s);
+        for (u32 i = threadIdx.x; i < sizeof(hlk::ScState) / 4; i += IR_TAIL_T) dst[i] = src[i];
+        if (a.mask) {
+            for (u32 i = threadIdx.x; i < 2u * (a.mask_vars * degree + 2); i += IR_TAIL_T) mask_s[i] = a.mask[i];
+            for (u32 i = threadIdx.x; i < 2u * a.mask_vars; i += IR_TAIL_T) hs_s[i] = a.mask_half_suffix[i];
+        }
+        if ((int)threadIdx.x < np) invden_s[threadIdx.x] = a.inv_den[threadIdx.x];
+    }
+    hlk::ScState* const st_global = a.state;
+    if (a.mask) { a.mask = mask_s; a.mask_half_suffix = hs_s; }
+    a.inv_den = invden_s;
+    a.state = &st_s;
+    __syncthreads();
+    fp2 tv[ir::MAX_TABLES], nv[ir::MAX_NODES];
+    for (int rd = 0; rd < nrounds; rd++) {
+        const u32 half = len >> 1;  // a power of two
+        const bool have_claim = a.recover && (rd > 0 || first_has_claim);
+        fp2 acc[hlk::SC_MAX_POINTS];
+#pragma unroll
+        for (int d = 0; d < hlk::SC_MAX_POINTS; d++) acc[d] = f2(0, 0);
+        for (u32 x = threadIdx.x; x < half * (u32)np; x += IR_TAIL_T) {
+            const u32 d = x / half, i = x - d * half;
+            if (d == 1 && have_claim) continue;
+            const fp2 v = ir_point(p.shape, ir_smem, cf_s, tables, stride, i, half, d, tv, nv);
+#pragma unroll
+            for (int dd = 0; dd < hlk::SC_MAX_POINTS; dd++)
+                if ((u32)dd == d) acc[dd] = f2_add(acc[dd], v);
+        }
+        for (int d = 0; d < np; d++) {
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) {
+                acc[d].c0 = gl_add(acc[d].c0, shfl_down64(acc[d].c0, off));
+                acc[d].c1 = gl_add(acc[d].c1, shfl_down64(acc[d].c1, off));
+            }
+        }
+        if (lane == 0) {
+            for (int d = 0; d < np; d++) { wsum[warp][2 * d] = acc[d].c0; wsum[warp][2 * d + 1] = acc[d].c1; }
+        }
+        __syncthreads();
+        if ((int)threadIdx.x < 2 * np) {
+            u64 s = 0;
+#pragma unroll
+            for (int w = 0; w < IR_TAIL_T / 32; w++) s = gl_add(s, wsum[w][threadIdx.x]);
+            sm.sums[threadIdx.x] = s;
+        }
+        __syncthreads();
+        if (warp == 0) {
+            ScStep b = a;
+            b.round = a.round + rd; b.use_claim = have_claim ? 1 : 0; b.fs = 1;
+            step_body(b, sm, lane);
+        }
+        __syncthreads();
+        const fp2 r = a.state->r;
+        for (u32 x = threadIdx.x; x < half * (u32)k; x += IR_TAIL_T) {
+            const u32 t = x / half, i = x - t * half;
+            u64* tb = tables + 2 * (size_t)t * stride;
+            fp2 lo = ld2(tb + 2 * (size_t)i), hi = ld2(tb + 2 * ((size_t)i + half));
+            st2(tb + 2 * (size_t)i, f2_add(lo, f2_mul(r, f2_sub(hi, lo))));
+        }
+        __syncthreads();
+        len = half;
+    }
+    {
+        const u32* src = reinterpret_cast<const u32*>(&st_s);
+        u32* dst = reinterpret_cast<u32*>(st_global);
+        for (u32 i = threadIdx.x; i < sizeof(hlk::ScState) / 4; i += IR_TAIL_T) dst[i] = src[i];
+    }
+}
+
+size_t ir_smem_bytes(const ir::Shape& s) { return (((size_t)s.n_words + 3) & ~(size_t)3) * 4 + (size_t)s.n_coefs * 16 + 16; }
+
 template <int POLY, int K, int D>
 cudaError_t launch_round(const u64* tables, size_t stride, u32 half, const u64* coefs, int eval_one, u64* partials, u32 nblocks, cudaStream_t s) {
     k_sc_round<POLY, K, D><<<nblocks, RT, 0, s>>>(tables, stride, half, coefs, eval_one, partials);
@@ -359,7 +512,35 @@ u32 sc_round_blocks(u32 half, int sm_count) {
     return b > cap ? cap : b;
 }
 
+u32 sc_ir_blocks(u32 half, int sm_count) {
+    u32 b = (half + IRT - 1) / IRT, cap = (u32)sm_count * 2;
+    if (b < 1) b = 1;
+    return b > cap ? cap : b;
+}
+
+// The single-CTA tail pays off only while a round's work is below the cost of three launches; a heavy
+// program leaves the multi-CTA rounds later than a light one.
+u32 sc_ir_tail_len(const ir::Shape& s, int degree) {
+    const u32 work = s.n_words * (u32)(degree + 1);
+    return work <= 256 ? 4096u : work <= 1024 ? 1024u : 256u;
+}
+
+cudaError_t sc_round_ir(const IrDev& p, int k, const u64* tables, size_t stride, u32 half, int degree, int eval_one, u64* partials,
+                        u32 nblocks, cudaStream_t s) {
+    (void)k;
+    dim3 grid(nblocks, (unsigned)degree + 1);
+    k_sc_round_ir<<<grid, IRT, ir_smem_bytes(p.shape), s>>>(tables, stride, half, p, degree, eval_one, partials);
+    return cudaGetLastError();
+}
+
+cudaError_t sc_tail_ir(const IrDev& p, int k, u64* tables, size_t stride, u32 len, int degree, const ScStep& a, int nrounds,
+                       int first_has_claim, cudaStream_t s) {
+    k_sc_tail_ir<<<1, IR_TAIL_T, ir_smem_bytes(p.shape), s>>>(tables, stride, len, p, degree, k, a, nrounds, first_has_claim);
+    return cudaGetLastError();
+}
+
 bool sc_supported(int poly, int k, int degree) {
+    if (poly == POLY_IR) return k >= 1 && k <= (int)ir::MAX_TABLES && degree >= 1 && degree < SC_MAX_POINTS;
     if (poly == POLY_PROD) return k >= 1 && k <= 6 && degree == k;
     if (poly == POLY_ZC || poly == POLY_LOGUP_T) return k == 4 && degree == 3;
     if (poly == POLY_LOGUP_Q) return k == 3 && degree == 3;

@@ -2,10 +2,11 @@
 #pragma once
 #include <cuda_runtime.h>
 #include "gl_field.cuh"
+#include "slot_ir.cuh"
 
 namespace hlk {
 
-enum { POLY_PROD = 0, POLY_ZC = 1, POLY_LOGUP_Q = 2, POLY_LOGUP_T = 3 };
+enum { POLY_PROD = 0, POLY_ZC = 1, POLY_LOGUP_Q = 2, POLY_LOGUP_T = 3, POLY_IR = 4 };
 constexpr int SC_MAX_POINTS = 8;  // degree <= 7
 
 // Device-resident state of one evaluator: the transcript (state, counter, key), the running
@@ -38,7 +39,21 @@ struct ScStep {
     u64* out;                   // per round: (degree+1) sums, (degree+1) masked, r  (Fp2 each)
 };
 
+// a slot polynomial given as data (slot_ir.cuh), resident on the device
+struct IrDev {
+    const u32* words;
+    const u64* coefs;  // n_coefs Fp2
+    ir::Shape shape;
+};
+
 u32 sc_round_blocks(u32 half, int sm_count);
+// the data-driven evaluator: one CTA row per evaluation point, `sc_ir_blocks` CTAs per row
+u32 sc_ir_blocks(u32 half, int sm_count);
+u32 sc_ir_tail_len(const ir::Shape& s, int degree);
+cudaError_t sc_round_ir(const IrDev& p, int k, const u64* tables, size_t stride, u32 half, int degree, int eval_one, u64* partials,
+                        u32 nblocks, cudaStream_t s);
+cudaError_t sc_tail_ir(const IrDev& p, int k, u64* tables, size_t stride, u32 len, int degree, const ScStep& a, int nrounds,
+                       int first_has_claim, cudaStream_t s);
 bool sc_supported(int poly, int k, int degree);
 cudaError_t sc_round(int poly, int k, const u64* tables, size_t stride, u32 half, const u64* coefs, int eval_one, u64* partials,
                      u32 nblocks, cudaStream_t s);

@@ -82,7 +82,9 @@ void or_fold_rows_i8(const int8_t *m, size_t rows, size_t cols, const uint64_t *
 void or_fold_cols_i8(const int8_t *m, size_t rows, size_t cols, const uint64_t *c, uint64_t *out);
 /* poly ids: 0 = product of all k tables; 1 = t0 * (t1 * t2 - t3);
  * 2 = LogUp query zero-check  t0 * (t1 * (alpha - t2) - 1)        (coefs = alpha)
- * 3 = LogUp table zero-check  t0 * (t1 * (alpha - t2) - t3)       (coefs = alpha) */
+ * 3 = LogUp table zero-check  t0 * (t1 * (alpha - t2) - t3)       (coefs = alpha)
+ * 4 = the slot polynomial last given to or_ir_set (private_block/slot_ir.rs:352-377), coefs = its Fp2 coefficients */
+void or_ir_set(const uint32_t *words, size_t n_nodes, size_t n_terms);
 void or_poly_eval(int poly, const uint64_t *vals /* k x 2 */, size_t k, const uint64_t *coefs, uint64_t out[2]);
 void or_sc_round(int poly, const uint64_t *tables, size_t k, size_t len, size_t degree, const uint64_t *coefs,
                  int eval_one, uint64_t *sums);

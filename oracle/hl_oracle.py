@@ -408,7 +408,18 @@ def fold_cols_i8(m: np.ndarray, c: np.ndarray) -> np.ndarray:
     return out
 
 
-POLY_PROD, POLY_ZC, POLY_LOGUP_Q, POLY_LOGUP_T = 0, 1, 2, 3
+POLY_PROD, POLY_ZC, POLY_LOGUP_Q, POLY_LOGUP_T, POLY_IR = 0, 1, 2, 3, 4
+
+_ir_keep = None
+
+
+def ir_set(words: np.ndarray, n_nodes: int, n_terms: int) -> None:
+    """Select the slot polynomial that poly id POLY_IR evaluates (private_block/slot_ir.rs:352-377); `words` is the
+    32-bit stream documented in include/hl_b200.h."""
+    global _ir_keep
+    _ir_keep = np.ascontiguousarray(words, dtype=np.uint32)
+    _lib.or_ir_set(_ir_keep.ctypes.data_as(C.c_void_p), C.c_size_t(n_nodes), C.c_size_t(n_terms))
+
 
 
 def poly_eval(poly: int, vals, coefs=None) -> Tuple[int, int]:

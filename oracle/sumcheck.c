@@ -85,8 +85,53 @@ void or_fold_cols_i8(const int8_t *m, size_t rows, size_t cols, const uint64_t *
     }
 }
 
+/* ---- poly id 4: a slot polynomial given as data ------------------------------------------------
+ * The interpreter of private_block/slot_ir.rs:352-377 (`SlotIr::eval`): nodes in order, an affine node
+ * folds konst + sum coef * table (:356), a sum node folds coef * prod(factors) per subterm (:357-360),
+ * the value is the sum over terms of coef * prod(wrapper) * prod(inner) (:365-375).  The graph arrives
+ * as the 32-bit word stream documented in include/hl_b200.h; or_ir_set keeps the caller's pointer. */
+static struct { const uint32_t *w; size_t n_nodes, n_terms; } g_ir;
+void or_ir_set(const uint32_t *words, size_t n_nodes, size_t n_terms) {
+    g_ir.w = words; g_ir.n_nodes = n_nodes; g_ir.n_terms = n_terms;
+}
+static fp2_t ir_coef(uint32_t ci, const fp2_t *coefs) {
+    if (ci == 0xFFFFFFFFu) return FP2_ONE;
+    if (ci == 0xFFFFFFFEu) return fp2_sub(FP2_ZERO, FP2_ONE);
+    if (ci == 0xFFFFFFFDu) return FP2_ZERO;
+    return coefs[ci];
+}
+static fp2_t ir_product(const uint32_t **pw, const fp2_t *coefs, const fp2_t *v, const fp2_t *nv) {
+    const uint32_t *w = *pw;
+    fp2_t p = ir_coef(w[0], coefs);
+    uint32_t nf = w[1];
+    w += 2;
+    for (uint32_t i = 0; i < nf; i++, w++) p = fp2_mul(p, (*w & 0x80000000u) ? nv[*w & 0x7FFFFFFFu] : v[*w]);
+    *pw = w;
+    return p;
+}
+static fp2_t ir_eval(const fp2_t *v, const fp2_t *coefs) {
+    fp2_t nv[128];
+    const uint32_t *w = g_ir.w;
+    for (size_t n = 0; n < g_ir.n_nodes; n++) {
+        uint32_t head = *w++, cnt = head >> 8;
+        fp2_t a;
+        if ((head & 0xFF) == 0) {
+            a = ir_coef(*w++, coefs);
+            for (uint32_t i = 0; i < cnt; i++, w += 2) a = fp2_add(a, fp2_mul(ir_coef(w[0], coefs), v[w[1]]));
+        } else {
+            a = FP2_ZERO;
+            for (uint32_t i = 0; i < cnt; i++) a = fp2_add(a, ir_product(&w, coefs, v, nv));
+        }
+        nv[n] = a;
+    }
+    fp2_t total = FP2_ZERO;
+    for (size_t t = 0; t < g_ir.n_terms; t++) total = fp2_add(total, ir_product(&w, coefs, v, nv));
+    return total;
+}
+
 static fp2_t poly_eval(int poly, const fp2_t *v, size_t k, const fp2_t *coefs) {
     switch (poly) {
+    case 4: return ir_eval(v, coefs);
     case 0: { /* the "prod" family of the L6 corpus; slot matmuls v0*v1 (argument.rs:2174-2203) */
         fp2_t a = FP2_ONE;
         for (size_t t = 0; t < k; t++) a = fp2_mul(a, v[t]);

@@ -145,8 +145,16 @@ def test_two_rank_gloo_run_joins_to_the_one_process_state(tmp_path):
     script = tmp_path / "worker.py"
     script.write_text(WORKER)
     env = dict(os.environ, HL_ROOT=ROOT, OMP_NUM_THREADS="1")
-    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-                          "--master-port", "29517", str(script)], env=env, capture_output=True, text=True, timeout=300)
+    import socket
+
+    for attempt in range(2):  # a free port can still be taken between the probe and the rendezvous: one retry
+        with socket.socket() as sk:
+            sk.bind(("127.0.0.1", 0))
+            port = sk.getsockname()[1]
+        out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+                              "--master-port", str(port), str(script)], env=env, capture_output=True, text=True, timeout=300)
+        if out.returncode == 0:
+            break
     assert out.returncode == 0, out.stderr[-2000:]
     lines = [l.split() for l in out.stdout.splitlines() if l.startswith("S1")]
     assert len(lines) == 2
