@@ -205,6 +205,39 @@ def device_extras(dev, backend, np_data, np_pads, np_pows, col_key) -> dict:
         ctx.fold_cols_i8(wm, cw)
     t = ctx.timing_read(reset=True)
     out["fold_cols_i8_4096x14336_ms"] = t["fold"][0] / 2
+    # the heaviest slot polynomial of a block as data: the recorded structure of the D zero-check (60 tables, 71 nodes,
+    # declared degree 5) with seeded coefficients, at 2^17 points, through the interpreting evaluator
+    import json as _json
+
+    slot = _json.load(open(os.path.join(ROOT, "tests", "golden", "slot_ir_m125.json")))["slots"][14]
+    SP = backend.SlotProgram
+    prog, cs = SP(len(slot["table_fields"])), iter(splitmix_fp(86, 4096).tolist())
+
+    def coef(cls):
+        return "one" if cls == "one" else (next(cs) % (1 << 40), 0) if cls == "kbase" else (next(cs), next(cs))
+
+    def fw(f):
+        return SP.node(f["n"]) if "n" in f else f["t"]
+
+    for nd in slot["nodes"]:
+        if "affine" in nd:
+            prog.affine(coef("kbase") if nd["konst"] else "zero", [(coef(c), t) for c, t in nd["affine"]])
+        else:
+            prog.sum([(coef(c), [fw(f) for f in fs]) for c, fs in nd["sum"]])
+    for t in slot["terms"]:
+        prog.term(coef(t["coef"]), t["wrapper"], [fw(f) for f in t["inner"]])
+    n = 17
+    tables = splitmix_fp(87, prog.n_tables * (1 << n) * 2).reshape(prog.n_tables, 1 << n, 2)
+    deg = slot["declared_degree"]
+    mask = splitmix_fp(88, ((n + 1) * deg + 2) * 2).reshape(-1, 2)
+    for rep in range(3):
+        ev = backend.B200Rounds(ctx, prog, tables, deg)
+        if rep == 1:
+            ctx.timing_read(reset=True)
+        ev.batched(n, bytes(32), 0, None, mask=mask, mask_vars=n + 1, mask_c=(3, 5), recover_one=True, claim=(0, 0))
+        ev.free()
+    t = ctx.timing_read(reset=True)
+    out["sumcheck_slot_program_60tables_71nodes_deg5_2^17_ms"] = t["rounds"][0] / 2
     ctx.timing_enable(False)
     return out
 

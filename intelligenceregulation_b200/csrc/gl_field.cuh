@@ -55,13 +55,41 @@ GL_HD u64 gl_reduce128(u64 lo, u64 hi) {
     return gl_canon(r);
 }
 
-GL_HD u64 gl_mul(u64 a, u64 b) {
+// the 128-bit product as (lo, hi); on the device four 32x32 multiply-adds into 64-bit accumulators
+struct gl_wide {
+    u64 lo, hi;
+};
+GL_HD gl_wide gl_mulw(u64 a, u64 b) {
+    gl_wide r;
 #ifdef __CUDA_ARCH__
-    return gl_reduce128(a * b, __umul64hi(a, b));
+    const u32 a0 = (u32)a, a1 = (u32)(a >> 32), b0 = (u32)b, b1 = (u32)(b >> 32);
+    const u64 x = (u64)a0 * b0;
+    const u64 y = (u64)a0 * b1 + (x >> 32);
+    const u64 z = (u64)a1 * b0 + (u32)y;
+    const u64 w = (u64)a1 * b1 + (y >> 32) + (z >> 32);
+    r.lo = (z << 32) | (u32)x;
+    r.hi = w;
 #else
     unsigned __int128 x = (unsigned __int128)a * b;
-    return gl_reduce128((u64)x, (u64)(x >> 64));
+    r.lo = (u64)x;
+    r.hi = (u64)(x >> 64);
 #endif
+    return r;
+}
+
+GL_HD u64 gl_mul(u64 a, u64 b) {
+    const gl_wide w = gl_mulw(a, b);
+    return gl_reduce128(w.lo, w.hi);
+}
+
+// a b + c d with ONE reduction: the 129-bit sum's top bit weighs 2^128 = -2^32 (mod p)
+GL_HD u64 gl_mul_add2(u64 a, u64 b, u64 c, u64 d) {
+    const gl_wide p = gl_mulw(a, b), q = gl_mulw(c, d);
+    const u64 lo = p.lo + q.lo, cy = lo < p.lo ? 1u : 0u;
+    const u64 h0 = p.hi + q.hi, c2 = h0 < p.hi ? 1u : 0u;
+    const u64 hi = h0 + cy, c3 = hi < h0 ? 1u : 0u;
+    const u64 r = gl_reduce128(lo, hi);
+    return (c2 | c3) ? gl_sub(r, 1ull << 32) : r;
 }
 
 // ---- lazy forms for butterfly chains -------------------------------------------------------------
@@ -206,10 +234,8 @@ GL_HD fp2 f2_neg(fp2 a) { return f2(gl_neg(a.c0), gl_neg(a.c1)); }
 GL_HD fp2 f2_mul_base(fp2 a, u64 b) { return f2(gl_mul(a.c0, b), gl_mul(a.c1, b)); }
 // (a0 + a1 u)(b0 + b1 u) with u^2 = 7 (field.rs:163-169)
 GL_HD fp2 f2_mul(fp2 a, fp2 b) {
-    u64 ac = gl_mul(a.c0, b.c0), bd = gl_mul(a.c1, b.c1);
-    u64 ad = gl_mul(a.c0, b.c1), bc = gl_mul(a.c1, b.c0);
-    u64 bd7 = gl_sub(gl_reduce128(bd << 3, bd >> 61), bd);  // 7 bd = 8 bd - bd
-    return f2(gl_add(ac, bd7), gl_add(ad, bc));
+    const u64 a17 = gl_sub(gl_reduce128(a.c1 << 3, a.c1 >> 61), a.c1);  // 7 a1 = 8 a1 - a1
+    return f2(gl_mul_add2(a.c0, b.c0, a17, b.c1), gl_mul_add2(a.c0, b.c1, a.c1, b.c0));
 }
 GL_HD bool f2_is_zero(fp2 a) { return (a.c0 | a.c1) == 0; }
 // conj(a) / (a0^2 - 7 a1^2) (field.rs:180-185)

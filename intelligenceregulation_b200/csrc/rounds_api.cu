@@ -35,8 +35,8 @@ void free_rounds(hl_rounds* r) {
     dev_free(c, r->d_out, (r->n_vars ? r->n_vars : 1) * r->out_row() * 8);
     dev_free(c, r->d_inv_den, ((size_t)r->degree + 1) * 8);
     dev_free(c, r->d_state, sizeof(hlk::ScState));
-    if (r->ir.words) dev_free(c, (void*)r->ir.words, (size_t)r->ir.shape.n_words * 4);
-    if (r->ir.coefs) dev_free(c, (void*)r->ir.coefs, (size_t)(r->ir.shape.n_coefs ? r->ir.shape.n_coefs : 1) * 16);
+    if (r->ir.plan) dev_free(c, (void*)r->ir.plan, (size_t)r->ir.plan_words * 4);
+    if (r->ir.coefs) dev_free(c, (void*)r->ir.coefs, (size_t)(r->ir.n_coefs ? r->ir.n_coefs : 1) * 16);
     delete r;
 }
 
@@ -45,7 +45,7 @@ int launch_round(hl_rounds* r, int eval_one, int fs, int use_claim, int recover,
     hl_ctx* c = r->ctx;
     const u32 half = (u32)(r->len / 2);
     const bool is_ir = r->poly == hlk::POLY_IR;
-    const u32 nb = is_ir ? hlk::sc_ir_blocks(half, c->sm_count) : hlk::sc_round_blocks(half, c->sm_count);
+    const u32 nb = is_ir ? hlk::sc_ir_blocks(r->ir, half, (int)r->degree, c->sm_count) : hlk::sc_round_blocks(half, c->sm_count);
     cudaError_t e = is_ir ? hlk::sc_round_ir(r->ir, (int)r->k, r->d_tables, r->stride, half, (int)r->degree, eval_one, r->d_partials, nb, c->stream)
                           : hlk::sc_round(r->poly, (int)r->k, r->d_tables, r->stride, half, r->d_coefs, eval_one, r->d_partials, nb, c->stream);
     c->stats.kernel_launches++;
@@ -80,7 +80,7 @@ namespace {
 
 // the evaluator of either kind; `words` is the data form of the polynomial when poly == POLY_IR
 int rounds_build(hl_ctx* c, int poly, size_t k, uint32_t n_vars, uint32_t degree, const uint64_t* tables, const uint64_t* coefs,
-                 size_t ncoefs, const uint32_t* words, const ir::Shape* shape, hl_rounds** out) {
+                 size_t ncoefs, const std::vector<u32>* plan, hl_rounds** out) {
     std::lock_guard<std::mutex> g(c->mu);
     cudaSetDevice(c->device);
     hl_rounds* r = new hl_rounds();
@@ -88,9 +88,16 @@ int rounds_build(hl_ctx* c, int poly, size_t k, uint32_t n_vars, uint32_t degree
     r->stride = r->len = (size_t)1 << n_vars;
     r->max_blocks = hlk::sc_round_blocks((u32)(r->len / 2), c->sm_count);
     if (poly == hlk::POLY_IR) {
-        r->max_blocks = hlk::sc_ir_blocks((u32)(r->len / 2), c->sm_count);
-        r->tail_len = hlk::sc_ir_tail_len(*shape, (int)degree);
-        r->ir.shape = *shape;
+        const std::vector<u32>& pw = *plan;
+        r->ir.plan_words = (u32)pw.size(); r->ir.n_coefs = (u32)ncoefs; r->ir.n_tables = (u32)k;
+        r->ir.n_nodes = pw[1]; r->ir.n_units = pw[2];
+        const u32 *lvl = pw.data() + pw[3], *nus = pw.data() + pw[5];
+        for (u32 l = 0; l < pw[0]; l++) {
+            const u32 nu = nus[lvl[l + 1]] - nus[lvl[l]];
+            if (nu > r->ir.max_level_units) r->ir.max_level_units = nu;
+        }
+        r->max_blocks = hlk::sc_ir_max_blocks((u32)(r->len / 2), c->sm_count);
+        r->tail_len = hlk::sc_ir_tail_len(r->ir, (int)degree);
     }
     u64 inv_den[hlk::SC_MAX_POINTS];
     for (u32 i = 0; i <= degree; i++) {
@@ -109,10 +116,10 @@ int rounds_build(hl_ctx* c, int poly, size_t k, uint32_t n_vars, uint32_t degree
     if (!rc && ncoefs) rc = h2d(c, r->d_coefs, coefs, ncoefs * 16);
     if (!rc) rc = h2d(c, r->d_inv_den, inv_den, ((size_t)degree + 1) * 8);
     if (!rc && poly == hlk::POLY_IR) {
-        rc = dev_alloc(c, (void**)&r->ir.words, (size_t)shape->n_words * 4);
-        if (!rc) rc = dev_alloc(c, (void**)&r->ir.coefs, (size_t)(shape->n_coefs ? shape->n_coefs : 1) * 16);
-        if (!rc) rc = h2d(c, (void*)r->ir.words, words, (size_t)shape->n_words * 4);
-        if (!rc && shape->n_coefs) rc = h2d(c, (void*)r->ir.coefs, coefs, (size_t)shape->n_coefs * 16);
+        rc = dev_alloc(c, (void**)&r->ir.plan, (size_t)r->ir.plan_words * 4);
+        if (!rc) rc = dev_alloc(c, (void**)&r->ir.coefs, (size_t)(ncoefs ? ncoefs : 1) * 16);
+        if (!rc) rc = h2d(c, (void*)r->ir.plan, plan->data(), (size_t)r->ir.plan_words * 4);
+        if (!rc && ncoefs) rc = h2d(c, (void*)r->ir.coefs, coefs, ncoefs * 16);
     }
     if (!rc) {
         cudaError_t e = cudaMemsetAsync(r->d_state, 0, sizeof(hlk::ScState), c->stream);
@@ -135,7 +142,7 @@ int hl_b200_rounds_new(hl_ctx* c, int poly, size_t k, uint32_t n_vars, uint32_t 
     if (poly == hlk::POLY_IR) return fail(c, HL_B200_ERR_ARG, "rounds_new: a data-form polynomial goes through rounds_new_ir");
     if (!hlk::sc_supported(poly, (int)k, (int)degree)) return fail(c, HL_B200_ERR_UNSUPPORTED, "rounds_new: polynomial family / table count / degree");
     if ((poly == hlk::POLY_LOGUP_Q || poly == hlk::POLY_LOGUP_T) && (!coefs || ncoefs < 1)) return fail(c, HL_B200_ERR_ARG, "rounds_new: alpha missing");
-    return rounds_build(c, poly, k, n_vars, degree, tables, coefs, ncoefs, nullptr, nullptr, out);
+    return rounds_build(c, poly, k, n_vars, degree, tables, coefs, ncoefs, nullptr, out);
 }
 
 int hl_b200_rounds_new_ir(hl_ctx* c, size_t k, uint32_t n_vars, uint32_t degree, const uint64_t* tables, const uint32_t* words,
@@ -150,7 +157,13 @@ int hl_b200_rounds_new_ir(hl_ctx* c, size_t k, uint32_t n_vars, uint32_t degree,
         snprintf(buf, sizeof buf, "rounds_new_ir: malformed program (check %d)", why);
         return fail(c, HL_B200_ERR_ARG, buf);
     }
-    return rounds_build(c, hlk::POLY_IR, k, n_vars, degree, tables, coefs, ncoefs, words, &sh, out);
+    std::vector<u32> plan;
+    if (int why = ir::build_plan(sh, words, plan)) {
+        char buf[96];
+        snprintf(buf, sizeof buf, "rounds_new_ir: the program does not fit the evaluator's plan (reason %d)", why);
+        return fail(c, HL_B200_ERR_UNSUPPORTED, buf);
+    }
+    return rounds_build(c, hlk::POLY_IR, k, n_vars, degree, tables, coefs, ncoefs, &plan, out);
 }
 
 void hl_b200_rounds_free(hl_rounds* r) {

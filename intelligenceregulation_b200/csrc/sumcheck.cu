@@ -346,34 +346,31 @@ __global__ void __launch_bounds__(256) k_sc_fold(u64* __restrict__ tables, size_
 
 // ---------------------------------------------------------------------------------------------
 // Slot polynomials given as data (slot_ir.cuh): the same round / tail structure with the polynomial
-// interpreted from a word stream held in shared memory.  A work item is one (pair, evaluation point):
-// the table values at point d are T(i) + d (T(i+half) - T(i)), so the points of a pair are independent
-// and a heavy polynomial (60 tables, 70 nodes) still fills the machine in the short rounds.
-// The per-thread table and node values live in local memory (L1 / L2 resident).
+// interpreted from its evaluation plan, held in shared memory.  A work item is one (pair, evaluation
+// point): the table values at point d are T(i) + d (T(i+half) - T(i)), so the points of a pair are
+// independent.  Two forms:
+//   thread form  one item per thread, table and node values in local memory: the long rounds of a light
+//                polynomial (coalesced table reads, no idle lanes);
+//   warp form    one item per warp: the lanes share the table loads, take one unit of a level each and
+//                then one node each, values in shared memory.  A 60-table, 70-node polynomial costs one
+//                thread ~120 us per item; a warp gets through it in a few microseconds, which is what the
+//                short rounds (few items, every one on the critical path) need.
 // ---------------------------------------------------------------------------------------------
-constexpr int IRT = 128;
+constexpr int IRT = 128;                 // thread form
+constexpr int IRW_WARPS = 8;             // warp form, round kernel
+constexpr int IR_TAIL_WARPS = 16;        // warp form, single-CTA tail
 
 __device__ __forceinline__ void ir_stage(const hlk::IrDev& p, u32* w_s, fp2*& cf_s, int nthreads) {
-    for (u32 x = threadIdx.x; x < p.shape.n_words; x += nthreads) w_s[x] = p.words[x];
-    cf_s = reinterpret_cast<fp2*>(w_s + ((p.shape.n_words + 3u) & ~3u));
-    for (u32 x = threadIdx.x; x < p.shape.n_coefs; x += nthreads) cf_s[x] = ld2(p.coefs + 2 * (size_t)x);
+    for (u32 x = threadIdx.x; x < p.plan_words; x += nthreads) w_s[x] = p.plan[x];
+    cf_s = reinterpret_cast<fp2*>(w_s + ((p.plan_words + 3u) & ~3u));
+    for (u32 x = threadIdx.x; x < p.n_coefs; x += nthreads) cf_s[x] = ld2(p.coefs + 2 * (size_t)x);
 }
 
-// the polynomial at point d of pair i
-__device__ __forceinline__ fp2 ir_point(const ir::Shape& sh, const u32* w_s, const fp2* cf_s, const u64* __restrict__ tables, size_t stride,
-                                        u32 i, u32 half, u32 d, fp2* tv, fp2* nv) {
-    for (u32 t = 0; t < sh.n_tables; t++) {
-        const u64* tb = tables + 2 * (size_t)t * stride;
-        if (d == 0) {
-            tv[t] = ld2(tb + 2 * (size_t)i);
-        } else if (d == 1) {
-            tv[t] = ld2(tb + 2 * ((size_t)i + half));
-        } else {
-            const fp2 lo = ld2(tb + 2 * (size_t)i), hi = ld2(tb + 2 * ((size_t)i + half));
-            tv[t] = f2_add(lo, f2_mul_base(f2_sub(hi, lo), (u64)d));
-        }
-    }
-    return ir::eval(sh, w_s, cf_s, tv, nv);
+__device__ __forceinline__ fp2 ir_table_value(const u64* __restrict__ tb, u32 i, u32 half, u32 d) {
+    if (d == 0) return ld2(tb + 2 * (size_t)i);
+    if (d == 1) return ld2(tb + 2 * ((size_t)i + half));
+    const fp2 lo = ld2(tb + 2 * (size_t)i), hi = ld2(tb + 2 * ((size_t)i + half));
+    return f2_add(lo, f2_mul_base(f2_sub(hi, lo), (u64)d));
 }
 
 // grid (blocks, degree + 1): row y evaluates point y; partials[block][point] as in k_sc_round
@@ -390,10 +387,12 @@ __global__ void __launch_bounds__(IRT) k_sc_round_ir(const u64* __restrict__ tab
     }
     ir_stage(p, ir_smem, cf_s, IRT);
     __syncthreads();
-    fp2 tv[ir::MAX_TABLES], nv[ir::MAX_NODES];
+    fp2 tv[ir::MAX_TABLES], nv[ir::MAX_NODES + 1];
     fp2 acc = f2(0, 0);
-    for (u32 i = blockIdx.x * IRT + threadIdx.x; i < half; i += gridDim.x * IRT)
-        acc = f2_add(acc, ir_point(p.shape, ir_smem, cf_s, tables, stride, i, half, d, tv, nv));
+    for (u32 i = blockIdx.x * IRT + threadIdx.x; i < half; i += gridDim.x * IRT) {
+        for (u32 t = 0; t < p.n_tables; t++) tv[t] = ir_table_value(tables + 2 * (size_t)t * stride, i, half, d);
+        acc = f2_add(acc, ir::plan_eval(ir_smem, cf_s, tv, nv));
+    }
 #pragma unroll
     for (int off = 16; off >= 1; off >>= 1) {
         acc.c0 = gl_add(acc.c0, shfl_down64(acc.c0, off));
@@ -410,19 +409,69 @@ __global__ void __launch_bounds__(IRT) k_sc_round_ir(const u64* __restrict__ tab
     }
 }
 
-constexpr int IR_TAIL_T = 1024;
+// one item by one warp: returns the polynomial's value (every lane)
+__device__ __forceinline__ fp2 ir_warp_item(const hlk::IrDev& p, const u32* pw, const fp2* cf_s, const u64* __restrict__ tables, size_t stride,
+                                            u32 i, u32 half, u32 d, fp2* tv_s, fp2* nv_s, fp2* ub_s, u32 lane) {
+    for (u32 t = lane; t < p.n_tables; t += 32) tv_s[t] = ir_table_value(tables + 2 * (size_t)t * stride, i, half, d);
+    __syncwarp();
+    const u32 L = pw[0];
+    for (u32 l = 0; l < L; l++) {
+        ir::plan_level_units(pw, l, cf_s, tv_s, nv_s, ub_s, lane, 32);
+        __syncwarp();
+        ir::plan_level_nodes(pw, l, ub_s, nv_s, lane, 32);
+        __syncwarp();
+    }
+    const fp2 v = nv_s[p.n_nodes - 1];  // the final node has the highest id
+    __syncwarp();                        // every lane has read it before the next item overwrites the areas
+    return v;
+}
+
+__device__ __forceinline__ u32 ir_warp_area(const hlk::IrDev& p) { return p.n_tables + p.n_nodes + p.max_level_units; }  // Fp2 per warp
+
+__global__ void __launch_bounds__(IRW_WARPS * 32) k_sc_round_irw(const u64* __restrict__ tables, size_t stride, u32 half, hlk::IrDev p,
+                                                                 int degree, int eval_one, u64* __restrict__ partials) {
+    extern __shared__ __align__(16) u32 ir_smem[];
+    __shared__ u64 wsum[IRW_WARPS][2];
+    fp2* cf_s;
+    const u32 d = blockIdx.y;
+    u64* dst = partials + ((size_t)blockIdx.x * (degree + 1) + d) * 2;
+    if (d == 1 && !eval_one) {
+        if (threadIdx.x < 2) dst[threadIdx.x] = 0;
+        return;
+    }
+    ir_stage(p, ir_smem, cf_s, IRW_WARPS * 32);
+    __syncthreads();
+    const u32 lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    fp2* area = cf_s + p.n_coefs + (size_t)warp * ir_warp_area(p);
+    fp2 *tv_s = area, *nv_s = area + p.n_tables, *ub_s = nv_s + p.n_nodes;
+    fp2 acc = f2(0, 0);
+    for (u32 i = blockIdx.x * IRW_WARPS + warp; i < half; i += gridDim.x * IRW_WARPS)
+        acc = f2_add(acc, ir_warp_item(p, ir_smem, cf_s, tables, stride, i, half, d, tv_s, nv_s, ub_s, lane));
+    if (lane == 0) { wsum[warp][0] = acc.c0; wsum[warp][1] = acc.c1; }
+    __syncthreads();
+    if (threadIdx.x < 2) {
+        u64 s = 0;
+#pragma unroll
+        for (int w = 0; w < IRW_WARPS; w++) s = gl_add(s, wsum[w][threadIdx.x]);
+        dst[threadIdx.x] = s;
+    }
+}
+
+constexpr int IR_TAIL_T = IR_TAIL_WARPS * 32;
+template <bool WARP_FORM>
 __global__ void __launch_bounds__(IR_TAIL_T) k_sc_tail_ir(u64* __restrict__ tables, size_t stride, u32 len, hlk::IrDev p, int degree, int k,
                                                           ScStep a, int nrounds, int first_has_claim) {
     extern __shared__ __align__(16) u32 ir_smem[];
     __shared__ StepSmem sm;
-    __shared__ u64 wsum[IR_TAIL_T / 32][2 * hlk::SC_MAX_POINTS];
+    __shared__ u64 wsum[IR_TAIL_WARPS][2 * hlk::SC_MAX_POINTS];
     __shared__ hlk::ScState st_s;
     __shared__ u64 mask_s[2 * (63 * (hlk::SC_MAX_POINTS - 1) + 2)];
     __shared__ u64 hs_s[2 * 63];
     __shared__ u64 invden_s[hlk::SC_MAX_POINTS];
     fp2* cf_s;
     ir_stage(p, ir_smem, cf_s, IR_TAIL_T);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, np = degree + 1;
+    const u32 lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int np = degree + 1;
     {
         const u32* src = reinterpret_cast<const u32*>(a.state);
         u32* dst = reinterpret_cast<u32*>(&st_s);
@@ -438,26 +487,40 @@ __global__ void __launch_bounds__(IR_TAIL_T) k_sc_tail_ir(u64* __restrict__ tabl
     a.inv_den = invden_s;
     a.state = &st_s;
     __syncthreads();
-    fp2 tv[ir::MAX_TABLES], nv[ir::MAX_NODES];
+    fp2* area = cf_s + p.n_coefs + (size_t)warp * ir_warp_area(p);
+    fp2 *tv_s = area, *nv_s = area + p.n_tables, *ub_s = nv_s + p.n_nodes;
     for (int rd = 0; rd < nrounds; rd++) {
         const u32 half = len >> 1;  // a power of two
         const bool have_claim = a.recover && (rd > 0 || first_has_claim);
         fp2 acc[hlk::SC_MAX_POINTS];
 #pragma unroll
         for (int d = 0; d < hlk::SC_MAX_POINTS; d++) acc[d] = f2(0, 0);
-        for (u32 x = threadIdx.x; x < half * (u32)np; x += IR_TAIL_T) {
-            const u32 d = x / half, i = x - d * half;
-            if (d == 1 && have_claim) continue;
-            const fp2 v = ir_point(p.shape, ir_smem, cf_s, tables, stride, i, half, d, tv, nv);
+        if constexpr (WARP_FORM) {
+            for (u32 x = warp; x < half * (u32)np; x += IR_TAIL_WARPS) {
+                const u32 d = x / half, i = x - d * half;
+                if (d == 1 && have_claim) continue;
+                const fp2 v = ir_warp_item(p, ir_smem, cf_s, tables, stride, i, half, d, tv_s, nv_s, ub_s, lane);
 #pragma unroll
-            for (int dd = 0; dd < hlk::SC_MAX_POINTS; dd++)
-                if ((u32)dd == d) acc[dd] = f2_add(acc[dd], v);
-        }
-        for (int d = 0; d < np; d++) {
+                for (int dd = 0; dd < hlk::SC_MAX_POINTS; dd++)
+                    if ((u32)dd == d) acc[dd] = f2_add(acc[dd], v);
+            }
+        } else {
+            fp2 tv[ir::MAX_TABLES], nv[ir::MAX_NODES + 1];
+            for (u32 x = threadIdx.x; x < half * (u32)np; x += IR_TAIL_T) {
+                const u32 d = x / half, i = x - d * half;
+                if (d == 1 && have_claim) continue;
+                for (u32 t = 0; t < p.n_tables; t++) tv[t] = ir_table_value(tables + 2 * (size_t)t * stride, i, half, d);
+                const fp2 v = ir::plan_eval(ir_smem, cf_s, tv, nv);
 #pragma unroll
-            for (int off = 16; off >= 1; off >>= 1) {
-                acc[d].c0 = gl_add(acc[d].c0, shfl_down64(acc[d].c0, off));
-                acc[d].c1 = gl_add(acc[d].c1, shfl_down64(acc[d].c1, off));
+                for (int dd = 0; dd < hlk::SC_MAX_POINTS; dd++)
+                    if ((u32)dd == d) acc[dd] = f2_add(acc[dd], v);
+            }
+            for (int d = 0; d < np; d++) {
+#pragma unroll
+                for (int off = 16; off >= 1; off >>= 1) {
+                    acc[d].c0 = gl_add(acc[d].c0, shfl_down64(acc[d].c0, off));
+                    acc[d].c1 = gl_add(acc[d].c1, shfl_down64(acc[d].c1, off));
+                }
             }
         }
         if (lane == 0) {
@@ -467,14 +530,14 @@ __global__ void __launch_bounds__(IR_TAIL_T) k_sc_tail_ir(u64* __restrict__ tabl
         if ((int)threadIdx.x < 2 * np) {
             u64 s = 0;
 #pragma unroll
-            for (int w = 0; w < IR_TAIL_T / 32; w++) s = gl_add(s, wsum[w][threadIdx.x]);
+            for (int w = 0; w < IR_TAIL_WARPS; w++) s = gl_add(s, wsum[w][threadIdx.x]);
             sm.sums[threadIdx.x] = s;
         }
         __syncthreads();
         if (warp == 0) {
             ScStep b = a;
             b.round = a.round + rd; b.use_claim = have_claim ? 1 : 0; b.fs = 1;
-            step_body(b, sm, lane);
+            step_body(b, sm, (int)lane);
         }
         __syncthreads();
         const fp2 r = a.state->r;
@@ -494,7 +557,15 @@ __global__ void __launch_bounds__(IR_TAIL_T) k_sc_tail_ir(u64* __restrict__ tabl
     }
 }
 
-size_t ir_smem_bytes(const ir::Shape& s) { return (((size_t)s.n_words + 3) & ~(size_t)3) * 4 + (size_t)s.n_coefs * 16 + 16; }
+size_t ir_smem_bytes(const hlk::IrDev& p, int warps) {
+    return (((size_t)p.plan_words + 3) & ~(size_t)3) * 4 + (size_t)p.n_coefs * 16 + (size_t)warps * (p.n_tables + p.n_nodes + p.max_level_units) * 16 + 16;
+}
+
+// a polynomial of few units leaves most lanes of a warp idle: it stays in the thread form
+// measured on a 60-table, 219-unit polynomial: the thread form takes ~120 us for anything up to ~190k items and 2.5 ns per
+// item beyond; the warp form 20 us plus 8.7 ns per item
+bool ir_warp_form(const hlk::IrDev& p, u32 half, int degree) { return p.n_units >= 24 && (size_t)half * (degree + 1) <= 12288; }
+bool ir_warp_tail(const hlk::IrDev& p) { return p.n_units >= 24; }
 
 template <int POLY, int K, int D>
 cudaError_t launch_round(const u64* tables, size_t stride, u32 half, const u64* coefs, int eval_one, u64* partials, u32 nblocks, cudaStream_t s) {
@@ -512,30 +583,54 @@ u32 sc_round_blocks(u32 half, int sm_count) {
     return b > cap ? cap : b;
 }
 
-u32 sc_ir_blocks(u32 half, int sm_count) {
-    u32 b = (half + IRT - 1) / IRT, cap = (u32)sm_count * 2;
+u32 sc_ir_max_blocks(u32 half, int sm_count) {
+    u32 b = half, cap = (u32)sm_count * 4;  // the warp form at one pair per warp needs the most CTAs
     if (b < 1) b = 1;
     return b > cap ? cap : b;
 }
 
-// The single-CTA tail pays off only while a round's work is below the cost of three launches; a heavy
-// program leaves the multi-CTA rounds later than a light one.
-u32 sc_ir_tail_len(const ir::Shape& s, int degree) {
-    const u32 work = s.n_words * (u32)(degree + 1);
-    return work <= 256 ? 4096u : work <= 1024 ? 1024u : 256u;
+u32 sc_ir_blocks(const IrDev& p, u32 half, int degree, int sm_count) {
+    const bool warp = ir_warp_form(p, half, degree);
+    u32 per = warp ? IRW_WARPS : IRT, b = (half + per - 1) / per, cap = (u32)sm_count * (warp ? 4 : 2);
+    if (b < 1) b = 1;
+    return b > cap ? cap : b;
+}
+
+// The single-CTA tail pays off only while a round's items fit its warps a few times over.
+u32 sc_ir_tail_len(const IrDev& p, int degree) {
+    (void)degree;
+    return ir_warp_tail(p) ? 16u : p.n_units >= 4 ? 1024u : 4096u;
 }
 
 cudaError_t sc_round_ir(const IrDev& p, int k, const u64* tables, size_t stride, u32 half, int degree, int eval_one, u64* partials,
                         u32 nblocks, cudaStream_t s) {
     (void)k;
     dim3 grid(nblocks, (unsigned)degree + 1);
-    k_sc_round_ir<<<grid, IRT, ir_smem_bytes(p.shape), s>>>(tables, stride, half, p, degree, eval_one, partials);
+    if (ir_warp_form(p, half, degree)) {
+        const size_t smem = ir_smem_bytes(p, IRW_WARPS);
+        if (smem > 48 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(k_sc_round_irw, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return e;
+        }
+        k_sc_round_irw<<<grid, IRW_WARPS * 32, smem, s>>>(tables, stride, half, p, degree, eval_one, partials);
+    } else {
+        k_sc_round_ir<<<grid, IRT, ir_smem_bytes(p, 0), s>>>(tables, stride, half, p, degree, eval_one, partials);
+    }
     return cudaGetLastError();
 }
 
 cudaError_t sc_tail_ir(const IrDev& p, int k, u64* tables, size_t stride, u32 len, int degree, const ScStep& a, int nrounds,
                        int first_has_claim, cudaStream_t s) {
-    k_sc_tail_ir<<<1, IR_TAIL_T, ir_smem_bytes(p.shape), s>>>(tables, stride, len, p, degree, k, a, nrounds, first_has_claim);
+    if (ir_warp_tail(p)) {
+        const size_t smem = ir_smem_bytes(p, IR_TAIL_WARPS);
+        if (smem > 32 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(k_sc_tail_ir<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return e;
+        }
+        k_sc_tail_ir<true><<<1, IR_TAIL_T, smem, s>>>(tables, stride, len, p, degree, k, a, nrounds, first_has_claim);
+    } else {
+        k_sc_tail_ir<false><<<1, IR_TAIL_T, ir_smem_bytes(p, 0), s>>>(tables, stride, len, p, degree, k, a, nrounds, first_has_claim);
+    }
     return cudaGetLastError();
 }
 

@@ -60,6 +60,14 @@ def test_oracle_and_product_interpreters_agree_with_python_on_every_slot(oracle,
             out = np.zeros(2, dtype=np.uint64)
             emul.emul_ir_eval(_vp(w), w.size, k, prog.n_nodes, prog.n_terms, _vp(cf) if cf.size else None, cf.shape[0], _vp(v), _vp(out))
             assert (int(out[0]), int(out[1])) == want, (s["name"], rep)
+            # the evaluation plan the kernels run, as one worker and as 32 / 5 cooperating lanes
+            info = np.zeros(4, dtype=np.uint32)
+            for lanes in (0, 32, 5):
+                out[:] = 0
+                rc = emul.emul_ir_plan_eval(_vp(w), w.size, k, prog.n_nodes, prog.n_terms, _vp(cf) if cf.size else None, cf.shape[0], _vp(v),
+                                            lanes, _vp(out), _vp(info))
+                assert rc == 0 and (int(out[0]), int(out[1])) == want, (s["name"], rep, lanes)
+            assert info[1] == prog.n_nodes + 1
 
 
 def test_closed_form_families_written_as_programs(oracle):
