@@ -17,14 +17,17 @@ struct Shape {
 int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* key32, const uint64_t* h_data) {
     const u32 logn = st->logn, lognn = st->logn + st->logr;
     const size_t n = st->n(), nn = st->nn();
-    const u32 T = st->zk ? (u32)((n + st->q + n - 1) / n) : 1u;
+    // rows above 2^14 words run as 2 or 4 shared-memory transforms of 2^14 (encode_core.cuh)
+    const u32 logb = logn > 14 ? 14u : logn, loga = logn - logb;
+    const size_t nb = (size_t)1 << logb;
+    const u32 T = st->zk ? (u32)((n + st->q + nb - 1) / nb) : (u32)(n / nb);
     const u64* tw = nullptr;
     int rc = root_powers(c, lognn, &tw);
     if (rc) return rc;
     uint32_t* d_key = nullptr;
     u64* scratch = nullptr;
     uint32_t* cvs = nullptr;
-    const size_t scratch_words = hlk::encode_scratch_words(logn, T, c->sm_count, st->rows);
+    const size_t scratch_words = hlk::encode_scratch_words(logb, T, c->sm_count, st->rows);
     const u32 nchunks = hlk::hash_chunks(st->rows);
     const size_t cvs_bytes = nchunks > 1 ? (size_t)nchunks * nn * 32 : 0;
     rc = upload_key(c, key32, &d_key);
@@ -65,9 +68,9 @@ int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* 
             a.data = st->d_data + (size_t)r0 * n;
             a.pads = st->d_pads ? st->d_pads + (size_t)r0 * st->q : nullptr;
             a.pows = d_pows; a.tw_nn = tw; a.enc = st->d_enc + (size_t)r0 * nn; a.scratch = scratch;
-            a.rows = nr; a.q = st->zk ? st->q : 0; a.T = T; a.logr = st->logr; a.zk = st->zk ? 1 : 0;
+            a.rows = nr; a.q = st->zk ? st->q : 0; a.T = T; a.logr = st->logr + loga; a.loga = loga; a.zk = st->zk ? 1 : 0;
             a.ninv = gl_inv((u64)n);
-            cudaError_t e = hlk::encode_rows(a, logn, c->fast_encoder, c->sm_count, scratch_words, c->stream, &st->encoder_path);
+            cudaError_t e = hlk::encode_rows(a, logb, c->fast_encoder || loga, c->sm_count, scratch_words, c->stream, &st->encoder_path);
             c->stats.kernel_launches += 1;
             if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "row encoder launch", e);
         }
@@ -88,7 +91,7 @@ int check_shape(hl_ctx* c, uint32_t log_cols, uint32_t inv_rate, size_t rows, si
     int logr = log2_exact(inv_rate);
     if (logr < 0 || rows == 0 || rows > 0x7FFFFFFFu) return fail(c, HL_B200_ERR_ARG, "commit: rows or inv_rate");
     if (log_cols < 1) return fail(c, HL_B200_ERR_UNSUPPORTED, "commit: fewer than 2 columns");
-    if (log_cols > 14) return fail(c, HL_B200_ERR_UNSUPPORTED, "commit: more than 2^14 columns per row");
+    if (log_cols > 16) return fail(c, HL_B200_ERR_UNSUPPORTED, "commit: more than 2^16 columns per row");
     if (max_log && log_cols + (uint32_t)logr > max_log) return fail(c, HL_B200_ERR_ARG, "commit: transform exceeds the caller's NTT tables");
     size_t n = (size_t)1 << log_cols, nn = n << logr;
     if (zk && (q == 0 || n + q > nn)) return fail(c, HL_B200_ERR_ARG, "commit_zk: pad count (need 0 < q and n + q <= nn)");

@@ -48,8 +48,11 @@ struct RowArgs {
     const u64* pows;   // nn coset powers h^i (hiding form only)
     const u64* tw_nn;  // nn powers of the primitive nn-th root w_nn^j
     u64* enc;          // rows x nn
-    u64* scratch;      // per CTA: T x n words
-    u32 rows, q, T, logr;
+    u64* scratch;      // per CTA: T x N words, N = the size the shared-memory transforms run at
+    u32 rows, q;
+    u32 T;             // coefficient blocks of N words: ceil((n + q) / N) (hiding form) or n / N (plain form)
+    u32 logr;          // log2(nn / N): the number of output residues
+    u32 loga;          // log2(n / N): 0 unless the row is longer than one shared-memory transform
     int zk;
     u64 ninv;          // n^-1
 };
@@ -232,40 +235,55 @@ struct Fast {
     }
 
     // ---- the row pipeline ----
-    // inverse transform of the message row, then the coefficient blocks x[t n + i] into the scratch slot
+    // inverse transform of the message row, then the coefficient blocks x[idx] into the scratch slot.
+    // c[i] = F[(n - i) mod n] / n with F the forward transform of the message, one residue a of F per pass set.
     template <class Sync>
     GL_HD static void row_coeffs(const RowArgs& a, u32 row, u64* S, const u64* TW, u64* X, u32 tid, u32 nt, Sync sync) {
-        const u64* src = a.data + (size_t)row * N;
+        const u32 A = 1u << a.loga, n = N << a.loga, nn = N << a.logr, lognn = LOGN + a.logr;
+        const u64* src = a.data + (size_t)row * n;
         const u64* pad = a.pads + (size_t)row * a.q;
-        transform(S, TW, tid, nt, [&](u32 i) { return src[i]; },
-                  [&](u32 k, u64 v) {
-                      const u32 i = (N - k) & (N - 1);  // c[i] = X[(n - i) mod n] / n
-                      const u64 c = gl_mul(v, a.ninv);
-                      for (u32 t = 0; t < a.T; t++) {
-                          const u32 idx = i + t * N;
-                          u64 x = t == 0 ? c : 0;
-                          if (a.zk) {
-                              if (idx >= N + a.q) break;
-                              if (idx < a.q) x = gl_sub(x, pad[idx]);
-                              if (idx >= N && idx - N < a.q) x = gl_add(x, pad[idx - N]);
-                              x = gl_mul(x, a.pows[idx]);
+        const u32 Tn = a.zk ? (n + a.q + n - 1) / n : 1u;
+        for (u32 ra = 0; ra < A; ra++) {
+            transform(S, TW, tid, nt,
+                      [&](u32 i) {
+                          u64 y = src[i];
+                          if (a.loga) {
+                              for (u32 t = 1; t < A; t++)
+                                  y = gl_add(y, gl_mul(src[i + t * N], a.tw_nn[((t * ra) << (lognn - a.loga)) & (nn - 1)]));  // w_A^(t a)
+                              if (ra) y = gl_mul(y, a.tw_nn[((i * ra) << (a.logr - a.loga)) & (nn - 1)]);                     // w_n^(i a)
                           }
-                          X[(size_t)t * N + i] = x;
-                      }
-                  },
-                  sync);
+                          return y;
+                      },
+                      [&](u32 k, u64 v) {
+                          const u32 i = (n - ((k << a.loga) + ra)) & (n - 1);
+                          const u64 c = gl_mul(v, a.ninv);
+                          for (u32 t = 0; t < Tn; t++) {
+                              const u32 idx = i + t * n;
+                              u64 x = t == 0 ? c : 0;
+                              if (a.zk) {
+                                  if (idx >= n + a.q) break;
+                                  if (idx < a.q) x = gl_sub(x, pad[idx]);
+                                  if (idx >= n && idx - n < a.q) x = gl_add(x, pad[idx - n]);
+                                  x = gl_mul(x, a.pows[idx]);
+                              }
+                              X[idx] = x;
+                          }
+                      },
+                      sync);
+            if (ra + 1 < A) sync();  // the next residue's first pass overwrites the shared-memory row
+        }
     }
 
-    // output residue s: the size-n transform of the twisted coefficients, stored at out[R k + s]
+    // output residue s: the size-N transform of the twisted coefficients, stored at out[(nn/N) k + s]
     template <class Sync>
     GL_HD static void row_residue(const RowArgs& a, u32 row, u32 s, u64* S, const u64* TW, const u64* X, u32 tid, u32 nt, Sync sync) {
-        const u32 nn = N << a.logr;
+        const u32 nn = N << a.logr, live = (N << a.loga) + a.q;  // x is zero from n + q on (plain form: q = 0)
         u64* dst = a.enc + ((size_t)row * N << a.logr) + s;
         transform(S, TW, tid, nt,
                   [&](u32 i) {
                       u64 y = ENC_LDCG(X + i);
-                      // x[i + t n] is zero from i + t n >= n + q on, and those scratch words are never written
-                      for (u32 t = 1; t < a.T && i + t * N < N + a.q; t++)
+                      // the scratch words from n + q on are never written and never read
+                      for (u32 t = 1; t < a.T && i + t * N < live; t++)
                           y = gl_add(y, gl_mul(ENC_LDCG(X + (size_t)t * N + i), a.tw_nn[(t * s * N) & (nn - 1)]));
                       if (s) y = gl_mul(y, a.tw_nn[(i * s) & (nn - 1)]);
                       return y;

@@ -35,15 +35,17 @@ extern "C" int emul_encode(int fast, const u64* data, u32 rows, u32 logn, u32 lo
                            const u64* pows, int zk, u32 nt, u64* out) {
     u32 n = 1u << logn;
     std::vector<u64> tw = make_tw(logn + logr);
+    // rows above 2^14 words run as 2 or 4 transforms of 2^14, exactly as the library's commit sets them up
+    const u32 logb = logn > 14 ? 14 : logn, loga = logn - logb, nb = 1u << logb;
     RowArgs a;
     a.data = data; a.pads = pads; a.pows = pows; a.tw_nn = tw.data(); a.enc = out;
-    a.rows = rows; a.q = zk ? q : 0; a.logr = logr; a.zk = zk;
-    a.T = zk ? (n + q + n - 1) / n : 1;
+    a.rows = rows; a.q = zk ? q : 0; a.logr = logr + loga; a.loga = loga; a.zk = zk;
+    a.T = zk ? (n + q + nb - 1) / nb : n / nb;
     a.ninv = gl_inv(n);
-    std::vector<u64> X((size_t)a.T * n, 0xA5A5A5A5A5A5A5A5ULL);  // poisoned: unwritten words must never be read
+    std::vector<u64> X((size_t)a.T * nb, 0xA5A5A5A5A5A5A5A5ULL);  // poisoned: unwritten words must never be read
     a.scratch = X.data();
     if (fast) {
-        switch (logn) {
+        switch (logb) {
             case 8: run_fast<8>(a, nt); break;
             case 9: run_fast<9>(a, nt); break;
             case 10: run_fast<10>(a, nt); break;

@@ -138,6 +138,40 @@ def test_m1_zk_commit_and_opening_bytes_match_the_cpu(dev, oracle, keyed, fast):
     dev.ctx.set_encoder(True)
 
 
+@pytest.mark.parametrize("shape", [(15, 2, 37, 280), (16, 2, 9, 280), (15, 4, 5, 40000)])
+def test_rows_longer_than_one_shared_memory_transform(dev, oracle, shape):
+    """The T256 / T512 profiles commit rows of 2^15 / 2^16 words (shape.rs:248-262); such a row runs as 2 or 4
+    transforms of 2^14 each way.  Hiding + keyed commit: leaves, salted tree and complete opening bytes against the
+    CPU; plain commit: leaves.  The third shape has q > n (pads interleave, encode_buffer.rs:56-64)."""
+    o = oracle
+    log_cols, ir, rows, q = shape
+    n, nn = 1 << log_cols, (1 << log_cols) * ir
+    tag = o.HashTag.for_profile("hashline-zk-mr1/metal-test/1")
+    p = o.PcsParams(log_cols, ir, 8)
+    data = rnd(700 + log_cols, rows * n)
+    cpu = o.commit_zk(p, data, 18, q, o.ZkRng(77, b"long-rows"), tag)
+    rng = o.ZkRng(77, b"long-rows")
+    pads, salts = rng.fp_vec(rows * q), rng.salts(nn)
+    got = dev.try_commit_zk_keyed(log_cols, ir, data, pads, o.coset_powers(7, nn), 18, tag.column)
+    assert got is not None, dev.ctx.declines
+    store, leaves = got
+    assert (leaves == cpu.leaves).all()
+    levels = store.merkle(salts, tag.leaf, tag.node)
+    assert bytes(levels[-1]) == cpu.root and (levels == cpu.levels).all()
+    cpu.mask_rows, cpu.prox_mask_row = [rows - 3, rows - 2], rows - 1
+    cl = _claims(o, rows, log_cols, 1700 + log_cols)
+    t1, t2 = o.Transcript(b"long-open"), o.Transcript(b"long-open")
+    assert o.open_zk(cpu, cl, t1).to_bytes() == o.open_zk(cpu, cl, t2, fold=store.fold_rows_with_pads, columns=store.columns).to_bytes()
+    assert t1.challenge_fp2() == t2.challenge_fp2()
+    store.free()
+    enc = o.encode_rows_plain(data, rows, n, nn, 18)
+    store, leaves = dev.try_commit(log_cols, ir, data, 18)
+    assert (leaves == o.hash_columns(enc, rows, nn)).all()
+    idx = np.array([0, 1, nn - 1, nn // 2 + 3], dtype=np.uint64)
+    assert (store.columns(idx) == o.gather_columns(enc, rows, nn, idx)).all()
+    store.free()
+
+
 def _splitmix_fp(seed, n):
     out, s = [], seed
     for _ in range(n):

@@ -47,7 +47,7 @@ def test_allocation_failure_is_a_decline_and_the_context_survives(dev, oracle, m
 
 
 def test_shapes_outside_the_kernels_range_decline(dev, oracle):
-    assert dev.try_commit(15, 2, np.zeros(1 << 15, dtype=np.uint64), 16) is None          # rows of 2^15 words
+    assert dev.try_commit(17, 2, np.zeros(1 << 17, dtype=np.uint64), 18) is None          # rows of 2^17 words
     assert dev.try_commit(10, 3, np.zeros(1 << 10, dtype=np.uint64), 12) is None          # rate not a power of two
     assert dev.try_commit(10, 4, np.zeros(1 << 10, dtype=np.uint64), 11) is None          # beyond the caller's NTT tables
     pows = oracle.coset_powers(7, 1 << 11)

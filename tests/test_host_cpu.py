@@ -59,6 +59,8 @@ CASES = [  # fast, log_n, inv_rate, rows, q, zk, emulated threads
     (0, 3, 4, 2, 4, 1, 7), (0, 3, 4, 2, 12, 1, 32), (0, 6, 8, 3, 8, 1, 32), (0, 4, 4, 3, 0, 0, 5), (0, 1, 4, 2, 2, 1, 32),
     (1, 8, 2, 2, 8, 1, 32), (1, 8, 4, 2, 300, 1, 16), (1, 9, 4, 1, 8, 1, 32), (1, 10, 4, 2, 256, 1, 64), (1, 11, 2, 1, 40, 1, 128),
     (1, 12, 4, 1, 8, 0, 256), (1, 13, 2, 1, 280, 1, 512), (1, 14, 2, 1, 280, 1, 512), (1, 10, 4, 2, 0, 0, 64),
+    # rows longer than one shared-memory transform (the T256 / T512 profiles, shape.rs:248-262): 2 and 4 residues each way
+    (1, 15, 2, 1, 280, 1, 512), (1, 16, 2, 1, 280, 1, 512), (1, 15, 4, 1, 0, 0, 512), (1, 15, 4, 1, 40000, 1, 512),
 ]
 
 
