@@ -205,6 +205,22 @@ def device_extras(dev, backend, np_data, np_pads, np_pows, col_key) -> dict:
         ctx.fold_cols_i8(wm, cw)
     t = ctx.timing_read(reset=True)
     out["fold_cols_i8_4096x14336_ms"] = t["fold"][0] / 2
+    # a slot's tables built on the device from the resident rows of `A`: an eq cube of 2^21 entries and a witness plane of
+    # 2^19 entries partially evaluated at 3 fixed coordinates (8 rows of 2^14 words each folded per entry)
+    st, _ = dev.try_commit_zk_keyed(log_cols, ir, np_data, np_pads, np_pows, log_cols + 1, col_key)
+    point = splitmix_fp(90, 21 * 2).reshape(21, 2)
+    coords = [("fixed", (int(a), int(b))) for a, b in splitmix_fp(91, 6).reshape(3, 2)] + [("rho", k) for k in range(19)]
+    for rep in range(3):
+        if rep == 1:
+            ctx.timing_read(reset=True)
+        t21, t19 = backend.B200Tables(ctx, 1, 21), backend.B200Tables(ctx, 1, 19)
+        t21.plan_eq(0, point, 0)
+        t19.plan_plane(0, st, coords, [(0, (1, 0))])
+        t21.flush(); t19.flush()
+        t21.free(); t19.free()
+    t = ctx.timing_read(reset=True)
+    out["tables_eq_2^21_plus_plane_2^19_x8_ms"] = t["tables"][0] / 2
+    st.free()
     # the heaviest slot polynomial of a block as data: the recorded structure of the D zero-check (60 tables, 71 nodes,
     # declared degree 5) with seeded coefficients, at 2^17 points, through the interpreting evaluator
     import json as _json

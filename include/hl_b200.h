@@ -172,6 +172,36 @@ int hl_b200_rounds_new(hl_ctx* ctx, int poly, size_t k, uint32_t n_vars, uint32_
 #define HL_IR_ZERO 0xFFFFFFFDu
 int hl_b200_rounds_new_ir(hl_ctx* ctx, size_t k, uint32_t n_vars, uint32_t degree, const uint64_t* tables, const uint32_t* words,
                           size_t n_words, uint32_t n_nodes, uint32_t n_terms, const uint64_t* coefs, size_t ncoefs, hl_rounds** out);
+/* ---- a slot's tables built on the device (argument.rs:907 build_tables_device; the Metal form is
+ * gpu/metal.rs MetalTables::{new, tables_mut, plan_eq, plan_plane, build_planned, flush, to_vecs}) ----
+ * A table set is k tables of 2^n_vars Fp2 in device memory.  Each table is filled by ONE of:
+ *   tables_put     host-built words (public tables), as MetalTables::tables_mut + flush;
+ *   tables_eq      the eq cube of a point over cube variables [start, start + p): entry x is
+ *                  hi[y >> p/2] * lo[y & (2^(p/2) - 1)], y = (x >> (n_vars - start - p)) & (2^p - 1), with hi / lo the
+ *                  eq tables (msb first) of the point's first p - p/2 and last p/2 coordinates (argument.rs:643-660);
+ *   tables_plane   a committed plane: out[x] = sum_z eqf[z] * v(inv_hi[xu >> xlo] | inv_lo[xu & (2^xlo - 1)] | zbits[z]),
+ *                  xu = x & used, v(idx) = sum_s coef_s * rows[off_s + idx]; nz = 0 means no fixed coordinate
+ *                  (out[x] = v(..)).  The maps are the host builder's own (argument.rs:418-437, 486-512);
+ *                  slices = ns x (offset, coef c0, coef c1).  rows = the resident data rows of `store`
+ *                  (metal.rs:3105 resident_rows) or, with store NULL, n_words words at the DEVICE address d_rows.
+ *                  Every address the maps can form is checked against the rows before the launch.
+ * base_check != 0 declares the table base-valued; tables_flush (and rounds_from_tables) answer
+ * HL_B200_ERR_MISMATCH if a word of such a table has a non-zero imaginary part (metal.rs:2649-2665).
+ * The map arrays are read during the call when they are ordinary (pageable) host memory.
+ * rounds_from_tables[_ir] takes the set over on success (the handle stays valid but empty; free it). */
+typedef struct hl_tables hl_tables;
+int hl_b200_tables_new(hl_ctx* ctx, size_t k, uint32_t n_vars, hl_tables** out);
+int hl_b200_tables_put(hl_tables* t, size_t i, const uint64_t* words);
+int hl_b200_tables_eq(hl_tables* t, size_t i, uint32_t start, uint32_t p, const uint64_t* hi, const uint64_t* lo, int base_check);
+int hl_b200_tables_plane(hl_tables* t, size_t i, const hl_store* store, const uint64_t* d_rows, size_t n_words, uint64_t used,
+                         uint32_t xlo, const uint32_t* inv_lo, const uint32_t* inv_hi, const uint32_t* zbits, uint32_t nz,
+                         const uint64_t* eqf, const uint64_t* slices, uint32_t ns, int base_check);
+int hl_b200_tables_flush(hl_tables* t);
+int hl_b200_tables_read(hl_tables* t, size_t i, uint64_t* out);   /* MetalTables::to_vecs, one table */
+void hl_b200_tables_free(hl_tables* t);
+int hl_b200_rounds_from_tables(hl_ctx* ctx, int poly, uint32_t degree, hl_tables* t, const uint64_t* coefs, size_t ncoefs, hl_rounds** out);
+int hl_b200_rounds_from_tables_ir(hl_ctx* ctx, uint32_t degree, hl_tables* t, const uint32_t* words, size_t n_words, uint32_t n_nodes,
+                                  uint32_t n_terms, const uint64_t* coefs, size_t ncoefs, hl_rounds** out);
 /* SumcheckRounds::round: sums = degree + 1 Fp2.  eval_one == 0 skips the point 1 (left zero): the caller
  * recovers s(1) = claim - s(0) (rounds.rs:94-99,137-140). */
 int hl_b200_rounds_round(hl_rounds* r, uint32_t j, int eval_one, uint64_t* sums);
@@ -231,7 +261,7 @@ int hl_b200_stats(hl_ctx* ctx, hl_stats* out);
 
 /* ---- per-kernel-family device time: the phase clock of timing.rs:1-130 / HL_METAL_TIMING
  * (metal.rs:2148-2179), taken with CUDA events on the context's stream.  Off by default. ---- */
-enum { HL_T_ENCODE = 0, HL_T_HASH = 1, HL_T_MERKLE = 2, HL_T_FOLD = 3, HL_T_GATHER = 4, HL_T_ROUNDS = 5, HL_T_LOGUP = 6, HL_T_COUNT = 8 };
+enum { HL_T_ENCODE = 0, HL_T_HASH = 1, HL_T_MERKLE = 2, HL_T_FOLD = 3, HL_T_GATHER = 4, HL_T_ROUNDS = 5, HL_T_LOGUP = 6, HL_T_TABLES = 7, HL_T_COUNT = 8 };
 typedef struct {
     double ms[HL_T_COUNT];        /* summed device time per family since the last reset */
     uint64_t spans[HL_T_COUNT];   /* timed spans per family (one span = the family's launches of one call) */

@@ -55,6 +55,15 @@ class FsState(C.Structure):
 SIGNATURES.update({
     "hl_b200_rounds_new": (_int, [_vp, _int, _sz, _u32, _u32, _vp, _vp, _sz, _pp]),
     "hl_b200_rounds_new_ir": (_int, [_vp, _sz, _u32, _u32, _vp, _vp, _sz, _u32, _u32, _vp, _sz, _pp]),
+    "hl_b200_tables_new": (_int, [_vp, _sz, _u32, _pp]),
+    "hl_b200_tables_put": (_int, [_vp, _sz, _vp]),
+    "hl_b200_tables_eq": (_int, [_vp, _sz, _u32, _u32, _vp, _vp, _int]),
+    "hl_b200_tables_plane": (_int, [_vp, _sz, _vp, _vp, _sz, _u64, _u32, _vp, _vp, _vp, _u32, _vp, _vp, _u32, _int]),
+    "hl_b200_tables_flush": (_int, [_vp]),
+    "hl_b200_tables_read": (_int, [_vp, _sz, _vp]),
+    "hl_b200_tables_free": (None, [_vp]),
+    "hl_b200_rounds_from_tables": (_int, [_vp, _int, _u32, _vp, _vp, _sz, _pp]),
+    "hl_b200_rounds_from_tables_ir": (_int, [_vp, _u32, _vp, _vp, _sz, _u32, _u32, _vp, _sz, _pp]),
     "hl_b200_rounds_round": (_int, [_vp, _u32, _int, _vp]),
     "hl_b200_rounds_fold": (_int, [_vp, _vp]),
     "hl_b200_rounds_finals": (_int, [_vp, _vp]),
@@ -75,7 +84,7 @@ SIGNATURES["hl_b200_butterfly_peak"] = (_int, [_vp, _u32, C.POINTER(C.c_double)]
 
 SIGNATURES["hl_b200_set_alloc_cap"] = (_int, [_vp, _sz])
 
-T_NAMES = ("encode", "hash", "merkle", "fold", "gather", "rounds", "logup")
+T_NAMES = ("encode", "hash", "merkle", "fold", "gather", "rounds", "logup", "tables")
 
 
 class Timing(C.Structure):

@@ -276,6 +276,110 @@ class B200Backend:
 POLY_PROD, POLY_ZC, POLY_LOGUP_Q, POLY_LOGUP_T = 0, 1, 2, 3
 
 
+_P = 0xFFFFFFFF00000001
+
+
+def _f2_mul(a, b):
+    return ((a[0] * b[0] + 7 * a[1] * b[1]) % _P, (a[0] * b[1] + a[1] * b[0]) % _P)
+
+
+def eq_table_msb(point) -> np.ndarray:
+    """The eq table of a point, first coordinate = most significant index bit (zkp-core/src/mle.rs:53-59): host logic of the
+    table plans, small (a half point or a plane's fixed coordinates)."""
+    e = [(1, 0)]
+    for r in point:
+        r = (int(r[0]), int(r[1]))
+        one_minus = ((1 - r[0]) % _P, (-r[1]) % _P)
+        e = [v for x in e for v in (_f2_mul(x, one_minus), _f2_mul(x, r))]
+    return np.array(e, dtype=np.uint64).reshape(-1, 2)
+
+
+def plane_maps(n_vars: int, coords):
+    """The index maps of a committed plane's table, as the host builder makes them (private_block/argument.rs:486-512):
+    `used` (cube variables the plane reads), the inverse bit map in two halves (cube index -> plane index, split at
+    xlo = n_vars / 2), the plane-index bits of every pattern z of the fixed coordinates (first fixed coordinate = most
+    significant bit of z) and the eq table of the fixed coordinates.  Coordinate j reads plane-index bit log - 1 - j."""
+    n, log = n_vars, len(coords)
+    bit_of, fpos, fixed = {}, [], []
+    for j, c in enumerate(coords):
+        if c[0] == "fixed":
+            fpos.append(log - 1 - j)
+            fixed.append(c[1])
+        else:
+            xb = n - 1 - c[1]
+            if xb in bit_of:
+                raise ValueError("plane_maps: a cube variable read by two coordinates (the host builder accumulates; not planned)")
+            bit_of[xb] = (log - 1 - j, 1 if c[0] == "flip" else 0)
+    used = sum(1 << b for b in bit_of)
+    xlo = n // 2
+
+    def inverse_half(shift, bits):
+        out = np.zeros(1 << bits, dtype=np.uint32)
+        v = np.arange(1 << bits, dtype=np.uint32)
+        for b in range(bits):
+            if shift + b in bit_of:
+                ib, flip = bit_of[shift + b]
+                out |= (((v >> np.uint32(b)) & np.uint32(1)) ^ np.uint32(flip)) << np.uint32(ib)
+        return out
+
+    inv_lo, inv_hi = inverse_half(0, xlo), inverse_half(xlo, n - xlo)
+    nf = len(fpos)
+    nz = (1 << nf) if nf else 0
+    zbits = np.array([sum(((z >> (nf - 1 - t)) & 1) << fpos[t] for t in range(nf)) for z in range(nz)], dtype=np.uint32)
+    eqf = eq_table_msb(fixed) if nf else None
+    return used, xlo, inv_lo, inv_hi, zbits, eqf
+
+
+class B200Tables:
+    """A slot's tables built on the device: the mirror of the reference's `MetalTables` (gpu/metal.rs: `new`, `tables_mut`,
+    `plan_eq`, `plan_plane`, `build_planned` / `flush`, `to_vecs`).  The index maps of a plane are made here, on the host,
+    exactly as the host builder makes them (private_block/argument.rs:486-512); the kernels only read them."""
+
+    def __init__(self, ctx: Context, k: int, n_vars: int):
+        self.ctx, self.k, self.n_vars = ctx, k, n_vars
+        h = C.c_void_p()
+        ctx.check(ctx.lib.hl_b200_tables_new(ctx.h, k, n_vars, C.byref(h)))
+        self.h = h
+
+    def put(self, i: int, words: np.ndarray) -> None:
+        words = _u64(words)
+        assert words.size == 2 << self.n_vars
+        self.ctx.check(self.ctx.lib.hl_b200_tables_put(self.h, i, _ptr(words)))
+
+    def plan_eq(self, i: int, point, start: int, base_check: bool = False) -> None:
+        """`Tab::Eq { point, start }`: eq(point, x[start .. start + |point|]) (argument.rs:643-660)"""
+        point = _u64(point).reshape(-1, 2)
+        p = point.shape[0]
+        p_lo = p // 2
+        hi, lo = eq_table_msb(point[: p - p_lo]), eq_table_msb(point[p - p_lo:])
+        self.ctx.check(self.ctx.lib.hl_b200_tables_eq(self.h, i, start, p, _ptr(hi), _ptr(lo), 1 if base_check else 0))
+
+    def plan_plane(self, i: int, rows, coords, slices, base_check: bool = False) -> None:
+        """`Tab::Priv`: a committed plane (argument.rs:386-577).  `rows`: a `B200Commit` (its resident data rows) or a
+        (device address, word count) pair; `coords`: the plane's coordinates, first = most significant index bit, each
+        ("rho", k) | ("flip", k) | ("fixed", (c0, c1)); `slices`: [(word offset, (c0, c1))]."""
+        used, xlo, inv_lo, inv_hi, zbits, eqf = plane_maps(self.n_vars, coords)
+        nz = zbits.size
+        sl = np.array([[off, cf[0], cf[1]] for off, cf in slices], dtype=np.uint64)
+        store, d_rows, n_words = (rows.h, None, 0) if isinstance(rows, B200Commit) else (None, C.c_void_p(rows[0]), rows[1])
+        self.ctx.check(self.ctx.lib.hl_b200_tables_plane(self.h, i, store, d_rows, n_words, used, xlo, _ptr(inv_lo), _ptr(inv_hi),
+                                                         _ptr(zbits) if nz else None, nz, _ptr(eqf) if nz else None, _ptr(sl), sl.shape[0],
+                                                         1 if base_check else 0))
+
+    def flush(self) -> None:
+        self.ctx.check(self.ctx.lib.hl_b200_tables_flush(self.h))
+
+    def read(self, i: int) -> np.ndarray:
+        out = np.zeros((1 << self.n_vars, 2), dtype=np.uint64)
+        self.ctx.check(self.ctx.lib.hl_b200_tables_read(self.h, i, _ptr(out)))
+        return out
+
+    def free(self) -> None:
+        if self.h:
+            self.ctx.lib.hl_b200_tables_free(self.h)
+            self.h = None
+
+
 class SlotProgram:
     """A slot polynomial as data: the grammar of the reference's slot expression graph (private_block/slot_ir.rs:57-345:
     `TableRef`, `Node` with `NodeBody::{Affine, Sum}`, `SlotTerm`), flattened into the word stream the C ABI takes
@@ -346,14 +450,27 @@ class B200Rounds:
     device-side batch of rounds the reference's Metal evaluator runs (metal.rs:4141 ``masked_prove``)."""
 
     def __init__(self, ctx: Context, poly, tables: np.ndarray, degree: int, coefs=None):
-        """`poly`: one of the POLY_* families, or a `SlotProgram` (any slot polynomial, as data)."""
+        """`poly`: one of the POLY_* families, or a `SlotProgram` (any slot polynomial, as data).  `tables`: (k, 2^n, 2) host
+        words, or a `B200Tables` set built on the device (taken over: `metal_rounds_owned`, gpu/metal.rs:2804)."""
+        self._degree = degree
+        h = C.c_void_p()
+        if isinstance(tables, B200Tables):
+            self.ctx, self.k, self._n_vars = ctx, tables.k, tables.n_vars
+            if isinstance(poly, SlotProgram):
+                w, cf = poly.words(), poly.coef_array()
+                ctx.check(ctx.lib.hl_b200_rounds_from_tables_ir(ctx.h, degree, tables.h, w.ctypes.data_as(C.c_void_p), w.size, poly.n_nodes,
+                                                                poly.n_terms, _ptr(cf) if cf.size else None, cf.shape[0], C.byref(h)))
+            else:
+                cf = _u64(coefs).reshape(-1, 2) if coefs is not None else None
+                ctx.check(ctx.lib.hl_b200_rounds_from_tables(ctx.h, poly, degree, tables.h, _ptr(cf), 0 if cf is None else cf.shape[0], C.byref(h)))
+            tables.free()
+            self.h = h
+            return
         tables = _u64(tables)
         assert tables.ndim == 3 and tables.shape[2] == 2
         self.ctx, self.k = ctx, tables.shape[0]
         self._n_vars = int(tables.shape[1]).bit_length() - 1
         assert tables.shape[1] == 1 << self._n_vars
-        self._degree = degree
-        h = C.c_void_p()
         if isinstance(poly, SlotProgram):
             assert poly.n_tables == self.k
             w, cf = poly.words(), poly.coef_array()

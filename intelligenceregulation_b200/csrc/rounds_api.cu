@@ -8,6 +8,11 @@
 
 using namespace hlapi;
 
+struct hl_tables;
+u64* hl_tables_adopt(hl_tables* t);        // tables.cu: hands the device tables over (the set is empty afterwards)
+int hl_tables_flush_locked(hl_tables* t);  // waits for the builders; refuses a base-declared table with an extension word
+void hl_tables_shape(hl_tables* t, hl_ctx** c, size_t* k, uint32_t* n_vars);
+
 struct hl_rounds {
     hl_ctx* ctx = nullptr;
     int poly = 0;
@@ -29,7 +34,7 @@ namespace {
 
 void free_rounds(hl_rounds* r) {
     hl_ctx* c = r->ctx;
-    dev_free(c, r->d_tables, r->k * r->stride * 16);
+    if (r->d_tables) dev_free(c, r->d_tables, r->k * r->stride * 16);
     dev_free(c, r->d_coefs, (r->ncoefs ? r->ncoefs : 1) * 16);
     dev_free(c, r->d_partials, (size_t)r->max_blocks * (r->degree + 1) * 16);
     dev_free(c, r->d_out, (r->n_vars ? r->n_vars : 1) * r->out_row() * 8);
@@ -80,9 +85,12 @@ namespace {
 
 // the evaluator of either kind; `words` is the data form of the polynomial when poly == POLY_IR
 int rounds_build(hl_ctx* c, int poly, size_t k, uint32_t n_vars, uint32_t degree, const uint64_t* tables, const uint64_t* coefs,
-                 size_t ncoefs, const std::vector<u32>* plan, hl_rounds** out) {
+                 size_t ncoefs, const std::vector<u32>* plan, hl_rounds** out, hl_tables* built = nullptr) {
     std::lock_guard<std::mutex> g(c->mu);
     cudaSetDevice(c->device);
+    if (built) {
+        if (int rc = hl_tables_flush_locked(built)) return rc;
+    }
     hl_rounds* r = new hl_rounds();
     r->ctx = c; r->poly = poly; r->k = (u32)k; r->n_vars = n_vars; r->degree = degree; r->ncoefs = ncoefs;
     r->stride = r->len = (size_t)1 << n_vars;
@@ -106,13 +114,13 @@ int rounds_build(hl_ctx* c, int poly, size_t k, uint32_t n_vars, uint32_t degree
             if (j != i) den = gl_mul(den, gl_from_i64((long long)i - (long long)j));
         inv_den[i] = gl_inv(den);
     }
-    int rc = dev_alloc(c, (void**)&r->d_tables, k * r->stride * 16);
+    int rc = built ? HL_B200_OK : dev_alloc(c, (void**)&r->d_tables, k * r->stride * 16);
     if (!rc) rc = dev_alloc(c, (void**)&r->d_coefs, (ncoefs ? ncoefs : 1) * 16);
     if (!rc) rc = dev_alloc(c, (void**)&r->d_partials, (size_t)r->max_blocks * (degree + 1) * 16);
     if (!rc) rc = dev_alloc(c, (void**)&r->d_out, (n_vars ? n_vars : 1) * r->out_row() * 8);
     if (!rc) rc = dev_alloc(c, (void**)&r->d_inv_den, ((size_t)degree + 1) * 8);
     if (!rc) rc = dev_alloc(c, (void**)&r->d_state, sizeof(hlk::ScState));
-    if (!rc) rc = h2d(c, r->d_tables, tables, k * r->stride * 16);
+    if (!rc && !built) rc = h2d(c, r->d_tables, tables, k * r->stride * 16);
     if (!rc && ncoefs) rc = h2d(c, r->d_coefs, coefs, ncoefs * 16);
     if (!rc) rc = h2d(c, r->d_inv_den, inv_den, ((size_t)degree + 1) * 8);
     if (!rc && poly == hlk::POLY_IR) {
@@ -127,6 +135,7 @@ int rounds_build(hl_ctx* c, int poly, size_t k, uint32_t n_vars, uint32_t degree
     }
     if (!rc) rc = sync(c, "rounds_new");
     if (rc) { cudaStreamSynchronize(c->stream); free_rounds(r); return rc; }
+    if (built) r->d_tables = hl_tables_adopt(built);  // only now: a failed build leaves the set with its owner
     *out = r;
     return HL_B200_OK;
 }
@@ -164,6 +173,36 @@ int hl_b200_rounds_new_ir(hl_ctx* c, size_t k, uint32_t n_vars, uint32_t degree,
         return fail(c, HL_B200_ERR_UNSUPPORTED, buf);
     }
     return rounds_build(c, hlk::POLY_IR, k, n_vars, degree, tables, coefs, ncoefs, &plan, out);
+}
+
+int hl_b200_rounds_from_tables(hl_ctx* c, int poly, uint32_t degree, hl_tables* t, const uint64_t* coefs, size_t ncoefs, hl_rounds** out) {
+    if (!c || !t || !out) return fail(c, HL_B200_ERR_ARG, "rounds_from_tables: null argument");
+    hl_ctx* tc = nullptr;
+    size_t k = 0;
+    uint32_t n_vars = 0;
+    hl_tables_shape(t, &tc, &k, &n_vars);
+    if (tc != c || k == 0) return fail(c, HL_B200_ERR_ARG, "rounds_from_tables: the table set is empty or belongs to another context");
+    if (poly == hlk::POLY_IR) return fail(c, HL_B200_ERR_ARG, "rounds_from_tables: a data-form polynomial goes through rounds_from_tables_ir");
+    if (!hlk::sc_supported(poly, (int)k, (int)degree)) return fail(c, HL_B200_ERR_UNSUPPORTED, "rounds_from_tables: polynomial family / table count / degree");
+    if ((poly == hlk::POLY_LOGUP_Q || poly == hlk::POLY_LOGUP_T) && (!coefs || ncoefs < 1)) return fail(c, HL_B200_ERR_ARG, "rounds_from_tables: alpha missing");
+    return rounds_build(c, poly, k, n_vars, degree, nullptr, coefs, ncoefs, nullptr, out, t);
+}
+
+int hl_b200_rounds_from_tables_ir(hl_ctx* c, uint32_t degree, hl_tables* t, const uint32_t* words, size_t n_words, uint32_t n_nodes,
+                                  uint32_t n_terms, const uint64_t* coefs, size_t ncoefs, hl_rounds** out) {
+    if (!c || !t || !words || !out || (ncoefs && !coefs)) return fail(c, HL_B200_ERR_ARG, "rounds_from_tables_ir: null argument");
+    hl_ctx* tc = nullptr;
+    size_t k = 0;
+    uint32_t n_vars = 0;
+    hl_tables_shape(t, &tc, &k, &n_vars);
+    if (tc != c || k == 0) return fail(c, HL_B200_ERR_ARG, "rounds_from_tables_ir: the table set is empty or belongs to another context");
+    if (!hlk::sc_supported(hlk::POLY_IR, (int)k, (int)degree) || n_words > ir::MAX_WORDS || n_nodes > ir::MAX_NODES || ncoefs > ir::MAX_COEFS)
+        return fail(c, HL_B200_ERR_UNSUPPORTED, "rounds_from_tables_ir: table count, degree or program size beyond the evaluator's limits");
+    ir::Shape sh{(u32)k, n_nodes, n_terms, (u32)ncoefs, (u32)n_words};
+    if (ir::validate(sh, words)) return fail(c, HL_B200_ERR_ARG, "rounds_from_tables_ir: malformed program");
+    std::vector<u32> plan;
+    if (ir::build_plan(sh, words, plan)) return fail(c, HL_B200_ERR_UNSUPPORTED, "rounds_from_tables_ir: the program does not fit the evaluator's plan");
+    return rounds_build(c, hlk::POLY_IR, k, n_vars, degree, nullptr, coefs, ncoefs, &plan, out, t);
 }
 
 void hl_b200_rounds_free(hl_rounds* r) {

@@ -74,6 +74,11 @@ uint64_t or_rng_fp(or_rng *r);
 void or_rng_fill_fp(or_rng *r, uint64_t *out, size_t n);
 void or_rng_bytes32(or_rng *r, uint8_t out[32]);
 
+/* ---- tables.c (private_block/argument.rs host table builders) ---- */
+void or_eq_cube(const uint64_t *point, size_t p, size_t n_vars, size_t start, uint64_t *out);
+void or_priv_table(const int32_t *kind, const uint32_t *var, const uint64_t *fixed, size_t log,
+                   const uint64_t *slices, size_t ns, const uint64_t *data, size_t n_vars, uint64_t *out);
+
 /* ---- sumcheck.c (mle.rs, sumcheck.rs, sumcheck/rounds.rs) ---- */
 void or_eq_table(const uint64_t *r, size_t n, uint64_t *out);
 void or_eq_table_msb(const uint64_t *r, size_t n, uint64_t *out);

@@ -408,6 +408,28 @@ def fold_cols_i8(m: np.ndarray, c: np.ndarray) -> np.ndarray:
     return out
 
 
+def eq_cube(point: np.ndarray, n_vars: int, start: int) -> np.ndarray:
+    """argument.rs:586-627 over eq_table_msb(point); (2^n_vars, 2)"""
+    point = _u64(point).reshape(-1, 2)
+    out = np.zeros((1 << n_vars, 2), dtype=np.uint64)
+    _lib.or_eq_cube(_p(point), C.c_size_t(point.shape[0]), C.c_size_t(n_vars), C.c_size_t(start), _p(out))
+    return out
+
+
+def priv_table(coords, slices, data: np.ndarray, n_vars: int) -> np.ndarray:
+    """argument.rs:386-577 priv_table_fill (walked form).  coords: list of ("rho", k) / ("flip", k) / ("fixed", (c0, c1));
+    slices: list of (offset, (c0, c1)); data: the committed rows, flat."""
+    kind = np.array([{"rho": 0, "flip": 1, "fixed": 2}[c[0]] for c in coords], dtype=np.int32)
+    var = np.array([c[1] if c[0] != "fixed" else 0 for c in coords], dtype=np.uint32)
+    fx = np.array([c[1] for c in coords if c[0] == "fixed"], dtype=np.uint64).reshape(-1, 2)
+    sl = np.array([[off, cf[0], cf[1]] for off, cf in slices], dtype=np.uint64)
+    data = _u64(data)
+    out = np.zeros((1 << n_vars, 2), dtype=np.uint64)
+    _lib.or_priv_table(_p(kind), _p(var), _p(fx) if fx.size else None, C.c_size_t(len(coords)), _p(sl), C.c_size_t(sl.shape[0]), _p(data),
+                       C.c_size_t(n_vars), _p(out))
+    return out
+
+
 POLY_PROD, POLY_ZC, POLY_LOGUP_Q, POLY_LOGUP_T, POLY_IR = 0, 1, 2, 3, 4
 
 _ir_keep = None
