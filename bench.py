@@ -223,10 +223,27 @@ def device_extras(dev, backend, np_data, np_pads, np_pows, col_key) -> dict:
     st.free()
     # the heaviest slot polynomial of a block as data: the recorded structure of the D zero-check (60 tables, 71 nodes,
     # declared degree 5) with seeded coefficients, at 2^17 points, through the interpreting evaluator
+    prog, deg = slot14_program(backend.SlotProgram)
+    n = 17
+    tables = splitmix_fp(87, prog.n_tables * (1 << n) * 2).reshape(prog.n_tables, 1 << n, 2)
+    mask = splitmix_fp(88, ((n + 1) * deg + 2) * 2).reshape(-1, 2)
+    for rep in range(3):
+        ev = backend.B200Rounds(ctx, prog, tables, deg)
+        if rep == 1:
+            ctx.timing_read(reset=True)
+        ev.batched(n, bytes(32), 0, None, mask=mask, mask_vars=n + 1, mask_c=(3, 5), recover_one=True, claim=(0, 0))
+        ev.free()
+    t = ctx.timing_read(reset=True)
+    out["sumcheck_slot_program_60tables_71nodes_deg5_2^17_ms"] = t["rounds"][0] / 2
+    ctx.timing_enable(False)
+    return out
+
+
+def slot14_program(SP):
+    """the recorded structure of the D zero-check (60 tables, 71 nodes, declared degree 5) with seeded coefficients"""
     import json as _json
 
     slot = _json.load(open(os.path.join(ROOT, "tests", "golden", "slot_ir_m125.json")))["slots"][14]
-    SP = backend.SlotProgram
     prog, cs = SP(len(slot["table_fields"])), iter(splitmix_fp(86, 4096).tolist())
 
     def coef(cls):
@@ -242,19 +259,49 @@ def device_extras(dev, backend, np_data, np_pads, np_pows, col_key) -> dict:
             prog.sum([(coef(c), [fw(f) for f in fs]) for c, fs in nd["sum"]])
     for t in slot["terms"]:
         prog.term(coef(t["coef"]), t["wrapper"], [fw(f) for f in t["inner"]])
-    n = 17
-    tables = splitmix_fp(87, prog.n_tables * (1 << n) * 2).reshape(prog.n_tables, 1 << n, 2)
-    deg = slot["declared_degree"]
-    mask = splitmix_fp(88, ((n + 1) * deg + 2) * 2).reshape(-1, 2)
-    for rep in range(3):
-        ev = backend.B200Rounds(ctx, prog, tables, deg)
-        if rep == 1:
-            ctx.timing_read(reset=True)
-        ev.batched(n, bytes(32), 0, None, mask=mask, mask_vars=n + 1, mask_c=(3, 5), recover_one=True, claim=(0, 0))
-        ev.free()
-    t = ctx.timing_read(reset=True)
-    out["sumcheck_slot_program_60tables_71nodes_deg5_2^17_ms"] = t["rounds"][0] / 2
-    ctx.timing_enable(False)
+    return prog, slot["declared_degree"]
+
+
+def cpu_extras(o, backend, np_data) -> dict:
+    """The same operations as `device_extras` on the host cores through the CPU restatement (OpenMP where the reference
+    uses rayon), each on the sample named in its key's note; milliseconds scaled to the full operation."""
+    w = WORK
+    n, rows = 1 << w["log_cols"], w["rows"]
+    out, notes = {}, {}
+
+    def timed(f):
+        t0 = time.perf_counter()
+        f()
+        return (time.perf_counter() - t0) * 1e3
+
+    rhos = splitmix_fp(77, 4 * rows * 2).reshape(4, rows, 2)
+    out["open_A_fold_38rho_ms"] = timed(lambda: o.fold_rows(np_data, rows, n, n, 1, rhos)) * 38 / 4
+    notes["open_A_fold_38rho_ms"] = "4 of 38 vectors over the message columns, scaled"
+    nv = 21
+    tables = splitmix_fp(79, 3 * (1 << nv) * 2).reshape(3, 1 << nv, 2)
+    alpha = splitmix_fp(80, 2).reshape(1, 2)
+    mask = splitmix_fp(81, ((nv + 1) * 3 + 2) * 2).reshape(-1, 2)
+    out["sumcheck_logup_q_2^21_deg3_21rounds_ms"] = timed(lambda: o.sc_prove(o.POLY_LOGUP_Q, tables, 3, o.Transcript(b"bench"), coefs=alpha, mask=mask,
+                                                                             mask_c=(3, 5), mask_vars=nv + 1, recover_one=True, claim=(0, 0)))
+    nq = 1 << 21
+    qidx = (splitmix_fp(82, nq) % np.uint64(1 << 16)).astype(np.int32)
+    qout = (splitmix_fp(83, nq) % np.uint64(1 << 15)).astype(np.int32)
+    out["logup_helpers_2^21_ms"] = timed(lambda: o.logup_helpers(qidx, qout, (11, 12), (13, 14), (15, 16)))
+    wm = (splitmix_fp(84, 4096 * 14336) % np.uint64(256)).astype(np.uint8).view(np.int8).reshape(4096, 14336)
+    cw = splitmix_fp(85, 14336 * 2).reshape(14336, 2)
+    out["fold_cols_i8_4096x14336_ms"] = timed(lambda: o.fold_cols_i8(wm, cw))
+    point = splitmix_fp(90, 21 * 2).reshape(21, 2)
+    coords = [("fixed", (int(a), int(b))) for a, b in splitmix_fp(91, 6).reshape(3, 2)] + [("rho", k) for k in range(19)]
+    out["tables_eq_2^21_plus_plane_2^19_x8_ms"] = timed(lambda: (o.eq_cube(point, 21, 0), o.priv_table(coords, [(0, (1, 0))], np_data, 19)))
+    notes["tables_eq_2^21_plus_plane_2^19_x8_ms"] = "walked host builder, one thread"
+    prog, deg = slot14_program(backend.SlotProgram)
+    nv = 17
+    tables = splitmix_fp(87, prog.n_tables * (1 << nv) * 2).reshape(prog.n_tables, 1 << nv, 2)
+    mask = splitmix_fp(88, ((nv + 1) * deg + 2) * 2).reshape(-1, 2)
+    o.ir_set(prog.words(), prog.n_nodes, prog.n_terms)
+    out["sumcheck_slot_program_60tables_71nodes_deg5_2^17_ms"] = timed(lambda: o.sc_prove(o.POLY_IR, tables, deg, o.Transcript(b"bench"), coefs=prog.coef_array(),
+                                                                                          mask=mask, mask_c=(3, 5), mask_vars=nv + 1, recover_one=True, claim=(0, 0)))
+    out["notes"] = notes
     return out
 
 
@@ -373,6 +420,18 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     s1 = dev.ctx.stats()
     assert bytes(levels[-1]) == root_resident, "the two legs disagree on the root"
 
+    # what the upload alone costs on this box: the same pinned buffers, one copy each, nothing else on the device
+    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    d_data.copy_(h_data, non_blocking=True)
+    torch.cuda.synchronize()
+    c0.record(stream)
+    for _ in range(5):
+        d_data.copy_(h_data, non_blocking=True)
+        d_pads.copy_(h_pads, non_blocking=True)
+    c1.record(stream)
+    torch.cuda.synchronize()
+    h2d_only_ms = c0.elapsed_time(c1) / 5
+
     enc_bytes = rows * nn * 8
     value = world * enc_bytes * args.steps / (ms * 1e-3) / 1e9
     e2e_v = world * enc_bytes * args.steps / e2e_s / 1e9
@@ -406,6 +465,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     bfly_peak = dev.ctx.butterfly_peak(400)
     bfly_per_launch = rows * (1 + ir) * (n // 2) * log_cols
     extras = device_extras(dev, backend, np_data, np_pads, np_pows, col_key) if (world == 1 and rank == 0 and not args.no_extras) else None
+    extras_cpu = cpu_extras(o, backend, np_data) if extras is not None else None
 
     if rank == 0:
         line = {
@@ -413,7 +473,8 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": value / world / PUBLISHED_GBPS if world == 1 else None,
             "dtype": "u64", "data": "synthetic", "config": workload_config(world),
             "e2e": {"value": e2e_v, "unit": "GB/s", "h2d_bytes_per_step": (s1["bytes_h2d"] - s0["bytes_h2d"]) // args.steps,
-                    "d2h_bytes_per_step": (s1["bytes_d2h"] - s0["bytes_d2h"]) // args.steps, "ms_per_step": e2e_s * 1e3 / args.steps},
+                    "d2h_bytes_per_step": (s1["bytes_d2h"] - s0["bytes_d2h"]) // args.steps, "ms_per_step": e2e_s * 1e3 / args.steps,
+                    "h2d_only_ms": h2d_only_ms},
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": {"bound": "hbm", "kernel": "k_encode_fast<14,1024>", "achieved": achieved, "peak": peak,
@@ -426,6 +487,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             "kernel_ms_per_step": {"encode": enc_ms, "column_hash": hash_ms, "salt_and_tree": mer_ms},
             "cpu_baseline": cpu,
             "other_kernels_device_ms": extras,
+            "other_kernels_cpu_ms": extras_cpu,
             "root": root_resident.hex(),
         }
         print(json.dumps(line))
