@@ -33,10 +33,12 @@ int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* 
     rc = upload_key(c, key32, &d_key);
     if (!rc) rc = dev_alloc(c, (void**)&scratch, scratch_words * 8);
     if (!rc && cvs_bytes) rc = dev_alloc(c, (void**)&cvs, cvs_bytes);
-    // row chunks: two rows per SM per chunk keeps every encoder launch a whole number of waves
+    // row pieces of 256 rows = two 1 KiB hash chunks per column: a piece is encoded and its chunk values are hashed while
+    // the next piece is still on the bus, so that only the last piece (at most one wave of the encoder) follows the upload
     const size_t row_bytes = n * 8;
     u32 chunk = st->rows;
-    if (h_data && (size_t)st->rows * row_bytes >= ((size_t)32 << 20) && st->rows > 4u * (u32)c->sm_count) chunk = 2u * (u32)c->sm_count;
+    if (h_data && (size_t)st->rows * row_bytes >= ((size_t)32 << 20) && st->rows > 4u * (u32)c->sm_count) chunk = 256;
+    const bool pieces = chunk < st->rows;
     if (!rc && h_data && chunk < st->rows) {
         // the copy stream may touch the fresh allocations only after the main stream has made them
         cudaError_t e = cudaEventRecord(c->ev_main, c->stream);
@@ -46,8 +48,10 @@ int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* 
     if (!rc) {
         Timed t(c, HL_T_ENCODE);
         size_t ev_i = 0;
-        for (u32 r0 = 0; r0 < st->rows && !rc; r0 += chunk) {
-            const u32 nr = st->rows - r0 < chunk ? st->rows - r0 : chunk;
+        u32 nr = 0;
+        for (u32 r0 = 0; r0 < st->rows && !rc; r0 += nr) {
+            nr = st->rows - r0 < chunk ? st->rows - r0 : chunk;
+            if (pieces && r0 + nr == st->rows && nr > 128 && nr > (u32)c->sm_count) nr = 128;  // leave one wave or less for the end
             if (h_data) {
                 cudaStream_t cs = chunk < st->rows ? c->copy_stream : c->stream;
                 cudaError_t e = cudaMemcpyAsync(st->d_data + (size_t)r0 * n, h_data + (size_t)r0 * n, (size_t)nr * row_bytes, cudaMemcpyHostToDevice, cs);
@@ -73,9 +77,21 @@ int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* 
             cudaError_t e = hlk::encode_rows(a, logb, c->fast_encoder || loga, c->sm_count, scratch_words, c->stream, &st->encoder_path);
             c->stats.kernel_launches += 1;
             if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "row encoder launch", e);
+            if (!rc && pieces) {  // the hash chunks this piece completed (pieces start on multiples of 128 rows)
+                const u32 c0 = r0 / 128u, c1 = r0 + nr == st->rows ? nchunks : (r0 + nr) / 128u;
+                e = hlk::hash_column_chunks(st->d_enc, st->rows, (u32)nn, d_key, c0, c1 - c0, cvs, st->d_leaves, c->stream);
+                c->stats.kernel_launches += 1;
+                if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "column hash launch", e);
+            }
         }
     }
-    if (!rc) {
+    if (!rc && pieces) {
+        Timed t(c, HL_T_HASH);
+        cudaError_t e = hlk::hash_column_merge(st->rows, (u32)nn, d_key, cvs, st->d_leaves, c->stream);
+        c->stats.kernel_launches += 1;
+        if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "column hash merge launch", e);
+    }
+    if (!rc && !pieces) {
         Timed t(c, HL_T_HASH);
         cudaError_t e = hlk::hash_columns(st->d_enc, st->rows, (u32)nn, d_key, cvs, st->d_leaves, c->stream);
         c->stats.kernel_launches += nchunks > 1 ? 2 : 1;

@@ -15,9 +15,9 @@
 namespace {
 
 __global__ void __launch_bounds__(128) k_hash_col_chunks(const u64* __restrict__ enc, u32 rows, u32 nn,
-                                                         const uint32_t* __restrict__ key, u32 nchunks,
+                                                         const uint32_t* __restrict__ key, u32 nchunks, u32 chunk0,
                                                          uint32_t* __restrict__ cvs, uint32_t* __restrict__ leaves) {
-    const u32 col = blockIdx.x * blockDim.x + threadIdx.x, chunk = blockIdx.y;
+    const u32 col = blockIdx.x * blockDim.x + threadIdx.x, chunk = chunk0 + blockIdx.y;
     if (col >= nn) return;
     const u32 r0 = chunk * 128u, r1 = min(rows, r0 + 128u);
     const u32 nb = (r1 - r0 + 7u) / 8u;
@@ -134,11 +134,23 @@ u32 hash_chunks(u32 rows) { return (rows + 127u) / 128u; }
 cudaError_t hash_columns(const u64* enc, u32 rows, u32 nn, const uint32_t* d_key, uint32_t* d_cvs, uint32_t* d_leaves,
                          cudaStream_t st) {
     const u32 nchunks = hash_chunks(rows);
-    dim3 grid((nn + 127u) / 128u, nchunks);
-    k_hash_col_chunks<<<grid, 128, 0, st>>>(enc, rows, nn, d_key, nchunks, d_cvs, d_leaves);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = hash_column_chunks(enc, rows, nn, d_key, 0, nchunks, d_cvs, d_leaves, st);
     if (e != cudaSuccess || nchunks == 1) return e;
-    k_hash_col_merge<<<(nn + 127u) / 128u, 128, 0, st>>>(d_cvs, nn, nchunks, d_key, d_leaves);
+    return hash_column_merge(rows, nn, d_key, d_cvs, d_leaves, st);
+}
+
+// the chunk values of the 1 KiB chunks [chunk0, chunk0 + count) of every column (rows 128 chunk0 .. of the encoding
+// must be complete); a commitment whose rows arrive in pieces hashes each piece as soon as it is encoded
+cudaError_t hash_column_chunks(const u64* enc, u32 rows, u32 nn, const uint32_t* d_key, u32 chunk0, u32 count, uint32_t* d_cvs,
+                               uint32_t* d_leaves, cudaStream_t st) {
+    if (count == 0) return cudaSuccess;
+    dim3 grid((nn + 127u) / 128u, count);
+    k_hash_col_chunks<<<grid, 128, 0, st>>>(enc, rows, nn, d_key, hash_chunks(rows), chunk0, d_cvs, d_leaves);
+    return cudaGetLastError();
+}
+
+cudaError_t hash_column_merge(u32 rows, u32 nn, const uint32_t* d_key, const uint32_t* d_cvs, uint32_t* d_leaves, cudaStream_t st) {
+    k_hash_col_merge<<<(nn + 127u) / 128u, 128, 0, st>>>(d_cvs, nn, hash_chunks(rows), d_key, d_leaves);
     return cudaGetLastError();
 }
 

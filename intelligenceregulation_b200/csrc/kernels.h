@@ -13,6 +13,9 @@ cudaError_t encode_rows(const enc::RowArgs& a, u32 logn, bool allow_fast, int sm
 
 // hash.cu
 u32 hash_chunks(u32 rows);
+cudaError_t hash_column_chunks(const u64* enc, u32 rows, u32 nn, const uint32_t* d_key, u32 chunk0, u32 count, uint32_t* d_cvs,
+                               uint32_t* d_leaves, cudaStream_t st);
+cudaError_t hash_column_merge(u32 rows, u32 nn, const uint32_t* d_key, const uint32_t* d_cvs, uint32_t* d_leaves, cudaStream_t st);
 cudaError_t hash_columns(const u64* enc, u32 rows, u32 nn, const uint32_t* d_key, uint32_t* d_cvs, uint32_t* d_leaves,
                          cudaStream_t st);
 cudaError_t salt_leaves(const uint32_t* d_leaves, const uint32_t* d_salts, u32 nn, const uint32_t* d_leaf_key,
