@@ -222,9 +222,9 @@ def device_extras(dev, backend, np_data, np_pads, np_pows, col_key) -> dict:
     out["tables_eq_2^21_plus_plane_2^19_x8_ms"] = t["tables"][0] / 2
     st.free()
     # the heaviest slot polynomial of a block as data: the recorded structure of the D zero-check (60 tables, 71 nodes,
-    # declared degree 5) with seeded coefficients, at 2^17 points, through the interpreting evaluator
+    # declared degree 5) with seeded coefficients, at 2^19 points (the 8B block domain of this slot: 128 tokens x width 4096), through the interpreting evaluator
     prog, deg = slot14_program(backend.SlotProgram)
-    n = 17
+    n = 19
     tables = splitmix_fp(87, prog.n_tables * (1 << n) * 2).reshape(prog.n_tables, 1 << n, 2)
     mask = splitmix_fp(88, ((n + 1) * deg + 2) * 2).reshape(-1, 2)
     for rep in range(3):
@@ -234,7 +234,7 @@ def device_extras(dev, backend, np_data, np_pads, np_pows, col_key) -> dict:
         ev.batched(n, bytes(32), 0, None, mask=mask, mask_vars=n + 1, mask_c=(3, 5), recover_one=True, claim=(0, 0))
         ev.free()
     t = ctx.timing_read(reset=True)
-    out["sumcheck_slot_program_60tables_71nodes_deg5_2^17_ms"] = t["rounds"][0] / 2
+    out["sumcheck_slot_program_60tables_71nodes_deg5_2^19_ms"] = t["rounds"][0] / 2
     ctx.timing_enable(False)
     return out
 
@@ -295,11 +295,11 @@ def cpu_extras(o, backend, np_data) -> dict:
     out["tables_eq_2^21_plus_plane_2^19_x8_ms"] = timed(lambda: (o.eq_cube(point, 21, 0), o.priv_table(coords, [(0, (1, 0))], np_data, 19)))
     notes["tables_eq_2^21_plus_plane_2^19_x8_ms"] = "walked host builder, one thread"
     prog, deg = slot14_program(backend.SlotProgram)
-    nv = 17
+    nv = 19
     tables = splitmix_fp(87, prog.n_tables * (1 << nv) * 2).reshape(prog.n_tables, 1 << nv, 2)
     mask = splitmix_fp(88, ((nv + 1) * deg + 2) * 2).reshape(-1, 2)
     o.ir_set(prog.words(), prog.n_nodes, prog.n_terms)
-    out["sumcheck_slot_program_60tables_71nodes_deg5_2^17_ms"] = timed(lambda: o.sc_prove(o.POLY_IR, tables, deg, o.Transcript(b"bench"), coefs=prog.coef_array(),
+    out["sumcheck_slot_program_60tables_71nodes_deg5_2^19_ms"] = timed(lambda: o.sc_prove(o.POLY_IR, tables, deg, o.Transcript(b"bench"), coefs=prog.coef_array(),
                                                                                           mask=mask, mask_c=(3, 5), mask_vars=nv + 1, recover_one=True, claim=(0, 0)))
     out["notes"] = notes
     return out

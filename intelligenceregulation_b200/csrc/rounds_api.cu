@@ -99,10 +99,9 @@ int rounds_build(hl_ctx* c, int poly, size_t k, uint32_t n_vars, uint32_t degree
         const std::vector<u32>& pw = *plan;
         r->ir.plan_words = (u32)pw.size(); r->ir.n_coefs = (u32)ncoefs; r->ir.n_tables = (u32)k;
         r->ir.n_nodes = pw[1]; r->ir.n_units = pw[2];
-        const u32 *lvl = pw.data() + pw[3], *nus = pw.data() + pw[5];
-        for (u32 l = 0; l < pw[0]; l++) {
-            const u32 nu = nus[lvl[l + 1]] - nus[lvl[l]];
-            if (nu > r->ir.max_level_units) r->ir.max_level_units = nu;
+        if (!hlk::sc_ir_fits(r->ir, (int)degree)) {
+            delete r;
+            return fail(c, HL_B200_ERR_UNSUPPORTED, "slot program: tables x nodes x points beyond one CTA's shared memory");
         }
         r->max_blocks = hlk::sc_ir_max_blocks((u32)(r->len / 2), c->sm_count);
         r->tail_len = hlk::sc_ir_tail_len(r->ir, (int)degree);
@@ -167,7 +166,7 @@ int hl_b200_rounds_new_ir(hl_ctx* c, size_t k, uint32_t n_vars, uint32_t degree,
         return fail(c, HL_B200_ERR_ARG, buf);
     }
     std::vector<u32> plan;
-    if (int why = ir::build_plan(sh, words, plan)) {
+    if (int why = ir::build_plan(sh, words, ir::PLAN_UNIT_BUF / (degree + 1), plan)) {
         char buf[96];
         snprintf(buf, sizeof buf, "rounds_new_ir: the program does not fit the evaluator's plan (reason %d)", why);
         return fail(c, HL_B200_ERR_UNSUPPORTED, buf);
@@ -201,7 +200,7 @@ int hl_b200_rounds_from_tables_ir(hl_ctx* c, uint32_t degree, hl_tables* t, cons
     ir::Shape sh{(u32)k, n_nodes, n_terms, (u32)ncoefs, (u32)n_words};
     if (ir::validate(sh, words)) return fail(c, HL_B200_ERR_ARG, "rounds_from_tables_ir: malformed program");
     std::vector<u32> plan;
-    if (ir::build_plan(sh, words, plan)) return fail(c, HL_B200_ERR_UNSUPPORTED, "rounds_from_tables_ir: the program does not fit the evaluator's plan");
+    if (ir::build_plan(sh, words, ir::PLAN_UNIT_BUF / (degree + 1), plan)) return fail(c, HL_B200_ERR_UNSUPPORTED, "rounds_from_tables_ir: the program does not fit the evaluator's plan");
     return rounds_build(c, hlk::POLY_IR, k, n_vars, degree, nullptr, coefs, ncoefs, &plan, out, t);
 }
 

@@ -131,23 +131,36 @@ inline int validate(const Shape& s, const u32* w) {
 // ---------------------------------------------------------------------------------------------
 // The evaluation plan: the same graph regrouped for the kernels.  Every node becomes a sum of UNITS
 // (coef * prod(factors); an affine term is a unit with one table factor, its constant a unit with none),
-// the top-level terms become the units of one more node (id n_nodes) whose value is the polynomial, and
-// the nodes are ordered by LEVEL (a node's level is one more than the highest level it refers to), so
-// that all units of a level are independent: a thread walks them in order, a warp takes one unit per lane.
+// the top-level terms become the units of one more node (id n_nodes) whose value is the polynomial.
+// Node order: the affine nodes first, then the others by LEVEL (one more than the highest level a node
+// refers to), so that a single pass over the order is a valid evaluation and all units of a level are
+// independent.
 //
-//   pw[0] levels  pw[1] nodes (with the final one)  pw[2] units
-//   pw[3..7] offsets of: level -> first node (levels + 1), node -> id (nodes), node -> first unit (nodes + 1),
-//                        unit -> offset of its record (units), the unit records [coef] [nf] nf x [factor]
-//   pw[8] total words
-// A level never holds more than PLAN_LEVEL_UNITS units (wider levels are cut: their nodes are independent).
+//   pw[0]  sum levels          pw[1]  nodes (with the final one)      pw[2]  units
+//   pw[3]  -> level bounds over the node order, levels + 1 entries, first = pw[9] (the non-affine nodes,
+//             each level at most `level_cap` units: wider levels are cut, their nodes are independent)
+//   pw[4]  -> node id per position        pw[5]  -> first unit per position (nodes + 1)
+//   pw[6]  -> record offset per unit      pw[7]  -> the unit records [coef] [nf] nf x [factor]
+//   pw[8]  total words                    pw[9]  affine nodes (positions 0 .. pw[9])
+//   pw[10] -> bounds of the affine groups (at most PLAN_AFFINE_GROUP units each), pw[11] + 1 entries
+//   pw[13] -> the LIVE tables (read directly by a non-affine node or a term), pw[14] of them
+//   pw[12] -> a second copy of the non-affine nodes' unit records with COMPACT factor words: live table j -> j,
+//             node -> pw[14] + its position in the node order (record offsets relative to the first such unit),
+//             pw[15] -> their record offsets; the thread pair form keeps only these values in local memory
+//
+// Along a sumcheck round's variable every table is affine in the evaluation point d, T(i) + d (T(i+half) - T(i)),
+// hence so is every affine node: value at d = 0 and difference are computed once per pair and the other points
+// follow by additions; only the remaining ("sum") nodes are evaluated at every point.
 // ---------------------------------------------------------------------------------------------
-constexpr u32 PLAN_HEAD = 9, PLAN_LEVEL_UNITS = 256, PLAN_MAX_WORDS = 8192;
+constexpr u32 PLAN_HEAD = 16, PLAN_UNIT_BUF = 256, PLAN_AFFINE_GROUP = PLAN_UNIT_BUF / 2, PLAN_MAX_WORDS = 8192;
 
-// returns 0 and fills `pw`, or a non-zero reason (a node wider than a level, a plan beyond PLAN_MAX_WORDS)
-inline int build_plan(const Shape& s, const u32* w, std::vector<u32>& pw) {
-    struct Node { u32 id, level; std::vector<std::vector<u32>> units; };
+// level_cap: units per sum level (the pair form runs a level's units at every point at once: PLAN_UNIT_BUF / points).
+// Returns 0 and fills `pw`, or a non-zero reason (a node wider than a level, a plan beyond PLAN_MAX_WORDS).
+inline int build_plan(const Shape& s, const u32* w, u32 level_cap, std::vector<u32>& pw) {
+    struct Node { u32 id, level; bool affine = false; std::vector<std::vector<u32>> units; };
     std::vector<Node> nodes(s.n_nodes + 1);
     std::vector<u32> level(s.n_nodes + 1, 0);
+    if (level_cap == 0 || level_cap > PLAN_UNIT_BUF) return 3;
     u32 pc = 0;
     auto read_product = [&](Node& nd) {
         const u32 ci = w[pc++], nf = w[pc++];
@@ -169,6 +182,7 @@ inline int build_plan(const Shape& s, const u32* w, std::vector<u32>& pw) {
         } else {
             const u32 head = w[pc++], cnt = head >> 8;
             if ((head & 0xFFu) == IR_AFFINE) {
+                nd.affine = true;
                 const u32 kc = w[pc++];
                 if (kc != IR_ZERO) nd.units.push_back({kc, 0u});
                 for (u32 i = 0; i < cnt; i++, pc += 2) nd.units.push_back({w[pc], 1u, w[pc + 1]});
@@ -176,50 +190,79 @@ inline int build_plan(const Shape& s, const u32* w, std::vector<u32>& pw) {
                 for (u32 i = 0; i < cnt; i++) read_product(nd);
             }
         }
-        if (nd.units.size() > PLAN_LEVEL_UNITS) return 1;
+        if (nd.units.size() > (nd.affine ? PLAN_AFFINE_GROUP : level_cap)) return 1;
         level[n] = nd.level;
     }
-    // order by level (stable in the id), cutting levels that are too wide
-    std::vector<u32> order;
-    std::vector<u32> lvl_start{0};
+    std::vector<u32> order, agrp{0}, lvl;
+    u32 in_group = 0;
+    for (auto& nd : nodes) {  // affine nodes, grouped
+        if (!nd.affine) continue;
+        if (in_group + nd.units.size() > PLAN_AFFINE_GROUP) { agrp.push_back((u32)order.size()); in_group = 0; }
+        order.push_back(nd.id);
+        in_group += (u32)nd.units.size();
+    }
+    const u32 NA = (u32)order.size();
+    if (agrp.back() != NA) agrp.push_back(NA);
+    lvl.push_back(NA);
     u32 maxl = 0;
     for (auto& nd : nodes) maxl = nd.level > maxl ? nd.level : maxl;
-    for (u32 l = 1; l <= maxl; l++) {
+    for (u32 l = 1; l <= maxl; l++) {  // the others by level (stable in the id), cutting levels that are too wide
         u32 in_level = 0;
         bool any = false;
         for (auto& nd : nodes) {
-            if (nd.level != l) continue;
-            if (any && in_level + nd.units.size() > PLAN_LEVEL_UNITS) {
-                lvl_start.push_back((u32)order.size());
-                in_level = 0;
-            }
+            if (nd.affine || nd.level != l) continue;
+            if (any && in_level + nd.units.size() > level_cap) { lvl.push_back((u32)order.size()); in_level = 0; }
             order.push_back(nd.id);
             in_level += (u32)nd.units.size();
             any = true;
         }
-        if (any) lvl_start.push_back((u32)order.size());
+        if (any) lvl.push_back((u32)order.size());
     }
-    const u32 L = (u32)lvl_start.size() - 1, NN = (u32)order.size();
-    std::vector<u32> nus{0}, uoff, uw;
+    const u32 NN = (u32)order.size();
+    std::vector<u32> nus{0}, uoff, uw, live;
+    std::vector<bool> is_live(s.n_tables, false);
     for (u32 k = 0; k < NN; k++) {
-        for (auto& u : nodes[order[k]].units) {
+        const Node& nd = nodes[order[k]];
+        for (auto& u : nd.units) {
             uoff.push_back((u32)uw.size());
             uw.insert(uw.end(), u.begin(), u.end());
+            if (!nd.affine)
+                for (size_t f = 2; f < u.size(); f++)
+                    if (!(u[f] & IR_NODE)) is_live[u[f]] = true;
         }
         nus.push_back((u32)uoff.size());
     }
+    for (u32 t = 0; t < s.n_tables; t++)
+        if (is_live[t]) live.push_back(t);
     pw.assign(PLAN_HEAD, 0);
-    pw[0] = L; pw[1] = NN; pw[2] = (u32)uoff.size();
-    pw[3] = (u32)pw.size(); pw.insert(pw.end(), lvl_start.begin(), lvl_start.end());
+    pw[0] = (u32)lvl.size() - 1; pw[1] = NN; pw[2] = (u32)uoff.size(); pw[9] = NA; pw[11] = (u32)agrp.size() - 1; pw[14] = (u32)live.size();
+    pw[3] = (u32)pw.size(); pw.insert(pw.end(), lvl.begin(), lvl.end());
     pw[4] = (u32)pw.size(); pw.insert(pw.end(), order.begin(), order.end());
     pw[5] = (u32)pw.size(); pw.insert(pw.end(), nus.begin(), nus.end());
     pw[6] = (u32)pw.size(); pw.insert(pw.end(), uoff.begin(), uoff.end());
     pw[7] = (u32)pw.size(); pw.insert(pw.end(), uw.begin(), uw.end());
+    pw[10] = (u32)pw.size(); pw.insert(pw.end(), agrp.begin(), agrp.end());
+    pw[13] = (u32)pw.size(); pw.insert(pw.end(), live.begin(), live.end());
+    {   // compact records of the non-affine nodes' units
+        std::vector<u32> slot_of_table(s.n_tables, 0), pos_of_node(s.n_nodes + 1, 0), cw, coff;
+        for (u32 j = 0; j < live.size(); j++) slot_of_table[live[j]] = j;
+        for (u32 k = 0; k < NN; k++) pos_of_node[order[k]] = k;
+        for (u32 k = NA; k < NN; k++)
+            for (auto& u : nodes[order[k]].units) {
+                coff.push_back((u32)cw.size());
+                cw.push_back(u[0]);
+                cw.push_back(u[1]);
+                for (size_t f = 2; f < u.size(); f++)
+                    cw.push_back((u[f] & IR_NODE) ? (u32)live.size() + pos_of_node[u[f] & ~IR_NODE] : slot_of_table[u[f]]);
+            }
+        pw[12] = (u32)pw.size(); pw.insert(pw.end(), cw.begin(), cw.end());
+        pw[15] = (u32)pw.size(); pw.insert(pw.end(), coff.begin(), coff.end());
+    }
     pw[8] = (u32)pw.size();
     return pw.size() > PLAN_MAX_WORDS ? 2 : 0;
 }
 
-// one thread walks the whole plan; nv holds n_nodes + 1 values, the last one is the polynomial
+// ---- thread form: one worker walks the whole plan at ONE point; nv holds n_nodes + 1 values ----
 GL_HD fp2 plan_eval(const u32* pw, const fp2* cf, const fp2* tv, fp2* nv) {
     const u32 NN = pw[1];
     const u32 *nid = pw + pw[4], *nus = pw + pw[5], *uoff = pw + pw[6], *uw = pw + pw[7];
@@ -235,25 +278,140 @@ GL_HD fp2 plan_eval(const u32* pw, const fp2* cf, const fp2* tv, fp2* nv) {
     return acc;  // the final node is last in the order
 }
 
-// The same plan by `lanes` cooperating workers (a warp on the device; the host emulation runs the lanes of a
-// phase one after another).  Phase A of a level: lane takes units u0 + lane, + lanes, ... into ub; phase B: lane takes
-// nodes and sums their units.  The caller separates the phases with a barrier over the lanes.
-GL_HD void plan_level_units(const u32* pw, u32 l, const fp2* cf, const fp2* tv, const fp2* nv, fp2* ub, u32 lane, u32 lanes) {
-    const u32 *lvl = pw + pw[3], *nus = pw + pw[5], *uoff = pw + pw[6], *uw = pw + pw[7];
-    const u32 u0 = nus[lvl[l]], u1 = nus[lvl[l + 1]];
+// ---- thread pair form: one worker, one pair, every point, with a compact value array:
+// V[j] live table j, V[n_live + k] the node at position k; D[j], D[n_live + k] the differences of the live tables and
+// of the affine nodes (positions below pw[9]).  The affine nodes read their tables through `table(t, lo, dif)`. ----
+template <class Table>
+GL_HD void tpair_affine(const u32* pw, const fp2* cf, fp2* V, fp2* D, Table table) {
+    const u32 *nus = pw + pw[5], *uoff = pw + pw[6], *uw = pw + pw[7];
+    const u32 nl = pw[14], na = pw[9];
+    for (u32 k = 0; k < na; k++) {
+        fp2 v = f2(0, 0), d = f2(0, 0);
+        for (u32 u = nus[k]; u < nus[k + 1]; u++) {
+            const u32* r = uw + uoff[u];
+            if (r[1] == 0) {
+                v = f2_add(v, coef_value(r[0], cf));
+            } else {
+                fp2 lo, df;
+                table(r[2], lo, df);
+                v = f2_add(v, coef_mul(r[0], cf, lo));
+                d = f2_add(d, coef_mul(r[0], cf, df));
+            }
+        }
+        V[nl + k] = v;
+        D[nl + k] = d;
+    }
+}
+GL_HD void tpair_step(const u32* pw, fp2* V, const fp2* D) {
+    for (u32 j = 0; j < pw[14] + pw[9]; j++) V[j] = f2_add(V[j], D[j]);
+}
+// the non-affine nodes at the current point; returns the polynomial's value
+GL_HD fp2 tpair_sums(const u32* pw, const fp2* cf, fp2* V) {
+    const u32 *nus = pw + pw[5], *cw = pw + pw[12], *coff = pw + pw[15];
+    const u32 nl = pw[14], na = pw[9], nn = pw[1], u_base = nus[na];
+    fp2 acc = f2(0, 0);
+    for (u32 k = na; k < nn; k++) {
+        acc = f2(0, 0);
+        for (u32 u = nus[k]; u < nus[k + 1]; u++) {
+            const u32* r = cw + coff[u - u_base];
+            fp2 x;
+            if (r[1] == 0) {
+                x = coef_value(r[0], cf);
+            } else {
+                x = V[r[2]];
+                for (u32 i = 1; i < r[1]; i++) x = mul_mixed(x, V[r[2 + i]]);
+                x = coef_mul(r[0], cf, x);
+            }
+            acc = f2_add(acc, x);
+        }
+        V[nl + k] = acc;
+    }
+    return acc;
+}
+
+// ---- pair form: `lanes` cooperating workers (a warp; the host emulation runs the lanes of a phase one after
+// another) evaluate ONE pair at every point.  Values live in V[id * np + point] (id = table, or n_tables + node id),
+// differences in DV[id], products of the running phase in UB (PLAN_UNIT_BUF entries).  The caller fills V[t * np]
+// and DV[t] for every table and separates the phases with a barrier over the lanes. ----
+struct Pair {
+    const u32* pw;
+    const fp2* cf;
+    fp2 *V, *DV, *UB;
+    u32 n_tables, np;   // np = declared degree + 1
+    u32 npe;            // points evaluated: np, or np - 1 when the point 1 comes from the running claim
+    GL_HD u32 point(u32 pi) const { return npe == np || pi == 0 ? pi : pi + 1; }
+};
+
+// affine group g, phase 1: the units' products at point 0 (UB[j]) and along the difference (UB[half + j])
+GL_HD void pair_affine_units(const Pair& a, u32 g, u32 lane, u32 lanes) {
+    const u32 *grp = a.pw + a.pw[10], *nus = a.pw + a.pw[5], *uoff = a.pw + a.pw[6], *uw = a.pw + a.pw[7];
+    const u32 u0 = nus[grp[g]], u1 = nus[grp[g + 1]];
     for (u32 u = u0 + lane; u < u1; u += lanes) {
-        u32 pc = uoff[u];
-        ub[u - u0] = product(uw, pc, cf, tv, nv);
+        const u32* r = uw + uoff[u];
+        if (r[1] == 0) {
+            a.UB[u - u0] = coef_value(r[0], a.cf);
+            a.UB[PLAN_AFFINE_GROUP + u - u0] = f2(0, 0);
+        } else {
+            a.UB[u - u0] = coef_mul(r[0], a.cf, a.V[r[2] * a.np]);
+            a.UB[PLAN_AFFINE_GROUP + u - u0] = coef_mul(r[0], a.cf, a.DV[r[2]]);
+        }
     }
 }
-GL_HD void plan_level_nodes(const u32* pw, u32 l, const fp2* ub, fp2* nv, u32 lane, u32 lanes) {
-    const u32 *lvl = pw + pw[3], *nid = pw + pw[4], *nus = pw + pw[5];
-    const u32 n0 = lvl[l], n1 = lvl[l + 1], u0 = nus[n0];
-    for (u32 n = n0 + lane; n < n1; n += lanes) {
-        fp2 acc = f2(0, 0);
-        for (u32 u = nus[n]; u < nus[n + 1]; u++) acc = f2_add(acc, ub[u - u0]);
-        nv[nid[n]] = acc;
+// phase 2: the group's nodes sum their units
+GL_HD void pair_affine_nodes(const Pair& a, u32 g, u32 lane, u32 lanes) {
+    const u32 *grp = a.pw + a.pw[10], *nid = a.pw + a.pw[4], *nus = a.pw + a.pw[5];
+    const u32 k0 = grp[g], k1 = grp[g + 1], u0 = nus[k0];
+    for (u32 k = k0 + lane; k < k1; k += lanes) {
+        fp2 v = f2(0, 0), d = f2(0, 0);
+        for (u32 u = nus[k]; u < nus[k + 1]; u++) {
+            v = f2_add(v, a.UB[u - u0]);
+            d = f2_add(d, a.UB[PLAN_AFFINE_GROUP + u - u0]);
+        }
+        const u32 id = a.n_tables + nid[k];
+        a.V[id * a.np] = v;
+        a.DV[id] = d;
     }
 }
+// live tables and affine nodes at the points 1 .. np - 1, by additions
+GL_HD void pair_step(const Pair& a, u32 lane, u32 lanes) {
+    const u32 *live = a.pw + a.pw[13], *nid = a.pw + a.pw[4];
+    const u32 nl = a.pw[14], na = a.pw[9];
+    for (u32 j = lane; j < nl + na; j += lanes) {
+        const u32 id = j < nl ? live[j] : a.n_tables + nid[j - nl];
+        fp2 v = a.V[id * a.np];
+        const fp2 d = a.DV[id];
+        for (u32 p = 1; p < a.np; p++) { v = f2_add(v, d); a.V[id * a.np + p] = v; }
+    }
+}
+GL_HD fp2 pair_product(const Pair& a, const u32* r, u32 p) {
+    const u32 nf = r[1];
+    if (nf == 0) return coef_value(r[0], a.cf);
+    auto val = [&](u32 f) { return a.V[((f & IR_NODE) ? a.n_tables + (f & ~IR_NODE) : f) * a.np + p]; };
+    fp2 x = val(r[2]);
+    for (u32 i = 1; i < nf; i++) x = mul_mixed(x, val(r[2 + i]));
+    return coef_mul(r[0], a.cf, x);
+}
+// sum level l, phase 1: every (unit, evaluated point) product
+GL_HD void pair_level_units(const Pair& a, u32 l, u32 lane, u32 lanes) {
+    const u32 *lvl = a.pw + a.pw[3], *nus = a.pw + a.pw[5], *uoff = a.pw + a.pw[6], *uw = a.pw + a.pw[7];
+    const u32 u0 = nus[lvl[l]], u1 = nus[lvl[l + 1]];
+    for (u32 x = lane; x < (u1 - u0) * a.npe; x += lanes) {
+        const u32 u = x / a.npe, pi = x - u * a.npe;
+        a.UB[x] = pair_product(a, uw + uoff[u0 + u], a.point(pi));
+    }
+}
+// phase 2: every (node, evaluated point) sum
+GL_HD void pair_level_nodes(const Pair& a, u32 l, u32 lane, u32 lanes) {
+    const u32 *lvl = a.pw + a.pw[3], *nid = a.pw + a.pw[4], *nus = a.pw + a.pw[5];
+    const u32 k0 = lvl[l], k1 = lvl[l + 1], u0 = nus[k0];
+    for (u32 x = lane; x < (k1 - k0) * a.npe; x += lanes) {
+        const u32 k = k0 + x / a.npe, pi = x % a.npe;
+        fp2 v = f2(0, 0);
+        for (u32 u = nus[k]; u < nus[k + 1]; u++) v = f2_add(v, a.UB[(u - u0) * a.npe + pi]);
+        a.V[(a.n_tables + nid[k]) * a.np + a.point(pi)] = v;
+    }
+}
+// Fp2 entries of one worker group's areas: V, DV, UB
+GL_HD u32 pair_area(u32 n_tables, u32 n_nodes_with_final, u32 np) { return (n_tables + n_nodes_with_final) * (np + 1) + PLAN_UNIT_BUF; }
 
 }  // namespace ir

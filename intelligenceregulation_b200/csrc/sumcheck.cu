@@ -346,19 +346,18 @@ __global__ void __launch_bounds__(256) k_sc_fold(u64* __restrict__ tables, size_
 
 // ---------------------------------------------------------------------------------------------
 // Slot polynomials given as data (slot_ir.cuh): the same round / tail structure with the polynomial
-// interpreted from its evaluation plan, held in shared memory.  A work item is one (pair, evaluation
-// point): the table values at point d are T(i) + d (T(i+half) - T(i)), so the points of a pair are
-// independent.  Two forms:
-//   thread form  one item per thread, table and node values in local memory: the long rounds of a light
-//                polynomial (coalesced table reads, no idle lanes);
-//   warp form    one item per warp: the lanes share the table loads, take one unit of a level each and
-//                then one node each, values in shared memory.  A 60-table, 70-node polynomial costs one
-//                thread ~120 us per item; a warp gets through it in a few microseconds, which is what the
-//                short rounds (few items, every one on the critical path) need.
+// interpreted from its evaluation plan, held in shared memory.  Two forms:
+//   pair form    one PAIR per warp, every evaluation point at once.  Table values and affine nodes are stepped
+//                along the round's variable by additions; the remaining nodes run level by level with one
+//                (unit, point) product per lane, then one (node, point) sum per lane.  All values stay in shared
+//                memory (a 60-table, 70-node polynomial keeps ~19 KB per warp), nothing spills, and a pair costs
+//                microseconds, so the same kernel serves the long rounds and the short ones.
+//   thread form  one (pair, point) per thread with the values in local memory: polynomials of a few units, where
+//                a warp would idle.
 // ---------------------------------------------------------------------------------------------
-constexpr int IRT = 128;                 // thread form
-constexpr int IRW_WARPS = 8;             // warp form, round kernel
-constexpr int IR_TAIL_WARPS = 16;        // warp form, single-CTA tail
+constexpr int IRT = 128;             // thread form
+constexpr int IRC_MAX_WARPS = 8;     // pair form, warps per CTA (fewer when the areas are large)
+constexpr int IR_TAIL_T = 512;       // single-CTA tail, thread form (the pair form uses as many warps as fit)
 
 __device__ __forceinline__ void ir_stage(const hlk::IrDev& p, u32* w_s, fp2*& cf_s, int nthreads) {
     for (u32 x = threadIdx.x; x < p.plan_words; x += nthreads) w_s[x] = p.plan[x];
@@ -373,7 +372,7 @@ __device__ __forceinline__ fp2 ir_table_value(const u64* __restrict__ tb, u32 i,
     return f2_add(lo, f2_mul_base(f2_sub(hi, lo), (u64)d));
 }
 
-// grid (blocks, degree + 1): row y evaluates point y; partials[block][point] as in k_sc_round
+// thread form: grid (blocks, degree + 1), row y evaluates point y; partials[block][point] as in k_sc_round
 __global__ void __launch_bounds__(IRT) k_sc_round_ir(const u64* __restrict__ tables, size_t stride, u32 half, hlk::IrDev p, int degree,
                                                      int eval_one, u64* __restrict__ partials) {
     extern __shared__ __align__(16) u32 ir_smem[];
@@ -409,76 +408,147 @@ __global__ void __launch_bounds__(IRT) k_sc_round_ir(const u64* __restrict__ tab
     }
 }
 
-// one item by one warp: returns the polynomial's value (every lane)
-__device__ __forceinline__ fp2 ir_warp_item(const hlk::IrDev& p, const u32* pw, const fp2* cf_s, const u64* __restrict__ tables, size_t stride,
-                                            u32 i, u32 half, u32 d, fp2* tv_s, fp2* nv_s, fp2* ub_s, u32 lane) {
-    for (u32 t = lane; t < p.n_tables; t += 32) tv_s[t] = ir_table_value(tables + 2 * (size_t)t * stride, i, half, d);
-    __syncwarp();
-    const u32 L = pw[0];
-    for (u32 l = 0; l < L; l++) {
-        ir::plan_level_units(pw, l, cf_s, tv_s, nv_s, ub_s, lane, 32);
-        __syncwarp();
-        ir::plan_level_nodes(pw, l, ub_s, nv_s, lane, 32);
-        __syncwarp();
-    }
-    const fp2 v = nv_s[p.n_nodes - 1];  // the final node has the highest id
-    __syncwarp();                        // every lane has read it before the next item overwrites the areas
-    return v;
-}
-
-__device__ __forceinline__ u32 ir_warp_area(const hlk::IrDev& p) { return p.n_tables + p.n_nodes + p.max_level_units; }  // Fp2 per warp
-
-__global__ void __launch_bounds__(IRW_WARPS * 32) k_sc_round_irw(const u64* __restrict__ tables, size_t stride, u32 half, hlk::IrDev p,
-                                                                 int degree, int eval_one, u64* __restrict__ partials) {
+// thread pair form: one pair per thread, every point; only live tables and node values are kept (slot_ir.cuh).  The long
+// rounds: it evaluates the affine nodes once per pair instead of once per point and needs no interpolation of the tables.
+constexpr u32 IRP_VALUES = ir::MAX_TABLES + ir::MAX_NODES + 1;
+__global__ void __launch_bounds__(IRT) k_sc_round_irp(const u64* __restrict__ tables, size_t stride, u32 half, hlk::IrDev p, int degree,
+                                                      int eval_one, u64* __restrict__ partials) {
     extern __shared__ __align__(16) u32 ir_smem[];
-    __shared__ u64 wsum[IRW_WARPS][2];
+    __shared__ u64 wsum[IRT / 32][2 * hlk::SC_MAX_POINTS];
     fp2* cf_s;
-    const u32 d = blockIdx.y;
-    u64* dst = partials + ((size_t)blockIdx.x * (degree + 1) + d) * 2;
-    if (d == 1 && !eval_one) {
-        if (threadIdx.x < 2) dst[threadIdx.x] = 0;
-        return;
+    ir_stage(p, ir_smem, cf_s, IRT);
+    __syncthreads();
+    const u32* pw = ir_smem;
+    const u32 nl = pw[14];
+    const u32* live = pw + pw[13];
+    fp2 V[IRP_VALUES], D[IRP_VALUES];
+    fp2 acc[hlk::SC_MAX_POINTS];
+#pragma unroll
+    for (int d = 0; d < hlk::SC_MAX_POINTS; d++) acc[d] = f2(0, 0);
+    for (u32 i = blockIdx.x * IRT + threadIdx.x; i < half; i += gridDim.x * IRT) {
+        for (u32 j = 0; j < nl; j++) {
+            const u64* tb = tables + 2 * (size_t)live[j] * stride;
+            V[j] = ld2(tb + 2 * (size_t)i);
+            D[j] = f2_sub(ld2(tb + 2 * ((size_t)i + half)), V[j]);
+        }
+        ir::tpair_affine(pw, cf_s, V, D, [&](u32 t, fp2& lo, fp2& df) {
+            const u64* tb = tables + 2 * (size_t)t * stride;
+            lo = ld2(tb + 2 * (size_t)i);
+            df = f2_sub(ld2(tb + 2 * ((size_t)i + half)), lo);
+        });
+        acc[0] = f2_add(acc[0], ir::tpair_sums(pw, cf_s, V));
+        for (int d = 1; d <= degree; d++) {
+            ir::tpair_step(pw, V, D);
+            if (d == 1 && !eval_one) continue;
+            const fp2 v = ir::tpair_sums(pw, cf_s, V);
+#pragma unroll
+            for (int dd = 1; dd < hlk::SC_MAX_POINTS; dd++)
+                if (dd == d) acc[dd] = f2_add(acc[dd], v);
+        }
     }
-    ir_stage(p, ir_smem, cf_s, IRW_WARPS * 32);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, np = degree + 1;
+    for (int d = 0; d < np; d++) {
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+            acc[d].c0 = gl_add(acc[d].c0, shfl_down64(acc[d].c0, off));
+            acc[d].c1 = gl_add(acc[d].c1, shfl_down64(acc[d].c1, off));
+        }
+    }
+    if (lane == 0) {
+        for (int d = 0; d < np; d++) { wsum[warp][2 * d] = acc[d].c0; wsum[warp][2 * d + 1] = acc[d].c1; }
+    }
     __syncthreads();
-    const u32 lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    fp2* area = cf_s + p.n_coefs + (size_t)warp * ir_warp_area(p);
-    fp2 *tv_s = area, *nv_s = area + p.n_tables, *ub_s = nv_s + p.n_nodes;
-    fp2 acc = f2(0, 0);
-    for (u32 i = blockIdx.x * IRW_WARPS + warp; i < half; i += gridDim.x * IRW_WARPS)
-        acc = f2_add(acc, ir_warp_item(p, ir_smem, cf_s, tables, stride, i, half, d, tv_s, nv_s, ub_s, lane));
-    if (lane == 0) { wsum[warp][0] = acc.c0; wsum[warp][1] = acc.c1; }
-    __syncthreads();
-    if (threadIdx.x < 2) {
+    if ((int)threadIdx.x < 2 * np) {
         u64 s = 0;
 #pragma unroll
-        for (int w = 0; w < IRW_WARPS; w++) s = gl_add(s, wsum[w][threadIdx.x]);
-        dst[threadIdx.x] = s;
+        for (int w = 0; w < IRT / 32; w++) s = gl_add(s, wsum[w][threadIdx.x]);
+        partials[(size_t)blockIdx.x * 2 * np + threadIdx.x] = s;
     }
 }
 
-constexpr int IR_TAIL_T = IR_TAIL_WARPS * 32;
-template <bool WARP_FORM>
+// pair form, one pair by one warp; afterwards V holds the final node's value at every evaluated point
+__device__ __forceinline__ void ir_pair_item(const ir::Pair& a, const u64* __restrict__ tables, size_t stride, u32 i, u32 half, u32 lane) {
+    for (u32 t = lane; t < a.n_tables; t += 32) {
+        const u64* tb = tables + 2 * (size_t)t * stride;
+        const fp2 lo = ld2(tb + 2 * (size_t)i);
+        a.V[t * a.np] = lo;
+        a.DV[t] = f2_sub(ld2(tb + 2 * ((size_t)i + half)), lo);
+    }
+    __syncwarp();
+    for (u32 g = 0; g < a.pw[11]; g++) {
+        ir::pair_affine_units(a, g, lane, 32);
+        __syncwarp();
+        ir::pair_affine_nodes(a, g, lane, 32);
+        __syncwarp();
+    }
+    ir::pair_step(a, lane, 32);
+    __syncwarp();
+    for (u32 l = 0; l < a.pw[0]; l++) {
+        ir::pair_level_units(a, l, lane, 32);
+        __syncwarp();
+        ir::pair_level_nodes(a, l, lane, 32);
+        __syncwarp();
+    }
+}
+
+__device__ __forceinline__ ir::Pair ir_pair_setup(const hlk::IrDev& p, const u32* pw_s, fp2* cf_s, u32 warp, int degree, bool skip_one) {
+    ir::Pair a;
+    const u32 np = (u32)degree + 1, ids = p.n_tables + p.n_nodes;
+    fp2* area = cf_s + p.n_coefs + (size_t)warp * ir::pair_area(p.n_tables, p.n_nodes, np);
+    a.pw = pw_s; a.cf = cf_s; a.V = area; a.DV = area + (size_t)ids * np; a.UB = a.DV + ids;
+    a.n_tables = p.n_tables; a.np = np; a.npe = skip_one ? np - 1 : np;
+    return a;
+}
+
+__global__ void __launch_bounds__(IRC_MAX_WARPS * 32) k_sc_round_irc(const u64* __restrict__ tables, size_t stride, u32 half, hlk::IrDev p,
+                                                                     int degree, int eval_one, u64* __restrict__ partials) {
+    extern __shared__ __align__(16) u32 ir_smem[];
+    __shared__ u64 wsum[IRC_MAX_WARPS][2 * hlk::SC_MAX_POINTS];
+    fp2* cf_s;
+    ir_stage(p, ir_smem, cf_s, blockDim.x);
+    __syncthreads();
+    const u32 lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5, np = (u32)degree + 1;
+    const ir::Pair a = ir_pair_setup(p, ir_smem, cf_s, warp, degree, !eval_one);
+    const u32 fin = (p.n_tables + p.n_nodes - 1) * np;  // the final node's values
+    fp2 acc = f2(0, 0);  // lane pi: the sum at evaluated point pi
+    for (u32 i = blockIdx.x * nwarps + warp; i < half; i += gridDim.x * nwarps) {
+        ir_pair_item(a, tables, stride, i, half, lane);
+        if (lane < a.npe) acc = f2_add(acc, a.V[fin + a.point(lane)]);
+        __syncwarp();
+    }
+    if (lane < 2 * hlk::SC_MAX_POINTS) wsum[warp][lane] = 0;
+    __syncwarp();
+    if (lane < a.npe) { wsum[warp][2 * a.point(lane)] = acc.c0; wsum[warp][2 * a.point(lane) + 1] = acc.c1; }
+    __syncthreads();
+    if (threadIdx.x < 2 * np) {
+        u64 s = 0;
+        for (u32 w = 0; w < nwarps; w++) s = gl_add(s, wsum[w][threadIdx.x]);
+        partials[(size_t)blockIdx.x * 2 * np + threadIdx.x] = s;
+    }
+}
+
+template <bool PAIR_FORM>
 __global__ void __launch_bounds__(IR_TAIL_T) k_sc_tail_ir(u64* __restrict__ tables, size_t stride, u32 len, hlk::IrDev p, int degree, int k,
                                                           ScStep a, int nrounds, int first_has_claim) {
     extern __shared__ __align__(16) u32 ir_smem[];
     __shared__ StepSmem sm;
-    __shared__ u64 wsum[IR_TAIL_WARPS][2 * hlk::SC_MAX_POINTS];
+    __shared__ u64 wsum[IR_TAIL_T / 32][2 * hlk::SC_MAX_POINTS];
     __shared__ hlk::ScState st_s;
     __shared__ u64 mask_s[2 * (63 * (hlk::SC_MAX_POINTS - 1) + 2)];
     __shared__ u64 hs_s[2 * 63];
     __shared__ u64 invden_s[hlk::SC_MAX_POINTS];
     fp2* cf_s;
-    ir_stage(p, ir_smem, cf_s, IR_TAIL_T);
+    const u32 nthreads = blockDim.x, nwarps = nthreads >> 5;
+    ir_stage(p, ir_smem, cf_s, nthreads);
     const u32 lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int np = degree + 1;
     {
         const u32* src = reinterpret_cast<const u32*>(a.state);
         u32* dst = reinterpret_cast<u32*>(&st_s);
-        for (u32 i = threadIdx.x; i < sizeof(hlk::ScState) / 4; i += IR_TAIL_T) dst[i] = src[i];
+        for (u32 i = threadIdx.x; i < sizeof(hlk::ScState) / 4; i += nthreads) dst[i] = src[i];
         if (a.mask) {
-            for (u32 i = threadIdx.x; i < 2u * (a.mask_vars * degree + 2); i += IR_TAIL_T) mask_s[i] = a.mask[i];
-            for (u32 i = threadIdx.x; i < 2u * a.mask_vars; i += IR_TAIL_T) hs_s[i] = a.mask_half_suffix[i];
+            for (u32 i = threadIdx.x; i < 2u * (a.mask_vars * degree + 2); i += nthreads) mask_s[i] = a.mask[i];
+            for (u32 i = threadIdx.x; i < 2u * a.mask_vars; i += nthreads) hs_s[i] = a.mask_half_suffix[i];
         }
         if ((int)threadIdx.x < np) invden_s[threadIdx.x] = a.inv_den[threadIdx.x];
     }
@@ -487,26 +557,28 @@ __global__ void __launch_bounds__(IR_TAIL_T) k_sc_tail_ir(u64* __restrict__ tabl
     a.inv_den = invden_s;
     a.state = &st_s;
     __syncthreads();
-    fp2* area = cf_s + p.n_coefs + (size_t)warp * ir_warp_area(p);
-    fp2 *tv_s = area, *nv_s = area + p.n_tables, *ub_s = nv_s + p.n_nodes;
     for (int rd = 0; rd < nrounds; rd++) {
         const u32 half = len >> 1;  // a power of two
         const bool have_claim = a.recover && (rd > 0 || first_has_claim);
-        fp2 acc[hlk::SC_MAX_POINTS];
-#pragma unroll
-        for (int d = 0; d < hlk::SC_MAX_POINTS; d++) acc[d] = f2(0, 0);
-        if constexpr (WARP_FORM) {
-            for (u32 x = warp; x < half * (u32)np; x += IR_TAIL_WARPS) {
-                const u32 d = x / half, i = x - d * half;
-                if (d == 1 && have_claim) continue;
-                const fp2 v = ir_warp_item(p, ir_smem, cf_s, tables, stride, i, half, d, tv_s, nv_s, ub_s, lane);
-#pragma unroll
-                for (int dd = 0; dd < hlk::SC_MAX_POINTS; dd++)
-                    if ((u32)dd == d) acc[dd] = f2_add(acc[dd], v);
+        if (threadIdx.x < 2 * hlk::SC_MAX_POINTS)
+            for (u32 w = 0; w < nwarps; w++) wsum[w][threadIdx.x] = 0;
+        __syncthreads();
+        if constexpr (PAIR_FORM) {
+            const ir::Pair pa = ir_pair_setup(p, ir_smem, cf_s, warp, degree, have_claim);
+            const u32 fin = (p.n_tables + p.n_nodes - 1) * (u32)np;
+            fp2 acc = f2(0, 0);
+            for (u32 i = warp; i < half; i += nwarps) {
+                ir_pair_item(pa, tables, stride, i, half, lane);
+                if (lane < pa.npe) acc = f2_add(acc, pa.V[fin + pa.point(lane)]);
+                __syncwarp();
             }
+            if (lane < pa.npe) { wsum[warp][2 * pa.point(lane)] = acc.c0; wsum[warp][2 * pa.point(lane) + 1] = acc.c1; }
         } else {
+            fp2 acc[hlk::SC_MAX_POINTS];
+#pragma unroll
+            for (int d = 0; d < hlk::SC_MAX_POINTS; d++) acc[d] = f2(0, 0);
             fp2 tv[ir::MAX_TABLES], nv[ir::MAX_NODES + 1];
-            for (u32 x = threadIdx.x; x < half * (u32)np; x += IR_TAIL_T) {
+            for (u32 x = threadIdx.x; x < half * (u32)np; x += nthreads) {
                 const u32 d = x / half, i = x - d * half;
                 if (d == 1 && have_claim) continue;
                 for (u32 t = 0; t < p.n_tables; t++) tv[t] = ir_table_value(tables + 2 * (size_t)t * stride, i, half, d);
@@ -522,15 +594,14 @@ __global__ void __launch_bounds__(IR_TAIL_T) k_sc_tail_ir(u64* __restrict__ tabl
                     acc[d].c1 = gl_add(acc[d].c1, shfl_down64(acc[d].c1, off));
                 }
             }
-        }
-        if (lane == 0) {
-            for (int d = 0; d < np; d++) { wsum[warp][2 * d] = acc[d].c0; wsum[warp][2 * d + 1] = acc[d].c1; }
+            if (lane == 0) {
+                for (int d = 0; d < np; d++) { wsum[warp][2 * d] = acc[d].c0; wsum[warp][2 * d + 1] = acc[d].c1; }
+            }
         }
         __syncthreads();
         if ((int)threadIdx.x < 2 * np) {
             u64 s = 0;
-#pragma unroll
-            for (int w = 0; w < IR_TAIL_WARPS; w++) s = gl_add(s, wsum[w][threadIdx.x]);
+            for (u32 w = 0; w < nwarps; w++) s = gl_add(s, wsum[w][threadIdx.x]);
             sm.sums[threadIdx.x] = s;
         }
         __syncthreads();
@@ -541,7 +612,7 @@ __global__ void __launch_bounds__(IR_TAIL_T) k_sc_tail_ir(u64* __restrict__ tabl
         }
         __syncthreads();
         const fp2 r = a.state->r;
-        for (u32 x = threadIdx.x; x < half * (u32)k; x += IR_TAIL_T) {
+        for (u32 x = threadIdx.x; x < half * (u32)k; x += nthreads) {
             const u32 t = x / half, i = x - t * half;
             u64* tb = tables + 2 * (size_t)t * stride;
             fp2 lo = ld2(tb + 2 * (size_t)i), hi = ld2(tb + 2 * ((size_t)i + half));
@@ -553,19 +624,29 @@ __global__ void __launch_bounds__(IR_TAIL_T) k_sc_tail_ir(u64* __restrict__ tabl
     {
         const u32* src = reinterpret_cast<const u32*>(&st_s);
         u32* dst = reinterpret_cast<u32*>(st_global);
-        for (u32 i = threadIdx.x; i < sizeof(hlk::ScState) / 4; i += IR_TAIL_T) dst[i] = src[i];
+        for (u32 i = threadIdx.x; i < sizeof(hlk::ScState) / 4; i += nthreads) dst[i] = src[i];
     }
 }
 
-size_t ir_smem_bytes(const hlk::IrDev& p, int warps) {
-    return (((size_t)p.plan_words + 3) & ~(size_t)3) * 4 + (size_t)p.n_coefs * 16 + (size_t)warps * (p.n_tables + p.n_nodes + p.max_level_units) * 16 + 16;
+// A polynomial of few units leaves most lanes of a warp idle: it stays in the thread form.  So do the long rounds of
+// every polynomial: with more (pair, point) items than resident threads the thread form is bound by instruction
+// throughput, where it needs a third of the pair form's warp instructions (no idle lanes); measured on the 219-unit
+// graph it takes 2.5 ns per item (12.5 ns per pair) from 2^15 pairs up, the pair form 28 ns per pair but only
+// ~43 us for a whole short round, where one thread needs 120-290 us for its single item.
+bool ir_pair_capable(const hlk::IrDev& p) { return p.n_units >= 24; }
+bool ir_pair_form(const hlk::IrDev& p, u32 half) { return ir_pair_capable(p) && half < (1u << 15); }
+// the long rounds of a large polynomial: one pair per thread
+bool ir_thread_pair_form(const hlk::IrDev& p, u32 half) { return ir_pair_capable(p) && half >= (1u << 15); }
+constexpr size_t IR_SMEM_BUDGET = 200 * 1024;
+size_t ir_fixed_bytes(const hlk::IrDev& p) { return (((size_t)p.plan_words + 3) & ~(size_t)3) * 4 + (size_t)p.n_coefs * 16 + 16; }
+size_t ir_area_bytes(const hlk::IrDev& p, int degree) { return (size_t)ir::pair_area(p.n_tables, p.n_nodes, (u32)degree + 1) * 16; }
+// warps of a pair-form CTA: as many as the shared memory holds, at most `want`
+int ir_pair_warps(const hlk::IrDev& p, int degree, int want) {
+    const size_t fixed = ir_fixed_bytes(p), area = ir_area_bytes(p, degree);
+    if (fixed + area > IR_SMEM_BUDGET) return 0;
+    const size_t fit = (IR_SMEM_BUDGET - fixed) / area;
+    return (int)(fit < (size_t)want ? fit : (size_t)want);
 }
-
-// a polynomial of few units leaves most lanes of a warp idle: it stays in the thread form
-// measured on a 60-table, 219-unit polynomial: the thread form takes ~120 us for anything up to ~190k items and 2.5 ns per
-// item beyond; the warp form 20 us plus 8.7 ns per item
-bool ir_warp_form(const hlk::IrDev& p, u32 half, int degree) { return p.n_units >= 24 && (size_t)half * (degree + 1) <= 12288; }
-bool ir_warp_tail(const hlk::IrDev& p) { return p.n_units >= 24; }
 
 template <int POLY, int K, int D>
 cudaError_t launch_round(const u64* tables, size_t stride, u32 half, const u64* coefs, int eval_one, u64* partials, u32 nblocks, cudaStream_t s) {
@@ -584,52 +665,72 @@ u32 sc_round_blocks(u32 half, int sm_count) {
 }
 
 u32 sc_ir_max_blocks(u32 half, int sm_count) {
-    u32 b = half, cap = (u32)sm_count * 4;  // the warp form at one pair per warp needs the most CTAs
+    u32 b = half, cap = (u32)sm_count * 8;  // the largest grid either form launches
     if (b < 1) b = 1;
     return b > cap ? cap : b;
 }
+
+bool sc_ir_fits(const IrDev& p, int degree) { return !ir_pair_capable(p) || ir_pair_warps(p, degree, 1) >= 1; }
 
 u32 sc_ir_blocks(const IrDev& p, u32 half, int degree, int sm_count) {
-    const bool warp = ir_warp_form(p, half, degree);
-    u32 per = warp ? IRW_WARPS : IRT, b = (half + per - 1) / per, cap = (u32)sm_count * (warp ? 4 : 2);
+    u32 per = IRT, cap = (u32)sm_count * 2;
+    if (ir_pair_form(p, half)) {
+        const int w = ir_pair_warps(p, degree, IRC_MAX_WARPS);
+        per = (u32)(w > 0 ? w : 1);
+        // CTAs per SM by shared memory
+        const size_t cta = ir_fixed_bytes(p) + (size_t)per * ir_area_bytes(p, degree);
+        const u32 per_sm = (u32)(IR_SMEM_BUDGET / cta);
+        cap = (u32)sm_count * (per_sm < 1 ? 1 : per_sm > 4 ? 4 : per_sm);
+    } else if (ir_thread_pair_form(p, half)) {
+        cap = (u32)sm_count * 8;
+    }
+    u32 b = (half + per - 1) / per;
     if (b < 1) b = 1;
     return b > cap ? cap : b;
 }
 
-// The single-CTA tail pays off only while a round's items fit its warps a few times over.
+// The single-CTA tail pays off only while a round's pairs fit its warps a few times over.
 u32 sc_ir_tail_len(const IrDev& p, int degree) {
     (void)degree;
-    return ir_warp_tail(p) ? 16u : p.n_units >= 4 ? 1024u : 4096u;
+    return ir_pair_capable(p) ? 32u : p.n_units >= 4 ? 1024u : 4096u;
 }
 
 cudaError_t sc_round_ir(const IrDev& p, int k, const u64* tables, size_t stride, u32 half, int degree, int eval_one, u64* partials,
                         u32 nblocks, cudaStream_t s) {
     (void)k;
-    dim3 grid(nblocks, (unsigned)degree + 1);
-    if (ir_warp_form(p, half, degree)) {
-        const size_t smem = ir_smem_bytes(p, IRW_WARPS);
+    if (ir_pair_form(p, half)) {
+        const int w = ir_pair_warps(p, degree, IRC_MAX_WARPS);
+        if (w < 1) return cudaErrorInvalidValue;
+        const size_t smem = ir_fixed_bytes(p) + (size_t)w * ir_area_bytes(p, degree);
         if (smem > 48 * 1024) {
-            cudaError_t e = cudaFuncSetAttribute(k_sc_round_irw, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            cudaError_t e = cudaFuncSetAttribute(k_sc_round_irc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return e;
         }
-        k_sc_round_irw<<<grid, IRW_WARPS * 32, smem, s>>>(tables, stride, half, p, degree, eval_one, partials);
-    } else {
-        k_sc_round_ir<<<grid, IRT, ir_smem_bytes(p, 0), s>>>(tables, stride, half, p, degree, eval_one, partials);
+        k_sc_round_irc<<<nblocks, w * 32, smem, s>>>(tables, stride, half, p, degree, eval_one, partials);
+        return cudaGetLastError();
     }
+    if (ir_thread_pair_form(p, half)) {
+        k_sc_round_irp<<<nblocks, IRT, ir_fixed_bytes(p), s>>>(tables, stride, half, p, degree, eval_one, partials);
+        return cudaGetLastError();
+    }
+    dim3 grid(nblocks, (unsigned)degree + 1);
+    k_sc_round_ir<<<grid, IRT, ir_fixed_bytes(p), s>>>(tables, stride, half, p, degree, eval_one, partials);
     return cudaGetLastError();
 }
 
 cudaError_t sc_tail_ir(const IrDev& p, int k, u64* tables, size_t stride, u32 len, int degree, const ScStep& a, int nrounds,
                        int first_has_claim, cudaStream_t s) {
-    if (ir_warp_tail(p)) {
-        const size_t smem = ir_smem_bytes(p, IR_TAIL_WARPS);
+    if (ir_pair_capable(p)) {
+        const int w = ir_pair_warps(p, degree, IR_TAIL_T / 32);
+        if (w < 1) return cudaErrorInvalidValue;
+        const size_t smem = ir_fixed_bytes(p) + (size_t)w * ir_area_bytes(p, degree);
         if (smem > 32 * 1024) {
             cudaError_t e = cudaFuncSetAttribute(k_sc_tail_ir<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return e;
         }
-        k_sc_tail_ir<true><<<1, IR_TAIL_T, smem, s>>>(tables, stride, len, p, degree, k, a, nrounds, first_has_claim);
+        k_sc_tail_ir<true><<<1, w * 32, smem, s>>>(tables, stride, len, p, degree, k, a, nrounds, first_has_claim);
     } else {
-        k_sc_tail_ir<false><<<1, IR_TAIL_T, ir_smem_bytes(p, 0), s>>>(tables, stride, len, p, degree, k, a, nrounds, first_has_claim);
+        k_sc_tail_ir<false><<<1, IR_TAIL_T, ir_fixed_bytes(p), s>>>(tables, stride, len, p, degree, k, a, nrounds, first_has_claim);
     }
     return cudaGetLastError();
 }

@@ -43,7 +43,7 @@ struct ScStep {
 struct IrDev {
     const u32* plan;   // the evaluation plan (slot_ir.cuh)
     const u64* coefs;  // n_coefs Fp2
-    u32 plan_words, n_coefs, n_tables, n_nodes /* with the final one */, n_units, max_level_units;
+    u32 plan_words, n_coefs, n_tables, n_nodes /* with the final one */, n_units;
 };
 
 u32 sc_round_blocks(u32 half, int sm_count);
@@ -51,6 +51,7 @@ u32 sc_round_blocks(u32 half, int sm_count);
 u32 sc_ir_blocks(const IrDev& p, u32 half, int degree, int sm_count);
 u32 sc_ir_max_blocks(u32 half, int sm_count);
 u32 sc_ir_tail_len(const IrDev& p, int degree);
+bool sc_ir_fits(const IrDev& p, int degree);  // the pair form's areas fit one CTA's shared memory
 cudaError_t sc_round_ir(const IrDev& p, int k, const u64* tables, size_t stride, u32 half, int degree, int eval_one, u64* partials,
                         u32 nblocks, cudaStream_t s);
 cudaError_t sc_tail_ir(const IrDev& p, int k, u64* tables, size_t stride, u32 len, int degree, const ScStep& a, int nrounds,

@@ -16,31 +16,84 @@ extern "C" void emul_ir_eval(const u32* words, u32 n_words, u32 n_tables, u32 n_
     out[1] = r.c1;
 }
 
-// The evaluation plan the kernels run: built from the same word stream, then evaluated either by one worker
-// (`lanes` == 0, the thread form) or level by level with `lanes` workers run one after another (the warp form).
-// Returns the plan builder's code (0 = built).
+// The evaluation plan the kernels run, thread form: built from the same word stream, then walked by one worker at one
+// point.  Returns the plan builder's code (0 = built).
 extern "C" int emul_ir_plan_eval(const u32* words, u32 n_words, u32 n_tables, u32 n_nodes, u32 n_terms, const u64* coefs, u32 n_coefs,
-                                 const u64* values, u32 lanes, u64* out, u32* plan_info /* levels, nodes, units, words */) {
+                                 const u64* values, u32 degree, u64* out, u32* plan_info /* sum levels, nodes, units, words, affine nodes */) {
     ir::Shape s{n_tables, n_nodes, n_terms, n_coefs, n_words};
     std::vector<u32> pw;
-    if (int why = ir::build_plan(s, words, pw)) return why;
-    plan_info[0] = pw[0]; plan_info[1] = pw[1]; plan_info[2] = pw[2]; plan_info[3] = pw[8];
-    const fp2* cf = reinterpret_cast<const fp2*>(coefs);
-    const fp2* tv = reinterpret_cast<const fp2*>(values);
-    std::vector<fp2> nv(pw[1]), ub(ir::PLAN_LEVEL_UNITS);
-    for (auto& x : nv) x = f2(0xA5A5A5A5A5A5A5A5ull, 0x5A5A5A5A5A5A5A5Aull);  // poisoned: a read before the write shows
-    for (auto& x : ub) x = f2(0xA5A5A5A5A5A5A5A5ull, 0x5A5A5A5A5A5A5A5Aull);
-    fp2 r;
-    if (lanes == 0) {
-        r = ir::plan_eval(pw.data(), cf, tv, nv.data());
-    } else {
-        for (u32 l = 0; l < pw[0]; l++) {
-            for (u32 lane = 0; lane < lanes; lane++) ir::plan_level_units(pw.data(), l, cf, tv, nv.data(), ub.data(), lane, lanes);
-            for (u32 lane = 0; lane < lanes; lane++) ir::plan_level_nodes(pw.data(), l, ub.data(), nv.data(), lane, lanes);
-        }
-        r = nv[pw[1] - 1];
-    }
+    if (int why = ir::build_plan(s, words, ir::PLAN_UNIT_BUF / (degree + 1), pw)) return why;
+    plan_info[0] = pw[0]; plan_info[1] = pw[1]; plan_info[2] = pw[2]; plan_info[3] = pw[8]; plan_info[4] = pw[9];
+    std::vector<fp2> nv(pw[1], f2(0xA5A5A5A5A5A5A5A5ull, 0x5A5A5A5A5A5A5A5Aull));  // poisoned: a read before the write shows
+    fp2 r = ir::plan_eval(pw.data(), reinterpret_cast<const fp2*>(coefs), reinterpret_cast<const fp2*>(values), nv.data());
     out[0] = r.c0;
     out[1] = r.c1;
+    return 0;
+}
+
+// The pair form of a round: the polynomial at the points 0..=degree of one pair (lo = T(i), hi = T(i+half)) by `lanes`
+// cooperating workers, the lanes of every phase run one after another.  With skip_one the point 1 is not evaluated
+// (its output stays zero).
+extern "C" int emul_ir_pair(const u32* words, u32 n_words, u32 n_tables, u32 n_nodes, u32 n_terms, const u64* coefs, u32 n_coefs,
+                            const u64* lo, const u64* hi, u32 degree, u32 lanes, int skip_one, u64* out /* (degree + 1) x 2 */) {
+    ir::Shape s{n_tables, n_nodes, n_terms, n_coefs, n_words};
+    std::vector<u32> pw;
+    const u32 np = degree + 1;
+    if (int why = ir::build_plan(s, words, ir::PLAN_UNIT_BUF / np, pw)) return why;
+    const fp2 poison = f2(0xA5A5A5A5A5A5A5A5ull, 0x5A5A5A5A5A5A5A5Aull);
+    const u32 ids = n_tables + pw[1];
+    std::vector<fp2> area(ir::pair_area(n_tables, pw[1], np), poison);
+    ir::Pair a;
+    a.pw = pw.data(); a.cf = reinterpret_cast<const fp2*>(coefs);
+    a.V = area.data(); a.DV = a.V + (size_t)ids * np; a.UB = a.DV + ids;
+    a.n_tables = n_tables; a.np = np; a.npe = skip_one ? np - 1 : np;
+    for (u32 t = 0; t < n_tables; t++) {
+        a.V[t * np] = f2(lo[2 * t], lo[2 * t + 1]);
+        a.DV[t] = f2_sub(f2(hi[2 * t], hi[2 * t + 1]), a.V[t * np]);
+    }
+    for (u32 g = 0; g < pw[11]; g++) {
+        for (u32 l = 0; l < lanes; l++) ir::pair_affine_units(a, g, l, lanes);
+        for (u32 l = 0; l < lanes; l++) ir::pair_affine_nodes(a, g, l, lanes);
+    }
+    for (u32 l = 0; l < lanes; l++) ir::pair_step(a, l, lanes);
+    for (u32 lv = 0; lv < pw[0]; lv++) {
+        for (u32 l = 0; l < lanes; l++) ir::pair_level_units(a, lv, l, lanes);
+        for (u32 l = 0; l < lanes; l++) ir::pair_level_nodes(a, lv, l, lanes);
+    }
+    const u32 fin = (n_tables + pw[1] - 1) * np;
+    for (u32 d = 0; d < 2 * np; d++) out[d] = 0;
+    for (u32 pi = 0; pi < a.npe; pi++) {
+        const fp2 v = a.V[fin + a.point(pi)];
+        out[2 * a.point(pi)] = v.c0;
+        out[2 * a.point(pi) + 1] = v.c1;
+    }
+    return 0;
+}
+
+// The thread pair form: one worker, one pair, every point, compact values (live tables and nodes only).
+extern "C" int emul_ir_tpair(const u32* words, u32 n_words, u32 n_tables, u32 n_nodes, u32 n_terms, const u64* coefs, u32 n_coefs,
+                             const u64* lo, const u64* hi, u32 degree, u64* out /* (degree + 1) x 2 */) {
+    ir::Shape s{n_tables, n_nodes, n_terms, n_coefs, n_words};
+    std::vector<u32> pw;
+    if (int why = ir::build_plan(s, words, ir::PLAN_UNIT_BUF / (degree + 1), pw)) return why;
+    const fp2* cf = reinterpret_cast<const fp2*>(coefs);
+    const fp2 poison = f2(0xA5A5A5A5A5A5A5A5ull, 0x5A5A5A5A5A5A5A5Aull);
+    const u32 nl = pw[14];
+    std::vector<fp2> V(nl + pw[1], poison), D(nl + pw[1], poison);
+    const u32* live = pw.data() + pw[13];
+    for (u32 j = 0; j < nl; j++) {
+        V[j] = f2(lo[2 * live[j]], lo[2 * live[j] + 1]);
+        D[j] = f2_sub(f2(hi[2 * live[j]], hi[2 * live[j] + 1]), V[j]);
+    }
+    ir::tpair_affine(pw.data(), cf, V.data(), D.data(), [&](u32 t, fp2& l, fp2& df) {
+        l = f2(lo[2 * t], lo[2 * t + 1]);
+        df = f2_sub(f2(hi[2 * t], hi[2 * t + 1]), l);
+    });
+    for (u32 d = 0; d <= degree; d++) {
+        if (d) ir::tpair_step(pw.data(), V.data(), D.data());
+        const fp2 v = ir::tpair_sums(pw.data(), cf, V.data());
+        out[2 * d] = v.c0;
+        out[2 * d + 1] = v.c1;
+    }
     return 0;
 }

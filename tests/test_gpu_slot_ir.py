@@ -26,13 +26,18 @@ def _n_vars(slot):
     return 13 if k <= 5 else 11 if k <= 25 else 10
 
 
-@pytest.mark.parametrize("idx", list(range(23)))
-def test_slot_program_batched_masked_rounds(ctx, oracle, golden_dir, idx):
+# every slot at a size that runs the point form, the warp form and the single-CTA tail; three slots at sizes whose first
+# rounds have more pairs than the machine has threads (the pair form)
+CASES = [(i, None) for i in range(23)] + [(14, 16), (3, 17), (5, 16)]
+
+
+@pytest.mark.parametrize("idx,n_long", CASES)
+def test_slot_program_batched_masked_rounds(ctx, oracle, golden_dir, idx, n_long):
     from intelligenceregulation_b200 import backend
 
     o = oracle
     slot = U.load_slots(golden_dir)[idx]
-    n, deg = _n_vars(slot), slot["declared_degree"]
+    n, deg = n_long or _n_vars(slot), slot["declared_degree"]
     prog, _ = U.build_program(backend, slot, 9000 + idx)
     tables = U.random_tables(slot, n, 100 + idx)
     w, cf = prog.words(), prog.coef_array()

@@ -60,14 +60,45 @@ def test_oracle_and_product_interpreters_agree_with_python_on_every_slot(oracle,
             out = np.zeros(2, dtype=np.uint64)
             emul.emul_ir_eval(_vp(w), w.size, k, prog.n_nodes, prog.n_terms, _vp(cf) if cf.size else None, cf.shape[0], _vp(v), _vp(out))
             assert (int(out[0]), int(out[1])) == want, (s["name"], rep)
-            # the evaluation plan the kernels run, as one worker and as 32 / 5 cooperating lanes
-            info = np.zeros(4, dtype=np.uint32)
-            for lanes in (0, 32, 5):
-                out[:] = 0
-                rc = emul.emul_ir_plan_eval(_vp(w), w.size, k, prog.n_nodes, prog.n_terms, _vp(cf) if cf.size else None, cf.shape[0], _vp(v),
-                                            lanes, _vp(out), _vp(info))
-                assert rc == 0 and (int(out[0]), int(out[1])) == want, (s["name"], rep, lanes)
+            # the evaluation plan the kernels run, walked by one worker (the thread form)
+            info = np.zeros(5, dtype=np.uint32)
+            out[:] = 0
+            rc = emul.emul_ir_plan_eval(_vp(w), w.size, k, prog.n_nodes, prog.n_terms, _vp(cf) if cf.size else None, cf.shape[0], _vp(v),
+                                        s["declared_degree"], _vp(out), _vp(info))
+            assert rc == 0 and (int(out[0]), int(out[1])) == want, (s["name"], rep)
             assert info[1] == prog.n_nodes + 1
+            assert info[4] == sum(1 for n in s["nodes"] if "affine" in n)
+
+
+def test_pair_form_gives_the_values_at_every_point(oracle, emul, golden_dir):
+    """the kernels' pair form (tables and affine nodes stepped by their differences, the other nodes level by level with
+    one (unit, point) per lane) == the polynomial at T(i) + d (T(i+half) - T(i)), for 32 lanes and for 5, with and
+    without the point 1"""
+    from intelligenceregulation_b200 import backend
+
+    for s in U.load_slots(golden_dir):
+        prog, desc = U.build_program(backend, s, 5000 + s["slot"])
+        w, cf = prog.words(), prog.coef_array()
+        k, deg = prog.n_tables, s["declared_degree"]
+        rng = np.random.default_rng(77 + s["slot"])
+        lo = rng.integers(0, U.P, size=(k, 2), dtype=np.uint64)
+        hi = rng.integers(0, U.P, size=(k, 2), dtype=np.uint64)
+        want = []
+        for d in range(deg + 1):
+            v = [((int(a[0]) + d * (int(b[0]) - int(a[0]))) % U.P, (int(a[1]) + d * (int(b[1]) - int(a[1]))) % U.P) for a, b in zip(lo, hi)]
+            want.append(U.py_eval(desc, v))
+        out = np.zeros((deg + 1, 2), dtype=np.uint64)
+        assert emul.emul_ir_tpair(_vp(w), w.size, k, prog.n_nodes, prog.n_terms, _vp(cf) if cf.size else None, cf.shape[0], _vp(lo), _vp(hi),
+                                  deg, _vp(out)) == 0
+        assert [(int(a), int(b)) for a, b in out] == want, (s["name"], "thread pair form")
+        for lanes, skip in ((32, 0), (5, 1), (32, 1)):
+            out = np.zeros((deg + 1, 2), dtype=np.uint64)
+            rc = emul.emul_ir_pair(_vp(w), w.size, k, prog.n_nodes, prog.n_terms, _vp(cf) if cf.size else None, cf.shape[0], _vp(lo), _vp(hi),
+                                   deg, lanes, skip, _vp(out))
+            assert rc == 0
+            for d in range(deg + 1):
+                exp = (0, 0) if (skip and d == 1) else want[d]
+                assert (int(out[d][0]), int(out[d][1])) == exp, (s["name"], d, lanes, skip)
 
 
 def test_closed_form_families_written_as_programs(oracle):
