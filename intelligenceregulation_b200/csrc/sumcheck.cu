@@ -411,7 +411,7 @@ __global__ void __launch_bounds__(IRT) k_sc_round_ir(const u64* __restrict__ tab
 // thread pair form: one pair per thread, every point; only live tables and node values are kept (slot_ir.cuh).  The long
 // rounds: it evaluates the affine nodes once per pair instead of once per point and needs no interpolation of the tables.
 constexpr u32 IRP_VALUES = ir::MAX_TABLES + ir::MAX_NODES + 1;
-__global__ void __launch_bounds__(IRT) k_sc_round_irp(const u64* __restrict__ tables, size_t stride, u32 half, hlk::IrDev p, int degree,
+__global__ void __launch_bounds__(IRT, 8) k_sc_round_irp(const u64* __restrict__ tables, size_t stride, u32 half, hlk::IrDev p, int degree,
                                                       int eval_one, u64* __restrict__ partials) {
     extern __shared__ __align__(16) u32 ir_smem[];
     __shared__ u64 wsum[IRT / 32][2 * hlk::SC_MAX_POINTS];
