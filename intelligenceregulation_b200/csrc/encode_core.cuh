@@ -249,14 +249,14 @@ struct Fast {
                           u64 y = src[i];
                           if (a.loga) {
                               for (u32 t = 1; t < A; t++)
-                                  y = gl_add(y, gl_mul(src[i + t * N], a.tw_nn[((t * ra) << (lognn - a.loga)) & (nn - 1)]));  // w_A^(t a)
-                              if (ra) y = gl_mul(y, a.tw_nn[((i * ra) << (a.logr - a.loga)) & (nn - 1)]);                     // w_n^(i a)
+                                  y = gl_add(y, gl_mul_fast(src[i + t * N], a.tw_nn[((t * ra) << (lognn - a.loga)) & (nn - 1)]));  // w_A^(t a)
+                              if (ra) y = gl_mul_lazy(y, a.tw_nn[((i * ra) << (a.logr - a.loga)) & (nn - 1)]);                // w_n^(i a); a pass takes lazy words
                           }
                           return y;
                       },
                       [&](u32 k, u64 v) {
                           const u32 i = (n - ((k << a.loga) + ra)) & (n - 1);
-                          const u64 c = gl_mul(v, a.ninv);
+                          const u64 c = gl_mul_fast(v, a.ninv);
                           for (u32 t = 0; t < Tn; t++) {
                               const u32 idx = i + t * n;
                               u64 x = t == 0 ? c : 0;
@@ -264,7 +264,7 @@ struct Fast {
                                   if (idx >= n + a.q) break;
                                   if (idx < a.q) x = gl_sub(x, pad[idx]);
                                   if (idx >= n && idx - n < a.q) x = gl_add(x, pad[idx - n]);
-                                  x = gl_mul(x, a.pows[idx]);
+                                  x = gl_mul_fast(x, a.pows[idx]);
                               }
                               X[idx] = x;
                           }
@@ -284,8 +284,8 @@ struct Fast {
                       u64 y = ENC_LDCG(X + i);
                       // the scratch words from n + q on are never written and never read
                       for (u32 t = 1; t < a.T && i + t * N < live; t++)
-                          y = gl_add(y, gl_mul(ENC_LDCG(X + (size_t)t * N + i), a.tw_nn[(t * s * N) & (nn - 1)]));
-                      if (s) y = gl_mul(y, a.tw_nn[(i * s) & (nn - 1)]);
+                          y = gl_add(y, gl_mul_fast(ENC_LDCG(X + (size_t)t * N + i), a.tw_nn[(t * s * N) & (nn - 1)]));
+                      if (s) y = gl_mul_lazy(y, a.tw_nn[(i * s) & (nn - 1)]);  // a pass takes lazy words
                       return y;
                   },
                   [&](u32 k, u64 v) { dst[(size_t)k << a.logr] = gl_canon_fast(v); }, sync);

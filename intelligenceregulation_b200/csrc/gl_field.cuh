@@ -222,6 +222,9 @@ GL_HD u64 gl_inv(u64 a) {
     return gl_mul(gl_sqn(b, 32), a32);
 }
 
+// canonical product through the carry-chain multiply (device) / the plain one (host)
+GL_HD u64 gl_mul_fast(u64 a, u64 b) { return gl_canon_fast(gl_mul_lazy(a, b)); }
+
 GL_HD fp2 f2(u64 a, u64 b) {
     fp2 r;
     r.c0 = a;
