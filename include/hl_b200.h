@@ -165,7 +165,8 @@ int hl_b200_rounds_new(hl_ctx* ctx, int poly, size_t k, uint32_t n_vars, uint32_
  *     factor        table id, or 0x80000000 | node id (a node refers only to earlier nodes)
  *     coef          index into `coefs` (Fp2 each), or HL_IR_ONE / HL_IR_NEG_ONE / HL_IR_ZERO
  * Limits: k <= 64 tables, 128 nodes, 4096 words, 512 coefficients, degree <= 7.  A malformed stream is
- * HL_B200_ERR_ARG and reaches no kernel.  `degree` is the slot's DECLARED degree (the message length). */
+ * HL_B200_ERR_ARG and reaches no kernel.  `degree` is the slot's DECLARED degree (the message length); where the
+ * graph attains less, the values above the attained degree are extrapolated exactly (gpu/metal.rs:2516-2548). */
 #define HL_IR_NODE 0x80000000u
 #define HL_IR_ONE 0xFFFFFFFFu
 #define HL_IR_NEG_ONE 0xFFFFFFFEu

@@ -24,6 +24,8 @@ struct hl_rounds {
     u64* d_partials = nullptr;
     u64* d_out = nullptr;      // n_vars rows of (2 (degree+1) + 1) Fp2
     u64* d_inv_den = nullptr;
+    u64* d_extrap = nullptr;   // weights of the points above the evaluated degree (data-form polynomials only)
+    u32 eval_degree = 0;
     hlk::ScState* d_state = nullptr;
     hlk::IrDev ir{};           // poly == POLY_IR: the polynomial as data
     u32 tail_len = hlk::SC_TAIL_LEN;
@@ -39,6 +41,7 @@ void free_rounds(hl_rounds* r) {
     dev_free(c, r->d_partials, (size_t)r->max_blocks * (r->degree + 1) * 16);
     dev_free(c, r->d_out, (r->n_vars ? r->n_vars : 1) * r->out_row() * 8);
     dev_free(c, r->d_inv_den, ((size_t)r->degree + 1) * 8);
+    if (r->d_extrap) dev_free(c, r->d_extrap, (size_t)hlk::SC_MAX_POINTS * hlk::SC_MAX_POINTS * 8);
     dev_free(c, r->d_state, sizeof(hlk::ScState));
     if (r->ir.plan) dev_free(c, (void*)r->ir.plan, (size_t)r->ir.plan_words * 4);
     if (r->ir.coefs) dev_free(c, (void*)r->ir.coefs, (size_t)(r->ir.n_coefs ? r->ir.n_coefs : 1) * 16);
@@ -59,6 +62,7 @@ int launch_round(hl_rounds* r, int eval_one, int fs, int use_claim, int recover,
     a.partials = r->d_partials; a.nblocks = nb; a.degree = (int)r->degree; a.round = (int)r->next;
     a.use_claim = use_claim; a.recover = recover; a.fs = fs; a.mask = d_mask; a.mask_half_suffix = d_hs; a.mask_vars = mask_vars;
     a.inv_den = r->d_inv_den; a.state = r->d_state; a.out = r->d_out;
+    a.eval_degree = (int)r->eval_degree; a.extrap = r->d_extrap;
     e = hlk::sc_step(a, c->stream);
     c->stats.kernel_launches++;
     if (e != cudaSuccess) return fail(c, HL_B200_ERR_DEVICE, "round step launch", e);
@@ -95,8 +99,11 @@ int rounds_build(hl_ctx* c, int poly, size_t k, uint32_t n_vars, uint32_t degree
     r->ctx = c; r->poly = poly; r->k = (u32)k; r->n_vars = n_vars; r->degree = degree; r->ncoefs = ncoefs;
     r->stride = r->len = (size_t)1 << n_vars;
     r->max_blocks = hlk::sc_round_blocks((u32)(r->len / 2), c->sm_count);
+    r->eval_degree = degree;
     if (poly == hlk::POLY_IR) {
         const std::vector<u32>& pw = *plan;
+        r->eval_degree = r->ir.eval_degree = pw[16];
+        r->ir.all_points = ir::tpair_all_fits(pw.data()) ? 1 : 0;
         r->ir.plan_words = (u32)pw.size(); r->ir.n_coefs = (u32)ncoefs; r->ir.n_tables = (u32)k;
         r->ir.n_nodes = pw[1]; r->ir.n_units = pw[2];
         if (!hlk::sc_ir_fits(r->ir, (int)degree)) {
@@ -122,6 +129,23 @@ int rounds_build(hl_ctx* c, int poly, size_t k, uint32_t n_vars, uint32_t degree
     if (!rc && !built) rc = h2d(c, r->d_tables, tables, k * r->stride * 16);
     if (!rc && ncoefs) rc = h2d(c, r->d_coefs, coefs, ncoefs * 16);
     if (!rc) rc = h2d(c, r->d_inv_den, inv_den, ((size_t)degree + 1) * 8);
+    if (!rc && r->eval_degree < degree) {
+        // s(p) = sum_i s(i) prod_{j != i} (p - j) / (i - j) over i, j <= eval_degree, for p above it
+        u64 wts[hlk::SC_MAX_POINTS * hlk::SC_MAX_POINTS] = {0};
+        const u32 de = r->eval_degree;
+        for (u32 pnt = de + 1; pnt <= degree; pnt++)
+            for (u32 i = 0; i <= de; i++) {
+                u64 num = 1, den = 1;
+                for (u32 j = 0; j <= de; j++)
+                    if (j != i) {
+                        num = gl_mul(num, gl_from_i64((long long)pnt - (long long)j));
+                        den = gl_mul(den, gl_from_i64((long long)i - (long long)j));
+                    }
+                wts[(pnt - de - 1) * (de + 1) + i] = gl_mul(num, gl_inv(den));
+            }
+        rc = dev_alloc(c, (void**)&r->d_extrap, sizeof wts);
+        if (!rc) rc = h2d(c, r->d_extrap, wts, sizeof wts);
+    }
     if (!rc && poly == hlk::POLY_IR) {
         rc = dev_alloc(c, (void**)&r->ir.plan, (size_t)r->ir.plan_words * 4);
         if (!rc) rc = dev_alloc(c, (void**)&r->ir.coefs, (size_t)(ncoefs ? ncoefs : 1) * 16);
@@ -166,7 +190,7 @@ int hl_b200_rounds_new_ir(hl_ctx* c, size_t k, uint32_t n_vars, uint32_t degree,
         return fail(c, HL_B200_ERR_ARG, buf);
     }
     std::vector<u32> plan;
-    if (int why = ir::build_plan(sh, words, ir::PLAN_UNIT_BUF / (degree + 1), plan)) {
+    if (int why = ir::build_plan(sh, words, degree, plan)) {
         char buf[96];
         snprintf(buf, sizeof buf, "rounds_new_ir: the program does not fit the evaluator's plan (reason %d)", why);
         return fail(c, HL_B200_ERR_UNSUPPORTED, buf);
@@ -200,7 +224,7 @@ int hl_b200_rounds_from_tables_ir(hl_ctx* c, uint32_t degree, hl_tables* t, cons
     ir::Shape sh{(u32)k, n_nodes, n_terms, (u32)ncoefs, (u32)n_words};
     if (ir::validate(sh, words)) return fail(c, HL_B200_ERR_ARG, "rounds_from_tables_ir: malformed program");
     std::vector<u32> plan;
-    if (ir::build_plan(sh, words, ir::PLAN_UNIT_BUF / (degree + 1), plan)) return fail(c, HL_B200_ERR_UNSUPPORTED, "rounds_from_tables_ir: the program does not fit the evaluator's plan");
+    if (ir::build_plan(sh, words, degree, plan)) return fail(c, HL_B200_ERR_UNSUPPORTED, "rounds_from_tables_ir: the program does not fit the evaluator's plan");
     return rounds_build(c, hlk::POLY_IR, k, n_vars, degree, nullptr, coefs, ncoefs, &plan, out, t);
 }
 
@@ -312,6 +336,7 @@ int hl_b200_rounds_batched(hl_rounds* r, uint32_t nd, hl_fs_state* fs, const uin
             a.partials = r->d_partials; a.nblocks = 1; a.degree = (int)r->degree; a.round = (int)r->next;
             a.use_claim = 0; a.recover = fs->recover_one ? 1 : 0; a.fs = 1; a.mask = d_mask; a.mask_half_suffix = d_hs; a.mask_vars = (int)mask_vars;
             a.inv_den = r->d_inv_den; a.state = r->d_state; a.out = r->d_out;
+            a.eval_degree = (int)r->eval_degree; a.extrap = r->d_extrap;
             const u32 left = nd - i;
             cudaError_t e = r->poly == hlk::POLY_IR
                                 ? hlk::sc_tail_ir(r->ir, (int)r->k, r->d_tables, r->stride, (u32)r->len, (int)r->degree, a, (int)left, have_claim ? 1 : 0, c->stream)

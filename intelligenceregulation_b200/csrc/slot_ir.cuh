@@ -144,6 +144,9 @@ inline int validate(const Shape& s, const u32* w) {
 //   pw[8]  total words                    pw[9]  affine nodes (positions 0 .. pw[9])
 //   pw[10] -> bounds of the affine groups (at most PLAN_AFFINE_GROUP units each), pw[11] + 1 entries
 //   pw[13] -> the LIVE tables (read directly by a non-affine node or a term), pw[14] of them
+//   pw[16] the degree the graph ATTAINS along one variable (every table counts 1; slot_ir.rs:380-413): the round
+//             polynomial is evaluated at 0 .. min(declared, attained) only, the points above follow by exact
+//             extrapolation (gpu/metal.rs:2516-2548 does the same)
 //   pw[12] -> a second copy of the non-affine nodes' unit records with COMPACT factor words: live table j -> j,
 //             node -> pw[14] + its position in the node order (record offsets relative to the first such unit),
 //             pw[15] -> their record offsets; the thread pair form keeps only these values in local memory
@@ -152,15 +155,43 @@ inline int validate(const Shape& s, const u32* w) {
 // hence so is every affine node: value at d = 0 and difference are computed once per pair and the other points
 // follow by additions; only the remaining ("sum") nodes are evaluated at every point.
 // ---------------------------------------------------------------------------------------------
-constexpr u32 PLAN_HEAD = 16, PLAN_UNIT_BUF = 256, PLAN_AFFINE_GROUP = PLAN_UNIT_BUF / 2, PLAN_MAX_WORDS = 8192;
+constexpr u32 PLAN_HEAD = 17, PLAN_UNIT_BUF = 256, PLAN_AFFINE_GROUP = PLAN_UNIT_BUF / 2, PLAN_MAX_WORDS = 8192;
 
-// level_cap: units per sum level (the pair form runs a level's units at every point at once: PLAN_UNIT_BUF / points).
+// the degree a well-formed stream attains along one variable
+inline u32 attained_degree(const Shape& s, const u32* w) {
+    std::vector<u32> deg(s.n_nodes, 0);
+    u32 pc = 0, top = 0;
+    auto prod_deg = [&]() {
+        const u32 nf = w[pc + 1];
+        u32 d = 0;
+        for (u32 i = 0; i < nf; i++) d += (w[pc + 2 + i] & IR_NODE) ? deg[w[pc + 2 + i] & ~IR_NODE] : 1u;
+        pc += 2 + nf;
+        return d;
+    };
+    for (u32 n = 0; n < s.n_nodes; n++) {
+        const u32 head = w[pc++], cnt = head >> 8;
+        u32 d = 0;
+        if ((head & 0xFFu) == IR_AFFINE) {
+            d = cnt ? 1u : 0u;
+            pc += 1 + 2 * cnt;
+        } else {
+            for (u32 i = 0; i < cnt; i++) { const u32 x = prod_deg(); d = x > d ? x : d; }
+        }
+        deg[n] = d;
+    }
+    for (u32 t = 0; t < s.n_terms; t++) { const u32 x = prod_deg(); top = x > top ? x : top; }
+    return top;
+}
+
+// degree: the slot's declared degree; the plan evaluates min(declared, attained) + 1 points, and a sum level holds at
+// most PLAN_UNIT_BUF / points units (the pair form runs a level's units at every point at once).
 // Returns 0 and fills `pw`, or a non-zero reason (a node wider than a level, a plan beyond PLAN_MAX_WORDS).
-inline int build_plan(const Shape& s, const u32* w, u32 level_cap, std::vector<u32>& pw) {
+inline int build_plan(const Shape& s, const u32* w, u32 degree, std::vector<u32>& pw) {
     struct Node { u32 id, level; bool affine = false; std::vector<std::vector<u32>> units; };
     std::vector<Node> nodes(s.n_nodes + 1);
     std::vector<u32> level(s.n_nodes + 1, 0);
-    if (level_cap == 0 || level_cap > PLAN_UNIT_BUF) return 3;
+    const u32 attained = attained_degree(s, w), de = attained < degree ? attained : degree;
+    const u32 level_cap = PLAN_UNIT_BUF / (de + 1);
     u32 pc = 0;
     auto read_product = [&](Node& nd) {
         const u32 ci = w[pc++], nf = w[pc++];
@@ -235,6 +266,7 @@ inline int build_plan(const Shape& s, const u32* w, u32 level_cap, std::vector<u
     for (u32 t = 0; t < s.n_tables; t++)
         if (is_live[t]) live.push_back(t);
     pw.assign(PLAN_HEAD, 0);
+    pw[16] = de;
     pw[0] = (u32)lvl.size() - 1; pw[1] = NN; pw[2] = (u32)uoff.size(); pw[9] = NA; pw[11] = (u32)agrp.size() - 1; pw[14] = (u32)live.size();
     pw[3] = (u32)pw.size(); pw.insert(pw.end(), lvl.begin(), lvl.end());
     pw[4] = (u32)pw.size(); pw.insert(pw.end(), order.begin(), order.end());
@@ -327,6 +359,74 @@ GL_HD fp2 tpair_sums(const u32* pw, const fp2* cf, fp2* V) {
         V[nl + k] = acc;
     }
     return acc;
+}
+
+// The same, unit by unit with every point at once: a unit's record is decoded ONCE per pair, its affine-type factors
+// (live tables, affine nodes) are stepped in registers, and the products of the points are independent chains.
+// W[(k - na) * npw + p] holds the non-affine node at position k at point p (npw = points evaluated, at most
+// TPAIR_POINTS); out receives the final node's values.  With skip_one the point 1 is left zero.
+constexpr u32 TPAIR_POINTS = 6, TPAIR_SUM_NODES = 40, TPAIR_AFFINE_VALUES = 128;
+GL_HD bool tpair_all_fits(const u32* pw) {
+    return pw[16] + 1 <= TPAIR_POINTS && pw[1] - pw[9] <= TPAIR_SUM_NODES && pw[14] + pw[9] <= TPAIR_AFFINE_VALUES;
+}
+GL_HD void tpair_sums_all(const u32* pw, const fp2* cf, const fp2* V, const fp2* D, fp2* W, bool skip_one, fp2* out) {
+    const u32 *nus = pw + pw[5], *cw = pw + pw[12], *coff = pw + pw[15];
+    const u32 nl = pw[14], na = pw[9], nn = pw[1], u_base = nus[na], npw = pw[16] + 1, naff = nl + na;
+    fp2 acc[TPAIR_POINTS];
+    for (u32 k = na; k < nn; k++) {
+#pragma unroll
+        for (u32 p = 0; p < TPAIR_POINTS; p++) acc[p] = f2(0, 0);
+        for (u32 u = nus[k]; u < nus[k + 1]; u++) {
+            const u32* r = cw + coff[u - u_base];
+            const u32 ci = r[0], nf = r[1];
+            fp2 x[TPAIR_POINTS];
+            if (nf == 0) {
+                const fp2 c = coef_value(ci, cf);
+#pragma unroll
+                for (u32 p = 0; p < TPAIR_POINTS; p++) x[p] = c;
+            } else {
+                // first factor with the coefficient folded in: coef (v + p d) = coef v + p (coef d) for an affine-type factor
+                const u32 s0 = r[2];
+                if (s0 < naff) {
+                    fp2 v = coef_mul(ci, cf, V[s0]);
+                    const fp2 d = coef_mul(ci, cf, D[s0]);
+#pragma unroll
+                    for (u32 p = 0; p < TPAIR_POINTS; p++) {
+                        x[p] = v;
+                        if (p + 1 < npw) v = f2_add(v, d);
+                    }
+                } else {
+#pragma unroll
+                    for (u32 p = 0; p < TPAIR_POINTS; p++)
+                        if (p < npw && !(skip_one && p == 1)) x[p] = coef_mul(ci, cf, W[(s0 - naff) * npw + p]);
+                }
+                for (u32 i = 1; i < nf; i++) {
+                    const u32 si = r[2 + i];
+                    if (si < naff) {
+                        fp2 v = V[si];
+                        const fp2 d = D[si];
+#pragma unroll
+                        for (u32 p = 0; p < TPAIR_POINTS; p++) {
+                            if (p < npw && !(skip_one && p == 1)) x[p] = mul_mixed(x[p], v);
+                            if (p + 1 < npw) v = f2_add(v, d);
+                        }
+                    } else {
+#pragma unroll
+                        for (u32 p = 0; p < TPAIR_POINTS; p++)
+                            if (p < npw && !(skip_one && p == 1)) x[p] = mul_mixed(x[p], W[(si - naff) * npw + p]);
+                    }
+                }
+            }
+#pragma unroll
+            for (u32 p = 0; p < TPAIR_POINTS; p++)
+                if (p < npw && !(skip_one && p == 1)) acc[p] = f2_add(acc[p], x[p]);
+        }
+#pragma unroll
+        for (u32 p = 0; p < TPAIR_POINTS; p++)
+            if (p < npw) W[(k - na) * npw + p] = (skip_one && p == 1) ? f2(0, 0) : acc[p];
+    }
+#pragma unroll
+    for (u32 p = 0; p < TPAIR_POINTS; p++) out[p] = (p < npw && !(skip_one && p == 1)) ? acc[p] : f2(0, 0);
 }
 
 // ---- pair form: `lanes` cooperating workers (a warp; the host emulation runs the lanes of a phase one after

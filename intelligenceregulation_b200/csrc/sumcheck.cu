@@ -140,6 +140,17 @@ __device__ void step_body(const ScStep& a, StepSmem& sm, int lane) {
     fp2* s = reinterpret_cast<fp2*>(sums);
     if (lane == 0 && a.use_claim) s[1] = f2_sub(st->claim, s[0]);  // s(1) = claim - s(0) (rounds.rs:137-140)
     __syncwarp();
+    if (a.extrap && a.eval_degree < a.degree) {
+        // a polynomial of degree eval_degree is fixed by its values at 0..eval_degree: the points above, exactly
+        fp2 v = f2(0, 0);
+        if (lane > a.eval_degree && lane < np) {
+            const u64* wrow = a.extrap + (size_t)(lane - a.eval_degree - 1) * (a.eval_degree + 1);
+            for (int i = 0; i <= a.eval_degree; i++) v = f2_add(v, f2_mul_base(s[i], wrow[i]));
+        }
+        __syncwarp();
+        if (lane > a.eval_degree && lane < np) s[lane] = v;
+        __syncwarp();
+    }
     u64* orow = a.out + (size_t)j * (2 * (size_t)np + 1) * 2;
     if (lane < np) st2(orow + 2 * lane, s[lane]);
     if (!a.fs) return;  // plain round(): the host drives the transcript
@@ -437,7 +448,7 @@ __global__ void __launch_bounds__(IRT, 8) k_sc_round_irp(const u64* __restrict__
             df = f2_sub(ld2(tb + 2 * ((size_t)i + half)), lo);
         });
         acc[0] = f2_add(acc[0], ir::tpair_sums(pw, cf_s, V));
-        for (int d = 1; d <= degree; d++) {
+        for (int d = 1; d <= (int)p.eval_degree; d++) {
             ir::tpair_step(pw, V, D);
             if (d == 1 && !eval_one) continue;
             const fp2 v = ir::tpair_sums(pw, cf_s, V);
@@ -456,6 +467,63 @@ __global__ void __launch_bounds__(IRT, 8) k_sc_round_irp(const u64* __restrict__
     }
     if (lane == 0) {
         for (int d = 0; d < np; d++) { wsum[warp][2 * d] = acc[d].c0; wsum[warp][2 * d + 1] = acc[d].c1; }
+    }
+    __syncthreads();
+    if ((int)threadIdx.x < 2 * np) {
+        u64 s = 0;
+#pragma unroll
+        for (int w = 0; w < IRT / 32; w++) s = gl_add(s, wsum[w][threadIdx.x]);
+        partials[(size_t)blockIdx.x * 2 * np + threadIdx.x] = s;
+    }
+}
+
+// The same with every unit evaluated at all points at once (slot_ir.cuh tpair_sums_all): a fifth of the record decoding
+// and of the value loads, and independent product chains per point.  For plans within its fixed array sizes.
+__global__ void __launch_bounds__(IRT, 4) k_sc_round_irq(const u64* __restrict__ tables, size_t stride, u32 half, hlk::IrDev p, int degree,
+                                                         int eval_one, u64* __restrict__ partials) {
+    extern __shared__ __align__(16) u32 ir_smem[];
+    __shared__ u64 wsum[IRT / 32][2 * hlk::SC_MAX_POINTS];
+    fp2* cf_s;
+    ir_stage(p, ir_smem, cf_s, IRT);
+    __syncthreads();
+    const u32* pw = ir_smem;
+    const u32 nl = pw[14];
+    const u32* live = pw + pw[13];
+    const bool skip_one = !eval_one && p.eval_degree >= 1;
+    fp2 V[ir::TPAIR_AFFINE_VALUES], D[ir::TPAIR_AFFINE_VALUES], W[ir::TPAIR_SUM_NODES * ir::TPAIR_POINTS];
+    fp2 acc[ir::TPAIR_POINTS];
+#pragma unroll
+    for (u32 d = 0; d < ir::TPAIR_POINTS; d++) acc[d] = f2(0, 0);
+    for (u32 i = blockIdx.x * IRT + threadIdx.x; i < half; i += gridDim.x * IRT) {
+        for (u32 j = 0; j < nl; j++) {
+            const u64* tb = tables + 2 * (size_t)live[j] * stride;
+            V[j] = ld2(tb + 2 * (size_t)i);
+            D[j] = f2_sub(ld2(tb + 2 * ((size_t)i + half)), V[j]);
+        }
+        ir::tpair_affine(pw, cf_s, V, D, [&](u32 t, fp2& lo, fp2& df) {
+            const u64* tb = tables + 2 * (size_t)t * stride;
+            lo = ld2(tb + 2 * (size_t)i);
+            df = f2_sub(ld2(tb + 2 * ((size_t)i + half)), lo);
+        });
+        fp2 res[ir::TPAIR_POINTS];
+        ir::tpair_sums_all(pw, cf_s, V, D, W, skip_one, res);
+#pragma unroll
+        for (u32 d = 0; d < ir::TPAIR_POINTS; d++) acc[d] = f2_add(acc[d], res[d]);
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, np = degree + 1;
+#pragma unroll
+    for (u32 d = 0; d < ir::TPAIR_POINTS; d++) {
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+            acc[d].c0 = gl_add(acc[d].c0, shfl_down64(acc[d].c0, off));
+            acc[d].c1 = gl_add(acc[d].c1, shfl_down64(acc[d].c1, off));
+        }
+    }
+    if (lane < 2 * hlk::SC_MAX_POINTS) wsum[warp][lane] = 0;
+    __syncwarp();
+    if (lane == 0) {
+#pragma unroll
+        for (u32 d = 0; d < ir::TPAIR_POINTS; d++) { wsum[warp][2 * d] = acc[d].c0; wsum[warp][2 * d + 1] = acc[d].c1; }
     }
     __syncthreads();
     if ((int)threadIdx.x < 2 * np) {
@@ -493,7 +561,8 @@ __device__ __forceinline__ void ir_pair_item(const ir::Pair& a, const u64* __res
 
 __device__ __forceinline__ ir::Pair ir_pair_setup(const hlk::IrDev& p, const u32* pw_s, fp2* cf_s, u32 warp, int degree, bool skip_one) {
     ir::Pair a;
-    const u32 np = (u32)degree + 1, ids = p.n_tables + p.n_nodes;
+    (void)degree;
+    const u32 np = p.eval_degree + 1, ids = p.n_tables + p.n_nodes;
     fp2* area = cf_s + p.n_coefs + (size_t)warp * ir::pair_area(p.n_tables, p.n_nodes, np);
     a.pw = pw_s; a.cf = cf_s; a.V = area; a.DV = area + (size_t)ids * np; a.UB = a.DV + ids;
     a.n_tables = p.n_tables; a.np = np; a.npe = skip_one ? np - 1 : np;
@@ -508,8 +577,8 @@ __global__ void __launch_bounds__(IRC_MAX_WARPS * 32) k_sc_round_irc(const u64* 
     ir_stage(p, ir_smem, cf_s, blockDim.x);
     __syncthreads();
     const u32 lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5, np = (u32)degree + 1;
-    const ir::Pair a = ir_pair_setup(p, ir_smem, cf_s, warp, degree, !eval_one);
-    const u32 fin = (p.n_tables + p.n_nodes - 1) * np;  // the final node's values
+    const ir::Pair a = ir_pair_setup(p, ir_smem, cf_s, warp, degree, !eval_one && p.eval_degree >= 1);
+    const u32 fin = (p.n_tables + p.n_nodes - 1) * a.np;  // the final node's values
     fp2 acc = f2(0, 0);  // lane pi: the sum at evaluated point pi
     for (u32 i = blockIdx.x * nwarps + warp; i < half; i += gridDim.x * nwarps) {
         ir_pair_item(a, tables, stride, i, half, lane);
@@ -537,6 +606,7 @@ __global__ void __launch_bounds__(IR_TAIL_T) k_sc_tail_ir(u64* __restrict__ tabl
     __shared__ u64 mask_s[2 * (63 * (hlk::SC_MAX_POINTS - 1) + 2)];
     __shared__ u64 hs_s[2 * 63];
     __shared__ u64 invden_s[hlk::SC_MAX_POINTS];
+    __shared__ u64 extrap_s[hlk::SC_MAX_POINTS * hlk::SC_MAX_POINTS];
     fp2* cf_s;
     const u32 nthreads = blockDim.x, nwarps = nthreads >> 5;
     ir_stage(p, ir_smem, cf_s, nthreads);
@@ -551,10 +621,12 @@ __global__ void __launch_bounds__(IR_TAIL_T) k_sc_tail_ir(u64* __restrict__ tabl
             for (u32 i = threadIdx.x; i < 2u * a.mask_vars; i += nthreads) hs_s[i] = a.mask_half_suffix[i];
         }
         if ((int)threadIdx.x < np) invden_s[threadIdx.x] = a.inv_den[threadIdx.x];
+        if (a.extrap && (int)threadIdx.x < (a.degree - a.eval_degree) * (a.eval_degree + 1)) extrap_s[threadIdx.x] = a.extrap[threadIdx.x];
     }
     hlk::ScState* const st_global = a.state;
     if (a.mask) { a.mask = mask_s; a.mask_half_suffix = hs_s; }
     a.inv_den = invden_s;
+    if (a.extrap) a.extrap = extrap_s;
     a.state = &st_s;
     __syncthreads();
     for (int rd = 0; rd < nrounds; rd++) {
@@ -564,8 +636,8 @@ __global__ void __launch_bounds__(IR_TAIL_T) k_sc_tail_ir(u64* __restrict__ tabl
             for (u32 w = 0; w < nwarps; w++) wsum[w][threadIdx.x] = 0;
         __syncthreads();
         if constexpr (PAIR_FORM) {
-            const ir::Pair pa = ir_pair_setup(p, ir_smem, cf_s, warp, degree, have_claim);
-            const u32 fin = (p.n_tables + p.n_nodes - 1) * (u32)np;
+            const ir::Pair pa = ir_pair_setup(p, ir_smem, cf_s, warp, degree, have_claim && p.eval_degree >= 1);
+            const u32 fin = (p.n_tables + p.n_nodes - 1) * pa.np;
             fp2 acc = f2(0, 0);
             for (u32 i = warp; i < half; i += nwarps) {
                 ir_pair_item(pa, tables, stride, i, half, lane);
@@ -578,7 +650,7 @@ __global__ void __launch_bounds__(IR_TAIL_T) k_sc_tail_ir(u64* __restrict__ tabl
 #pragma unroll
             for (int d = 0; d < hlk::SC_MAX_POINTS; d++) acc[d] = f2(0, 0);
             fp2 tv[ir::MAX_TABLES], nv[ir::MAX_NODES + 1];
-            for (u32 x = threadIdx.x; x < half * (u32)np; x += nthreads) {
+            for (u32 x = threadIdx.x; x < half * (p.eval_degree + 1); x += nthreads) {
                 const u32 d = x / half, i = x - d * half;
                 if (d == 1 && have_claim) continue;
                 for (u32 t = 0; t < p.n_tables; t++) tv[t] = ir_table_value(tables + 2 * (size_t)t * stride, i, half, d);
@@ -639,7 +711,7 @@ bool ir_pair_form(const hlk::IrDev& p, u32 half) { return ir_pair_capable(p) && 
 bool ir_thread_pair_form(const hlk::IrDev& p, u32 half) { return ir_pair_capable(p) && half >= (1u << 15); }
 constexpr size_t IR_SMEM_BUDGET = 200 * 1024;
 size_t ir_fixed_bytes(const hlk::IrDev& p) { return (((size_t)p.plan_words + 3) & ~(size_t)3) * 4 + (size_t)p.n_coefs * 16 + 16; }
-size_t ir_area_bytes(const hlk::IrDev& p, int degree) { return (size_t)ir::pair_area(p.n_tables, p.n_nodes, (u32)degree + 1) * 16; }
+size_t ir_area_bytes(const hlk::IrDev& p, int degree) { (void)degree; return (size_t)ir::pair_area(p.n_tables, p.n_nodes, p.eval_degree + 1) * 16; }
 // warps of a pair-form CTA: as many as the shared memory holds, at most `want`
 int ir_pair_warps(const hlk::IrDev& p, int degree, int want) {
     const size_t fixed = ir_fixed_bytes(p), area = ir_area_bytes(p, degree);
@@ -710,10 +782,13 @@ cudaError_t sc_round_ir(const IrDev& p, int k, const u64* tables, size_t stride,
         return cudaGetLastError();
     }
     if (ir_thread_pair_form(p, half)) {
-        k_sc_round_irp<<<nblocks, IRT, ir_fixed_bytes(p), s>>>(tables, stride, half, p, degree, eval_one, partials);
+        if (p.all_points)
+            k_sc_round_irq<<<nblocks, IRT, ir_fixed_bytes(p), s>>>(tables, stride, half, p, degree, eval_one, partials);
+        else
+            k_sc_round_irp<<<nblocks, IRT, ir_fixed_bytes(p), s>>>(tables, stride, half, p, degree, eval_one, partials);
         return cudaGetLastError();
     }
-    dim3 grid(nblocks, (unsigned)degree + 1);
+    dim3 grid(nblocks, p.eval_degree + 1);  // the rows above are extrapolated by the step
     k_sc_round_ir<<<grid, IRT, ir_fixed_bytes(p), s>>>(tables, stride, half, p, degree, eval_one, partials);
     return cudaGetLastError();
 }

@@ -35,6 +35,8 @@ struct ScStep {
     const u64* mask_half_suffix;  // per round j: sum_{i>j} u_i(1)/2
     int mask_vars;
     const u64* inv_den;         // degree+1 inverse Lagrange denominators
+    int eval_degree;            // the sums arrive at the points 0..eval_degree; the points above are extrapolated
+    const u64* extrap;          // (degree - eval_degree) rows of eval_degree + 1 base-field weights, or NULL
     ScState* state;
     u64* out;                   // per round: (degree+1) sums, (degree+1) masked, r  (Fp2 each)
 };
@@ -44,6 +46,8 @@ struct IrDev {
     const u32* plan;   // the evaluation plan (slot_ir.cuh)
     const u64* coefs;  // n_coefs Fp2
     u32 plan_words, n_coefs, n_tables, n_nodes /* with the final one */, n_units;
+    u32 eval_degree;   // min(declared, attained): the points the kernels evaluate are 0 .. eval_degree
+    int all_points;    // the plan fits the thread pair form that evaluates a unit at every point at once
 };
 
 u32 sc_round_blocks(u32 half, int sm_count);

@@ -22,7 +22,7 @@ extern "C" int emul_ir_plan_eval(const u32* words, u32 n_words, u32 n_tables, u3
                                  const u64* values, u32 degree, u64* out, u32* plan_info /* sum levels, nodes, units, words, affine nodes */) {
     ir::Shape s{n_tables, n_nodes, n_terms, n_coefs, n_words};
     std::vector<u32> pw;
-    if (int why = ir::build_plan(s, words, ir::PLAN_UNIT_BUF / (degree + 1), pw)) return why;
+    if (int why = ir::build_plan(s, words, degree, pw)) return why;
     plan_info[0] = pw[0]; plan_info[1] = pw[1]; plan_info[2] = pw[2]; plan_info[3] = pw[8]; plan_info[4] = pw[9];
     std::vector<fp2> nv(pw[1], f2(0xA5A5A5A5A5A5A5A5ull, 0x5A5A5A5A5A5A5A5Aull));  // poisoned: a read before the write shows
     fp2 r = ir::plan_eval(pw.data(), reinterpret_cast<const fp2*>(coefs), reinterpret_cast<const fp2*>(values), nv.data());
@@ -38,8 +38,8 @@ extern "C" int emul_ir_pair(const u32* words, u32 n_words, u32 n_tables, u32 n_n
                             const u64* lo, const u64* hi, u32 degree, u32 lanes, int skip_one, u64* out /* (degree + 1) x 2 */) {
     ir::Shape s{n_tables, n_nodes, n_terms, n_coefs, n_words};
     std::vector<u32> pw;
-    const u32 np = degree + 1;
-    if (int why = ir::build_plan(s, words, ir::PLAN_UNIT_BUF / np, pw)) return why;
+    if (int why = ir::build_plan(s, words, degree, pw)) return why;
+    const u32 np = pw[16] + 1;  // the points the kernels evaluate: 0 .. min(declared, attained degree)
     const fp2 poison = f2(0xA5A5A5A5A5A5A5A5ull, 0x5A5A5A5A5A5A5A5Aull);
     const u32 ids = n_tables + pw[1];
     std::vector<fp2> area(ir::pair_area(n_tables, pw[1], np), poison);
@@ -61,7 +61,7 @@ extern "C" int emul_ir_pair(const u32* words, u32 n_words, u32 n_tables, u32 n_n
         for (u32 l = 0; l < lanes; l++) ir::pair_level_nodes(a, lv, l, lanes);
     }
     const u32 fin = (n_tables + pw[1] - 1) * np;
-    for (u32 d = 0; d < 2 * np; d++) out[d] = 0;
+    for (u32 d = 0; d < 2 * (degree + 1); d++) out[d] = 0;
     for (u32 pi = 0; pi < a.npe; pi++) {
         const fp2 v = a.V[fin + a.point(pi)];
         out[2 * a.point(pi)] = v.c0;
@@ -72,10 +72,11 @@ extern "C" int emul_ir_pair(const u32* words, u32 n_words, u32 n_tables, u32 n_n
 
 // The thread pair form: one worker, one pair, every point, compact values (live tables and nodes only).
 extern "C" int emul_ir_tpair(const u32* words, u32 n_words, u32 n_tables, u32 n_nodes, u32 n_terms, const u64* coefs, u32 n_coefs,
-                             const u64* lo, const u64* hi, u32 degree, u64* out /* (degree + 1) x 2 */) {
+                             const u64* lo, const u64* hi, u32 degree, int all_points /* 0 point by point, 1 all at once, 2 all but 1 */,
+                             u64* out /* (degree + 1) x 2 */) {
     ir::Shape s{n_tables, n_nodes, n_terms, n_coefs, n_words};
     std::vector<u32> pw;
-    if (int why = ir::build_plan(s, words, ir::PLAN_UNIT_BUF / (degree + 1), pw)) return why;
+    if (int why = ir::build_plan(s, words, degree, pw)) return why;
     const fp2* cf = reinterpret_cast<const fp2*>(coefs);
     const fp2 poison = f2(0xA5A5A5A5A5A5A5A5ull, 0x5A5A5A5A5A5A5A5Aull);
     const u32 nl = pw[14];
@@ -89,7 +90,16 @@ extern "C" int emul_ir_tpair(const u32* words, u32 n_words, u32 n_tables, u32 n_
         l = f2(lo[2 * t], lo[2 * t + 1]);
         df = f2_sub(f2(hi[2 * t], hi[2 * t + 1]), l);
     });
-    for (u32 d = 0; d <= degree; d++) {
+    for (u32 d = 0; d < 2 * (degree + 1); d++) out[d] = 0;
+    if (all_points) {  // unit by unit, every point at once
+        if (!ir::tpair_all_fits(pw.data())) return -1;
+        std::vector<fp2> W((size_t)ir::TPAIR_SUM_NODES * ir::TPAIR_POINTS, poison);
+        fp2 res[ir::TPAIR_POINTS];
+        ir::tpair_sums_all(pw.data(), cf, V.data(), D.data(), W.data(), all_points == 2, res);
+        for (u32 d = 0; d <= pw[16]; d++) { out[2 * d] = res[d].c0; out[2 * d + 1] = res[d].c1; }
+        return 0;
+    }
+    for (u32 d = 0; d <= pw[16]; d++) {
         if (d) ir::tpair_step(pw.data(), V.data(), D.data());
         const fp2 v = ir::tpair_sums(pw.data(), cf, V.data());
         out[2 * d] = v.c0;

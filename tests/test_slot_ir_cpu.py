@@ -83,21 +83,27 @@ def test_pair_form_gives_the_values_at_every_point(oracle, emul, golden_dir):
         rng = np.random.default_rng(77 + s["slot"])
         lo = rng.integers(0, U.P, size=(k, 2), dtype=np.uint64)
         hi = rng.integers(0, U.P, size=(k, 2), dtype=np.uint64)
+        de = min(deg, max(U.degrees(s)[1]))  # the kernels evaluate 0 .. min(declared, attained); the step extrapolates the rest
         want = []
         for d in range(deg + 1):
             v = [((int(a[0]) + d * (int(b[0]) - int(a[0]))) % U.P, (int(a[1]) + d * (int(b[1]) - int(a[1]))) % U.P) for a, b in zip(lo, hi)]
             want.append(U.py_eval(desc, v))
-        out = np.zeros((deg + 1, 2), dtype=np.uint64)
-        assert emul.emul_ir_tpair(_vp(w), w.size, k, prog.n_nodes, prog.n_terms, _vp(cf) if cf.size else None, cf.shape[0], _vp(lo), _vp(hi),
-                                  deg, _vp(out)) == 0
-        assert [(int(a), int(b)) for a, b in out] == want, (s["name"], "thread pair form")
+        for mode in (0, 1, 2):  # point by point; every point per unit; the same without the point 1
+            out = np.zeros((deg + 1, 2), dtype=np.uint64)
+            rc = emul.emul_ir_tpair(_vp(w), w.size, k, prog.n_nodes, prog.n_terms, _vp(cf) if cf.size else None, cf.shape[0], _vp(lo), _vp(hi),
+                                    deg, mode, _vp(out))
+            if rc == -1 and mode:
+                continue  # beyond the all-points form's limits: the kernels use the point-by-point form there
+            assert rc == 0
+            exp = [(0, 0) if (mode == 2 and d == 1) else want[d] for d in range(de + 1)]
+            assert [(int(a), int(b)) for a, b in out[: de + 1]] == exp, (s["name"], "thread pair form", mode)
         for lanes, skip in ((32, 0), (5, 1), (32, 1)):
             out = np.zeros((deg + 1, 2), dtype=np.uint64)
             rc = emul.emul_ir_pair(_vp(w), w.size, k, prog.n_nodes, prog.n_terms, _vp(cf) if cf.size else None, cf.shape[0], _vp(lo), _vp(hi),
                                    deg, lanes, skip, _vp(out))
             assert rc == 0
             for d in range(deg + 1):
-                exp = (0, 0) if (skip and d == 1) else want[d]
+                exp = (0, 0) if (skip and d == 1) or d > de else want[d]
                 assert (int(out[d][0]), int(out[d][1])) == exp, (s["name"], d, lanes, skip)
 
 
