@@ -121,6 +121,8 @@ def run_reference(args, rank: int) -> None:
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import hl_oracle as o
 
+    if "LOCAL_RANK" in os.environ:  # torchrun pins OMP_NUM_THREADS=1 for its workers; this arm is the only worker that computes
+        o.set_threads(len(os.sched_getaffinity(0)))
     w = WORK
     nn = (1 << w["log_cols"]) * w["inv_rate"]
     rows_s = 128
@@ -452,6 +454,8 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
         sys.path.insert(0, os.path.join(ROOT, "oracle"))
         import hl_oracle as o
 
+        if "LOCAL_RANK" in os.environ:
+            o.set_threads(len(os.sched_getaffinity(0)))
         rows_s = 32
         sec = cpu_commit_sample(o, rows_s, "")
         rows_s = int(min(rows, max(32, rows_s * 10.0 / max(sec, 1e-3)) // 8 * 8))  # about ten seconds of CPU work

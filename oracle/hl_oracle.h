@@ -117,6 +117,7 @@ void or_logup_query_values(const int32_t *idx, const int32_t *outv, size_t n, co
 void or_fp2_sum(const uint64_t *v, size_t n, uint64_t out[2]);
 
 int or_num_threads(void);
+void or_set_threads(int n);
 
 #ifdef __cplusplus
 }

@@ -74,6 +74,10 @@ def num_threads() -> int:
     return int(_lib.or_num_threads())
 
 
+def set_threads(n: int) -> None:
+    _lib.or_set_threads(C.c_int(n))
+
+
 # ----------------------------------------------------------------------------- field
 def fp_add(a, b): return int(_lib.or_fp_add(a, b))
 def fp_sub(a, b): return int(_lib.or_fp_sub(a, b))

@@ -10,6 +10,15 @@
 #include <omp.h>
 #endif
 
+/* the launcher of a multi-process job pins OMP_NUM_THREADS to 1; the CPU baseline wants the host's cores */
+void or_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int or_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();
