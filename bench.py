@@ -155,6 +155,17 @@ def workload_config(world: int) -> dict:
             "published_baseline": "26.0 GB/s, reference Metal backend on Apple M3 Ultra, same shape"}
 
 
+def structured_rhos(dense: np.ndarray) -> np.ndarray:
+    k, rows, _ = dense.shape
+    out = np.zeros_like(dense)
+    out[k - 1] = dense[k - 1]
+    for g in range(k - 1):
+        r0 = (g * 64) % (rows - 40)
+        out[g, r0:r0 + 32] = dense[g, r0:r0 + 32]
+        out[g, rows - 3:rows - 1] = dense[g, rows - 3:rows - 1]
+    return out
+
+
 def device_extras(dev, backend, np_data, np_pads, np_pows, col_key) -> dict:
     """Device time (CUDA events inside the library, per kernel family) of the rest of one block's device work at the
     same shape: the opening of `A` (38 row combinations with pads, 280 gathered columns), a 2^21-point degree-3
@@ -177,6 +188,15 @@ def device_extras(dev, backend, np_data, np_pads, np_pows, col_key) -> dict:
     t = ctx.timing_read(reset=True)
     out["open_A_fold_38rho_ms"] = t["fold"][0] / 3
     out["open_A_gather_280cols_ms"] = t["gather"][0] / 3
+    # the shape of a real opening (pcs.rs:851-891, 952-973): 37 group vectors that live on their claim's 32 plane rows and
+    # the two mask rows, one dense proximity vector; the dense figure above is the worst case
+    srho = structured_rhos(rhos)
+    for _ in range(2):
+        st.fold_rows_with_pads(srho)
+    ctx.timing_read(reset=True)
+    for _ in range(3):
+        st.fold_rows_with_pads(srho)
+    out["open_A_fold_37_plane_vectors_1_dense_ms"] = ctx.timing_read(reset=True)["fold"][0] / 3
     st.free()
     n = 21
     tables = splitmix_fp(79, 3 * (1 << n) * 2).reshape(3, 1 << n, 2)
@@ -279,6 +299,9 @@ def cpu_extras(o, backend, np_data) -> dict:
     rhos = splitmix_fp(77, 4 * rows * 2).reshape(4, rows, 2)
     out["open_A_fold_38rho_ms"] = timed(lambda: o.fold_rows(np_data, rows, n, n, 1, rhos)) * 38 / 4
     notes["open_A_fold_38rho_ms"] = "4 of 38 vectors over the message columns, scaled"
+    srho = structured_rhos(splitmix_fp(77, 38 * rows * 2).reshape(38, rows, 2))
+    out["open_A_fold_37_plane_vectors_1_dense_ms"] = timed(lambda: o.fold_rows(np_data, rows, n, n, 1, srho))
+    notes["open_A_fold_37_plane_vectors_1_dense_ms"] = "message columns only; the restatement skips zero weights as the reference does"
     nv = 21
     tables = splitmix_fp(79, 3 * (1 << nv) * 2).reshape(3, 1 << nv, 2)
     alpha = splitmix_fp(80, 2).reshape(1, 2)

@@ -234,24 +234,74 @@ int hl_b200_store_fold(hl_store* st, const uint64_t* rhos, size_t k, int with_pa
     if (k > 0xFFFFu * 8u) return fail(c, HL_B200_ERR_ARG, "store_fold: too many vectors");
     std::lock_guard<std::mutex> g(c->mu);
     cudaSetDevice(c->device);
-    const u32 n = (u32)st->n(), q = with_pads ? st->q : 0, w = n + q;
-    u64 *d_rhos = nullptr, *d_out = nullptr;
-    const size_t rb = k * (size_t)st->rows * 16, ob = k * (size_t)w * 16;
-    int rc = dev_alloc(c, (void**)&d_rhos, rb);
-    if (!rc) rc = dev_alloc(c, (void**)&d_out, ob);
-    if (!rc) rc = h2d(c, d_rhos, rhos, rb);
+    const u32 n = (u32)st->n(), q = with_pads ? st->q : 0, w = n + q, rows = st->rows;
+    // An opening's group vectors are zero outside their claims' rows (pcs.rs:851-891), its proximity vector is dense.
+    // Vectors with few non-zero rows go to the list kernel, the others to the dense one; both write the caller's order.
+    std::vector<u32> dense_map, sparse_map, s_off{0}, s_rows;
+    std::vector<u64> dense_rhos, s_w;
+    for (size_t g = 0; g < k; g++) {
+        const uint64_t* r = rhos + g * (size_t)rows * 2;
+        u32 support = 0;
+        for (u32 i = 0; i < rows; i++) support += (r[2 * i] | r[2 * i + 1]) != 0;
+        if (support * 8u <= rows) {
+            for (u32 i = 0; i < rows; i++)
+                if (r[2 * i] | r[2 * i + 1]) { s_rows.push_back(i); s_w.push_back(r[2 * i]); s_w.push_back(r[2 * i + 1]); }
+            s_off.push_back((u32)s_rows.size());
+            sparse_map.push_back((u32)g);
+        } else {
+            dense_rhos.insert(dense_rhos.end(), r, r + (size_t)rows * 2);
+            dense_map.push_back((u32)g);
+        }
+    }
+    const u32 kd = (u32)dense_map.size(), ks = (u32)sparse_map.size();
+    u64 *d_rhos = nullptr, *d_out = nullptr, *d_sw = nullptr;
+    u32 *d_dmap = nullptr, *d_smap = nullptr, *d_soff = nullptr, *d_srows = nullptr;
+    const size_t rb = (size_t)(kd ? kd : 1) * rows * 16, ob = k * (size_t)w * 16, ne = s_rows.size() ? s_rows.size() : 1;
+    int rc = dev_alloc(c, (void**)&d_out, ob);
+    if (!rc && kd) {
+        rc = dev_alloc(c, (void**)&d_rhos, rb);
+        if (!rc) rc = dev_alloc(c, (void**)&d_dmap, kd * 4);
+        if (!rc) rc = h2d(c, d_rhos, dense_rhos.data(), (size_t)kd * rows * 16);
+        if (!rc) rc = h2d(c, d_dmap, dense_map.data(), kd * 4);
+    }
+    if (!rc && ks) {
+        rc = dev_alloc(c, (void**)&d_smap, ks * 4);
+        if (!rc) rc = dev_alloc(c, (void**)&d_soff, (ks + 1) * 4);
+        if (!rc) rc = dev_alloc(c, (void**)&d_srows, ne * 4);
+        if (!rc) rc = dev_alloc(c, (void**)&d_sw, ne * 16);
+        if (!rc) rc = h2d(c, d_smap, sparse_map.data(), ks * 4);
+        if (!rc) rc = h2d(c, d_soff, s_off.data(), (ks + 1) * 4);
+        if (!rc && s_rows.size()) rc = h2d(c, d_srows, s_rows.data(), s_rows.size() * 4);
+        if (!rc && s_rows.size()) rc = h2d(c, d_sw, s_w.data(), s_w.size() * 8);
+    }
     if (!rc) {
         Timed t(c, HL_T_FOLD);
         // hiding form: the message is the resident data (the encoding is not systematic, pcs.rs:985-987);
         // plain form: the systematic positions of the encoding (pcs.rs:332-340)
-        cudaError_t e = st->zk ? hlk::fold_rows(st->d_data, st->rows, n, n, 1, q ? st->d_pads : nullptr, q, q, d_rhos, (u32)k, d_out, w, c->stream)
-                               : hlk::fold_rows(st->d_enc, st->rows, n, st->nn(), 1u << st->logr, nullptr, 0, 0, d_rhos, (u32)k, d_out, w, c->stream);
-        c->stats.kernel_launches++;
+        const u64* src = st->zk ? st->d_data : st->d_enc;
+        const size_t ld = st->zk ? n : st->nn();
+        const u32 ir = st->zk ? 1u : 1u << st->logr;
+        const u64* src2 = st->zk && q ? st->d_pads : nullptr;
+        cudaError_t e = cudaSuccess;
+        if (kd) {
+            e = hlk::fold_rows(src, rows, n, ld, ir, src2, q, q, d_rhos, kd, d_dmap, d_out, w, c->stream);
+            c->stats.kernel_launches++;
+        }
+        if (e == cudaSuccess && ks) {
+            e = hlk::fold_rows_sparse(src, n, ld, ir, src2, q, q, d_soff, d_srows, d_sw, ks, d_smap, d_out, w, c->stream);
+            c->stats.kernel_launches++;
+        }
         if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "fold launch", e);
     }
     if (!rc) rc = d2h(c, out, d_out, ob);
     if (!rc) rc = sync(c, "store_fold");
-    dev_free(c, d_rhos, rb); dev_free(c, d_out, ob);
+    if (d_rhos) dev_free(c, d_rhos, rb);
+    if (d_dmap) dev_free(c, d_dmap, kd * 4);
+    if (d_smap) dev_free(c, d_smap, ks * 4);
+    if (d_soff) dev_free(c, d_soff, (ks + 1) * 4);
+    if (d_srows) dev_free(c, d_srows, ne * 4);
+    if (d_sw) dev_free(c, d_sw, ne * 16);
+    if (d_out) dev_free(c, d_out, ob);
     if (!rc) c->stats.folds++;
     return rc;
 }

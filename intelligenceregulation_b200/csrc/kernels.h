@@ -25,7 +25,9 @@ cudaError_t merkle_levels(uint32_t* d_levels, u32 nn, const uint32_t* d_node_key
 // store.cu
 // out[g] = rho_g^T [src | src2]: ncols entries from src (element (i, j) at src[i ld + j ir]), then ncols2 from src2 (may be NULL)
 cudaError_t fold_rows(const u64* src, u32 rows, u32 ncols, size_t ld, u32 ir, const u64* src2, u32 ncols2, size_t ld2,
-                      const u64* d_rhos, u32 k, u64* d_out, u32 out_ld, cudaStream_t st);
+                      const u64* d_rhos, u32 k, const u32* d_out_map, u64* d_out, u32 out_ld, cudaStream_t st);
+cudaError_t fold_rows_sparse(const u64* src, u32 ncols, size_t ld, u32 ir, const u64* src2, u32 ncols2, size_t ld2, const u32* d_off,
+                             const u32* d_rows, const u64* d_weights, u32 k, const u32* d_out_map, u64* d_out, u32 out_ld, cudaStream_t st);
 cudaError_t gather_columns(const u64* enc, u32 rows, size_t nn, const u64* d_idx, u32 nidx, u64* d_out, cudaStream_t st);
 
 // misc.cu

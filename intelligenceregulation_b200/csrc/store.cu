@@ -38,6 +38,7 @@ struct FoldSeg {
 
 __global__ void __launch_bounds__(FOLD_THREADS) k_fold_rows(FoldSeg seg0, FoldSeg seg1, u32 rows,
                                                             const u64* __restrict__ rhos /* k x rows x 2 */, u32 k,
+                                                            const u32* __restrict__ out_map /* vector -> output row, or NULL */,
                                                             u64* __restrict__ out, u32 out_ld) {
     __shared__ uint2 rho_s[FOLD_BLOCK][FOLD_G * 2];  // [row][vector * 2 + component] = (low half, high half)
     const bool second = blockIdx.x >= seg0.tiles;
@@ -122,12 +123,40 @@ __global__ void __launch_bounds__(FOLD_THREADS) k_fold_rows(FoldSeg seg0, FoldSe
         for (int v = 0; v < FOLD_RPT; v++) {
             const u32 g = grp * FOLD_RPT + v;
             if (g < ng) {
-                u64* o = out + ((size_t)(g0 + g) * out_ld + out_off + col) * 2;
+                u64* o = out + ((size_t)(out_map ? out_map[g0 + g] : g0 + g) * out_ld + out_off + col) * 2;
                 o[0] = run[2 * v];
                 o[1] = run[2 * v + 1];
             }
         }
     }
+}
+
+// The same combination for a vector that is zero outside a few rows (an opening's group weights live on their claims'
+// rows only, pcs.rs:851-891): the rows and weights arrive as a list, one thread per column walks it.  Products are
+// summed as 128-bit integers with a wrap count and reduced once per component (2^128 = -2^32 mod p).
+constexpr int SPARSE_COLS = 256;
+__global__ void __launch_bounds__(SPARSE_COLS) k_fold_sparse(FoldSeg seg0, FoldSeg seg1, const u32* __restrict__ off /* vectors + 1 */,
+                                                            const u32* __restrict__ srow, const u64* __restrict__ sw /* 2 per entry */,
+                                                            const u32* __restrict__ out_map, u64* __restrict__ out, u32 out_ld) {
+    const bool second = blockIdx.x >= seg0.tiles;
+    const FoldSeg& sg = second ? seg1 : seg0;
+    const u32 col = (second ? blockIdx.x - seg0.tiles : blockIdx.x) * SPARSE_COLS + threadIdx.x;
+    if (col >= sg.ncols) return;
+    const u32 v = blockIdx.y;
+    const u64* p = sg.src + (size_t)col * sg.ir;
+    u64 lo0 = 0, hi0 = 0, w0 = 0, lo1 = 0, hi1 = 0, w1 = 0;
+    for (u32 e = off[v]; e < off[v + 1]; e++) {
+        const u64 d = p[(size_t)srow[e] * sg.ld];
+        const gl_wide p0 = gl_mulw(sw[2 * (size_t)e], d), p1 = gl_mulw(sw[2 * (size_t)e + 1], d);
+        u64 t = lo0 + p0.lo, c = t < lo0; lo0 = t;
+        t = hi0 + p0.hi; u64 c2 = t < hi0; hi0 = t + c; c2 += hi0 < t; w0 += c2;
+        t = lo1 + p1.lo; c = t < lo1; lo1 = t;
+        t = hi1 + p1.hi; c2 = t < hi1; hi1 = t + c; c2 += hi1 < t; w1 += c2;
+    }
+    const u64 two128 = 0xFFFFFFFE00000001ull;  // 2^128 mod p
+    u64* o = out + ((size_t)out_map[v] * out_ld + sg.out_off + col) * 2;
+    o[0] = gl_add(gl_reduce128(lo0, hi0), gl_mul(w0, two128));
+    o[1] = gl_add(gl_reduce128(lo1, hi1), gl_mul(w1, two128));
 }
 
 // out[c * rows + i] = enc[i * nn + idx[c]]   (pcs.rs:1055-1067; order of idx, duplicates repeated)
@@ -143,12 +172,22 @@ __global__ void k_gather_cols(const u64* __restrict__ enc, u32 rows, size_t nn, 
 namespace hlk {
 
 cudaError_t fold_rows(const u64* src, u32 rows, u32 ncols, size_t ld, u32 ir, const u64* src2, u32 ncols2, size_t ld2,
-                      const u64* d_rhos, u32 k, u64* d_out, u32 out_ld, cudaStream_t st) {
+                      const u64* d_rhos, u32 k, const u32* d_out_map, u64* d_out, u32 out_ld, cudaStream_t st) {
     if (k == 0 || ncols == 0) return cudaSuccess;
     FoldSeg a{src, ld, ncols, ir, 0u, (ncols + FOLD_COLS - 1) / FOLD_COLS};
     FoldSeg b{src2, ld2, src2 ? ncols2 : 0u, 1u, ncols, src2 ? (ncols2 + FOLD_COLS - 1) / FOLD_COLS : 0u};
     dim3 grid(a.tiles + b.tiles, (k + FOLD_G - 1) / FOLD_G);
-    k_fold_rows<<<grid, FOLD_THREADS, 0, st>>>(a, b, rows, d_rhos, k, d_out, out_ld);
+    k_fold_rows<<<grid, FOLD_THREADS, 0, st>>>(a, b, rows, d_rhos, k, d_out_map, d_out, out_ld);
+    return cudaGetLastError();
+}
+
+cudaError_t fold_rows_sparse(const u64* src, u32 ncols, size_t ld, u32 ir, const u64* src2, u32 ncols2, size_t ld2, const u32* d_off,
+                             const u32* d_rows, const u64* d_weights, u32 k, const u32* d_out_map, u64* d_out, u32 out_ld, cudaStream_t st) {
+    if (k == 0 || ncols == 0) return cudaSuccess;
+    FoldSeg a{src, ld, ncols, ir, 0u, (ncols + SPARSE_COLS - 1) / SPARSE_COLS};
+    FoldSeg b{src2, ld2, src2 ? ncols2 : 0u, 1u, ncols, src2 ? (ncols2 + SPARSE_COLS - 1) / SPARSE_COLS : 0u};
+    dim3 grid(a.tiles + b.tiles, k);
+    k_fold_sparse<<<grid, SPARSE_COLS, 0, st>>>(a, b, d_off, d_rows, d_weights, d_out_map, d_out, out_ld);
     return cudaGetLastError();
 }
 

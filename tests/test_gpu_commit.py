@@ -172,6 +172,35 @@ def test_rows_longer_than_one_shared_memory_transform(dev, oracle, shape):
     store.free()
 
 
+def test_fold_with_sparse_dense_and_zero_vectors_in_one_call(dev, oracle):
+    """An opening mixes group vectors that live on a few rows with a dense proximity vector (pcs.rs:851-891, 952-973); the
+    store routes them to two kernels and must return them in the caller's order.  Also: an all-zero vector, a vector at
+    the routing threshold, the plain (systematic) store."""
+    o = oracle
+    log_cols, ir, rows, q = 9, 4, 320, 24
+    n, nn = 1 << log_cols, (1 << log_cols) * ir
+    data, pads = rnd(31, rows * n), rnd(32, rows * q)
+    full = np.stack([rnd2(40 + g, rows) for g in range(9)])
+    rhos = np.zeros_like(full)
+    rhos[0] = full[0]                       # dense
+    rhos[1, 5:37] = full[1, 5:37]           # a plane's 32 rows
+    rhos[2, 317:320] = full[2, 317:320]     # the mask rows at the end
+    # rhos[3] stays all zero
+    rhos[4, ::8] = full[4, ::8]             # exactly rows / 8 non-zero rows: still the list kernel
+    rhos[5, ::7] = full[5, ::7]             # just above: the dense kernel
+    rhos[6] = full[6]
+    rhos[7, 100, 1] = full[7, 100, 1]       # a single imaginary word
+    rhos[8, 0:40] = full[8, 0:40]
+    store, _ = dev.try_commit_zk_keyed(log_cols, ir, data, pads, o.coset_powers(7, nn), 12, None)
+    want = np.concatenate([o.fold_rows(data, rows, n, n, 1, rhos), o.fold_rows(pads, rows, q, q, 1, rhos)], axis=1)
+    assert (store.fold_rows_with_pads(rhos) == want).all()
+    assert (store.fold_rows(rhos) == want[:, :n]).all()
+    store.free()
+    store, _ = dev.try_commit(log_cols, ir, data, 12)
+    assert (store.fold_rows(rhos) == want[:, :n]).all()
+    store.free()
+
+
 def _splitmix_fp(seed, n):
     out, s = [], seed
     for _ in range(n):
