@@ -68,6 +68,8 @@ int hl_b200_set_encoder(hl_ctx* ctx, int fast);
  * Runs the encoder's butterfly arithmetic on registers only, on every SM, and reports radix-2 Goldilocks
  * butterflies per second: the denominator for the encoder's integer-pipe utilisation. */
 int hl_b200_butterfly_peak(hl_ctx* ctx, uint32_t iters, double* butterflies_per_second);
+/* the same for the column hash: register-resident BLAKE3 compressions per second, all SMs */
+int hl_b200_compress_peak(hl_ctx* ctx, uint32_t iters, double* compressions_per_second);
 
 /* ---- field self-test: metal_probe_field (tests/zk60_metal_commit.rs:69-89), k_probe ----
  * out3n[3i..3i+2] = (a_i + b_i, a_i - b_i, a_i * b_i) */

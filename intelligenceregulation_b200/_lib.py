@@ -81,6 +81,7 @@ SIGNATURES.update({
 })
 
 SIGNATURES["hl_b200_butterfly_peak"] = (_int, [_vp, _u32, C.POINTER(C.c_double)])
+SIGNATURES["hl_b200_compress_peak"] = (_int, [_vp, _u32, C.POINTER(C.c_double)])
 
 SIGNATURES["hl_b200_set_alloc_cap"] = (_int, [_vp, _sz])
 

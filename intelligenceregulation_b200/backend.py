@@ -112,6 +112,12 @@ class Context:
         self.check(self.lib.hl_b200_butterfly_peak(self.h, iters, C.byref(v)))
         return float(v.value)
 
+    def compress_peak(self, iters: int = 400) -> float:
+        """Register-resident BLAKE3 compressions per second on this device (the column hash's integer ceiling)."""
+        v = C.c_double()
+        self.check(self.lib.hl_b200_compress_peak(self.h, iters, C.byref(v)))
+        return float(v.value)
+
     def probe_field(self, a, b) -> np.ndarray:
         """metal_probe_field: (a+b, a-b, a*b) per pair, shape (n, 3)."""
         a, b = _u64(a), _u64(b)

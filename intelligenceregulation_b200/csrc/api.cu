@@ -282,4 +282,36 @@ int hl_b200_butterfly_peak(hl_ctx* c, uint32_t iters, double* butterflies_per_se
     return rc;
 }
 
+int hl_b200_compress_peak(hl_ctx* c, uint32_t iters, double* compressions_per_second) {
+    if (!c || !compressions_per_second || iters == 0) return fail(c, HL_B200_ERR_ARG, "compress_peak: argument");
+    std::lock_guard<std::mutex> g(c->mu);
+    cudaSetDevice(c->device);
+    std::vector<u64> seed(4096);
+    u64 x = 88172645463325252ULL;
+    for (auto& v : seed) { x ^= x << 13; x ^= x >> 7; x ^= x << 17; v = gl_canon(x); }
+    u64 *d_seed = nullptr, *d_sink = nullptr;
+    int rc = dev_alloc(c, (void**)&d_seed, 4096 * 8);
+    if (!rc) rc = dev_alloc(c, (void**)&d_sink, 8);
+    if (!rc) rc = h2d(c, d_seed, seed.data(), 4096 * 8);
+    cudaEvent_t a = nullptr, b = nullptr;
+    float ms = 0.f;
+    const int blocks = c->sm_count * 16;
+    if (!rc) {
+        cudaEventCreate(&a); cudaEventCreate(&b);
+        cudaError_t e = hlk::compress_peak(d_seed, d_sink, 8, blocks, c->stream);  // warm-up
+        cudaEventRecord(a, c->stream);
+        if (e == cudaSuccess) e = hlk::compress_peak(d_seed, d_sink, iters, blocks, c->stream);
+        cudaEventRecord(b, c->stream);
+        c->stats.kernel_launches += 2;
+        if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "compress_peak launch", e);
+    }
+    if (!rc) rc = sync(c, "compress_peak");
+    if (!rc && cudaEventElapsedTime(&ms, a, b) != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "compress_peak timing");
+    if (a) cudaEventDestroy(a);
+    if (b) cudaEventDestroy(b);
+    dev_free(c, d_seed, 4096 * 8); dev_free(c, d_sink, 8);
+    if (!rc) *compressions_per_second = (double)blocks * 128.0 * iters / (ms * 1e-3);
+    return rc;
+}
+
 }  // extern "C"

@@ -33,5 +33,6 @@ cudaError_t gather_columns(const u64* enc, u32 rows, size_t nn, const u64* d_idx
 // misc.cu
 cudaError_t probe_field(const u64* d_a, const u64* d_b, size_t n, u64* d_out3, cudaStream_t st);
 cudaError_t butterfly_peak(const u64* d_seed, u64* d_sink, u32 iters, int blocks, cudaStream_t st);
+cudaError_t compress_peak(const u64* d_seed, u64* d_sink, u32 iters, int blocks, cudaStream_t st);
 
 }  // namespace hlk

@@ -1,4 +1,5 @@
 // Small kernels: the field self-test.
+#include "b3.cuh"
 #include "gl_field.cuh"
 #include "kernels.h"
 
@@ -39,9 +40,29 @@ __global__ void __launch_bounds__(256) k_butterfly_peak(const u64* __restrict__ 
     for (int j = 0; j < 16; j++) x ^= e[j];
     if (x == 0x5EEDull) sink[0] = x;  // keeps the loop alive; practically never true
 }
+// Register-resident BLAKE3 compressions: the column hash's integer ceiling (its adds, xors and rotates all issue on the
+// ALU pipe).  The chaining value feeds the next compression, the message words are perturbed by it.
+__global__ void __launch_bounds__(128) k_compress_peak(const u64* __restrict__ seed, u64* __restrict__ sink, u32 iters) {
+    const size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    uint32_t cv[8], m[16];
+#pragma unroll
+    for (int j = 0; j < 8; j++) cv[j] = (uint32_t)seed[(t * 8 + j) & 4095];
+#pragma unroll
+    for (int j = 0; j < 16; j++) m[j] = (uint32_t)(seed[(t * 16 + j + 31) & 4095] >> 32);
+    for (u32 it = 0; it < iters; it++) {
+        b3::compress(cv, m, it, 64, 0);
+        m[it & 15] ^= cv[0];
+    }
+    if ((cv[0] ^ cv[7]) == 0x5EEDu) sink[0] = cv[1];
+}
 }  // namespace
 
 namespace hlk {
+cudaError_t compress_peak(const u64* d_seed, u64* d_sink, u32 iters, int blocks, cudaStream_t st) {
+    k_compress_peak<<<blocks, 128, 0, st>>>(d_seed, d_sink, iters);
+    return cudaGetLastError();
+}
+
 cudaError_t butterfly_peak(const u64* d_seed, u64* d_sink, u32 iters, int blocks, cudaStream_t st) {
     k_butterfly_peak<<<blocks, 256, 0, st>>>(d_seed, d_sink, iters);
     return cudaGetLastError();
