@@ -31,10 +31,10 @@ sys.path.insert(0, ROOT)
 
 WORK = {"log_cols": 14, "inv_rate": 2, "q": 280, "rows": 2504, "profile": "hashline-zk-mr1/b200-bench/1"}
 P = 0xFFFFFFFF00000001
-# dram__bytes_read.sum + dram__bytes_write.sum of one k_encode_fast<14,512> launch at this workload (ncu capture summarised in
+# dram__bytes_read.sum + dram__bytes_write.sum of one k_encode_fast<14,1024> launch at this workload (ncu capture summarised in
 # profiles/k_encode_fast_8b_A.md); the kernel's shape is fixed, so the figure is per launch of the timed kernel
 ENCODE_DRAM_TRAFFIC = 783_464_960 + 1_224_247_000
-PUBLISHED_GBPS = 26.0  # the reference's Metal backend on an M3 Ultra at this exact shape
+PUBLISHED_GBPS = 26.0  # the reference's own published figure: its Metal backend on an M3 Ultra at this exact shape
 
 
 def splitmix_fp(seed: int, n: int) -> np.ndarray:
@@ -245,9 +245,9 @@ def device_extras(dev, backend, np_data, np_pads, np_pows, col_key) -> dict:
     st.free()
     # the heaviest slot polynomial of a block as data: the recorded structure of the D zero-check (60 tables, 71 nodes,
     # declared degree 5) with seeded coefficients, at 2^19 points (the 8B block domain of this slot: 128 tokens x width 4096), through the interpreting evaluator
-    prog, deg = slot14_program(backend.SlotProgram)
+    prog, deg, base = slot14_program(backend.SlotProgram)
     n = 19
-    tables = splitmix_fp(87, prog.n_tables * (1 << n) * 2).reshape(prog.n_tables, 1 << n, 2)
+    tables = slot14_tables(prog, base, n)
     mask = splitmix_fp(88, ((n + 1) * deg + 2) * 2).reshape(-1, 2)
     for rep in range(3):
         ev = backend.B200Rounds(ctx, prog, tables, deg)
@@ -281,7 +281,17 @@ def slot14_program(SP):
             prog.sum([(coef(c), [fw(f) for f in fs]) for c, fs in nd["sum"]])
     for t in slot["terms"]:
         prog.term(coef(t["coef"]), t["wrapper"], [fw(f) for f in t["inner"]])
-    return prog, slot["declared_degree"]
+    return prog, slot["declared_degree"], [f == "base" for f in slot["table_fields"]]
+
+
+def slot14_tables(prog, base, nv):
+    """seeded tables; the ones the reference records as base-valued (witness planes, public shape tables: 40 of 60) keep a
+    zero imaginary word, as they do until the first fold"""
+    t = splitmix_fp(87, prog.n_tables * (1 << nv) * 2).reshape(prog.n_tables, 1 << nv, 2)
+    for i, b in enumerate(base):
+        if b:
+            t[i, :, 1] = 0
+    return t
 
 
 def cpu_extras(o, backend, np_data) -> dict:
@@ -319,9 +329,9 @@ def cpu_extras(o, backend, np_data) -> dict:
     coords = [("fixed", (int(a), int(b))) for a, b in splitmix_fp(91, 6).reshape(3, 2)] + [("rho", k) for k in range(19)]
     out["tables_eq_2^21_plus_plane_2^19_x8_ms"] = timed(lambda: (o.eq_cube(point, 21, 0), o.priv_table(coords, [(0, (1, 0))], np_data, 19)))
     notes["tables_eq_2^21_plus_plane_2^19_x8_ms"] = "walked host builder, one thread"
-    prog, deg = slot14_program(backend.SlotProgram)
+    prog, deg, base = slot14_program(backend.SlotProgram)
     nv = 19
-    tables = splitmix_fp(87, prog.n_tables * (1 << nv) * 2).reshape(prog.n_tables, 1 << nv, 2)
+    tables = slot14_tables(prog, base, nv)
     mask = splitmix_fp(88, ((nv + 1) * deg + 2) * 2).reshape(-1, 2)
     o.ir_set(prog.words(), prog.n_nodes, prog.n_terms)
     out["sumcheck_slot_program_60tables_71nodes_deg5_2^19_ms"] = timed(lambda: o.sc_prove(o.POLY_IR, tables, deg, o.Transcript(b"bench"), coefs=prog.coef_array(),

@@ -2,7 +2,7 @@
 
 Run once, in a checkout that has the reference tree mounted:
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path to the reference checkout>
 
 It copies DATA only (recorded test vectors and agreement corpora), never source:
 
@@ -46,4 +46,6 @@ def main(ref: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit(__doc__)
+    main(sys.argv[1])

@@ -8,7 +8,7 @@ challenge, i.e. an extension element).  Labels, notes and prose are dropped; coe
 the export (they are challenges), so the tests draw them from a seed by class.
 
 Run in the build container (the reference tree is not present where the GPU tests run):
-    python tests/golden/make_ir_golden.py /root/reference
+    python tests/golden/make_ir_golden.py <path to the reference checkout>
 """
 import json
 import os
@@ -40,4 +40,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit(__doc__)
+    main(sys.argv[1])
