@@ -242,6 +242,8 @@ def device_extras(dev, backend, np_data, np_pads, np_pows, col_key) -> dict:
         t21.free(); t19.free()
     t = ctx.timing_read(reset=True)
     out["tables_eq_2^21_plus_plane_2^19_x8_ms"] = t["tables"][0] / 2
+    slot_replay(dev, backend, st, rows, 1 << log_cols)  # warm-up: first launches size the device's local-memory pool
+    out["slot_replay"] = slot_replay(dev, backend, st, rows, 1 << log_cols)
     st.free()
     # the heaviest slot polynomial of a block as data: the recorded structure of the D zero-check (60 tables, 71 nodes,
     # declared degree 5) with seeded coefficients, at 2^19 points (the 8B block domain of this slot: 128 tokens x width 4096), through the interpreting evaluator
@@ -292,6 +294,63 @@ def slot14_tables(prog, base, nv):
         if b:
             t[i, :, 1] = 0
     return t
+
+
+def slot_replay(dev, backend, st, rows, n) -> dict:
+    """All 23 slot sumchecks of one block, replayed on the device at the sizes the reference records for its 125M shape
+    (the one shape whose slot graphs it exports: tests/golden/slot_ir_m125.json): per slot the tables are built ON THE
+    DEVICE from the resident rows of a commitment (an eq cube for table 0, committed planes for the rest: base-valued
+    where the reference records a base table, partially evaluated at one fixed coordinate where it records an extension
+    table), then the masked sumcheck runs with the device Fiat-Shamir step.  Coefficients, points and plane positions are
+    seeded; the graphs, table counts, degrees and cube sizes are the reference's.  This is device WORK of the recorded
+    shape, not a proof: the protocol layer that would drive it is the reference's Rust crate."""
+    import json as _json
+
+    ctx = dev.ctx
+    slots = _json.load(open(os.path.join(ROOT, "tests", "golden", "slot_ir_m125.json")))["slots"]
+    SP = backend.SlotProgram
+    words_avail = rows * n
+    per_slot, total_tables_ms, total_rounds_ms, total_bytes = {}, 0.0, 0.0, 0
+    cs = iter(splitmix_fp(95, 1 << 16).tolist())
+
+    def coef(cls):
+        return "one" if cls == "one" else (next(cs) % (1 << 40), 0) if cls == "kbase" else (next(cs), next(cs))
+
+    def fw(f):
+        return SP.node(f["n"]) if "n" in f else f["t"]
+
+    for sl in slots:
+        nv, k, deg = sl["main_rounds"], len(sl["table_fields"]), sl["declared_degree"]
+        prog = SP(k)
+        for nd in sl["nodes"]:
+            if "affine" in nd:
+                prog.affine(coef("kbase") if nd["konst"] else "zero", [(coef(c), t) for c, t in nd["affine"]])
+            else:
+                prog.sum([(coef(c), [fw(f) for f in fs]) for c, fs in nd["sum"]])
+        for t in sl["terms"]:
+            prog.term(coef(t["coef"]), t["wrapper"], [fw(f) for f in t["inner"]])
+        point = np.array([next(cs) for _ in range(2 * nv)], dtype=np.uint64).reshape(nv, 2)
+        mask = np.array([next(cs) for _ in range(2 * ((nv + 1) * deg + 2))], dtype=np.uint64).reshape(-1, 2)
+        ctx.timing_read(reset=True)
+        tabs = backend.B200Tables(ctx, k, nv)
+        tabs.plan_eq(0, point, 0)
+        for t in range(1, k):
+            if sl["table_fields"][t] == "base":
+                coords, span = [("rho", v) for v in range(nv)], 1 << nv
+            else:
+                coords, span = [("fixed", (next(cs), next(cs)))] + [("rho", v) for v in range(nv)], 2 << nv
+            off = (next(cs) % max(1, words_avail - span)) if span < words_avail else 0
+            tabs.plan_plane(t, st, coords, [(int(off), (1, 0))])
+        ev = backend.B200Rounds(ctx, prog, tabs, deg)
+        ev.batched(nv, bytes(32), 0, None, mask=mask, mask_vars=nv + 1, mask_c=(3, 5), recover_one=True, claim=(0, 0))
+        ev.free()
+        tm = ctx.timing_read(reset=True)
+        per_slot[sl["name"]] = round(tm["tables"][0] + tm["rounds"][0], 3)
+        total_tables_ms += tm["tables"][0]
+        total_rounds_ms += tm["rounds"][0]
+        total_bytes += k * (16 << nv)
+    return {"slots": len(slots), "tables_ms": total_tables_ms, "sumchecks_ms": total_rounds_ms, "table_bytes": total_bytes, "per_slot_ms": per_slot,
+            "shape": "the reference's recorded 125M slot graphs (T512 / d768 / f2048): 23 slots, 258 tables, cubes of 2^8 .. 2^22 points"}
 
 
 def cpu_extras(o, backend, np_data) -> dict:
