@@ -42,7 +42,15 @@ GL_HD fp2 coef_value(u32 ci, const fp2* cf) {
 // a b where either may lie in the base field (imaginary word zero): one or two base multiplications instead of
 // the extension product's four.  Witness planes and public shape tables are base-valued until the first fold
 // (slot_ir.rs:160-177), which is half of a sumcheck's work; within a warp the test goes the same way for every lane.
-GL_HD fp2 mul_mixed(fp2 a, fp2 b) {
+// Called, not inlined, on the device: the evaluators' loops are unrolled over the points, and a copy of the four
+// multiplication forms at every site makes kernels that wait on instruction fetch (measured: a quarter of all stall
+// cycles of the thread pair form).
+#ifdef __CUDACC__
+#define IR_CALL static __host__ __device__ __noinline__
+#else
+#define IR_CALL inline
+#endif
+IR_CALL fp2 mul_mixed(fp2 a, fp2 b) {
     if (a.c1 == 0) return b.c1 == 0 ? f2(gl_mul(a.c0, b.c0), 0) : f2_mul_base(b, a.c0);
     if (b.c1 == 0) return f2_mul_base(a, b.c0);
     return f2_mul(a, b);
