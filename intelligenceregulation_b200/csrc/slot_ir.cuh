@@ -377,21 +377,24 @@ constexpr u32 TPAIR_POINTS = 6, TPAIR_SUM_NODES = 40, TPAIR_AFFINE_VALUES = 128;
 GL_HD bool tpair_all_fits(const u32* pw) {
     return pw[16] + 1 <= TPAIR_POINTS && pw[1] - pw[9] <= TPAIR_SUM_NODES && pw[14] + pw[9] <= TPAIR_AFFINE_VALUES;
 }
-GL_HD void tpair_sums_all(const u32* pw, const fp2* cf, const fp2* V, const fp2* D, fp2* W, bool skip_one, fp2* out) {
+// NPW = points evaluated (pw[16] + 1), SKIP = the point 1 is not evaluated: compile-time, so that the unrolled point loops
+// carry no tests.
+template <u32 NPW, bool SKIP>
+GL_HD void tpair_sums_all_t(const u32* pw, const fp2* cf, const fp2* V, const fp2* D, fp2* W, fp2* out) {
     const u32 *nus = pw + pw[5], *cw = pw + pw[12], *coff = pw + pw[15];
-    const u32 nl = pw[14], na = pw[9], nn = pw[1], u_base = nus[na], npw = pw[16] + 1, naff = nl + na;
-    fp2 acc[TPAIR_POINTS];
+    const u32 nl = pw[14], na = pw[9], nn = pw[1], u_base = nus[na], naff = nl + na;
+    fp2 acc[NPW];
     for (u32 k = na; k < nn; k++) {
 #pragma unroll
-        for (u32 p = 0; p < TPAIR_POINTS; p++) acc[p] = f2(0, 0);
+        for (u32 p = 0; p < NPW; p++) acc[p] = f2(0, 0);
         for (u32 u = nus[k]; u < nus[k + 1]; u++) {
             const u32* r = cw + coff[u - u_base];
             const u32 ci = r[0], nf = r[1];
-            fp2 x[TPAIR_POINTS];
+            fp2 x[NPW];
             if (nf == 0) {
                 const fp2 c = coef_value(ci, cf);
 #pragma unroll
-                for (u32 p = 0; p < TPAIR_POINTS; p++) x[p] = c;
+                for (u32 p = 0; p < NPW; p++) x[p] = c;
             } else {
                 // first factor with the coefficient folded in: coef (v + p d) = coef v + p (coef d) for an affine-type factor
                 const u32 s0 = r[2];
@@ -399,14 +402,14 @@ GL_HD void tpair_sums_all(const u32* pw, const fp2* cf, const fp2* V, const fp2*
                     fp2 v = coef_mul(ci, cf, V[s0]);
                     const fp2 d = coef_mul(ci, cf, D[s0]);
 #pragma unroll
-                    for (u32 p = 0; p < TPAIR_POINTS; p++) {
+                    for (u32 p = 0; p < NPW; p++) {
                         x[p] = v;
-                        if (p + 1 < npw) v = f2_add(v, d);
+                        if (p + 1 < NPW) v = f2_add(v, d);
                     }
                 } else {
 #pragma unroll
-                    for (u32 p = 0; p < TPAIR_POINTS; p++)
-                        if (p < npw && !(skip_one && p == 1)) x[p] = coef_mul(ci, cf, W[(s0 - naff) * npw + p]);
+                    for (u32 p = 0; p < NPW; p++)
+                        if (!(SKIP && p == 1)) x[p] = coef_mul(ci, cf, W[(s0 - naff) * NPW + p]);
                 }
                 for (u32 i = 1; i < nf; i++) {
                     const u32 si = r[2 + i];
@@ -414,27 +417,37 @@ GL_HD void tpair_sums_all(const u32* pw, const fp2* cf, const fp2* V, const fp2*
                         fp2 v = V[si];
                         const fp2 d = D[si];
 #pragma unroll
-                        for (u32 p = 0; p < TPAIR_POINTS; p++) {
-                            if (p < npw && !(skip_one && p == 1)) x[p] = mul_mixed(x[p], v);
-                            if (p + 1 < npw) v = f2_add(v, d);
+                        for (u32 p = 0; p < NPW; p++) {
+                            if (!(SKIP && p == 1)) x[p] = mul_mixed(x[p], v);
+                            if (p + 1 < NPW) v = f2_add(v, d);
                         }
                     } else {
 #pragma unroll
-                        for (u32 p = 0; p < TPAIR_POINTS; p++)
-                            if (p < npw && !(skip_one && p == 1)) x[p] = mul_mixed(x[p], W[(si - naff) * npw + p]);
+                        for (u32 p = 0; p < NPW; p++)
+                            if (!(SKIP && p == 1)) x[p] = mul_mixed(x[p], W[(si - naff) * NPW + p]);
                     }
                 }
             }
 #pragma unroll
-            for (u32 p = 0; p < TPAIR_POINTS; p++)
-                if (p < npw && !(skip_one && p == 1)) acc[p] = f2_add(acc[p], x[p]);
+            for (u32 p = 0; p < NPW; p++)
+                if (!(SKIP && p == 1)) acc[p] = f2_add(acc[p], x[p]);
         }
 #pragma unroll
-        for (u32 p = 0; p < TPAIR_POINTS; p++)
-            if (p < npw) W[(k - na) * npw + p] = (skip_one && p == 1) ? f2(0, 0) : acc[p];
+        for (u32 p = 0; p < NPW; p++) W[(k - na) * NPW + p] = (SKIP && p == 1) ? f2(0, 0) : acc[p];
     }
 #pragma unroll
-    for (u32 p = 0; p < TPAIR_POINTS; p++) out[p] = (p < npw && !(skip_one && p == 1)) ? acc[p] : f2(0, 0);
+    for (u32 p = 0; p < TPAIR_POINTS; p++) out[p] = f2(0, 0);
+#pragma unroll
+    for (u32 p = 0; p < NPW; p++)
+        if (!(SKIP && p == 1)) out[p] = acc[p];
+}
+
+// host-side dispatch for the emulation (the kernels are instantiated per point count)
+inline void tpair_sums_all(const u32* pw, const fp2* cf, const fp2* V, const fp2* D, fp2* W, bool skip_one, fp2* out) {
+    const u32 npw = pw[16] + 1;
+#define IR_TP(N) case N: if (skip_one) tpair_sums_all_t<N, true>(pw, cf, V, D, W, out); else tpair_sums_all_t<N, false>(pw, cf, V, D, W, out); break;
+    switch (npw) { IR_TP(1) IR_TP(2) IR_TP(3) IR_TP(4) IR_TP(5) IR_TP(6) }
+#undef IR_TP
 }
 
 // ---- pair form: `lanes` cooperating workers (a warp; the host emulation runs the lanes of a phase one after

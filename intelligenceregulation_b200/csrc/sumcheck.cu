@@ -479,8 +479,9 @@ __global__ void __launch_bounds__(IRT, 8) k_sc_round_irp(const u64* __restrict__
 
 // The same with every unit evaluated at all points at once (slot_ir.cuh tpair_sums_all): a fifth of the record decoding
 // and of the value loads, and independent product chains per point.  For plans within its fixed array sizes.
+template <u32 NPW, bool SKIP>
 __global__ void __launch_bounds__(IRT, 4) k_sc_round_irq(const u64* __restrict__ tables, size_t stride, u32 half, hlk::IrDev p, int degree,
-                                                         int eval_one, u64* __restrict__ partials) {
+                                                         u64* __restrict__ partials) {
     extern __shared__ __align__(16) u32 ir_smem[];
     __shared__ u64 wsum[IRT / 32][2 * hlk::SC_MAX_POINTS];
     fp2* cf_s;
@@ -489,8 +490,7 @@ __global__ void __launch_bounds__(IRT, 4) k_sc_round_irq(const u64* __restrict__
     const u32* pw = ir_smem;
     const u32 nl = pw[14];
     const u32* live = pw + pw[13];
-    const bool skip_one = !eval_one && p.eval_degree >= 1;
-    fp2 V[ir::TPAIR_AFFINE_VALUES], D[ir::TPAIR_AFFINE_VALUES], W[ir::TPAIR_SUM_NODES * ir::TPAIR_POINTS];
+    fp2 V[ir::TPAIR_AFFINE_VALUES], D[ir::TPAIR_AFFINE_VALUES], W[ir::TPAIR_SUM_NODES * NPW];
     fp2 acc[ir::TPAIR_POINTS];
 #pragma unroll
     for (u32 d = 0; d < ir::TPAIR_POINTS; d++) acc[d] = f2(0, 0);
@@ -506,7 +506,7 @@ __global__ void __launch_bounds__(IRT, 4) k_sc_round_irq(const u64* __restrict__
             df = f2_sub(ld2(tb + 2 * ((size_t)i + half)), lo);
         });
         fp2 res[ir::TPAIR_POINTS];
-        ir::tpair_sums_all(pw, cf_s, V, D, W, skip_one, res);
+        ir::tpair_sums_all_t<NPW, SKIP>(pw, cf_s, V, D, W, res);
 #pragma unroll
         for (u32 d = 0; d < ir::TPAIR_POINTS; d++) acc[d] = f2_add(acc[d], res[d]);
     }
@@ -782,10 +782,18 @@ cudaError_t sc_round_ir(const IrDev& p, int k, const u64* tables, size_t stride,
         return cudaGetLastError();
     }
     if (ir_thread_pair_form(p, half)) {
-        if (p.all_points)
-            k_sc_round_irq<<<nblocks, IRT, ir_fixed_bytes(p), s>>>(tables, stride, half, p, degree, eval_one, partials);
-        else
-            k_sc_round_irp<<<nblocks, IRT, ir_fixed_bytes(p), s>>>(tables, stride, half, p, degree, eval_one, partials);
+        if (p.all_points) {
+            const bool skip = !eval_one && p.eval_degree >= 1;
+#define IRQ(N)                                                                                                             \
+    case N:                                                                                                                \
+        if (skip) k_sc_round_irq<N, true><<<nblocks, IRT, ir_fixed_bytes(p), s>>>(tables, stride, half, p, degree, partials); \
+        else k_sc_round_irq<N, false><<<nblocks, IRT, ir_fixed_bytes(p), s>>>(tables, stride, half, p, degree, partials);     \
+        break;
+            switch (p.eval_degree + 1) { IRQ(1) IRQ(2) IRQ(3) IRQ(4) IRQ(5) IRQ(6) default: return cudaErrorInvalidValue; }
+#undef IRQ
+            return cudaGetLastError();
+        }
+        k_sc_round_irp<<<nblocks, IRT, ir_fixed_bytes(p), s>>>(tables, stride, half, p, degree, eval_one, partials);
         return cudaGetLastError();
     }
     dim3 grid(nblocks, p.eval_degree + 1);  // the rows above are extrapolated by the step
