@@ -706,9 +706,9 @@ __global__ void __launch_bounds__(IR_TAIL_T) k_sc_tail_ir(u64* __restrict__ tabl
 // graph it takes 2.5 ns per item (12.5 ns per pair) from 2^15 pairs up, the pair form 28 ns per pair but only
 // ~43 us for a whole short round, where one thread needs 120-290 us for its single item.
 bool ir_pair_capable(const hlk::IrDev& p) { return p.n_units >= 24; }
-bool ir_pair_form(const hlk::IrDev& p, u32 half) { return ir_pair_capable(p) && half < (1u << 15); }
+bool ir_pair_form(const hlk::IrDev& p, u32 half) { return ir_pair_capable(p) && half < (1u << 14); }
 // the long rounds of a large polynomial: one pair per thread
-bool ir_thread_pair_form(const hlk::IrDev& p, u32 half) { return ir_pair_capable(p) && half >= (1u << 15); }
+bool ir_thread_pair_form(const hlk::IrDev& p, u32 half) { return ir_pair_capable(p) && half >= (1u << 14); }
 constexpr size_t IR_SMEM_BUDGET = 200 * 1024;
 size_t ir_fixed_bytes(const hlk::IrDev& p) { return (((size_t)p.plan_words + 3) & ~(size_t)3) * 4 + (size_t)p.n_coefs * 16 + 16; }
 size_t ir_area_bytes(const hlk::IrDev& p, int degree) { (void)degree; return (size_t)ir::pair_area(p.n_tables, p.n_nodes, p.eval_degree + 1) * 16; }
