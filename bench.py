@@ -227,6 +227,23 @@ def device_extras(dev, backend, np_data, np_pads, np_pows, col_key) -> dict:
         ctx.fold_cols_i8(wm, cw)
     t = ctx.timing_read(reset=True)
     out["fold_cols_i8_4096x14336_ms"] = t["fold"][0] / 2
+    # the pads and salts of the hiding commitment of `A` expanded on the device from the caller's generator key
+    # (rows * q field draws, then nn salts of four words: 11.2 MB + 1 MB of BLAKE3 extended output)
+    import torch
+
+    d_rng = torch.empty(rows * q + 4 * ((1 << log_cols) * ir), dtype=torch.int64, device="cuda")
+    nn_ = (1 << log_cols) * ir
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    cs = torch.cuda.current_stream()
+    for rep in range(3):
+        if rep == 1:
+            ev0.record(cs)
+        ctx.rng_fill_dev(bytes(range(32)), 0, rows * q, True, d_rng.data_ptr())
+        ctx.rng_fill_dev(bytes(range(32)), 2 * rows * q, 4 * nn_, False, d_rng.data_ptr() + 8 * rows * q)
+    ev1.record(cs)
+    torch.cuda.synchronize()
+    out["draw_pads_and_salts_of_A_ms"] = ev0.elapsed_time(ev1) / 2
+    del d_rng
     # a slot's tables built on the device from the resident rows of `A`: an eq cube of 2^21 entries and a witness plane of
     # 2^19 entries partially evaluated at 3 fixed coordinates (8 rows of 2^14 words each folded per entry)
     st, _ = dev.try_commit_zk_keyed(log_cols, ir, np_data, np_pads, np_pows, log_cols + 1, col_key)
@@ -384,6 +401,9 @@ def cpu_extras(o, backend, np_data) -> dict:
     wm = (splitmix_fp(84, 4096 * 14336) % np.uint64(256)).astype(np.uint8).view(np.int8).reshape(4096, 14336)
     cw = splitmix_fp(85, 14336 * 2).reshape(14336, 2)
     out["fold_cols_i8_4096x14336_ms"] = timed(lambda: o.fold_cols_i8(wm, cw))
+    g = o.ZkRng(1, b"bench")
+    out["draw_pads_and_salts_of_A_ms"] = timed(lambda: (g.fp_vec(rows * w["q"]), g.salts(n * w["inv_rate"])))
+    notes["draw_pads_and_salts_of_A_ms"] = "one thread, as the reference draws them (pcs.rs:788-792)"
     point = splitmix_fp(90, 21 * 2).reshape(21, 2)
     coords = [("fixed", (int(a), int(b))) for a, b in splitmix_fp(91, 6).reshape(3, 2)] + [("rho", k) for k in range(19)]
     out["tables_eq_2^21_plus_plane_2^19_x8_ms"] = timed(lambda: (o.eq_cube(point, 21, 0), o.priv_table(coords, [(0, (1, 0))], np_data, 19)))

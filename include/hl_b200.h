@@ -175,6 +175,15 @@ int hl_b200_rounds_new(hl_ctx* ctx, int poly, size_t k, uint32_t n_vars, uint32_
 #define HL_IR_ZERO 0xFFFFFFFDu
 int hl_b200_rounds_new_ir(hl_ctx* ctx, size_t k, uint32_t n_vars, uint32_t degree, const uint64_t* tables, const uint32_t* words,
                           size_t n_words, uint32_t n_nodes, uint32_t n_terms, const uint64_t* coefs, size_t ncoefs, hl_rounds** out);
+/* ---- the prover's random stream expanded on the device (zkp-core/src/rng.rs:279-417 ZkRng) ----
+ * key32 = the generator's key, BLAKE3("hashline-zk-rng/" || domain || LE64(seed)) (rng.rs:280-284), computed by the caller;
+ * first_word = u64 words of the stream already consumed; count words (as_fp == 0: next_u64 draws, four per bytes32), or
+ * count field elements (as_fp != 0: fp() draws, two words each, rng.rs:323-332).  The caller's generator then skips
+ * count (or 2 count) words.  rng_fill writes host memory, rng_fill_dev device memory (e.g. the pads and salts that
+ * hl_b200_commit_zk_dev / hl_b200_store_merkle_dev take, in the draw order of pcs.rs:733-745: pads first, then salts). */
+int hl_b200_rng_fill(hl_ctx* ctx, const uint8_t* key32, uint64_t first_word, uint64_t count, int as_fp, uint64_t* out);
+int hl_b200_rng_fill_dev(hl_ctx* ctx, const uint8_t* key32, uint64_t first_word, uint64_t count, int as_fp, uint64_t* d_out);
+
 /* ---- a slot's tables built on the device (argument.rs:907 build_tables_device; the Metal form is
  * gpu/metal.rs MetalTables::{new, tables_mut, plan_eq, plan_plane, build_planned, flush, to_vecs}) ----
  * A table set is k tables of 2^n_vars Fp2 in device memory.  Each table is filled by ONE of:

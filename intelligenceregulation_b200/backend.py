@@ -118,6 +118,16 @@ class Context:
         self.check(self.lib.hl_b200_compress_peak(self.h, iters, C.byref(v)))
         return float(v.value)
 
+    def rng_fill(self, key32: bytes, first_word: int, count: int, as_fp: bool) -> np.ndarray:
+        """`count` draws of the caller's ZkRng stream (rng.rs:279-417) from word position `first_word`, expanded on the
+        device: u64 words, or field elements (two words each) when `as_fp`."""
+        out = np.zeros(count, dtype=np.uint64)
+        self.check(self.lib.hl_b200_rng_fill(self.h, key32, first_word, count, 1 if as_fp else 0, _ptr(out)))
+        return out
+
+    def rng_fill_dev(self, key32: bytes, first_word: int, count: int, as_fp: bool, d_out: int) -> None:
+        self.check(self.lib.hl_b200_rng_fill_dev(self.h, key32, first_word, count, 1 if as_fp else 0, C.c_void_p(d_out)))
+
     def probe_field(self, a, b) -> np.ndarray:
         """metal_probe_field: (a+b, a-b, a*b) per pair, shape (n, 3)."""
         a, b = _u64(a), _u64(b)

@@ -68,6 +68,22 @@ __device__ __forceinline__ void compress(uint32_t (&cv)[8], const uint32_t (&m)[
     for (int i = 0; i < 8; i++) cv[i] = v[i] ^ v[i + 8];
 }
 
+// all sixteen output words of compress(cv, m, counter, block_len, flags): the extended output of a root node, whose
+// counter is the index of the 64-byte output piece
+__device__ __forceinline__ void compress_xof(uint32_t (&out)[16], const uint32_t* cv, const uint32_t (&m)[16], uint64_t counter,
+                                             uint32_t block_len, uint32_t flags) {
+    uint32_t v[16];
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = cv[i];
+    v[8] = 0x6A09E667u; v[9] = 0xBB67AE85u; v[10] = 0x3C6EF372u; v[11] = 0xA54FF53Au;
+    v[12] = (uint32_t)counter; v[13] = (uint32_t)(counter >> 32);
+    v[14] = block_len; v[15] = flags;
+    round_fn<0>(v, m); round_fn<1>(v, m); round_fn<2>(v, m); round_fn<3>(v, m);
+    round_fn<4>(v, m); round_fn<5>(v, m); round_fn<6>(v, m);
+#pragma unroll
+    for (int i = 0; i < 8; i++) { out[i] = v[i] ^ v[i + 8]; out[i + 8] = v[i + 8] ^ cv[i]; }
+}
+
 // start-of-hash chaining value: the IV, or the key words in keyed mode
 __device__ __forceinline__ void init_cv(uint32_t (&cv)[8], const uint32_t* key) {
 #pragma unroll

@@ -329,6 +329,15 @@ class ZkRng:
         self._r = _RngStruct()
         _lib.or_rng_new(C.byref(self._r), C.c_uint64(seed), domain, C.c_size_t(len(domain)))
 
+    @property
+    def key(self) -> bytes:
+        return bytes(self._r.key)
+
+    @property
+    def words_consumed(self) -> int:
+        """u64 words of the stream drawn so far (block counter and position, rng.rs:300-310)"""
+        return (int(self._r.counter) - 1) * 1024 + int(self._r.pos) // 8 if self._r.counter else 0
+
     def next_u64(self) -> int:
         return int(_lib.or_rng_next_u64(C.byref(self._r)))
 
