@@ -244,6 +244,23 @@ def device_extras(dev, backend, np_data, np_pads, np_pows, col_key) -> dict:
     torch.cuda.synchronize()
     out["draw_pads_and_salts_of_A_ms"] = ev0.elapsed_time(ev1) / 2
     del d_rng
+    # the helper half of H for the byte-table lookups (protocol.rs:1700-1800): one job = 2^25 looked word pairs, two
+    # 256-entry inverse tables, two planes written (2 x 8 B read, 2 x 8 B written per pair)
+    npair = 1 << 25
+    d_a = torch.from_numpy((splitmix_fp(92, npair) % np.uint64(256)).astype(np.int64)).cuda()
+    d_b = torch.from_numpy((splitmix_fp(93, npair) % np.uint64(256)).astype(np.int64)).cuda()
+    d_t = torch.empty(1024, dtype=torch.int64, device="cuda")
+    d_h = torch.empty(2 * npair, dtype=torch.int64, device="cuda")
+    torch.cuda.synchronize()
+    for rep in range(3):
+        if rep == 1:
+            ctx.timing_read(reset=True)
+        ctx.lookup_inverse_table((21, 22), (23, 24), 8, d_t.data_ptr())
+        ctx.lookup_inverse_table((21, 22), (25, 26), 8, d_t.data_ptr() + 4096)
+        ctx.lookup_helpers_dev(d_a.data_ptr(), d_t.data_ptr(), 8, (23, 24), (21, 22), npair, d_h.data_ptr(), d_h.data_ptr() + 8 * npair,
+                               d_b=d_b.data_ptr(), d_table_b=d_t.data_ptr() + 4096, log_b=8, g_b=(25, 26))
+    out["lookup_helpers_u8_pairs_2^25_ms"] = ctx.timing_read(reset=True)["logup"][0] / 2
+    del d_a, d_b, d_t, d_h
     # a slot's tables built on the device from the resident rows of `A`: an eq cube of 2^21 entries and a witness plane of
     # 2^19 entries partially evaluated at 3 fixed coordinates (8 rows of 2^14 words each folded per entry)
     st, _ = dev.try_commit_zk_keyed(log_cols, ir, np_data, np_pads, np_pows, log_cols + 1, col_key)
@@ -401,6 +418,16 @@ def cpu_extras(o, backend, np_data) -> dict:
     wm = (splitmix_fp(84, 4096 * 14336) % np.uint64(256)).astype(np.uint8).view(np.int8).reshape(4096, 14336)
     cw = splitmix_fp(85, 14336 * 2).reshape(14336, 2)
     out["fold_cols_i8_4096x14336_ms"] = timed(lambda: o.fold_cols_i8(wm, cw))
+    npair = 1 << 22
+    la = (splitmix_fp(92, npair) % np.uint64(256)).astype(np.int64)
+    lb = (splitmix_fp(93, npair) % np.uint64(256)).astype(np.int64)
+
+    def lookup():
+        ta, tb = o.lookup_inverse_table((21, 22), (23, 24), 256), o.lookup_inverse_table((21, 22), (25, 26), 256)
+        o.lookup_helpers(la, ta, (23, 24), (21, 22), b=lb, tab_b=tb, g_b=(25, 26))
+
+    out["lookup_helpers_u8_pairs_2^25_ms"] = timed(lookup) * 8
+    notes["lookup_helpers_u8_pairs_2^25_ms"] = "2^22 of 2^25 pairs, scaled"
     g = o.ZkRng(1, b"bench")
     out["draw_pads_and_salts_of_A_ms"] = timed(lambda: (g.fp_vec(rows * w["q"]), g.salts(n * w["inv_rate"])))
     notes["draw_pads_and_salts_of_A_ms"] = "one thread, as the reference draws them (pcs.rs:788-792)"

@@ -256,6 +256,18 @@ int hl_b200_logup_histogram(hl_ctx* ctx, const int32_t* idx, size_t nq, size_t t
 int hl_b200_logup_helpers(hl_ctx* ctx, const int32_t* idx, const int32_t* outv, size_t n, const uint64_t alpha[2],
                           const uint64_t beta[2], const uint64_t tag[2], int64_t idx_off, const uint64_t* mult, uint64_t* h);
 
+/* ---- LogUp helper columns of TABLE-INDEXED lookups (protocol.rs:1125-1230 u8_denominator_inverses, helper_one,
+ * helper_pair_inverses_u8; :1700-1800 write_helpers_w16_cols): the byte tables and the range families ----
+ * lookup_inverse_table: d_table[v] = 1 / (alpha - (v + g)) for v < 2^log_len (DEVICE memory, Fp2 per entry); an entry
+ * whose denominator is zero is written as (0, 0) = absent, and does not refuse (protocol.rs:1122-1124).
+ * lookup_helpers_dev: re[i], im[i] = the two words of entry_a(a[i]) (+ entry_b(b[i]) when d_b is given): the two planes
+ * of H a helper job fills.  a, b: looked words as int64 in DEVICE memory; a word outside its table takes the direct
+ * inversion (protocol.rs:1172-1180).  HL_B200_ERR_ZERO when a word's denominator is zero (its entry absent). */
+int hl_b200_lookup_inverse_table(hl_ctx* ctx, const uint64_t alpha[2], const uint64_t g[2], uint32_t log_len, uint64_t* d_table);
+int hl_b200_lookup_helpers_dev(hl_ctx* ctx, const int64_t* d_a, const uint64_t* d_table_a, uint32_t log_a, const uint64_t g_a[2],
+                               const int64_t* d_b, const uint64_t* d_table_b, uint32_t log_b, const uint64_t g_b[2],
+                               const uint64_t alpha[2], size_t n, uint64_t* d_re, uint64_t* d_im);
+
 /* ---- weight folds (zkp-core/src/mle.rs:157-205 fold_rows_i8 / fold_cols_i8, deferred forms :256-319) ----
  * m: rows x cols int8, row-major.  fold_rows: out[j] = sum_i w[i] m[i][j] (w: rows Fp2, out: cols Fp2);
  * fold_cols: out[i] = sum_j c[j] m[i][j] (c: cols Fp2, out: rows Fp2).  Exact integer sums, one reduction. */

@@ -118,6 +118,19 @@ class Context:
         self.check(self.lib.hl_b200_compress_peak(self.h, iters, C.byref(v)))
         return float(v.value)
 
+    def lookup_inverse_table(self, alpha, g, log_len: int, d_table: int) -> None:
+        """`u8_denominator_inverses` / a range family's table (protocol.rs:1125-1140) into device memory."""
+        a, gg = np.array(alpha, dtype=np.uint64), np.array(g, dtype=np.uint64)
+        self.check(self.lib.hl_b200_lookup_inverse_table(self.h, _ptr(a), _ptr(gg), log_len, C.c_void_p(d_table)))
+
+    def lookup_helpers_dev(self, d_a: int, d_table_a: int, log_a: int, g_a, alpha, n: int, d_re: int, d_im: int,
+                           d_b: int = 0, d_table_b: int = 0, log_b: int = 0, g_b=None) -> None:
+        """One helper job (protocol.rs:1700-1800): H's two planes from one looked column or a pair, device to device."""
+        al, ga = np.array(alpha, dtype=np.uint64), np.array(g_a, dtype=np.uint64)
+        gb = np.array(g_b, dtype=np.uint64) if g_b is not None else None
+        self.check(self.lib.hl_b200_lookup_helpers_dev(self.h, C.c_void_p(d_a), C.c_void_p(d_table_a), log_a, _ptr(ga), C.c_void_p(d_b) if d_b else None,
+                                                       C.c_void_p(d_table_b) if d_b else None, log_b, _ptr(gb), _ptr(al), n, C.c_void_p(d_re), C.c_void_p(d_im)))
+
     def rng_fill(self, key32: bytes, first_word: int, count: int, as_fp: bool) -> np.ndarray:
         """`count` draws of the caller's ZkRng stream (rng.rs:279-417) from word position `first_word`, expanded on the
         device: u64 words, or field elements (two words each) when `as_fp`."""

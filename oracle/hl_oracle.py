@@ -567,6 +567,29 @@ def logup_helpers(idx, outv, alpha, beta, tag, idx_off: int = 0) -> np.ndarray:
     return h
 
 
+def lookup_inverse_table(alpha, g, length: int):
+    """protocol.rs:1125-1140: (table (length, 2) u64, absent (length,) u8)."""
+    table, absent = np.zeros((length, 2), dtype=np.uint64), np.zeros(length, dtype=np.uint8)
+    _lib.or_lookup_inverse_table((C.c_uint64 * 2)(*alpha), (C.c_uint64 * 2)(*g), C.c_size_t(length), _p(table), _p(absent))
+    return table, absent
+
+
+def lookup_helpers(a, tab_a, g_a, alpha, b=None, tab_b=None, g_b=None):
+    """protocol.rs:1186-1216: (re, im) planes of one helper job, or None for "zero LogUp denominator"."""
+    a = np.ascontiguousarray(a, np.int64)
+    re, im = np.zeros(a.size, dtype=np.uint64), np.zeros(a.size, dtype=np.uint64)
+    if b is not None:
+        b = np.ascontiguousarray(b, np.int64)
+        assert b.size == a.size
+    tb = tab_b if b is not None else tab_a
+    gb = g_b if b is not None else g_a
+    _lib.or_lookup_helpers.restype = C.c_int
+    bad = _lib.or_lookup_helpers(_p(a), _p(tab_a[0]), _p(tab_a[1]), C.c_size_t(tab_a[1].size), (C.c_uint64 * 2)(*g_a),
+                                 _p(b) if b is not None else None, _p(tb[0]), _p(tb[1]), C.c_size_t(tb[1].size), (C.c_uint64 * 2)(*gb),
+                                 (C.c_uint64 * 2)(*alpha), C.c_size_t(a.size), _p(re), _p(im))
+    return None if bad else (re, im)
+
+
 def logup_table_helper(table_out, mult, alpha, beta, tag) -> np.ndarray:
     table_out, mult = np.ascontiguousarray(table_out, np.int32), _u64(mult)
     ht = np.empty((table_out.size, 2), dtype=np.uint64)

@@ -75,3 +75,58 @@ void or_fp2_sum(const uint64_t *v, size_t n, uint64_t out[2]) {
     for (size_t i = 0; i < n; i++) acc = fp2_add(acc, fp2_new(v[2 * i], v[2 * i + 1]));
     out[0] = acc.c0; out[1] = acc.c1;
 }
+
+/* protocol.rs:1125-1140 (u8_denominator_inverses): table[v] = 1/(alpha - (v + g)), the non-zero denominators in one
+ * batch inversion; absent[v] = 1 where the denominator is zero (the entry is then left (0, 0)). */
+void or_lookup_inverse_table(const uint64_t alpha[2], const uint64_t g[2], size_t len, uint64_t *table, uint8_t *absent) {
+    fp2_t a = fp2_new(alpha[0], alpha[1]), gg = fp2_new(g[0], g[1]);
+    fp2_t *nz = (fp2_t *)malloc(sizeof(fp2_t) * (len ? len : 1));
+    size_t k = 0;
+    for (size_t v = 0; v < len; v++) {
+        fp2_t d = fp2_sub(a, fp2_add(from_i64((int64_t)v), gg));
+        absent[v] = (d.c0 | d.c1) == 0;
+        if (!absent[v]) nz[k++] = d;
+    }
+    or_batch_inverse2((uint64_t *)nz, k);
+    k = 0;
+    for (size_t v = 0; v < len; v++) {
+        fp2_t e = absent[v] ? fp2_new(0, 0) : nz[k++];
+        table[2 * v] = e.c0;
+        table[2 * v + 1] = e.c1;
+    }
+    free(nz);
+}
+
+/* protocol.rs:1168-1182 (helper_one) */
+static int lookup_one(int64_t v, fp2_t a, fp2_t g, const uint64_t *table, const uint8_t *absent, size_t len, fp2_t *out) {
+    if (v >= 0 && (uint64_t)v < len) {
+        if (absent[v]) return 0;
+        *out = fp2_new(table[2 * v], table[2 * v + 1]);
+        return 1;
+    }
+    fp2_t d = fp2_sub(a, fp2_add(from_i64(v), g));
+    if ((d.c0 | d.c1) == 0) return 0;
+    *out = fp2_inv(d);
+    return 1;
+}
+
+/* protocol.rs:1186-1193, 1206-1216 (helper_inverses_u8 / helper_pair_inverses_u8) written as the two planes of H
+ * (write_helpers_w16_cols :1730): returns 0, or 1 for "zero LogUp denominator" (the first column asked first). */
+int or_lookup_helpers(const int64_t *a, const uint64_t *table_a, const uint8_t *absent_a, size_t len_a, const uint64_t g_a[2],
+                      const int64_t *b, const uint64_t *table_b, const uint8_t *absent_b, size_t len_b, const uint64_t g_b[2],
+                      const uint64_t alpha[2], size_t n, uint64_t *re, uint64_t *im) {
+    fp2_t al = fp2_new(alpha[0], alpha[1]), ga = fp2_new(g_a[0], g_a[1]), gb = b ? fp2_new(g_b[0], g_b[1]) : ga;
+    int bad = 0;
+#pragma omp parallel for schedule(static) reduction(| : bad)
+    for (size_t i = 0; i < n; i++) {
+        fp2_t h, y;
+        if (!lookup_one(a[i], al, ga, table_a, absent_a, len_a, &h)) { bad |= 1; continue; }
+        if (b) {
+            if (!lookup_one(b[i], al, gb, table_b, absent_b, len_b, &y)) { bad |= 1; continue; }
+            h = fp2_add(h, y);
+        }
+        re[i] = h.c0;
+        im[i] = h.c1;
+    }
+    return bad;
+}
