@@ -62,12 +62,14 @@ class ClockSampler:
     Q = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown," \
         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
 
-    def __init__(self, gpu_index: int):
-        self.idx, self.rows, self.proc = gpu_index, [], None
+    def __init__(self, gpu_indices):
+        self.idx, self.rows, self.proc = ",".join(str(i) for i in gpu_indices), [], None
 
     def start(self):
+        if not self.idx:
+            return
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.idx)],
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", self.idx],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -492,12 +494,21 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
 
     np_data, np_pads, np_pows, np_salts = (t.numpy().view(np.uint64) if t.dtype == torch.int64 else t.numpy() for t in (h_data, h_pads, h_pows, h_salts))
 
+    e2e_parts = [0.0, 0.0, 0.0]  # this rank's wall time in the commitment call, the tree call, the exchange of roots
+
     def step_e2e():
+        t0 = time.perf_counter()
         st, leaves = dev.try_commit_zk_keyed(log_cols, ir, np_data, np_pads, np_pows, log_cols + 1, col_key)
+        t1 = time.perf_counter()
         levels = st.merkle(np_salts.reshape(nn, 32), leaf_key, node_key)
         st.free()
+        t2 = time.perf_counter()
         if world > 1:
             dist.all_gather_into_tensor(roots, torch.from_numpy(levels[-1].copy()).cuda())
+            stream.synchronize()
+        e2e_parts[0] += t1 - t0
+        e2e_parts[1] += t2 - t1
+        e2e_parts[2] += time.perf_counter() - t2
         return leaves, levels
 
     def barrier():
@@ -519,7 +530,9 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
         return
 
     # ---- resident-input leg ----
-    sampler = ClockSampler(local_rank)
+    # one sampling process for all the job's GPUs, on rank 0: every query takes the driver's lock, and one process per
+    # rank stalled the other ranks' copies and allocations
+    sampler = ClockSampler(range(world) if rank == 0 else [])
     sampler.start()
     for _ in range(args.warmup):
         step_resident()
@@ -557,10 +570,12 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     barrier()
     s0 = dev.ctx.stats()
     t0 = time.perf_counter()
+    e2e_parts[:] = [0.0, 0.0, 0.0]
     for _ in range(args.steps):
         leaves, levels = step_e2e()
     barrier()
-    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    e2e_own = time.perf_counter() - t0
+    e2e_s = max_over_ranks(e2e_own)
     clocks = sampler.stop()
     s1 = dev.ctx.stats()
     assert bytes(levels[-1]) == root_resident, "the two legs disagree on the root"
@@ -576,6 +591,12 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     c1.record(stream)
     torch.cuda.synchronize()
     h2d_only_ms = c0.elapsed_time(c1) / 5
+    per_rank = None
+    if world > 1:  # every rank's own wall time and upload time: the ranks share the host's memory and PCIe root complexes
+        t = torch.tensor([e2e_own * 1e3 / args.steps, h2d_only_ms] + [x * 1e3 / args.steps for x in e2e_parts], dtype=torch.float64, device="cuda")
+        allt = torch.empty(5 * world, dtype=torch.float64, device="cuda")
+        dist.all_gather_into_tensor(allt, t)
+        per_rank = [[round(x, 3) for x in row] for row in allt.view(world, 5).tolist()]
 
     enc_bytes = rows * nn * 8
     value = world * enc_bytes * args.steps / (ms * 1e-3) / 1e9
@@ -624,7 +645,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             "dtype": "u64", "data": "synthetic", "config": workload_config(world),
             "e2e": {"value": e2e_v, "unit": "GB/s", "h2d_bytes_per_step": (s1["bytes_h2d"] - s0["bytes_h2d"]) // args.steps,
                     "d2h_bytes_per_step": (s1["bytes_d2h"] - s0["bytes_d2h"]) // args.steps, "ms_per_step": e2e_s * 1e3 / args.steps,
-                    "h2d_only_ms": h2d_only_ms},
+                    "h2d_only_ms": h2d_only_ms, **({"per_rank_ms": {"columns": ["step", "h2d_only", "commit_call", "tree_call", "root_exchange"], "rows": per_rank}} if per_rank else {})},
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": {"bound": "hbm", "kernel": "k_encode_fast<14,1024>", "achieved": achieved, "peak": peak,
