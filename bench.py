@@ -295,6 +295,23 @@ def device_extras(dev, backend, np_data, np_pads, np_pows, col_key) -> dict:
         ev.free()
     t = ctx.timing_read(reset=True)
     out["sumcheck_slot_program_60tables_71nodes_deg5_2^19_ms"] = t["rounds"][0] / 2
+    # the T256 / T512 profiles (shape.rs:248-262): the same 41 M words as rows of 2^15 and 2^16, which run as 2 or 4
+    # shared-memory transforms of 2^14 each way
+    for lc, rws in ((15, rows // 2), (16, rows // 4)):
+        nnl = (1 << lc) * ir
+        dd = torch.from_numpy(splitmix_fp(0xB2000300 + lc, rws << lc).view(np.int64)).cuda()
+        dp = torch.from_numpy(splitmix_fp(0xB2000400 + lc, rws * q).view(np.int64)).cuda()
+        dw = torch.from_numpy(coset_powers(nnl).view(np.int64)).cuda()
+        torch.cuda.synchronize()
+        for rep in range(4):
+            if rep == 1:
+                ctx.timing_read(reset=True)
+            stl = dev.commit_zk_dev(lc, ir, dd.data_ptr(), rws, dp.data_ptr(), q, dw.data_ptr(), col_key)
+            stl.free()
+        t = ctx.timing_read(reset=True)
+        out[f"commit_rows_of_2^{lc}_x{rws}_encode_ms"] = t["encode"][0] / 3
+        out[f"commit_rows_of_2^{lc}_x{rws}_hash_ms"] = t["hash"][0] / 3
+        del dd, dp, dw
     ctx.timing_enable(False)
     return out
 

@@ -256,6 +256,24 @@ int hl_b200_logup_histogram(hl_ctx* ctx, const int32_t* idx, size_t nq, size_t t
 int hl_b200_logup_helpers(hl_ctx* ctx, const int32_t* idx, const int32_t* outv, size_t n, const uint64_t alpha[2],
                           const uint64_t beta[2], const uint64_t tag[2], int64_t idx_off, const uint64_t* mult, uint64_t* h);
 
+/* ---- the masking commitment M of a block (hashline/src/zk.rs:447-536 mask_commit / mask_commit_tagged) and the product
+ * polynomial of its opening (zk.rs:618-637 mask_open) ----
+ * mask_commit: `msgs` = n_msg_rows rows of 2^log_msg EVALUATIONS (a mask's real or imaginary coefficients, its pads, zeros:
+ * what zk.rs:466-470 assembles before `ntt.inverse`), `coef_rows` = n_coef_rows rows of 2^(log_msg + 1) COEFFICIENTS (b_re,
+ * b_im, u_re, u_im with b[m] = -b[0] already set, zk.rs:478-483), `pows` = the 2^log_dom coset powers 7^i.  Every row is
+ * evaluated on the coset (encode_coeffs_coset, zk.rs:441-445), columns are hashed under key32 (hash_columns[_keyed]).
+ * Out: leaves32 (2^log_dom x 32 bytes, unsalted), a_coefs (n_msg_rows x 2^log_msg, the `a_coefs` of MaskCommit; may be
+ * NULL) and a store whose data rows are the coefficient rows (2^(log_msg + 1) words each, message rows zero-extended):
+ *   hl_b200_store_merkle            the salted tree (salt_leaf[_keyed], MerkleTree::build[_keyed])
+ *   hl_b200_store_columns           the opened columns (zk.rs:650-654)
+ *   hl_b200_store_fold(with_pads 0) the proximity combination (zk.rs:641-647) with weights (r_0 .. r_{rows-3}, 1, U)
+ * log_msg 8 .. 11, log_dom - log_msg 1 .. 6; the reference's constants are 9 and 12.
+ * mask_open_q: ws = n_masks x 2^log_msg Fp2 (combined_weights' vectors, zero-extended to the message length);
+ * q = 2^(log_msg + 1) Fp2 = sum_s p_{a_s} p_{W_s} + p_b (zk.rs:623-637), rows 2s / 2s+1 the masks, rows 2 n_masks / +1 b. */
+int hl_b200_mask_commit(hl_ctx* ctx, uint32_t log_msg, uint32_t log_dom, const uint64_t* msgs, size_t n_msg_rows, const uint64_t* coef_rows,
+                        size_t n_coef_rows, const uint64_t* pows, const uint8_t* key32, hl_store** store, uint64_t* a_coefs, uint8_t* leaves32);
+int hl_b200_mask_open_q(hl_store* store, size_t n_masks, const uint64_t* ws, uint64_t* q);
+
 /* ---- LogUp helper columns of TABLE-INDEXED lookups (protocol.rs:1125-1230 u8_denominator_inverses, helper_one,
  * helper_pair_inverses_u8; :1700-1800 write_helpers_w16_cols): the byte tables and the range families ----
  * lookup_inverse_table: d_table[v] = 1 / (alpha - (v + g)) for v < 2^log_len (DEVICE memory, Fp2 per entry); an entry

@@ -55,6 +55,8 @@ class FsState(C.Structure):
 SIGNATURES.update({
     "hl_b200_rounds_new": (_int, [_vp, _int, _sz, _u32, _u32, _vp, _vp, _sz, _pp]),
     "hl_b200_rounds_new_ir": (_int, [_vp, _sz, _u32, _u32, _vp, _vp, _sz, _u32, _u32, _vp, _sz, _pp]),
+    "hl_b200_mask_commit": (_int, [_vp, _u32, _u32, _vp, _sz, _vp, _sz, _vp, _vp, _vp, _vp, _vp]),
+    "hl_b200_mask_open_q": (_int, [_vp, _sz, _vp, _vp]),
     "hl_b200_lookup_inverse_table": (_int, [_vp, _vp, _vp, _u32, _vp]),
     "hl_b200_lookup_helpers_dev": (_int, [_vp, _vp, _vp, _u32, _vp, _vp, _vp, _u32, _vp, _vp, _sz, _vp, _vp]),
     "hl_b200_rng_fill": (_int, [_vp, _vp, _u64, _u64, _int, _vp]),

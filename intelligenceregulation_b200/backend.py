@@ -302,6 +302,47 @@ class B200Backend:
         return B200Commit(self.ctx, h)
 
 
+class B200Mask(B200Commit):
+    """``MaskCommit`` on the device (hashline/src/zk.rs:395-411, 447-536): a store whose data rows are the coefficient rows
+    (a_coefs zero-extended, b_re, b_im, u_re, u_im), so the tree, the opened columns and the proximity combination are the
+    store's own calls; ``open_q`` is the product polynomial of ``mask_open`` (zk.rs:623-637)."""
+
+    def __init__(self, ctx: Context, handle: C.c_void_p, n_masks: int, a_coefs: np.ndarray, leaves: np.ndarray):
+        super().__init__(ctx, handle)
+        self.n_masks, self.a_coefs, self.leaves = n_masks, a_coefs, leaves
+
+    def open_q(self, ws: np.ndarray) -> np.ndarray:
+        """ws: (n_masks, m, 2) combined weights (zk.rs:553-578) -> q' (2 m, 2)."""
+        ws = _u64(ws)
+        q = np.empty((self.n, 2), dtype=np.uint64)
+        self.ctx.check(self.ctx.lib.hl_b200_mask_open_q(self.h, self.n_masks, _ptr(ws), _ptr(q)))
+        return q
+
+    def prox(self, rs: np.ndarray) -> np.ndarray:
+        """sum_row r_row p_row + u (zk.rs:641-647): rs (2 n_masks + 2, 2) -> (2 m, 2)."""
+        rs = _u64(rs).reshape(-1, 2)
+        w = np.concatenate([rs, np.array([[1, 0], [0, 1]], dtype=np.uint64)])  # u = u_re + U u_im
+        return self.fold_rows(w.reshape(1, self.rows, 2))[0]
+
+
+def mask_commit(ctx: Context, msgs: np.ndarray, coef_rows: np.ndarray, pows: np.ndarray, col_key: Optional[bytes], log_msg: int = 9, log_dom: int = 12):
+    """``mask_commit[_tagged]`` (zk.rs:447-536) after its draws: msgs = the 2 S message rows (coefficients of a mask's real or
+    imaginary part, its pads, zeros) as they stand before ``ntt.inverse``; coef_rows = (b_re, b_im, u_re, u_im).  Returns the
+    ``B200Mask`` (``a_coefs`` and unsalted ``leaves`` on it), or None when the device declines."""
+    msgs, coef_rows, pows = _u64(msgs), _u64(coef_rows), _u64(pows)
+    m = 1 << log_msg
+    n_msg, n_coef = msgs.size // m, coef_rows.size // (2 * m)
+    a_coefs = np.empty((n_msg, m), dtype=np.uint64)
+    leaves = np.empty((1 << log_dom, 32), dtype=np.uint8)
+    h = C.c_void_p()
+    rc = ctx.lib.hl_b200_mask_commit(ctx.h, log_msg, log_dom, _ptr(msgs), n_msg, _ptr(coef_rows), n_coef, _ptr(pows), _ptr(col_key), C.byref(h),
+                                     _ptr(a_coefs), _ptr(leaves))
+    if rc != 0:
+        ctx.declined("b200 mask commit", rc)
+        return None
+    return B200Mask(ctx, h, n_msg // 2, a_coefs, leaves)
+
+
 POLY_PROD, POLY_ZC, POLY_LOGUP_Q, POLY_LOGUP_T = 0, 1, 2, 3
 
 

@@ -37,6 +37,7 @@ struct hl_store {
     u32 rows = 0, logn = 0, logr = 0, q = 0;
     bool zk = false;
     bool owns_inputs = true;      // false: d_data / d_pads belong to the caller
+    bool fold_data = false;       // a plain store whose row fold reads d_data (a masking commitment's coefficient rows)
     u64* d_data = nullptr;        // rows x n
     u64* d_pads = nullptr;        // rows x q
     u64* d_enc = nullptr;         // rows x nn
@@ -56,6 +57,7 @@ int sync(hl_ctx* c, const char* what);
 int root_powers(hl_ctx* c, u32 lognn, const u64** out);
 int upload_key(hl_ctx* c, const uint8_t* key32, uint32_t** d_key);
 int log2_exact(size_t v);
+void store_release(hl_store* st);  // frees a store; the caller holds the context's lock
 
 // Brackets the launches of one kernel family with two events when the context's timing is on.
 struct Timed {

@@ -73,7 +73,7 @@ int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* 
             a.pads = st->d_pads ? st->d_pads + (size_t)r0 * st->q : nullptr;
             a.pows = d_pows; a.tw_nn = tw; a.enc = st->d_enc + (size_t)r0 * nn; a.scratch = scratch;
             a.rows = nr; a.q = st->zk ? st->q : 0; a.T = T; a.logr = st->logr + loga; a.loga = loga; a.zk = st->zk ? 1 : 0;
-            a.ninv = gl_inv((u64)n);
+            a.ninv = gl_inv((u64)n); a.coef_out = nullptr;
             cudaError_t e = hlk::encode_rows(a, logb, c->fast_encoder || loga, c->sm_count, scratch_words, c->stream, &st->encoder_path);
             c->stats.kernel_launches += 1;
             if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "row encoder launch", e);
@@ -151,6 +151,8 @@ int commit_host(hl_ctx* c, const Shape& s, const uint64_t* data, const uint64_t*
 }
 
 }  // namespace
+
+void hlapi::store_release(hl_store* st) { free_store(st); }
 
 extern "C" {
 
@@ -278,9 +280,10 @@ int hl_b200_store_fold(hl_store* st, const uint64_t* rhos, size_t k, int with_pa
         Timed t(c, HL_T_FOLD);
         // hiding form: the message is the resident data (the encoding is not systematic, pcs.rs:985-987);
         // plain form: the systematic positions of the encoding (pcs.rs:332-340)
-        const u64* src = st->zk ? st->d_data : st->d_enc;
-        const size_t ld = st->zk ? n : st->nn();
-        const u32 ir = st->zk ? 1u : 1u << st->logr;
+        const bool from_data = st->zk || st->fold_data;
+        const u64* src = from_data ? st->d_data : st->d_enc;
+        const size_t ld = from_data ? n : st->nn();
+        const u32 ir = from_data ? 1u : 1u << st->logr;
         const u64* src2 = st->zk && q ? st->d_pads : nullptr;
         cudaError_t e = cudaSuccess;
         if (kd) {

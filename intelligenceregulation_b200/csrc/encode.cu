@@ -35,7 +35,7 @@ __global__ void k_encode_generic(enc::RowArgs a, u32 logn) {
     }
 }
 
-template <int LOGN, int THREADS>
+template <int LOGN, int THREADS, int FORM = enc::FORM_PCS>
 __global__ void __launch_bounds__(THREADS) k_encode_fast(enc::RowArgs a) {
     using F = enc::Fast<LOGN>;
     extern __shared__ u64 smem[];
@@ -46,7 +46,7 @@ __global__ void __launch_bounds__(THREADS) k_encode_fast(enc::RowArgs a) {
     F::load_twiddles(a, TW, tid, THREADS);
     __syncthreads();
     for (u32 row = blockIdx.x; row < a.rows; row += gridDim.x) {
-        F::row_coeffs(a, row, S, TW, X, tid, THREADS, CtaSync());
+        F::template row_coeffs<CtaSync, FORM>(a, row, S, TW, X, tid, THREADS, CtaSync());
         __syncthreads();  // the scratch slot is complete and shared memory is free again
         for (u32 s = 0; s < (1u << a.logr); s++) {
             F::row_residue(a, row, s, S, TW, X, tid, THREADS, CtaSync());
@@ -61,11 +61,11 @@ constexpr int fast_threads() {
     return g < 32 ? 32 : (g > 1024 ? 1024 : g);
 }
 
-template <int LOGN>
+template <int LOGN, int FORM = enc::FORM_PCS>
 cudaError_t launch_fast(const enc::RowArgs& a, int sm_count, size_t scratch_words, cudaStream_t st, int* grid_out) {
     using F = enc::Fast<LOGN>;
     constexpr int T = fast_threads<LOGN>();
-    auto kern = k_encode_fast<LOGN, T>;
+    auto kern = k_encode_fast<LOGN, T, FORM>;
     size_t smem = (size_t)(F::N + F::TW_WORDS) * 8;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
@@ -127,6 +127,20 @@ cudaError_t encode_rows(const enc::RowArgs& a, u32 logn, bool allow_fast, int sm
     if (g < 1) return cudaErrorInvalidValue;
     k_encode_generic<<<(unsigned)g, threads, smem, st>>>(a, logn);
     return cudaGetLastError();
+}
+
+// the rows of a masking commitment (messages of 2^8 .. 2^11 words): FORM_COSET or FORM_COEF, always the fast path
+cudaError_t encode_rows_form(const enc::RowArgs& a, u32 logn, int form, int sm_count, size_t scratch_words, cudaStream_t st) {
+    int grid = 0;
+    const bool coef = form == enc::FORM_COEF;
+    if (form != enc::FORM_COSET && !coef) return cudaErrorInvalidValue;
+    switch (logn) {
+        case 8: return coef ? launch_fast<8, enc::FORM_COEF>(a, sm_count, scratch_words, st, &grid) : launch_fast<8, enc::FORM_COSET>(a, sm_count, scratch_words, st, &grid);
+        case 9: return coef ? launch_fast<9, enc::FORM_COEF>(a, sm_count, scratch_words, st, &grid) : launch_fast<9, enc::FORM_COSET>(a, sm_count, scratch_words, st, &grid);
+        case 10: return coef ? launch_fast<10, enc::FORM_COEF>(a, sm_count, scratch_words, st, &grid) : launch_fast<10, enc::FORM_COSET>(a, sm_count, scratch_words, st, &grid);
+        case 11: return coef ? launch_fast<11, enc::FORM_COEF>(a, sm_count, scratch_words, st, &grid) : launch_fast<11, enc::FORM_COSET>(a, sm_count, scratch_words, st, &grid);
+    }
+    return cudaErrorInvalidValue;
 }
 
 }  // namespace hlk

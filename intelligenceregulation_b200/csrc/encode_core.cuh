@@ -55,7 +55,15 @@ struct RowArgs {
     u32 loga;          // log2(n / N): 0 unless the row is longer than one shared-memory transform
     int zk;
     u64 ninv;          // n^-1
+    u64* coef_out;     // FORM_COSET only: the row's n coefficients, in rows of 2n words (or NULL)
 };
+
+// What a row is and how its coefficients are twisted (template argument of Fast::row_coeffs).
+//   FORM_PCS    the commitment forms above: plain (no twist) or hiding (pads folded in, coset powers)
+//   FORM_COSET  n evaluations -> n coefficients c, x[i] = c[i] h^i, c kept in coef_out (a masking commitment's message rows,
+//               hashline/src/zk.rs:463-476: pads sit inside the message, the coset is applied to every row)
+//   FORM_COEF   n + q coefficients given as such, x[i] = c[i] h^i (its blinding and proximity rows, zk.rs:478-487)
+enum { FORM_PCS = 0, FORM_COSET = 1, FORM_COEF = 2 };
 
 // ---------------------------------------------------------------------------------------------
 // Generic path: radix-2 stages straight on shared memory, any n from 2 to 2^14, any thread count.
@@ -237,9 +245,14 @@ struct Fast {
     // ---- the row pipeline ----
     // inverse transform of the message row, then the coefficient blocks x[idx] into the scratch slot.
     // c[i] = F[(n - i) mod n] / n with F the forward transform of the message, one residue a of F per pass set.
-    template <class Sync>
+    template <class Sync, int FORM = FORM_PCS>
     GL_HD static void row_coeffs(const RowArgs& a, u32 row, u64* S, const u64* TW, u64* X, u32 tid, u32 nt, Sync sync) {
         const u32 A = 1u << a.loga, n = N << a.loga, nn = N << a.logr, lognn = LOGN + a.logr;
+        if constexpr (FORM == FORM_COEF) {
+            const u64* cs = a.data + (size_t)row * (n + a.q);
+            for (u32 i = tid; i < n + a.q; i += nt) X[i] = gl_mul(cs[i], a.pows[i]);
+            return;
+        }
         const u64* src = a.data + (size_t)row * n;
         const u64* pad = a.pads + (size_t)row * a.q;
         const u32 Tn = a.zk ? (n + a.q + n - 1) / n : 1u;
@@ -257,16 +270,21 @@ struct Fast {
                       [&](u32 k, u64 v) {
                           const u32 i = (n - ((k << a.loga) + ra)) & (n - 1);
                           const u64 c = gl_mul_fast(v, a.ninv);
-                          for (u32 t = 0; t < Tn; t++) {
-                              const u32 idx = i + t * n;
-                              u64 x = t == 0 ? c : 0;
-                              if (a.zk) {
-                                  if (idx >= n + a.q) break;
-                                  if (idx < a.q) x = gl_sub(x, pad[idx]);
-                                  if (idx >= n && idx - n < a.q) x = gl_add(x, pad[idx - n]);
-                                  x = gl_mul_fast(x, a.pows[idx]);
+                          if constexpr (FORM == FORM_COSET) {
+                              X[i] = gl_mul(c, a.pows[i]);
+                              if (a.coef_out) a.coef_out[(size_t)row * 2 * n + i] = c;
+                          } else {
+                              for (u32 t = 0; t < Tn; t++) {
+                                  const u32 idx = i + t * n;
+                                  u64 x = t == 0 ? c : 0;
+                                  if (a.zk) {
+                                      if (idx >= n + a.q) break;
+                                      if (idx < a.q) x = gl_sub(x, pad[idx]);
+                                      if (idx >= n && idx - n < a.q) x = gl_add(x, pad[idx - n]);
+                                      x = gl_mul_fast(x, a.pows[idx]);
+                                  }
+                                  X[idx] = x;
                               }
-                              X[idx] = x;
                           }
                       },
                       sync);

@@ -776,3 +776,173 @@ def open_zk(cmz: CommittedZk, claims: Sequence[ZClaim], tr: Transcript, fold=Non
     cols = gather_columns(cmz.encoded, rows, nn, idx) if columns is None else columns(idx)
     out = [(int(j), cols[c], bytes(cmz.salts[int(j)]), merkle_path(cmz.levels, nn, int(j))) for c, j in enumerate(idx)]
     return OpeningZk(vecs[:-1], vecs[-1], out)
+
+
+# ----------------------------------------------------------------------------- the masking commitment M (hashline/src/zk.rs)
+# Parity of this part is UNPINNED: the reference tree holds no golden vector of an M commitment or opening (its L10 corpus is
+# present only as a checksum).  Every primitive below IS pinned (transforms by the encode conformance vectors, hashing and
+# trees by the L5 corpus, the generator and CfsMask::random by L5 / L6), and the restated verifier accepts the restated prover.
+MASK_LOG_MSG, MASK_LOG_DOM, MASK_Q = 9, 12, 256  # zk.rs:391-393
+_P = 0xFFFFFFFF00000001
+
+
+def _mulp(a, b) -> np.ndarray:
+    return ((_u64(a).astype(object) * _u64(b).astype(object)) % _P).astype(np.uint64)
+
+
+def _addp(a, b) -> np.ndarray:
+    return ((_u64(a).astype(object) + _u64(b).astype(object)) % _P).astype(np.uint64)
+
+
+def encode_coeffs_coset(coeffs, pows, log_dom: int) -> np.ndarray:
+    """zk.rs:441-445"""
+    out = np.zeros(1 << log_dom, dtype=np.uint64)
+    out[:len(coeffs)] = _mulp(coeffs, pows[:len(coeffs)])
+    return ntt_forward(out, log_dom)
+
+
+@dataclass
+class MaskCommit:
+    specs: list
+    masks: list       # per spec: (n d + 2, 2) coefficients of the CFS mask
+    a_coefs: np.ndarray  # 2 S x m
+    encoded: np.ndarray  # (2 S + 4) x dom
+    b: tuple
+    u: tuple
+    salts: np.ndarray
+    levels: np.ndarray
+    msgs: np.ndarray  # 2 S x m: the message rows before the inverse transform (what a device commit is handed)
+
+    @property
+    def root(self) -> bytes:
+        return bytes(self.levels[-1])
+
+
+def mask_commit(specs, rng: "ZkRng", tag: "HashTag" = None, log_msg: int = MASK_LOG_MSG, log_dom: int = MASK_LOG_DOM, q: int = MASK_Q) -> MaskCommit:
+    """zk.rs:447-487 (mask_commit) / :499-536 (mask_commit_tagged): the draws in the reference's order."""
+    tag = tag or HashTag.legacy()
+    m, dom = 1 << log_msg, 1 << log_dom
+    pows = coset_powers(7, dom)
+    masks = [rng.fp2_vec(n * d + 2) for n, d in specs]  # CfsMask::random
+    n_base = 2 * len(masks) + 4
+    encoded = np.zeros((n_base, dom), dtype=np.uint64)
+    a_coefs, msgs = [], []
+    for s, mk in enumerate(masks):
+        for k in range(2):
+            part = mk[:, k]
+            assert len(part) + q <= m
+            msg = np.zeros(m, dtype=np.uint64)
+            msg[:len(part)] = part
+            msg[len(part):len(part) + q] = rng.fp_vec(q)
+            msgs.append(msg)
+            c = ntt_inverse(msg, log_dom)
+            encoded[2 * s + k] = encode_coeffs_coset(c, pows, log_dom)
+            a_coefs.append(c)
+    b_re, b_im = rng.fp_vec(2 * m), rng.fp_vec(2 * m)
+    b_re[m], b_im[m] = fp_neg(int(b_re[0])), fp_neg(int(b_im[0]))
+    u_re, u_im = rng.fp_vec(2 * m), rng.fp_vec(2 * m)
+    for k, c in enumerate((b_re, b_im, u_re, u_im)):
+        encoded[2 * len(masks) + k] = encode_coeffs_coset(c, pows, log_dom)
+    salts = rng.salts(dom)
+    leaves = hash_columns(encoded, n_base, dom, tag.column)
+    levels = merkle_build(salt_leaves(leaves, salts, tag.leaf), tag.node)
+    return MaskCommit(list(specs), masks, np.array(a_coefs), encoded, (b_re, b_im), (u_re, u_im), salts, levels, np.array(msgs))
+
+
+def mask_combined_weights(specs, functionals, theta, m: int):
+    """zk.rs:553-578: functional i weighted by theta^(i+1).  functionals: [(value, [(row, weights (l, 2))])]."""
+    ws = np.zeros((len(specs), m, 2), dtype=np.uint64)
+    v, th = (0, 0), theta
+    for value, terms in functionals:
+        for row, w in terms:
+            assert len(w) == specs[row][0] * specs[row][1] + 2
+            for j, x in enumerate(w):
+                ws[row, j] = fp2_add(tuple(int(t) for t in ws[row, j]), fp2_mul(th, (int(x[0]), int(x[1]))))
+        v = fp2_add(v, fp2_mul(th, value))
+        th = fp2_mul(th, theta)
+    return ws, v
+
+
+def _poly_mul(a, b, log_m: int) -> np.ndarray:
+    """zk.rs:605-616 (poly_mul_512)"""
+    m2 = 2 << log_m
+    ea, eb = np.zeros(m2, dtype=np.uint64), np.zeros(m2, dtype=np.uint64)
+    ea[:len(a)], eb[:len(b)] = a, b
+    return ntt_inverse(_mulp(ntt_forward(ea, log_m + 1), ntt_forward(eb, log_m + 1)), log_m + 1)
+
+
+def mask_open(mc: MaskCommit, functionals, tr: "Transcript", log_msg: int = MASK_LOG_MSG, log_dom: int = MASK_LOG_DOM, q: int = MASK_Q):
+    """zk.rs:618-656: (q', prox, [(j, column, salt, path)]); the intermediate weights are returned as a fourth item."""
+    m, dom, S = 1 << log_msg, 1 << log_dom, len(mc.masks)
+    theta = tr.challenge_fp2()
+    ws, _ = mask_combined_weights(mc.specs, functionals, theta, m)
+    q_re, q_im = mc.b[0].copy(), mc.b[1].copy()
+    seven = np.full(2 * m, 7, dtype=np.uint64)
+    for s in range(S):
+        w_re, w_im = ntt_inverse(ws[s, :, 0], log_dom), ntt_inverse(ws[s, :, 1], log_dom)  # weight_polys
+        a_re, a_im = mc.a_coefs[2 * s], mc.a_coefs[2 * s + 1]
+        rr, ii = _poly_mul(a_re, w_re, log_msg), _poly_mul(a_im, w_im, log_msg)
+        ri, ir = _poly_mul(a_re, w_im, log_msg), _poly_mul(a_im, w_re, log_msg)
+        q_re = _addp(_addp(q_re, rr), _mulp(ii, seven))
+        q_im = _addp(_addp(q_im, ri), ir)
+    qv = np.stack([q_re, q_im], axis=1)
+    tr.absorb_fp2(b"mask-q", qv)
+    rs = tr.challenge_fp2_vec(2 * S + 2)
+    prox = np.stack([mc.u[0], mc.u[1]], axis=1).astype(object)
+    for row in range(2 * S + 2):
+        coeffs = mc.a_coefs[row] if row < 2 * S else mc.b[row - 2 * S]
+        c = _u64(coeffs).astype(object)
+        prox[:len(c), 0] = (prox[:len(c), 0] + int(rs[row, 0]) * c) % _P
+        prox[:len(c), 1] = (prox[:len(c), 1] + int(rs[row, 1]) * c) % _P
+    prox = prox.astype(np.uint64)
+    tr.absorb_fp2(b"mask-prox", prox)
+    idx = tr.challenge_indices(q, dom)
+    cols = [(int(j), mc.encoded[:, int(j)].copy(), bytes(mc.salts[int(j)]), merkle_path(mc.levels, dom, int(j))) for j in idx]
+    return qv, prox, cols, ws, rs
+
+
+def mask_verify(root: bytes, specs, functionals, opening, tr: "Transcript", tag: "HashTag" = None, log_msg: int = MASK_LOG_MSG,
+                log_dom: int = MASK_LOG_DOM, q: int = MASK_Q) -> Optional[str]:
+    """zk.rs:658-700 (mask_verify) / :712-760 (mask_verify_tagged): None when accepted, else the refusal's text."""
+    tag = tag or HashTag.legacy()
+    qv, prox, cols = opening[0], opening[1], opening[2]
+    m, dom, S = 1 << log_msg, 1 << log_dom, len(specs)
+    n_base = 2 * S + 4
+    theta = tr.challenge_fp2()
+    ws, v = mask_combined_weights(specs, functionals, theta, m)
+    if len(qv) != 2 * m:
+        return "mask: q length"
+    got = fp2_mul_base(fp2_add(tuple(int(t) for t in qv[0]), tuple(int(t) for t in qv[m])), m)
+    if got != v:
+        return "mask: the product polynomial's sum != the combined functional"
+    tr.absorb_fp2(b"mask-q", qv)
+    rs = tr.challenge_fp2_vec(2 * S + 2)
+    if len(prox) != 2 * m:
+        return "mask: prox length"
+    tr.absorb_fp2(b"mask-prox", prox)
+    idx = tr.challenge_indices(q, dom)
+    if len(cols) != len(idx):
+        return "mask: column count"
+    pows = coset_powers(7, dom)
+    enc = lambda c: encode_coeffs_coset(c, pows, log_dom)
+    w_enc = [(enc(ntt_inverse(ws[s, :, 0], log_dom)), enc(ntt_inverse(ws[s, :, 1], log_dom))) for s in range(S)]
+    q_enc, p_enc = (enc(qv[:, 0]), enc(qv[:, 1])), (enc(prox[:, 0]), enc(prox[:, 1]))
+    for (j, col, salt, path), want in zip(cols, idx):
+        if j != int(want):
+            return "mask: column index"
+        if len(col) != n_base:
+            return "mask: column length"
+        leaf = salt_leaves(hash_columns(np.ascontiguousarray(col).reshape(n_base, 1), n_base, 1, tag.column), np.frombuffer(salt, np.uint8).reshape(1, 32), tag.leaf)
+        if not merkle_verify_path(root, j, bytes(leaf[0]), path, tag.node):
+            return f"mask: Merkle path for column {j} fails"
+        acc = (int(col[2 * S]), int(col[2 * S + 1]))
+        for s in range(S):
+            acc = fp2_add(acc, fp2_mul((int(col[2 * s]), int(col[2 * s + 1])), (int(w_enc[s][0][j]), int(w_enc[s][1][j]))))
+        if acc != (int(q_enc[0][j]), int(q_enc[1][j])):
+            return f"mask: column {j} disagrees with the product polynomial"
+        pacc = (int(col[n_base - 2]), int(col[n_base - 1]))
+        for row in range(2 * S + 2):
+            pacc = fp2_add(pacc, fp2_mul_base((int(rs[row, 0]), int(rs[row, 1])), int(col[row])))
+        if pacc != (int(p_enc[0][j]), int(p_enc[1][j])):
+            return f"mask: column {j} disagrees with the proximity vector"
+    return None
