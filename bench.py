@@ -295,6 +295,28 @@ def device_extras(dev, backend, np_data, np_pads, np_pows, col_key) -> dict:
         ev.free()
     t = ctx.timing_read(reset=True)
     out["sumcheck_slot_program_60tables_71nodes_deg5_2^19_ms"] = t["rounds"][0] / 2
+    # the masking commitment M of a block (zk.rs:447-656): 24 masks -> 48 message rows of 512 + 4 rows of 1024 coefficients
+    # on the coset of 4096, column hashes, salted tree; then the opening's product polynomial, proximity fold, 256 columns
+    S = 24
+    mm = splitmix_fp(94, 2 * S * 512).reshape(2 * S, 512)
+    mm[:, 320:] = 0
+    mcoef, mpows = splitmix_fp(95, 4 * 1024).reshape(4, 1024), coset_powers(4096)
+    msalts = splitmix_fp(96, 4096 * 4).view(np.uint8).reshape(4096, 32)
+    mws, mrs = splitmix_fp(97, S * 512 * 2).reshape(S, 512, 2), splitmix_fp(98, (2 * S + 2) * 2).reshape(-1, 2)
+    midx = (splitmix_fp(99, 256) % np.uint64(4096)).astype(np.uint64)
+    t_c = t_o = 0.0
+    for rep in range(4):
+        t0 = time.perf_counter()
+        dm = backend.mask_commit(ctx, mm, mcoef, mpows, col_key)
+        dm.merkle(msalts, col_key, col_key)
+        t1 = time.perf_counter()
+        dm.open_q(mws); dm.prox(mrs); dm.columns(midx)
+        t2 = time.perf_counter()
+        dm.free()
+        if rep:
+            t_c, t_o = t_c + (t1 - t0) * 1e3 / 3, t_o + (t2 - t1) * 1e3 / 3
+    out["mask_M_24masks_commit_and_tree_wall_ms"] = t_c  # host wall time of the calls: uploads, launches, read-backs
+    out["mask_M_24masks_open_wall_ms"] = t_o
     # the T256 / T512 profiles (shape.rs:248-262): the same 41 M words as rows of 2^15 and 2^16, which run as 2 or 4
     # shared-memory transforms of 2^14 each way
     for lc, rws in ((15, rows // 2), (16, rows // 4)):
@@ -445,6 +467,14 @@ def cpu_extras(o, backend, np_data) -> dict:
         ta, tb = o.lookup_inverse_table((21, 22), (23, 24), 256), o.lookup_inverse_table((21, 22), (25, 26), 256)
         o.lookup_helpers(la, ta, (23, 24), (21, 22), b=lb, tab_b=tb, g_b=(25, 26))
 
+    specs = [(21, 3)] * 12 + [(19, 5)] * 8 + [(14, 2)] * 4
+    tg = o.HashTag.for_profile(w["profile"])
+    box = {}
+    out["mask_M_24masks_commit_and_tree_wall_ms"] = timed(lambda: box.setdefault("mc", o.mask_commit(specs, o.ZkRng(3, b"bench-mask"), tg)))
+    fr = o.ZkRng(4, b"bench-mask-f")
+    fs = [((1, 2), [(s_, fr.fp2_vec(specs[s_][0] * specs[s_][1] + 2))]) for s_ in range(len(specs))]
+    out["mask_M_24masks_open_wall_ms"] = timed(lambda: o.mask_open(box["mc"], fs, o.Transcript(b"bench-mask")))
+    notes["mask_M_24masks_open_wall_ms"] = "numpy restatement (transforms and hashing in C, one thread; includes the functionals' weight combination)"
     out["lookup_helpers_u8_pairs_2^25_ms"] = timed(lookup) * 8
     notes["lookup_helpers_u8_pairs_2^25_ms"] = "2^22 of 2^25 pairs, scaled"
     g = o.ZkRng(1, b"bench")
