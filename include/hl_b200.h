@@ -256,6 +256,19 @@ int hl_b200_logup_histogram(hl_ctx* ctx, const int32_t* idx, size_t nq, size_t t
 int hl_b200_logup_helpers(hl_ctx* ctx, const int32_t* idx, const int32_t* outv, size_t n, const uint64_t alpha[2],
                           const uint64_t beta[2], const uint64_t tag[2], int64_t idx_off, const uint64_t* mult, uint64_t* h);
 
+/* ---- witness weight products (hashline/src/gpu/metal.rs:4646-4680 witness_product; private_block/witness.rs:818-835 on_device,
+ * :979-991 matmul_reference): out[t * os + j] = sum_i x[t * xs + i] * w(i, j) for t < t_rows, j < outer, with
+ * w(i, j) = w[j * inner + i], or w[i * outer + j] when in_out; every other word of the out_len plane zero.  Exact: each
+ * activation splits as 256 hi + lo (hi signed, lo unsigned byte), the two int8 products accumulate in int32 on the tensor
+ * cores (|sum lo w| <= K * 32,640 < 2^31 for K <= 65,536, metal.rs:4234), and the plane is 256 P_hi + P_lo in int64.
+ * *taken = 0 (and HL_B200_OK) when the CPU must take the product: an activation outside int16, or a shape outside
+ * inner <= 65,536, xs >= inner, os >= outer, the rows inside x_len / out_len, inner * outer <= w_len.
+ * The _dev form takes device pointers (weights resident in HBM across requests) and is asynchronous up to its own flag read. */
+int hl_b200_witness_product(hl_ctx* ctx, size_t t_rows, const int64_t* x, size_t x_len, size_t xs, const int8_t* w, size_t w_len, size_t inner,
+                            size_t outer, size_t os, size_t out_len, int in_out, int64_t* out, int* taken);
+int hl_b200_witness_product_dev(hl_ctx* ctx, size_t t_rows, const int64_t* d_x, size_t x_len, size_t xs, const int8_t* d_w, size_t w_len, size_t inner,
+                                size_t outer, size_t os, size_t out_len, int in_out, int64_t* d_out, int* taken);
+
 /* ---- the masking commitment M of a block (hashline/src/zk.rs:447-536 mask_commit / mask_commit_tagged) and the product
  * polynomial of its opening (zk.rs:618-637 mask_open) ----
  * mask_commit: `msgs` = n_msg_rows rows of 2^log_msg EVALUATIONS (a mask's real or imaginary coefficients, its pads, zeros:
@@ -303,7 +316,7 @@ int hl_b200_stats(hl_ctx* ctx, hl_stats* out);
 
 /* ---- per-kernel-family device time: the phase clock of timing.rs:1-130 / HL_METAL_TIMING
  * (metal.rs:2148-2179), taken with CUDA events on the context's stream.  Off by default. ---- */
-enum { HL_T_ENCODE = 0, HL_T_HASH = 1, HL_T_MERKLE = 2, HL_T_FOLD = 3, HL_T_GATHER = 4, HL_T_ROUNDS = 5, HL_T_LOGUP = 6, HL_T_TABLES = 7, HL_T_COUNT = 8 };
+enum { HL_T_ENCODE = 0, HL_T_HASH = 1, HL_T_MERKLE = 2, HL_T_FOLD = 3, HL_T_GATHER = 4, HL_T_ROUNDS = 5, HL_T_LOGUP = 6, HL_T_TABLES = 7, HL_T_WITNESS = 8, HL_T_COUNT = 9 };
 typedef struct {
     double ms[HL_T_COUNT];        /* summed device time per family since the last reset */
     uint64_t spans[HL_T_COUNT];   /* timed spans per family (one span = the family's launches of one call) */

@@ -55,6 +55,8 @@ class FsState(C.Structure):
 SIGNATURES.update({
     "hl_b200_rounds_new": (_int, [_vp, _int, _sz, _u32, _u32, _vp, _vp, _sz, _pp]),
     "hl_b200_rounds_new_ir": (_int, [_vp, _sz, _u32, _u32, _vp, _vp, _sz, _u32, _u32, _vp, _sz, _pp]),
+    "hl_b200_witness_product": (_int, [_vp, _sz, _vp, _sz, _sz, _vp, _sz, _sz, _sz, _sz, _sz, _int, _vp, _vp]),
+    "hl_b200_witness_product_dev": (_int, [_vp, _sz, _vp, _sz, _sz, _vp, _sz, _sz, _sz, _sz, _sz, _int, _vp, _vp]),
     "hl_b200_mask_commit": (_int, [_vp, _u32, _u32, _vp, _sz, _vp, _sz, _vp, _vp, _vp, _vp, _vp]),
     "hl_b200_mask_open_q": (_int, [_vp, _sz, _vp, _vp]),
     "hl_b200_lookup_inverse_table": (_int, [_vp, _vp, _vp, _u32, _vp]),
@@ -91,11 +93,11 @@ SIGNATURES["hl_b200_compress_peak"] = (_int, [_vp, _u32, C.POINTER(C.c_double)])
 
 SIGNATURES["hl_b200_set_alloc_cap"] = (_int, [_vp, _sz])
 
-T_NAMES = ("encode", "hash", "merkle", "fold", "gather", "rounds", "logup", "tables")
+T_NAMES = ("encode", "hash", "merkle", "fold", "gather", "rounds", "logup", "tables", "witness")
 
 
 class Timing(C.Structure):
-    _fields_ = [("ms", C.c_double * 8), ("spans", C.c_uint64 * 8)]
+    _fields_ = [("ms", C.c_double * 9), ("spans", C.c_uint64 * 9)]
 
 
 SIGNATURES["hl_b200_timing_enable"] = (_int, [_vp, _int])

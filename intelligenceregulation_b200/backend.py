@@ -131,6 +131,23 @@ class Context:
         self.check(self.lib.hl_b200_lookup_helpers_dev(self.h, C.c_void_p(d_a), C.c_void_p(d_table_a), log_a, _ptr(ga), C.c_void_p(d_b) if d_b else None,
                                                        C.c_void_p(d_table_b) if d_b else None, log_b, _ptr(gb), _ptr(al), n, C.c_void_p(d_re), C.c_void_p(d_im)))
 
+    def witness_product(self, t_rows: int, x, xs: int, w, inner: int, outer: int, os_: int, out_len: int, in_out: bool) -> Optional[np.ndarray]:
+        """``gpu::witness_product`` (metal.rs:4646-4680): the exact int16 x int8 -> int64 plane, or None when the CPU must take
+        it (an activation outside int16, a shape outside the kernels' bounds)."""
+        x, w = np.ascontiguousarray(x, np.int64), np.ascontiguousarray(w, np.int8)
+        out, taken = np.empty(out_len, dtype=np.int64), C.c_int(0)
+        self.check(self.lib.hl_b200_witness_product(self.h, t_rows, _ptr(x), x.size, xs, _ptr(w), w.size, inner, outer, os_, out_len,
+                                                    1 if in_out else 0, _ptr(out), C.byref(taken)))
+        return out if taken.value else None
+
+    def witness_product_dev(self, t_rows: int, d_x: int, x_len: int, xs: int, d_w: int, w_len: int, inner: int, outer: int, os_: int, out_len: int,
+                            in_out: bool, d_out: int) -> bool:
+        """The same with activations, weights and the result plane resident on the device; False = not taken."""
+        taken = C.c_int(0)
+        self.check(self.lib.hl_b200_witness_product_dev(self.h, t_rows, C.c_void_p(d_x), x_len, xs, C.c_void_p(d_w), w_len, inner, outer, os_, out_len,
+                                                        1 if in_out else 0, C.c_void_p(d_out), C.byref(taken)))
+        return bool(taken.value)
+
     def rng_fill(self, key32: bytes, first_word: int, count: int, as_fp: bool) -> np.ndarray:
         """`count` draws of the caller's ZkRng stream (rng.rs:279-417) from word position `first_word`, expanded on the
         device: u64 words, or field elements (two words each) when `as_fp`."""

@@ -26,7 +26,7 @@ _SO = os.path.join(_HERE, "libhl_oracle.so")
 
 def build(force: bool = False) -> str:
     """Compile the oracle with the system gcc (the Makefile beside this file)."""
-    srcs = [os.path.join(_HERE, f) for f in ("blake3.c", "ntt.c", "transcript.c", "sumcheck.c", "logup.c", "hl_oracle.h", "field.h")]
+    srcs = [os.path.join(_HERE, f) for f in ("blake3.c", "ntt.c", "transcript.c", "sumcheck.c", "logup.c", "tables.c", "witness.c", "hl_oracle.h", "field.h")]
     if force or not os.path.exists(_SO) or any(os.path.getmtime(s) > os.path.getmtime(_SO) for s in srcs):
         subprocess.check_call(["make", "-C", _HERE, "-s"])
     return _SO
@@ -946,3 +946,14 @@ def mask_verify(root: bytes, specs, functionals, opening, tr: "Transcript", tag:
         if pacc != (int(p_enc[0][j]), int(p_enc[1][j])):
             return f"mask: column {j} disagrees with the proximity vector"
     return None
+
+
+# ----------------------------------------------------------------------------- witness weight products
+def witness_product(t_rows: int, x, xs: int, w, inner: int, outer: int, os_: int, out_len: int, in_out: bool) -> np.ndarray:
+    """witness.rs:979-991 (matmul_reference)"""
+    x, w = np.ascontiguousarray(x, np.int64), np.ascontiguousarray(w, np.int8)
+    assert (t_rows - 1) * xs + inner <= x.size and inner * outer <= w.size and (t_rows - 1) * os_ + outer <= out_len
+    out = np.empty(out_len, dtype=np.int64)
+    _lib.or_witness_product(C.c_size_t(t_rows), _p(x), C.c_size_t(xs), _p(w), C.c_size_t(inner), C.c_size_t(outer), C.c_size_t(os_),
+                            C.c_size_t(out_len), C.c_int(1 if in_out else 0), _p(out))
+    return out
