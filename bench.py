@@ -317,6 +317,30 @@ def device_extras(dev, backend, np_data, np_pads, np_pows, col_key) -> dict:
             t_c, t_o = t_c + (t1 - t0) * 1e3 / 3, t_o + (t2 - t1) * 1e3 / 3
     out["mask_M_24masks_commit_and_tree_wall_ms"] = t_c  # host wall time of the calls: uploads, launches, read-backs
     out["mask_M_24masks_open_wall_ms"] = t_o
+    # the witness weight products of one 8B block at T = 128 (witness.rs:818-835): q, k, v, o, gate, up, down with the
+    # weights resident; int16 activations, int8 weights, exact int64 planes
+    wp_shapes = [("q", 4096, 4096), ("k", 4096, 1024), ("v", 4096, 1024), ("o", 4096, 4096), ("gate", 4096, 14336), ("up", 4096, 14336), ("down", 14336, 4096)]
+    gw = torch.Generator(device="cuda").manual_seed(5)
+    d_wmax = torch.randint(-128, 128, (4096 * 14336,), dtype=torch.int8, device="cuda", generator=gw)
+    d_xw = torch.randint(-32768, 32768, (128 * 14336,), dtype=torch.int64, device="cuda", generator=gw)
+    d_ow = torch.empty(128 * 14336, dtype=torch.int64, device="cuda")
+    torch.cuda.synchronize()
+    per, macs = {}, 0
+    for name, kk, nn2 in wp_shapes:
+        for rep in range(4):
+            if rep == 1:
+                ctx.timing_read(reset=True)
+            assert ctx.witness_product_dev(128, d_xw.data_ptr(), 128 * kk, kk, d_wmax.data_ptr(), kk * nn2, kk, nn2, nn2, 128 * nn2, False, d_ow.data_ptr())
+        per[name] = round(ctx.timing_read(reset=True)["witness"][0] / 3, 4)
+        macs += 128 * kk * nn2
+    tot = sum(per.values())
+    out["witness_products_8B_block_T128_ms"] = tot
+    mma_peak = ctx.mma_i8_peak(2000)
+    out["witness_products_detail"] = {"per_product_ms": per, "int8_TMAC_per_s": 2 * macs / (tot * 1e-3) / 1e12,
+                                      "mma_m16n8k32_register_resident_TMAC_per_s": mma_peak / 1e12,
+                                      "weight_bytes": sum(k_ * n_ for _, k_, n_ in wp_shapes),
+                                      "weights_read_once_at_measured_hbm_ms": sum(k_ * n_ for _, k_, n_ in wp_shapes) / 6549.8e9 * 1e3}
+    del d_wmax, d_xw, d_ow
     # the T256 / T512 profiles (shape.rs:248-262): the same 41 M words as rows of 2^15 and 2^16, which run as 2 or 4
     # shared-memory transforms of 2^14 each way
     for lc, rws in ((15, rows // 2), (16, rows // 4)):
@@ -467,6 +491,10 @@ def cpu_extras(o, backend, np_data) -> dict:
         ta, tb = o.lookup_inverse_table((21, 22), (23, 24), 256), o.lookup_inverse_table((21, 22), (25, 26), 256)
         o.lookup_helpers(la, ta, (23, 24), (21, 22), b=lb, tab_b=tb, g_b=(25, 26))
 
+    rngw = np.random.default_rng(5)
+    xw, ww = rngw.integers(-32768, 32768, 128 * 4096, dtype=np.int64), rngw.integers(-128, 128, 4096 * 1024, dtype=np.int8)
+    out["witness_products_8B_block_T128_ms"] = timed(lambda: o.witness_product(128, xw, 4096, ww, 4096, 1024, 1024, 128 * 1024, False)) * (218103808 / 4194304)
+    notes["witness_products_8B_block_T128_ms"] = "the k projection (128 x 4096 x 1024) on all cores, scaled by weight count to the block's seven products"
     specs = [(21, 3)] * 12 + [(19, 5)] * 8 + [(14, 2)] * 4
     tg = o.HashTag.for_profile(w["profile"])
     box = {}

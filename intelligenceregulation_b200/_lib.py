@@ -55,6 +55,7 @@ class FsState(C.Structure):
 SIGNATURES.update({
     "hl_b200_rounds_new": (_int, [_vp, _int, _sz, _u32, _u32, _vp, _vp, _sz, _pp]),
     "hl_b200_rounds_new_ir": (_int, [_vp, _sz, _u32, _u32, _vp, _vp, _sz, _u32, _u32, _vp, _sz, _pp]),
+    "hl_b200_mma_i8_peak": (_int, [_vp, _u32, _vp]),
     "hl_b200_witness_product": (_int, [_vp, _sz, _vp, _sz, _sz, _vp, _sz, _sz, _sz, _sz, _sz, _int, _vp, _vp]),
     "hl_b200_witness_product_dev": (_int, [_vp, _sz, _vp, _sz, _sz, _vp, _sz, _sz, _sz, _sz, _sz, _int, _vp, _vp]),
     "hl_b200_mask_commit": (_int, [_vp, _u32, _u32, _vp, _sz, _vp, _sz, _vp, _vp, _vp, _vp, _vp]),

@@ -131,6 +131,12 @@ class Context:
         self.check(self.lib.hl_b200_lookup_helpers_dev(self.h, C.c_void_p(d_a), C.c_void_p(d_table_a), log_a, _ptr(ga), C.c_void_p(d_b) if d_b else None,
                                                        C.c_void_p(d_table_b) if d_b else None, log_b, _ptr(gb), _ptr(al), n, C.c_void_p(d_re), C.c_void_p(d_im)))
 
+    def mma_i8_peak(self, iters: int = 2000) -> float:
+        """int8 tensor-core multiply-adds per second of the product kernel's instruction, register resident."""
+        v = C.c_double()
+        self.check(self.lib.hl_b200_mma_i8_peak(self.h, iters, C.byref(v)))
+        return v.value
+
     def witness_product(self, t_rows: int, x, xs: int, w, inner: int, outer: int, os_: int, out_len: int, in_out: bool) -> Optional[np.ndarray]:
         """``gpu::witness_product`` (metal.rs:4646-4680): the exact int16 x int8 -> int64 plane, or None when the CPU must take
         it (an activation outside int16, a shape outside the kernels' bounds)."""

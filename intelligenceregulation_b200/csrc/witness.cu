@@ -70,6 +70,12 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
+// four 8 x 16-byte matrices from shared memory, one row address per lane (lanes 8 i .. 8 i + 7 give matrix i)
+__device__ __forceinline__ void ldmatrix_x4(u32 (&r)[4], const void* smem_row) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem_row);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+
 __device__ __forceinline__ void mma_s8s8(int (&c)[4], const u32 (&a)[4], const u32 (&b)[2]) {
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                  : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
@@ -132,20 +138,17 @@ __global__ void __launch_bounds__(WP_THREADS, 2) k_wp_gemm(const uint8_t* __rest
         const uint8_t* bs = Bs + (size_t)(it % WP_STAGES) * WP_NT * WP_LD + (size_t)(warp_n * 32) * WP_LD;
 #pragma unroll
         for (int kk = 0; kk < WP_KT; kk += 32) {
+            // fragments of m16n8k32 with 8-bit operands: A = (rows g / g + 8) x (bytes 4 tig.. / 16 + 4 tig..), B = column g x the same
+            // bytes: exactly the 8 x 16-byte matrices ldmatrix hands out, one instruction per A tile and per pair of B tiles
             u32 a[4][4], b[4][2];
 #pragma unroll
-            for (int mi = 0; mi < 4; mi++) {
-                const uint8_t* p = as + (size_t)(mi * 16 + g) * WP_LD + kk + tig * 4;
-                a[mi][0] = *reinterpret_cast<const u32*>(p);
-                a[mi][1] = *reinterpret_cast<const u32*>(p + 8 * WP_LD);
-                a[mi][2] = *reinterpret_cast<const u32*>(p + 16);
-                a[mi][3] = *reinterpret_cast<const u32*>(p + 8 * WP_LD + 16);
-            }
+            for (int mi = 0; mi < 4; mi++)
+                ldmatrix_x4(a[mi], as + (size_t)(mi * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * WP_LD + kk + (lane >> 4) * 16);
 #pragma unroll
-            for (int ni = 0; ni < 4; ni++) {
-                const uint8_t* p = bs + (size_t)(ni * 8 + g) * WP_LD + kk + tig * 4;
-                b[ni][0] = *reinterpret_cast<const u32*>(p);
-                b[ni][1] = *reinterpret_cast<const u32*>(p + 16);
+            for (int np = 0; np < 2; np++) {
+                u32 r[4];
+                ldmatrix_x4(r, bs + (size_t)(np * 16 + (lane & 7) + (lane >> 4) * 8) * WP_LD + kk + ((lane >> 3) & 1) * 16);
+                b[2 * np][0] = r[0]; b[2 * np][1] = r[1]; b[2 * np + 1][0] = r[2]; b[2 * np + 1][1] = r[3];
             }
             if (warp_m < 2) {  // rows 0..127 of the stacked tile: the signed high bytes
 #pragma unroll
@@ -188,6 +191,29 @@ __global__ void __launch_bounds__(256) k_wp_combine(const int* __restrict__ P, u
         out[(size_t)t * os + j] = 256ll * hi[j] + lo[j];
 }
 
+// Register-resident int8 tensor-core products: the ceiling of the m16n8k32 instruction the product kernel issues (16
+// independent accumulators per warp, 8 warps per CTA, 2 CTAs per SM, operands never reloaded).
+__global__ void __launch_bounds__(WP_THREADS, 2) k_mma_i8_peak(u32 iters, int* __restrict__ sink) {
+    int acc[16][4];
+    u32 a[4], b[2];
+#pragma unroll
+    for (int i = 0; i < 4; i++) a[i] = threadIdx.x * 0x01010101u + i;
+    b[0] = threadIdx.x ^ 0x7F3C11A5u;
+    b[1] = blockIdx.x + 0x01020304u;
+#pragma unroll
+    for (int i = 0; i < 16; i++)
+#pragma unroll
+        for (int x = 0; x < 4; x++) acc[i][x] = 0;
+    for (u32 it = 0; it < iters; it++) {
+#pragma unroll
+        for (int i = 0; i < 16; i++) mma_s8s8(acc[i], a, b);
+    }
+    int v = 0;
+#pragma unroll
+    for (int i = 0; i < 16; i++) v ^= acc[i][0] ^ acc[i][3];
+    if (v == 0x5EED5EED) sink[0] = v;
+}
+
 // everything on the context's stream; d_* are device pointers; *flag_out is read after one synchronisation
 int product_on_device(hl_ctx* c, size_t t_rows, const int64_t* d_x, size_t xs, const int8_t* d_w, size_t K, size_t N, size_t os, size_t out_len,
                       int in_out, int64_t* d_out, int* taken) {
@@ -204,10 +230,16 @@ int product_on_device(hl_ctx* c, size_t t_rows, const int64_t* d_x, size_t xs, c
     if (!rc && b_bytes) rc = dev_alloc(c, (void**)&d_b, b_bytes);
     // the split over K: enough CTAs for two per SM, each with at least four K stages
     const u32 n_tiles = Np / WP_NT, kt_all = Kp / WP_KT;
-    u32 splits = (2u * (u32)c->sm_count + n_tiles * tiles - 1) / (n_tiles * tiles);
-    if (splits > kt_all / 4) splits = kt_all / 4;
-    if (splits < 1) splits = 1;
-    if (splits > 65535) splits = 65535;
+    // every CTA does the same work, so what counts is how full the last wave of 2 CTAs per SM is: the smallest split that
+    // fills the waves best, each split keeping at least four K stages
+    const u32 slots = 2u * (u32)c->sm_count, base = n_tiles * tiles;
+    u32 splits = 1;
+    double best = 0.0;
+    for (u32 sp = 1; sp <= 16 && sp <= (kt_all / 4 ? kt_all / 4 : 1); sp++) {
+        const u64 ctas = (u64)base * sp;
+        const double eff = (double)ctas / (double)((ctas + slots - 1) / slots * slots);
+        if (eff > best + 0.02) { best = eff; splits = sp; }
+    }
     int flag = 0;
     if (!rc) {
         Timed t(c, HL_T_WITNESS);
@@ -263,6 +295,34 @@ bool shape_fits(size_t t_rows, size_t x_len, size_t xs, size_t w_len, size_t inn
 }  // namespace
 
 extern "C" {
+
+int hl_b200_mma_i8_peak(hl_ctx* c, uint32_t iters, double* macs_per_second) {
+    if (!c || !macs_per_second || iters == 0) return fail(c, HL_B200_ERR_ARG, "mma_i8_peak: argument");
+    std::lock_guard<std::mutex> g(c->mu);
+    cudaSetDevice(c->device);
+    int* d_sink = nullptr;
+    int rc = dev_alloc(c, (void**)&d_sink, 4);
+    cudaEvent_t a = nullptr, b = nullptr;
+    float ms = 0.f;
+    const int blocks = c->sm_count * 2;
+    if (!rc) {
+        cudaEventCreate(&a); cudaEventCreate(&b);
+        k_mma_i8_peak<<<blocks, WP_THREADS, 0, c->stream>>>(8, d_sink);  // warm-up
+        cudaEventRecord(a, c->stream);
+        k_mma_i8_peak<<<blocks, WP_THREADS, 0, c->stream>>>(iters, d_sink);
+        cudaEventRecord(b, c->stream);
+        c->stats.kernel_launches += 2;
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "mma_i8_peak launch", e);
+    }
+    if (!rc) rc = sync(c, "mma_i8_peak");
+    if (!rc && cudaEventElapsedTime(&ms, a, b) != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "mma_i8_peak timing");
+    if (a) cudaEventDestroy(a);
+    if (b) cudaEventDestroy(b);
+    if (d_sink) dev_free(c, d_sink, 4);
+    if (!rc) *macs_per_second = (double)blocks * (WP_THREADS / 32) * 16.0 * 4096.0 * iters / (ms * 1e-3);
+    return rc;
+}
 
 int hl_b200_witness_product_dev(hl_ctx* c, size_t t_rows, const int64_t* d_x, size_t x_len, size_t xs, const int8_t* d_w, size_t w_len, size_t inner,
                                 size_t outer, size_t os, size_t out_len, int in_out, int64_t* d_out, int* taken) {
