@@ -16,11 +16,13 @@ using namespace hlapi;
 namespace {
 
 constexpr int WP_MT = 128;      // tokens per tile; the stacked tile has 2 * WP_MT rows (hi rows, then lo rows)
-constexpr int WP_NT = 64;       // output columns per CTA
-constexpr int WP_KT = 64;       // K bytes per stage
-constexpr int WP_LD = 80;       // shared-memory row pitch in bytes: 20 words, so the 8 rows of a fragment fall in distinct banks
+constexpr int WP_NT = 128;      // output columns per CTA
+constexpr int WP_KT = 128;      // K bytes per stage: whole 128-byte lines of every row
+constexpr int WP_LD = WP_KT + 16;  // shared-memory row pitch in bytes: 36 words, so the 8 rows of a fragment fall in distinct banks
 constexpr int WP_STAGES = 3;
-constexpr int WP_THREADS = 256;
+constexpr int WP_THREADS = 512;  // 16 warps: 4 over the stacked rows x 4 over the columns, 64 x 32 outputs each
+constexpr int WP_CTAS_PER_SM = 1;
+constexpr int WP_CH = WP_KT / 16;  // 16-byte chunks per row and stage
 constexpr size_t WP_MAX_K = (size_t)1 << 16;
 
 __global__ void __launch_bounds__(256) k_wp_pack(const long long* __restrict__ x, size_t xs, u32 t_rows, u32 K, u32 Kp,
@@ -88,7 +90,7 @@ __device__ __forceinline__ void mma_u8s8(int (&c)[4], const u32 (&a)[4], const u
 }
 
 // grid (N tiles, K splits, token tiles); B rows of ldb bytes hold one output column's K weights, readable up to Kp
-__global__ void __launch_bounds__(WP_THREADS, 2) k_wp_gemm(const uint8_t* __restrict__ A, const int8_t* __restrict__ B, size_t ldb, u32 N, u32 Kp,
+__global__ void __launch_bounds__(WP_THREADS, WP_CTAS_PER_SM) k_wp_gemm(const uint8_t* __restrict__ A, const int8_t* __restrict__ B, size_t ldb, u32 N, u32 Kp,
                                                           u32 Np, int* __restrict__ P /* tiles x 2 WP_MT x Np */) {
     extern __shared__ __align__(16) uint8_t smem[];
     uint8_t* As = smem;                                        // stages x 256 x WP_LD
@@ -104,12 +106,13 @@ __global__ void __launch_bounds__(WP_THREADS, 2) k_wp_gemm(const uint8_t* __rest
         uint8_t* as = As + (size_t)st * 2 * WP_MT * WP_LD;
         uint8_t* bs = Bs + (size_t)st * WP_NT * WP_LD;
 #pragma unroll
-        for (int i = 0; i < 4; i++) {  // 256 rows x 4 chunks of 16 bytes
-            const u32 e = tid + i * WP_THREADS, row = e >> 2, c = e & 3;
+        for (int i = 0; i < 2 * WP_MT * WP_CH / WP_THREADS; i++) {
+            const u32 e = tid + i * WP_THREADS, row = e / WP_CH, c = e % WP_CH;
             cp_async16(as + row * WP_LD + c * 16, Ag + (size_t)row * Kp + k0 + c * 16);
         }
-        {
-            const u32 row = tid >> 2, c = tid & 3;
+#pragma unroll
+        for (int i = 0; i < WP_NT * WP_CH / WP_THREADS; i++) {
+            const u32 e = tid + i * WP_THREADS, row = e / WP_CH, c = e % WP_CH;
             const u32 n = min(n0 + row, N - 1);  // columns past N repeat the last one; they are never written out
             cp_async16(bs + row * WP_LD + c * 16, B + (size_t)n * ldb + k0 + c * 16);
         }
@@ -193,24 +196,36 @@ __global__ void __launch_bounds__(256) k_wp_combine(const int* __restrict__ P, u
 
 // Register-resident int8 tensor-core products: the ceiling of the m16n8k32 instruction the product kernel issues (16
 // independent accumulators per warp, 8 warps per CTA, 2 CTAs per SM, operands never reloaded).
-__global__ void __launch_bounds__(WP_THREADS, 2) k_mma_i8_peak(u32 iters, int* __restrict__ sink) {
-    int acc[16][4];
-    u32 a[4], b[2];
+__global__ void __launch_bounds__(256, 2) k_mma_i8_peak(u32 iters, int* __restrict__ sink) {
+    int acc[4][4][4];
+    u32 a[4][4], b[4][2];
 #pragma unroll
-    for (int i = 0; i < 4; i++) a[i] = threadIdx.x * 0x01010101u + i;
-    b[0] = threadIdx.x ^ 0x7F3C11A5u;
-    b[1] = blockIdx.x + 0x01020304u;
+    for (int m = 0; m < 4; m++)
 #pragma unroll
-    for (int i = 0; i < 16; i++)
+        for (int i = 0; i < 4; i++) a[m][i] = threadIdx.x * 0x01010101u + 16 * m + i;
 #pragma unroll
-        for (int x = 0; x < 4; x++) acc[i][x] = 0;
+    for (int n = 0; n < 4; n++) {
+        b[n][0] = threadIdx.x ^ (0x7F3C11A5u + n);
+        b[n][1] = blockIdx.x + 0x01020304u * (n + 1);
+    }
+#pragma unroll
+    for (int m = 0; m < 4; m++)
+#pragma unroll
+        for (int n = 0; n < 4; n++)
+#pragma unroll
+            for (int x = 0; x < 4; x++) acc[m][n][x] = 0;
+    // the product kernel's own register pattern: 4 A tiles x 4 B tiles, 16 accumulators
     for (u32 it = 0; it < iters; it++) {
 #pragma unroll
-        for (int i = 0; i < 16; i++) mma_s8s8(acc[i], a, b);
+        for (int m = 0; m < 4; m++)
+#pragma unroll
+            for (int n = 0; n < 4; n++) mma_s8s8(acc[m][n], a[m], b[n]);
     }
     int v = 0;
 #pragma unroll
-    for (int i = 0; i < 16; i++) v ^= acc[i][0] ^ acc[i][3];
+    for (int m = 0; m < 4; m++)
+#pragma unroll
+        for (int n = 0; n < 4; n++) v ^= acc[m][n][0] ^ acc[m][n][3];
     if (v == 0x5EED5EED) sink[0] = v;
 }
 
@@ -230,14 +245,15 @@ int product_on_device(hl_ctx* c, size_t t_rows, const int64_t* d_x, size_t xs, c
     if (!rc && b_bytes) rc = dev_alloc(c, (void**)&d_b, b_bytes);
     // the split over K: enough CTAs for two per SM, each with at least four K stages
     const u32 n_tiles = Np / WP_NT, kt_all = Kp / WP_KT;
-    // every CTA does the same work, so what counts is how full the last wave of 2 CTAs per SM is: the smallest split that
-    // fills the waves best, each split keeping at least four K stages
-    const u32 slots = 2u * (u32)c->sm_count, base = n_tiles * tiles;
+    // every CTA does the same work, so what counts is how full the last wave of resident CTAs is: the smallest split that
+    // fills the waves best, each split keeping at least two K stages
+    const u32 slots = (u32)WP_CTAS_PER_SM * (u32)c->sm_count, base = n_tiles * tiles;
     u32 splits = 1;
     double best = 0.0;
-    for (u32 sp = 1; sp <= 16 && sp <= (kt_all / 4 ? kt_all / 4 : 1); sp++) {
+    for (u32 sp = 1; sp <= 32 && sp <= (kt_all / 2 ? kt_all / 2 : 1); sp++) {
         const u64 ctas = (u64)base * sp;
-        const double eff = (double)ctas / (double)((ctas + slots - 1) / slots * slots);
+        // each further split adds one pass of integer atomics over the 256 x N plane: charged at 3 % of a product's time
+        const double eff = (double)ctas / (double)((ctas + slots - 1) / slots * slots) / (1.0 + 0.03 * (sp - 1));
         if (eff > best + 0.02) { best = eff; splits = sp; }
     }
     int flag = 0;
@@ -307,9 +323,9 @@ int hl_b200_mma_i8_peak(hl_ctx* c, uint32_t iters, double* macs_per_second) {
     const int blocks = c->sm_count * 2;
     if (!rc) {
         cudaEventCreate(&a); cudaEventCreate(&b);
-        k_mma_i8_peak<<<blocks, WP_THREADS, 0, c->stream>>>(8, d_sink);  // warm-up
+        k_mma_i8_peak<<<blocks, 256, 0, c->stream>>>(8, d_sink);  // warm-up
         cudaEventRecord(a, c->stream);
-        k_mma_i8_peak<<<blocks, WP_THREADS, 0, c->stream>>>(iters, d_sink);
+        k_mma_i8_peak<<<blocks, 256, 0, c->stream>>>(iters, d_sink);
         cudaEventRecord(b, c->stream);
         c->stats.kernel_launches += 2;
         cudaError_t e = cudaGetLastError();
@@ -320,7 +336,7 @@ int hl_b200_mma_i8_peak(hl_ctx* c, uint32_t iters, double* macs_per_second) {
     if (a) cudaEventDestroy(a);
     if (b) cudaEventDestroy(b);
     if (d_sink) dev_free(c, d_sink, 4);
-    if (!rc) *macs_per_second = (double)blocks * (WP_THREADS / 32) * 16.0 * 4096.0 * iters / (ms * 1e-3);
+    if (!rc) *macs_per_second = (double)blocks * 8 * 16.0 * 4096.0 * iters / (ms * 1e-3);
     return rc;
 }
 
