@@ -256,6 +256,22 @@ int hl_b200_logup_histogram(hl_ctx* ctx, const int32_t* idx, size_t nq, size_t t
 int hl_b200_logup_helpers(hl_ctx* ctx, const int32_t* idx, const int32_t* outv, size_t n, const uint64_t alpha[2],
                           const uint64_t beta[2], const uint64_t tag[2], int64_t idx_off, const uint64_t* mult, uint64_t* h);
 
+/* ---- the three-coordinate activation lookup of the accuracy lane (private_block/accuracy_act.rs:13-117) ----
+ * Queries sit on rows of f_pad words (n = rows * f_pad); group(i) = group_ids[i % f_pad] when i / f_pad < tokens and
+ * i % f_pad < hidden, else 0 (query_group, :52-54).  tables = groups x 4096 words (scaled_tables), groups 1 .. 4.
+ * act_histogram (:61-79): counts[group * 4096 + gate + 2048]++ when the key is in range and tables[group][key] == output, else
+ *   counts[0]++ and (*misses)++; every query counted, padding included.
+ * act_helpers: h[i] = 1 / (alpha - (gate_i + 2048 + beta * output_i + beta^2 * group(i) + tag)) (denominators, :106-124, then
+ *   protocol.rs:993 inverses); HL_B200_ERR_ZERO on a zero denominator, nothing written then.
+ * act_table (:13-31 with protocol.rs:1928 table_helper): compressed[i] = (i % 4096) + beta * word_i + beta^2 * (i / 4096) + tag for
+ *   i < groups * 4096, 2048 + tag up to len (a power of two); ht[i] = mult[i] / (alpha - compressed[i]).  compressed may be NULL. */
+int hl_b200_act_histogram(hl_ctx* ctx, const int64_t* gates, const int64_t* outputs, size_t n, size_t f_pad, size_t tokens, size_t hidden,
+                          const uint32_t* group_ids, const int64_t* tables, size_t groups, uint64_t* counts, uint64_t* misses);
+int hl_b200_act_helpers(hl_ctx* ctx, const int64_t* gates, const int64_t* outputs, size_t n, size_t f_pad, size_t tokens, size_t hidden,
+                        const uint32_t* group_ids, const uint64_t alpha[2], const uint64_t beta[2], const uint64_t tag[2], uint64_t* h);
+int hl_b200_act_table(hl_ctx* ctx, const int64_t* tables, size_t groups, size_t len, const uint64_t* mult, const uint64_t alpha[2],
+                      const uint64_t beta[2], const uint64_t tag[2], uint64_t* compressed, uint64_t* ht);
+
 /* ---- witness weight products (hashline/src/gpu/metal.rs:4646-4680 witness_product; private_block/witness.rs:818-835 on_device,
  * :979-991 matmul_reference): out[t * os + j] = sum_i x[t * xs + i] * w(i, j) for t < t_rows, j < outer, with
  * w(i, j) = w[j * inner + i], or w[i * outer + j] when in_out; every other word of the out_len plane zero.  Exact: each

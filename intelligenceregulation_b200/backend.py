@@ -131,6 +131,34 @@ class Context:
         self.check(self.lib.hl_b200_lookup_helpers_dev(self.h, C.c_void_p(d_a), C.c_void_p(d_table_a), log_a, _ptr(ga), C.c_void_p(d_b) if d_b else None,
                                                        C.c_void_p(d_table_b) if d_b else None, log_b, _ptr(gb), _ptr(al), n, C.c_void_p(d_re), C.c_void_p(d_im)))
 
+    def act_histogram(self, gates, outputs, f_pad: int, tokens: int, hidden: int, group_ids, tables):
+        """``accuracy_act::histogram`` (accuracy_act.rs:61-79): (counts, misses)."""
+        gates, outputs = np.ascontiguousarray(gates, np.int64), np.ascontiguousarray(outputs, np.int64)
+        ids, tables = np.ascontiguousarray(group_ids, np.uint32), np.ascontiguousarray(tables, np.int64)
+        groups = tables.size // 4096
+        counts, misses = np.empty(groups * 4096, dtype=np.uint64), C.c_uint64(0)
+        self.check(self.lib.hl_b200_act_histogram(self.h, _ptr(gates), _ptr(outputs), gates.size, f_pad, tokens, hidden, _ptr(ids), _ptr(tables),
+                                                  groups, _ptr(counts), C.byref(misses)))
+        return counts, int(misses.value)
+
+    def act_helpers(self, gates, outputs, f_pad: int, tokens: int, hidden: int, group_ids, alpha, beta, tag) -> np.ndarray:
+        """1 / ``accuracy_act::denominators`` (accuracy_act.rs:106-124, protocol.rs:993); DeviceError ERR_ZERO on a zero one."""
+        gates, outputs = np.ascontiguousarray(gates, np.int64), np.ascontiguousarray(outputs, np.int64)
+        ids = np.ascontiguousarray(group_ids, np.uint32)
+        a, b, t = (np.array(v, dtype=np.uint64) for v in (alpha, beta, tag))
+        h = np.empty((gates.size, 2), dtype=np.uint64)
+        self.check(self.lib.hl_b200_act_helpers(self.h, _ptr(gates), _ptr(outputs), gates.size, f_pad, tokens, hidden, _ptr(ids), _ptr(a), _ptr(b),
+                                                _ptr(t), _ptr(h)))
+        return h
+
+    def act_table(self, tables, length: int, mult, alpha, beta, tag):
+        """``accuracy_act::table`` (accuracy_act.rs:13-31) and its helper m / (alpha - t) (protocol.rs:1928): (compressed, ht)."""
+        tables, mult = np.ascontiguousarray(tables, np.int64), _u64(mult)
+        a, b, t = (np.array(v, dtype=np.uint64) for v in (alpha, beta, tag))
+        comp, ht = np.empty((length, 2), dtype=np.uint64), np.empty((length, 2), dtype=np.uint64)
+        self.check(self.lib.hl_b200_act_table(self.h, _ptr(tables), tables.size // 4096, length, _ptr(mult), _ptr(a), _ptr(b), _ptr(t), _ptr(comp), _ptr(ht)))
+        return comp, ht
+
     def mma_i8_peak(self, iters: int = 2000) -> float:
         """int8 tensor-core multiply-adds per second of the product kernel's instruction, register resident."""
         v = C.c_double()

@@ -590,6 +590,48 @@ def lookup_helpers(a, tab_a, g_a, alpha, b=None, tab_b=None, g_b=None):
     return None if bad else (re, im)
 
 
+def act_histogram(gates, outputs, f_pad: int, tokens: int, hidden: int, group_ids, tables):
+    """accuracy_act.rs:61-79: (counts (groups * 4096,), misses)."""
+    gates, outputs = np.ascontiguousarray(gates, np.int64), np.ascontiguousarray(outputs, np.int64)
+    ids, tables = np.ascontiguousarray(group_ids, np.uint32), np.ascontiguousarray(tables, np.int64)
+    groups = tables.size // 4096
+    counts = np.empty(groups * 4096, dtype=np.uint64)
+    _lib.or_act_histogram.restype = C.c_uint64
+    misses = _lib.or_act_histogram(_p(gates), _p(outputs), C.c_size_t(gates.size), C.c_size_t(f_pad), C.c_size_t(tokens), C.c_size_t(hidden),
+                                   _p(ids), _p(tables), C.c_size_t(groups), _p(counts))
+    return counts, int(misses)
+
+
+def act_query_values(gates, outputs, f_pad: int, tokens: int, hidden: int, group_ids, beta, tag) -> np.ndarray:
+    """accuracy_act.rs:88-95"""
+    gates, outputs = np.ascontiguousarray(gates, np.int64), np.ascontiguousarray(outputs, np.int64)
+    ids = np.ascontiguousarray(group_ids, np.uint32)
+    q = np.empty((gates.size, 2), dtype=np.uint64)
+    _lib.or_act_query_values(_p(gates), _p(outputs), C.c_size_t(gates.size), C.c_size_t(f_pad), C.c_size_t(tokens), C.c_size_t(hidden), _p(ids),
+                             (C.c_uint64 * 2)(*beta), (C.c_uint64 * 2)(*tag), _p(q))
+    return q
+
+
+def act_helpers(gates, outputs, f_pad: int, tokens: int, hidden: int, group_ids, alpha, beta, tag):
+    """denominators (accuracy_act.rs:106-124) then protocol.rs:993 inverses; None = "zero LogUp denominator"."""
+    q = act_query_values(gates, outputs, f_pad, tokens, hidden, group_ids, beta, tag).astype(object)
+    den = np.stack([(int(alpha[0]) - q[:, 0]) % _P0, (int(alpha[1]) - q[:, 1]) % _P0], axis=1).astype(np.uint64)
+    if ((den[:, 0] | den[:, 1]) == 0).any():
+        return None
+    return batch_inverse2(den)
+
+
+def act_table(tables, length: int, beta, tag):
+    """accuracy_act.rs:13-31: (compressed (length, 2), support (length, 2))."""
+    tables = np.ascontiguousarray(tables, np.int64)
+    comp, sup = np.empty((length, 2), dtype=np.uint64), np.empty((length, 2), dtype=np.uint64)
+    _lib.or_act_table(_p(tables), C.c_size_t(tables.size // 4096), C.c_size_t(length), (C.c_uint64 * 2)(*beta), (C.c_uint64 * 2)(*tag), _p(comp), _p(sup))
+    return comp, sup
+
+
+_P0 = 0xFFFFFFFF00000001
+
+
 def logup_table_helper(table_out, mult, alpha, beta, tag) -> np.ndarray:
     table_out, mult = np.ascontiguousarray(table_out, np.int32), _u64(mult)
     ht = np.empty((table_out.size, 2), dtype=np.uint64)

@@ -130,3 +130,63 @@ int or_lookup_helpers(const int64_t *a, const uint64_t *table_a, const uint8_t *
     }
     return bad;
 }
+
+/* ---- the three-coordinate activation lookup (private_block/accuracy_act.rs) ---- */
+static size_t act_group(size_t index, size_t f_pad, size_t tokens, size_t hidden, const uint32_t *group_ids) {
+    /* accuracy_act.rs:52-54 (query_group) */
+    return (index / f_pad < tokens && index % f_pad < hidden) ? group_ids[index % f_pad] : 0;
+}
+
+/* accuracy_act.rs:61-79 (histogram): returns the misses */
+uint64_t or_act_histogram(const int64_t *gates, const int64_t *outputs, size_t n, size_t f_pad, size_t tokens, size_t hidden,
+                          const uint32_t *group_ids, const int64_t *tables, size_t groups, uint64_t *counts) {
+    uint64_t misses = 0;
+    memset(counts, 0, groups * 4096 * sizeof(uint64_t));
+    for (size_t i = 0; i < n; i++) {
+        size_t group = act_group(i, f_pad, tokens, hidden, group_ids), bucket = 0;
+        int64_t g = gates[i];
+        int hit = 0;
+        if (g >= -2048 && g < 2048) {
+            size_t key = (size_t)(g + 2048);
+            if (tables[group * 4096 + key] == outputs[i]) { hit = 1; bucket = group * 4096 + key; }
+        }
+        if (!hit) misses++;
+        counts[bucket]++;
+    }
+    return misses;
+}
+
+/* accuracy_act.rs:88-95 (query_values) */
+void or_act_query_values(const int64_t *gates, const int64_t *outputs, size_t n, size_t f_pad, size_t tokens, size_t hidden,
+                         const uint32_t *group_ids, const uint64_t beta[2], const uint64_t tag[2], uint64_t *q) {
+    fp2_t b = fp2_new(beta[0], beta[1]), tg = fp2_new(tag[0], tag[1]), b2 = fp2_mul(b, b);
+#pragma omp parallel for schedule(static)
+    for (size_t i = 0; i < n; i++) {
+        fp2_t v = fp2_add(from_i64(gates[i]), from_i64(2048));
+        v = fp2_add(v, fp2_mul(b, from_i64(outputs[i])));
+        v = fp2_add(v, fp2_mul(b2, from_i64((int64_t)act_group(i, f_pad, tokens, hidden, group_ids))));
+        v = fp2_add(v, tg);
+        q[2 * i] = v.c0;
+        q[2 * i + 1] = v.c1;
+    }
+}
+
+/* accuracy_act.rs:13-31 (table): compressed and support, len entries */
+void or_act_table(const int64_t *tables, size_t groups, size_t len, const uint64_t beta[2], const uint64_t tag[2], uint64_t *compressed,
+                  uint64_t *support) {
+    fp2_t b = fp2_new(beta[0], beta[1]), tg = fp2_new(tag[0], tag[1]), b2 = fp2_mul(b, b);
+    fp2_t zero = fp2_add(from_i64(2048), tg);
+    for (size_t i = 0; i < len; i++) {
+        compressed[2 * i] = zero.c0; compressed[2 * i + 1] = zero.c1;
+        support[2 * i] = 0; support[2 * i + 1] = 0;
+    }
+    for (size_t g = 0; g < groups; g++) {
+        fp2_t gt = fp2_mul(b2, from_i64((int64_t)g));
+        for (size_t k = 0; k < 4096; k++) {
+            size_t i = g * 4096 + k;
+            fp2_t v = fp2_add(fp2_add(fp2_add(from_i64((int64_t)k), fp2_mul(b, from_i64(tables[i]))), gt), tg);
+            compressed[2 * i] = v.c0; compressed[2 * i + 1] = v.c1;
+            support[2 * i] = 1;
+        }
+    }
+}
