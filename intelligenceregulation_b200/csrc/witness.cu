@@ -2,12 +2,11 @@
 // dense contraction of the system, exact integers: int16 activations times int8 weights into int64.
 //
 //   k_wp_pack      x (int64, row stride xs) -> two byte planes per 128-token tile: hi = x >> 8 (signed), lo = x & 255
-//                  (unsigned), K padded with zeros to a multiple of 64; an activation outside int16 raises the flag
-//   k_wp_repack    weights the product kernel cannot read in place (in_out layout, or K not a multiple of 64) -> rows of Kp bytes
-//   k_wp_gemm      P[256 x N] += A[256 x K] B[K x N] per 128-token tile, int8 tensor-core products (m16n8k32: signed x signed
-//                  for the hi rows, unsigned x signed for the lo rows), int32 accumulators, split over K with integer atomics
-//                  (integer addition: any order gives the same words)
-//   k_wp_combine   out[t * os + j] = 256 P_hi[t][j] + P_lo[t][j] in int64
+//                  (unsigned), K padded with zeros to a multiple of 128; an activation outside int16 raises the flag
+//   k_wp_repack    weights the product kernel cannot read in place (in_out layout, or K not a multiple of 128) -> rows of Kp bytes
+//   k_wp_umma      out[128 x 256 tile] = 256 (A_hi B) + (A_lo B): tcgen05.mma kind::i8 (signed x signed for the high bytes,
+//                  unsigned x signed for the low bytes), int32 accumulators in TMEM, int64 result written by the epilogue;
+//                  split over K with integer atomics (integer addition: any order gives the same words)
 // |sum lo w| <= K * 255 * 128 < 2^31 for K <= 65,536 (metal.rs:4234 states the same bound), so int32 never wraps.
 #include "api_internal.h"
 
@@ -16,13 +15,6 @@ using namespace hlapi;
 namespace {
 
 constexpr int WP_MT = 128;      // tokens per tile; the stacked tile has 2 * WP_MT rows (hi rows, then lo rows)
-constexpr int WP_NT = 128;      // output columns per CTA
-constexpr int WP_KT = 128;      // K bytes per stage: whole 128-byte lines of every row
-constexpr int WP_LD = WP_KT + 16;  // shared-memory row pitch in bytes: 36 words, so the 8 rows of a fragment fall in distinct banks
-constexpr int WP_STAGES = 3;
-constexpr int WP_THREADS = 512;  // 16 warps: 4 over the stacked rows x 4 over the columns, 64 x 32 outputs each
-constexpr int WP_CTAS_PER_SM = 1;
-constexpr int WP_CH = WP_KT / 16;  // 16-byte chunks per row and stage
 constexpr size_t WP_MAX_K = (size_t)1 << 16;
 
 __global__ void __launch_bounds__(256) k_wp_pack(const long long* __restrict__ x, size_t xs, u32 t_rows, u32 K, u32 Kp,
@@ -72,126 +64,179 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
-// four 8 x 16-byte matrices from shared memory, one row address per lane (lanes 8 i .. 8 i + 7 give matrix i)
-__device__ __forceinline__ void ldmatrix_x4(u32 (&r)[4], const void* smem_row) {
-    const unsigned s = (unsigned)__cvta_generic_to_shared(smem_row);
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
-}
-
 __device__ __forceinline__ void mma_s8s8(int (&c)[4], const u32 (&a)[4], const u32 (&b)[2]) {
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                  : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
-__device__ __forceinline__ void mma_u8s8(int (&c)[4], const u32 (&a)[4], const u32 (&b)[2]) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+// ---------------------------------------------------------------------------------------------------------------
+// The product on the 5th-generation tensor cores: tcgen05.mma kind::i8, operands in shared memory, accumulators in TMEM.
+// One CTA per SM owns a 128-token tile (two 128-row operands: the signed high bytes and the unsigned low bytes) and 256
+// output columns; per K stage of 128 bytes one thread issues 4 x 2 instructions of shape 128 x 256 x 32 (hi: s8 x s8 into
+// TMEM columns 0..255, lo: u8 x s8 into columns 256..511), the epilogue reads both accumulators lane by lane and writes
+// 256 hi + lo as int64 straight into the result plane (integer atomics when K is split).
+// Shared-memory operand layout (K-major, no swizzle): 8-row x 16-byte core matrices of 128 contiguous bytes; the two
+// 16-byte K chunks of one instruction are UM_LBO apart, consecutive 8-row groups UM_SBO apart.
+// Every wait is bounded: a wait that runs out sets the error word, every thread leaves the loop together and TMEM is freed.
+constexpr int UM_NT = 256, UM_KT = 128, UM_STAGES = 3, UM_THREADS = 256;
+constexpr u32 UM_LBO = 128, UM_SBO = 1024;
+constexpr u32 UM_A_BYTES = WP_MT * UM_KT, UM_B_BYTES = UM_NT * UM_KT, UM_STAGE_BYTES = 2 * UM_A_BYTES + UM_B_BYTES;
+constexpr u32 UM_SPIN_LIMIT = 1u << 22;
+
+__device__ __forceinline__ u32 um_off(u32 row, u32 chunk) { return (row >> 3) * UM_SBO + chunk * UM_LBO + (row & 7) * 16; }
+
+__device__ __forceinline__ u64 um_desc(u32 smem_addr) {
+    // start address, leading and stride byte offsets in 16-byte units; descriptor version 1; layout type 0 (no swizzle)
+    return (u64)((smem_addr >> 4) & 0x3FFF) | ((u64)(UM_LBO >> 4) << 16) | ((u64)(UM_SBO >> 4) << 32) | (1ull << 46);
 }
 
-// grid (N tiles, K splits, token tiles); B rows of ldb bytes hold one output column's K weights, readable up to Kp
-__global__ void __launch_bounds__(WP_THREADS, WP_CTAS_PER_SM) k_wp_gemm(const uint8_t* __restrict__ A, const int8_t* __restrict__ B, size_t ldb, u32 N, u32 Kp,
-                                                          u32 Np, int* __restrict__ P /* tiles x 2 WP_MT x Np */) {
+// instruction descriptor of kind::i8: D = s32, B = s8, A = s8 or u8, both K-major, N = 256, M = 128
+__host__ __device__ constexpr u32 um_idesc(bool a_signed) {
+    return (2u << 4) | ((a_signed ? 1u : 0u) << 7) | (1u << 10) | ((u32)(UM_NT >> 3) << 17) | ((u32)(WP_MT >> 4) << 24);
+}
+
+__device__ __forceinline__ void um_mma(u32 tmem_d, u64 a_desc, u64 b_desc, u32 idesc, u32 accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}\n" ::"r"(tmem_d),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void um_commit(u32 mbar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(mbar) : "memory");
+}
+__device__ __forceinline__ bool um_wait(u32 mbar, u32 parity) {
+    for (u32 spin = 0; spin < UM_SPIN_LIMIT; spin++) {
+        u32 ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+                     : "=r"(ok)
+                     : "r"(mbar), "r"(parity)
+                     : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void um_ld32(u32 taddr, u32 (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, "
+        "%23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+
+// grid (N tiles of 256, K splits, token tiles)
+__global__ void __launch_bounds__(UM_THREADS, 1) k_wp_umma(const uint8_t* __restrict__ A, const int8_t* __restrict__ B, size_t ldb, u32 N, u32 Kp,
+                                                          u32 t_rows, size_t os, long long* __restrict__ out, int* __restrict__ err) {
     extern __shared__ __align__(16) uint8_t smem[];
-    uint8_t* As = smem;                                        // stages x 256 x WP_LD
-    uint8_t* Bs = smem + (size_t)WP_STAGES * 2 * WP_MT * WP_LD;  // stages x WP_NT x WP_LD
-    const u32 tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tig = lane & 3;
-    const u32 warp_m = warp & 3, warp_n = warp >> 2;
-    const u32 n0 = blockIdx.x * WP_NT, mt = blockIdx.z;
-    const u32 kt_all = Kp / WP_KT, kt0 = (u32)((u64)kt_all * blockIdx.y / gridDim.y), kt1 = (u32)((u64)kt_all * (blockIdx.y + 1) / gridDim.y);
+    __shared__ __align__(8) u64 bars[UM_STAGES + 1];
+    __shared__ u32 tmem_slot;
+    const u32 tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const u32 n0 = blockIdx.x * UM_NT, mt = blockIdx.z;
+    const u32 kt_all = Kp / UM_KT, kt0 = (u32)((u64)kt_all * blockIdx.y / gridDim.y), kt1 = (u32)((u64)kt_all * (blockIdx.y + 1) / gridDim.y);
+    const u32 nkt = kt1 - kt0;
     const uint8_t* Ag = A + (size_t)mt * 2 * WP_MT * Kp;
+    const u32 smem_base = (u32)__cvta_generic_to_shared(smem);
+    const u32 bar_base = (u32)__cvta_generic_to_shared(bars);
+
+    if (tid == 0) {
+        for (int i = 0; i <= UM_STAGES; i++) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(bar_base + 8 * i));
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::);
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"((u32)__cvta_generic_to_shared(&tmem_slot)), "r"(512u));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::);
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
+    const u32 tmem = tmem_slot;
 
     auto load_stage = [&](u32 kt, u32 st) {
-        const u32 k0 = kt * WP_KT;
-        uint8_t* as = As + (size_t)st * 2 * WP_MT * WP_LD;
-        uint8_t* bs = Bs + (size_t)st * WP_NT * WP_LD;
+        const u32 k0 = kt * UM_KT;
+        uint8_t* sa = smem + (size_t)st * UM_STAGE_BYTES;
+        uint8_t* sb = sa + 2 * UM_A_BYTES;
 #pragma unroll
-        for (int i = 0; i < 2 * WP_MT * WP_CH / WP_THREADS; i++) {
-            const u32 e = tid + i * WP_THREADS, row = e / WP_CH, c = e % WP_CH;
-            cp_async16(as + row * WP_LD + c * 16, Ag + (size_t)row * Kp + k0 + c * 16);
+        for (int i = 0; i < 2 * WP_MT * 8 / UM_THREADS; i++) {  // stacked rows: 0..127 the high bytes, 128..255 the low bytes
+            const u32 e = tid + i * UM_THREADS, row = e >> 3, c = e & 7;
+            cp_async16(sa + (row >> 7) * UM_A_BYTES + um_off(row & 127, c), Ag + (size_t)row * Kp + k0 + c * 16);
         }
 #pragma unroll
-        for (int i = 0; i < WP_NT * WP_CH / WP_THREADS; i++) {
-            const u32 e = tid + i * WP_THREADS, row = e / WP_CH, c = e % WP_CH;
+        for (int i = 0; i < UM_NT * 8 / UM_THREADS; i++) {
+            const u32 e = tid + i * UM_THREADS, row = e >> 3, c = e & 7;
             const u32 n = min(n0 + row, N - 1);  // columns past N repeat the last one; they are never written out
-            cp_async16(bs + row * WP_LD + c * 16, B + (size_t)n * ldb + k0 + c * 16);
+            cp_async16(sb + um_off(row, c), B + (size_t)n * ldb + k0 + c * 16);
         }
     };
 
-    int acc[4][4][4];
 #pragma unroll
-    for (int i = 0; i < 4; i++)
-#pragma unroll
-        for (int j = 0; j < 4; j++)
-#pragma unroll
-            for (int x = 0; x < 4; x++) acc[i][j][x] = 0;
-
-    const u32 nkt = kt1 - kt0;
-#pragma unroll
-    for (int s = 0; s < WP_STAGES - 1; s++) {
+    for (int s = 0; s < UM_STAGES - 1; s++) {
         if ((u32)s < nkt) load_stage(kt0 + s, s);
         cp_async_commit();
     }
+    bool failed = false;
     for (u32 it = 0; it < nkt; it++) {
-        cp_async_wait<WP_STAGES - 2>();
-        __syncthreads();  // stage `it` has landed for every thread, and stage it-1's readers are done
-        if (it + WP_STAGES - 1 < nkt) load_stage(kt0 + it + WP_STAGES - 1, (it + WP_STAGES - 1) % WP_STAGES);
-        cp_async_commit();
-        const uint8_t* as = As + (size_t)(it % WP_STAGES) * 2 * WP_MT * WP_LD + (size_t)(warp_m * 64) * WP_LD;
-        const uint8_t* bs = Bs + (size_t)(it % WP_STAGES) * WP_NT * WP_LD + (size_t)(warp_n * 32) * WP_LD;
+        cp_async_wait<UM_STAGES - 2>();
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // the copies above are generic-proxy writes; the tensor core reads through the async proxy
+        __syncthreads();
+        const u32 st = it % UM_STAGES;
+        if (tid == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
+            const u32 sa = smem_base + st * UM_STAGE_BYTES, sb = sa + 2 * UM_A_BYTES;
 #pragma unroll
-        for (int kk = 0; kk < WP_KT; kk += 32) {
-            // fragments of m16n8k32 with 8-bit operands: A = (rows g / g + 8) x (bytes 4 tig.. / 16 + 4 tig..), B = column g x the same
-            // bytes: exactly the 8 x 16-byte matrices ldmatrix hands out, one instruction per A tile and per pair of B tiles
-            u32 a[4][4], b[4][2];
-#pragma unroll
-            for (int mi = 0; mi < 4; mi++)
-                ldmatrix_x4(a[mi], as + (size_t)(mi * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * WP_LD + kk + (lane >> 4) * 16);
-#pragma unroll
-            for (int np = 0; np < 2; np++) {
-                u32 r[4];
-                ldmatrix_x4(r, bs + (size_t)(np * 16 + (lane & 7) + (lane >> 4) * 8) * WP_LD + kk + ((lane >> 3) & 1) * 16);
-                b[2 * np][0] = r[0]; b[2 * np][1] = r[1]; b[2 * np + 1][0] = r[2]; b[2 * np + 1][1] = r[3];
+            for (u32 kk = 0; kk < UM_KT / 32; kk++) {
+                const u64 bd = um_desc(sb + kk * 2 * UM_LBO);
+                const u32 accumulate = (it | kk) ? 1u : 0u;
+                um_mma(tmem, um_desc(sa + kk * 2 * UM_LBO), bd, um_idesc(true), accumulate);
+                um_mma(tmem + 256, um_desc(sa + UM_A_BYTES + kk * 2 * UM_LBO), bd, um_idesc(false), accumulate);
             }
-            if (warp_m < 2) {  // rows 0..127 of the stacked tile: the signed high bytes
+            um_commit(bar_base + 8 * st);  // arrives when the instructions above have read this stage
+        }
+        // the stage the next copies overwrite was read by the instructions issued one iteration ago
+        bool ok = true;
+        if (it >= 1 && it + UM_STAGES - 1 < nkt) ok = um_wait(bar_base + 8 * ((it - 1) % UM_STAGES), ((it - 1) / UM_STAGES) & 1);
+        failed = __syncthreads_or(!ok);
+        if (failed) break;
+        if (it + UM_STAGES - 1 < nkt) load_stage(kt0 + it + UM_STAGES - 1, (it + UM_STAGES - 1) % UM_STAGES);
+        cp_async_commit();
+    }
+    cp_async_wait<0>();
+    if (!failed) {
+        if (tid == 0) um_commit(bar_base + 8 * UM_STAGES);  // arrives when every instruction of this CTA has completed
+        const bool ok = um_wait(bar_base + 8 * UM_STAGES, 0);
+        failed = __syncthreads_or(!ok);
+    }
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
+    if (!failed && nkt) {
+        // warp w reads TMEM lanes 32 (w % 4) .. +31 (the rows of the token tile), columns 128 (w / 4) .. +127
+        const u32 q = warp & 3, half = warp >> 2;
+        const u32 row = q * 32 + lane, t = mt * WP_MT + row;
+        const bool split = gridDim.y > 1;
+#pragma unroll 1
+        for (u32 cc = 0; cc < 4; cc++) {
+            const u32 col = half * 128 + cc * 32;
+            u32 hi[32], lo[32];
+            um_ld32(tmem + ((q * 32) << 16) + col, hi);
+            um_ld32(tmem + ((q * 32) << 16) + 256 + col, lo);
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+            if (t < t_rows) {
+                long long* o = out + (size_t)t * os + n0 + col;
 #pragma unroll
-                for (int mi = 0; mi < 4; mi++)
-#pragma unroll
-                    for (int ni = 0; ni < 4; ni++) mma_s8s8(acc[mi][ni], a[mi], b[ni]);
-            } else {            // rows 128..255: the unsigned low bytes
-#pragma unroll
-                for (int mi = 0; mi < 4; mi++)
-#pragma unroll
-                    for (int ni = 0; ni < 4; ni++) mma_u8s8(acc[mi][ni], a[mi], b[ni]);
+                for (int j = 0; j < 32; j++) {
+                    if (n0 + col + j < N) {
+                        const long long v = 256ll * (int)hi[j] + (int)lo[j];
+                        if (split) atomicAdd(reinterpret_cast<unsigned long long*>(o + j), (unsigned long long)v);
+                        else o[j] = v;
+                    }
+                }
             }
         }
     }
-    cp_async_wait<0>();
-    int* Pt = P + (size_t)mt * 2 * WP_MT * Np;
-    const bool split = gridDim.y > 1;
-#pragma unroll
-    for (int mi = 0; mi < 4; mi++)
-#pragma unroll
-        for (int ni = 0; ni < 4; ni++) {
-            const u32 row = warp_m * 64 + mi * 16 + g, col = n0 + warp_n * 32 + ni * 8 + tig * 2;
-            int* p0 = Pt + (size_t)row * Np + col;
-            int* p1 = p0 + (size_t)8 * Np;
-            if (split) {
-                atomicAdd(p0, acc[mi][ni][0]); atomicAdd(p0 + 1, acc[mi][ni][1]);
-                atomicAdd(p1, acc[mi][ni][2]); atomicAdd(p1 + 1, acc[mi][ni][3]);
-            } else {
-                *reinterpret_cast<int2*>(p0) = make_int2(acc[mi][ni][0], acc[mi][ni][1]);
-                *reinterpret_cast<int2*>(p1) = make_int2(acc[mi][ni][2], acc[mi][ni][3]);
-            }
-        }
-}
-
-__global__ void __launch_bounds__(256) k_wp_combine(const int* __restrict__ P, u32 Np, u32 N, u32 t_rows, size_t os, long long* __restrict__ out) {
-    const u32 t = blockIdx.y, mt = t / WP_MT, r = t % WP_MT;
-    const int* hi = P + ((size_t)mt * 2 * WP_MT + r) * Np;
-    const int* lo = hi + (size_t)WP_MT * Np;
-    for (u32 j = blockIdx.x * blockDim.x + threadIdx.x; j < N; j += gridDim.x * blockDim.x)
-        out[(size_t)t * os + j] = 256ll * hi[j] + lo[j];
+    if (failed && tid == 0) atomicExch(err, 2);
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::);
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512u));
 }
 
 // Register-resident int8 tensor-core products: the ceiling of the m16n8k32 instruction the product kernel issues (16
@@ -232,27 +277,24 @@ __global__ void __launch_bounds__(256, 2) k_mma_i8_peak(u32 iters, int* __restri
 // everything on the context's stream; d_* are device pointers; *flag_out is read after one synchronisation
 int product_on_device(hl_ctx* c, size_t t_rows, const int64_t* d_x, size_t xs, const int8_t* d_w, size_t K, size_t N, size_t os, size_t out_len,
                       int in_out, int64_t* d_out, int* taken) {
-    const u32 Kp = (u32)((K + WP_KT - 1) / WP_KT * WP_KT), Np = (u32)((N + WP_NT - 1) / WP_NT * WP_NT);
+    const u32 Kp = (u32)((K + UM_KT - 1) / UM_KT * UM_KT);
     const u32 tiles = (u32)((t_rows + WP_MT - 1) / WP_MT);
-    const bool in_place = !in_out && K % WP_KT == 0 && ((uintptr_t)d_w & 15) == 0;
-    const size_t a_bytes = (size_t)tiles * 2 * WP_MT * Kp, p_bytes = (size_t)tiles * 2 * WP_MT * Np * 4, b_bytes = in_place ? 0 : (size_t)N * Kp;
+    const bool in_place = !in_out && K % UM_KT == 0 && ((uintptr_t)d_w & 15) == 0;
+    const size_t a_bytes = (size_t)tiles * 2 * WP_MT * Kp, b_bytes = in_place ? 0 : (size_t)N * Kp;
     uint8_t* d_a = nullptr;
     int8_t* d_b = nullptr;
-    int *d_p = nullptr, *d_flag = nullptr;
+    int* d_flag = nullptr;
     int rc = dev_alloc(c, (void**)&d_a, a_bytes);
-    if (!rc) rc = dev_alloc(c, (void**)&d_p, p_bytes);
     if (!rc) rc = dev_alloc(c, (void**)&d_flag, 4);
     if (!rc && b_bytes) rc = dev_alloc(c, (void**)&d_b, b_bytes);
-    // the split over K: enough CTAs for two per SM, each with at least four K stages
-    const u32 n_tiles = Np / WP_NT, kt_all = Kp / WP_KT;
-    // every CTA does the same work, so what counts is how full the last wave of resident CTAs is: the smallest split that
-    // fills the waves best, each split keeping at least two K stages
-    const u32 slots = (u32)WP_CTAS_PER_SM * (u32)c->sm_count, base = n_tiles * tiles;
+    // every CTA does the same work, so what counts is how full the last wave of one CTA per SM is: the smallest split over K
+    // that fills the waves best; each further split adds a pass of integer atomics over the plane, charged at 3 %
+    const u32 n_tiles = (u32)((N + UM_NT - 1) / UM_NT), kt_all = Kp / UM_KT;
+    const u32 slots = (u32)c->sm_count, base = n_tiles * tiles;
     u32 splits = 1;
     double best = 0.0;
-    for (u32 sp = 1; sp <= 32 && sp <= (kt_all / 2 ? kt_all / 2 : 1); sp++) {
+    for (u32 sp = 1; sp <= 32 && sp <= kt_all; sp++) {
         const u64 ctas = (u64)base * sp;
-        // each further split adds one pass of integer atomics over the 256 x N plane: charged at 3 % of a product's time
         const double eff = (double)ctas / (double)((ctas + slots - 1) / slots * slots) / (1.0 + 0.03 * (sp - 1));
         if (eff > best + 0.02) { best = eff; splits = sp; }
     }
@@ -261,7 +303,6 @@ int product_on_device(hl_ctx* c, size_t t_rows, const int64_t* d_x, size_t xs, c
         Timed t(c, HL_T_WITNESS);
         cudaError_t e = cudaMemsetAsync(d_flag, 0, 4, c->stream);
         if (e == cudaSuccess) e = cudaMemsetAsync(d_out, 0, out_len * 8, c->stream);
-        if (e == cudaSuccess && splits > 1) e = cudaMemsetAsync(d_p, 0, p_bytes, c->stream);
         if (e == cudaSuccess && b_bytes) e = cudaMemsetAsync(d_b, 0, b_bytes, c->stream);
         if (e == cudaSuccess) {
             k_wp_pack<<<dim3((Kp + 1023) / 1024, tiles * WP_MT), 256, 0, c->stream>>>((const long long*)d_x, xs, (u32)t_rows, (u32)K, Kp, d_a, d_flag);
@@ -269,19 +310,15 @@ int product_on_device(hl_ctx* c, size_t t_rows, const int64_t* d_x, size_t xs, c
             c->stats.kernel_launches++;
         }
         if (e == cudaSuccess && b_bytes) {
-            k_wp_repack<<<dim3(Kp / 64, Np / 64), 256, 0, c->stream>>>(d_w, (u32)K, (u32)N, Kp, in_out, d_b);
+            k_wp_repack<<<dim3(Kp / 64, (unsigned)((N + 63) / 64)), 256, 0, c->stream>>>(d_w, (u32)K, (u32)N, Kp, in_out, d_b);
             e = cudaGetLastError();
             c->stats.kernel_launches++;
         }
-        const size_t smem = (size_t)WP_STAGES * (2 * WP_MT + WP_NT) * WP_LD;
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(k_wp_gemm, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        const size_t smem = (size_t)UM_STAGES * UM_STAGE_BYTES;
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(k_wp_umma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e == cudaSuccess) {
-            k_wp_gemm<<<dim3(n_tiles, splits, tiles), WP_THREADS, smem, c->stream>>>(d_a, in_place ? d_w : d_b, in_place ? K : (size_t)Kp, (u32)N, Kp, Np, d_p);
-            e = cudaGetLastError();
-            c->stats.kernel_launches++;
-        }
-        if (e == cudaSuccess) {
-            k_wp_combine<<<dim3((unsigned)((N + 1023) / 1024), (unsigned)t_rows), 256, 0, c->stream>>>(d_p, Np, (u32)N, (u32)t_rows, os, (long long*)d_out);
+            k_wp_umma<<<dim3(n_tiles, splits, tiles), UM_THREADS, smem, c->stream>>>(d_a, in_place ? d_w : d_b, in_place ? K : (size_t)Kp, (u32)N, Kp,
+                                                                                   (u32)t_rows, os, (long long*)d_out, d_flag);
             e = cudaGetLastError();
             c->stats.kernel_launches++;
         }
@@ -291,9 +328,9 @@ int product_on_device(hl_ctx* c, size_t t_rows, const int64_t* d_x, size_t xs, c
     if (!rc) rc = sync(c, "witness_product");
     else cudaStreamSynchronize(c->stream);
     if (d_a) dev_free(c, d_a, a_bytes);
-    if (d_p) dev_free(c, d_p, p_bytes);
     if (d_flag) dev_free(c, d_flag, 4);
     if (d_b) dev_free(c, d_b, b_bytes);
+    if (!rc && flag == 2) rc = fail(c, HL_B200_ERR_TIMEOUT, "witness product: a bounded wait on the tensor-core pipeline ran out");
     if (!rc) *taken = flag ? 0 : 1;
     return rc;
 }
