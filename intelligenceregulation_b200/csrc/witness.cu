@@ -8,6 +8,8 @@
 //                  unsigned x signed for the low bytes), int32 accumulators in TMEM, int64 result written by the epilogue;
 //                  split over K with integer atomics (integer addition: any order gives the same words)
 // |sum lo w| <= K * 255 * 128 < 2^31 for K <= 65,536 (metal.rs:4234 states the same bound), so int32 never wraps.
+#include <cstdlib>
+
 #include "api_internal.h"
 
 using namespace hlapi;
@@ -297,6 +299,11 @@ int product_on_device(hl_ctx* c, size_t t_rows, const int64_t* d_x, size_t xs, c
         const u64 ctas = (u64)base * sp;
         const double eff = (double)ctas / (double)((ctas + slots - 1) / slots * slots) / (1.0 + 0.03 * (sp - 1));
         if (eff > best + 0.02) { best = eff; splits = sp; }
+    }
+    // HL_B200_WP_SPLITS=<n>: a tuning override of the split (the result does not depend on it)
+    if (const char* ov = getenv("HL_B200_WP_SPLITS")) {
+        const long v = atol(ov);
+        if (v >= 1 && v <= (long)kt_all && v <= 65535) splits = (u32)v;
     }
     int flag = 0;
     if (!rc) {
