@@ -8,6 +8,8 @@
 //                  unsigned x signed for the low bytes), int32 accumulators in TMEM, int64 result written by the epilogue;
 //                  split over K with integer atomics (integer addition: any order gives the same words)
 // |sum lo w| <= K * 255 * 128 < 2^31 for K <= 65,536 (metal.rs:4234 states the same bound), so int32 never wraps.
+#include <cuda.h>
+
 #include <cstdlib>
 
 #include "api_internal.h"
@@ -58,38 +60,30 @@ __global__ void __launch_bounds__(256) k_wp_repack(const int8_t* __restrict__ sr
     }
 }
 
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
-    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
-
 __device__ __forceinline__ void mma_s8s8(int (&c)[4], const u32 (&a)[4], const u32 (&b)[2]) {
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                  : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 // ---------------------------------------------------------------------------------------------------------------
-// The product on the 5th-generation tensor cores: tcgen05.mma kind::i8, operands in shared memory, accumulators in TMEM.
+// The product on the 5th-generation tensor cores: TMA tiles into shared memory, tcgen05.mma kind::i8, accumulators in TMEM.
 // One CTA per SM owns a 128-token tile (two 128-row operands: the signed high bytes and the unsigned low bytes) and 256
-// output columns; per K stage of 128 bytes one thread issues 4 x 2 instructions of shape 128 x 256 x 32 (hi: s8 x s8 into
-// TMEM columns 0..255, lo: u8 x s8 into columns 256..511), the epilogue reads both accumulators lane by lane and writes
-// 256 hi + lo as int64 straight into the result plane (integer atomics when K is split).
-// Shared-memory operand layout (K-major, no swizzle): 8-row x 16-byte core matrices of 128 contiguous bytes; the two
-// 16-byte K chunks of one instruction are UM_LBO apart, consecutive 8-row groups UM_SBO apart.
-// Every wait is bounded: a wait that runs out sets the error word, every thread leaves the loop together and TMEM is freed.
+// output columns.  Per K stage of 128 bytes one thread asks the TMA unit for two boxes (256 stacked activation rows and 256
+// weight rows of 128 bytes, 128-byte swizzle) and, when they have landed, issues 4 x 2 instructions of shape 128 x 256 x 32
+// (hi: s8 x s8 into TMEM columns 0..255, lo: u8 x s8 into columns 256..511); the epilogue reads both accumulators lane by
+// lane and writes 256 hi + lo as int64 straight into the result plane (integer atomics when K is split).
+// Shared-memory operands are K-major with the 128-byte swizzle the TMA unit writes: rows of 128 bytes, 8-row groups
+// UM_SBO apart, a K step of 32 bytes is 32 bytes further along the row.
+// Every wait is bounded: a wait that runs out sets the error word, every thread leaves together and TMEM is freed.
 constexpr int UM_NT = 256, UM_KT = 128, UM_STAGES = 3, UM_THREADS = 256;
-constexpr u32 UM_LBO = 128, UM_SBO = 1024;
+constexpr u32 UM_SBO = 1024;
 constexpr u32 UM_A_BYTES = WP_MT * UM_KT, UM_B_BYTES = UM_NT * UM_KT, UM_STAGE_BYTES = 2 * UM_A_BYTES + UM_B_BYTES;
 constexpr u32 UM_SPIN_LIMIT = 1u << 22;
 
-__device__ __forceinline__ u32 um_off(u32 row, u32 chunk) { return (row >> 3) * UM_SBO + chunk * UM_LBO + (row & 7) * 16; }
-
 __device__ __forceinline__ u64 um_desc(u32 smem_addr) {
-    // start address, leading and stride byte offsets in 16-byte units; descriptor version 1; layout type 0 (no swizzle)
-    return (u64)((smem_addr >> 4) & 0x3FFF) | ((u64)(UM_LBO >> 4) << 16) | ((u64)(UM_SBO >> 4) << 32) | (1ull << 46);
+    // start address and stride byte offset in 16-byte units (the leading offset is not used by a swizzled K-major operand and is
+    // set to 1 as the canonical form has it); descriptor version 1; layout type 2 = 128-byte swizzle
+    return (u64)((smem_addr >> 4) & 0x3FFF) | (1ull << 16) | ((u64)(UM_SBO >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
 
 // instruction descriptor of kind::i8: D = s32, B = s8, A = s8 or u8, both K-major, N = 256, M = 128
@@ -118,6 +112,12 @@ __device__ __forceinline__ bool um_wait(u32 mbar, u32 parity) {
     }
     return false;
 }
+// one box of the tensor map into shared memory; its bytes are counted on the mbarrier
+__device__ __forceinline__ void um_tma_2d(u32 smem_dst, const CUtensorMap* map, u32 mbar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::"r"(smem_dst),
+                 "l"((u64)map), "r"(mbar), "r"(x), "r"(y)
+                 : "memory");
+}
 __device__ __forceinline__ void um_ld32(u32 taddr, u32 (&r)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, "
@@ -128,22 +128,26 @@ __device__ __forceinline__ void um_ld32(u32 taddr, u32 (&r)[32]) {
         : "r"(taddr));
 }
 
-// grid (N tiles of 256, K splits, token tiles)
-__global__ void __launch_bounds__(UM_THREADS, 1) k_wp_umma(const uint8_t* __restrict__ A, const int8_t* __restrict__ B, size_t ldb, u32 N, u32 Kp,
-                                                          u32 t_rows, size_t os, long long* __restrict__ out, int* __restrict__ err) {
-    extern __shared__ __align__(16) uint8_t smem[];
-    __shared__ __align__(8) u64 bars[UM_STAGES + 1];
+// grid (N tiles of 256, K splits, token tiles).  map_a: the packed activations, (tiles * 256) rows of Kp bytes; map_b: the weights,
+// N rows of K bytes (rows past N read as zero).  Barriers: full[s] (the stage's two boxes have landed), empty[s] (the instructions
+// that read the stage have completed), done.
+__global__ void __launch_bounds__(UM_THREADS, 1) k_wp_umma(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, u32 N,
+                                                          u32 Kp, u32 t_rows, size_t os, long long* __restrict__ out, int* __restrict__ err) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    __shared__ __align__(8) u64 bars[2 * UM_STAGES + 1];
     __shared__ u32 tmem_slot;
+    __shared__ volatile u32 gave_up;  // set by the issuing thread when one of its waits ran out
     const u32 tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const u32 n0 = blockIdx.x * UM_NT, mt = blockIdx.z;
     const u32 kt_all = Kp / UM_KT, kt0 = (u32)((u64)kt_all * blockIdx.y / gridDim.y), kt1 = (u32)((u64)kt_all * (blockIdx.y + 1) / gridDim.y);
     const u32 nkt = kt1 - kt0;
-    const uint8_t* Ag = A + (size_t)mt * 2 * WP_MT * Kp;
-    const u32 smem_base = (u32)__cvta_generic_to_shared(smem);
+    const u32 smem_base = ((u32)__cvta_generic_to_shared(smem_raw) + 1023u) & ~1023u;  // the swizzle pattern repeats every 1024 bytes
     const u32 bar_base = (u32)__cvta_generic_to_shared(bars);
+    const u32 full0 = bar_base, empty0 = bar_base + 8 * UM_STAGES, done = bar_base + 16 * UM_STAGES;
 
     if (tid == 0) {
-        for (int i = 0; i <= UM_STAGES; i++) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(bar_base + 8 * i));
+        gave_up = 0;
+        for (int i = 0; i <= 2 * UM_STAGES; i++) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(bar_base + 8 * i));
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::);
     }
     if (warp == 0) {
@@ -155,62 +159,54 @@ __global__ void __launch_bounds__(UM_THREADS, 1) k_wp_umma(const uint8_t* __rest
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
     const u32 tmem = tmem_slot;
 
-    auto load_stage = [&](u32 kt, u32 st) {
-        const u32 k0 = kt * UM_KT;
-        uint8_t* sa = smem + (size_t)st * UM_STAGE_BYTES;
-        uint8_t* sb = sa + 2 * UM_A_BYTES;
-#pragma unroll
-        for (int i = 0; i < 2 * WP_MT * 8 / UM_THREADS; i++) {  // stacked rows: 0..127 the high bytes, 128..255 the low bytes
-            const u32 e = tid + i * UM_THREADS, row = e >> 3, c = e & 7;
-            cp_async16(sa + (row >> 7) * UM_A_BYTES + um_off(row & 127, c), Ag + (size_t)row * Kp + k0 + c * 16);
-        }
-#pragma unroll
-        for (int i = 0; i < UM_NT * 8 / UM_THREADS; i++) {
-            const u32 e = tid + i * UM_THREADS, row = e >> 3, c = e & 7;
-            const u32 n = min(n0 + row, N - 1);  // columns past N repeat the last one; they are never written out
-            cp_async16(sb + um_off(row, c), B + (size_t)n * ldb + k0 + c * 16);
-        }
-    };
-
-#pragma unroll
-    for (int s = 0; s < UM_STAGES - 1; s++) {
-        if ((u32)s < nkt) load_stage(kt0 + s, s);
-        cp_async_commit();
-    }
-    bool failed = false;
-    for (u32 it = 0; it < nkt; it++) {
-        cp_async_wait<UM_STAGES - 2>();
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // the copies above are generic-proxy writes; the tensor core reads through the async proxy
-        __syncthreads();
-        const u32 st = it % UM_STAGES;
-        if (tid == 0) {
+    bool ok = true;
+    if (tid == 0) {
+        auto load_stage = [&](u32 kt, u32 st) {
+            const u32 sa = smem_base + st * UM_STAGE_BYTES;
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(full0 + 8 * st), "r"(UM_STAGE_BYTES) : "memory");
+            um_tma_2d(sa, &map_a, full0 + 8 * st, (int)(kt * UM_KT), (int)(mt * 2 * WP_MT));
+            um_tma_2d(sa + 2 * UM_A_BYTES, &map_b, full0 + 8 * st, (int)(kt * UM_KT), (int)n0);
+        };
+        for (u32 s = 0; s < UM_STAGES && s < nkt; s++) load_stage(kt0 + s, s);
+        for (u32 it = 0; it < nkt && ok; it++) {
+            const u32 st = it % UM_STAGES;
+            ok = um_wait(full0 + 8 * st, (it / UM_STAGES) & 1);
+            if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
             const u32 sa = smem_base + st * UM_STAGE_BYTES, sb = sa + 2 * UM_A_BYTES;
 #pragma unroll
             for (u32 kk = 0; kk < UM_KT / 32; kk++) {
-                const u64 bd = um_desc(sb + kk * 2 * UM_LBO);
+                const u64 bd = um_desc(sb + kk * 32);
                 const u32 accumulate = (it | kk) ? 1u : 0u;
-                um_mma(tmem, um_desc(sa + kk * 2 * UM_LBO), bd, um_idesc(true), accumulate);
-                um_mma(tmem + 256, um_desc(sa + UM_A_BYTES + kk * 2 * UM_LBO), bd, um_idesc(false), accumulate);
+                um_mma(tmem, um_desc(sa + kk * 32), bd, um_idesc(true), accumulate);
+                um_mma(tmem + 256, um_desc(sa + UM_A_BYTES + kk * 32), bd, um_idesc(false), accumulate);
             }
-            um_commit(bar_base + 8 * st);  // arrives when the instructions above have read this stage
+            um_commit(empty0 + 8 * st);  // arrives when the instructions above have read this stage
+            // refill the stage read one iteration ago, once its instructions have completed
+            if (it >= 1 && it - 1 + UM_STAGES < nkt) {
+                ok = um_wait(empty0 + 8 * ((it - 1) % UM_STAGES), ((it - 1) / UM_STAGES) & 1);
+                if (ok) load_stage(kt0 + it - 1 + UM_STAGES, (it - 1) % UM_STAGES);
+            }
         }
-        // the stage the next copies overwrite was read by the instructions issued one iteration ago
-        bool ok = true;
-        if (it >= 1 && it + UM_STAGES - 1 < nkt) ok = um_wait(bar_base + 8 * ((it - 1) % UM_STAGES), ((it - 1) / UM_STAGES) & 1);
-        failed = __syncthreads_or(!ok);
-        if (failed) break;
-        if (it + UM_STAGES - 1 < nkt) load_stage(kt0 + it + UM_STAGES - 1, (it + UM_STAGES - 1) % UM_STAGES);
-        cp_async_commit();
+        if (ok) um_commit(done);  // arrives when every instruction of this CTA has completed
+        else gave_up = 1;
     }
-    cp_async_wait<0>();
-    if (!failed) {
-        if (tid == 0) um_commit(bar_base + 8 * UM_STAGES);  // arrives when every instruction of this CTA has completed
-        const bool ok = um_wait(bar_base + 8 * UM_STAGES, 0);
-        failed = __syncthreads_or(!ok);
+    // everyone waits for the accumulators, in slices so that a wait the issuing thread gave up on ends the others' too
+    bool ready = false;
+    for (u32 round = 0; round < 1024 && !ready && !gave_up; round++) {
+        for (u32 spin = 0; spin < (UM_SPIN_LIMIT >> 10) && !ready; spin++) {
+            u32 p;
+            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+                         : "=r"(p)
+                         : "r"(done), "r"(0u)
+                         : "memory");
+            ready = p != 0;
+            if (!ready) __nanosleep(128);  // the polling threads stay off the shared memory the tensor core is reading
+        }
     }
+    const bool failed = __syncthreads_or(!ready);
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::);
-    if (!failed && nkt) {
+    if (!failed) {
         // warp w reads TMEM lanes 32 (w % 4) .. +31 (the rows of the token tile), columns 128 (w / 4) .. +127
         const u32 q = warp & 3, half = warp >> 2;
         const u32 row = q * 32 + lane, t = mt * WP_MT + row;
@@ -277,18 +273,44 @@ __global__ void __launch_bounds__(256, 2) k_mma_i8_peak(u32 iters, int* __restri
 }
 
 // everything on the context's stream; d_* are device pointers; *flag_out is read after one synchronisation
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// a byte matrix of `rows` rows of `inner` readable bytes, `pitch` bytes apart (a multiple of 16), read in boxes of 128 bytes x 256 rows
+// with the 128-byte swizzle; rows and bytes outside the matrix read as zero
+int byte_matrix_map(hl_ctx* c, const void* base, size_t inner, size_t rows, size_t pitch, CUtensorMap* map) {
+    static EncodeTiledFn encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn)
+            return fail(c, HL_B200_ERR_DEVICE, "witness product: the driver has no tensor-map encoder");
+        encode = (EncodeTiledFn)fn;
+    }
+    const cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)rows}, strides[1] = {(cuuint64_t)pitch};
+    const cuuint32_t box[2] = {(cuuint32_t)UM_KT, 256u}, elem[2] = {1u, 1u};
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? HL_B200_OK : fail(c, HL_B200_ERR_DEVICE, "witness product: tensor-map encoding refused");
+}
+
 int product_on_device(hl_ctx* c, size_t t_rows, const int64_t* d_x, size_t xs, const int8_t* d_w, size_t K, size_t N, size_t os, size_t out_len,
                       int in_out, int64_t* d_out, int* taken) {
     const u32 Kp = (u32)((K + UM_KT - 1) / UM_KT * UM_KT);
     const u32 tiles = (u32)((t_rows + WP_MT - 1) / WP_MT);
-    const bool in_place = !in_out && K % UM_KT == 0 && ((uintptr_t)d_w & 15) == 0;
-    const size_t a_bytes = (size_t)tiles * 2 * WP_MT * Kp, b_bytes = in_place ? 0 : (size_t)N * Kp;
+    // weights are read in place when their rows are whole K stages and there is at least one box of rows; else from a padded copy
+    const bool in_place = !in_out && K % UM_KT == 0 && ((uintptr_t)d_w & 15) == 0 && N >= (size_t)UM_NT;
+    const size_t n_pad = (N + UM_NT - 1) / UM_NT * UM_NT;
+    const size_t a_bytes = (size_t)tiles * 2 * WP_MT * Kp, b_bytes = in_place ? 0 : n_pad * Kp;
     uint8_t* d_a = nullptr;
     int8_t* d_b = nullptr;
     int* d_flag = nullptr;
     int rc = dev_alloc(c, (void**)&d_a, a_bytes);
     if (!rc) rc = dev_alloc(c, (void**)&d_flag, 4);
     if (!rc && b_bytes) rc = dev_alloc(c, (void**)&d_b, b_bytes);
+    CUtensorMap map_a, map_b;
+    if (!rc) rc = byte_matrix_map(c, d_a, Kp, (size_t)tiles * 2 * WP_MT, Kp, &map_a);
+    if (!rc) rc = byte_matrix_map(c, in_place ? (const void*)d_w : (const void*)d_b, Kp, in_place ? N : n_pad, Kp, &map_b);
     // every CTA does the same work, so what counts is how full the last wave of one CTA per SM is: the smallest split over K
     // that fills the waves best; each further split adds a pass of integer atomics over the plane, charged at 3 %
     const u32 n_tiles = (u32)((N + UM_NT - 1) / UM_NT), kt_all = Kp / UM_KT;
@@ -321,11 +343,10 @@ int product_on_device(hl_ctx* c, size_t t_rows, const int64_t* d_x, size_t xs, c
             e = cudaGetLastError();
             c->stats.kernel_launches++;
         }
-        const size_t smem = (size_t)UM_STAGES * UM_STAGE_BYTES;
+        const size_t smem = (size_t)UM_STAGES * UM_STAGE_BYTES + 1024;
         if (e == cudaSuccess) e = cudaFuncSetAttribute(k_wp_umma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e == cudaSuccess) {
-            k_wp_umma<<<dim3(n_tiles, splits, tiles), UM_THREADS, smem, c->stream>>>(d_a, in_place ? d_w : d_b, in_place ? K : (size_t)Kp, (u32)N, Kp,
-                                                                                   (u32)t_rows, os, (long long*)d_out, d_flag);
+            k_wp_umma<<<dim3(n_tiles, splits, tiles), UM_THREADS, smem, c->stream>>>(map_a, map_b, (u32)N, Kp, (u32)t_rows, os, (long long*)d_out, d_flag);
             e = cudaGetLastError();
             c->stats.kernel_launches++;
         }
