@@ -181,6 +181,7 @@ void hl_b200_shutdown(hl_ctx* c) {
     cudaSetDevice(c->device);
     cudaStreamSynchronize(c->stream);
     for (auto& kv : c->tw) cudaFree(kv.second);
+    if (c->d_wp_flag) cudaFree(c->d_wp_flag);
     for (auto& s : c->spans) { cudaEventDestroy(s.a); cudaEventDestroy(s.b); }
     for (auto e : c->ev_pool) cudaEventDestroy(e);
     for (auto e : c->ev_chunks) cudaEventDestroy(e);

@@ -28,6 +28,8 @@ struct hl_ctx {
     std::vector<Span> spans;          // recorded, not yet read
     std::vector<cudaEvent_t> ev_pool;  // events ready for reuse
     hl_timing timing_acc{};
+    int* d_wp_flag = nullptr;  // the witness products' status word: zero between calls
+    bool wp_attr = false;      // the product kernel's shared-memory size has been raised on this device
     size_t alloc_live = 0;   // bytes handed out and not yet returned
     size_t alloc_cap = 0;    // 0 = none; a host-side failure-injection cap (mod.rs:121 set_alloc_cap_for_test)
 };

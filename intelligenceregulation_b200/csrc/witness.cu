@@ -304,23 +304,30 @@ int product_on_device(hl_ctx* c, size_t t_rows, const int64_t* d_x, size_t xs, c
     const size_t a_bytes = (size_t)tiles * 2 * WP_MT * Kp, b_bytes = in_place ? 0 : n_pad * Kp;
     uint8_t* d_a = nullptr;
     int8_t* d_b = nullptr;
-    int* d_flag = nullptr;
     int rc = dev_alloc(c, (void**)&d_a, a_bytes);
-    if (!rc) rc = dev_alloc(c, (void**)&d_flag, 4);
+    if (!rc && !c->d_wp_flag) {  // the status word lives with the context and is zero between calls: no clear on the launch path
+        if (cudaMalloc((void**)&c->d_wp_flag, 4) != cudaSuccess || cudaMemsetAsync(c->d_wp_flag, 0, 4, c->stream) != cudaSuccess) {
+            c->d_wp_flag = nullptr;
+            rc = fail(c, HL_B200_ERR_OOM, "witness product: status word");
+        }
+    }
+    int* d_flag = c->d_wp_flag;
     if (!rc && b_bytes) rc = dev_alloc(c, (void**)&d_b, b_bytes);
     CUtensorMap map_a, map_b;
     if (!rc) rc = byte_matrix_map(c, d_a, Kp, (size_t)tiles * 2 * WP_MT, Kp, &map_a);
     if (!rc) rc = byte_matrix_map(c, in_place ? (const void*)d_w : (const void*)d_b, Kp, in_place ? N : n_pad, Kp, &map_b);
-    // every CTA does the same work, so what counts is how full the last wave of one CTA per SM is: the smallest split over K
-    // that fills the waves best; each further split adds a pass of integer atomics over the plane, charged at 3 %
+    // The split over K by a cost model fitted to measurements on B200: a CTA streams one K stage (64 KB of operands) in about
+    // 1.3 us, CTAs run in waves of one per SM, and every split beyond the first adds a pass of 64-bit integer atomics over the
+    // result plane at about 195 G atomics per second.
     const u32 n_tiles = (u32)((N + UM_NT - 1) / UM_NT), kt_all = Kp / UM_KT;
     const u32 slots = (u32)c->sm_count, base = n_tiles * tiles;
     u32 splits = 1;
-    double best = 0.0;
-    for (u32 sp = 1; sp <= 32 && sp <= kt_all; sp++) {
+    double best = 1e30;
+    for (u32 sp = 1; sp <= 64 && sp <= kt_all; sp++) {
         const u64 ctas = (u64)base * sp;
-        const double eff = (double)ctas / (double)((ctas + slots - 1) / slots * slots) / (1.0 + 0.03 * (sp - 1));
-        if (eff > best + 0.02) { best = eff; splits = sp; }
+        const double waves = (double)((ctas + slots - 1) / slots), stages = (double)((kt_all + sp - 1) / sp);
+        const double cost = waves * stages * 1.3e-6 + (sp > 1 ? (double)sp * (double)tiles * WP_MT * (double)N / 195e9 : 0.0);
+        if (cost < best * 0.98) { best = cost; splits = sp; }
     }
     // HL_B200_WP_SPLITS=<n>: a tuning override of the split (the result does not depend on it)
     if (const char* ov = getenv("HL_B200_WP_SPLITS")) {
@@ -330,8 +337,9 @@ int product_on_device(hl_ctx* c, size_t t_rows, const int64_t* d_x, size_t xs, c
     int flag = 0;
     if (!rc) {
         Timed t(c, HL_T_WITNESS);
-        cudaError_t e = cudaMemsetAsync(d_flag, 0, 4, c->stream);
-        if (e == cudaSuccess) e = cudaMemsetAsync(d_out, 0, out_len * 8, c->stream);
+        // the plane is cleared unless the product kernel writes every word of it exactly once
+        const bool dense = splits == 1 && os == N && out_len == t_rows * N;
+        cudaError_t e = dense ? cudaSuccess : cudaMemsetAsync(d_out, 0, out_len * 8, c->stream);
         if (e == cudaSuccess && b_bytes) e = cudaMemsetAsync(d_b, 0, b_bytes, c->stream);
         if (e == cudaSuccess) {
             k_wp_pack<<<dim3((Kp + 1023) / 1024, tiles * WP_MT), 256, 0, c->stream>>>((const long long*)d_x, xs, (u32)t_rows, (u32)K, Kp, d_a, d_flag);
@@ -344,7 +352,10 @@ int product_on_device(hl_ctx* c, size_t t_rows, const int64_t* d_x, size_t xs, c
             c->stats.kernel_launches++;
         }
         const size_t smem = (size_t)UM_STAGES * UM_STAGE_BYTES + 1024;
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(k_wp_umma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess && !c->wp_attr) {
+            e = cudaFuncSetAttribute(k_wp_umma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            c->wp_attr = e == cudaSuccess;
+        }
         if (e == cudaSuccess) {
             k_wp_umma<<<dim3(n_tiles, splits, tiles), UM_THREADS, smem, c->stream>>>(map_a, map_b, (u32)N, Kp, (u32)t_rows, os, (long long*)d_out, d_flag);
             e = cudaGetLastError();
@@ -355,8 +366,8 @@ int product_on_device(hl_ctx* c, size_t t_rows, const int64_t* d_x, size_t xs, c
     if (!rc) rc = d2h(c, &flag, d_flag, 4);
     if (!rc) rc = sync(c, "witness_product");
     else cudaStreamSynchronize(c->stream);
+    if (flag && d_flag) cudaMemsetAsync(d_flag, 0, 4, c->stream);  // back to zero for the next call
     if (d_a) dev_free(c, d_a, a_bytes);
-    if (d_flag) dev_free(c, d_flag, 4);
     if (d_b) dev_free(c, d_b, b_bytes);
     if (!rc && flag == 2) rc = fail(c, HL_B200_ERR_TIMEOUT, "witness product: a bounded wait on the tensor-core pipeline ran out");
     if (!rc) *taken = flag ? 0 : 1;
