@@ -27,14 +27,23 @@ __global__ void __launch_bounds__(256) k_wp_pack(const long long* __restrict__ x
     const u32 mt = t / WP_MT, r = t % WP_MT;
     uint8_t* hi = A + ((size_t)mt * 2 * WP_MT + r) * Kp;
     uint8_t* lo = hi + (size_t)WP_MT * Kp;
-    for (u32 k = blockIdx.x * blockDim.x + threadIdx.x; k < Kp; k += gridDim.x * blockDim.x) {
-        long long v = 0;
-        if (t < t_rows && k < K) {
-            v = x[(size_t)t * xs + k];
-            if (v < -32768 || v > 32767) { atomicExch(flag, 1); v = 0; }
+    // four activations (one 32-byte sector) per thread, one 4-byte word of each plane out
+    for (u32 k = (blockIdx.x * blockDim.x + threadIdx.x) * 4; k < Kp; k += gridDim.x * blockDim.x * 4) {
+        u32 h = 0, l = 0;
+        bool bad = false;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            long long v = 0;
+            if (t < t_rows && k + j < K) {
+                v = x[(size_t)t * xs + k + j];
+                if (v < -32768 || v > 32767) { bad = true; v = 0; }
+            }
+            h |= (u32)((v >> 8) & 255) << (8 * j);
+            l |= (u32)(v & 255) << (8 * j);
         }
-        hi[k] = (uint8_t)(v >> 8);
-        lo[k] = (uint8_t)(v & 255);
+        if (bad) atomicExch(flag, 1);
+        *reinterpret_cast<u32*>(hi + k) = h;
+        *reinterpret_cast<u32*>(lo + k) = l;
     }
 }
 
