@@ -277,8 +277,12 @@ class B200Commit:
         self.ctx.check(self.ctx.lib.hl_b200_store_columns(self.h, _ptr(idx), idx.size, _ptr(out)))
         return out
 
-    def merkle(self, salts: Optional[np.ndarray], leaf_key: Optional[bytes], node_key: Optional[bytes]) -> np.ndarray:
-        out = np.empty((2 * self.nn - 1, 32), dtype=np.uint8)
+    def merkle(self, salts: Optional[np.ndarray], leaf_key: Optional[bytes], node_key: Optional[bytes], out: Optional[np.ndarray] = None) -> np.ndarray:
+        """All levels of the salted tree, (2 nn - 1, 32).  `out`: the caller's buffer for them (page-locked memory makes the read-back
+        a direct copy)."""
+        if out is None:
+            out = np.empty((2 * self.nn - 1, 32), dtype=np.uint8)
+        assert out.dtype == np.uint8 and out.size == (2 * self.nn - 1) * 32 and out.flags.c_contiguous
         s = np.ascontiguousarray(salts, dtype=np.uint8) if salts is not None else None
         self.ctx.check(self.ctx.lib.hl_b200_store_merkle(self.h, _ptr(s), _ptr(leaf_key), _ptr(node_key), _ptr(out)))
         return out
@@ -331,11 +335,12 @@ class B200Backend:
     def try_commit_zk(self, log_cols: int, inv_rate: int, data, pads, pows, max_log: int):
         return self.try_commit_zk_keyed(log_cols, inv_rate, data, pads, pows, max_log, None)
 
-    def try_commit_zk_keyed(self, log_cols: int, inv_rate: int, data, pads, pows, max_log: int, key: Optional[bytes]):
+    def try_commit_zk_keyed(self, log_cols: int, inv_rate: int, data, pads, pows, max_log: int, key: Optional[bytes], leaves_out: Optional[np.ndarray] = None):
         data, pads, pows = _u64(data), _u64(pads), _u64(pows)
         rows = data.size >> log_cols
         q = pads.size // rows if rows else 0
-        leaves = np.empty((inv_rate << log_cols, 32), dtype=np.uint8)
+        leaves = leaves_out if leaves_out is not None else np.empty((inv_rate << log_cols, 32), dtype=np.uint8)
+        assert leaves.dtype == np.uint8 and leaves.size == (inv_rate << log_cols) * 32 and leaves.flags.c_contiguous
         h = C.c_void_p()
         rc = self.ctx.lib.hl_b200_commit_zk(self.ctx.h, log_cols, inv_rate, _ptr(data), rows, _ptr(pads), q, _ptr(pows), max_log,
                                              _ptr(key), C.byref(h), _ptr(leaves))
@@ -343,6 +348,25 @@ class B200Backend:
             self.ctx.declined("b200 zk commit", rc)
             return None
         return B200Commit(self.ctx, h), leaves
+
+    def try_commit_zk_tree(self, log_cols: int, inv_rate: int, data, pads, pows, max_log: int, key: Optional[bytes], salts, leaf_key: Optional[bytes],
+                           node_key: Optional[bytes], leaves_out: Optional[np.ndarray] = None, levels_out: Optional[np.ndarray] = None):
+        """The commitment and its salted tree in one call (pcs.rs:782-817: the salts are drawn before the commitment is offered):
+        (store, leaves, levels) or None on a decline."""
+        data, pads, pows = _u64(data), _u64(pads), _u64(pows)
+        salts = np.ascontiguousarray(salts, dtype=np.uint8)
+        rows, nn = data.size >> log_cols, inv_rate << log_cols
+        q = pads.size // rows if rows else 0
+        leaves = leaves_out if leaves_out is not None else np.empty((nn, 32), dtype=np.uint8)
+        levels = levels_out if levels_out is not None else np.empty((2 * nn - 1, 32), dtype=np.uint8)
+        assert leaves.size == nn * 32 and levels.size == (2 * nn - 1) * 32 and salts.size == nn * 32
+        h = C.c_void_p()
+        rc = self.ctx.lib.hl_b200_commit_zk_tree(self.ctx.h, log_cols, inv_rate, _ptr(data), rows, _ptr(pads), q, _ptr(pows), max_log, _ptr(key),
+                                                  _ptr(salts), _ptr(leaf_key), _ptr(node_key), C.byref(h), _ptr(leaves), _ptr(levels))
+        if rc != 0:
+            self.ctx.declined("b200 zk commit with tree", rc)
+            return None
+        return B200Commit(self.ctx, h), leaves, levels
 
     def commit_zk_dev(self, log_cols: int, inv_rate: int, d_data: int, rows: int, d_pads: int, q: int, d_pows: int,
                       key: Optional[bytes], d_leaves: int = 0) -> B200Commit:

@@ -3,6 +3,32 @@
 
 using namespace hlapi;
 
+static int merkle_on_device(hl_ctx* c, const uint32_t* d_leaves, const uint32_t* d_salts, size_t nn, const uint8_t* leaf_key32,
+                            const uint8_t* node_key32, uint32_t* d_levels) {
+    uint32_t *d_lk = nullptr, *d_nk = nullptr;
+    int rc = upload_key(c, leaf_key32, &d_lk);
+    if (!rc) rc = upload_key(c, node_key32, &d_nk);
+    if (!rc) {
+        Timed t(c, HL_T_MERKLE);
+        cudaError_t e;
+        if (d_salts) {
+            e = hlk::salt_leaves(d_leaves, d_salts, (u32)nn, d_lk, d_levels, c->stream);
+            c->stats.kernel_launches++;
+        } else {
+            e = cudaMemcpyAsync(d_levels, d_leaves, nn * 32, cudaMemcpyDeviceToDevice, c->stream);
+        }
+        if (e == cudaSuccess) {
+            e = hlk::merkle_levels(d_levels, (u32)nn, d_nk, c->stream);
+            for (size_t w = nn; w > 2048; w >>= 1) c->stats.kernel_launches++;
+            if (nn > 1) c->stats.kernel_launches++;
+        }
+        if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "merkle launch", e);
+    }
+    if (d_lk) dev_free(c, d_lk, 32);
+    if (d_nk) dev_free(c, d_nk, 32);
+    return rc;
+}
+
 namespace {
 
 struct Shape {
@@ -127,13 +153,23 @@ void free_store(hl_store* st) {
     delete st;
 }
 
+// the salted tree to build in the same call (commit_zk_owned_with_tag draws the salts before it offers the commitment, pcs.rs:788-792)
+struct TreeAsk {
+    const uint8_t *salts32, *leaf_key32, *node_key32;
+    uint8_t* levels_out;
+};
+
 int commit_host(hl_ctx* c, const Shape& s, const uint64_t* data, const uint64_t* pads, const uint64_t* pows,
-                const uint8_t* key32, hl_store** store, uint8_t* leaves32) {
+                const uint8_t* key32, hl_store** store, uint8_t* leaves32, const TreeAsk* tree = nullptr) {
     hl_store* st = new hl_store();
     st->ctx = c; st->rows = s.rows; st->logn = s.logn; st->logr = s.logr; st->q = s.q; st->zk = s.zk;
     const size_t n = st->n(), nn = st->nn();
     u64* d_pows = nullptr;
+    uint32_t *d_salts = nullptr, *d_levels = nullptr;
     int rc = dev_alloc(c, (void**)&st->d_data, (size_t)s.rows * n * 8);
+    if (!rc && tree) rc = dev_alloc(c, (void**)&d_salts, nn * 32);
+    if (!rc && tree) rc = dev_alloc(c, (void**)&d_levels, (2 * nn - 1) * 32);
+    if (!rc && tree) rc = h2d(c, d_salts, tree->salts32, nn * 32);
     if (!rc && s.zk) rc = dev_alloc(c, (void**)&st->d_pads, (size_t)s.rows * s.q * 8);
     if (!rc && s.zk) rc = dev_alloc(c, (void**)&d_pows, nn * 8);
     if (!rc) rc = dev_alloc(c, (void**)&st->d_enc, (size_t)s.rows * nn * 8);
@@ -141,9 +177,14 @@ int commit_host(hl_ctx* c, const Shape& s, const uint64_t* data, const uint64_t*
     if (!rc && s.zk) rc = h2d(c, st->d_pads, pads, (size_t)s.rows * s.q * 8);
     if (!rc && s.zk) rc = h2d(c, d_pows, pows, nn * 8);
     if (!rc) rc = commit_on_device(c, st, d_pows, key32, data);
+    if (!rc && tree) rc = merkle_on_device(c, st->d_leaves, d_salts, nn, tree->leaf_key32, tree->node_key32, d_levels);
     if (!rc) rc = d2h(c, leaves32, st->d_leaves, nn * 32);
+    if (!rc && tree) rc = d2h(c, tree->levels_out, d_levels, (2 * nn - 1) * 32);
     if (!rc) rc = sync(c, "commit");
+    if (!rc && tree) c->stats.merkles++;
     if (d_pows) dev_free(c, d_pows, nn * 8);
+    if (d_salts) dev_free(c, d_salts, nn * 32);
+    if (d_levels) dev_free(c, d_levels, (2 * nn - 1) * 32);
     if (rc) { cudaStreamSynchronize(c->copy_stream); cudaStreamSynchronize(c->stream); free_store(st); return rc; }
     c->stats.commits++;
     *store = st;
@@ -177,6 +218,19 @@ int hl_b200_commit_zk(hl_ctx* c, uint32_t log_cols, uint32_t inv_rate, const uin
     int rc = check_shape(c, log_cols, inv_rate, rows, q, true, max_log, &s);
     if (rc) return rc;
     return commit_host(c, s, data, pads, pows, key32, store, leaves32);
+}
+
+int hl_b200_commit_zk_tree(hl_ctx* c, uint32_t log_cols, uint32_t inv_rate, const uint64_t* data, size_t rows, const uint64_t* pads, size_t q,
+                           const uint64_t* pows, uint32_t max_log, const uint8_t* key32, const uint8_t* salts32, const uint8_t* leaf_key32,
+                           const uint8_t* node_key32, hl_store** store, uint8_t* leaves32, uint8_t* levels_out) {
+    if (!c || !data || !pads || !pows || !salts32 || !store || !leaves32 || !levels_out) return fail(c, HL_B200_ERR_ARG, "commit_zk_tree: null argument");
+    std::lock_guard<std::mutex> g(c->mu);
+    cudaSetDevice(c->device);
+    Shape s;
+    int rc = check_shape(c, log_cols, inv_rate, rows, q, true, max_log, &s);
+    if (rc) return rc;
+    const TreeAsk tree{salts32, leaf_key32, node_key32, levels_out};
+    return commit_host(c, s, data, pads, pows, key32, store, leaves32, &tree);
 }
 
 int hl_b200_commit_zk_dev(hl_ctx* c, uint32_t log_cols, uint32_t inv_rate, const uint64_t* d_data, size_t rows,
@@ -338,32 +392,6 @@ int hl_b200_store_columns(hl_store* st, const uint64_t* idx, size_t nidx, uint64
 }
 
 // salted leaves + all levels into d_levels, from device leaves (and device salts, or none)
-static int merkle_on_device(hl_ctx* c, const uint32_t* d_leaves, const uint32_t* d_salts, size_t nn, const uint8_t* leaf_key32,
-                            const uint8_t* node_key32, uint32_t* d_levels) {
-    uint32_t *d_lk = nullptr, *d_nk = nullptr;
-    int rc = upload_key(c, leaf_key32, &d_lk);
-    if (!rc) rc = upload_key(c, node_key32, &d_nk);
-    if (!rc) {
-        Timed t(c, HL_T_MERKLE);
-        cudaError_t e;
-        if (d_salts) {
-            e = hlk::salt_leaves(d_leaves, d_salts, (u32)nn, d_lk, d_levels, c->stream);
-            c->stats.kernel_launches++;
-        } else {
-            e = cudaMemcpyAsync(d_levels, d_leaves, nn * 32, cudaMemcpyDeviceToDevice, c->stream);
-        }
-        if (e == cudaSuccess) {
-            e = hlk::merkle_levels(d_levels, (u32)nn, d_nk, c->stream);
-            for (size_t w = nn; w > 2048; w >>= 1) c->stats.kernel_launches++;
-            if (nn > 1) c->stats.kernel_launches++;
-        }
-        if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "merkle launch", e);
-    }
-    if (d_lk) dev_free(c, d_lk, 32);
-    if (d_nk) dev_free(c, d_nk, 32);
-    return rc;
-}
-
 static int merkle_common(hl_ctx* c, const uint32_t* d_leaves_in, const uint8_t* h_leaves, const uint8_t* salts32, size_t nn,
                          const uint8_t* leaf_key32, const uint8_t* node_key32, uint8_t* levels_out) {
     if (log2_exact(nn) < 0 || nn > ((size_t)1 << 26)) return fail(c, HL_B200_ERR_ARG, "merkle: leaf count must be a power of two");
