@@ -22,7 +22,12 @@ constexpr int WP_MT = 128;      // tokens per tile; the stacked tile has 2 * WP_
 constexpr size_t WP_MAX_K = (size_t)1 << 16;
 
 __global__ void __launch_bounds__(256) k_wp_pack(const long long* __restrict__ x, size_t xs, u32 t_rows, u32 K, u32 Kp,
-                                                 uint8_t* __restrict__ A /* tiles x 2 x WP_MT x Kp */, int* __restrict__ flag) {
+                                                 uint8_t* __restrict__ A /* tiles x 2 x WP_MT x Kp */, int* __restrict__ flag,
+                                                 long long* __restrict__ clear, size_t clear_words) {
+    // the result plane's clear rides along (the product kernel runs after this one): one launch less on a launch-bound path
+    for (size_t i = ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * blockDim.x + threadIdx.x; i < clear_words;
+         i += (size_t)gridDim.x * gridDim.y * blockDim.x)
+        clear[i] = 0;
     const u32 t = blockIdx.y;  // padded token index
     const u32 mt = t / WP_MT, r = t % WP_MT;
     uint8_t* hi = A + ((size_t)mt * 2 * WP_MT + r) * Kp;
@@ -160,6 +165,8 @@ __global__ void __launch_bounds__(UM_THREADS, 1) k_wp_umma(const __grid_constant
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::);
     }
     if (warp == 0) {
+        // all 512 columns: the allocation cannot wait on another CTA, because this kernel's shared memory (3 stages of 64 KB) lets
+        // only one CTA live on an SM and no other kernel of the library holds TMEM
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"((u32)__cvta_generic_to_shared(&tmem_slot)), "r"(512u));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
     }
@@ -348,10 +355,11 @@ int product_on_device(hl_ctx* c, size_t t_rows, const int64_t* d_x, size_t xs, c
         Timed t(c, HL_T_WITNESS);
         // the plane is cleared unless the product kernel writes every word of it exactly once
         const bool dense = splits == 1 && os == N && out_len == t_rows * N;
-        cudaError_t e = dense ? cudaSuccess : cudaMemsetAsync(d_out, 0, out_len * 8, c->stream);
+        cudaError_t e = cudaSuccess;
         if (e == cudaSuccess && b_bytes) e = cudaMemsetAsync(d_b, 0, b_bytes, c->stream);
         if (e == cudaSuccess) {
-            k_wp_pack<<<dim3((Kp + 1023) / 1024, tiles * WP_MT), 256, 0, c->stream>>>((const long long*)d_x, xs, (u32)t_rows, (u32)K, Kp, d_a, d_flag);
+            k_wp_pack<<<dim3((Kp + 1023) / 1024, tiles * WP_MT), 256, 0, c->stream>>>((const long long*)d_x, xs, (u32)t_rows, (u32)K, Kp, d_a, d_flag,
+                                                                                       (long long*)d_out, dense ? 0 : out_len);
             e = cudaGetLastError();
             c->stats.kernel_launches++;
         }
