@@ -83,3 +83,29 @@ def test_resident_operands(ctx, oracle):
     torch.cuda.synchronize()
     assert ctx.witness_product_dev(t, d_x.data_ptr(), x.size, k, d_w.data_ptr(), w.size, k, n, n, out_len, False, d_out.data_ptr())
     assert (d_out.cpu().numpy() == oracle.witness_product(t, x, k, w, k, n, n, out_len, False)).all()
+
+
+@pytest.mark.parametrize("k,n", [(4096, 14336), (14336, 4096), (4096, 1024)])
+def test_block_size_products_on_sampled_columns(ctx, oracle, k, n):
+    """The 8B block's own shapes (T = 128): weights read in place, K split with atomics; the CPU restatement on three
+    bands of output columns (the whole product would take it a minute)."""
+    import torch
+
+    t = 128
+    g = torch.Generator().manual_seed(k + n)
+    x = torch.randint(-32768, 32768, (t * k,), dtype=torch.int64, generator=g).numpy()
+    w = torch.randint(-128, 128, (k * n,), dtype=torch.int8, generator=g).numpy()
+    got = ctx.witness_product(t, x, k, w, k, n, n, t * n, False)
+    assert got is not None
+    got = got.reshape(t, n)
+    for c0 in (0, (n // 2 // 64) * 64 + 13, n - 64):
+        band = np.ascontiguousarray(w.reshape(n, k)[c0:c0 + 64])
+        want = oracle.witness_product(t, x, k, band, k, 64, 64, t * 64, False).reshape(t, 64)
+        assert (got[:, c0:c0 + 64] == want).all(), c0
+    # linearity in the activations: W (x + x') = W x + W x' on the full plane (exact integers)
+    x2 = torch.randint(-1000, 1000, (t * k,), dtype=torch.int64, generator=g).numpy()
+    xs_ = np.clip(x, -30000, 30000)
+    a = ctx.witness_product(t, xs_, k, w, k, n, n, t * n, False)
+    b = ctx.witness_product(t, x2, k, w, k, n, n, t * n, False)
+    c = ctx.witness_product(t, xs_ + x2, k, w, k, n, n, t * n, False)
+    assert (a + b == c).all()
