@@ -330,6 +330,12 @@ int hl_b200_store_fold(hl_store* st, const uint64_t* rhos, size_t k, int with_pa
         if (!rc && s_rows.size()) rc = h2d(c, d_srows, s_rows.data(), s_rows.size() * 4);
         if (!rc && s_rows.size()) rc = h2d(c, d_sw, s_w.data(), s_w.size() * 8);
     }
+    const bool contiguous = st->zk || st->fold_data;
+    const u32 few = kd ? hlk::fold_few_ranges(rows, n, q, kd, contiguous ? 1u : 2u, c->sm_count) : 0;
+    const u32 fsplits = kd && !few ? hlk::fold_row_splits(rows, n, q, kd, c->sm_count) : 1;
+    u64* d_part = nullptr;
+    const size_t part_bytes = few ? (size_t)few * kd * w * 16 : fsplits > 1 ? (size_t)fsplits * kd * w * 16 : 0;
+    if (!rc && part_bytes) rc = dev_alloc(c, (void**)&d_part, part_bytes);
     if (!rc) {
         Timed t(c, HL_T_FOLD);
         // hiding form: the message is the resident data (the encoding is not systematic, pcs.rs:985-987);
@@ -340,9 +346,12 @@ int hl_b200_store_fold(hl_store* st, const uint64_t* rhos, size_t k, int with_pa
         const u32 ir = from_data ? 1u : 1u << st->logr;
         const u64* src2 = st->zk && q ? st->d_pads : nullptr;
         cudaError_t e = cudaSuccess;
-        if (kd) {
-            e = hlk::fold_rows(src, rows, n, ld, ir, src2, q, q, d_rhos, kd, d_dmap, d_out, w, c->stream);
-            c->stats.kernel_launches++;
+        if (kd && few) {
+            e = hlk::fold_rows_few(src, rows, n, ld, src2, q, q, d_rhos, kd, d_dmap, d_out, w, few, d_part, c->stream);
+            c->stats.kernel_launches += 2;
+        } else if (kd) {
+            e = hlk::fold_rows(src, rows, n, ld, ir, src2, q, q, d_rhos, kd, d_dmap, d_out, w, c->stream, fsplits, d_part);
+            c->stats.kernel_launches += fsplits > 1 ? 2 : 1;
         }
         if (e == cudaSuccess && ks) {
             e = hlk::fold_rows_sparse(src, n, ld, ir, src2, q, q, d_soff, d_srows, d_sw, ks, d_smap, d_out, w, c->stream);
@@ -352,6 +361,7 @@ int hl_b200_store_fold(hl_store* st, const uint64_t* rhos, size_t k, int with_pa
     }
     if (!rc) rc = d2h(c, out, d_out, ob);
     if (!rc) rc = sync(c, "store_fold");
+    if (d_part) dev_free(c, d_part, part_bytes);
     if (d_rhos) dev_free(c, d_rhos, rb);
     if (d_dmap) dev_free(c, d_dmap, kd * 4);
     if (d_smap) dev_free(c, d_smap, ks * 4);

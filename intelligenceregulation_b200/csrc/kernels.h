@@ -25,8 +25,16 @@ cudaError_t merkle_levels(uint32_t* d_levels, u32 nn, const uint32_t* d_node_key
 
 // store.cu
 // out[g] = rho_g^T [src | src2]: ncols entries from src (element (i, j) at src[i ld + j ir]), then ncols2 from src2 (may be NULL)
-cudaError_t fold_rows(const u64* src, u32 rows, u32 ncols, size_t ld, u32 ir, const u64* src2, u32 ncols2, size_t ld2,
-                      const u64* d_rhos, u32 k, const u32* d_out_map, u64* d_out, u32 out_ld, cudaStream_t st);
+// rows cut into `splits` ranges (fold_row_splits: > 1 when a few dense vectors would leave the machine short of loads in flight);
+// d_part = splits x k x out_ld Fp2 of scratch when splits > 1
+u32 fold_row_splits(u32 rows, u32 ncols, u32 ncols2, u32 k, int sm_count);
+// one or two dense vectors over contiguous rows in one memory-shaped pass: fold_few_ranges > 0 when it applies (d_part = ranges x k x
+// out_ld Fp2 of scratch)
+u32 fold_few_ranges(u32 rows, u32 ncols, u32 ncols2, u32 k, u32 ir, int sm_count);
+cudaError_t fold_rows_few(const u64* src, u32 rows, u32 ncols, size_t ld, const u64* src2, u32 ncols2, size_t ld2, const u64* d_rhos, u32 k,
+                          const u32* d_out_map, u64* d_out, u32 out_ld, u32 ranges, u64* d_part, cudaStream_t st);
+cudaError_t fold_rows(const u64* src, u32 rows, u32 ncols, size_t ld, u32 ir, const u64* src2, u32 ncols2, size_t ld2, const u64* d_rhos, u32 k,
+                      const u32* d_out_map, u64* d_out, u32 out_ld, cudaStream_t st, u32 splits = 1, u64* d_part = nullptr);
 cudaError_t fold_rows_sparse(const u64* src, u32 ncols, size_t ld, u32 ir, const u64* src2, u32 ncols2, size_t ld2, const u32* d_off,
                              const u32* d_rows, const u64* d_weights, u32 k, const u32* d_out_map, u64* d_out, u32 out_ld, cudaStream_t st);
 cudaError_t gather_columns(const u64* enc, u32 rows, size_t nn, const u64* d_idx, u32 nidx, u64* d_out, cudaStream_t st);
