@@ -196,6 +196,76 @@ __global__ void __launch_bounds__(32 * FC_WARPS) k_fold_cols_i8(const signed cha
     }
 }
 
+// The same sum for rows of whole 16-byte groups (cols a multiple of 16, 16-byte aligned matrix): the matrix is read once with
+// 16-byte loads, one row per warp, and the coefficients come from shared memory, a tile of FCV_TILE columns at a time (split
+// into their 32-bit halves once per CTA, padded by one entry per 16 so that a quarter-warp's 16-byte reads fall in distinct
+// banks).  The bias term 128 * sum_j c[j] is the same for every row: one field sum per CTA instead of four integer
+// additions per matrix byte.
+constexpr int FCV_WARPS = 8;          // rows per CTA
+constexpr int FCV_TILE = 2048;        // columns per shared-memory tile
+__global__ void __launch_bounds__(32 * FCV_WARPS) k_fold_cols_i8_vec(const signed char* __restrict__ m, u32 rows, u32 cols, const u64* __restrict__ c,
+                                                                     u64* __restrict__ out) {
+    __shared__ uint4 cs[FCV_TILE + FCV_TILE / 16];
+    __shared__ u64 csum_part[FCV_WARPS][2];
+    const u32 lane = threadIdx.x & 31, warp = threadIdx.x >> 5, row = blockIdx.x * FCV_WARPS + warp;
+    u64 s[4] = {0, 0, 0, 0}, run0 = 0, run1 = 0, cs0 = 0, cs1 = 0;
+    u32 since = 0;
+    for (u32 t0 = 0; t0 < cols; t0 += FCV_TILE) {
+        const u32 nt = min((u32)FCV_TILE, cols - t0);
+        __syncthreads();
+        for (u32 j = threadIdx.x; j < nt; j += 32 * FCV_WARPS) {
+            const ulonglong2 cw = *reinterpret_cast<const ulonglong2*>(c + 2 * (size_t)(t0 + j));
+            cs[j + (j >> 4)] = make_uint4((u32)cw.x, (u32)(cw.x >> 32), (u32)cw.y, (u32)(cw.y >> 32));
+            cs0 = gl_add(cs0, cw.x);
+            cs1 = gl_add(cs1, cw.y);
+        }
+        __syncthreads();
+        if (row < rows) {
+            for (u32 j = lane * 16; j < nt; j += 32 * 16) {
+                const uint4 mv = *reinterpret_cast<const uint4*>(m + (size_t)row * cols + t0 + j);
+                const u32 words[4] = {mv.x ^ 0x80808080u, mv.y ^ 0x80808080u, mv.z ^ 0x80808080u, mv.w ^ 0x80808080u};  // +128 on every byte
+                const uint4* ce = cs + j + (j >> 4);
+#pragma unroll
+                for (int e = 0; e < 16; e++) {
+                    const u32 v = (words[e >> 2] >> (8 * (e & 3))) & 0xFFu;
+                    const uint4 cv = ce[e];
+                    s[0] += (u64)cv.x * v; s[1] += (u64)cv.y * v; s[2] += (u64)cv.z * v; s[3] += (u64)cv.w * v;
+                }
+                since += 16;
+                if (since + 16 > I8_BLOCK) {  // keep every accumulator below 2^56
+                    const u64 W32 = 1ull << 32;
+                    run0 = gl_add(run0, gl_add(s[0], gl_mul(s[1], W32)));
+                    run1 = gl_add(run1, gl_add(s[2], gl_mul(s[3], W32)));
+                    s[0] = s[1] = s[2] = s[3] = 0;
+                    since = 0;
+                }
+            }
+        }
+    }
+    // sum_j c[j] over the CTA (each thread staged a share of every tile)
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+        cs0 = gl_add(cs0, shfl_xor64(cs0, off));
+        cs1 = gl_add(cs1, shfl_xor64(cs1, off));
+    }
+    if (lane == 0) { csum_part[warp][0] = cs0; csum_part[warp][1] = cs1; }
+    __syncthreads();
+    const u64 W32 = 1ull << 32;
+    u64 x0 = gl_add(run0, gl_add(s[0], gl_mul(s[1], W32))), x1 = gl_add(run1, gl_add(s[2], gl_mul(s[3], W32)));
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+        x0 = gl_add(x0, shfl_xor64(x0, off));
+        x1 = gl_add(x1, shfl_xor64(x1, off));
+    }
+    if (lane == 0 && row < rows) {
+        u64 t0 = 0, t1 = 0;
+#pragma unroll
+        for (int w = 0; w < FCV_WARPS; w++) { t0 = gl_add(t0, csum_part[w][0]); t1 = gl_add(t1, csum_part[w][1]); }
+        out[2 * (size_t)row] = gl_sub(x0, gl_mul(t0, 128));
+        out[2 * (size_t)row + 1] = gl_sub(x1, gl_mul(t1, 128));
+    }
+}
+
 }  // namespace
 
 namespace hlk {
@@ -222,6 +292,10 @@ cudaError_t fold_rows_i8(const signed char* d_m, u32 rows, u32 cols, const u64* 
 }
 
 cudaError_t fold_cols_i8(const signed char* d_m, u32 rows, u32 cols, const u64* d_c, u64* d_out, cudaStream_t st) {
+    if (cols % 16 == 0 && (reinterpret_cast<uintptr_t>(d_m) & 15) == 0 && cols >= 512) {
+        k_fold_cols_i8_vec<<<(rows + FCV_WARPS - 1) / FCV_WARPS, 32 * FCV_WARPS, 0, st>>>(d_m, rows, cols, d_c, d_out);
+        return cudaGetLastError();
+    }
     k_fold_cols_i8<<<(rows + FC_ROWS - 1) / FC_ROWS, 32 * FC_WARPS, 0, st>>>(d_m, rows, cols, d_c, d_out);
     return cudaGetLastError();
 }
