@@ -229,6 +229,12 @@ def device_extras(dev, backend, np_data, np_pads, np_pows, col_key) -> dict:
         ctx.fold_cols_i8(wm, cw)
     t = ctx.timing_read(reset=True)
     out["fold_cols_i8_4096x14336_ms"] = t["fold"][0] / 2
+    rw = splitmix_fp(89, 4096 * 2).reshape(4096, 2)
+    for rep in range(3):
+        if rep == 1:
+            ctx.timing_read(reset=True)
+        ctx.fold_rows_i8(wm, rw)
+    out["fold_rows_i8_4096x14336_ms"] = ctx.timing_read(reset=True)["fold"][0] / 2
     # the pads and salts of the hiding commitment of `A` expanded on the device from the caller's generator key
     # (rows * q field draws, then nn salts of four words: 11.2 MB + 1 MB of BLAKE3 extended output)
     import torch
@@ -483,6 +489,8 @@ def cpu_extras(o, backend, np_data) -> dict:
     wm = (splitmix_fp(84, 4096 * 14336) % np.uint64(256)).astype(np.uint8).view(np.int8).reshape(4096, 14336)
     cw = splitmix_fp(85, 14336 * 2).reshape(14336, 2)
     out["fold_cols_i8_4096x14336_ms"] = timed(lambda: o.fold_cols_i8(wm, cw))
+    rw = splitmix_fp(89, 4096 * 2).reshape(4096, 2)
+    out["fold_rows_i8_4096x14336_ms"] = timed(lambda: o.fold_rows_i8(wm, rw))
     npair = 1 << 22
     la = (splitmix_fp(92, npair) % np.uint64(256)).astype(np.int64)
     lb = (splitmix_fp(93, npair) % np.uint64(256)).astype(np.int64)

@@ -8,6 +8,8 @@ cudaError_t logup_histogram(const int* d_idx, size_t nq, u32 table_len, u64* d_m
 cudaError_t logup_helpers(const int* d_idx, const int* d_out, size_t nq, fp2 base, fp2 beta, const u64* d_mult, u64* d_h, int* d_err,
                           cudaStream_t st);
 cudaError_t fold_rows_i8(const signed char* d_m, u32 rows, u32 cols, const u64* d_w, u64* d_out, cudaStream_t st);
+u32 fold_rows_i8_range(const signed char* d_m, u32 rows, u32 cols, int sm_count);
+cudaError_t fold_rows_i8_big(const signed char* d_m, u32 rows, u32 cols, const u64* d_w, u64* d_out, u32 range, u64* d_part, cudaStream_t st);
 cudaError_t fold_cols_i8(const signed char* d_m, u32 rows, u32 cols, const u64* d_c, u64* d_out, cudaStream_t st);
 }  // namespace hlk
 
@@ -88,15 +90,21 @@ static int fold_i8(hl_ctx* c, bool by_rows, const int8_t* m, size_t rows, size_t
     if (!rc) rc = dev_alloc(c, (void**)&d_o, no * 16);
     if (!rc) rc = h2d(c, d_m, m, rows * cols);
     if (!rc) rc = h2d(c, d_w, w, nw * 16);
+    const u32 range = !rc && by_rows ? hlk::fold_rows_i8_range(d_m, (u32)rows, (u32)cols, c->sm_count) : 0;
+    const u32 ranges = range ? (u32)((rows + range - 1) / range) : 0;
+    u64* d_part = nullptr;
+    if (!rc && ranges) rc = dev_alloc(c, (void**)&d_part, (size_t)ranges * cols * 16);
     if (!rc) {
         Timed t(c, HL_T_FOLD);
-        cudaError_t e = by_rows ? hlk::fold_rows_i8(d_m, (u32)rows, (u32)cols, d_w, d_o, c->stream)
-                                : hlk::fold_cols_i8(d_m, (u32)rows, (u32)cols, d_w, d_o, c->stream);
-        c->stats.kernel_launches++;
+        cudaError_t e = ranges    ? hlk::fold_rows_i8_big(d_m, (u32)rows, (u32)cols, d_w, d_o, range, d_part, c->stream)
+                        : by_rows ? hlk::fold_rows_i8(d_m, (u32)rows, (u32)cols, d_w, d_o, c->stream)
+                                  : hlk::fold_cols_i8(d_m, (u32)rows, (u32)cols, d_w, d_o, c->stream);
+        c->stats.kernel_launches += ranges ? 2 : 1;
         if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "int8 fold launch", e);
     }
     if (!rc) rc = d2h(c, out, d_o, no * 16);
     if (!rc) rc = sync(c, "fold_i8");
+    if (d_part) dev_free(c, d_part, (size_t)ranges * cols * 16);
     dev_free(c, d_m, rows * cols); dev_free(c, d_w, nw * 16); dev_free(c, d_o, no * 16);
     return rc;
 }

@@ -266,6 +266,60 @@ __global__ void __launch_bounds__(32 * FCV_WARPS) k_fold_cols_i8_vec(const signe
     }
 }
 
+// out[j] = sum_i w[i] * M[i][j] for a matrix with many rows (a weight matrix folded over its input dimension, mle.rs:157-200): the
+// rows are cut into ranges of FRB_RANGE so that the grid fills the machine, a thread owns eight adjacent columns (8-byte loads, a
+// CTA reads 2 KB of every row), the range's weights sit in shared memory as 32-bit halves and are broadcast; range z writes its
+// bias-corrected partial sums to part[z][cols] and k_fold_i8_sum adds the ranges.
+constexpr int FRB_THREADS = 256, FRB_CPT = 8, FRB_RANGE = 64;
+__global__ void __launch_bounds__(FRB_THREADS) k_fold_rows_i8_big(const signed char* __restrict__ m, u32 rows, u32 cols, const u64* __restrict__ w,
+                                                                  u32 range /* rows per CTA, at most FRB_RANGE */, u64* __restrict__ part) {
+    __shared__ uint4 ws[FRB_RANGE];
+    __shared__ u64 wsum[2];
+    const u32 row_lo = blockIdx.y * range, nr = min(range, rows - row_lo);
+    if (threadIdx.x < nr) {
+        const u64 a = w[(size_t)(row_lo + threadIdx.x) * 2], b = w[(size_t)(row_lo + threadIdx.x) * 2 + 1];
+        ws[threadIdx.x] = make_uint4((u32)a, (u32)(a >> 32), (u32)b, (u32)(b >> 32));
+    }
+    if (threadIdx.x < 2) {
+        u64 t = 0;
+        for (u32 i = 0; i < nr; i++) t = gl_add(t, w[(size_t)(row_lo + i) * 2 + threadIdx.x]);
+        wsum[threadIdx.x] = t;
+    }
+    __syncthreads();
+    const u32 col = (blockIdx.x * FRB_THREADS + threadIdx.x) * FRB_CPT;
+    if (col >= cols) return;
+    u64 s[FRB_CPT][4];
+#pragma unroll
+    for (int e = 0; e < FRB_CPT; e++) s[e][0] = s[e][1] = s[e][2] = s[e][3] = 0;
+    const signed char* p = m + (size_t)row_lo * cols + col;
+#pragma unroll 8
+    for (u32 i = 0; i < nr; i++) {
+        const uint2 mv = *reinterpret_cast<const uint2*>(p + (size_t)i * cols);
+        const u32 lo = mv.x ^ 0x80808080u, hi = mv.y ^ 0x80808080u;  // +128 on every byte
+        const uint4 wv = ws[i];
+#pragma unroll
+        for (int e = 0; e < FRB_CPT; e++) {
+            const u32 v = ((e < 4 ? lo : hi) >> (8 * (e & 3))) & 0xFFu;
+            s[e][0] += (u64)wv.x * v; s[e][1] += (u64)wv.y * v; s[e][2] += (u64)wv.z * v; s[e][3] += (u64)wv.w * v;
+        }
+    }
+    const u64 W32 = 1ull << 32, b0 = gl_mul(wsum[0], 128), b1 = gl_mul(wsum[1], 128);
+    u64* o = part + ((size_t)blockIdx.y * cols + col) * 2;
+#pragma unroll
+    for (int e = 0; e < FRB_CPT; e++) {  // at most 64 terms below 2^40 each: canonical words
+        o[2 * e] = gl_sub(gl_add(s[e][0], gl_mul(s[e][1], W32)), b0);
+        o[2 * e + 1] = gl_sub(gl_add(s[e][2], gl_mul(s[e][3], W32)), b1);
+    }
+}
+
+__global__ void __launch_bounds__(256) k_fold_i8_sum(const u64* __restrict__ part, u32 ranges, size_t words, u64* __restrict__ out) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= words) return;
+    u64 s = 0;
+    for (u32 z = 0; z < ranges; z++) s = gl_add(s, part[(size_t)z * words + i]);
+    out[i] = s;
+}
+
 }  // namespace
 
 namespace hlk {
@@ -282,6 +336,28 @@ cudaError_t logup_helpers(const int* d_idx, const int* d_out, size_t nq, fp2 bas
     if (nq == 0) return cudaSuccess;
     size_t threads = (nq + LB - 1) / LB;
     k_logup_helpers<<<(unsigned)((threads + 127) / 128), 128, 0, st>>>(d_idx, d_out, nq, base, beta, d_mult, d_h, d_err);
+    return cudaGetLastError();
+}
+
+// rows per CTA of the many-row form: enough ranges for two CTAs per SM, between 8 and FRB_RANGE rows each (0: the single-pass
+// kernel serves the shape); scratch = ceil(rows / range) x cols Fp2
+u32 fold_rows_i8_range(const signed char* d_m, u32 rows, u32 cols, int sm_count) {
+    if (rows < 32 || cols % FRB_CPT != 0 || (reinterpret_cast<uintptr_t>(d_m) & 7) != 0) return 0;
+    const u32 tiles = (cols / FRB_CPT + FRB_THREADS - 1) / FRB_THREADS;
+    u32 range = (u32)(((u64)rows * tiles + 2u * (u32)sm_count - 1) / (2u * (u32)sm_count));
+    if (range < 8) range = 8;
+    if (range > (u32)FRB_RANGE) range = FRB_RANGE;
+    return range;
+}
+
+cudaError_t fold_rows_i8_big(const signed char* d_m, u32 rows, u32 cols, const u64* d_w, u64* d_out, u32 range, u64* d_part, cudaStream_t st) {
+    const u32 ranges = (rows + range - 1) / range;
+    dim3 grid((cols / FRB_CPT + FRB_THREADS - 1) / FRB_THREADS, ranges);
+    k_fold_rows_i8_big<<<grid, FRB_THREADS, 0, st>>>(d_m, rows, cols, d_w, range, d_part);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    const size_t words = (size_t)cols * 2;
+    k_fold_i8_sum<<<(unsigned)((words + 255) / 256), 256, 0, st>>>(d_part, ranges, words, d_out);
     return cudaGetLastError();
 }
 

@@ -34,3 +34,24 @@ def test_fold_cols_block_shape(ctx, oracle):
     got = ctx.fold_cols_i8(m, c)
     for r0 in (0, 2000, 4088):
         assert (got[r0:r0 + 8] == oracle.fold_cols_i8(m[r0:r0 + 8], c)).all()
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 8), (100, 64), (255, 4096), (256, 8), (257, 24), (1000, 520), (4096, 1030), (2049, 4096), (300, 6)])
+def test_fold_rows(ctx, oracle, rows, cols):
+    rng = np.random.default_rng(rows * 3 + cols)
+    m = rng.integers(-128, 128, size=(rows, cols), dtype=np.int8)
+    m[:, 0] = -128
+    if cols > 1:
+        m[:, 1] = 127
+    w = oracle.ZkRng(rows, b"i8-fold-rows").fp2_vec(rows)
+    w[::53] = np.array([0xFFFFFFFF00000000, 0xFFFFFFFF00000000], dtype=np.uint64)
+    assert (ctx.fold_rows_i8(m, w) == oracle.fold_rows_i8(m, w)).all()
+
+
+def test_fold_rows_block_shape(ctx, oracle):
+    rng = np.random.default_rng(4)
+    m = rng.integers(-128, 128, size=(14336, 4096), dtype=np.int8)
+    w = oracle.ZkRng(6, b"i8-fold-rows").fp2_vec(14336)
+    got = ctx.fold_rows_i8(m, w)
+    for c0 in (0, 2048, 4032):
+        assert (got[c0:c0 + 64] == oracle.fold_rows_i8(np.ascontiguousarray(m[:, c0:c0 + 64]), w)).all()
