@@ -64,7 +64,7 @@ bool sc_supported(int poly, int k, int degree);
 cudaError_t sc_round(int poly, int k, const u64* tables, size_t stride, u32 half, const u64* coefs, int eval_one, u64* partials,
                      u32 nblocks, cudaStream_t s);
 cudaError_t sc_step(const ScStep& a, cudaStream_t s);
-constexpr u32 SC_TAIL_LEN = 4096;  // table length from which the remaining rounds run in one CTA
+constexpr u32 SC_TAIL_LEN = 1024;  // table length from which the remaining rounds run in one CTA (one SM: above it a round's arithmetic costs more than three launches)
 cudaError_t sc_tail(int poly, int k, u64* tables, size_t stride, u32 len, const u64* coefs, const ScStep& a, int nrounds,
                     int first_has_claim, u64* scratch, cudaStream_t s);
 cudaError_t sc_fold(u64* tables, size_t stride, u32 half, u32 k, const ScState* st, cudaStream_t s);
