@@ -62,19 +62,36 @@ __device__ __forceinline__ bool helper_one(const Col& c, size_t i, fp2& out) {
     return true;
 }
 
+// two looked words per thread: 16-byte reads of the columns and 16-byte writes of the planes where the addresses allow
 __global__ void __launch_bounds__(256) k_lookup_helpers(Col a, Col b, int paired, size_t n, u64* __restrict__ re, u64* __restrict__ im,
                                                         int* __restrict__ err) {
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    fp2 h, y;
-    bool ok = helper_one(a, i, h);
-    if (ok && paired) {
-        ok = helper_one(b, i, y);
-        if (ok) h = f2_add(h, y);
+    const size_t i0 = 2 * ((size_t)blockIdx.x * blockDim.x + threadIdx.x);
+    if (i0 >= n) return;
+    const int cnt = i0 + 1 < n ? 2 : 1;
+    u64 r[2] = {0, 0}, m[2] = {0, 0};
+    bool ok = true;
+#pragma unroll
+    for (int e = 0; e < 2; e++) {
+        if (e < cnt) {
+            fp2 h, y;
+            bool good = helper_one(a, i0 + e, h);
+            if (good && paired) {
+                good = helper_one(b, i0 + e, y);
+                if (good) h = f2_add(h, y);
+            }
+            ok &= good;
+            r[e] = h.c0;
+            m[e] = h.c1;
+        }
     }
     if (!ok) { atomicExch(err, 1); return; }
-    re[i] = h.c0;
-    im[i] = h.c1;
+    const bool wide = cnt == 2 && ((reinterpret_cast<uintptr_t>(re + i0) | reinterpret_cast<uintptr_t>(im + i0)) & 15) == 0;
+    if (wide) {
+        *reinterpret_cast<ulonglong2*>(re + i0) = make_ulonglong2(r[0], r[1]);
+        *reinterpret_cast<ulonglong2*>(im + i0) = make_ulonglong2(m[0], m[1]);
+    } else {
+        for (int e = 0; e < cnt; e++) { re[i0 + e] = r[e]; im[i0 + e] = m[e]; }
+    }
 }
 
 int check_log(hl_ctx* c, uint32_t log_len) {
@@ -118,7 +135,7 @@ int hl_b200_lookup_helpers_dev(hl_ctx* c, const int64_t* d_a, const uint64_t* d_
     if (d_b) b = Col{reinterpret_cast<const long long*>(d_b), reinterpret_cast<const u64*>(d_table_b), 1u << log_b, f2_sub(al, f2(g_b[0], g_b[1]))};
     if (!rc) {
         Timed t(c, HL_T_LOGUP);
-        k_lookup_helpers<<<(unsigned)((n + 255) / 256), 256, 0, c->stream>>>(a, b, d_b ? 1 : 0, n, reinterpret_cast<u64*>(d_re),
+        k_lookup_helpers<<<(unsigned)((n + 511) / 512), 256, 0, c->stream>>>(a, b, d_b ? 1 : 0, n, reinterpret_cast<u64*>(d_re),
                                                                             reinterpret_cast<u64*>(d_im), d_err);
         c->stats.kernel_launches++;
         cudaError_t e = cudaGetLastError();

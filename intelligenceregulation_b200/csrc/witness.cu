@@ -295,14 +295,14 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 // a byte matrix of `rows` rows of `inner` readable bytes, `pitch` bytes apart (a multiple of 16), read in boxes of 128 bytes x 256 rows
 // with the 128-byte swizzle; rows and bytes outside the matrix read as zero
 int byte_matrix_map(hl_ctx* c, const void* base, size_t inner, size_t rows, size_t pitch, CUtensorMap* map) {
-    static EncodeTiledFn encode = nullptr;
-    if (!encode) {
+    // looked up once per process (a function-local static is initialised under the language's own lock)
+    static const EncodeTiledFn encode = [] {
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn)
-            return fail(c, HL_B200_ERR_DEVICE, "witness product: the driver has no tensor-map encoder");
-        encode = (EncodeTiledFn)fn;
-    }
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) fn = nullptr;
+        return (EncodeTiledFn)fn;
+    }();
+    if (!encode) return fail(c, HL_B200_ERR_DEVICE, "witness product: the driver has no tensor-map encoder");
     const cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)rows}, strides[1] = {(cuuint64_t)pitch};
     const cuuint32_t box[2] = {(cuuint32_t)UM_KT, 256u}, elem[2] = {1u, 1u};
     const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
