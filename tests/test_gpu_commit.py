@@ -336,3 +336,27 @@ def test_block_size_commit_properties(dev, oracle):
     want0 = o.fold_rows(data, rows, n, n, 1, rho[:1])
     assert (f[0, :n] == want0[0]).all()
     store.free()
+
+
+def test_verifier_encodes_the_clear_vectors_through_the_commit_entry(dev, oracle):
+    """verify_zk_tagged (pcs.rs:1290-1302) encodes every clear vector of an opening (group vectors and the proximity vector, real and
+    imaginary parts apart) with encode_row_zk(v[..n], v[n..]) and reads the encodings at the opened indices: on the device that is
+    a hiding commitment whose data rows are the vectors' heads and whose pad rows are their tails, followed by the store's column
+    gather; the column hash that comes with it is not used."""
+    o = oracle
+    log_cols, ir, q, nvec, nidx = 10, 2, 40, 7, 33
+    n, nn = 1 << log_cols, (1 << log_cols) * ir
+    vecs = o.ZkRng(71, b"verify-vecs").fp2_vec(nvec * (n + q)).reshape(nvec, n + q, 2)
+    idx = o.ZkRng(72, b"verify-idx").fp_vec(nidx) % np.uint64(nn)
+    pows = o.coset_powers(7, nn)
+    rows = np.concatenate([vecs[:, :, 0], vecs[:, :, 1]])            # 2 nvec rows of n + q words: re parts, then im parts
+    heads, tails = np.ascontiguousarray(rows[:, :n]), np.ascontiguousarray(rows[:, n:])
+    got = dev.try_commit_zk_keyed(log_cols, ir, heads.reshape(-1), tails.reshape(-1), pows, log_cols + 1, None)
+    assert got is not None
+    store, _ = got
+    cols = store.columns(idx)                                        # (nidx, 2 nvec)
+    for g in range(nvec):
+        ere = o.encode_row_zk(heads[g], tails[g], pows, log_cols + 1)
+        eim = o.encode_row_zk(heads[nvec + g], tails[nvec + g], pows, log_cols + 1)
+        assert (cols[:, g] == ere[idx.astype(np.int64)]).all() and (cols[:, nvec + g] == eim[idx.astype(np.int64)]).all()
+    store.free()
