@@ -10,18 +10,9 @@ static int merkle_on_device(hl_ctx* c, const uint32_t* d_leaves, const uint32_t*
     if (!rc) rc = upload_key(c, node_key32, &d_nk);
     if (!rc) {
         Timed t(c, HL_T_MERKLE);
-        cudaError_t e;
-        if (d_salts) {
-            e = hlk::salt_leaves(d_leaves, d_salts, (u32)nn, d_lk, d_levels, c->stream);
-            c->stats.kernel_launches++;
-        } else {
-            e = cudaMemcpyAsync(d_levels, d_leaves, nn * 32, cudaMemcpyDeviceToDevice, c->stream);
-        }
-        if (e == cudaSuccess) {
-            e = hlk::merkle_levels(d_levels, (u32)nn, d_nk, c->stream);
-            for (size_t w = nn; w > 2048; w >>= 1) c->stats.kernel_launches++;
-            if (nn > 1) c->stats.kernel_launches++;
-        }
+        int launches = 0;
+        const cudaError_t e = hlk::merkle_tree(d_leaves, d_salts, (u32)nn, d_lk, d_nk, d_levels, c->stream, &launches);
+        c->stats.kernel_launches += launches;
         if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "merkle launch", e);
     }
     if (d_lk) dev_free(c, d_lk, 32);

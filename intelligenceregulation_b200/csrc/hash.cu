@@ -125,9 +125,75 @@ __global__ void __launch_bounds__(1024) k_merkle_top(uint32_t* __restrict__ leve
     }
 }
 
+// Salted leaves and the lowest levels of the tree in one launch: a CTA owns SUB consecutive leaves, salts them (or takes them as
+// they are when there are no salts), and hashes its subtree level by level through shared memory, writing every level to its place
+// in `levels`; k_merkle_top then joins the nn / SUB subtree roots.  Two launches for a tree instead of one per level.
+constexpr u32 SUBTREE = 512, SUBTREE_T = 256;
+__global__ void __launch_bounds__(SUBTREE_T) k_merkle_subtrees(const uint32_t* __restrict__ leaves, const uint32_t* __restrict__ salts, u32 nn,
+                                                               const uint32_t* __restrict__ leaf_key, const uint32_t* __restrict__ node_key,
+                                                               uint32_t* __restrict__ levels) {
+    __shared__ uint4 buf[2][SUBTREE][2];  // two levels of 32-byte nodes
+    const u32 first = blockIdx.x * SUBTREE;
+    for (u32 t = threadIdx.x; t < SUBTREE; t += SUBTREE_T) {
+        const uint4* pl = reinterpret_cast<const uint4*>(leaves + (size_t)(first + t) * 8);
+        uint4 a = pl[0], b = pl[1];
+        if (salts) {
+            const uint4* ps = reinterpret_cast<const uint4*>(salts + (size_t)(first + t) * 8);
+            const uint4 z = ps[0], w = ps[1];
+            uint32_t m[16] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w, z.x, z.y, z.z, z.w, w.x, w.y, w.z, w.w}, out[8];
+            b3::hash64(out, m, leaf_key);
+            a = make_uint4(out[0], out[1], out[2], out[3]);
+            b = make_uint4(out[4], out[5], out[6], out[7]);
+        }
+        buf[0][t][0] = a; buf[0][t][1] = b;
+        uint4* pd = reinterpret_cast<uint4*>(levels + (size_t)(first + t) * 8);
+        pd[0] = a; pd[1] = b;
+    }
+    __syncthreads();
+    size_t off = (size_t)nn * 8;  // words before the level being written
+    u32 cur = 0, level_w = nn >> 1;
+    for (u32 w = SUBTREE >> 1; w >= 1; w >>= 1) {
+        for (u32 j = threadIdx.x; j < w; j += SUBTREE_T) {
+            const uint4 x = buf[cur][2 * j][0], y = buf[cur][2 * j][1], z = buf[cur][2 * j + 1][0], v = buf[cur][2 * j + 1][1];
+            uint32_t m[16] = {x.x, x.y, x.z, x.w, y.x, y.y, y.z, y.w, z.x, z.y, z.z, z.w, v.x, v.y, v.z, v.w}, out[8];
+            b3::hash64(out, m, node_key);
+            const uint4 a = make_uint4(out[0], out[1], out[2], out[3]), b = make_uint4(out[4], out[5], out[6], out[7]);
+            buf[cur ^ 1][j][0] = a; buf[cur ^ 1][j][1] = b;
+            uint4* pd = reinterpret_cast<uint4*>(levels + off + ((size_t)blockIdx.x * w + j) * 8);
+            pd[0] = a; pd[1] = b;
+        }
+        __syncthreads();
+        off += (size_t)level_w * 8;
+        level_w >>= 1;
+        cur ^= 1;
+    }
+}
+
 }  // namespace
 
 namespace hlk {
+
+// salted leaves (salts may be NULL: the leaves are the lowest level as they are) and every level above them
+cudaError_t merkle_tree(const uint32_t* d_leaves, const uint32_t* d_salts, u32 nn, const uint32_t* d_leaf_key, const uint32_t* d_node_key,
+                        uint32_t* d_levels, cudaStream_t st, int* launches) {
+    if (nn >= 2 * SUBTREE && nn / SUBTREE <= 2048) {
+        k_merkle_subtrees<<<nn / SUBTREE, SUBTREE_T, 0, st>>>(d_leaves, d_salts, nn, d_leaf_key, d_node_key, d_levels);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+        size_t off = 0;  // words before the level of the subtree roots
+        for (u32 w = nn; w > nn / SUBTREE; w >>= 1) off += (size_t)w * 8;
+        k_merkle_top<<<1, 1024, 0, st>>>(d_levels, off, nn / SUBTREE, d_node_key);
+        *launches = 2;
+        return cudaGetLastError();
+    }
+    cudaError_t e = d_salts ? salt_leaves(d_leaves, d_salts, nn, d_leaf_key, d_levels, st)
+                            : cudaMemcpyAsync(d_levels, d_leaves, (size_t)nn * 32, cudaMemcpyDeviceToDevice, st);
+    *launches = d_salts ? 1 : 0;
+    if (e != cudaSuccess) return e;
+    for (u32 w = nn; w > 2048; w >>= 1) (*launches)++;
+    if (nn > 1) (*launches)++;
+    return merkle_levels(d_levels, nn, d_node_key, st);
+}
 
 u32 hash_chunks(u32 rows) { return (rows + 127u) / 128u; }
 

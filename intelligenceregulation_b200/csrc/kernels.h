@@ -22,6 +22,8 @@ cudaError_t hash_columns(const u64* enc, u32 rows, u32 nn, const uint32_t* d_key
 cudaError_t salt_leaves(const uint32_t* d_leaves, const uint32_t* d_salts, u32 nn, const uint32_t* d_leaf_key,
                         uint32_t* d_out, cudaStream_t st);
 cudaError_t merkle_levels(uint32_t* d_levels, u32 nn, const uint32_t* d_node_key, cudaStream_t st);
+cudaError_t merkle_tree(const uint32_t* d_leaves, const uint32_t* d_salts, u32 nn, const uint32_t* d_leaf_key, const uint32_t* d_node_key,
+                        uint32_t* d_levels, cudaStream_t st, int* launches);
 
 // store.cu
 // out[g] = rho_g^T [src | src2]: ncols entries from src (element (i, j) at src[i ld + j ir]), then ncols2 from src2 (may be NULL)
