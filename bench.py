@@ -580,13 +580,12 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     e2e_parts = [0.0, 0.0, 0.0]  # this rank's wall time in the commitment call, the tree call, the exchange of roots
 
     # the caller's result buffers, page-locked like its inputs
-    np_leaves = torch.empty(nn * 32, dtype=torch.uint8).pin_memory().numpy().reshape(nn, 32)
     np_levels = torch.empty((2 * nn - 1) * 32, dtype=torch.uint8).pin_memory().numpy().reshape(2 * nn - 1, 32)
 
     def step_e2e():
         t0 = time.perf_counter()
         st, leaves, levels = dev.try_commit_zk_tree(log_cols, ir, np_data, np_pads, np_pows, log_cols + 1, col_key, np_salts.reshape(nn, 32), leaf_key,
-                                                    node_key, leaves_out=np_leaves, levels_out=np_levels)
+                                                    node_key, levels_out=np_levels, want_leaves=False)
         t1 = time.perf_counter()
         st.free()
         t2 = time.perf_counter()

@@ -93,7 +93,8 @@ int hl_b200_commit_zk(hl_ctx* ctx, uint32_t log_cols, uint32_t inv_rate, const u
 
 /* hl_b200_commit_zk and hl_b200_store_merkle in one call: commit_zk_owned_with_tag (pcs.rs:782-817) has drawn the salts before it
  * offers the commitment, so they travel with the rows, the salted tree follows the column hash on the device, and leaves32
- * (nn x 32, unsalted) and levels_out ((2 nn - 1) x 32) come back under one synchronisation. */
+ * (nn x 32, unsalted; may be NULL: the salted leaves are the first nn entries of levels_out) and levels_out ((2 nn - 1) x 32) come
+ * back under one synchronisation. */
 int hl_b200_commit_zk_tree(hl_ctx* ctx, uint32_t log_cols, uint32_t inv_rate, const uint64_t* data, size_t rows, const uint64_t* pads, size_t q,
                            const uint64_t* pows, uint32_t max_log, const uint8_t* key32, const uint8_t* salts32, const uint8_t* leaf_key32,
                            const uint8_t* node_key32, hl_store** store, uint8_t* leaves32, uint8_t* levels_out);

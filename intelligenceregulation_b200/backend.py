@@ -350,16 +350,17 @@ class B200Backend:
         return B200Commit(self.ctx, h), leaves
 
     def try_commit_zk_tree(self, log_cols: int, inv_rate: int, data, pads, pows, max_log: int, key: Optional[bytes], salts, leaf_key: Optional[bytes],
-                           node_key: Optional[bytes], leaves_out: Optional[np.ndarray] = None, levels_out: Optional[np.ndarray] = None):
+                           node_key: Optional[bytes], leaves_out: Optional[np.ndarray] = None, levels_out: Optional[np.ndarray] = None,
+                           want_leaves: bool = True):
         """The commitment and its salted tree in one call (pcs.rs:782-817: the salts are drawn before the commitment is offered):
-        (store, leaves, levels) or None on a decline."""
+        (store, leaves, levels) or None on a decline.  want_leaves False: the unsalted leaves stay on the device (leaves is None)."""
         data, pads, pows = _u64(data), _u64(pads), _u64(pows)
         salts = np.ascontiguousarray(salts, dtype=np.uint8)
         rows, nn = data.size >> log_cols, inv_rate << log_cols
         q = pads.size // rows if rows else 0
-        leaves = leaves_out if leaves_out is not None else np.empty((nn, 32), dtype=np.uint8)
+        leaves = None if not want_leaves else leaves_out if leaves_out is not None else np.empty((nn, 32), dtype=np.uint8)
         levels = levels_out if levels_out is not None else np.empty((2 * nn - 1, 32), dtype=np.uint8)
-        assert leaves.size == nn * 32 and levels.size == (2 * nn - 1) * 32 and salts.size == nn * 32
+        assert (leaves is None or leaves.size == nn * 32) and levels.size == (2 * nn - 1) * 32 and salts.size == nn * 32
         h = C.c_void_p()
         rc = self.ctx.lib.hl_b200_commit_zk_tree(self.ctx.h, log_cols, inv_rate, _ptr(data), rows, _ptr(pads), q, _ptr(pows), max_log, _ptr(key),
                                                   _ptr(salts), _ptr(leaf_key), _ptr(node_key), C.byref(h), _ptr(leaves), _ptr(levels))

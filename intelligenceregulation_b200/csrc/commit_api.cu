@@ -169,7 +169,7 @@ int commit_host(hl_ctx* c, const Shape& s, const uint64_t* data, const uint64_t*
     if (!rc && s.zk) rc = h2d(c, d_pows, pows, nn * 8);
     if (!rc) rc = commit_on_device(c, st, d_pows, key32, data);
     if (!rc && tree) rc = merkle_on_device(c, st->d_leaves, d_salts, nn, tree->leaf_key32, tree->node_key32, d_levels);
-    if (!rc) rc = d2h(c, leaves32, st->d_leaves, nn * 32);
+    if (!rc && leaves32) rc = d2h(c, leaves32, st->d_leaves, nn * 32);
     if (!rc && tree) rc = d2h(c, tree->levels_out, d_levels, (2 * nn - 1) * 32);
     if (!rc) rc = sync(c, "commit");
     if (!rc && tree) c->stats.merkles++;
@@ -214,7 +214,7 @@ int hl_b200_commit_zk(hl_ctx* c, uint32_t log_cols, uint32_t inv_rate, const uin
 int hl_b200_commit_zk_tree(hl_ctx* c, uint32_t log_cols, uint32_t inv_rate, const uint64_t* data, size_t rows, const uint64_t* pads, size_t q,
                            const uint64_t* pows, uint32_t max_log, const uint8_t* key32, const uint8_t* salts32, const uint8_t* leaf_key32,
                            const uint8_t* node_key32, hl_store** store, uint8_t* leaves32, uint8_t* levels_out) {
-    if (!c || !data || !pads || !pows || !salts32 || !store || !leaves32 || !levels_out) return fail(c, HL_B200_ERR_ARG, "commit_zk_tree: null argument");
+    if (!c || !data || !pads || !pows || !salts32 || !store || !levels_out) return fail(c, HL_B200_ERR_ARG, "commit_zk_tree: null argument");
     std::lock_guard<std::mutex> g(c->mu);
     cudaSetDevice(c->device);
     Shape s;

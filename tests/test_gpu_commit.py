@@ -123,6 +123,10 @@ def test_m1_zk_commit_and_opening_bytes_match_the_cpu(dev, oracle, keyed, fast):
         st2, leaves2, levels2 = dev.try_commit_zk_tree(log_cols, ir, data, pads, o.coset_powers(7, nn), 16, tag.column, salts, tag.leaf, tag.node)
         assert (leaves2 == cpu.leaves).all() and (levels2 == cpu.levels).all()
         st2.free()
+        st3, none, levels3 = dev.try_commit_zk_tree(log_cols, ir, data, pads, o.coset_powers(7, nn), 16, tag.column, salts, tag.leaf, tag.node,
+                                                    want_leaves=False)
+        assert none is None and (levels3 == cpu.levels).all()
+        st3.free()
         for c in (cpu,):
             c.mask_rows, c.prox_mask_row = [rows - 3, rows - 2], rows - 1
         cl = _claims(o, rows, log_cols, 900 + si)
