@@ -91,6 +91,8 @@ int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* 
             a.pows = d_pows; a.tw_nn = tw; a.enc = st->d_enc + (size_t)r0 * nn; a.scratch = scratch;
             a.rows = nr; a.q = st->zk ? st->q : 0; a.T = T; a.logr = st->logr + loga; a.loga = loga; a.zk = st->zk ? 1 : 0;
             a.ninv = gl_inv((u64)n); a.coef_out = nullptr;
+            // a handful of rows (a boundary commitment, the last piece of an upload): one CTA per (row, residue)
+            a.split = (loga == 0 && st->logr >= 1 && ((u64)nr << st->logr) <= (u64)c->sm_count) ? 1 : 0;
             cudaError_t e = hlk::encode_rows(a, logb, c->fast_encoder || loga, c->sm_count, scratch_words, c->stream, &st->encoder_path);
             c->stats.kernel_launches += 1;
             if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "row encoder launch", e);

@@ -45,6 +45,16 @@ __global__ void __launch_bounds__(THREADS) k_encode_fast(enc::RowArgs a) {
     u64* X = a.scratch + (size_t)blockIdx.x * a.T * F::N;
     F::load_twiddles(a, TW, tid, THREADS);
     __syncthreads();
+    if (a.split) {
+        for (u32 unit = blockIdx.x; unit < (a.rows << a.logr); unit += gridDim.x) {
+            const u32 row = unit >> a.logr, s = unit & ((1u << a.logr) - 1u);
+            F::template row_coeffs<CtaSync, FORM>(a, row, S, TW, X, tid, THREADS, CtaSync());
+            __syncthreads();
+            F::row_residue(a, row, s, S, TW, X, tid, THREADS, CtaSync());
+            __syncthreads();
+        }
+        return;
+    }
     for (u32 row = blockIdx.x; row < a.rows; row += gridDim.x) {
         F::template row_coeffs<CtaSync, FORM>(a, row, S, TW, X, tid, THREADS, CtaSync());
         __syncthreads();  // the scratch slot is complete and shared memory is free again
@@ -74,7 +84,8 @@ cudaError_t launch_fast(const enc::RowArgs& a, int sm_count, size_t scratch_word
     if (e != cudaSuccess) return e;
     if (per_sm < 1) per_sm = 1;
     size_t grid = (size_t)sm_count * per_sm;
-    if (grid > a.rows) grid = a.rows;
+    const size_t units = a.split ? (size_t)a.rows << a.logr : (size_t)a.rows;
+    if (grid > units) grid = units;
     size_t max_by_scratch = scratch_words / ((size_t)a.T * F::N);
     if (grid > max_by_scratch) grid = max_by_scratch;
     if (grid < 1) return cudaErrorInvalidValue;
@@ -88,9 +99,11 @@ cudaError_t launch_fast(const enc::RowArgs& a, int sm_count, size_t scratch_word
 namespace hlk {
 
 size_t encode_scratch_words(u32 logn, u32 T, int sm_count, u32 rows) {
-    // enough for the largest grid any path launches: 32 CTAs per SM at most
+    // enough for the largest grid any path launches: 32 CTAs per SM at most, one per row (or, for a handful of rows, one per
+    // (row, residue): at most one CTA per SM then)
     size_t ctas = (size_t)sm_count * 32;
-    if (ctas > rows) ctas = rows;
+    if (ctas > rows && rows >= (u32)sm_count) ctas = rows;
+    if (rows < (u32)sm_count) ctas = (size_t)sm_count;
     return ctas * T * ((size_t)1 << logn);
 }
 

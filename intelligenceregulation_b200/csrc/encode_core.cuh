@@ -56,6 +56,8 @@ struct RowArgs {
     int zk;
     u64 ninv;          // n^-1
     u64* coef_out;     // FORM_COSET only: the row's n coefficients, in rows of 2n words (or NULL)
+    int split;         // fast path: a CTA takes one (row, output residue) instead of a whole row, repeating the row's inverse transform:
+                       // for a handful of rows (fewer than SMs / residues) the latency of a row falls from 1 + R transforms to 2
 };
 
 // What a row is and how its coefficients are twisted (template argument of Fast::row_coeffs).

@@ -157,7 +157,7 @@ int hl_b200_mask_commit(hl_ctx* c, uint32_t log_msg, uint32_t log_dom, const uin
     if (!rc) {
         Timed t(c, HL_T_ENCODE);
         enc::RowArgs a;
-        a.pads = nullptr; a.pows = d_pows; a.tw_nn = tw; a.scratch = scratch; a.loga = 0; a.zk = 0;
+        a.pads = nullptr; a.pows = d_pows; a.tw_nn = tw; a.scratch = scratch; a.loga = 0; a.zk = 0; a.split = 0;
         a.ninv = gl_inv((u64)m);
         // message rows: m evaluations -> coefficients (kept) -> the coset
         a.data = d_msgs; a.enc = st->d_enc; a.rows = (u32)n_msg_rows; a.q = 0; a.T = 1; a.logr = log_dom - log_msg; a.coef_out = st->d_data;

@@ -41,7 +41,7 @@ extern "C" int emul_encode(int fast, const u64* data, u32 rows, u32 logn, u32 lo
     a.data = data; a.pads = pads; a.pows = pows; a.tw_nn = tw.data(); a.enc = out;
     a.rows = rows; a.q = zk ? q : 0; a.logr = logr + loga; a.loga = loga; a.zk = zk;
     a.T = zk ? (n + q + nb - 1) / nb : n / nb;
-    a.ninv = gl_inv(n); a.coef_out = nullptr;
+    a.ninv = gl_inv(n); a.coef_out = nullptr; a.split = 0;
     std::vector<u64> X((size_t)a.T * nb, 0xA5A5A5A5A5A5A5A5ULL);  // poisoned: unwritten words must never be read
     a.scratch = X.data();
     if (fast) {
