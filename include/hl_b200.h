@@ -288,7 +288,8 @@ int hl_b200_act_table(hl_ctx* ctx, const int64_t* tables, size_t groups, size_t 
  * *taken = 0 (and HL_B200_OK) when the CPU must take the product: an activation outside int16, or a shape outside
  * inner <= 65,536, xs >= inner, os >= outer, the rows inside x_len / out_len, inner * outer <= w_len.
  * The _dev form takes device pointers (weights resident in HBM across requests) and is asynchronous up to its own flag read. */
-/* the int8 m16n8k32 tensor-core instruction of the product kernel, register resident on every SM: multiply-adds per second */
+/* a yardstick for the witness products: the warp-level int8 tensor-core instruction (mma.sync m16n8k32, the path the product kernel
+ * does NOT use) register resident on every SM, in multiply-adds per second */
 int hl_b200_mma_i8_peak(hl_ctx* ctx, uint32_t iters, double* macs_per_second);
 int hl_b200_witness_product(hl_ctx* ctx, size_t t_rows, const int64_t* x, size_t x_len, size_t xs, const int8_t* w, size_t w_len, size_t inner,
                             size_t outer, size_t os, size_t out_len, int in_out, int64_t* out, int* taken);

@@ -160,7 +160,7 @@ class Context:
         return comp, ht
 
     def mma_i8_peak(self, iters: int = 2000) -> float:
-        """int8 tensor-core multiply-adds per second of the product kernel's instruction, register resident."""
+        """int8 multiply-adds per second of the warp-level tensor-core instruction (mma.sync), register resident: a yardstick for the products."""
         v = C.c_double()
         self.check(self.lib.hl_b200_mma_i8_peak(self.h, iters, C.byref(v)))
         return v.value

@@ -253,8 +253,9 @@ __global__ void __launch_bounds__(UM_THREADS, 1) k_wp_umma(const __grid_constant
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512u));
 }
 
-// Register-resident int8 tensor-core products: the ceiling of the m16n8k32 instruction the product kernel issues (16
-// independent accumulators per warp, 8 warps per CTA, 2 CTAs per SM, operands never reloaded).
+// A yardstick, not a product path: the warp-level int8 tensor-core instruction (mma.sync m16n8k32) issued register resident, 16
+// independent accumulators per warp, 8 warps per CTA, 2 CTAs per SM.  The first form of the product kernel was built on it and
+// reached a fifth of this rate; the tcgen05 kernel above is compared with it in the bench.
 __global__ void __launch_bounds__(256, 2) k_mma_i8_peak(u32 iters, int* __restrict__ sink) {
     int acc[4][4][4];
     u32 a[4][4], b[4][2];
