@@ -182,6 +182,10 @@ void hl_b200_shutdown(hl_ctx* c) {
     cudaStreamSynchronize(c->stream);
     for (auto& kv : c->tw) cudaFree(kv.second);
     if (c->d_wp_flag) cudaFree(c->d_wp_flag);
+    for (int i = 0; i < 2; i++) {
+        if (c->stage[i]) cudaFreeHost(c->stage[i]);
+        if (c->stage_ev[i]) cudaEventDestroy(c->stage_ev[i]);
+    }
     for (auto& s : c->spans) { cudaEventDestroy(s.a); cudaEventDestroy(s.b); }
     for (auto e : c->ev_pool) cudaEventDestroy(e);
     for (auto e : c->ev_chunks) cudaEventDestroy(e);

@@ -28,6 +28,9 @@ struct hl_ctx {
     std::vector<Span> spans;          // recorded, not yet read
     std::vector<cudaEvent_t> ev_pool;  // events ready for reuse
     hl_timing timing_acc{};
+    void* stage[2] = {nullptr, nullptr};       // page-locked staging for uploads from pageable host memory (lazily allocated)
+    size_t stage_bytes = 0;
+    cudaEvent_t stage_ev[2] = {nullptr, nullptr};  // the copy out of stage[i] has completed
     int* d_wp_flag = nullptr;  // the witness products' status word: zero between calls
     bool wp_attr = false;      // the product kernel's shared-memory size has been raised on this device
     size_t alloc_live = 0;   // bytes handed out and not yet returned

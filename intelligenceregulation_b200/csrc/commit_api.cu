@@ -1,4 +1,7 @@
 // C ABI: commitments (Backend::try_commit*), stores (EncodedStore), Merkle trees.
+#include <cstring>
+#include <thread>
+
 #include "api_internal.h"
 
 using namespace hlapi;
@@ -62,6 +65,28 @@ int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* 
         if (e == cudaSuccess) e = cudaStreamWaitEvent(c->copy_stream, c->ev_main, 0);
         if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "stream ordering", e);
     }
+    // Rows in ordinary pageable memory: the driver would stage them through its own buffer at about 10 GB/s, so the pieces go
+    // through two page-locked buffers of the context instead, filled by a few host threads while the previous piece is on the bus.
+    bool staged = false;
+    if (!rc && pieces) {
+        cudaPointerAttributes attr;
+        const bool pageable = cudaPointerGetAttributes(&attr, h_data) != cudaSuccess || attr.type == cudaMemoryTypeUnregistered;
+        cudaGetLastError();  // an unregistered pointer is not an error here
+        const size_t need = (size_t)chunk * row_bytes;
+        if (pageable) {
+            staged = true;
+            if (c->stage_bytes < need) {
+                for (int i = 0; i < 2; i++) {
+                    if (c->stage[i]) { cudaFreeHost(c->stage[i]); c->stage[i] = nullptr; }
+                    if (cudaHostAlloc(&c->stage[i], need, cudaHostAllocDefault) != cudaSuccess) { c->stage[i] = nullptr; staged = false; }
+                    if (!c->stage_ev[i] && cudaEventCreateWithFlags(&c->stage_ev[i], cudaEventDisableTiming) != cudaSuccess) staged = false;
+                }
+                c->stage_bytes = staged ? need : 0;
+                cudaGetLastError();
+            }
+        }
+    }
+    size_t piece_i = 0;
     if (!rc) {
         Timed t(c, HL_T_ENCODE);
         size_t ev_i = 0;
@@ -71,7 +96,22 @@ int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* 
             if (pieces && r0 + nr == st->rows && nr > 128 && nr > (u32)c->sm_count) nr = 128;  // leave one wave or less for the end
             if (h_data) {
                 cudaStream_t cs = chunk < st->rows ? c->copy_stream : c->stream;
-                cudaError_t e = cudaMemcpyAsync(st->d_data + (size_t)r0 * n, h_data + (size_t)r0 * n, (size_t)nr * row_bytes, cudaMemcpyHostToDevice, cs);
+                const void* from = h_data + (size_t)r0 * n;
+                if (staged) {
+                    const int b = (int)(piece_i++ & 1);
+                    if (piece_i > 2) cudaEventSynchronize(c->stage_ev[b]);  // the copy that last read this buffer is done
+                    const size_t bytes = (size_t)nr * row_bytes;
+                    const unsigned hw = std::thread::hardware_concurrency();
+                    const int nth = bytes >= ((size_t)8 << 20) ? (int)(hw >= 8 ? 8 : hw >= 2 ? hw : 1) : 1;
+                    std::vector<std::thread> th;
+                    for (int k = 1; k < nth; k++)
+                        th.emplace_back([=] { memcpy((char*)c->stage[b] + bytes * k / nth, (const char*)from + bytes * k / nth, bytes * (k + 1) / nth - bytes * k / nth); });
+                    memcpy(c->stage[b], from, bytes / nth);
+                    for (auto& x : th) x.join();
+                    from = c->stage[b];
+                }
+                cudaError_t e = cudaMemcpyAsync(st->d_data + (size_t)r0 * n, from, (size_t)nr * row_bytes, cudaMemcpyHostToDevice, cs);
+                if (staged && e == cudaSuccess) e = cudaEventRecord(c->stage_ev[(piece_i - 1) & 1], cs);
                 c->stats.bytes_h2d += (size_t)nr * row_bytes;
                 if (e == cudaSuccess && cs != c->stream) {
                     if (ev_i == c->ev_chunks.size()) {

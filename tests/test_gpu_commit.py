@@ -364,3 +364,33 @@ def test_verifier_encodes_the_clear_vectors_through_the_commit_entry(dev, oracle
         eim = o.encode_row_zk(heads[nvec + g], tails[nvec + g], pows, log_cols + 1)
         assert (cols[:, g] == ere[idx.astype(np.int64)]).all() and (cols[:, nvec + g] == eim[idx.astype(np.int64)]).all()
     store.free()
+
+
+def test_rows_from_pageable_and_from_page_locked_memory_give_the_same_commitment(dev, oracle):
+    """A large commitment is uploaded in pieces; rows in ordinary pageable memory go through the context's staging buffers (filled by
+    host threads), rows in page-locked memory are copied directly, rows already on the device are not copied: one commitment."""
+    import torch
+
+    o = oracle
+    log_cols, ir, q, rows = 14, 2, 280, 640
+    n, nn = 1 << log_cols, (1 << log_cols) * ir
+    data = rnd(4242, rows * n)
+    pads, pows = rnd(4243, rows * q), o.coset_powers(7, nn)
+    a = dev.try_commit_zk_keyed(log_cols, ir, data, pads, pows, log_cols + 1, None)
+    pinned = torch.from_numpy(data.view(np.int64)).pin_memory().numpy().view(np.uint64)
+    b = dev.try_commit_zk_keyed(log_cols, ir, pinned, pads, pows, log_cols + 1, None)
+    assert a is not None and b is not None and (a[1] == b[1]).all()
+    d_data, d_pads, d_pows = (torch.from_numpy(x.view(np.int64)).cuda() for x in (data, pads, pows))
+    d_leaves = torch.empty(nn * 32, dtype=torch.uint8, device="cuda")
+    torch.cuda.synchronize()
+    st = dev.commit_zk_dev(log_cols, ir, d_data.data_ptr(), rows, d_pads.data_ptr(), q, d_pows.data_ptr(), None, d_leaves.data_ptr())
+    dev.ctx.sync()
+    assert (d_leaves.cpu().numpy().reshape(nn, 32) == a[1]).all()
+    # and the rows themselves: three sampled rows against the CPU encoder, through the opened columns of the first commitment
+    idx = np.arange(0, nn, 997, dtype=np.uint64)
+    cols = a[0].columns(idx)
+    for r in (0, 255, 639):
+        enc = o.encode_row_zk(data[r * n:(r + 1) * n], pads[r * q:(r + 1) * q], pows, log_cols + 1)
+        assert (cols[:, r] == enc[idx.astype(np.int64)]).all()
+    for x in (a[0], b[0], st):
+        x.free()
