@@ -266,6 +266,14 @@ class Transcript:
         self.key = key
         _lib.or_tr_new(C.byref(self._t), domain, C.c_size_t(len(domain)), _p(key) if key else None)
 
+    @staticmethod
+    def from_state(state: bytes, counter: int, key: Optional[bytes] = None) -> "Transcript":
+        """a transcript resumed at a recorded (state, squeeze counter), as the reference's `Transcript::clone_state` leaves one"""
+        t = Transcript(b"", key)
+        C.memmove(t._t.state, state, 32)
+        t._t.counter = counter
+        return t
+
     def clone(self) -> "Transcript":
         t = Transcript.__new__(Transcript)
         t._t = _TrStruct()

@@ -468,3 +468,142 @@ def test_l6_whole_sumchecks_prover_and_verifier(oracle, l6):
             assert (out2.rounds == out.rounds).all() and t2.state == tp.state
         honest += 1
     assert honest == 15 and verdicts >= 171
+
+
+# ----------------------------------------------------------------------------- L11: the slots of a real W16R2 block core
+@pytest.fixture(scope="module")
+def l11(golden_dir):
+    import l11_util
+
+    return l11_util.load(golden_dir)
+
+
+def _eq_point(o, point, s):
+    """mle.rs:62-71"""
+    acc = (1, 0)
+    for a, b in zip(point, s):
+        t = o.fp2_add(o.fp2_mul(a, b), o.fp2_mul(o.fp2_sub((1, 0), a), o.fp2_sub((1, 0), b)))
+        acc = o.fp2_mul(acc, t)
+    return acc
+
+
+def test_l11_head_replays_to_the_logup_challenges(oracle, l11):
+    """`verify_core`'s head (protocol.rs:2827-2837) from the recorded header state: absorb the `A` root, `M`, draw beta,
+    gamma, alpha, absorb the `H` root; the tag constants are gamma times the table tags."""
+    o, h = oracle, l11["head"]
+    r = h["roots"]
+    tr = o.Transcript.from_state(*h["head"], key=h["key"])
+    for label, root, rows in ((b"A", r["a_root"], r["a_rows"]),):
+        tr.absorb(label, root)
+        tr.absorb_u64(b"rows", rows)
+        tr.absorb_u64(b"log-cols", r["log_cols"])
+    tr.absorb(b"M", r["mask_root"])
+    assert tr.challenge_fp2() == h["beta"]
+    gamma = tr.challenge_fp2()
+    assert gamma == h["gamma"]
+    assert tr.challenge_fp2() == h["alpha"]
+    tr.absorb(b"H", r["h_root"])
+    tr.absorb_u64(b"rows", r["h_rows"])
+    tr.absorb_u64(b"log-cols", r["log_cols"])
+    assert (tr.state, tr.counter) == h["headend"]
+    # the three tags are gamma times the table tags (tables_attn.rs:49,70,77: TAG_EXP 129, TAG_U8 133, TAG_ACT 134)
+    for name, tag in (("g_u8", 133), ("g_exp", 129), ("g_act", 134)):
+        assert o.fp2_mul_base(gamma, tag) == h[name]
+
+
+def test_l11_slot_graphs_evaluate_to_the_reference_value(oracle, l11):
+    """Every slot's expression graph, WITH the recorded coefficient values, evaluated at the recorded terminal values by
+    the oracle's interpreter and by the independent Python walk: the reference's own `poly(vals)` (slot_ir.rs:352-377,
+    the `ir.eval(&vals) == (def.poly)(&vals)` assertion of lean_l11_export_tests.rs:243)."""
+    from intelligenceregulation_b200 import backend
+    import ir_util
+    import l11_util
+
+    o = oracle
+    for s in l11["slots"]:
+        assert len(s["vals"]) == s["n_tabs"] == s["ir_counts"][0] == len(s["tabs"])
+        prog, desc = l11_util.build_program(backend, s)
+        assert ir_util.py_eval(desc, s["vals"]) == s["pv"], s["slot"]
+        cf = prog.coef_array()
+        o.ir_set(prog.words(), prog.n_nodes, prog.n_terms)
+        assert o.poly_eval(o.POLY_IR, np.array(s["vals"], dtype=np.uint64), cf if cf.size else None) == s["pv"], s["slot"]
+
+
+def test_l11_verify_arm_of_every_slot(oracle, l11):
+    """`run_slot`'s VERIFY arm (argument.rs:1434-1468) recomputed from the recorded proof: the slot challenge `c`, the claimed
+    sum with its hosted terms, the sumcheck verifier through every recorded round to `fin` and `rho`, the terminal values of
+    eq tables (`sel * eq_point`) and public tables (`sel * mle(pub)(rho)`), the mask value `g = (fin - poly(vals)) / c`, the
+    transcript state after `pb-term`; and the chain between slots (a definition only squeezes)."""
+    o, key = oracle, l11["head"]["key"]
+    scalars = []
+    prev = l11["head"]["headend"]
+    for s in l11["slots"]:
+        # the definition's draws: squeezes only, from where the previous slot (or the head) ended
+        tr = o.Transcript.from_state(*prev, key=key)
+        assert [tr.challenge_fp2() for _ in s["draws"]] == s["draws"]
+        assert (tr.state, tr.counter) == s["trb"]
+        n, ext, deg = s["n"], s["ext"], s["degree"]
+        tr.absorb_u64(b"pb-slot", s["slot"])
+        c = tr.challenge_fp2()
+        assert c == s["c"]
+        tr.absorb_fp2(b"pb-scalar", np.array([s["scalar"]], dtype=np.uint64))
+        claimed = s["scalar"]
+        for hs, coef in s["hosted"]:
+            claimed = o.fp2_add(claimed, o.fp2_mul(coef, scalars[hs]))
+        assert claimed == s["claimed"]
+        rounds = [np.array(r, dtype=np.uint64) for r in s["rounds"]]
+        got, err = o.sc_verify(claimed, deg, n + ext, rounds, tr)
+        assert err is None, (s["slot"], err)
+        fin, rho_full = got
+        assert fin == s["fin"] and [tuple(map(int, r)) for r in rho_full] == s["rho_full"]
+        rho, es = s["rho_full"][:n], s["rho_full"][n:]
+        sel = (1, 0)
+        for e in es:
+            sel = o.fp2_mul(sel, o.fp2_sub((1, 0), e))
+        k = 0
+        for i, t in enumerate(s["tabs"]):
+            if t[0] == "eq":
+                want = o.fp2_mul(sel, _eq_point(o, t[2], rho[t[1]:t[1] + len(t[2])]))
+            elif t[0] == "pub":
+                assert len(t[2]) == t[1] == 1 << n
+                want = o.fp2_mul(sel, o.eval_mle_ext(np.array(t[2], dtype=np.uint64), np.array(rho, dtype=np.uint64)))
+            elif t[0] == "pubv":
+                want = o.fp2_mul(sel, t[2])
+            else:
+                assert t[1] == k
+                want = s["terms_vals"][k]
+                k += 1
+            assert want == s["vals"][i], (s["slot"], i, t[0])
+        assert k == s["n_priv"] == len(s["terms_vals"])
+        assert o.fp2_mul(o.fp2_sub(fin, s["pv"]), o.fp2_inv(c)) == s["g"]
+        tr.absorb_fp2(b"pb-term", np.array(s["terms_vals"], dtype=np.uint64).reshape(-1, 2))
+        assert (tr.state, tr.counter) == s["tra"], s["slot"]
+        scalars.append(s["scalar"])
+        prev = s["tra"]
+
+
+def test_l11_lookup_denominator_rule(oracle, l11):
+    """The table-indexed helper rule of protocol.rs:1125-1230 as the slot graphs record it with real values: a helper
+    constraint's affine node is `alpha - (word + cst + g_tag)` (konst `alpha - (cst + g_tag)`, coefficient -1 on the looked
+    word, `cst` a small integer offset), and the oracle's inverse table holds `1 / (alpha - (v + g_tag))` at `v = word + cst`.
+    For every such node of the corpus, inverting the node's value at a word reproduces the oracle's table entry."""
+    o, h = oracle, l11["head"]
+    seen = {}
+    for s in l11["slots"]:
+        for n in s["nodes"]:
+            if n[0] != "affine" or len(n[2]) != 1 or n[2][0][0][0] != (P - 1, 0):
+                continue
+            konst = n[1][0]
+            for tag in ("g_u8", "g_exp", "g_act"):
+                cst = o.fp2_sub(o.fp2_sub(h["alpha"], h[tag]), konst)
+                if cst[1] != 0 or not (cst[0] < 4096 or P - cst[0] < 4096):
+                    continue
+                off = cst[0] if cst[0] < 4096 else cst[0] - P
+                tab, absent = o.lookup_inverse_table(h["alpha"], h[tag], 8192)
+                for word in (0, 1, 77, 255, 4000):
+                    if not 0 <= word + off < 8192:
+                        continue
+                    den = o.fp2_sub(konst, (word, 0))
+                    assert not absent[word + off] and tuple(map(int, tab[word + off])) == o.fp2_inv(den)
+                seen[tag] = seen.get(tag, 0) + 1
+    assert seen.get("g_u8", 0) > 0, seen
