@@ -14,6 +14,7 @@ int fail(hl_ctx* c, int code, const char* what, cudaError_t e) {
         char buf[512];
         if (e != cudaSuccess) snprintf(buf, sizeof buf, "%s: %s", what, cudaGetErrorString(e));
         else snprintf(buf, sizeof buf, "%s", what);
+        std::lock_guard<std::mutex> g(c->err_mu);
         c->last_error = buf;
         c->stats.declines++;
     }
@@ -48,6 +49,34 @@ int h2d(hl_ctx* c, void* d, const void* h, size_t bytes) {
     if (e != cudaSuccess) return fail(c, HL_B200_ERR_DEVICE, "copy to device", e);
     c->stats.bytes_h2d += bytes;
     return HL_B200_OK;
+}
+
+// An asynchronous copy out of page-locked caller memory reads the source when the DMA runs, not when the call is made: a call
+// that returns without synchronising would let the caller overwrite inputs that are still to be read.  Small inputs are
+// bounced through a page-locked area of the context (reused after a synchronisation when it wraps); large ones are copied
+// in place and waited for.
+constexpr size_t ARENA_BYTES = (size_t)4 << 20;
+int h2d_owned(hl_ctx* c, void* d, const void* h, size_t bytes) {
+    if (!bytes) return HL_B200_OK;
+    if (!c->arena && cudaHostAlloc((void**)&c->arena, ARENA_BYTES, cudaHostAllocDefault) != cudaSuccess) {
+        cudaGetLastError();
+        c->arena = nullptr;
+    }
+    if (c->arena && bytes <= ARENA_BYTES / 4) {
+        const size_t need = (bytes + 63) & ~(size_t)63;
+        if (c->arena_off + need > ARENA_BYTES) {
+            cudaError_t e = cudaStreamSynchronize(c->stream);
+            if (e != cudaSuccess) return fail(c, HL_B200_ERR_DEVICE, "staging area", e);
+            c->arena_off = 0;
+        }
+        char* slot = c->arena + c->arena_off;
+        c->arena_off += need;
+        memcpy(slot, h, bytes);
+        return h2d(c, d, slot, bytes);
+    }
+    int rc = h2d(c, d, h, bytes);
+    if (!rc) rc = sync(c, "copy to device");
+    return rc;
 }
 
 int d2h(hl_ctx* c, void* h, const void* d, size_t bytes) {
@@ -91,7 +120,7 @@ int upload_key(hl_ctx* c, const uint8_t* key32, uint32_t** d_key) {
     if (!key32) return HL_B200_OK;
     int rc = dev_alloc(c, (void**)d_key, 32);
     if (rc) return rc;
-    return h2d(c, *d_key, key32, 32);  // little-endian host: the bytes are the words
+    return h2d_owned(c, *d_key, key32, 32);  // little-endian host: the bytes are the words
 }
 
 int log2_exact(size_t v) {
@@ -186,6 +215,7 @@ void hl_b200_shutdown(hl_ctx* c) {
         if (c->stage[i]) cudaFreeHost(c->stage[i]);
         if (c->stage_ev[i]) cudaEventDestroy(c->stage_ev[i]);
     }
+    if (c->arena) cudaFreeHost(c->arena);
     for (auto& s : c->spans) { cudaEventDestroy(s.a); cudaEventDestroy(s.b); }
     for (auto e : c->ev_pool) cudaEventDestroy(e);
     for (auto e : c->ev_chunks) cudaEventDestroy(e);
@@ -197,7 +227,14 @@ void hl_b200_shutdown(hl_ctx* c) {
 }
 
 const char* hl_b200_label(hl_ctx* c) { return c ? c->label.c_str() : "hl_b200: no context"; }
-const char* hl_b200_last_error(hl_ctx* c) { return c ? c->last_error.c_str() : "no context"; }
+const char* hl_b200_last_error(hl_ctx* c) {
+    if (!c) return "no context";
+    // a copy per calling thread: the text stays valid until this thread asks again, whatever the other threads decline meanwhile
+    thread_local std::string mine;
+    std::lock_guard<std::mutex> g(c->err_mu);
+    mine = c->last_error;
+    return mine.c_str();
+}
 
 int hl_b200_set_stream(hl_ctx* c, void* s) {
     if (!c) return HL_B200_ERR_ARG;
@@ -230,6 +267,7 @@ int hl_b200_set_encoder(hl_ctx* c, int fast) {
 int hl_b200_stats(hl_ctx* c, hl_stats* out) {
     if (!c || !out) return HL_B200_ERR_ARG;
     std::lock_guard<std::mutex> g(c->mu);
+    std::lock_guard<std::mutex> ge(c->err_mu);
     *out = c->stats;
     return HL_B200_OK;
 }

@@ -20,6 +20,7 @@ struct hl_ctx {
     std::vector<cudaEvent_t> ev_chunks;
     bool fast_encoder = true;
     std::mutex mu;
+    std::mutex err_mu;       // guards last_error and stats.declines: a decline may be recorded before `mu` is taken, from any thread
     std::map<u32, u64*> tw;  // log2 nn -> nn powers of the nn-th root
     std::string label, last_error;
     hl_stats stats{};
@@ -31,6 +32,8 @@ struct hl_ctx {
     void* stage[2] = {nullptr, nullptr};       // page-locked staging for uploads from pageable host memory (lazily allocated)
     size_t stage_bytes = 0;
     cudaEvent_t stage_ev[2] = {nullptr, nullptr};  // the copy out of stage[i] has completed
+    char* arena = nullptr;     // page-locked bounce area for small caller-owned inputs of calls that return before their copies run
+    size_t arena_off = 0;
     int* d_wp_flag = nullptr;  // the witness products' status word: zero between calls
     bool wp_attr = false;      // the product kernel's shared-memory size has been raised on this device
     size_t alloc_live = 0;   // bytes handed out and not yet returned
@@ -58,6 +61,8 @@ int dev_alloc(hl_ctx* c, void** p, size_t bytes);
 void dev_free(hl_ctx* c, void* p, size_t bytes);
 int h2d(hl_ctx* c, void* d, const void* h, size_t bytes);
 int d2h(hl_ctx* c, void* h, const void* d, size_t bytes);
+// like h2d, but the caller's bytes are no longer needed when it returns, whatever kind of host memory they live in
+int h2d_owned(hl_ctx* c, void* d, const void* h, size_t bytes);
 int sync(hl_ctx* c, const char* what);
 int root_powers(hl_ctx* c, u32 lognn, const u64** out);
 int upload_key(hl_ctx* c, const uint8_t* key32, uint32_t** d_key);

@@ -482,6 +482,8 @@ int hl_b200_store_merkle_dev(hl_store* st, const uint8_t* d_salts32, const uint8
                              uint8_t* d_levels_out) {
     if (!st || !d_levels_out) return HL_B200_ERR_ARG;
     hl_ctx* c = st->ctx;
+    // the tree kernels move digests as 16-byte vectors: a misaligned caller pointer would be a device fault, not a status
+    if (((uintptr_t)d_levels_out & 15) || ((uintptr_t)d_salts32 & 15)) return fail(c, HL_B200_ERR_ARG, "store_merkle_dev: device pointers must be 16-byte aligned");
     std::lock_guard<std::mutex> g(c->mu);
     cudaSetDevice(c->device);
     int rc = merkle_on_device(c, st->d_leaves, (const uint32_t*)d_salts32, st->nn(), leaf_key32, node_key32, (uint32_t*)d_levels_out);

@@ -110,6 +110,7 @@ void* g_cv_addr[MAX_DEVICES];  // per device: the array's device address, resolv
 extern "C" int hl_b200_hash_columns_static(const uint64_t* d_encoded, size_t rows, size_t nn, const uint8_t* key32,
                                            uint8_t* d_leaves32, void* cuda_stream) {
     if (!d_encoded || !d_leaves32 || rows == 0 || nn == 0 || rows > 0x7FFFFFFFu || nn > 0x7FFFFFFFu) return HL_B200_ERR_ARG;
+    if (((uintptr_t)d_encoded & 7) || ((uintptr_t)d_leaves32 & 3)) return HL_B200_ERR_ARG;  // words are loaded as u64, leaves stored as u32
     const size_t nchunks = (rows + 127) / 128;
     if (nchunks > 65535) return HL_B200_ERR_UNSUPPORTED;
     if (nchunks > 1 && nchunks * nn * 32 > (size_t)HL_B200_STATIC_CV_BYTES) return HL_B200_ERR_UNSUPPORTED;  // beyond the static scratch

@@ -105,6 +105,7 @@ extern "C" {
 int hl_b200_lookup_inverse_table(hl_ctx* c, const uint64_t alpha[2], const uint64_t g[2], uint32_t log_len, uint64_t* d_table) {
     if (!c || !alpha || !g || !d_table) return fail(c, HL_B200_ERR_ARG, "lookup_inverse_table: null argument");
     if (int rc = check_log(c, log_len)) return rc;
+    if ((uintptr_t)d_table & 15) return fail(c, HL_B200_ERR_ARG, "lookup_inverse_table: the table must be 16-byte aligned");
     std::lock_guard<std::mutex> lk(c->mu);
     cudaSetDevice(c->device);
     const u32 len = 1u << log_len;
@@ -124,6 +125,8 @@ int hl_b200_lookup_helpers_dev(hl_ctx* c, const int64_t* d_a, const uint64_t* d_
     if (int rc = check_log(c, log_a)) return rc;
     if (d_b) if (int rc = check_log(c, log_b)) return rc;
     if (n == 0) return HL_B200_OK;
+    if (((uintptr_t)d_table_a & 15) || ((uintptr_t)d_table_b & 15) || ((uintptr_t)d_a & 7) || ((uintptr_t)d_b & 7) || ((uintptr_t)d_re & 7) || ((uintptr_t)d_im & 7))
+        return fail(c, HL_B200_ERR_ARG, "lookup_helpers: tables must be 16-byte aligned, columns and planes 8-byte aligned");
     std::lock_guard<std::mutex> lk(c->mu);
     cudaSetDevice(c->device);
     int* d_err = nullptr;

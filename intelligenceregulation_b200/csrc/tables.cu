@@ -106,7 +106,7 @@ int upload(hl_ctx* c, const void* h, size_t count, T** d) {
     *d = nullptr;
     if (count == 0) return HL_B200_OK;
     int rc = dev_alloc(c, (void**)d, count * sizeof(T));
-    if (!rc) rc = h2d(c, *d, h, count * sizeof(T));
+    if (!rc) rc = h2d_owned(c, *d, h, count * sizeof(T));
     return rc;
 }
 
@@ -173,7 +173,7 @@ int hl_b200_tables_put(hl_tables* t, size_t i, const uint64_t* words) {
     hl_ctx* c = t->ctx;
     std::lock_guard<std::mutex> g(c->mu);
     cudaSetDevice(c->device);
-    return h2d(c, t->d_tables + 2 * i * t->len(), words, t->len() * 16);
+    return h2d_owned(c, t->d_tables + 2 * i * t->len(), words, t->len() * 16);
 }
 
 int hl_b200_tables_eq(hl_tables* t, size_t i, uint32_t start, uint32_t p, const uint64_t* hi, const uint64_t* lo, int base_check) {

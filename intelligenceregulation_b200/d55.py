@@ -182,21 +182,55 @@ def join(s0: HostTranscript, records: Sequence[JoinRecord], blocks: int) -> Host
     return tr
 
 
+FAILED_K = (1 << 64) - 1  # the `k` word of a record that reports a failed fork instead of a join record
+
+
+class ForkFailed(RuntimeError):
+    """A fork failed on some rank; raised on EVERY rank after the exchange, with the same text."""
+
+    def __init__(self, failures: Sequence[Tuple[int, int, str]]):
+        self.failures = list(failures)  # (rank, block, text)
+        super().__init__("D55: " + "; ".join(f"block {k} on rank {r}: {t}" for r, k, t in self.failures))
+
+
+def _failure_record(k: int, text: str, claim_cap: int) -> bytes:
+    msg = text.encode("utf-8", "replace")[: 32 + 2 * claim_cap]
+    return struct.pack("<QQQQ", FAILED_K, k, len(msg), 0) + msg.ljust(32 + 2 * claim_cap, b"\0")
+
+
 def run_forks(header: RunHeader, roots: Sequence[bytes], rows: Sequence[int], log_cols: Sequence[int], block_digests: Sequence[bytes],
               prove_fork: Callable[[int, HostTranscript], JoinRecord], rank: int = 0, world: int = 1,
               all_gather: Optional[Callable[[bytes], List[bytes]]] = None, claim_cap: int = 4096) -> HostTranscript:
     """Phase 2 and 3 of a fork run on this rank: prove the blocks this rank owns from fork(S0, k), exchange the
     join records (one fixed-size buffer per rank through `all_gather`), replay the join.  Returns S1.
-    A fork that fails raises here, before the gather, so no rank waits on a dead peer's kernels."""
+    A fork that fails does not leave the exchange: its rank still takes part in the gather, with a fixed-size failure
+    record in the block's slot (so no healthy rank blocks in a collective a dead peer never joins), stops proving its
+    remaining blocks, and every rank raises `ForkFailed` with the same text once the records are in."""
     s0 = header.transcript()
     absorb_commit(s0, header.blocks, roots, rows, log_cols)
-    mine = [prove_fork(k, fork(s0, k, block_digests[k])) for k in blocks_of(rank, world, header.blocks)]
-    per_rank = -(-header.blocks // world)
     size = JoinRecord.size(claim_cap)
-    buf = b"".join(r.pack(claim_cap) for r in mine).ljust(per_rank * size, b"\xff")
+    packed, failed = [], False
+    for k in blocks_of(rank, world, header.blocks):
+        if failed:
+            packed.append(_failure_record(k, "not run: an earlier fork of this rank failed", claim_cap))
+            continue
+        try:
+            packed.append(prove_fork(k, fork(s0, k, block_digests[k])).pack(claim_cap))
+        except Exception as e:  # noqa: BLE001  (reported to every rank below)
+            failed = True
+            packed.append(_failure_record(k, f"{type(e).__name__}: {e}", claim_cap))
+    per_rank = -(-header.blocks // world)
+    buf = b"".join(packed).ljust(per_rank * size, b"\xff")
     bufs = [buf] if world == 1 or all_gather is None else all_gather(buf)
-    records = []
+    records, failures = [], []
     for r, b in enumerate(bufs):
         for i in range(len(blocks_of(r, world, header.blocks))):
-            records.append(JoinRecord.unpack(b[i * size:(i + 1) * size], claim_cap))
+            rec = b[i * size:(i + 1) * size]
+            k0, k1, mlen, _ = struct.unpack_from("<QQQQ", rec, 0)
+            if k0 == FAILED_K:
+                failures.append((r, k1, bytes(rec[32:32 + min(mlen, size - 32)]).decode("utf-8", "replace")))
+            else:
+                records.append(JoinRecord.unpack(rec, claim_cap))
+    if failures:
+        raise ForkFailed(failures)
     return join(s0, records, header.blocks)

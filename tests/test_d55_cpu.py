@@ -130,22 +130,29 @@ def gather(buf):
     out = [torch.empty_like(mine) for _ in range(world)]
     dist.all_gather(out, mine)
     return [bytes(o.tolist()) for o in out]
-s1 = d55.run_forks(h, roots, rows, logs, digs, T._stub_fork(d55), rank, world, gather)
+prove = T._stub_fork(d55)
+if os.environ.get("HL_FAIL_BLOCK"):
+    bad, good = int(os.environ["HL_FAIL_BLOCK"]), prove
+    def prove(k, tr):
+        if k == bad:
+            raise RuntimeError("injected fork failure")
+        return good(k, tr)
+try:
+    s1 = d55.run_forks(h, roots, rows, logs, digs, prove, rank, world, gather)
+except d55.ForkFailed as e:
+    open(os.path.join(os.environ["HL_OUT"], "rank%d.txt" % rank), "w").write("FAILED " + str(e))
+    dist.destroy_process_group()
+    sys.exit(0)
 # one file per rank: the ranks share the launcher's pipe, where their output can interleave
 open(os.path.join(os.environ["HL_OUT"], "rank%d.txt" % rank), "w").write("%s %d" % (s1.state.hex(), s1.counter))
 dist.destroy_process_group()
 '''
 
 
-def test_two_rank_gloo_run_joins_to_the_one_process_state(tmp_path):
-    from intelligenceregulation_b200 import d55
-
-    h = _header(d55, bytes(range(32)))
-    roots, rows, logs, digs = _inputs()
-    want = d55.run_forks(h, roots, rows, logs, digs, _stub_fork(d55))
+def _run_two_ranks(tmp_path, extra_env=None):
     script = tmp_path / "worker.py"
     script.write_text(WORKER)
-    env = dict(os.environ, HL_ROOT=ROOT, HL_OUT=str(tmp_path), OMP_NUM_THREADS="1")
+    env = dict(os.environ, HL_ROOT=ROOT, HL_OUT=str(tmp_path), OMP_NUM_THREADS="1", **(extra_env or {}))
     import socket
 
     for attempt in range(2):  # a free port can still be taken between the probe and the rendezvous: one retry
@@ -157,6 +164,45 @@ def test_two_rank_gloo_run_joins_to_the_one_process_state(tmp_path):
         if out.returncode == 0:
             break
     assert out.returncode == 0, out.stderr[-2000:]
-    for rank in (0, 1):
-        state, counter = (tmp_path / ("rank%d.txt" % rank)).read_text().split()
+    return [(tmp_path / ("rank%d.txt" % rank)).read_text() for rank in (0, 1)]
+
+
+def test_two_rank_gloo_run_joins_to_the_one_process_state(tmp_path):
+    from intelligenceregulation_b200 import d55
+
+    h = _header(d55, bytes(range(32)))
+    roots, rows, logs, digs = _inputs()
+    want = d55.run_forks(h, roots, rows, logs, digs, _stub_fork(d55))
+    for text in _run_two_ranks(tmp_path):
+        state, counter = text.split()
         assert state == want.state.hex() and int(counter) == want.counter
+
+
+def test_a_fork_that_fails_on_one_rank_ends_every_rank_with_the_same_error(tmp_path):
+    """Block 1 belongs to rank 1 and its fork raises (a host-side failure: nothing on a device is involved).  Rank 1 still
+    takes part in the exchange, so rank 0 does not wait in the gather for a peer that never comes; both ranks end promptly
+    with the same `ForkFailed` text, which names the rank, the block and the cause."""
+    import time
+
+    t0 = time.time()
+    texts = _run_two_ranks(tmp_path, {"HL_FAIL_BLOCK": "1"})
+    assert time.time() - t0 < 120
+    assert texts[0] == texts[1] and texts[0].startswith("FAILED D55: block 1 on rank 1: RuntimeError: injected fork failure")
+    assert "block 3 on rank 1: not run" in texts[0]
+
+
+def test_a_failed_fork_in_one_process_raises_fork_failed():
+    from intelligenceregulation_b200 import d55
+
+    h = _header(d55, None)
+    roots, rows, logs, digs = _inputs()
+    good = _stub_fork(d55)
+
+    def prove(k, tr):
+        if k == 2:
+            raise ValueError("zero LogUp denominator")
+        return good(k, tr)
+
+    with pytest.raises(d55.ForkFailed) as ei:
+        d55.run_forks(h, roots, rows, logs, digs, prove)
+    assert ei.value.failures[0][:2] == (0, 2) and "zero LogUp denominator" in ei.value.failures[0][2]

@@ -65,3 +65,30 @@ def test_single_row_and_single_chunk_edges(dev, oracle):
         assert (store.columns(np.arange(nn, dtype=np.uint64)).T.reshape(-1) == enc).all()
         assert store.columns(np.zeros(0, dtype=np.uint64)).shape == (0, rows)
         store.free()
+
+
+def test_misaligned_caller_device_pointers_are_a_bad_argument_not_a_fault(dev, oracle):
+    """Device pointers that the kernels would move as 16-byte vectors are checked on the host: the call answers
+    HL_B200_ERR_ARG and launches nothing."""
+    import ctypes as C
+    import torch
+    from intelligenceregulation_b200 import backend
+
+    buf = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    base = buf.data_ptr()
+    assert base % 16 == 0
+    log_cols, ir, rows = 8, 2, 4
+    store, _ = dev.try_commit(log_cols, ir, _data(rows << log_cols), 10)
+    launches = dev.ctx.stats()["kernel_launches"]
+    with pytest.raises(backend.DeviceError) as e:
+        dev.ctx.lookup_inverse_table((5, 6), (7, 8), 8, base + 8)
+    assert e.value.code == -1
+    with pytest.raises(backend.DeviceError) as e:
+        store.merkle_dev(base + 4, None, None, base + 4096)
+    assert e.value.code == -1
+    with pytest.raises(backend.DeviceError) as e:
+        store.merkle_dev(base, None, None, base + 4096 + 8)
+    assert e.value.code == -1
+    assert dev.ctx.stats()["kernel_launches"] == launches
+    store.free()
+    del buf

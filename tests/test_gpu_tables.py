@@ -122,3 +122,54 @@ def test_refusals(dev, oracle, committed):
     with pytest.raises(backend.DeviceError):
         t.plan_eq(0, oracle.ZkRng(1, b"e").fp2_vec(3), 2)
     t.free()
+
+
+def test_page_locked_inputs_may_be_overwritten_when_the_call_returns(dev, oracle):
+    """`tables_put`, `tables_eq` and `tables_plane` return before their copies run.  From page-locked caller memory such a
+    copy reads its source when the DMA engine gets to it, so the library must have taken the bytes by then: every input
+    here lives in page-locked memory and is overwritten as soon as its call returns; the tables must hold the values that
+    were passed.  A large table (copied in place and waited for) and many small ones (bounced through the context's own
+    page-locked area, which wraps several times) are both covered."""
+    import torch
+    from intelligenceregulation_b200 import backend
+
+    def pinned(a):
+        t = torch.empty(a.size, dtype=torch.int64, pin_memory=True)
+        v = t.numpy().view(np.uint64).reshape(a.shape)
+        v[...] = a
+        return t, v
+
+    rng = oracle.ZkRng(4242, b"pinned")
+    # one large table after a long kernel, so that the copy is still queued when the call returns
+    n_big = 20
+    big = rng.fp2_vec(1 << n_big)
+    keep, view = pinned(big)
+    t = backend.B200Tables(dev.ctx, 2, n_big)
+    t.plan_eq(0, rng.fp2_vec(n_big), 0)
+    t.put(1, view)
+    view[...] = 0
+    t.flush()
+    assert (t.read(1) == big).all()
+    t.free()
+    # many small ones: 24 KiB each through the 4 MiB bounce area, 600 calls = 3.5 wraps; eq halves the same way
+    n_small, k = 9, 60
+    for rep in range(10):
+        want = [rng.fp2_vec(1 << n_small) for _ in range(k)]
+        t = backend.B200Tables(dev.ctx, k + 1, n_small)
+        keep, view = pinned(want[0])
+        point = rng.fp2_vec(n_small)
+        p_lo = n_small // 2
+        hi, lo = backend.eq_table_msb(point[: n_small - p_lo]), backend.eq_table_msb(point[n_small - p_lo:])
+        (kh, vh), (kl, vl) = pinned(hi), pinned(lo)
+        dev.ctx.check(dev.ctx.lib.hl_b200_tables_eq(t.h, k, 0, n_small, backend._ptr(vh), backend._ptr(vl), 0))
+        vh[...] = 0
+        vl[...] = 0
+        for i in range(k):
+            view[...] = want[i]
+            t.put(i, view)
+            view[...] = 0xDEAD
+        t.flush()
+        for i in range(k):
+            assert (t.read(i) == want[i]).all(), (rep, i)
+        assert (t.read(k) == oracle.eq_cube(point, n_small, 0)).all()
+        t.free()

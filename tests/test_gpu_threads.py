@@ -57,3 +57,90 @@ def test_four_threads_on_one_context_equal_the_serial_results():
         assert got == serial
     assert not dev.ctx.declines
     dev.ctx.close()
+
+
+def test_threads_that_decline_do_not_disturb_the_ones_that_work():
+    """Declines are routine in a fork run (a shape the device refuses, an argument check): two threads provoke them without
+    pause, two others read the error text, and two work.  The error text and the decline counter have their own lock, so the
+    workers' results still equal the serial ones and every error text read is a whole message."""
+    from intelligenceregulation_b200 import backend
+
+    dev = backend.B200Backend(device=0)
+    seeds = [5, 6]
+    serial = [_work(dev, backend, s) for s in seeds]
+    stop = threading.Event()
+    errs, texts = [], set()
+
+    def decliner(k):
+        tables = np.zeros((2, 8, 2), dtype=np.uint64)
+        while not stop.is_set():
+            try:
+                if k == 0:
+                    assert dev.try_commit(30, 2, np.zeros(4, dtype=np.uint64), 31) is None  # rows of 2^30 words: unsupported
+                else:
+                    backend.B200Rounds(dev.ctx, backend.POLY_ZC, tables, 7)  # the zero-check family has 4 tables, degree 3
+                    errs.append("an unsupported family was accepted")
+            except backend.DeviceError:
+                pass
+            except Exception as e:
+                errs.append(e)
+
+    def reader():
+        while not stop.is_set():
+            texts.add(dev.ctx.last_error())
+
+    got = [None] * len(seeds)
+
+    def worker(i):
+        try:
+            for _ in range(3):
+                got[i] = _work(dev, backend, seeds[i])
+                assert got[i] == serial[i]
+        except Exception as e:
+            errs.append(e)
+
+    side = [threading.Thread(target=decliner, args=(k,)) for k in (0, 1)] + [threading.Thread(target=reader) for _ in range(2)]
+    work = [threading.Thread(target=worker, args=(i,)) for i in range(len(seeds))]
+    for t in side + work:
+        t.start()
+    for t in work:
+        t.join()
+    stop.set()
+    for t in side:
+        t.join()
+    assert not errs, errs
+    assert got == serial
+    assert dev.ctx.stats()["declines"] > 0
+    assert all(t.isprintable() and len(t) < 200 for t in texts), texts
+    dev.ctx.close()
+
+
+def test_one_context_per_thread_on_one_gpu_equals_the_serial_results():
+    """The arrangement the header recommends for concurrent forks: every worker thread owns a context (its own stream,
+    twiddle tables and staging) on the same GPU, so that their calls overlap instead of queueing behind one lock."""
+    from intelligenceregulation_b200 import backend
+
+    seeds = [1, 2, 3, 4]
+    ref = backend.B200Backend(device=0)
+    serial = [_work(ref, backend, s) for s in seeds]
+    ref.ctx.close()
+    got, errs = [None] * len(seeds), []
+
+    def run(i):
+        try:
+            dev = backend.B200Backend(device=0)
+            for _ in range(3):
+                got[i] = _work(dev, backend, seeds[i])
+                assert got[i] == serial[i]
+            assert not dev.ctx.declines
+            dev.ctx.close()
+        except Exception as e:
+            errs.append(e)
+
+    th = [threading.Thread(target=run, args=(i,)) for i in range(len(seeds))]
+    for t in th:
+        t.start()
+    for t in th:
+        t.join()
+    assert not errs, errs
+    assert got == serial

@@ -36,6 +36,17 @@ def test_no_device_means_an_error_not_a_fallback():
         backend.Context(0)
 
 
+def test_misaligned_device_pointers_are_refused_before_any_cuda_call():
+    """The allocation-free column hash loads words as u64 and stores leaves as u32: a pointer that is not aligned for that
+    is a bad argument, answered on the host (no device is needed to be told so)."""
+    from intelligenceregulation_b200 import _lib
+
+    lib = _lib.load()
+    ok_enc, ok_out = 0x10000, 0x20000  # never dereferenced: the refusal comes first
+    assert lib.hl_b200_hash_columns_static(C.c_void_p(ok_enc + 4), 130, 1024, None, C.c_void_p(ok_out), None) == -1
+    assert lib.hl_b200_hash_columns_static(C.c_void_p(ok_enc), 130, 1024, None, C.c_void_p(ok_out + 2), None) == -1
+
+
 def test_product_does_not_reach_the_oracle():
     pkg = os.path.join(ROOT, "intelligenceregulation_b200")
     for dirpath, _, files in os.walk(pkg):
