@@ -99,6 +99,20 @@ int hl_b200_commit_zk_tree(hl_ctx* ctx, uint32_t log_cols, uint32_t inv_rate, co
                            const uint64_t* pows, uint32_t max_log, const uint8_t* key32, const uint8_t* salts32, const uint8_t* leaf_key32,
                            const uint8_t* node_key32, hl_store** store, uint8_t* leaves32, uint8_t* levels_out);
 
+/* The hiding commitment from NARROW witness rows: the reference's CUDA uploader sends int8 / int16 / int32 witness planes as 1, 2
+ * or 4 bytes per word and restores the identical 64-bit image on the device (hashline/src/gpu/cuda.rs:893-1099 `narrow_class`,
+ * `pack_narrow`, `upload_narrow`; kernel `k_widen`, hashline/src/gpu/kernels.cu:220-236; rationale gpu/mod.rs:270-300).
+ * packed: the rows back to back, row r as 2^log_cols little-endian two's-complement integers of row_width[r] bytes (1, 2 or 4;
+ * a word x >= 0 stands for x, x < 0 for p + x, field.rs:32-34) or, at width 8, its canonical field words as they are.  The
+ * width is per ROW here (the reference picks one per upload), so wide rows (masks, hashes) and narrow planes share a call.
+ * The bytes are copied as they are and widened inside the encoder's first pass, which also leaves the 64-bit rows resident
+ * for the opening.  Every result (leaves, tree, folds, columns) is that of hl_b200_commit_zk[_tree] on the widened matrix.
+ * salts32 NULL: no tree (levels_out ignored, leaves32 required); otherwise as hl_b200_commit_zk_tree (leaves32 may be NULL). */
+int hl_b200_commit_zk_packed(hl_ctx* ctx, uint32_t log_cols, uint32_t inv_rate, const void* packed, const uint8_t* row_width, size_t rows,
+                             const uint64_t* pads, size_t q, const uint64_t* pows, uint32_t max_log, const uint8_t* key32,
+                             const uint8_t* salts32, const uint8_t* leaf_key32, const uint8_t* node_key32, hl_store** store,
+                             uint8_t* leaves32, uint8_t* levels_out);
+
 /* The same commitment for inputs that already live in device memory (the reference's
  * device-buffer commitment, pcs.rs:801-803 / metal.rs:3105 resident rows).  Asynchronous on
  * the context's stream; d_leaves32 (nn x 32 bytes, device) is ready when the stream reaches

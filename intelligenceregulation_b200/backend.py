@@ -369,6 +369,35 @@ class B200Backend:
             return None
         return B200Commit(self.ctx, h), leaves, levels
 
+    def try_commit_zk_packed(self, log_cols: int, inv_rate: int, packed: np.ndarray, row_width: np.ndarray, pads, pows, max_log: int,
+                             key: Optional[bytes], salts=None, leaf_key: Optional[bytes] = None, node_key: Optional[bytes] = None,
+                             levels_out: Optional[np.ndarray] = None, want_leaves: bool = True):
+        """The hiding commitment from packed narrow rows (`pack_rows`): (store, leaves[, levels]) or None on a decline.  The
+        device restores the 64-bit image (gpu/cuda.rs:1073-1105 `upload_narrow` + `k_widen`), so every result equals the
+        wide call's."""
+        packed = np.ascontiguousarray(packed, dtype=np.uint8)
+        row_width = np.ascontiguousarray(row_width, dtype=np.uint8)
+        pads, pows = _u64(pads), _u64(pows)
+        rows, nn = row_width.size, inv_rate << log_cols
+        q = pads.size // rows if rows else 0
+        assert packed.size == int(row_width.astype(np.int64).sum()) << log_cols
+        tree = salts is not None
+        leaves = np.empty((nn, 32), dtype=np.uint8) if (want_leaves or not tree) else None
+        levels = None
+        if tree:
+            salts = np.ascontiguousarray(salts, dtype=np.uint8)
+            levels = levels_out if levels_out is not None else np.empty((2 * nn - 1, 32), dtype=np.uint8)
+            assert salts.size == nn * 32 and levels.size == (2 * nn - 1) * 32
+        h = C.c_void_p()
+        rc = self.ctx.lib.hl_b200_commit_zk_packed(self.ctx.h, log_cols, inv_rate, _ptr(packed), _ptr(row_width), rows, _ptr(pads), q, _ptr(pows), max_log,
+                                                   _ptr(key), _ptr(salts) if tree else None, _ptr(leaf_key), _ptr(node_key), C.byref(h),
+                                                   _ptr(leaves) if leaves is not None else None, _ptr(levels) if tree else None)
+        if rc != 0:
+            self.ctx.declined("b200 zk commit (packed rows)", rc)
+            return None
+        st = B200Commit(self.ctx, h)
+        return (st, leaves, levels) if tree else (st, leaves)
+
     def commit_zk_dev(self, log_cols: int, inv_rate: int, d_data: int, rows: int, d_pads: int, q: int, d_pows: int,
                       key: Optional[bytes], d_leaves: int = 0) -> B200Commit:
         """The device-buffer commitment: inputs are device addresses, asynchronous on the context's stream."""
@@ -376,6 +405,35 @@ class B200Backend:
         self.ctx.check(self.ctx.lib.hl_b200_commit_zk_dev(self.ctx.h, log_cols, inv_rate, C.c_void_p(d_data), rows, C.c_void_p(d_pads), q,
                                                             C.c_void_p(d_pows), _ptr(key), C.byref(h), C.c_void_p(d_leaves)))
         return B200Commit(self.ctx, h)
+
+
+def narrow_class(words: np.ndarray) -> int:
+    """The signed byte width that represents every word of `words` exactly (gpu/cuda.rs:903-910 `narrow_class`): 1, 2 or 4
+    for int8 / int16 / int32 valued field words (x >= 0 stored as x, x < 0 as p + x), 8 for anything wider."""
+    w = _u64(words)
+    P = np.uint64(0xFFFFFFFF00000001)
+    for width, hi in ((1, 0x80), (2, 0x8000), (4, 0x80000000)):
+        if bool(np.all((w < np.uint64(hi)) | (w >= P - np.uint64(hi)))):
+            return width
+    return 8
+
+
+def pack_rows(data: np.ndarray, rows: int) -> Tuple[np.ndarray, np.ndarray]:
+    """(packed bytes, per-row widths) of a rows x n matrix of canonical field words for `try_commit_zk_packed`: every row
+    at the narrowest width that holds it (gpu/cuda.rs:926-960 `pack_narrow`, per row instead of per upload)."""
+    d = _u64(data).reshape(rows, -1)
+    widths = np.array([narrow_class(d[r]) for r in range(rows)], dtype=np.uint8)
+    P = np.uint64(0xFFFFFFFF00000001)
+    parts = []
+    for r in range(rows):
+        w = int(widths[r])
+        if w == 8:
+            parts.append(d[r].view(np.uint8))
+            continue
+        with np.errstate(over="ignore"):
+            signed = np.where(d[r] < np.uint64(1 << 63), d[r], d[r] - P).astype(np.uint64).view(np.int64)  # p + x -> x (mod 2^64)
+        parts.append(signed.astype({1: np.int8, 2: "<i2", 4: "<i4"}[w]).view(np.uint8))
+    return np.concatenate(parts), widths
 
 
 class B200Mask(B200Commit):

@@ -30,11 +30,19 @@ struct Shape {
     bool zk;
 };
 
-// Encode + column-hash.  With `h_data` NULL the data rows are already in st->d_data; otherwise they are
+// Where the data rows come from: NULL base = already in st->d_data; otherwise host memory, either 64-bit words (row_w NULL) or
+// packed rows of 1-, 2-, 4- or 8-byte two's-complement words (row r at byte off[r], width row_w[r]).
+struct HostRows {
+    const void* base = nullptr;
+    const uint8_t* row_w = nullptr;
+    std::vector<u64> off;  // packed form only: rows + 1 byte offsets
+};
+
+// Encode + column-hash.  With no host rows the data rows are already in st->d_data; otherwise they are
 // uploaded here in row chunks on the context's copy stream while the encoder works on the chunks that
-// have arrived (the upload of a block-sized matrix takes longer than its encoding).  Leaves stay in
-// st->d_leaves.
-int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* key32, const uint64_t* h_data) {
+// have arrived (the upload of a block-sized matrix takes longer than its encoding).  Packed rows travel as
+// their narrow bytes and are widened into st->d_data by the encoder's first pass.  Leaves stay in st->d_leaves.
+int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* key32, const HostRows& hr) {
     const u32 logn = st->logn, lognn = st->logn + st->logr;
     const size_t n = st->n(), nn = st->nn();
     // rows above 2^14 words run as 2 or 4 shared-memory transforms of 2^14 (encode_core.cuh)
@@ -44,20 +52,31 @@ int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* 
     const u64* tw = nullptr;
     int rc = root_powers(c, lognn, &tw);
     if (rc) return rc;
+    const void* h_data = hr.base;
+    const bool packed = h_data && hr.row_w;
+    const bool fused_widen = packed && loga == 0 && logb >= 8 && c->fast_encoder;  // else a widening pass of its own per piece
     uint32_t* d_key = nullptr;
     u64* scratch = nullptr;
     uint32_t* cvs = nullptr;
+    unsigned char *d_narrow = nullptr, *d_row_w = nullptr;
+    u64* d_row_off = nullptr;
     const size_t scratch_words = hlk::encode_scratch_words(logb, T, c->sm_count, st->rows);
     const u32 nchunks = hlk::hash_chunks(st->rows);
     const size_t cvs_bytes = nchunks > 1 ? (size_t)nchunks * nn * 32 : 0;
+    const size_t total_bytes = packed ? (size_t)hr.off[st->rows] : (size_t)st->rows * n * 8;
     rc = upload_key(c, key32, &d_key);
     if (!rc) rc = dev_alloc(c, (void**)&scratch, scratch_words * 8);
     if (!rc && cvs_bytes) rc = dev_alloc(c, (void**)&cvs, cvs_bytes);
+    if (!rc && packed) rc = dev_alloc(c, (void**)&d_narrow, total_bytes + 16);
+    if (!rc && packed) rc = dev_alloc(c, (void**)&d_row_off, (size_t)st->rows * 8);
+    if (!rc && packed) rc = dev_alloc(c, (void**)&d_row_w, st->rows);
+    if (!rc && packed) rc = h2d_owned(c, d_row_off, hr.off.data(), (size_t)st->rows * 8);
+    if (!rc && packed) rc = h2d_owned(c, d_row_w, hr.row_w, st->rows);
     // row pieces of 256 rows = two 1 KiB hash chunks per column: a piece is encoded and its chunk values are hashed while
     // the next piece is still on the bus, so that only the last piece (at most one wave of the encoder) follows the upload
-    const size_t row_bytes = n * 8;
+    auto byte_at = [&](u32 r) { return packed ? (size_t)hr.off[r] : (size_t)r * n * 8; };
     u32 chunk = st->rows;
-    if (h_data && (size_t)st->rows * row_bytes >= ((size_t)32 << 20) && st->rows > 4u * (u32)c->sm_count) chunk = 256;
+    if (h_data && total_bytes >= ((size_t)32 << 20) && st->rows > 4u * (u32)c->sm_count) chunk = 256;
     const bool pieces = chunk < st->rows;
     if (!rc && h_data && chunk < st->rows) {
         // the copy stream may touch the fresh allocations only after the main stream has made them
@@ -72,7 +91,11 @@ int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* 
         cudaPointerAttributes attr;
         const bool pageable = cudaPointerGetAttributes(&attr, h_data) != cudaSuccess || attr.type == cudaMemoryTypeUnregistered;
         cudaGetLastError();  // an unregistered pointer is not an error here
-        const size_t need = (size_t)chunk * row_bytes;
+        size_t need = 0;
+        for (u32 r0 = 0; r0 < st->rows; r0 += chunk) {
+            const u32 r1 = r0 + chunk < st->rows ? r0 + chunk : st->rows;
+            need = byte_at(r1) - byte_at(r0) > need ? byte_at(r1) - byte_at(r0) : need;
+        }
         if (pageable) {
             staged = true;
             if (c->stage_bytes < need) {
@@ -96,11 +119,11 @@ int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* 
             if (pieces && r0 + nr == st->rows && nr > 128 && nr > (u32)c->sm_count) nr = 128;  // leave one wave or less for the end
             if (h_data) {
                 cudaStream_t cs = chunk < st->rows ? c->copy_stream : c->stream;
-                const void* from = h_data + (size_t)r0 * n;
+                const size_t b0 = byte_at(r0), bytes = byte_at(r0 + nr) - b0;
+                const void* from = (const char*)h_data + b0;
                 if (staged) {
                     const int b = (int)(piece_i++ & 1);
                     if (piece_i > 2) cudaEventSynchronize(c->stage_ev[b]);  // the copy that last read this buffer is done
-                    const size_t bytes = (size_t)nr * row_bytes;
                     const unsigned hw = std::thread::hardware_concurrency();
                     const int nth = bytes >= ((size_t)8 << 20) ? (int)(hw >= 8 ? 8 : hw >= 2 ? hw : 1) : 1;
                     std::vector<std::thread> th;
@@ -110,9 +133,10 @@ int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* 
                     for (auto& x : th) x.join();
                     from = c->stage[b];
                 }
-                cudaError_t e = cudaMemcpyAsync(st->d_data + (size_t)r0 * n, from, (size_t)nr * row_bytes, cudaMemcpyHostToDevice, cs);
+                void* to = packed ? (void*)(d_narrow + b0) : (void*)(st->d_data + (size_t)r0 * n);
+                cudaError_t e = cudaMemcpyAsync(to, from, bytes, cudaMemcpyHostToDevice, cs);
                 if (staged && e == cudaSuccess) e = cudaEventRecord(c->stage_ev[(piece_i - 1) & 1], cs);
-                c->stats.bytes_h2d += (size_t)nr * row_bytes;
+                c->stats.bytes_h2d += bytes;
                 if (e == cudaSuccess && cs != c->stream) {
                     if (ev_i == c->ev_chunks.size()) {
                         cudaEvent_t ev = nullptr;
@@ -125,12 +149,18 @@ int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* 
                 }
                 if (e != cudaSuccess) { rc = fail(c, HL_B200_ERR_DEVICE, "row upload", e); break; }
             }
+            if (packed && !fused_widen) {
+                cudaError_t e = hlk::widen_rows(d_narrow, d_row_off + r0, d_row_w + r0, st->d_data + (size_t)r0 * n, nr, (u32)n, c->sm_count, c->stream);
+                c->stats.kernel_launches += 1;
+                if (e != cudaSuccess) { rc = fail(c, HL_B200_ERR_DEVICE, "row widening launch", e); break; }
+            }
             enc::RowArgs a;
             a.data = st->d_data + (size_t)r0 * n;
             a.pads = st->d_pads ? st->d_pads + (size_t)r0 * st->q : nullptr;
             a.pows = d_pows; a.tw_nn = tw; a.enc = st->d_enc + (size_t)r0 * nn; a.scratch = scratch;
             a.rows = nr; a.q = st->zk ? st->q : 0; a.T = T; a.logr = st->logr + loga; a.loga = loga; a.zk = st->zk ? 1 : 0;
             a.ninv = gl_inv((u64)n); a.coef_out = nullptr;
+            if (fused_widen) { a.narrow = d_narrow; a.row_off = d_row_off + r0; a.row_w = d_row_w + r0; }
             // a handful of rows (a boundary commitment, the last piece of an upload): one CTA per (row, residue)
             a.split = (loga == 0 && st->logr >= 1 && ((u64)nr << st->logr) <= (u64)c->sm_count) ? 1 : 0;
             cudaError_t e = hlk::encode_rows(a, logb, c->fast_encoder || loga, c->sm_count, scratch_words, c->stream, &st->encoder_path);
@@ -159,6 +189,9 @@ int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* 
     dev_free(c, scratch, scratch_words * 8);
     if (cvs) dev_free(c, cvs, cvs_bytes);
     if (d_key) dev_free(c, d_key, 32);
+    if (d_narrow) dev_free(c, d_narrow, total_bytes + 16);
+    if (d_row_off) dev_free(c, d_row_off, (size_t)st->rows * 8);
+    if (d_row_w) dev_free(c, d_row_w, st->rows);
     return rc;
 }
 
@@ -192,7 +225,7 @@ struct TreeAsk {
     uint8_t* levels_out;
 };
 
-int commit_host(hl_ctx* c, const Shape& s, const uint64_t* data, const uint64_t* pads, const uint64_t* pows,
+int commit_host(hl_ctx* c, const Shape& s, const HostRows& data, const uint64_t* pads, const uint64_t* pows,
                 const uint8_t* key32, hl_store** store, uint8_t* leaves32, const TreeAsk* tree = nullptr) {
     hl_store* st = new hl_store();
     st->ctx = c; st->rows = s.rows; st->logn = s.logn; st->logr = s.logr; st->q = s.q; st->zk = s.zk;
@@ -238,7 +271,9 @@ int hl_b200_commit(hl_ctx* c, uint32_t log_cols, uint32_t inv_rate, const uint64
     Shape s;
     int rc = check_shape(c, log_cols, inv_rate, rows, 0, false, max_log, &s);
     if (rc) return rc;
-    return commit_host(c, s, data, nullptr, nullptr, key32, store, leaves32);
+    HostRows hr;
+    hr.base = data;
+    return commit_host(c, s, hr, nullptr, nullptr, key32, store, leaves32);
 }
 
 int hl_b200_commit_zk(hl_ctx* c, uint32_t log_cols, uint32_t inv_rate, const uint64_t* data, size_t rows,
@@ -250,7 +285,9 @@ int hl_b200_commit_zk(hl_ctx* c, uint32_t log_cols, uint32_t inv_rate, const uin
     Shape s;
     int rc = check_shape(c, log_cols, inv_rate, rows, q, true, max_log, &s);
     if (rc) return rc;
-    return commit_host(c, s, data, pads, pows, key32, store, leaves32);
+    HostRows hr;
+    hr.base = data;
+    return commit_host(c, s, hr, pads, pows, key32, store, leaves32);
 }
 
 int hl_b200_commit_zk_tree(hl_ctx* c, uint32_t log_cols, uint32_t inv_rate, const uint64_t* data, size_t rows, const uint64_t* pads, size_t q,
@@ -263,7 +300,38 @@ int hl_b200_commit_zk_tree(hl_ctx* c, uint32_t log_cols, uint32_t inv_rate, cons
     int rc = check_shape(c, log_cols, inv_rate, rows, q, true, max_log, &s);
     if (rc) return rc;
     const TreeAsk tree{salts32, leaf_key32, node_key32, levels_out};
-    return commit_host(c, s, data, pads, pows, key32, store, leaves32, &tree);
+    HostRows hr;
+    hr.base = data;
+    return commit_host(c, s, hr, pads, pows, key32, store, leaves32, &tree);
+}
+
+int hl_b200_commit_zk_packed(hl_ctx* c, uint32_t log_cols, uint32_t inv_rate, const void* packed, const uint8_t* row_width, size_t rows,
+                             const uint64_t* pads, size_t q, const uint64_t* pows, uint32_t max_log, const uint8_t* key32, const uint8_t* salts32,
+                             const uint8_t* leaf_key32, const uint8_t* node_key32, hl_store** store, uint8_t* leaves32, uint8_t* levels_out) {
+    if (!c || !packed || !row_width || !pads || !pows || !store || (salts32 && !levels_out) || (!salts32 && !leaves32))
+        return fail(c, HL_B200_ERR_ARG, "commit_zk_packed: null argument");
+    Shape s;
+    HostRows hr;
+    if (int rc = check_shape(c, log_cols, inv_rate, rows, q, true, max_log, &s)) return rc;
+    if (log_cols < 3) return fail(c, HL_B200_ERR_UNSUPPORTED, "commit_zk_packed: rows of fewer than 8 words");  // keeps every row 8-byte aligned
+    hr.base = packed;
+    hr.row_w = row_width;
+    hr.off.resize(rows + 1);
+    u64 at = 0;
+    for (size_t r = 0; r < rows; r++) {
+        const uint8_t w = row_width[r];
+        if (w != 1 && w != 2 && w != 4 && w != 8) return fail(c, HL_B200_ERR_ARG, "commit_zk_packed: a row width other than 1, 2, 4 or 8 bytes");
+        hr.off[r] = at;
+        at += (u64)w << log_cols;
+    }
+    hr.off[rows] = at;
+    std::lock_guard<std::mutex> g(c->mu);
+    cudaSetDevice(c->device);
+    if (salts32) {
+        const TreeAsk tree{salts32, leaf_key32, node_key32, levels_out};
+        return commit_host(c, s, hr, pads, pows, key32, store, leaves32, &tree);
+    }
+    return commit_host(c, s, hr, pads, pows, key32, store, leaves32);
 }
 
 int hl_b200_commit_zk_dev(hl_ctx* c, uint32_t log_cols, uint32_t inv_rate, const uint64_t* d_data, size_t rows,
@@ -283,7 +351,7 @@ int hl_b200_commit_zk_dev(hl_ctx* c, uint32_t log_cols, uint32_t inv_rate, const
     const size_t nn = st->nn();
     rc = dev_alloc(c, (void**)&st->d_enc, (size_t)s.rows * nn * 8);
     if (!rc) rc = dev_alloc(c, (void**)&st->d_leaves, nn * 32);
-    if (!rc) rc = commit_on_device(c, st, (const u64*)d_pows, key32, nullptr);
+    if (!rc) rc = commit_on_device(c, st, (const u64*)d_pows, key32, HostRows());
     if (!rc && d_leaves32) {
         cudaError_t e = cudaMemcpyAsync(d_leaves32, st->d_leaves, nn * 32, cudaMemcpyDeviceToDevice, c->stream);
         if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "leaf copy", e);

@@ -35,7 +35,7 @@ __global__ void k_encode_generic(enc::RowArgs a, u32 logn) {
     }
 }
 
-template <int LOGN, int THREADS, int FORM = enc::FORM_PCS>
+template <int LOGN, int THREADS, int FORM = enc::FORM_PCS, bool NARROW = false>
 __global__ void __launch_bounds__(THREADS) k_encode_fast(enc::RowArgs a) {
     using F = enc::Fast<LOGN>;
     extern __shared__ u64 smem[];
@@ -48,7 +48,7 @@ __global__ void __launch_bounds__(THREADS) k_encode_fast(enc::RowArgs a) {
     if (a.split) {
         for (u32 unit = blockIdx.x; unit < (a.rows << a.logr); unit += gridDim.x) {
             const u32 row = unit >> a.logr, s = unit & ((1u << a.logr) - 1u);
-            F::template row_coeffs<CtaSync, FORM>(a, row, S, TW, X, tid, THREADS, CtaSync());
+            F::template row_coeffs<CtaSync, FORM, NARROW>(a, row, S, TW, X, tid, THREADS, CtaSync());
             __syncthreads();
             F::row_residue(a, row, s, S, TW, X, tid, THREADS, CtaSync());
             __syncthreads();
@@ -56,12 +56,22 @@ __global__ void __launch_bounds__(THREADS) k_encode_fast(enc::RowArgs a) {
         return;
     }
     for (u32 row = blockIdx.x; row < a.rows; row += gridDim.x) {
-        F::template row_coeffs<CtaSync, FORM>(a, row, S, TW, X, tid, THREADS, CtaSync());
+        F::template row_coeffs<CtaSync, FORM, NARROW>(a, row, S, TW, X, tid, THREADS, CtaSync());
         __syncthreads();  // the scratch slot is complete and shared memory is free again
         for (u32 s = 0; s < (1u << a.logr); s++) {
             F::row_residue(a, row, s, S, TW, X, tid, THREADS, CtaSync());
             __syncthreads();
         }
+    }
+}
+
+// packed rows widened in a pass of their own: the shapes the fast path does not cover (rows below 2^8 or above 2^14 words)
+__global__ void __launch_bounds__(256) k_widen_rows(const unsigned char* __restrict__ narrow, const u64* __restrict__ row_off,
+                                                    const unsigned char* __restrict__ row_w, u64* __restrict__ out, u32 rows, u32 n) {
+    const size_t total = (size_t)rows * n;
+    for (size_t x = (size_t)blockIdx.x * blockDim.x + threadIdx.x; x < total; x += (size_t)gridDim.x * blockDim.x) {
+        const u32 row = (u32)(x / n), i = (u32)(x - (size_t)row * n);
+        out[x] = enc::widen_word(narrow + row_off[row], i, row_w[row]);
     }
 }
 
@@ -71,11 +81,11 @@ constexpr int fast_threads() {
     return g < 32 ? 32 : (g > 1024 ? 1024 : g);
 }
 
-template <int LOGN, int FORM = enc::FORM_PCS>
+template <int LOGN, int FORM = enc::FORM_PCS, bool NARROW = false>
 cudaError_t launch_fast(const enc::RowArgs& a, int sm_count, size_t scratch_words, cudaStream_t st, int* grid_out) {
     using F = enc::Fast<LOGN>;
     constexpr int T = fast_threads<LOGN>();
-    auto kern = k_encode_fast<LOGN, T, FORM>;
+    auto kern = k_encode_fast<LOGN, T, FORM, NARROW>;
     size_t smem = (size_t)(F::N + F::TW_WORDS) * 8;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
@@ -110,6 +120,19 @@ size_t encode_scratch_words(u32 logn, u32 T, int sm_count, u32 rows) {
 cudaError_t encode_rows(const enc::RowArgs& a, u32 logn, bool allow_fast, int sm_count, size_t scratch_words,
                         cudaStream_t st, int* path_out) {
     int grid = 0;
+    if (a.narrow) {  // packed rows: the widening first pass exists on the fast path only (the caller widens separately otherwise)
+        if (!allow_fast || logn < 8 || logn > 14 || a.loga) return cudaErrorInvalidValue;
+        if (path_out) *path_out = 2;
+        switch (logn) {
+            case 8: return launch_fast<8, enc::FORM_PCS, true>(a, sm_count, scratch_words, st, &grid);
+            case 9: return launch_fast<9, enc::FORM_PCS, true>(a, sm_count, scratch_words, st, &grid);
+            case 10: return launch_fast<10, enc::FORM_PCS, true>(a, sm_count, scratch_words, st, &grid);
+            case 11: return launch_fast<11, enc::FORM_PCS, true>(a, sm_count, scratch_words, st, &grid);
+            case 12: return launch_fast<12, enc::FORM_PCS, true>(a, sm_count, scratch_words, st, &grid);
+            case 13: return launch_fast<13, enc::FORM_PCS, true>(a, sm_count, scratch_words, st, &grid);
+            case 14: return launch_fast<14, enc::FORM_PCS, true>(a, sm_count, scratch_words, st, &grid);
+        }
+    }
     if (allow_fast && logn >= 8 && logn <= 14) {
         if (path_out) *path_out = 1;
         switch (logn) {
@@ -139,6 +162,15 @@ cudaError_t encode_rows(const enc::RowArgs& a, u32 logn, bool allow_fast, int sm
     if (g > max_by_scratch) g = max_by_scratch;
     if (g < 1) return cudaErrorInvalidValue;
     k_encode_generic<<<(unsigned)g, threads, smem, st>>>(a, logn);
+    return cudaGetLastError();
+}
+
+cudaError_t widen_rows(const unsigned char* narrow, const u64* row_off, const unsigned char* row_w, u64* out, u32 rows, u32 n, int sm_count, cudaStream_t st) {
+    const size_t total = (size_t)rows * n;
+    size_t blocks = (total + 255) / 256, cap = (size_t)sm_count * 16;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    k_widen_rows<<<(unsigned)blocks, 256, 0, st>>>(narrow, row_off, row_w, out, rows, n);
     return cudaGetLastError();
 }
 

@@ -37,6 +37,16 @@
 
 namespace enc {
 
+// one packed witness word widened to its canonical field word
+GL_HD u64 widen_word(const unsigned char* base, u32 i, u32 w) {
+    long long x;
+    if (w == 1) x = (long long)reinterpret_cast<const signed char*>(base)[i];
+    else if (w == 2) x = (long long)reinterpret_cast<const short*>(base)[i];
+    else if (w == 4) x = (long long)reinterpret_cast<const int*>(base)[i];
+    else return reinterpret_cast<const u64*>(base)[i];
+    return x >= 0 ? (u64)x : GL_P - (u64)(-x);
+}
+
 // Shared-memory index swizzle: XOR every higher nibble into the low nibble.  Any access
 // in which the 16 lanes of a half-warp differ in four consecutive index bits (at any
 // position, in any order, e.g. bit-reversed) then touches 16 distinct 8-byte banks.
@@ -56,6 +66,12 @@ struct RowArgs {
     int zk;
     u64 ninv;          // n^-1
     u64* coef_out;     // FORM_COSET only: the row's n coefficients, in rows of 2n words (or NULL)
+    // packed witness rows (fast path, FORM_PCS): row r is `row_w[r]`-byte two's-complement little-endian integers (1, 2, 4; 8 =
+    // the canonical word itself) starting at byte `row_off[r]` of `narrow`; the first pass widens them (x >= 0 -> x, x < 0 ->
+    // p + x, field.rs:32-34) and leaves the 64-bit row in `data`, which the opening folds read later.  NULL: `data` is the input.
+    const unsigned char* narrow = nullptr;
+    const u64* row_off = nullptr;
+    const unsigned char* row_w = nullptr;
     int split;         // fast path: a CTA takes one (row, output residue) instead of a whole row, repeating the row's inverse transform:
                        // for a handful of rows (fewer than SMs / residues) the latency of a row falls from 1 + R transforms to 2
 };
@@ -247,7 +263,7 @@ struct Fast {
     // ---- the row pipeline ----
     // inverse transform of the message row, then the coefficient blocks x[idx] into the scratch slot.
     // c[i] = F[(n - i) mod n] / n with F the forward transform of the message, one residue a of F per pass set.
-    template <class Sync, int FORM = FORM_PCS>
+    template <class Sync, int FORM = FORM_PCS, bool NARROW = false>
     GL_HD static void row_coeffs(const RowArgs& a, u32 row, u64* S, const u64* TW, u64* X, u32 tid, u32 nt, Sync sync) {
         const u32 A = 1u << a.loga, n = N << a.loga, nn = N << a.logr, lognn = LOGN + a.logr;
         if constexpr (FORM == FORM_COEF) {
@@ -258,10 +274,19 @@ struct Fast {
         const u64* src = a.data + (size_t)row * n;
         const u64* pad = a.pads + (size_t)row * a.q;
         const u32 Tn = a.zk ? (n + a.q + n - 1) / n : 1u;
+        const unsigned char* nsrc = nullptr;
+        u32 nw = 8;
+        if constexpr (NARROW) { nsrc = a.narrow + a.row_off[row]; nw = a.row_w[row]; }
         for (u32 ra = 0; ra < A; ra++) {
             transform(S, TW, tid, nt,
                       [&](u32 i) {
-                          u64 y = src[i];
+                          u64 y;
+                          if constexpr (NARROW) {  // loga == 0 on this path: every word of the row passes here exactly once
+                              y = widen_word(nsrc, i, nw);
+                              const_cast<u64*>(src)[i] = y;
+                          } else {
+                              y = src[i];
+                          }
                           if (a.loga) {
                               for (u32 t = 1; t < A; t++)
                                   y = gl_add(y, gl_mul_fast(src[i + t * N], a.tw_nn[((t * ra) << (lognn - a.loga)) & (nn - 1)]));  // w_A^(t a)

@@ -10,6 +10,7 @@ namespace hlk {
 size_t encode_scratch_words(u32 logn, u32 T, int sm_count, u32 rows);
 cudaError_t encode_rows(const enc::RowArgs& a, u32 logn, bool allow_fast, int sm_count, size_t scratch_words,
                         cudaStream_t st, int* path_out);
+cudaError_t widen_rows(const unsigned char* narrow, const u64* row_off, const unsigned char* row_w, u64* out, u32 rows, u32 n, int sm_count, cudaStream_t st);
 cudaError_t encode_rows_form(const enc::RowArgs& a, u32 logn, int form, int sm_count, size_t scratch_words, cudaStream_t st);
 
 // hash.cu
