@@ -8,9 +8,12 @@ per row, keyed column hash), through to its salted Merkle root: inverse NTT, pad
 forward NTT, BLAKE3 column leaves, salted leaves, tree.  Metric: encoded bytes (rows * nn * 8)
 per second, the reference's own accounting for "commit GB/s".
 
+The witness is what a block's `A` matrix holds: int16-valued words (seeded, uniform) in all but eight rows, which carry
+full-width field words (the rows a prover fills with digests and masks).
 `value`  - inputs already resident in HBM, timed with CUDA events on the library's stream.
-`e2e`    - the same commitment through the host-pointer C-ABI call a prover makes
-           (hl_b200_commit_zk + hl_b200_store_merkle), pinned host inputs, H2D and D2H inside the clock.
+`e2e`    - the same commitment through the host-pointer C-ABI call a prover makes (hl_b200_commit_zk_packed: the witness
+           rows travel as their narrow bytes, as the reference's CUDA uploader sends them, and are widened on the device),
+           page-locked host inputs, H2D and D2H inside the clock.
 With N > 1 every rank commits its own blocks (D55 sharding: block k belongs to rank k mod N; no
 data-path collective) and the 32-byte roots are all-gathered over NCCL, as the join needs them.
 """
@@ -31,9 +34,18 @@ sys.path.insert(0, ROOT)
 
 WORK = {"log_cols": 14, "inv_rate": 2, "q": 280, "rows": 2504, "profile": "hashline-zk-mr1/b200-bench/1"}
 P = 0xFFFFFFFF00000001
-# dram__bytes_read.sum + dram__bytes_write.sum of one k_encode_fast<14,1024> launch at this workload (ncu capture summarised in
-# profiles/k_encode_fast_8b_A.md); the kernel's shape is fixed, so the figure is per launch of the timed kernel
-ENCODE_DRAM_TRAFFIC = 783_464_960 + 1_224_247_000
+WIDE_ROW_STEP = 313  # every 313th row of the witness holds full-width words (8 of 2,504)
+
+
+def encode_dram_traffic():
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch of the encoder at this workload, from the committed record of
+    the ncu capture (with its command) beside the text summary of the same capture; None when the record is absent."""
+    try:
+        rec = json.load(open(os.path.join(ROOT, "profiles", "k_encode_fast_8b_A.json")))
+        return int(rec["dram_bytes_read"]) + int(rec["dram_bytes_write"])
+    except (OSError, KeyError, ValueError):
+        return None
+
 PUBLISHED_GBPS = 26.0  # the reference's own published figure: its Metal backend on an M3 Ultra at this exact shape
 
 
@@ -47,6 +59,27 @@ def splitmix_fp(seed: int, n: int) -> np.ndarray:
         z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
         z = z ^ (z >> np.uint64(31))
     return z % np.uint64(P)
+
+
+def witness_words(seed: int, rows: int, n: int) -> np.ndarray:
+    """The block's `A` rows: int16-valued field words (x >= 0 as x, x < 0 as p + x), every WIDE_ROW_STEP-th row full-width."""
+    v = (splitmix_fp(seed, rows * n) % np.uint64(65536)).astype(np.int64) - 32768
+    out = np.where(v >= 0, v.astype(np.uint64), (v + (1 << 32)).astype(np.uint64) + np.uint64(P - (1 << 32))).reshape(rows, n)
+    wide = np.arange(0, rows, WIDE_ROW_STEP)
+    out[wide] = splitmix_fp(seed ^ 0x5A5A, wide.size * n).reshape(wide.size, n)
+    return out.reshape(-1)
+
+
+def block_inputs(block: int):
+    """seeded inputs of one block's commitment: (data, pads, salts) as the prover would hold them"""
+    import blake3 as b3
+
+    w = WORK
+    n, nn = 1 << w["log_cols"], (1 << w["log_cols"]) * w["inv_rate"]
+    data = witness_words(0xB2000100 + block, w["rows"], n)
+    pads = splitmix_fp(0xB2000200 + block, w["rows"] * w["q"])
+    salts = np.frombuffer(b3.blake3(b"bench-salts-%d" % block).digest(length=nn * 32), dtype=np.uint8).copy()
+    return data, pads, salts
 
 
 def coset_powers(nn: int) -> np.ndarray:
@@ -98,25 +131,28 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def cpu_commit_sample(o, rows_s: int, threads_note: str):
-    """One hiding commitment of `rows_s` rows at the workload's n / nn / q on the host cores (the CPU
-    restatement of pcs.rs:782-817); returns seconds."""
+def cpu_commit(o, data, pads, salts):
+    """One hiding commitment of the whole workload matrix on the host cores (the CPU restatement of pcs.rs:782-817): encode,
+    keyed column hash, salted leaves, tree.  Returns (seconds, root)."""
     w = WORK
-    n, nn, q = 1 << w["log_cols"], (1 << w["log_cols"]) * w["inv_rate"], w["q"]
+    n, nn, q, rows = 1 << w["log_cols"], (1 << w["log_cols"]) * w["inv_rate"], w["q"], w["rows"]
     tag = o.HashTag.for_profile(w["profile"])
-    data, pads = splitmix_fp(11, rows_s * n), splitmix_fp(12, rows_s * q)
-    salts = np.frombuffer(o.blake3(b"bench-salts", None, nn * 32), dtype=np.uint8).reshape(nn, 32)
     pows = o.coset_powers(7, nn)
     t0 = time.perf_counter()
-    enc = o.encode_rows_zk(data, rows_s, n, pads, q, pows, w["log_cols"] + 1)
-    leaves = o.hash_columns(enc, rows_s, nn, tag.column)
-    o.merkle_build(o.salt_leaves(leaves, salts, tag.leaf), tag.node)
-    return time.perf_counter() - t0
+    enc = o.encode_rows_zk(data, rows, n, pads, q, pows, w["log_cols"] + 1)
+    leaves = o.hash_columns(enc, rows, nn, tag.column)
+    levels = o.merkle_build(o.salt_leaves(leaves, salts.reshape(nn, 32), tag.leaf), tag.node)
+    return time.perf_counter() - t0, bytes(levels[-1])
+
+
+CPU_NOTE = ("all {rows} rows per step, the same seeded matrix the GPU arm commits: encode + keyed column hash + salt + tree; C restatement "
+            "(OpenMP, scalar BLAKE3 compiled for x86-64-v2) of the reference's Rust CPU path, which cannot be built in this image "
+            "(no cargo); the reference's own CPU hashes with the blake3 crate's SIMD code, so this baseline is slower than the reference's would be")
 
 
 def run_reference(args, rank: int) -> None:
-    """The reference arm: the prover's CPU path on this box's host cores.  The reference's own binary is
-    Rust and cannot be built here (no cargo in this image), so this times the C restatement of it
+    """The reference arm: the prover's CPU path on this box's host cores, on the whole workload matrix of block 0.  The
+    reference's own binary is Rust and cannot be built here (no cargo in this image), so this times the C restatement of it
     (oracle/, OpenMP over rows / column tiles, the reference's task grains) and says so."""
     if rank != 0:
         return
@@ -127,22 +163,24 @@ def run_reference(args, rank: int) -> None:
         o.set_threads(len(os.sched_getaffinity(0)))
     w = WORK
     nn = (1 << w["log_cols"]) * w["inv_rate"]
-    rows_s = 128
+    data, pads, salts = block_inputs(0)
+    root = b""
     for _ in range(args.warmup):
-        cpu_commit_sample(o, rows_s, "")
-    t = [cpu_commit_sample(o, rows_s, "") for _ in range(args.steps)]
+        cpu_commit(o, data, pads, salts)
+    t = []
+    for _ in range(args.steps):
+        sec, root = cpu_commit(o, data, pads, salts)
+        t.append(sec)
     sec = sum(t) / len(t)
-    gbps = rows_s * nn * 8 / sec / 1e9
+    gbps = w["rows"] * nn * 8 / sec / 1e9
     cores = o.num_threads()
     line = {
         "impl": "reference", "metric": "ligero_commit_GBps", "value": gbps, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u64",
-        "data": "synthetic", "config": workload_config(1) | {"sample_rows": rows_s},
-        "cpu_baseline": {"value": gbps, "unit": "GB/s", "cores": cores, "kind": "port",
-                         "sample": f"{rows_s} of {w['rows']} rows per step at the same n/nn/q: encode + column hash + salt + tree; "
-                                   "C restatement of the reference's Rust CPU path (no Rust toolchain in this image)"},
+        "data": "synthetic", "config": workload_config(1),
+        "cpu_baseline": {"value": gbps, "unit": "GB/s", "cores": cores, "kind": "port", "sample": CPU_NOTE.format(rows=w["rows"])},
         "e2e": {"value": gbps, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
+        "gpu_launches": 0, "root": root.hex(),
     }
     print(json.dumps(line))
 
@@ -152,6 +190,7 @@ def workload_config(world: int) -> dict:
     return {"workload": "Ligero hiding commit of the Llama-3-8B block's A matrix (W16R2_8B_T128_H24): "
                         f"{w['rows']} rows x 2^{w['log_cols']} -> 2^{w['log_cols'] + 1} (rate 1/2), Q = {w['q']}, keyed BLAKE3 leaves, salted tree to the root",
             "rows": w["rows"], "log_cols": w["log_cols"], "inv_rate": w["inv_rate"], "q_pad": w["q"],
+            "witness": f"int16-valued words (seeded uniform), every {WIDE_ROW_STEP}th row full-width field words; pads and salts seeded",
             "parallelism": f"d55-block-sharding x{world}" if world > 1 else "single",
             "l2": "inputs (328 MB) and encoding (656 MB) exceed the 126 MB L2; no flush needed",
             "published_baseline": "26.0 GB/s, reference Metal backend on Apple M3 Ultra, same shape"}
@@ -168,7 +207,7 @@ def structured_rhos(dense: np.ndarray) -> np.ndarray:
     return out
 
 
-def device_extras(dev, backend, np_data, np_pads, np_pows, col_key) -> dict:
+def device_extras(dev, backend, np_data, np_pads, np_pows, col_key, only: str = "") -> dict:
     """Device time (CUDA events inside the library, per kernel family) of the rest of one block's device work at the
     same shape: the opening of `A` (38 row combinations with pads, 280 gathered columns), a 2^21-point degree-3
     zero-check sumcheck batch (the LogUp query side), the LogUp helper column of 2^21 queries, and one FFN weight fold."""
@@ -176,207 +215,259 @@ def device_extras(dev, backend, np_data, np_pads, np_pows, col_key) -> dict:
     log_cols, ir, q, rows = w["log_cols"], w["inv_rate"], w["q"], w["rows"]
     ctx = dev.ctx
     out = {}
-    st, _ = dev.try_commit_zk_keyed(log_cols, ir, np_data, np_pads, np_pows, log_cols + 1, col_key)
-    rhos = splitmix_fp(77, 38 * rows * 2).reshape(38, rows, 2)
-    idx = (splitmix_fp(78, 280) % np.uint64(st.nn)).astype(np.uint64)
-    for _ in range(2):
-        st.fold_rows_with_pads(rhos)
-        st.columns(idx)
-    ctx.timing_read(reset=True)
-    ctx.timing_enable(True)
-    for _ in range(3):
-        st.fold_rows_with_pads(rhos)
-        st.columns(idx)
-    t = ctx.timing_read(reset=True)
-    out["open_A_fold_38rho_ms"] = t["fold"][0] / 3
-    out["open_A_gather_280cols_ms"] = t["gather"][0] / 3
-    # the shape of a real opening (pcs.rs:851-891, 952-973): 37 group vectors that live on their claim's 32 plane rows and
-    # the two mask rows, one dense proximity vector; the dense figure above is the worst case
-    srho = structured_rhos(rhos)
-    for _ in range(2):
-        st.fold_rows_with_pads(srho)
-    ctx.timing_read(reset=True)
-    for _ in range(3):
-        st.fold_rows_with_pads(srho)
-    out["open_A_fold_37_plane_vectors_1_dense_ms"] = ctx.timing_read(reset=True)["fold"][0] / 3
-    st.free()
-    n = 21
-    tables = splitmix_fp(79, 3 * (1 << n) * 2).reshape(3, 1 << n, 2)
-    alpha = splitmix_fp(80, 2).reshape(1, 2)
-    mask = splitmix_fp(81, ((n + 1) * 3 + 2) * 2).reshape(-1, 2)
-    for rep in range(3):
-        ev = backend.B200Rounds(ctx, backend.POLY_LOGUP_Q, tables, 3, alpha)
-        if rep == 1:
-            ctx.timing_read(reset=True)
-        ev.batched(n, bytes(32), 0, None, mask=mask, mask_vars=n + 1, mask_c=(3, 5), recover_one=True, claim=(0, 0))
-        ev.free()
-    t = ctx.timing_read(reset=True)
-    out["sumcheck_logup_q_2^21_deg3_21rounds_ms"] = t["rounds"][0] / 2
-    nq = 1 << 21
-    qidx = (splitmix_fp(82, nq) % np.uint64(1 << 16)).astype(np.int32)
-    qout = (splitmix_fp(83, nq) % np.uint64(1 << 15)).astype(np.int32)
-    for rep in range(3):
-        if rep == 1:
-            ctx.timing_read(reset=True)
-        ctx.logup_helpers(qidx, qout, (11, 12), (13, 14), (15, 16))
-    t = ctx.timing_read(reset=True)
-    out["logup_helpers_2^21_ms"] = t["logup"][0] / 2
-    wm = (splitmix_fp(84, 4096 * 14336) % np.uint64(256)).astype(np.uint8).view(np.int8).reshape(4096, 14336)
-    cw = splitmix_fp(85, 14336 * 2).reshape(14336, 2)
-    for rep in range(3):
-        if rep == 1:
-            ctx.timing_read(reset=True)
-        ctx.fold_cols_i8(wm, cw)
-    t = ctx.timing_read(reset=True)
-    out["fold_cols_i8_4096x14336_ms"] = t["fold"][0] / 2
-    rw = splitmix_fp(89, 4096 * 2).reshape(4096, 2)
-    for rep in range(3):
-        if rep == 1:
-            ctx.timing_read(reset=True)
-        ctx.fold_rows_i8(wm, rw)
-    out["fold_rows_i8_4096x14336_ms"] = ctx.timing_read(reset=True)["fold"][0] / 2
-    # the pads and salts of the hiding commitment of `A` expanded on the device from the caller's generator key
-    # (rows * q field draws, then nn salts of four words: 11.2 MB + 1 MB of BLAKE3 extended output)
     import torch
 
-    d_rng = torch.empty(rows * q + 4 * ((1 << log_cols) * ir), dtype=torch.int64, device="cuda")
-    nn_ = (1 << log_cols) * ir
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    cs = torch.cuda.current_stream()
-    for rep in range(3):
-        if rep == 1:
-            ev0.record(cs)
-        ctx.rng_fill_dev(bytes(range(32)), 0, rows * q, True, d_rng.data_ptr())
-        ctx.rng_fill_dev(bytes(range(32)), 2 * rows * q, 4 * nn_, False, d_rng.data_ptr() + 8 * rows * q)
-    ev1.record(cs)
-    torch.cuda.synchronize()
-    out["draw_pads_and_salts_of_A_ms"] = ev0.elapsed_time(ev1) / 2
-    del d_rng
-    # the helper half of H for the byte-table lookups (protocol.rs:1700-1800): one job = 2^25 looked word pairs, two
-    # 256-entry inverse tables, two planes written (2 x 8 B read, 2 x 8 B written per pair)
-    npair = 1 << 25
-    d_a = torch.from_numpy((splitmix_fp(92, npair) % np.uint64(256)).astype(np.int64)).cuda()
-    d_b = torch.from_numpy((splitmix_fp(93, npair) % np.uint64(256)).astype(np.int64)).cuda()
-    d_t = torch.empty(1024, dtype=torch.int64, device="cuda")
-    d_h = torch.empty(2 * npair, dtype=torch.int64, device="cuda")
-    torch.cuda.synchronize()
-    for rep in range(3):
-        if rep == 1:
-            ctx.timing_read(reset=True)
-        ctx.lookup_inverse_table((21, 22), (23, 24), 8, d_t.data_ptr())
-        ctx.lookup_inverse_table((21, 22), (25, 26), 8, d_t.data_ptr() + 4096)
-        ctx.lookup_helpers_dev(d_a.data_ptr(), d_t.data_ptr(), 8, (23, 24), (21, 22), npair, d_h.data_ptr(), d_h.data_ptr() + 8 * npair,
-                               d_b=d_b.data_ptr(), d_table_b=d_t.data_ptr() + 4096, log_b=8, g_b=(25, 26))
-    out["lookup_helpers_u8_pairs_2^25_ms"] = ctx.timing_read(reset=True)["logup"][0] / 2
-    del d_a, d_b, d_t, d_h
-    # a slot's tables built on the device from the resident rows of `A`: an eq cube of 2^21 entries and a witness plane of
-    # 2^19 entries partially evaluated at 3 fixed coordinates (8 rows of 2^14 words each folded per entry)
-    st, _ = dev.try_commit_zk_keyed(log_cols, ir, np_data, np_pads, np_pows, log_cols + 1, col_key)
-    point = splitmix_fp(90, 21 * 2).reshape(21, 2)
-    coords = [("fixed", (int(a), int(b))) for a, b in splitmix_fp(91, 6).reshape(3, 2)] + [("rho", k) for k in range(19)]
-    for rep in range(3):
-        if rep == 1:
-            ctx.timing_read(reset=True)
-        t21, t19 = backend.B200Tables(ctx, 1, 21), backend.B200Tables(ctx, 1, 19)
-        t21.plan_eq(0, point, 0)
-        t19.plan_plane(0, st, coords, [(0, (1, 0))])
-        t21.flush(); t19.flush()
-        t21.free(); t19.free()
-    t = ctx.timing_read(reset=True)
-    out["tables_eq_2^21_plus_plane_2^19_x8_ms"] = t["tables"][0] / 2
-    slot_replay(dev, backend, st, rows, 1 << log_cols)  # warm-up: first launches size the device's local-memory pool
-    out["slot_replay"] = slot_replay(dev, backend, st, rows, 1 << log_cols)
-    st.free()
-    # the heaviest slot polynomial of a block as data: the recorded structure of the D zero-check (60 tables, 71 nodes,
-    # declared degree 5) with seeded coefficients, at 2^19 points (the 8B block domain of this slot: 128 tokens x width 4096), through the interpreting evaluator
-    prog, deg, base = slot14_program(backend.SlotProgram)
-    n = 19
-    tables = slot14_tables(prog, base, n)
-    mask = splitmix_fp(88, ((n + 1) * deg + 2) * 2).reshape(-1, 2)
-    for rep in range(3):
-        ev = backend.B200Rounds(ctx, prog, tables, deg)
-        if rep == 1:
-            ctx.timing_read(reset=True)
-        ev.batched(n, bytes(32), 0, None, mask=mask, mask_vars=n + 1, mask_c=(3, 5), recover_one=True, claim=(0, 0))
-        ev.free()
-    t = ctx.timing_read(reset=True)
-    out["sumcheck_slot_program_60tables_71nodes_deg5_2^19_ms"] = t["rounds"][0] / 2
-    # the masking commitment M of a block (zk.rs:447-656): 24 masks -> 48 message rows of 512 + 4 rows of 1024 coefficients
-    # on the coset of 4096, column hashes, salted tree; then the opening's product polynomial, proximity fold, 256 columns
-    S = 24
-    mm = splitmix_fp(94, 2 * S * 512).reshape(2 * S, 512)
-    mm[:, 320:] = 0
-    mcoef, mpows = splitmix_fp(95, 4 * 1024).reshape(4, 1024), coset_powers(4096)
-    msalts = splitmix_fp(96, 4096 * 4).view(np.uint8).reshape(4096, 32)
-    mws, mrs = splitmix_fp(97, S * 512 * 2).reshape(S, 512, 2), splitmix_fp(98, (2 * S + 2) * 2).reshape(-1, 2)
-    midx = (splitmix_fp(99, 256) % np.uint64(4096)).astype(np.uint64)
-    t_c = t_o = 0.0
-    for rep in range(4):
-        t0 = time.perf_counter()
-        dm = backend.mask_commit(ctx, mm, mcoef, mpows, col_key)
-        dm.merkle(msalts, col_key, col_key)
-        t1 = time.perf_counter()
-        dm.open_q(mws); dm.prox(mrs); dm.columns(midx)
-        t2 = time.perf_counter()
-        dm.free()
-        if rep:
-            t_c, t_o = t_c + (t1 - t0) * 1e3 / 3, t_o + (t2 - t1) * 1e3 / 3
-    out["mask_M_24masks_commit_and_tree_wall_ms"] = t_c  # host wall time of the calls: uploads, launches, read-backs
-    out["mask_M_24masks_open_wall_ms"] = t_o
-    # the witness weight products of one 8B block at T = 128 (witness.rs:818-835): q, k, v, o, gate, up, down with the
-    # weights resident; int16 activations, int8 weights, exact int64 planes
-    wp_shapes = [("q", 4096, 4096), ("k", 4096, 1024), ("v", 4096, 1024), ("o", 4096, 4096), ("gate", 4096, 14336), ("up", 4096, 14336), ("down", 14336, 4096)]
-    gw = torch.Generator(device="cuda").manual_seed(5)
-    d_wmax = torch.randint(-128, 128, (4096 * 14336,), dtype=torch.int8, device="cuda", generator=gw)
-    d_xw = torch.randint(-32768, 32768, (128 * 14336,), dtype=torch.int64, device="cuda", generator=gw)
-    d_ow = torch.empty(128 * 14336, dtype=torch.int64, device="cuda")
-    torch.cuda.synchronize()
-    per, macs = {}, 0
-    for name, kk, nn2 in wp_shapes:
-        for rep in range(4):
+    def want(name):  # --only a,b,c limits the run to those families (a profiler capture of one kernel family)
+        return not only or name in only.split(",")
+
+    rhos = splitmix_fp(77, 38 * rows * 2).reshape(38, rows, 2)
+    ctx.timing_read(reset=True)
+    ctx.timing_enable(True)
+    if want("open"):
+        st, _ = dev.try_commit_zk_keyed(log_cols, ir, np_data, np_pads, np_pows, log_cols + 1, col_key)
+        idx = (splitmix_fp(78, 280) % np.uint64(st.nn)).astype(np.uint64)
+        for _ in range(2):
+            st.fold_rows_with_pads(rhos)
+            st.columns(idx)
+        ctx.timing_read(reset=True)
+        ctx.timing_enable(True)
+        for _ in range(3):
+            st.fold_rows_with_pads(rhos)
+            st.columns(idx)
+        t = ctx.timing_read(reset=True)
+        out["open_A_fold_38rho_ms"] = t["fold"][0] / 3
+        out["open_A_gather_280cols_ms"] = t["gather"][0] / 3
+        # the shape of a real opening (pcs.rs:851-891, 952-973): 37 group vectors that live on their claim's 32 plane rows and
+        # the two mask rows, one dense proximity vector; the dense figure above is the worst case
+        srho = structured_rhos(rhos)
+        for _ in range(2):
+            st.fold_rows_with_pads(srho)
+        ctx.timing_read(reset=True)
+        for _ in range(3):
+            st.fold_rows_with_pads(srho)
+        out["open_A_fold_37_plane_vectors_1_dense_ms"] = ctx.timing_read(reset=True)["fold"][0] / 3
+        st.free()
+    if want("sumcheck"):
+        n = 21
+        tables = splitmix_fp(79, 3 * (1 << n) * 2).reshape(3, 1 << n, 2)
+        alpha = splitmix_fp(80, 2).reshape(1, 2)
+        mask = splitmix_fp(81, ((n + 1) * 3 + 2) * 2).reshape(-1, 2)
+        for rep in range(3):
+            ev = backend.B200Rounds(ctx, backend.POLY_LOGUP_Q, tables, 3, alpha)
             if rep == 1:
                 ctx.timing_read(reset=True)
-            assert ctx.witness_product_dev(128, d_xw.data_ptr(), 128 * kk, kk, d_wmax.data_ptr(), kk * nn2, kk, nn2, nn2, 128 * nn2, False, d_ow.data_ptr())
-        per[name] = round(ctx.timing_read(reset=True)["witness"][0] / 3, 4)
-        macs += 128 * kk * nn2
-    tot = sum(per.values())
-    out["witness_products_8B_block_T128_ms"] = tot
-    mma_peak = ctx.mma_i8_peak(2000)
-    out["witness_products_detail"] = {"per_product_ms": per, "int8_TMAC_per_s": 2 * macs / (tot * 1e-3) / 1e12,
-                                      "mma_m16n8k32_register_resident_TMAC_per_s": mma_peak / 1e12,
-                                      "weight_bytes": sum(k_ * n_ for _, k_, n_ in wp_shapes),
-                                      "weights_read_once_at_measured_hbm_ms": sum(k_ * n_ for _, k_, n_ in wp_shapes) / 6549.8e9 * 1e3}
-    del d_wmax, d_xw, d_ow
-    # the T256 / T512 profiles (shape.rs:248-262): the same 41 M words as rows of 2^15 and 2^16, which run as 2 or 4
-    # shared-memory transforms of 2^14 each way
-    for lc, rws in ((15, rows // 2), (16, rows // 4)):
-        nnl = (1 << lc) * ir
-        dd = torch.from_numpy(splitmix_fp(0xB2000300 + lc, rws << lc).view(np.int64)).cuda()
-        dp = torch.from_numpy(splitmix_fp(0xB2000400 + lc, rws * q).view(np.int64)).cuda()
-        dw = torch.from_numpy(coset_powers(nnl).view(np.int64)).cuda()
+            ev.batched(n, bytes(32), 0, None, mask=mask, mask_vars=n + 1, mask_c=(3, 5), recover_one=True, claim=(0, 0))
+            ev.free()
+        t = ctx.timing_read(reset=True)
+        out["sumcheck_logup_q_2^21_deg3_21rounds_ms"] = t["rounds"][0] / 2
+    if want("helpers"):
+        nq = 1 << 21
+        qidx = (splitmix_fp(82, nq) % np.uint64(1 << 16)).astype(np.int32)
+        qout = (splitmix_fp(83, nq) % np.uint64(1 << 15)).astype(np.int32)
+        for rep in range(3):
+            if rep == 1:
+                ctx.timing_read(reset=True)
+            ctx.logup_helpers(qidx, qout, (11, 12), (13, 14), (15, 16))
+        t = ctx.timing_read(reset=True)
+        out["logup_helpers_2^21_ms"] = t["logup"][0] / 2
+    if want("i8folds"):
+        wm = (splitmix_fp(84, 4096 * 14336) % np.uint64(256)).astype(np.uint8).view(np.int8).reshape(4096, 14336)
+        cw = splitmix_fp(85, 14336 * 2).reshape(14336, 2)
+        for rep in range(3):
+            if rep == 1:
+                ctx.timing_read(reset=True)
+            ctx.fold_cols_i8(wm, cw)
+        t = ctx.timing_read(reset=True)
+        out["fold_cols_i8_4096x14336_ms"] = t["fold"][0] / 2
+        rw = splitmix_fp(89, 4096 * 2).reshape(4096, 2)
+        for rep in range(3):
+            if rep == 1:
+                ctx.timing_read(reset=True)
+            ctx.fold_rows_i8(wm, rw)
+        out["fold_rows_i8_4096x14336_ms"] = ctx.timing_read(reset=True)["fold"][0] / 2
+    if want("rng"):
+        # the pads and salts of the hiding commitment of `A` expanded on the device from the caller's generator key
+        # (rows * q field draws, then nn salts of four words: 11.2 MB + 1 MB of BLAKE3 extended output)
+
+        d_rng = torch.empty(rows * q + 4 * ((1 << log_cols) * ir), dtype=torch.int64, device="cuda")
+        nn_ = (1 << log_cols) * ir
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        cs = torch.cuda.current_stream()
+        for rep in range(3):
+            if rep == 1:
+                ev0.record(cs)
+            ctx.rng_fill_dev(bytes(range(32)), 0, rows * q, True, d_rng.data_ptr())
+            ctx.rng_fill_dev(bytes(range(32)), 2 * rows * q, 4 * nn_, False, d_rng.data_ptr() + 8 * rows * q)
+        ev1.record(cs)
+        torch.cuda.synchronize()
+        out["draw_pads_and_salts_of_A_ms"] = ev0.elapsed_time(ev1) / 2
+        del d_rng
+    if want("lookup"):
+        # the helper half of H for the byte-table lookups (protocol.rs:1700-1800): one job = 2^25 looked word pairs, two
+        # 256-entry inverse tables, two planes written (2 x 8 B read, 2 x 8 B written per pair)
+        npair = 1 << 25
+        d_a = torch.from_numpy((splitmix_fp(92, npair) % np.uint64(256)).astype(np.int64)).cuda()
+        d_b = torch.from_numpy((splitmix_fp(93, npair) % np.uint64(256)).astype(np.int64)).cuda()
+        d_t = torch.empty(1024, dtype=torch.int64, device="cuda")
+        d_h = torch.empty(2 * npair, dtype=torch.int64, device="cuda")
+        torch.cuda.synchronize()
+        for rep in range(3):
+            if rep == 1:
+                ctx.timing_read(reset=True)
+            ctx.lookup_inverse_table((21, 22), (23, 24), 8, d_t.data_ptr())
+            ctx.lookup_inverse_table((21, 22), (25, 26), 8, d_t.data_ptr() + 4096)
+            ctx.lookup_helpers_dev(d_a.data_ptr(), d_t.data_ptr(), 8, (23, 24), (21, 22), npair, d_h.data_ptr(), d_h.data_ptr() + 8 * npair,
+                                   d_b=d_b.data_ptr(), d_table_b=d_t.data_ptr() + 4096, log_b=8, g_b=(25, 26))
+        out["lookup_helpers_u8_pairs_2^25_ms"] = ctx.timing_read(reset=True)["logup"][0] / 2
+        del d_a, d_b, d_t, d_h
+    if want("slots"):
+        # a slot's tables built on the device from the resident rows of `A`: an eq cube of 2^21 entries and a witness plane of
+        # 2^19 entries partially evaluated at 3 fixed coordinates (8 rows of 2^14 words each folded per entry)
+        st, _ = dev.try_commit_zk_keyed(log_cols, ir, np_data, np_pads, np_pows, log_cols + 1, col_key)
+        point = splitmix_fp(90, 21 * 2).reshape(21, 2)
+        coords = [("fixed", (int(a), int(b))) for a, b in splitmix_fp(91, 6).reshape(3, 2)] + [("rho", k) for k in range(19)]
+        for rep in range(3):
+            if rep == 1:
+                ctx.timing_read(reset=True)
+            t21, t19 = backend.B200Tables(ctx, 1, 21), backend.B200Tables(ctx, 1, 19)
+            t21.plan_eq(0, point, 0)
+            t19.plan_plane(0, st, coords, [(0, (1, 0))])
+            t21.flush(); t19.flush()
+            t21.free(); t19.free()
+        t = ctx.timing_read(reset=True)
+        out["tables_eq_2^21_plus_plane_2^19_x8_ms"] = t["tables"][0] / 2
+        m125 = _m125_replay_slots(backend.SlotProgram)
+        note125 = "the reference's recorded 125M slot graphs (T512 / d768 / f2048) at their recorded sizes: 23 slots, 258 tables, cubes of 2^8 .. 2^22 points"
+        slot_replay(dev, backend, st, rows, 1 << log_cols, m125, note125)  # warm-up: first launches size the device's local-memory pool
+        out["slot_replay"] = slot_replay(dev, backend, st, rows, 1 << log_cols, m125, note125)
+        w16 = _w16r2_slots(backend.SlotProgram)
+        note8b = ("the slot graphs of a real W16R2 block core (recorded coefficient values) at the cube sizes of the Llama-3-8B block shape "
+                  "W16R2_8B_T128_H24: 23 slots, 1.44 GB of tables")
+        slot_replay(dev, backend, st, rows, 1 << log_cols, w16, note8b)
+        out["slot_replay_8B_T128"] = slot_replay(dev, backend, st, rows, 1 << log_cols, w16, note8b)
+        # the opening of `H` (10 row combinations: the proximity vector and nine that live on a plane's rows) on this store as a stand-in
+        hrho = structured_rhos(rhos[:10])
+        for rep in range(3):
+            if rep == 1:
+                ctx.timing_read(reset=True)
+            st.fold_rows_with_pads(hrho)
+        out["open_H_fold_9_plane_vectors_1_dense_ms"] = ctx.timing_read(reset=True)["fold"][0] / 2
+        st.free()
+    if want("slot_program"):
+        # the heaviest slot polynomial of a block as data: the recorded structure of the D zero-check (60 tables, 71 nodes,
+        # declared degree 5) with seeded coefficients, at 2^19 points (the 8B block domain of this slot: 128 tokens x width 4096), through the interpreting evaluator
+        prog, deg, base = slot14_program(backend.SlotProgram)
+        n = 19
+        tables = slot14_tables(prog, base, n)
+        mask = splitmix_fp(88, ((n + 1) * deg + 2) * 2).reshape(-1, 2)
+        for rep in range(3):
+            ev = backend.B200Rounds(ctx, prog, tables, deg)
+            if rep == 1:
+                ctx.timing_read(reset=True)
+            ev.batched(n, bytes(32), 0, None, mask=mask, mask_vars=n + 1, mask_c=(3, 5), recover_one=True, claim=(0, 0))
+            ev.free()
+        t = ctx.timing_read(reset=True)
+        out["sumcheck_slot_program_60tables_71nodes_deg5_2^19_ms"] = t["rounds"][0] / 2
+    if want("mask"):
+        # the masking commitment M of a block (zk.rs:447-656): 24 masks -> 48 message rows of 512 + 4 rows of 1024 coefficients
+        # on the coset of 4096, column hashes, salted tree; then the opening's product polynomial, proximity fold, 256 columns
+        S = 24
+        mm = splitmix_fp(94, 2 * S * 512).reshape(2 * S, 512)
+        mm[:, 320:] = 0
+        mcoef, mpows = splitmix_fp(95, 4 * 1024).reshape(4, 1024), coset_powers(4096)
+        msalts = splitmix_fp(96, 4096 * 4).view(np.uint8).reshape(4096, 32)
+        mws, mrs = splitmix_fp(97, S * 512 * 2).reshape(S, 512, 2), splitmix_fp(98, (2 * S + 2) * 2).reshape(-1, 2)
+        midx = (splitmix_fp(99, 256) % np.uint64(4096)).astype(np.uint64)
+        t_c = t_o = 0.0
+        for rep in range(4):
+            t0 = time.perf_counter()
+            dm = backend.mask_commit(ctx, mm, mcoef, mpows, col_key)
+            dm.merkle(msalts, col_key, col_key)
+            t1 = time.perf_counter()
+            dm.open_q(mws); dm.prox(mrs); dm.columns(midx)
+            t2 = time.perf_counter()
+            dm.free()
+            if rep:
+                t_c, t_o = t_c + (t1 - t0) * 1e3 / 3, t_o + (t2 - t1) * 1e3 / 3
+        out["mask_M_24masks_commit_and_tree_wall_ms"] = t_c  # host wall time of the calls: uploads, launches, read-backs
+        out["mask_M_24masks_open_wall_ms"] = t_o
+    if want("witness"):
+        # the witness weight products of one 8B block at T = 128 (witness.rs:818-835): q, k, v, o, gate, up, down with the
+        # weights resident; int16 activations, int8 weights, exact int64 planes
+        wp_shapes = [("q", 4096, 4096), ("k", 4096, 1024), ("v", 4096, 1024), ("o", 4096, 4096), ("gate", 4096, 14336), ("up", 4096, 14336), ("down", 14336, 4096)]
+        gw = torch.Generator(device="cuda").manual_seed(5)
+        d_wmax = torch.randint(-128, 128, (4096 * 14336,), dtype=torch.int8, device="cuda", generator=gw)
+        d_xw = torch.randint(-32768, 32768, (128 * 14336,), dtype=torch.int64, device="cuda", generator=gw)
+        d_ow = torch.empty(128 * 14336, dtype=torch.int64, device="cuda")
+        torch.cuda.synchronize()
+        per, macs = {}, 0
+        for name, kk, nn2 in wp_shapes:
+            for rep in range(4):
+                if rep == 1:
+                    ctx.timing_read(reset=True)
+                assert ctx.witness_product_dev(128, d_xw.data_ptr(), 128 * kk, kk, d_wmax.data_ptr(), kk * nn2, kk, nn2, nn2, 128 * nn2, False, d_ow.data_ptr())
+            per[name] = round(ctx.timing_read(reset=True)["witness"][0] / 3, 4)
+            macs += 128 * kk * nn2
+        tot = sum(per.values())
+        out["witness_products_8B_block_T128_ms"] = tot
+        mma_peak = ctx.mma_i8_peak(2000)
+        out["witness_products_detail"] = {"per_product_ms": per, "int8_TMAC_per_s": 2 * macs / (tot * 1e-3) / 1e12,
+                                          "mma_m16n8k32_register_resident_TMAC_per_s": mma_peak / 1e12,
+                                          "weight_bytes": sum(k_ * n_ for _, k_, n_ in wp_shapes),
+                                          "weights_read_once_at_measured_hbm_ms": sum(k_ * n_ for _, k_, n_ in wp_shapes) / 6549.8e9 * 1e3}
+        del d_wmax, d_xw, d_ow
+    if want("long_rows"):
+        # the T256 / T512 profiles (shape.rs:248-262): the same 41 M words as rows of 2^15 and 2^16, which run as 2 or 4
+        # shared-memory transforms of 2^14 each way
+        for lc, rws in ((15, rows // 2), (16, rows // 4)):
+            nnl = (1 << lc) * ir
+            dd = torch.from_numpy(splitmix_fp(0xB2000300 + lc, rws << lc).view(np.int64)).cuda()
+            dp = torch.from_numpy(splitmix_fp(0xB2000400 + lc, rws * q).view(np.int64)).cuda()
+            dw = torch.from_numpy(coset_powers(nnl).view(np.int64)).cuda()
+            torch.cuda.synchronize()
+            for rep in range(4):
+                if rep == 1:
+                    ctx.timing_read(reset=True)
+                stl = dev.commit_zk_dev(lc, ir, dd.data_ptr(), rws, dp.data_ptr(), q, dw.data_ptr(), col_key)
+                stl.free()
+            t = ctx.timing_read(reset=True)
+            out[f"commit_rows_of_2^{lc}_x{rws}_encode_ms"] = t["encode"][0] / 3
+            out[f"commit_rows_of_2^{lc}_x{rws}_hash_ms"] = t["hash"][0] / 3
+            del dd, dp, dw
+    if want("commit_h"):
+        # the helper commitment `H` of the block: 2,606 rows of 2^14 full-width words (the helper columns are field inverses), resident
+        rows_h = 2606
+        dd = torch.from_numpy(splitmix_fp(0xB2000500, rows_h << log_cols).view(np.int64)).cuda()
+        dp = torch.from_numpy(splitmix_fp(0xB2000600, rows_h * q).view(np.int64)).cuda()
+        dw = torch.from_numpy(coset_powers((1 << log_cols) * ir).view(np.int64)).cuda()
+        dsalt = torch.zeros(((1 << log_cols) * ir) * 32, dtype=torch.uint8, device="cuda")
+        dlev = torch.empty((2 * ((1 << log_cols) * ir) - 1) * 32, dtype=torch.uint8, device="cuda")
+        ea, eb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        cs = torch.cuda.current_stream()
         torch.cuda.synchronize()
         for rep in range(4):
             if rep == 1:
-                ctx.timing_read(reset=True)
-            stl = dev.commit_zk_dev(lc, ir, dd.data_ptr(), rws, dp.data_ptr(), q, dw.data_ptr(), col_key)
-            stl.free()
-        t = ctx.timing_read(reset=True)
-        out[f"commit_rows_of_2^{lc}_x{rws}_encode_ms"] = t["encode"][0] / 3
-        out[f"commit_rows_of_2^{lc}_x{rws}_hash_ms"] = t["hash"][0] / 3
-        del dd, dp, dw
-    ctx.timing_enable(False)
-    return out
+                ea.record(cs)
+            sth = dev.commit_zk_dev(log_cols, ir, dd.data_ptr(), rows_h, dp.data_ptr(), q, dw.data_ptr(), col_key)
+            sth.merkle_dev(dsalt.data_ptr(), col_key, col_key, dlev.data_ptr())
+            sth.free()
+        eb.record(cs)
+        torch.cuda.synchronize()
+        out["commit_H_2606x2^14_to_root_ms"] = ea.elapsed_time(eb) / 3
+        del dd, dp, dw, dsalt, dlev
+        ctx.timing_enable(False)
+        return out
 
 
-def slot14_program(SP):
-    """the recorded structure of the D zero-check (60 tables, 71 nodes, declared degree 5) with seeded coefficients"""
+def _m125_slots():
     import json as _json
 
-    slot = _json.load(open(os.path.join(ROOT, "tests", "golden", "slot_ir_m125.json")))["slots"][14]
-    prog, cs = SP(len(slot["table_fields"])), iter(splitmix_fp(86, 4096).tolist())
+    return _json.load(open(os.path.join(ROOT, "bench_data", "slot_ir_m125.json")))["slots"]
 
-    def coef(cls):
-        return "one" if cls == "one" else (next(cs) % (1 << 40), 0) if cls == "kbase" else (next(cs), next(cs))
+
+def _program_from_structure(SP, slot, coef):
+    """a recorded slot graph (structure only) with coefficients drawn by class from `coef`"""
+    prog = SP(len(slot["table_fields"]))
 
     def fw(f):
         return SP.node(f["n"]) if "n" in f else f["t"]
@@ -388,7 +479,18 @@ def slot14_program(SP):
             prog.sum([(coef(c), [fw(f) for f in fs]) for c, fs in nd["sum"]])
     for t in slot["terms"]:
         prog.term(coef(t["coef"]), t["wrapper"], [fw(f) for f in t["inner"]])
-    return prog, slot["declared_degree"], [f == "base" for f in slot["table_fields"]]
+    return prog
+
+
+def slot14_program(SP):
+    """the recorded structure of the D zero-check (60 tables, 71 nodes, declared degree 5) with seeded coefficients"""
+    slot = _m125_slots()[14]
+    cs = iter(splitmix_fp(86, 4096).tolist())
+
+    def coef(cls):
+        return "one" if cls == "one" else (next(cs) % (1 << 40), 0) if cls == "kbase" else (next(cs), next(cs))
+
+    return _program_from_structure(SP, slot, coef), slot["declared_degree"], [f == "base" for f in slot["table_fields"]]
 
 
 def slot14_tables(prog, base, nv):
@@ -401,46 +503,76 @@ def slot14_tables(prog, base, nv):
     return t
 
 
-def slot_replay(dev, backend, st, rows, n) -> dict:
-    """All 23 slot sumchecks of one block, replayed on the device at the sizes the reference records for its 125M shape
-    (the one shape whose slot graphs it exports: tests/golden/slot_ir_m125.json): per slot the tables are built ON THE
-    DEVICE from the resident rows of a commitment (an eq cube for table 0, committed planes for the rest: base-valued
-    where the reference records a base table, partially evaluated at one fixed coordinate where it records an extension
-    table), then the masked sumcheck runs with the device Fiat-Shamir step.  Coefficients, points and plane positions are
-    seeded; the graphs, table counts, degrees and cube sizes are the reference's.  This is device WORK of the recorded
-    shape, not a proof: the protocol layer that would drive it is the reference's Rust crate."""
+# main-round counts of the 23 slots at the Llama-3-8B block shape W16R2_8B_T128_H24 (T = 128, width 4096, hidden 14336, 32 query and
+# 8 key-value heads of 128, rows of 2^14 words): shape.rs:2660-2714 `slots()` over the domain logs of shape.rs:2415-2451 with the
+# lift of layout.rs:175-181 (T 7, L 14, D 19, Q 19, Kv 17, S 19, F 21, Tab 14; matmul inner axes 12, 12, 12, 10, 10, 12, 12, 12, 14)
+SLOT_ROUNDS_8B = [19, 19, 7, 14, 19, 12, 12, 12, 10, 10, 12, 12, 12, 14, 19, 19, 17, 19, 21, 14, 14, 19, 19]
+SLOT_NAMES = ["SS", "SSM", "TZC", "LZC", "RS", "QMM", "KMM", "VMM", "SCORE", "PV", "WO", "GMM", "UMM", "DMM", "DZC", "QZC", "KVZC", "SZC", "FZC", "TAB", "ZS",
+              "IO_IN", "IO_OUT"]
+
+
+def _w16r2_slots(SP):
+    """[(name, main rounds at the 8B shape, degree, program, per-table kind)] from the slot graphs of a real W16R2 block core with
+    their recorded coefficient values (bench_data/l11_slot_graphs.json)"""
     import json as _json
 
-    ctx = dev.ctx
-    slots = _json.load(open(os.path.join(ROOT, "tests", "golden", "slot_ir_m125.json")))["slots"]
-    SP = backend.SlotProgram
-    words_avail = rows * n
-    per_slot, total_tables_ms, total_rounds_ms, total_bytes = {}, 0.0, 0.0, 0
+    out = []
+    for sl in _json.load(open(os.path.join(ROOT, "bench_data", "l11_slot_graphs.json")))["slots"]:
+        prog = SP(len(sl["tables"]))
+
+        def cv(c):
+            return "one" if c[2] == "one" else "neg-one" if c[2] == "neg-one" else (c[0], c[1])
+
+        def fw(f):
+            return SP.node(f[1]) if f[0] == "n" else f[1]
+
+        for nd in sl["nodes"]:
+            if "affine" in nd:
+                prog.affine((nd["konst"][0], nd["konst"][1]), [(cv(c), t) for c, t in nd["affine"]])
+            else:
+                prog.sum([(cv(c), [fw(f) for f in fs]) for c, fs in nd["sum"]])
+        for t in sl["terms"]:
+            prog.term(cv(t["coef"]), t["wrapper"], [fw(f) for f in t["inner"]])
+        kinds = ["eq" if k in ("eq", "geq") else "base" for k in sl["tables"]]  # planes, supports and public tables are base-valued until the first fold
+        out.append((SLOT_NAMES[sl["slot"]], SLOT_ROUNDS_8B[sl["slot"]], sl["degree"], prog, kinds))
+    return out
+
+
+def _m125_replay_slots(SP):
     cs = iter(splitmix_fp(95, 1 << 16).tolist())
 
     def coef(cls):
         return "one" if cls == "one" else (next(cs) % (1 << 40), 0) if cls == "kbase" else (next(cs), next(cs))
 
-    def fw(f):
-        return SP.node(f["n"]) if "n" in f else f["t"]
+    out = []
+    for sl in _m125_slots():
+        kinds = ["eq"] + ["base" if f == "base" else "ext" for f in sl["table_fields"][1:]]
+        out.append((sl["name"], sl["main_rounds"], sl["declared_degree"], _program_from_structure(SP, sl, coef), kinds))
+    return out
 
-    for sl in slots:
-        nv, k, deg = sl["main_rounds"], len(sl["table_fields"]), sl["declared_degree"]
-        prog = SP(k)
-        for nd in sl["nodes"]:
-            if "affine" in nd:
-                prog.affine(coef("kbase") if nd["konst"] else "zero", [(coef(c), t) for c, t in nd["affine"]])
-            else:
-                prog.sum([(coef(c), [fw(f) for f in fs]) for c, fs in nd["sum"]])
-        for t in sl["terms"]:
-            prog.term(coef(t["coef"]), t["wrapper"], [fw(f) for f in t["inner"]])
+
+def slot_replay(dev, backend, st, rows, n, slots, shape_note) -> dict:
+    """All 23 slot sumchecks of one block, replayed on the device: per slot the tables are built ON THE DEVICE from the
+    resident rows of a commitment (an eq cube for an eq table, committed planes for the rest: base-valued where the reference
+    records a base table, partially evaluated at one fixed coordinate where it records an extension table), then the masked
+    sumcheck runs with the device Fiat-Shamir step.  Points and plane positions are seeded; the graphs, table counts and degrees
+    are the reference's.  This is device WORK of the stated shape, not a proof: the protocol layer that would drive it is the
+    reference's Rust crate."""
+    ctx = dev.ctx
+    words_avail = rows * n
+    per_slot, total_tables_ms, total_rounds_ms, total_bytes = {}, 0.0, 0.0, 0
+    cs = iter(splitmix_fp(96, 1 << 16).tolist())
+    for name, nv, deg, prog, kinds in slots:
+        k = len(kinds)
         point = np.array([next(cs) for _ in range(2 * nv)], dtype=np.uint64).reshape(nv, 2)
         mask = np.array([next(cs) for _ in range(2 * ((nv + 1) * deg + 2))], dtype=np.uint64).reshape(-1, 2)
         ctx.timing_read(reset=True)
         tabs = backend.B200Tables(ctx, k, nv)
-        tabs.plan_eq(0, point, 0)
-        for t in range(1, k):
-            if sl["table_fields"][t] == "base":
+        for t in range(k):
+            if kinds[t] == "eq":
+                tabs.plan_eq(t, point, 0)
+                continue
+            if kinds[t] == "base":
                 coords, span = [("rho", v) for v in range(nv)], 1 << nv
             else:
                 coords, span = [("fixed", (next(cs), next(cs)))] + [("rho", v) for v in range(nv)], 2 << nv
@@ -450,12 +582,12 @@ def slot_replay(dev, backend, st, rows, n) -> dict:
         ev.batched(nv, bytes(32), 0, None, mask=mask, mask_vars=nv + 1, mask_c=(3, 5), recover_one=True, claim=(0, 0))
         ev.free()
         tm = ctx.timing_read(reset=True)
-        per_slot[sl["name"]] = round(tm["tables"][0] + tm["rounds"][0], 3)
+        per_slot[name] = {"rounds": nv, "tables": k, "degree": deg, "tables_ms": round(tm["tables"][0], 3), "sumcheck_ms": round(tm["rounds"][0], 3)}
         total_tables_ms += tm["tables"][0]
         total_rounds_ms += tm["rounds"][0]
         total_bytes += k * (16 << nv)
-    return {"slots": len(slots), "tables_ms": total_tables_ms, "sumchecks_ms": total_rounds_ms, "table_bytes": total_bytes, "per_slot_ms": per_slot,
-            "shape": "the reference's recorded 125M slot graphs (T512 / d768 / f2048): 23 slots, 258 tables, cubes of 2^8 .. 2^22 points"}
+    return {"slots": len(slots), "tables_ms": total_tables_ms, "sumchecks_ms": total_rounds_ms, "table_bytes": total_bytes, "per_slot": per_slot,
+            "shape": shape_note}
 
 
 def cpu_extras(o, backend, np_data) -> dict:
@@ -531,6 +663,145 @@ def cpu_extras(o, backend, np_data) -> dict:
     return out
 
 
+def extras_rooflines(extras: dict, peak_gbs: float) -> dict:
+    """Algorithmic bytes (and field multiply-adds where arithmetic is the bound) of every timed operation of `device_extras`,
+    with the achieved rate as a fraction of the measured HBM copy peak.  Bytes are what the operation must read and write once."""
+    w = WORK
+    n, nn, q, rows = 1 << w["log_cols"], (1 << w["log_cols"]) * w["inv_rate"], w["q"], w["rows"]
+    a_bytes = 8 * rows * (n + q)
+    spec = {
+        "open_A_fold_38rho_ms": (a_bytes + 38 * (n + q) * 16, {"field_multiply_adds": 38 * rows * (n + q) * 2, "bound": "arithmetic (every vector dense: the worst case)"}),
+        "open_A_fold_37_plane_vectors_1_dense_ms": (a_bytes + 38 * (n + q) * 16, {"bound": "hbm (the dense proximity vector reads every row once)"}),
+        "open_H_fold_9_plane_vectors_1_dense_ms": (a_bytes + 10 * (n + q) * 16, {"bound": "hbm"}),
+        "open_A_gather_280cols_ms": (280 * rows * 32, {"bound": "latency (one 32-byte sector per gathered word)"}),
+        "sumcheck_logup_q_2^21_deg3_21rounds_ms": (3 * 16 * 3 * (1 << 21), {"bound": "hbm in the long rounds (each round reads its tables, each fold reads and writes them), then launch latency"}),
+        "logup_helpers_2^21_ms": ((4 + 4 + 16) << 21, {"bound": "integer (one Fp2 inversion per 8 queries)"}),
+        "fold_cols_i8_4096x14336_ms": (4096 * 14336, {"field_multiply_adds": 4096 * 14336 * 2, "bound": "arithmetic (two wide multiply-adds per matrix byte)"}),
+        "fold_rows_i8_4096x14336_ms": (4096 * 14336, {"field_multiply_adds": 4096 * 14336 * 2, "bound": "arithmetic"}),
+        "draw_pads_and_salts_of_A_ms": (8 * rows * q + 32 * nn, {"bound": "integer (one BLAKE3 compression per 64 bytes)"}),
+        "lookup_helpers_u8_pairs_2^25_ms": (32 << 25, {"bound": "hbm"}),
+        "tables_eq_2^21_plus_plane_2^19_x8_ms": ((16 << 21) + (16 << 19) + (8 * 8 << 19), {"bound": "hbm"}),
+        "sumcheck_slot_program_60tables_71nodes_deg5_2^19_ms": (3 * 16 * 60 * (1 << 19), {"bound": "integer issue (219 products of extension-field values per pair and point)"}),
+        "witness_products_8B_block_T128_ms": (218103808 + 7 * 0, {"int8_multiply_adds": 128 * 218103808, "bound": "weights streamed once; launch structure"}),
+    }
+    out = {}
+    for key, (nbytes, more) in spec.items():
+        if key in extras and extras[key]:
+            gbs = nbytes / (extras[key] * 1e-3) / 1e9
+            out[key] = {"ms": extras[key], "algorithmic_bytes": nbytes, "achieved_GBps": gbs, "frac_of_measured_hbm": gbs / peak_gbs, **more}
+    return out
+
+
+def reference_cuda_extras(dev, backend, d_data, d_pads, d_pows, col_key) -> dict:
+    """The reference's OWN CUDA kernels (hashline/src/gpu/kernels.cu compiled unchanged for sm_100a, launched as
+    hashline/src/gpu/cuda.rs launches them) on this GPU, beside this repository's kernels on the same inputs: device
+    milliseconds, CUDA events.  None when the compiled module is absent."""
+    import torch
+
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import ref_cuda
+
+    if not ref_cuda.available():
+        return None
+    w = WORK
+    log_cols, ir, q, rows = w["log_cols"], w["inv_rate"], w["q"], w["rows"]
+    n, nn = 1 << log_cols, (1 << log_cols) * ir
+    ref = ref_cuda.RefCuda(max_log=log_cols + 1)
+    ctx = dev.ctx
+    cs = torch.cuda.current_stream()
+
+    def timed(f, reps=3):
+        f()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(cs)
+        for _ in range(reps):
+            f()
+        b.record(cs)
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+
+    out, mine = {}, {}
+    box = {}
+    out["encode"] = timed(lambda: box.__setitem__("enc", ref.encode_zk(d_data, d_pads, d_pows, rows, log_cols, log_cols + 1, q)))
+    enc = box["enc"]
+    out["column_hash"] = timed(lambda: ref.hash_cols(enc, rows, nn, col_key))
+    # the reference folds at most 4 vectors per launch over the data columns (cuda.rs:3437-3460): 38 vectors = 10 launches
+    rhos = torch.from_numpy(splitmix_fp(77, 4 * rows * 2).view(np.int64)).cuda()
+    out["open_A_fold_38rho"] = timed(lambda: [ref.fold_rows(d_data, rhos, rows, n, 4) for _ in range(10)])
+    del enc, box
+    nv = 21
+    tabs = torch.from_numpy(splitmix_fp(79, 3 * (1 << nv) * 2).view(np.int64)).cuda()
+
+    def all_folds():
+        half = 1 << (nv - 1)
+        while half >= 1:
+            ref.sc_fold(tabs, 3, half, 1 << nv, (3, 5))
+            half //= 2
+
+    out["sumcheck_folds_3tables_2^21_all_rounds"] = timed(all_folds)
+    point = splitmix_fp(90, 21 * 2).reshape(21, 2)
+    out["eq_table_2^21"] = timed(lambda: ref.eq_table(point))
+    nq = 1 << 21
+    a_dev = torch.from_numpy(np.concatenate([splitmix_fp(82, nq) % np.uint64(1 << 16), splitmix_fp(83, nq) % np.uint64(1 << 15),
+                                             splitmix_fp(84, nq) % np.uint64(256)]).view(np.int64)).cuda()
+    h_dev = torch.empty(2 * nq, dtype=torch.int64, device="cuda")
+    out["helper_column_2^21"] = timed(lambda: ref.helper(a_dev, 0, nq, 2 * nq, nq, (11, 12), (13, 14), (15, 16), (17, 18), h_dev, 0, nq))
+    del tabs, a_dev, h_dev
+    # this repository's kernels on the same operations (library timing classes: kernels only)
+    ctx.timing_enable(True)
+    tables = splitmix_fp(79, 3 * (1 << nv) * 2).reshape(3, 1 << nv, 2)
+    ev = backend.B200Rounds(ctx, backend.POLY_LOGUP_Q, tables, 3, splitmix_fp(80, 2).reshape(1, 2))
+    ctx.timing_read(reset=True)
+    for _ in range(nv):
+        ev.fold((3, 5))
+    mine["sumcheck_folds_3tables_2^21_all_rounds"] = ctx.timing_read(reset=True)["rounds"][0]
+    ev.free()
+    for rep in range(3):
+        if rep == 1:
+            ctx.timing_read(reset=True)
+        t21 = backend.B200Tables(ctx, 1, 21)
+        t21.plan_eq(0, point, 0)
+        t21.flush()
+        t21.free()
+    mine["eq_table_2^21"] = ctx.timing_read(reset=True)["tables"][0] / 2
+    ctx.timing_enable(False)
+    return {"ms": out, "this_repository_ms": mine,
+            "note": "reference kernels: k_ntt_p1/k_ntt_p2_f/k_zk_pad_scale (encode), k_hash_cols_keyed, k_fold_rows x10, k_sc_fold x21, k_eq_table + k_eq_join, "
+                    "k_helper; this repository's figures for encode, column hash, the opening fold and the helper column are kernel_ms_per_step and "
+                    "other_kernels_device_ms of the same line"}
+
+
+def block_device_trace(line: dict, extras: dict, commit_h_ms: float) -> dict:
+    """A MODEL of one block's device time at the Llama-3-8B block shape, summed from measured device times of this run, with
+    host work = 0 and no overlap between steps: the per-block call list of a W16R2_8B_T128_H24 block core (commit A, LogUp
+    helper columns, commit H, commit M, 23 slot sumchecks with their tables, openings of M, A and H, the witness products and
+    the public weight folds).  It is not a measurement of proved tokens per second: the protocol layer that drives these calls
+    is the reference's Rust crate."""
+    rep = extras["slot_replay_8B_T128"]
+    steps = {
+        "commit_A_2504x2^14": line["ms_per_step"],
+        "commit_H_2606x2^14": commit_h_ms,
+        "commit_M_24_masks_and_tree": extras["mask_M_24masks_commit_and_tree_wall_ms"],
+        "helper_columns_32M_looked_words": extras["lookup_helpers_u8_pairs_2^25_ms"] * 0.5,
+        "helper_columns_exp_and_activation_2.6M_inversions": extras["logup_helpers_2^21_ms"] * 2.6 / 2.1,
+        "slot_tables_1.44GB": rep["tables_ms"],
+        "slot_sumchecks_23": rep["sumchecks_ms"],
+        "open_M": extras["mask_M_24masks_open_wall_ms"],
+        "open_A_38_vectors_280_columns": extras["open_A_fold_37_plane_vectors_1_dense_ms"] + extras["open_A_gather_280cols_ms"],
+        "open_H_10_vectors_280_columns": extras["open_H_fold_9_plane_vectors_1_dense_ms"] * 2606 / 2504 + extras["open_A_gather_280cols_ms"],
+        "witness_products_7": extras["witness_products_8B_block_T128_ms"],
+        "public_weight_folds_218MB_int8": extras["fold_cols_i8_4096x14336_ms"] * 218103808 / (4096 * 14336),
+    }
+    block_ms = sum(steps.values())
+    blocks, tokens = 32, 128
+    request_ms = blocks * block_ms
+    return {"model": True, "label": "MODEL, not a measurement: sum of this run's measured device times, host work = 0, no overlap, no boundary commitments or join",
+            "shape": "W16R2_8B_T128_H24: one block of Llama-3-8B shapes, 128 tokens", "steps_ms": {k: round(v, 4) for k, v in steps.items()},
+            "block_device_ms": block_ms, "blocks_per_request": blocks, "request_device_ms": request_ms,
+            "modelled_device_only_tokens_per_s": tokens / (request_ms * 1e-3),
+            "reference_published": "22.9 - 34.2 proved tokens/s on an Apple M3 Ultra (whole prover, host work included)"}
+
+
 def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     import torch
     import torch.distributed as dist
@@ -554,10 +825,16 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
 
     # this rank's block (D55: block k -> rank k mod world); seeded synthetic witness words uniform in [0, p)
     block = rank
-    h_data = torch.from_numpy(splitmix_fp(0xB2000100 + block, rows * n).view(np.int64)).pin_memory()
-    h_pads = torch.from_numpy(splitmix_fp(0xB2000200 + block, rows * q).view(np.int64)).pin_memory()
+    blk_data, blk_pads, blk_salts = block_inputs(block)
+    h_data = torch.from_numpy(blk_data.view(np.int64)).pin_memory()
+    h_pads = torch.from_numpy(blk_pads.view(np.int64)).pin_memory()
     h_pows = torch.from_numpy(coset_powers(nn).view(np.int64)).pin_memory()
-    h_salts = torch.from_numpy(np.frombuffer(b3.blake3(b"bench-salts-%d" % block).digest(length=nn * 32), dtype=np.uint8).copy()).pin_memory()
+    h_salts = torch.from_numpy(blk_salts).pin_memory()
+    # the same rows as the prover's uploader sends them: every row at the narrowest width that holds it, page-locked
+    packed_np, row_width = backend.pack_rows(blk_data, rows)
+    h_packed = torch.from_numpy(packed_np).pin_memory()
+    np_packed = h_packed.numpy()
+    del packed_np, blk_data, blk_pads
 
     dev = backend.B200Backend(device=local_rank)
     stream = torch.cuda.Stream()  # the library, torch's copies and the timing events all use this one stream
@@ -582,10 +859,14 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     # the caller's result buffers, page-locked like its inputs
     np_levels = torch.empty((2 * nn - 1) * 32, dtype=torch.uint8).pin_memory().numpy().reshape(2 * nn - 1, 32)
 
-    def step_e2e():
+    def step_e2e(wide: bool = False):
         t0 = time.perf_counter()
-        st, leaves, levels = dev.try_commit_zk_tree(log_cols, ir, np_data, np_pads, np_pows, log_cols + 1, col_key, np_salts.reshape(nn, 32), leaf_key,
-                                                    node_key, levels_out=np_levels, want_leaves=False)
+        if wide:  # the 64-bit upload (hl_b200_commit_zk_tree), for the comparison line only
+            st, leaves, levels = dev.try_commit_zk_tree(log_cols, ir, np_data, np_pads, np_pows, log_cols + 1, col_key, np_salts.reshape(nn, 32), leaf_key,
+                                                        node_key, levels_out=np_levels, want_leaves=False)
+        else:
+            st, leaves, levels = dev.try_commit_zk_packed(log_cols, ir, np_packed, row_width, np_pads, np_pows, log_cols + 1, col_key, np_salts.reshape(nn, 32),
+                                                          leaf_key, node_key, levels_out=np_levels, want_leaves=False)
         t1 = time.perf_counter()
         st.free()
         t2 = time.perf_counter()
@@ -611,7 +892,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
 
     if args.profile_extras:
         if rank == 0:
-            print(json.dumps({"profile_run": True, "other_kernels_device_ms": device_extras(dev, backend, np_data, np_pads, np_pows, col_key)}))
+            print(json.dumps({"profile_run": True, "only": args.only, "other_kernels_device_ms": device_extras(dev, backend, np_data, np_pads, np_pows, col_key, args.only)}))
         dev.ctx.close()
         return
 
@@ -665,18 +946,31 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     clocks = sampler.stop()
     s1 = dev.ctx.stats()
     assert bytes(levels[-1]) == root_resident, "the two legs disagree on the root"
+    # the same call with the rows as 64-bit words (what the end-to-end leg cost before the narrow upload), a few steps
+    wide_steps = min(args.steps, 8)
+    step_e2e(wide=True)
+    barrier()
+    tw0 = time.perf_counter()
+    for _ in range(wide_steps):
+        _, levels_w = step_e2e(wide=True)
+    barrier()
+    e2e_wide_ms = max_over_ranks((time.perf_counter() - tw0) * 1e3 / wide_steps)
+    assert bytes(levels_w[-1]) == root_resident, "the wide upload disagrees on the root"
 
     # what the upload alone costs on this box: the same pinned buffers, one copy each, nothing else on the device
     c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    d_data.copy_(h_data, non_blocking=True)
+    d_packed = torch.empty_like(h_packed, device="cuda")
+    d_packed.copy_(h_packed, non_blocking=True)
     torch.cuda.synchronize()
     c0.record(stream)
     for _ in range(5):
-        d_data.copy_(h_data, non_blocking=True)
+        d_packed.copy_(h_packed, non_blocking=True)
         d_pads.copy_(h_pads, non_blocking=True)
+        d_salts.copy_(h_salts, non_blocking=True)
     c1.record(stream)
     torch.cuda.synchronize()
     h2d_only_ms = c0.elapsed_time(c1) / 5
+    del d_packed
     per_rank = None
     if world > 1:  # every rank's own wall time and upload time: the ranks share the host's memory and PCIe root complexes
         t = torch.tensor([e2e_own * 1e3 / args.steps, h2d_only_ms] + [x * 1e3 / args.steps for x in e2e_parts], dtype=torch.float64, device="cuda")
@@ -706,13 +1000,15 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
 
         if "LOCAL_RANK" in os.environ:
             o.set_threads(len(os.sched_getaffinity(0)))
-        rows_s = 32
-        sec = cpu_commit_sample(o, rows_s, "")
-        rows_s = int(min(rows, max(32, rows_s * 10.0 / max(sec, 1e-3)) // 8 * 8))  # about ten seconds of CPU work
-        sec = cpu_commit_sample(o, rows_s, "")
-        cpu = {"value": rows_s * nn * 8 / sec / 1e9, "unit": "GB/s", "cores": o.num_threads(), "kind": "port",
-               "sample": f"{rows_s} of {rows} rows at the same n/nn/q, {sec:.1f} s: encode + column hash + salt + tree; C restatement "
-                         "(OpenMP) of the reference's Rust CPU path, which cannot be built in this image"}
+        # the SAME matrix, pads and salts on the host cores: the CPU root must be the GPU root; repeated for about ten seconds
+        sec, cpu_root = cpu_commit(o, np_data, np_pads, np_salts)
+        assert cpu_root == root_resident, "the CPU restatement and the device disagree on the root of the bench's own matrix"
+        reps, spent = 1, sec
+        while spent < 10.0 and reps < 30:
+            s2, _ = cpu_commit(o, np_data, np_pads, np_salts)
+            sec, spent, reps = min(sec, s2), spent + s2, reps + 1
+        cpu = {"value": rows * nn * 8 / sec / 1e9, "unit": "GB/s", "cores": o.num_threads(), "kind": "port", "root_equals_gpu_root": True,
+               "sample": f"best of {reps} commitments ({spent:.1f} s): " + CPU_NOTE.format(rows=rows)}
 
     # integer ceiling: the same butterfly arithmetic on registers only; radix-2 butterflies of one encoder launch:
     # rows * (1 + R) * (n/2) log2 n (one inverse and R forward size-n transforms per row)
@@ -723,6 +1019,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     bfly_per_launch = rows * (1 + ir) * (n // 2) * log_cols
     extras = device_extras(dev, backend, np_data, np_pads, np_pows, col_key) if (world == 1 and rank == 0 and not args.no_extras) else None
     extras_cpu = cpu_extras(o, backend, np_data) if extras is not None else None
+    ref_cuda_ms = reference_cuda_extras(dev, backend, d_data, d_pads, d_pows, col_key) if extras is not None else None
 
     if rank == 0:
         line = {
@@ -731,13 +1028,16 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             "dtype": "u64", "data": "synthetic", "config": workload_config(world),
             "e2e": {"value": e2e_v, "unit": "GB/s", "h2d_bytes_per_step": (s1["bytes_h2d"] - s0["bytes_h2d"]) // args.steps,
                     "d2h_bytes_per_step": (s1["bytes_d2h"] - s0["bytes_d2h"]) // args.steps, "ms_per_step": e2e_s * 1e3 / args.steps,
-                    "h2d_only_ms": h2d_only_ms, **({"per_rank_ms": {"columns": ["step", "h2d_only", "commit_and_tree_call", "store_free", "root_exchange"], "rows": per_rank}} if per_rank else {})},
+                    "h2d_only_ms": h2d_only_ms, "call": "hl_b200_commit_zk_packed (rows as 2-byte / 8-byte words, widened on the device)",
+                    "wide_u64_upload": {"call": "hl_b200_commit_zk_tree", "ms_per_step": e2e_wide_ms, "h2d_bytes_per_step": 8 * rows * (n + q) + nn * 40,
+                                        "value": world * rows * nn * 8 / (e2e_wide_ms * 1e-3) / 1e9}, **({"per_rank_ms": {"columns": ["step", "h2d_only", "commit_and_tree_call", "store_free", "root_exchange"], "rows": per_rank}} if per_rank else {})},
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": {"bound": "hbm", "kernel": "k_encode_fast<14,1024>", "achieved": achieved, "peak": peak,
                          "peak_source": "MEASURED_PEAKS.json hbm_gbs" if peaks else "fallback 6650 GB/s", "unit": "GB/s", "frac": achieved / peak,
                          "frac_of_nominal_8000_GBps": achieved / 8000.0,
-                         "traffic": ENCODE_DRAM_TRAFFIC, "algorithmic_bytes_per_launch": alg_bytes, "ms_per_launch": enc_ms,
+                         "traffic": encode_dram_traffic(), "traffic_source": "profiles/k_encode_fast_8b_A.json (ncu capture of this kernel at this workload)",
+                         "algorithmic_bytes_per_launch": alg_bytes, "ms_per_launch": enc_ms,
                          "note": "integer-issue bound kernel (64-bit modular multiplies on the IMAD pipe); HBM fraction reported as the contract asks"},
             "integer_roofline": {"kernel": "k_encode_fast<14,1024>", "unit": "Gbutterfly/s", "achieved": bfly_per_launch / (enc_ms * 1e-3) / 1e9,
                                  "peak": bfly_peak / 1e9, "frac": bfly_per_launch / (enc_ms * 1e-3) / bfly_peak,
@@ -752,9 +1052,13 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             "kernel_ms_per_step": {"encode": enc_ms, "column_hash": hash_ms, "salt_and_tree": mer_ms},
             "cpu_baseline": cpu,
             "other_kernels_device_ms": extras,
+            "other_kernels_rooflines": extras_rooflines(extras, peak) if extras else None,
             "other_kernels_cpu_ms": extras_cpu,
+            "reference_cuda_ms": ref_cuda_ms,
             "root": root_resident.hex(),
         }
+        if extras:
+            line["block_device_trace_8B_T128"] = block_device_trace(line, extras, extras["commit_H_2606x2^14_to_root_ms"])
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -770,6 +1074,8 @@ def main() -> None:
     ap.add_argument("--no-extras", action="store_true", help="skip the device times of the opening, sumcheck and LogUp kernels")
     ap.add_argument("--profile", action="store_true", help="resident-input leg only (for a run under a profiler)")
     ap.add_argument("--profile-extras", action="store_true", help="opening, sumcheck and LogUp kernels only (for a run under a profiler)")
+    ap.add_argument("--only", default="", help="with --profile-extras: comma-separated families to run (open, sumcheck, helpers, i8folds, rng, lookup, slots, "
+                                               "slot_program, mask, witness, long_rows, commit_h)")
     args = ap.parse_args()
     rank, local_rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     if args.impl == "reference":
