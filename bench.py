@@ -410,9 +410,7 @@ def device_extras(dev, backend, np_data, np_pads, np_pows, col_key, only: str = 
             macs += 128 * kk * nn2
         tot = sum(per.values())
         out["witness_products_8B_block_T128_ms"] = tot
-        mma_peak = ctx.mma_i8_peak(2000)
         out["witness_products_detail"] = {"per_product_ms": per, "int8_TMAC_per_s": 2 * macs / (tot * 1e-3) / 1e12,
-                                          "mma_m16n8k32_register_resident_TMAC_per_s": mma_peak / 1e12,
                                           "weight_bytes": sum(k_ * n_ for _, k_, n_ in wp_shapes),
                                           "weights_read_once_at_measured_hbm_ms": sum(k_ * n_ for _, k_, n_ in wp_shapes) / 6549.8e9 * 1e3}
         del d_wmax, d_xw, d_ow
@@ -462,7 +460,7 @@ def device_extras(dev, backend, np_data, np_pads, np_pows, col_key, only: str = 
 def _m125_slots():
     import json as _json
 
-    return _json.load(open(os.path.join(ROOT, "bench_data", "slot_ir_m125.json")))["slots"]
+    return _json.load(open(os.path.join(ROOT, "intelligenceregulation_b200", "slot_graphs", "m125.json")))["slots"]
 
 
 def _program_from_structure(SP, slot, coef):
@@ -513,11 +511,11 @@ SLOT_NAMES = ["SS", "SSM", "TZC", "LZC", "RS", "QMM", "KMM", "VMM", "SCORE", "PV
 
 def _w16r2_slots(SP):
     """[(name, main rounds at the 8B shape, degree, program, per-table kind)] from the slot graphs of a real W16R2 block core with
-    their recorded coefficient values (bench_data/l11_slot_graphs.json)"""
+    their recorded coefficient values (intelligenceregulation_b200/slot_graphs/w16r2.json)"""
     import json as _json
 
     out = []
-    for sl in _json.load(open(os.path.join(ROOT, "bench_data", "l11_slot_graphs.json")))["slots"]:
+    for sl in _json.load(open(os.path.join(ROOT, "intelligenceregulation_b200", "slot_graphs", "w16r2.json")))["slots"]:
         prog = SP(len(sl["tables"]))
 
         def cv(c):
@@ -533,7 +531,10 @@ def _w16r2_slots(SP):
                 prog.sum([(cv(c), [fw(f) for f in fs]) for c, fs in nd["sum"]])
         for t in sl["terms"]:
             prog.term(cv(t["coef"]), t["wrapper"], [fw(f) for f in t["inner"]])
-        kinds = ["eq" if k in ("eq", "geq") else "base" for k in sl["tables"]]  # planes, supports and public tables are base-valued until the first fold
+        # witness planes, supports and endpoints are base-valued until the first fold; helper tables (h = re + u im) and, in the matmul
+        # slots, the public folded weights are extension-valued from the start (the field kinds the reference records for these tables)
+        matmul = 5 <= sl["slot"] <= 13
+        kinds = ["eq" if k in ("eq", "geq") else "ext" if (k == "H" or (k == "pub" and matmul)) else "base" for k in sl["tables"]]
         out.append((SLOT_NAMES[sl["slot"]], SLOT_ROUNDS_8B[sl["slot"]], sl["degree"], prog, kinds))
     return out
 

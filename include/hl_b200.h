@@ -63,13 +63,10 @@ int hl_b200_set_alloc_cap(hl_ctx* ctx, size_t bytes);
 /* Which encoder runs: 0 = radix-2 shared-memory stages (any n <= 2^14), 1 = the 16-point
  * register passes when 2^8 <= n <= 2^14 (default).  Same words either way. */
 int hl_b200_set_encoder(hl_ctx* ctx, int fast);
-
-/* ---- integer-issue ceiling (no counterpart in the reference; a measurement aid) ----
- * Runs the encoder's butterfly arithmetic on registers only, on every SM, and reports radix-2 Goldilocks
- * butterflies per second: the denominator for the encoder's integer-pipe utilisation. */
-int hl_b200_butterfly_peak(hl_ctx* ctx, uint32_t iters, double* butterflies_per_second);
-/* the same for the column hash: register-resident BLAKE3 compressions per second, all SMs */
-int hl_b200_compress_peak(hl_ctx* ctx, uint32_t iters, double* compressions_per_second);
+/* Which evaluator runs a slot program whose graph the library has a generated kernel for: 1 = the generated kernel
+ * (default), 0 = the interpreter, which runs every other program anyway.  Same words either way; an A/B switch like the
+ * reference's HL_GPU_* switches (hashline/src/gpu/cuda.rs:74-125). */
+int hl_b200_set_slot_kernels(hl_ctx* ctx, int on);
 
 /* ---- field self-test: metal_probe_field (tests/zk60_metal_commit.rs:69-89), k_probe ----
  * out3n[3i..3i+2] = (a_i + b_i, a_i - b_i, a_i * b_i) */
@@ -302,9 +299,6 @@ int hl_b200_act_table(hl_ctx* ctx, const int64_t* tables, size_t groups, size_t 
  * *taken = 0 (and HL_B200_OK) when the CPU must take the product: an activation outside int16, or a shape outside
  * inner <= 65,536, xs >= inner, os >= outer, the rows inside x_len / out_len, inner * outer <= w_len.
  * The _dev form takes device pointers (weights resident in HBM across requests) and is asynchronous up to its own flag read. */
-/* a yardstick for the witness products: the warp-level int8 tensor-core instruction (mma.sync m16n8k32, the path the product kernel
- * does NOT use) register resident on every SM, in multiply-adds per second */
-int hl_b200_mma_i8_peak(hl_ctx* ctx, uint32_t iters, double* macs_per_second);
 int hl_b200_witness_product(hl_ctx* ctx, size_t t_rows, const int64_t* x, size_t x_len, size_t xs, const int8_t* w, size_t w_len, size_t inner,
                             size_t outer, size_t os, size_t out_len, int in_out, int64_t* out, int* taken);
 int hl_b200_witness_product_dev(hl_ctx* ctx, size_t t_rows, const int64_t* d_x, size_t x_len, size_t xs, const int8_t* d_w, size_t w_len, size_t inner,
@@ -352,6 +346,7 @@ typedef struct {
     uint64_t kernel_launches;   /* kernels this context has launched */
     uint64_t bytes_h2d, bytes_d2h;
     uint64_t declines;          /* calls that returned an error */
+    uint64_t generated_rounds;  /* sumcheck rounds of slot programs that ran a generated per-graph kernel */
 } hl_stats;
 int hl_b200_stats(hl_ctx* ctx, hl_stats* out);
 

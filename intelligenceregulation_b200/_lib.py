@@ -16,7 +16,7 @@ ERR_ARG, ERR_OOM, ERR_DEVICE, ERR_TIMEOUT, ERR_MISMATCH, ERR_ZERO, ERR_UNSUPPORT
 
 class Stats(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in ("commits", "folds", "gathers", "merkles", "round_batches", "kernel_launches",
-                                          "bytes_h2d", "bytes_d2h", "declines")]
+                                          "bytes_h2d", "bytes_d2h", "declines", "generated_rounds")]
 
 
 _vp, _u32, _u64, _sz, _int = C.c_void_p, C.c_uint32, C.c_uint64, C.c_size_t, C.c_int
@@ -31,6 +31,7 @@ SIGNATURES = {
     "hl_b200_set_stream": (_int, [_vp, _vp]),
     "hl_b200_sync": (_int, [_vp]),
     "hl_b200_set_encoder": (_int, [_vp, _int]),
+    "hl_b200_set_slot_kernels": (_int, [_vp, _int]),
     "hl_b200_probe_field": (_int, [_vp, _vp, _vp, _sz, _vp]),
     "hl_b200_commit": (_int, [_vp, _u32, _u32, _vp, _sz, _u32, _vp, _pp, _vp]),
     "hl_b200_commit_zk": (_int, [_vp, _u32, _u32, _vp, _sz, _vp, _sz, _vp, _u32, _vp, _pp, _vp]),
@@ -55,7 +56,6 @@ class FsState(C.Structure):
 SIGNATURES.update({
     "hl_b200_rounds_new": (_int, [_vp, _int, _sz, _u32, _u32, _vp, _vp, _sz, _pp]),
     "hl_b200_rounds_new_ir": (_int, [_vp, _sz, _u32, _u32, _vp, _vp, _sz, _u32, _u32, _vp, _sz, _pp]),
-    "hl_b200_mma_i8_peak": (_int, [_vp, _u32, _vp]),
     "hl_b200_witness_product": (_int, [_vp, _sz, _vp, _sz, _sz, _vp, _sz, _sz, _sz, _sz, _sz, _int, _vp, _vp]),
     "hl_b200_witness_product_dev": (_int, [_vp, _sz, _vp, _sz, _sz, _vp, _sz, _sz, _sz, _sz, _sz, _int, _vp, _vp]),
     "hl_b200_act_histogram": (_int, [_vp, _vp, _vp, _sz, _sz, _sz, _sz, _vp, _vp, _sz, _vp, _vp]),

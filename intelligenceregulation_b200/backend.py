@@ -85,6 +85,10 @@ class Context:
     def set_encoder(self, fast: bool) -> None:
         self.check(self.lib.hl_b200_set_encoder(self.h, 1 if fast else 0))
 
+    def set_slot_kernels(self, on: bool) -> None:
+        """generated per-graph round kernels (default) or the interpreter for slot programs with a known graph"""
+        self.check(self.lib.hl_b200_set_slot_kernels(self.h, 1 if on else 0))
+
     def set_alloc_cap(self, nbytes: int) -> None:
         """Host-side allocation-failure injection (0 = no cap)."""
         self.check(self.lib.hl_b200_set_alloc_cap(self.h, nbytes))
@@ -158,12 +162,6 @@ class Context:
         comp, ht = np.empty((length, 2), dtype=np.uint64), np.empty((length, 2), dtype=np.uint64)
         self.check(self.lib.hl_b200_act_table(self.h, _ptr(tables), tables.size // 4096, length, _ptr(mult), _ptr(a), _ptr(b), _ptr(t), _ptr(comp), _ptr(ht)))
         return comp, ht
-
-    def mma_i8_peak(self, iters: int = 2000) -> float:
-        """int8 multiply-adds per second of the warp-level tensor-core instruction (mma.sync), register resident: a yardstick for the products."""
-        v = C.c_double()
-        self.check(self.lib.hl_b200_mma_i8_peak(self.h, iters, C.byref(v)))
-        return v.value
 
     def witness_product(self, t_rows: int, x, xs: int, w, inner: int, outer: int, os_: int, out_len: int, in_out: bool) -> Optional[np.ndarray]:
         """``gpu::witness_product`` (metal.rs:4646-4680): the exact int16 x int8 -> int64 plane, or None when the CPU must take
@@ -611,6 +609,13 @@ class SlotProgram:
         if isinstance(c, str):
             return self._SPECIAL[c]
         key = (int(c[0]), int(c[1]))
+        # by VALUE, as the flattening of a `SlotIr` does: a coefficient equal to 1, -1 or 0 is the special word
+        if key == (1, 0):
+            return self._SPECIAL["one"]
+        if key == (0xFFFFFFFF00000000, 0):
+            return self._SPECIAL["neg-one"]
+        if key == (0, 0):
+            return self._SPECIAL["zero"]
         if key not in self._coef_index:
             self._coef_index[key] = len(self.coefs)
             self.coefs.append(key)

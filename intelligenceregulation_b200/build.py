@@ -30,13 +30,19 @@ def _stale() -> bool:
     if not os.path.exists(LIB):
         return True
     t = os.path.getmtime(LIB)
-    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(HERE, "..", "include", "hl_b200.h")]
+    graphs = os.path.join(HERE, "slot_graphs")
+    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f != "gen"] + [os.path.join(HERE, "..", "include", "hl_b200.h")]
+    deps += [os.path.join(HERE, "slotgen.py")] + [os.path.join(graphs, f) for f in os.listdir(graphs)]
     return any(os.path.getmtime(d) > t for d in deps)
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not _stale():
         return LIB
+    # the per-graph slot kernels are generated sources (csrc/gen/, not kept in the history)
+    from . import slotgen
+
+    gen_sources = [os.path.join("gen", f) for f in slotgen.generate()]
     objs = []
     obj_dir = os.path.join(HERE, "build")
     os.makedirs(obj_dir, exist_ok=True)
@@ -44,8 +50,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if verbose:
         common += ["-Xptxas", "-v"]
     procs = []
-    for src in SOURCES:
-        obj = os.path.join(obj_dir, src.replace(".cu", ".o"))
+    for src in SOURCES + gen_sources:
+        obj = os.path.join(obj_dir, os.path.basename(src).replace(".cu", ".o"))
         objs.append(obj)
         procs.append((src, subprocess.Popen(common + ["-c", os.path.join(CSRC, src), "-o", obj], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     failed = False

@@ -1,6 +1,7 @@
 // The C ABI of the backend (include/hl_b200.h): context, commitments, stores, Merkle trees.
 // Host runtime only; the kernels live in encode.cu, hash.cu, store.cu, misc.cu.
 #include "api_internal.h"
+#include "../../include/hl_b200_bench.h"
 
 #include <cstdio>
 #include <cstring>
@@ -261,6 +262,12 @@ int hl_b200_set_alloc_cap(hl_ctx* c, size_t bytes) {
 int hl_b200_set_encoder(hl_ctx* c, int fast) {
     if (!c) return HL_B200_ERR_ARG;
     c->fast_encoder = fast != 0;
+    return HL_B200_OK;
+}
+
+int hl_b200_set_slot_kernels(hl_ctx* c, int on) {
+    if (!c) return HL_B200_ERR_ARG;
+    c->slot_kernels = on != 0;
     return HL_B200_OK;
 }
 

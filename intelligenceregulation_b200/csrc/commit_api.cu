@@ -72,13 +72,18 @@ int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* 
     if (!rc && packed) rc = dev_alloc(c, (void**)&d_row_w, st->rows);
     if (!rc && packed) rc = h2d_owned(c, d_row_off, hr.off.data(), (size_t)st->rows * 8);
     if (!rc && packed) rc = h2d_owned(c, d_row_w, hr.row_w, st->rows);
-    // row pieces of 256 rows = two 1 KiB hash chunks per column: a piece is encoded and its chunk values are hashed while
-    // the next piece is still on the bus, so that only the last piece (at most one wave of the encoder) follows the upload
+    // Row pieces: a piece is encoded and its complete 1 KiB hash chunks (128 rows) are hashed while the next piece is still on
+    // the bus.  Piece sizes are whole waves of the encoder (one row per SM per wave).  When the bytes per row make the bus the
+    // slower side (64-bit words) the pieces are two waves and the last one a single wave, so that little follows the upload;
+    // when the device is the slower side (narrow rows) the first piece is one wave, so that the encoder starts early, and the
+    // rest are four waves, which keeps the number of partly filled waves at one.
     auto byte_at = [&](u32 r) { return packed ? (size_t)hr.off[r] : (size_t)r * n * 8; };
-    u32 chunk = st->rows;
-    if (h_data && total_bytes >= ((size_t)32 << 20) && st->rows > 4u * (u32)c->sm_count) chunk = 256;
-    const bool pieces = chunk < st->rows;
-    if (!rc && h_data && chunk < st->rows) {
+    const u32 wave = (u32)c->sm_count;
+    const bool split = h_data && total_bytes >= ((size_t)32 << 20) && st->rows > 4u * wave;
+    const bool bus_bound = total_bytes / st->rows >= n * 6;  // bytes per row near the 64-bit form
+    const u32 chunk = split ? (bus_bound ? 2u * wave : 4u * wave) : st->rows;
+    const bool pieces = split;
+    if (!rc && pieces) {
         // the copy stream may touch the fresh allocations only after the main stream has made them
         cudaError_t e = cudaEventRecord(c->ev_main, c->stream);
         if (e == cudaSuccess) e = cudaStreamWaitEvent(c->copy_stream, c->ev_main, 0);
@@ -91,8 +96,8 @@ int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* 
         cudaPointerAttributes attr;
         const bool pageable = cudaPointerGetAttributes(&attr, h_data) != cudaSuccess || attr.type == cudaMemoryTypeUnregistered;
         cudaGetLastError();  // an unregistered pointer is not an error here
-        size_t need = 0;
-        for (u32 r0 = 0; r0 < st->rows; r0 += chunk) {
+        size_t need = 0;  // the largest piece, whatever its start
+        for (u32 r0 = 0; r0 < st->rows; r0 += wave) {
             const u32 r1 = r0 + chunk < st->rows ? r0 + chunk : st->rows;
             need = byte_at(r1) - byte_at(r0) > need ? byte_at(r1) - byte_at(r0) : need;
         }
@@ -113,12 +118,13 @@ int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* 
     if (!rc) {
         Timed t(c, HL_T_ENCODE);
         size_t ev_i = 0;
-        u32 nr = 0;
+        u32 nr = 0, chunks_done = 0;
         for (u32 r0 = 0; r0 < st->rows && !rc; r0 += nr) {
             nr = st->rows - r0 < chunk ? st->rows - r0 : chunk;
-            if (pieces && r0 + nr == st->rows && nr > 128 && nr > (u32)c->sm_count) nr = 128;  // leave one wave or less for the end
+            if (pieces && !bus_bound && r0 == 0) nr = wave;                                            // start the encoder early
+            if (pieces && bus_bound && r0 + nr == st->rows && nr > wave) nr -= wave;                   // leave one wave or less for the end
             if (h_data) {
-                cudaStream_t cs = chunk < st->rows ? c->copy_stream : c->stream;
+                cudaStream_t cs = pieces ? c->copy_stream : c->stream;
                 const size_t b0 = byte_at(r0), bytes = byte_at(r0 + nr) - b0;
                 const void* from = (const char*)h_data + b0;
                 if (staged) {
@@ -166,11 +172,14 @@ int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* 
             cudaError_t e = hlk::encode_rows(a, logb, c->fast_encoder || loga, c->sm_count, scratch_words, c->stream, &st->encoder_path);
             c->stats.kernel_launches += 1;
             if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "row encoder launch", e);
-            if (!rc && pieces) {  // the hash chunks this piece completed (pieces start on multiples of 128 rows)
-                const u32 c0 = r0 / 128u, c1 = r0 + nr == st->rows ? nchunks : (r0 + nr) / 128u;
-                e = hlk::hash_column_chunks(st->d_enc, st->rows, (u32)nn, d_key, c0, c1 - c0, cvs, st->d_leaves, c->stream);
-                c->stats.kernel_launches += 1;
-                if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "column hash launch", e);
+            if (!rc && pieces) {  // the 128-row hash chunks that are complete now
+                const u32 c1 = r0 + nr == st->rows ? nchunks : (r0 + nr) / 128u;
+                if (c1 > chunks_done) {
+                    e = hlk::hash_column_chunks(st->d_enc, st->rows, (u32)nn, d_key, chunks_done, c1 - chunks_done, cvs, st->d_leaves, c->stream);
+                    c->stats.kernel_launches += 1;
+                    if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "column hash launch", e);
+                    chunks_done = c1;
+                }
             }
         }
     }

@@ -4,12 +4,14 @@
 #include <cstring>
 
 #include "api_internal.h"
+#include "slot_gen.cuh"
 #include "sumcheck.h"
 
 using namespace hlapi;
 
 struct hl_tables;
 u64* hl_tables_adopt(hl_tables* t);        // tables.cu: hands the device tables over (the set is empty afterwards)
+const u64* hl_tables_peek(hl_tables* t);   // the device tables, still owned by the set
 int hl_tables_flush_locked(hl_tables* t);  // waits for the builders; refuses a base-declared table with an extension word
 void hl_tables_shape(hl_tables* t, hl_ctx** c, size_t* k, uint32_t* n_vars);
 
@@ -28,6 +30,10 @@ struct hl_rounds {
     u32 eval_degree = 0;
     hlk::ScState* d_state = nullptr;
     hlk::IrDev ir{};           // poly == POLY_IR: the polynomial as data
+    const sg::Entry* gen = nullptr;  // the generated kernel of this program's graph, when there is one
+    u64* d_cfo = nullptr;      // its coefficients by occurrence
+    u64* d_nonbase = nullptr;  // one word: bit t set when table t is extension-valued before the first fold
+    u64 nonbase = ~0ull;
     u32 tail_len = hlk::SC_TAIL_LEN;
     size_t out_row() const { return (2 * ((size_t)degree + 1) + 1) * 2; }
 };
@@ -43,6 +49,8 @@ void free_rounds(hl_rounds* r) {
     dev_free(c, r->d_inv_den, ((size_t)r->degree + 1) * 8);
     if (r->d_extrap) dev_free(c, r->d_extrap, (size_t)hlk::SC_MAX_POINTS * hlk::SC_MAX_POINTS * 8);
     dev_free(c, r->d_state, sizeof(hlk::ScState));
+    if (r->d_cfo) dev_free(c, r->d_cfo, (size_t)(r->gen ? r->gen->n_cfo : 1) * 16);
+    if (r->d_nonbase) dev_free(c, r->d_nonbase, 8);
     if (r->ir.plan) dev_free(c, (void*)r->ir.plan, (size_t)r->ir.plan_words * 4);
     if (r->ir.coefs) dev_free(c, (void*)r->ir.coefs, (size_t)(r->ir.n_coefs ? r->ir.n_coefs : 1) * 16);
     delete r;
@@ -53,9 +61,24 @@ int launch_round(hl_rounds* r, int eval_one, int fs, int use_claim, int recover,
     hl_ctx* c = r->ctx;
     const u32 half = (u32)(r->len / 2);
     const bool is_ir = r->poly == hlk::POLY_IR;
-    const u32 nb = is_ir ? hlk::sc_ir_blocks(r->ir, half, (int)r->degree, c->sm_count) : hlk::sc_round_blocks(half, c->sm_count);
-    cudaError_t e = is_ir ? hlk::sc_round_ir(r->ir, (int)r->k, r->d_tables, r->stride, half, (int)r->degree, eval_one, r->d_partials, nb, c->stream)
-                          : hlk::sc_round(r->poly, (int)r->k, r->d_tables, r->stride, half, r->d_coefs, eval_one, r->d_partials, nb, c->stream);
+    u32 nb = is_ir ? hlk::sc_ir_blocks(r->ir, half, (int)r->degree, c->sm_count) : hlk::sc_round_blocks(half, c->sm_count);
+    cudaError_t e;
+    if (is_ir && r->gen && c->slot_kernels) {
+        // the generated kernel of this graph: the first-round typing while the tables it reads as base words are base-valued
+        const u32 skip = (!eval_one && r->eval_degree >= 1) ? 1u : 0u, npe = r->eval_degree + 1 - skip;
+        const bool r0 = r->next == 0 && (r->gen->base_mask & r->nonbase) == 0;
+        const bool per_point = (u64)half < (u64)c->sm_count * sg::GT * 2;
+        u32 bx = (half + sg::GT - 1) / sg::GT, cap = (u32)c->sm_count * 4;
+        if (bx > cap) bx = cap;
+        if (bx > r->max_blocks) bx = r->max_blocks;
+        if (bx < 1) bx = 1;
+        nb = bx;
+        c->stats.generated_rounds++;
+        e = r->gen->launch(r0, per_point, bx, r->d_tables, r->stride, half, r->d_cfo, (int)r->degree, npe, skip, r->d_partials, c->stream);
+    } else {
+        e = is_ir ? hlk::sc_round_ir(r->ir, (int)r->k, r->d_tables, r->stride, half, (int)r->degree, eval_one, r->d_partials, nb, c->stream)
+                  : hlk::sc_round(r->poly, (int)r->k, r->d_tables, r->stride, half, r->d_coefs, eval_one, r->d_partials, nb, c->stream);
+    }
     c->stats.kernel_launches++;
     if (e != cudaSuccess) return fail(c, HL_B200_ERR_DEVICE, "round launch", e);
     hlk::ScStep a;
@@ -88,8 +111,13 @@ extern "C" {
 namespace {
 
 // the evaluator of either kind; `words` is the data form of the polynomial when poly == POLY_IR
+struct GenAsk {  // a slot program's generated kernel, looked up by the caller
+    const sg::Entry* entry = nullptr;
+    std::vector<fp2> cfo;
+};
+
 int rounds_build(hl_ctx* c, int poly, size_t k, uint32_t n_vars, uint32_t degree, const uint64_t* tables, const uint64_t* coefs,
-                 size_t ncoefs, const std::vector<u32>* plan, hl_rounds** out, hl_tables* built = nullptr) {
+                 size_t ncoefs, const std::vector<u32>* plan, hl_rounds** out, hl_tables* built = nullptr, const GenAsk* gen = nullptr) {
     std::lock_guard<std::mutex> g(c->mu);
     cudaSetDevice(c->device);
     if (built) {
@@ -156,6 +184,21 @@ int rounds_build(hl_ctx* c, int poly, size_t k, uint32_t n_vars, uint32_t degree
         cudaError_t e = cudaMemsetAsync(r->d_state, 0, sizeof(hlk::ScState), c->stream);
         if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "state clear", e);
     }
+    if (!rc && gen && gen->entry && gen->entry->n_tables == k && gen->entry->n_cfo == gen->cfo.size()) {
+        // the graph has a generated kernel: its coefficients by occurrence, and which tables are base-valued right now
+        r->gen = gen->entry;
+        rc = dev_alloc(c, (void**)&r->d_cfo, (size_t)(gen->cfo.size() ? gen->cfo.size() : 1) * 16);
+        if (!rc) rc = dev_alloc(c, (void**)&r->d_nonbase, 8);
+        if (!rc && gen->cfo.size()) rc = h2d(c, r->d_cfo, gen->cfo.data(), gen->cfo.size() * 16);
+        if (!rc && cudaMemsetAsync(r->d_nonbase, 0, 8, c->stream) != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "mask clear");
+        if (!rc) {
+            const u64* tabs = built ? hl_tables_peek(built) : r->d_tables;
+            cudaError_t e = hlk::sc_nonbase_mask(tabs, r->stride, r->len, (u32)k, r->d_nonbase, c->sm_count, c->stream);
+            c->stats.kernel_launches++;
+            if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "table typing launch", e);
+        }
+        if (!rc) rc = d2h(c, &r->nonbase, r->d_nonbase, 8);
+    }
     if (!rc) rc = sync(c, "rounds_new");
     if (rc) { cudaStreamSynchronize(c->stream); free_rounds(r); return rc; }
     if (built) r->d_tables = hl_tables_adopt(built);  // only now: a failed build leaves the set with its owner
@@ -195,7 +238,9 @@ int hl_b200_rounds_new_ir(hl_ctx* c, size_t k, uint32_t n_vars, uint32_t degree,
         snprintf(buf, sizeof buf, "rounds_new_ir: the program does not fit the evaluator's plan (reason %d)", why);
         return fail(c, HL_B200_ERR_UNSUPPORTED, buf);
     }
-    return rounds_build(c, hlk::POLY_IR, k, n_vars, degree, tables, coefs, ncoefs, &plan, out);
+    GenAsk gen;
+    gen.entry = sg::find(ir::signature(sh, words, reinterpret_cast<const fp2*>(coefs), &gen.cfo));
+    return rounds_build(c, hlk::POLY_IR, k, n_vars, degree, tables, coefs, ncoefs, &plan, out, nullptr, &gen);
 }
 
 int hl_b200_rounds_from_tables(hl_ctx* c, int poly, uint32_t degree, hl_tables* t, const uint64_t* coefs, size_t ncoefs, hl_rounds** out) {
@@ -225,7 +270,9 @@ int hl_b200_rounds_from_tables_ir(hl_ctx* c, uint32_t degree, hl_tables* t, cons
     if (ir::validate(sh, words)) return fail(c, HL_B200_ERR_ARG, "rounds_from_tables_ir: malformed program");
     std::vector<u32> plan;
     if (ir::build_plan(sh, words, degree, plan)) return fail(c, HL_B200_ERR_UNSUPPORTED, "rounds_from_tables_ir: the program does not fit the evaluator's plan");
-    return rounds_build(c, hlk::POLY_IR, k, n_vars, degree, nullptr, coefs, ncoefs, &plan, out, t);
+    GenAsk gen;
+    gen.entry = sg::find(ir::signature(sh, words, reinterpret_cast<const fp2*>(coefs), &gen.cfo));
+    return rounds_build(c, hlk::POLY_IR, k, n_vars, degree, nullptr, coefs, ncoefs, &plan, out, t, &gen);
 }
 
 void hl_b200_rounds_free(hl_rounds* r) {

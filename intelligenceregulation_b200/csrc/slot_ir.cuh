@@ -136,6 +136,44 @@ inline int validate(const Shape& s, const u32* w) {
     return pc == s.n_words ? 0 : 8;
 }
 
+// The SIGNATURE of a well-formed stream: FNV-1a over (n_tables, n_nodes, n_terms) and the stream's words with every
+// coefficient word replaced by the coefficient's class (the special words as they are; a general coefficient by whether
+// its value lies in the base field), so that a graph is recognised whatever its challenges are.  The generated kernels
+// (slot_gen.cuh) are keyed by it and read their coefficients by OCCURRENCE: `by_occurrence` receives the value of the
+// j-th coefficient word of the stream.
+constexpr u32 IR_CLASS_BASE = 0xFFFFFFF0u, IR_CLASS_EXT = 0xFFFFFFF1u;
+inline u64 signature(const Shape& s, const u32* w, const fp2* cf, std::vector<fp2>* by_occurrence) {
+    u64 h = 0xCBF29CE484222325ull;
+    auto mix = [&](u32 word) {
+        for (int b = 0; b < 4; b++) h = (h ^ ((word >> (8 * b)) & 0xFFu)) * 0x100000001B3ull;
+    };
+    auto coef = [&](u32 ci) {
+        const fp2 v = coef_value(ci, cf);
+        if (by_occurrence) by_occurrence->push_back(v);
+        mix((ci == IR_ONE || ci == IR_NEG_ONE || ci == IR_ZERO) ? ci : (v.c1 == 0 ? IR_CLASS_BASE : IR_CLASS_EXT));
+    };
+    mix(s.n_tables); mix(s.n_nodes); mix(s.n_terms);
+    u32 pc = 0;
+    auto product = [&]() {
+        coef(w[pc++]);
+        const u32 nf = w[pc++];
+        mix(nf);
+        for (u32 i = 0; i < nf; i++) mix(w[pc++]);
+    };
+    for (u32 n = 0; n < s.n_nodes; n++) {
+        const u32 head = w[pc++], cnt = head >> 8;
+        mix(head);
+        if ((head & 0xFFu) == IR_AFFINE) {
+            coef(w[pc++]);
+            for (u32 i = 0; i < cnt; i++) { coef(w[pc++]); mix(w[pc++]); }
+        } else {
+            for (u32 i = 0; i < cnt; i++) product();
+        }
+    }
+    for (u32 t = 0; t < s.n_terms; t++) product();
+    return h;
+}
+
 // ---------------------------------------------------------------------------------------------
 // The evaluation plan: the same graph regrouped for the kernels.  Every node becomes a sum of UNITS
 // (coef * prod(factors); an affine term is a unit with one table factor, its constant a unit with none),

@@ -345,6 +345,15 @@ __global__ void __launch_bounds__(TAIL_T) k_sc_tail(u64* __restrict__ tables, si
     }
 }
 
+// which tables are extension-valued: one CTA row per table, the second words OR-ed
+__global__ void __launch_bounds__(256) k_sc_nonbase(const u64* __restrict__ tables, size_t stride, size_t len, u64* __restrict__ mask) {
+    const u32 t = blockIdx.y;
+    const u64* tb = tables + 2 * (size_t)t * stride;
+    u64 any = 0;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < len; i += (size_t)gridDim.x * blockDim.x) any |= tb[2 * i + 1];
+    if (__syncthreads_or(any != 0) && threadIdx.x == 0) atomicOr(mask, 1ull << t);
+}
+
 __global__ void __launch_bounds__(256) k_sc_fold(u64* __restrict__ tables, size_t stride, u32 half, u32 k, const hlk::ScState* __restrict__ st) {
     const u32 i = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
     if (i >= half || t >= k) return;
@@ -879,6 +888,13 @@ cudaError_t sc_tail(int poly, int k, u64* tables, size_t stride, u32 len, const 
 
 cudaError_t sc_step(const ScStep& a, cudaStream_t s) {
     k_sc_step<<<1, STEP_T, 0, s>>>(a);
+    return cudaGetLastError();
+}
+
+cudaError_t sc_nonbase_mask(const u64* tables, size_t stride, size_t len, u32 k, u64* d_mask, int sm_count, cudaStream_t s) {
+    size_t bx = (len + 255) / 256, cap = (size_t)sm_count * 8 / (k ? k : 1) + 1;
+    if (bx > cap) bx = cap;
+    k_sc_nonbase<<<dim3((unsigned)bx, k), 256, 0, s>>>(tables, stride, len, d_mask);
     return cudaGetLastError();
 }
 

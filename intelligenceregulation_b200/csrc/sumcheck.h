@@ -67,6 +67,8 @@ cudaError_t sc_step(const ScStep& a, cudaStream_t s);
 constexpr u32 SC_TAIL_LEN = 1024;  // table length from which the remaining rounds run in one CTA (one SM: above it a round's arithmetic costs more than three launches)
 cudaError_t sc_tail(int poly, int k, u64* tables, size_t stride, u32 len, const u64* coefs, const ScStep& a, int nrounds,
                     int first_has_claim, u64* scratch, cudaStream_t s);
+// bit t of *d_mask is set when table t holds a non-zero second word anywhere in its first `len` entries (*d_mask zeroed by the caller)
+cudaError_t sc_nonbase_mask(const u64* tables, size_t stride, size_t len, u32 k, u64* d_mask, int sm_count, cudaStream_t s);
 cudaError_t sc_fold(u64* tables, size_t stride, u32 half, u32 k, const ScState* st, cudaStream_t s);
 
 }  // namespace hlk

@@ -118,6 +118,8 @@ u64* hl_tables_adopt(hl_tables* t) {  // rounds_api.cu takes the device tables o
     return p;
 }
 
+const u64* hl_tables_peek(hl_tables* t) { return t->d_tables; }
+
 void hl_tables_shape(hl_tables* t, hl_ctx** c, size_t* k, uint32_t* n_vars) {
     *c = t->ctx;
     *k = t->d_tables ? t->k : 0;

@@ -74,11 +74,6 @@ __global__ void __launch_bounds__(256) k_wp_repack(const int8_t* __restrict__ sr
     }
 }
 
-__device__ __forceinline__ void mma_s8s8(int (&c)[4], const u32 (&a)[4], const u32 (&b)[2]) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
-}
 // ---------------------------------------------------------------------------------------------------------------
 // The product on the 5th-generation tensor cores: TMA tiles into shared memory, tcgen05.mma kind::i8, accumulators in TMEM.
 // One CTA per SM owns a 128-token tile (two 128-row operands: the signed high bytes and the unsigned low bytes) and 256
@@ -253,42 +248,6 @@ __global__ void __launch_bounds__(UM_THREADS, 1) k_wp_umma(const __grid_constant
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512u));
 }
 
-// A yardstick, not a product path: the warp-level int8 tensor-core instruction (mma.sync m16n8k32) issued register resident, 16
-// independent accumulators per warp, 8 warps per CTA, 2 CTAs per SM.  The first form of the product kernel was built on it and
-// reached a fifth of this rate; the tcgen05 kernel above is compared with it in the bench.
-__global__ void __launch_bounds__(256, 2) k_mma_i8_peak(u32 iters, int* __restrict__ sink) {
-    int acc[4][4][4];
-    u32 a[4][4], b[4][2];
-#pragma unroll
-    for (int m = 0; m < 4; m++)
-#pragma unroll
-        for (int i = 0; i < 4; i++) a[m][i] = threadIdx.x * 0x01010101u + 16 * m + i;
-#pragma unroll
-    for (int n = 0; n < 4; n++) {
-        b[n][0] = threadIdx.x ^ (0x7F3C11A5u + n);
-        b[n][1] = blockIdx.x + 0x01020304u * (n + 1);
-    }
-#pragma unroll
-    for (int m = 0; m < 4; m++)
-#pragma unroll
-        for (int n = 0; n < 4; n++)
-#pragma unroll
-            for (int x = 0; x < 4; x++) acc[m][n][x] = 0;
-    // the product kernel's own register pattern: 4 A tiles x 4 B tiles, 16 accumulators
-    for (u32 it = 0; it < iters; it++) {
-#pragma unroll
-        for (int m = 0; m < 4; m++)
-#pragma unroll
-            for (int n = 0; n < 4; n++) mma_s8s8(acc[m][n], a[m], b[n]);
-    }
-    int v = 0;
-#pragma unroll
-    for (int m = 0; m < 4; m++)
-#pragma unroll
-        for (int n = 0; n < 4; n++) v ^= acc[m][n][0] ^ acc[m][n][3];
-    if (v == 0x5EED5EED) sink[0] = v;
-}
-
 // everything on the context's stream; d_* are device pointers; *flag_out is read after one synchronisation
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -346,11 +305,6 @@ int product_on_device(hl_ctx* c, size_t t_rows, const int64_t* d_x, size_t xs, c
         const double cost = waves * stages * 1.3e-6 + (sp > 1 ? (double)sp * (double)tiles * WP_MT * (double)N / 195e9 : 0.0);
         if (cost < best * 0.98) { best = cost; splits = sp; }
     }
-    // HL_B200_WP_SPLITS=<n>: a tuning override of the split (the result does not depend on it)
-    if (const char* ov = getenv("HL_B200_WP_SPLITS")) {
-        const long v = atol(ov);
-        if (v >= 1 && v <= (long)kt_all && v <= 65535) splits = (u32)v;
-    }
     int flag = 0;
     if (!rc) {
         Timed t(c, HL_T_WITNESS);
@@ -405,34 +359,6 @@ bool shape_fits(size_t t_rows, size_t x_len, size_t xs, size_t w_len, size_t inn
 }  // namespace
 
 extern "C" {
-
-int hl_b200_mma_i8_peak(hl_ctx* c, uint32_t iters, double* macs_per_second) {
-    if (!c || !macs_per_second || iters == 0) return fail(c, HL_B200_ERR_ARG, "mma_i8_peak: argument");
-    std::lock_guard<std::mutex> g(c->mu);
-    cudaSetDevice(c->device);
-    int* d_sink = nullptr;
-    int rc = dev_alloc(c, (void**)&d_sink, 4);
-    cudaEvent_t a = nullptr, b = nullptr;
-    float ms = 0.f;
-    const int blocks = c->sm_count * 2;
-    if (!rc) {
-        cudaEventCreate(&a); cudaEventCreate(&b);
-        k_mma_i8_peak<<<blocks, 256, 0, c->stream>>>(8, d_sink);  // warm-up
-        cudaEventRecord(a, c->stream);
-        k_mma_i8_peak<<<blocks, 256, 0, c->stream>>>(iters, d_sink);
-        cudaEventRecord(b, c->stream);
-        c->stats.kernel_launches += 2;
-        cudaError_t e = cudaGetLastError();
-        if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "mma_i8_peak launch", e);
-    }
-    if (!rc) rc = sync(c, "mma_i8_peak");
-    if (!rc && cudaEventElapsedTime(&ms, a, b) != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "mma_i8_peak timing");
-    if (a) cudaEventDestroy(a);
-    if (b) cudaEventDestroy(b);
-    if (d_sink) dev_free(c, d_sink, 4);
-    if (!rc) *macs_per_second = (double)blocks * 8 * 16.0 * 4096.0 * iters / (ms * 1e-3);
-    return rc;
-}
 
 int hl_b200_witness_product_dev(hl_ctx* c, size_t t_rows, const int64_t* d_x, size_t x_len, size_t xs, const int8_t* d_w, size_t w_len, size_t inner,
                                 size_t outer, size_t os, size_t out_len, int in_out, int64_t* d_out, int* taken) {

@@ -1,11 +1,13 @@
-"""Writes the slot-graph inputs of bench.py from the reference's own exports (data only; run where the reference is mounted):
+"""Writes the known slot expression graphs from the reference's own exports (data only; run where the reference is mounted):
 
-    python bench_data/make_bench_data.py <path to the reference checkout>
+    python intelligenceregulation_b200/slot_graphs/make_slot_graphs.py <path to the reference checkout>
 
-* slot_ir_m125.json   - the STRUCTURE of the 23 slot polynomials at the reference's recorded 125M shape
+The build generates one compiled round kernel per graph listed here (slotgen.py); bench.py replays the same graphs.
+
+* m125.json           - the STRUCTURE of the 23 slot polynomials at the reference's recorded 125M shape
                         (results/zk60_slot_ir/slot_ir_m125.json; grammar private_block/slot_ir.rs:57-345): per slot its name,
                         round counts, declared degree, per table its field kind, per node and term the ids and coefficient classes.
-* l11_slot_graphs.json - the 23 slot polynomials of a real W16R2 block core WITH their coefficient values and table kinds
+* w16r2.json          - the 23 slot polynomials of a real W16R2 block core WITH their coefficient values and table kinds
                         (results/zk60_lean_l11_20261107/corpus.txt, records SLOT / IR / IRTAB / NODE / TERM; grammar
                         private_block/lean_l11_export_tests.rs:60-105).  The W16R2 profile is the one the Llama-3-8B block shape
                         (W16R2_8B_T128_H24) registers, so these graphs at that shape's cube sizes model a block's sumchecks.
@@ -32,7 +34,7 @@ def m125(ref_root, here):
         terms = [{"coef": t["coef_provenance"], "wrapper": t["wrapper"], "inner": [fac(f) for f in t["factors"]], "degree": t["degree"]} for t in s["terms"]]
         out["slots"].append({"slot": s["slot"], "name": s["name"], "main_rounds": s["main_rounds"], "extension_rounds": s["extension_rounds"],
                              "declared_degree": s["declared_degree"], "table_fields": [t["field"] for t in s["tables"]], "nodes": nodes, "terms": terms})
-    json.dump(out, open(os.path.join(here, "slot_ir_m125.json"), "w"), separators=(",", ":"))
+    json.dump(out, open(os.path.join(here, "m125.json"), "w"), separators=(",", ":"))
 
 
 def l11(ref_root, here):
@@ -60,7 +62,7 @@ def l11(ref_root, here):
         elif w[0] == "TERM":
             cur["terms"].append({"coef": coef(w[1]), "wrapper": [] if w[2] == "-" else [int(x) for x in w[2].split(",")], "inner": factors(w[3])})
     out = {"source": "results/zk60_lean_l11_20261107/corpus.txt", "profile": "W16R2_RUNG_H24", "slots": slots}
-    json.dump(out, open(os.path.join(here, "l11_slot_graphs.json"), "w"), separators=(",", ":"))
+    json.dump(out, open(os.path.join(here, "w16r2.json"), "w"), separators=(",", ":"))
 
 
 if __name__ == "__main__":
@@ -69,5 +71,5 @@ if __name__ == "__main__":
     here = os.path.dirname(os.path.abspath(__file__))
     m125(sys.argv[1], here)
     l11(sys.argv[1], here)
-    for f in ("slot_ir_m125.json", "l11_slot_graphs.json"):
+    for f in ("m125.json", "w16r2.json"):
         print(f, os.path.getsize(os.path.join(here, f)), "bytes")

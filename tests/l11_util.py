@@ -122,7 +122,7 @@ def build_program(backend, slot):
 
     for n in slot["nodes"]:
         if n[0] == "affine":
-            konst = _cw(n[1], False)
+            konst = _cw(n[1])
             terms = [(_cw(c), t) for c, t in n[2]]
             prog.affine(konst, terms)
             desc["nodes"].append(("affine", konst, terms))

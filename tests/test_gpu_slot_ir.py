@@ -34,10 +34,16 @@ def _n_vars(slot):
 CASES = [(i, None) for i in range(23)] + [(14, 16), (3, 17), (5, 16), (14, 19), (17, 20)]
 
 
+@pytest.mark.parametrize("generated", [True, False])
 @pytest.mark.parametrize("idx,n_long", CASES)
-def test_slot_program_batched_masked_rounds(ctx, oracle, golden_dir, idx, n_long):
+def test_slot_program_batched_masked_rounds(ctx, oracle, golden_dir, idx, n_long, generated):
+    """`generated`: the per-graph compiled kernel the library holds for each of these graphs, or the interpreter that serves any
+    graph (both must return the oracle's words; the largest sizes run once, through the generated kernels)"""
     from intelligenceregulation_b200 import backend
 
+    if not generated and (n_long or 0) >= 19:
+        pytest.skip("the largest sizes run through the generated kernels only")
+    ctx.set_slot_kernels(generated)
     o = oracle
     slot = U.load_slots(golden_dir)[idx]
     n, deg = n_long or _n_vars(slot), slot["declared_degree"]
@@ -62,6 +68,34 @@ def test_slot_program_batched_masked_rounds(ctx, oracle, golden_dir, idx, n_long
     assert st == t_cpu.state and ctr == t_cpu.counter
     assert (ev.finals() == want.finals).all()
     ev.free()
+    ctx.set_slot_kernels(True)
+
+
+def test_every_known_graph_has_its_generated_kernel(ctx, oracle, golden_dir):
+    """The dispatcher recognises all 23 recorded graphs and all 23 graphs of the real W16R2 core by their signature (the word
+    stream with coefficient classes in place of values): with the generated kernels on, a short sumcheck over each of them
+    launches exactly the round kernel, the step and the fold per multi-CTA round that the generated path launches, and with
+    random tables in place of base-valued ones (so that the first-round typing does not apply) the words still equal the
+    interpreter's."""
+    from intelligenceregulation_b200 import backend
+    import l11_util
+
+    o = oracle
+    progs = [(U.build_program(backend, s, 7000 + i)[0], s["declared_degree"], len(s["table_fields"])) for i, s in enumerate(U.load_slots(golden_dir))]
+    progs += [(l11_util.build_program(backend, s)[0], s["degree"], s["n_tabs"]) for s in l11_util.load(golden_dir)["slots"]]
+    n = 12
+    for j, (prog, deg, k) in enumerate(progs):
+        tables = o.ZkRng(600 + j, b"gen-any").fp2_vec(k << n).reshape(k, 1 << n, 2)  # every table extension-valued
+        outs = []
+        for gen in (True, False):
+            ctx.set_slot_kernels(gen)
+            before = ctx.stats()["generated_rounds"]
+            ev = backend.B200Rounds(ctx, prog, tables, deg)
+            outs.append(ev.batched(n, bytes(32), 5, None)[0])
+            ev.free()
+            assert (ctx.stats()["generated_rounds"] > before) == gen, (j, gen)
+        assert (outs[0] == outs[1]).all(), j
+    ctx.set_slot_kernels(True)
 
 
 def test_plan_beyond_the_all_points_form_runs_the_stepping_pair_form(ctx, oracle):

@@ -17,7 +17,7 @@ def test_library_exports_every_declared_symbol():
 
     build.build()
     lib = _lib.load()
-    hdr = open(os.path.join(ROOT, "include", "hl_b200.h")).read()
+    hdr = open(os.path.join(ROOT, "include", "hl_b200.h")).read() + open(os.path.join(ROOT, "include", "hl_b200_bench.h")).read()
     declared = set(re.findall(r"\b(hl_b200_[a-z0-9_]+)\s*\(", hdr))
     assert declared, "no declarations found"
     for name in sorted(declared):
