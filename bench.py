@@ -453,8 +453,8 @@ def device_extras(dev, backend, np_data, np_pads, np_pows, col_key, only: str = 
         torch.cuda.synchronize()
         out["commit_H_2606x2^14_to_root_ms"] = ea.elapsed_time(eb) / 3
         del dd, dp, dw, dsalt, dlev
-        ctx.timing_enable(False)
-        return out
+    ctx.timing_enable(False)
+    return out
 
 
 def _m125_slots():

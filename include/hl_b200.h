@@ -63,9 +63,10 @@ int hl_b200_set_alloc_cap(hl_ctx* ctx, size_t bytes);
 /* Which encoder runs: 0 = radix-2 shared-memory stages (any n <= 2^14), 1 = the 16-point
  * register passes when 2^8 <= n <= 2^14 (default).  Same words either way. */
 int hl_b200_set_encoder(hl_ctx* ctx, int fast);
-/* Which evaluator runs a slot program whose graph the library has a generated kernel for: 1 = the generated kernel
- * (default), 0 = the interpreter, which runs every other program anyway.  Same words either way; an A/B switch like the
- * reference's HL_GPU_* switches (hashline/src/gpu/cuda.rs:74-125). */
+/* Which evaluator runs a slot program whose graph the library has a generated kernel for (the CUDA counterpart of the
+ * reference's generated Metal slot kernels, private_block/metal_slot.rs:115-497): 0 = the interpreter, which runs every
+ * program (default: it is the faster one on this GPU for every recorded graph), 1 = the generated kernel.  Same words either
+ * way; an A/B switch like the reference's HL_GPU_* switches (hashline/src/gpu/cuda.rs:74-125). */
 int hl_b200_set_slot_kernels(hl_ctx* ctx, int on);
 
 /* ---- field self-test: metal_probe_field (tests/zk60_metal_commit.rs:69-89), k_probe ----

@@ -86,7 +86,7 @@ class Context:
         self.check(self.lib.hl_b200_set_encoder(self.h, 1 if fast else 0))
 
     def set_slot_kernels(self, on: bool) -> None:
-        """generated per-graph round kernels (default) or the interpreter for slot programs with a known graph"""
+        """the generated per-graph round kernels, or (default) the interpreter, for slot programs with a known graph"""
         self.check(self.lib.hl_b200_set_slot_kernels(self.h, 1 if on else 0))
 
     def set_alloc_cap(self, nbytes: int) -> None:

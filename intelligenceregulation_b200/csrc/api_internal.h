@@ -19,7 +19,7 @@ struct hl_ctx {
     cudaEvent_t ev_main = nullptr;
     std::vector<cudaEvent_t> ev_chunks;
     bool fast_encoder = true;
-    bool slot_kernels = true;  // use the generated per-graph round kernels where a slot program's signature is known
+    bool slot_kernels = false;  // run a slot program whose graph is known through its generated kernel instead of the interpreter (measured slower: off)
     std::mutex mu;
     std::mutex err_mu;       // guards last_error and stats.declines: a decline may be recorded before `mu` is taken, from any thread
     std::map<u32, u64*> tw;  // log2 nn -> nn powers of the nn-th root

@@ -50,7 +50,7 @@ __device__ __forceinline__ void add_e(AccE& a, fp2 x) {
 __device__ __forceinline__ void add_b(AccE& a, u64 x) { addw(a.a0, x); }
 // USED7: some extension x extension product went in
 template <bool USED7>
-__device__ __forceinline__ fp2 red_e(AccE& a) {
+static __device__ __noinline__ fp2 red_e(AccE& a) {
     if constexpr (USED7) mac(a.a0, red(a.a7), 7);
     return f2(red(a.a0), red(a.a1));
 }
@@ -62,21 +62,21 @@ __device__ __forceinline__ void fence() { asm volatile("" ::: "memory"); }
 // ---- reduced products for chains of factors ----
 __device__ __forceinline__ u64 mul_bb(u64 x, u64 y) { return gl_mul(x, y); }
 __device__ __forceinline__ fp2 mul_eb(fp2 x, u64 y) { return f2_mul_base(x, y); }
-__device__ __forceinline__ fp2 mul_ee(fp2 x, fp2 y) { return f2_mul(x, y); }
+static __device__ __noinline__ fp2 mul_ee(fp2 x, fp2 y) { return f2_mul(x, y); }
 __device__ __forceinline__ u64 neg_b(u64 x) { return gl_neg(x); }
 __device__ __forceinline__ fp2 neg_e(fp2 x) { return f2_neg(x); }
 
 // ---- a table's value at evaluation point p of the round's variable: T(i) + p (T(i + half) - T(i)) ----
 // p is the same for every thread of a warp.  A base-valued table keeps a zero second word until the first fold, and
 // only its first word is read.
-__device__ __forceinline__ u64 ld_b(const u64* __restrict__ tb, u32 i, u32 half, u32 p) {
+static __device__ __noinline__ u64 ld_b(const u64* __restrict__ tb, u32 i, u32 half, u32 p) {
     const u64 lo = tb[2 * (size_t)i];
     if (p == 0) return lo;
     const u64 hi = tb[2 * ((size_t)i + half)];
     if (p == 1) return hi;
     return gl_add(lo, gl_mul(gl_sub(hi, lo), (u64)p));
 }
-__device__ __forceinline__ fp2 ld_e(const u64* __restrict__ tb, u32 i, u32 half, u32 p) {
+static __device__ __noinline__ fp2 ld_e(const u64* __restrict__ tb, u32 i, u32 half, u32 p) {
     const ulonglong2 a = *reinterpret_cast<const ulonglong2*>(tb + 2 * (size_t)i);
     if (p == 0) return f2(a.x, a.y);
     const ulonglong2 b = *reinterpret_cast<const ulonglong2*>(tb + 2 * ((size_t)i + half));
@@ -97,7 +97,7 @@ constexpr int MAX_POINTS = 8;
 //   PER_POINT false: a thread takes a pair and walks the points (the tables' words come back from L1 for the later points);
 //   PER_POINT true:  a CTA row per point (blockIdx.y), for rounds with fewer pairs than the machine has threads.
 template <class G, bool R0, bool PER_POINT>
-__global__ void __launch_bounds__(GT) k_slot_round(const u64* __restrict__ tables, size_t stride, u32 half, const u64* __restrict__ cfo, u32 n_cfo,
+__global__ void __launch_bounds__(GT, 4) k_slot_round(const u64* __restrict__ tables, size_t stride, u32 half, const u64* __restrict__ cfo, u32 n_cfo,
                                                    int degree, u32 npe, u32 skip_one, u64* __restrict__ partials) {
     extern __shared__ __align__(16) u64 sg_smem[];
     __shared__ u64 wsum[GT / 32][2 * MAX_POINTS];

@@ -125,52 +125,73 @@ def all_graphs() -> List[Graph]:
 
 # ------------------------------------------------------------------------------------------------ code emission
 class Emitter:
-    """straight-line code of one typing of one graph; a value is (is_ext, C expression)"""
+    """Straight-line code of one typing of one graph; a value is (is_ext, C expression).
+
+    Nodes are emitted DEPTH FIRST from the terms: a node's code sits inside its first consumer's accumulation, right before
+    the product that needs it, so that a value used once dies at once and the registers hold little more than the open
+    accumulators of the current path through the graph (the stream's own order computes every node first and keeps all of
+    them alive to the end, which the compiler answers with kilobytes of spills on the 60-table graphs)."""
+
+    RELOAD_AFTER = 60  # a table value is kept for this many emitted lines after its last use, then read again (its words are in L1)
 
     def __init__(self, g: Graph, first_round: bool):
         self.g, self.r0 = g, first_round
         self.lines: List[str] = []
         self.tab: Dict[int, Tuple[bool, str]] = {}
-        self.node: List[Tuple[bool, str]] = []
-        self.k = 0  # coefficient occurrence counter
-        self.tmp = 0
-        self.now = 0          # index of the node being emitted
         self.last_use: Dict[int, int] = {}
         self.loads = 0
+        self.tmp = 0
+        self.done: Dict[int, Tuple[bool, str]] = {}
+        # coefficient occurrences in STREAM order, whatever order the code is emitted in
+        self.occ: List[List[int]] = []
+        k = 0
+        for nd in g.nodes:
+            cnt = 1 + len(nd[2]) if nd[0] == "affine" else len(nd[1])
+            self.occ.append(list(range(k, k + cnt)))
+            k += cnt
+        self.term_occ = list(range(k, k + len(g.terms)))
+        # static types, in stream order (a node refers back only)
+        self.ntype: List[bool] = []
+        for nd in g.nodes:
+            prods = self.products(nd)
+            self.ntype.append(any(self.product_type(c, fs) for c, fs in prods if c != "zero"))
+
+    @staticmethod
+    def products(nd):
+        """a node as [(class, [factor])]; an affine node's constant is a product without factors"""
+        if nd[0] == "affine":
+            return [(nd[1], [])] + [(c, [("t", t)]) for c, t in nd[2]]
+        return nd[1]
 
     def emit(self, s: str) -> None:
         self.lines.append("        " + s)
 
-    RELOAD_AFTER = 2  # a table value is kept for this many nodes after its last use, then read again (its words are in L1)
+    def table_type(self, t: int) -> bool:
+        return not (self.r0 and self.g.base[t])
 
-    def table(self, t: int) -> Tuple[bool, str]:
-        if t not in self.tab or self.now - self.last_use[t] > self.RELOAD_AFTER:
-            ext = not (self.r0 and self.g.base[t])
-            self.loads += 1
-            name = ("te%d_%d" if ext else "tb%d_%d") % (t, self.loads)
-            self.emit("const %s %s = sg::%s(T + 2 * (size_t)%d * stride, i, half, p);" % ("fp2" if ext else "u64", name, "ld_e" if ext else "ld_b", t))
-            self.tab[t] = (ext, name)
-        self.last_use[t] = self.now
-        return self.tab[t]
-
-    def factor(self, f) -> Tuple[bool, str]:
-        return self.node[f[1]] if f[0] == "n" else self.table(f[1])
-
-    def coef(self, cls: str):
-        """(class, value or None) of the next coefficient word"""
-        k = self.k
-        self.k += 1
-        if cls in ("one", "neg-one", "zero"):
-            return cls, None
-        return cls, ((True, "cf[%d]" % k) if cls == "ext" else (False, "cf[%d].c0" % k))
+    def peek_type(self, f) -> bool:
+        return self.ntype[f[1]] if f[0] == "n" else self.table_type(f[1])
 
     def product_type(self, cls: str, facs) -> bool:
         return cls == "ext" or any(self.peek_type(f) for f in facs)
 
-    def peek_type(self, f) -> bool:
-        if f[0] == "n":
-            return self.node[f[1]][0]
-        return not (self.r0 and self.g.base[f[1]])
+    def table(self, t: int) -> Tuple[bool, str]:
+        if t not in self.tab or len(self.lines) - self.last_use[t] > self.RELOAD_AFTER:
+            ext = self.table_type(t)
+            self.loads += 1
+            name = ("te%d_%d" if ext else "tb%d_%d") % (t, self.loads)
+            self.emit("const %s %s = sg::%s(T + 2 * (size_t)%d * stride, i, half, p);" % ("fp2" if ext else "u64", name, "ld_e" if ext else "ld_b", t))
+            self.tab[t] = (ext, name)
+        self.last_use[t] = len(self.lines)
+        return self.tab[t]
+
+    def factor(self, f) -> Tuple[bool, str]:
+        return self.node(f[1]) if f[0] == "n" else self.table(f[1])
+
+    def coef_value(self, cls: str, k: int):
+        if cls in ("one", "neg-one", "zero"):
+            return None
+        return (True, "cf[%d]" % k) if cls == "ext" else (False, "cf[%d].c0" % k)
 
     def fresh(self, ext: bool) -> str:
         self.tmp += 1
@@ -190,14 +211,21 @@ class Emitter:
         self.emit("const %s %s = %s;" % ("fp2" if ext else "u64", name, e))
         return ext, name
 
-    def accumulate(self, acc: str, acc_ext: bool, cls: str, cval, vals) -> bool:
-        """acc += coefficient * product(vals); returns True when an extension x extension product went in"""
+    def accumulate(self, acc: str, acc_ext: bool, cls: str, cval, facs, constant_term: bool) -> bool:
+        """acc += coefficient * product(factors); returns True when an extension x extension product went in"""
         if cls == "zero":
             return False
-        vals = sorted(vals, key=lambda v: v[0])  # base factors first: their products are the cheap ones
+        if constant_term and cval is not None:  # an affine node's constant: added as it is
+            if acc_ext:
+                self.emit(("sg::add_e(%s, %s);" if cval[0] else "sg::add_b(%s, %s);") % (acc, cval[1]))
+            else:
+                self.emit("sg::addw(%s, %s);" % (acc, cval[1]))
+            return False
+        vals = [self.factor(f) for f in facs]  # emits the factor nodes that are not computed yet, and the table loads
         if cval is not None:
-            vals = sorted([cval] + vals, key=lambda v: v[0])
-        if not vals:  # a constant
+            vals.append(cval)
+        vals = sorted(vals, key=lambda v: v[0])  # base factors first: their products are the cheap ones
+        if not vals:  # a constant 1 or -1
             word = "1" if cls == "one" else "%dull" % (P - 1)
             self.emit(("sg::add_b(%s, %s);" if acc_ext else "sg::addw(%s, %s);") % (acc, word))
             return False
@@ -230,59 +258,43 @@ class Emitter:
             self.emit("sg::mac_bb(%s, %s, %s);" % (acc, chain[1], last[1]))
         return False
 
-    def sum_of(self, name: str, products) -> Tuple[bool, str]:
-        """products: [(class, [factor])] in stream order -> the typed value `name`"""
-        ext = any(self.product_type(c, fs) for c, fs in products if c != "zero")
-        acc = "a_" + name
-        self.emit(("sg::AccE %s = sg::acce_zero();" if ext else "sg::Acc %s = sg::acc_zero();") % acc)
+    def sum_of(self, name: str, products, occ: List[int], ext: bool, affine: bool) -> Tuple[bool, str]:
+        # one accumulator per nesting depth and type, reused by every node that is evaluated at that depth
+        self.depth = getattr(self, "depth", -1) + 1
+        self.max_depth = max(getattr(self, "max_depth", 0), self.depth)
+        acc = ("ae%d" if ext else "ab%d") % self.depth
+        if not hasattr(self, "accs"):
+            self.accs = set()
+        self.accs.add(acc)
+        self.emit(("%s = sg::acce_zero();" if ext else "%s = sg::acc_zero();") % acc)
         used7 = False
-        for c, fs in products:
-            cls, cval = self.coef(c)
-            used7 |= self.accumulate(acc, ext, cls, cval, [self.factor(f) for f in fs])
+        for j, (c, fs) in enumerate(products):
+            used7 |= self.accumulate(acc, ext, c, self.coef_value(c, occ[j]), fs, affine and j == 0)
         var = ("ne_%s" if ext else "nb_%s") % name
         if ext:
             self.emit("const fp2 %s = sg::red_e<%s>(%s);" % (var, "true" if used7 else "false", acc))
         else:
             self.emit("const u64 %s = sg::red(%s);" % (var, acc))
         self.emit("sg::fence();")
+        self.depth -= 1
         return ext, var
+
+    def node(self, j: int) -> Tuple[bool, str]:
+        if j not in self.done:
+            nd = self.g.nodes[j]
+            self.done[j] = self.sum_of("n%d" % j, self.products(nd), self.occ[j], self.ntype[j], nd[0] == "affine")
+        return self.done[j]
 
     def run(self) -> List[str]:
-        for j, nd in enumerate(self.g.nodes):
-            self.now = j
-            if nd[0] == "affine":
-                # konst + sum coef_i * table_i: the constant is a product without factors whose coefficient is the constant itself
-                prods = [(nd[1], [])] + [(c, [("t", t)]) for c, t in nd[2]]
-                self.node.append(self.affine_of("n%d" % j, prods))
-            else:
-                self.node.append(self.sum_of("n%d" % j, nd[1]))
-        self.now = len(self.g.nodes)
-        ext, var = self.sum_of("out", self.g.terms)
+        ext = any(self.product_type(c, fs) for c, fs in self.g.terms if c != "zero")
+        ext, var = self.sum_of("out", self.g.terms, self.term_occ, ext, False)
         self.emit("return %s;" % (var if ext else "f2(%s, 0)" % var))
-        return self.lines
-
-    def affine_of(self, name: str, prods) -> Tuple[bool, str]:
-        """like sum_of, but the first product is the node's constant: with no factors a general coefficient is added as it is"""
-        ext = any(self.product_type(c, fs) for c, fs in prods if c != "zero")
-        acc = "a_" + name
-        self.emit(("sg::AccE %s = sg::acce_zero();" if ext else "sg::Acc %s = sg::acc_zero();") % acc)
-        used7 = False
-        for c, fs in prods:
-            cls, cval = self.coef(c)
-            if not fs and cval is not None:  # the constant term
-                if ext:
-                    self.emit(("sg::add_e(%s, %s);" if cval[0] else "sg::add_b(%s, %s);") % (acc, cval[1]))
-                else:
-                    self.emit("sg::addw(%s, %s);" % (acc, cval[1]))
-                continue
-            used7 |= self.accumulate(acc, ext, cls, cval, [self.factor(f) for f in fs])
-        var = ("ne_%s" if ext else "nb_%s") % name
-        if ext:
-            self.emit("const fp2 %s = sg::red_e<%s>(%s);" % (var, "true" if used7 else "false", acc))
-        else:
-            self.emit("const u64 %s = sg::red(%s);" % (var, acc))
-        self.emit("sg::fence();")
-        return ext, var
+        decl = []
+        for kind, pre in (("sg::AccE", "ae"), ("sg::Acc", "ab")):
+            names = sorted(a for a in self.accs if a.startswith(pre))
+            if names:
+                decl.append("        %s %s;" % (kind, ", ".join(names)))
+        return decl + self.lines
 
 
 def graph_code(g: Graph) -> str:
