@@ -803,6 +803,56 @@ def block_device_trace(line: dict, extras: dict, commit_h_ms: float) -> dict:
             "reference_published": "22.9 - 34.2 proved tokens/s on an Apple M3 Ultra (whole prover, host work included)"}
 
 
+D55_BLOCKS = 8
+# S1 of the bench's D55 run (below) proved by ONE process; every world size must join to the same state (run_fork.rs:1819-1827)
+D55_EXPECTED_S1 = "580eed19e1f6e23ffa6abdebff52bb1c09155fc84876e64d894e43aed53008cf"
+
+
+def d55_leg(dev, backend, rank: int, world: int, col_key, leaf_key, node_key) -> dict:
+    """A D55 commit-fork-join run with the forks' work on the device: D55_BLOCKS blocks, block k proved by rank k mod world (a
+    hiding commitment with its tree, an opening and a masked sumcheck with the device Fiat-Shamir step per fork:
+    d55.device_fork), the fixed-size join records all-gathered over NCCL, the join replayed on every rank.  Returns S1 and the
+    wall time; S1 does not depend on the world size."""
+    import torch
+    import torch.distributed as dist
+    from intelligenceregulation_b200 import d55
+
+    lc, ir, rows, q, nv = 12, 2, 296, 64, 14
+    nn = ir << lc
+    pows = coset_powers(nn)
+    header = d55.RunHeader(WORK["profile"].encode(), col_key, D55_BLOCKS, (128, 4096, 14336, 32, 8, 128), b"\x01" * 64, b"\x02" * 32, b"bench", b"\x03" * 16,
+                           b"\x04" * 32)
+    roots = [bytes([16 + k]) * 32 for k in range(D55_BLOCKS - 1)]  # boundary roots: rank 0 commits them in a real run; public here
+    digs = [bytes([64 + k]) * 32 for k in range(D55_BLOCKS)]
+
+    def block(k):
+        return dict(log_cols=lc, inv_rate=ir, data=witness_words(0xD5500 + k, rows, 1 << lc), pads=splitmix_fp(0xD5600 + k, rows * q),
+                    salts=(splitmix_fp(0xD5700 + k, nn * 4).view(np.uint8)).reshape(nn, 32), pows=pows, keys=(col_key, leaf_key, node_key),
+                    tables=splitmix_fp(0xD5800 + k, 4 * (1 << nv) * 2).reshape(4, 1 << nv, 2), mask=splitmix_fp(0xD5900 + k, ((nv + 1) * 3 + 2) * 2).reshape(-1, 2))
+
+    def gather(buf):
+        mine = torch.frombuffer(bytearray(buf), dtype=torch.uint8).cuda()
+        out = torch.empty(world * mine.numel(), dtype=torch.uint8, device="cuda")
+        dist.all_gather_into_tensor(out, mine)
+        host = out.cpu().numpy().tobytes()
+        return [host[i * len(buf):(i + 1) * len(buf)] for i in range(world)]
+
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    s1 = d55.run_forks(header, roots, [40] * (D55_BLOCKS - 1), [14] * (D55_BLOCKS - 1), digs,
+                       lambda k, tr: d55.device_fork(dev, backend, k, tr, block(k)), rank, world, gather if world > 1 else None)
+    wall = time.perf_counter() - t0
+    out = {"blocks": D55_BLOCKS, "s1": s1.state.hex(), "counter": s1.counter, "wall_ms": wall * 1e3,
+           "fork": f"commit {rows} x 2^{lc} -> 2^{lc + 1} with tree, opening (1 combination, 8 columns), masked zero-check sumcheck of 2^{nv} points",
+           "exchange": "one all-gather of fixed-size join records over NCCL" if world > 1 else "none (one process)"}
+    if D55_EXPECTED_S1 is not None:
+        assert out["s1"] == D55_EXPECTED_S1, "the D55 join state differs from the one-process value"
+        out["s1_equals_one_process_value"] = True
+    return out
+
+
 def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     import torch
     import torch.distributed as dist
@@ -1018,6 +1068,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     hash_compressions = nn * ((rows * 8 + 63) // 64 + (rows + 127) // 128 - 1)
     bfly_peak = dev.ctx.butterfly_peak(400)
     bfly_per_launch = rows * (1 + ir) * (n // 2) * log_cols
+    d55_out = d55_leg(dev, backend, rank, world, col_key, leaf_key, node_key)
     extras = device_extras(dev, backend, np_data, np_pads, np_pows, col_key) if (world == 1 and rank == 0 and not args.no_extras) else None
     extras_cpu = cpu_extras(o, backend, np_data) if extras is not None else None
     ref_cuda_ms = reference_cuda_extras(dev, backend, d_data, d_pads, d_pows, col_key) if extras is not None else None
@@ -1056,6 +1107,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
             "other_kernels_rooflines": extras_rooflines(extras, peak) if extras else None,
             "other_kernels_cpu_ms": extras_cpu,
             "reference_cuda_ms": ref_cuda_ms,
+            "d55": d55_out,
             "root": root_resident.hex(),
         }
         if extras:

@@ -234,3 +234,64 @@ def run_forks(header: RunHeader, roots: Sequence[bytes], rows: Sequence[int], lo
     if failures:
         raise ForkFailed(failures)
     return join(s0, records, header.blocks)
+
+
+# ----------------------------------------------------------------------------------------------- a fork's device work
+def squeeze_index(tr: HostTranscript, bound: int) -> int:
+    """one index below the power of two `bound` from one squeeze (transcript.rs:150-167 takes four per squeeze; a fork here
+    needs a handful)"""
+    return int.from_bytes(tr.squeeze()[:8], "little") & (bound - 1)
+
+
+def device_fork(dev, backend, k: int, tr: HostTranscript, block: dict) -> JoinRecord:
+    """What one block's fork asks of the device, in the order a block proof asks it (protocol.rs:2231-2434 in outline):
+    a hiding commitment with its salted tree, the root absorbed; an opening of that commitment at a transcript-drawn
+    combination and transcript-drawn columns, absorbed; a masked zero-check sumcheck with the device Fiat-Shamir step
+    continuing the fork's transcript.  `block`: log_cols, inv_rate, data, pads, salts, pows, keys (column, leaf, node),
+    tables (4 x 2^n x 2), mask.  Everything is a function of (k, transcript, block): whichever rank runs it, the record is
+    the same."""
+    import numpy as np
+
+    lc, ir = block["log_cols"], block["inv_rate"]
+    nn = ir << lc
+    rows = block["data"].size >> lc
+    ck, lk, nk = block["keys"]
+    got = dev.try_commit_zk_tree(lc, ir, block["data"], block["pads"], block["pows"], lc + (ir.bit_length() - 1), ck, block["salts"], lk, nk,
+                                 want_leaves=False)
+    if got is None:
+        raise RuntimeError("D55 fork %d: the device declined the commitment: %s" % (k, dev.ctx.declines[-1][1]))
+    store, _, levels = got
+    try:
+        tr.absorb(b"A", bytes(levels[-1]))
+        tr.absorb_u64(b"rows", rows)
+        tr.absorb_u64(b"log-cols", lc)
+        rho = np.array([tr.challenge_fp2() for _ in range(rows)], dtype=np.uint64).reshape(1, rows, 2)
+        fold = store.fold_rows_with_pads(rho)
+        tr.absorb(b"pb-open-fold", fold.tobytes())
+        idx = np.array([squeeze_index(tr, nn) for _ in range(8)], dtype=np.uint64)
+        cols = store.columns(idx)
+        tr.absorb(b"pb-open-cols", cols.tobytes())
+    finally:
+        store.free()
+    tables, mask = block["tables"], block["mask"]
+    n = int(tables.shape[1]).bit_length() - 1
+    tr.absorb_u64(b"pb-slot", k)
+    c = tr.challenge_fp2()
+    ev = backend.B200Rounds(dev.ctx, backend.POLY_ZC, tables, 3)
+    try:
+        sums, absorbed, _, state, counter, _ = ev.batched(n, tr.state, tr.counter, tr.key, mask=mask, mask_vars=n + 1, mask_c=c)
+        finals = ev.finals()
+    finally:
+        ev.free()
+    # the caller replays the device's rounds through its own transcript (gpu/metal.rs:4156-4171) and must land on the device's state
+    for j in range(n):
+        tr.absorb(b"sc-round", absorbed[j].tobytes())
+        tr.challenge_fp2()
+    if tr.state != state or tr.counter != counter:
+        raise RuntimeError("D55 fork %d: the device's transcript left the host's" % k)
+    tr.absorb(b"pb-term", finals.tobytes())
+    value = (int(fold[0, 0, 0]), int(fold[0, 0, 1]))
+    point = [(int(a), int(b)) for a, b in rho[0, :min(rows, lc)]]
+    ic = claim_bytes([(value, [(0, lc, (1, 0), point)])])
+    oc = claim_bytes([((int(finals[0, 0]), int(finals[0, 1])), [(1 << lc, lc, (1, 0), point)])])
+    return JoinRecord(k, tr.state, tr.counter, ic, oc)
