@@ -50,9 +50,14 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if verbose:
         common += ["-Xptxas", "-v"]
     procs = []
+    # a source is recompiled when it, or any header of the library, is newer than its object
+    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))] + [os.path.join(HERE, "..", "include", f) for f in ("hl_b200.h", "hl_b200_bench.h")]
+    newest_header = max(os.path.getmtime(h) for h in headers)
     for src in SOURCES + gen_sources:
         obj = os.path.join(obj_dir, os.path.basename(src).replace(".cu", ".o"))
         objs.append(obj)
+        if not force and not verbose and os.path.exists(obj) and os.path.getmtime(obj) > max(newest_header, os.path.getmtime(os.path.join(CSRC, src))):
+            continue
         procs.append((src, subprocess.Popen(common + ["-c", os.path.join(CSRC, src), "-o", obj], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     failed = False
     for src, p in procs:

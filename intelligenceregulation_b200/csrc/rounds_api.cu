@@ -56,6 +56,20 @@ void free_rounds(hl_rounds* r) {
     delete r;
 }
 
+// the reduce + Fiat-Shamir step of round r->next over `nb` partial rows
+int launch_step(hl_rounds* r, u32 nb, int fs, int use_claim, int recover, const u64* d_mask, const u64* d_hs, int mask_vars) {
+    hl_ctx* c = r->ctx;
+    hlk::ScStep a;
+    a.partials = r->d_partials; a.nblocks = nb; a.degree = (int)r->degree; a.round = (int)r->next;
+    a.use_claim = use_claim; a.recover = recover; a.fs = fs; a.mask = d_mask; a.mask_half_suffix = d_hs; a.mask_vars = mask_vars;
+    a.inv_den = r->d_inv_den; a.state = r->d_state; a.out = r->d_out;
+    a.eval_degree = (int)r->eval_degree; a.extrap = r->d_extrap;
+    cudaError_t e = hlk::sc_step(a, c->stream);
+    c->stats.kernel_launches++;
+    if (e != cudaSuccess) return fail(c, HL_B200_ERR_DEVICE, "round step launch", e);
+    return HL_B200_OK;
+}
+
 // launches round j's kernels; the caller holds the context lock
 int launch_round(hl_rounds* r, int eval_one, int fs, int use_claim, int recover, const u64* d_mask, const u64* d_hs, int mask_vars) {
     hl_ctx* c = r->ctx;
@@ -81,15 +95,7 @@ int launch_round(hl_rounds* r, int eval_one, int fs, int use_claim, int recover,
     }
     c->stats.kernel_launches++;
     if (e != cudaSuccess) return fail(c, HL_B200_ERR_DEVICE, "round launch", e);
-    hlk::ScStep a;
-    a.partials = r->d_partials; a.nblocks = nb; a.degree = (int)r->degree; a.round = (int)r->next;
-    a.use_claim = use_claim; a.recover = recover; a.fs = fs; a.mask = d_mask; a.mask_half_suffix = d_hs; a.mask_vars = mask_vars;
-    a.inv_den = r->d_inv_den; a.state = r->d_state; a.out = r->d_out;
-    a.eval_degree = (int)r->eval_degree; a.extrap = r->d_extrap;
-    e = hlk::sc_step(a, c->stream);
-    c->stats.kernel_launches++;
-    if (e != cudaSuccess) return fail(c, HL_B200_ERR_DEVICE, "round step launch", e);
-    return HL_B200_OK;
+    return launch_step(r, nb, fs, use_claim, recover, d_mask, d_hs, mask_vars);
 }
 
 int launch_fold(hl_rounds* r) {
@@ -111,6 +117,8 @@ extern "C" {
 namespace {
 
 // the evaluator of either kind; `words` is the data form of the polynomial when poly == POLY_IR
+constexpr size_t FUSED_FOLD_MAX_PAIRS = (size_t)1 << 15;
+
 struct GenAsk {  // a slot program's generated kernel, looked up by the caller
     const sg::Entry* entry = nullptr;
     std::vector<fp2> cfo;
@@ -373,10 +381,48 @@ int hl_b200_rounds_batched(hl_rounds* r, uint32_t nd, hl_fs_state* fs, const uin
     {
         Timed t(c, HL_T_ROUNDS);
         u32 i = 0;
-        for (; i < nd && !rc && r->len > r->tail_len; i++) {
-            rc = launch_round(r, have_claim ? 0 : 1, 1, have_claim ? 1 : 0, fs->recover_one ? 1 : 0, d_mask, d_hs, (int)mask_vars);
-            if (!rc) rc = launch_fold(r);
-            have_claim = fs->recover_one != 0;
+        if (r->poly == hlk::POLY_IR) {
+            for (; i < nd && !rc && r->len > r->tail_len; i++) {
+                rc = launch_round(r, have_claim ? 0 : 1, 1, have_claim ? 1 : 0, fs->recover_one ? 1 : 0, d_mask, d_hs, (int)mask_vars);
+                if (!rc) rc = launch_fold(r);
+                have_claim = fs->recover_one != 0;
+            }
+        } else {
+            // closed-form families: after the first long round the fold with the last challenge rides on the next round's pass
+            // (two launches per round, every table word read once and written once); `pending`: the tables are still stored at
+            // twice r->len
+            bool pending = false;
+            for (; i < nd && !rc && r->len > r->tail_len; i++) {
+                const int eval_one = have_claim ? 0 : 1;
+                // While a round's arithmetic fills the machine (the first rounds of a large cube) the fused pass is the slower
+                // one (it folds both halves before it can evaluate: measured 79 us against 40 + 15 at 2^19 pairs); once a round
+                // is down at the launch floor it saves one launch of three.
+                if (pending && r->len / 2 > FUSED_FOLD_MAX_PAIRS) {
+                    cudaError_t e = hlk::sc_fold(r->d_tables, r->stride, (u32)r->len, r->k, r->d_state, c->stream);
+                    c->stats.kernel_launches++;
+                    if (e != cudaSuccess) { rc = fail(c, HL_B200_ERR_DEVICE, "fold launch", e); break; }
+                    pending = false;
+                }
+                if (!pending) {
+                    rc = launch_round(r, eval_one, 1, have_claim ? 1 : 0, fs->recover_one ? 1 : 0, d_mask, d_hs, (int)mask_vars);
+                } else {
+                    const u32 nb = hlk::sc_round_blocks((u32)(r->len / 2), c->sm_count);
+                    cudaError_t e = hlk::sc_fold_round(r->poly, (int)r->k, r->d_tables, r->stride, (u32)r->len, r->d_coefs, r->d_state, eval_one, r->d_partials,
+                                                       nb, c->stream);
+                    c->stats.kernel_launches++;
+                    if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "fold + round launch", e);
+                    if (!rc) rc = launch_step(r, nb, 1, have_claim ? 1 : 0, fs->recover_one ? 1 : 0, d_mask, d_hs, (int)mask_vars);
+                }
+                r->len /= 2;
+                r->next++;
+                pending = true;
+                have_claim = fs->recover_one != 0;
+            }
+            if (!rc && pending) {  // the last challenge's fold
+                cudaError_t e = hlk::sc_fold(r->d_tables, r->stride, (u32)r->len, r->k, r->d_state, c->stream);
+                c->stats.kernel_launches++;
+                if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "fold launch", e);
+            }
         }
         if (!rc && i < nd) {  // the short rounds: one CTA, no launches in between
             hlk::ScStep a;

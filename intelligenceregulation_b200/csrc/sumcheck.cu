@@ -160,8 +160,8 @@ __device__ void step_body(const ScStep& a, StepSmem& sm, int lane) {
     if (lane < np) {
         fp2 m = s[lane];
         if (mk) {
-            const fp2* aj = mk + 2 + (size_t)j * a.degree;
-            const fp2 base = f2_add(f2_add(mk[0], st->acc_prev), reinterpret_cast<const fp2*>(a.mask_half_suffix)[j]);
+            const fp2* aj = a.mask_row ? reinterpret_cast<const fp2*>(a.mask_row) : mk + 2 + (size_t)j * a.degree;
+            const fp2 base = f2_add(f2_add(mk[0], st->acc_prev), a.hs_row ? reinterpret_cast<const fp2*>(a.hs_row)[0] : reinterpret_cast<const fp2*>(a.mask_half_suffix)[j]);
             const u64 scale = 1ull << (a.mask_vars - 1 - j);  // mask_vars <= 63: the power of two is its own canonical word
             const u64 x = (u64)lane;
             fp2 u = f2(0, 0);
@@ -217,7 +217,7 @@ __device__ void step_body(const ScStep& a, StepSmem& sm, int lane) {
         if (lane == 0) st->claim = term;
     }
     if (mk && lane == 8) {  // the mask's running terms: sum_i u_i(r_i) and prod r_i
-        const fp2* aj = mk + 2 + (size_t)j * a.degree;
+        const fp2* aj = a.mask_row ? reinterpret_cast<const fp2*>(a.mask_row) : mk + 2 + (size_t)j * a.degree;
         fp2 u = f2(0, 0), xp = f2_one();
         for (int e = 1; e <= a.degree; e++) { xp = f2_mul(xp, r); u = f2_add(u, f2_mul(aj[e - 1], xp)); }
         st->acc_prev = f2_add(st->acc_prev, u);
@@ -231,6 +231,25 @@ constexpr int STEP_T = 512;
 __global__ void __launch_bounds__(STEP_T) k_sc_step(ScStep a) {
     __shared__ StepSmem sm;
     __shared__ u64 red[STEP_T];
+    // everything the serial step reads is fetched by the whole CTA while the partials are summed: the step itself then waits on
+    // no global load (each one is most of a microsecond for a single warp)
+    __shared__ hlk::ScState st_s;
+    __shared__ u64 mk_s[4], row_s[2 * hlk::SC_MAX_POINTS], hs_s[2], invden_s[hlk::SC_MAX_POINTS], extrap_s[hlk::SC_MAX_POINTS * hlk::SC_MAX_POINTS];
+    hlk::ScState* const st_global = a.state;
+    {
+        const u32* src = reinterpret_cast<const u32*>(a.state);
+        u32* dst = reinterpret_cast<u32*>(&st_s);
+        if (threadIdx.x < sizeof(hlk::ScState) / 4) dst[threadIdx.x] = src[threadIdx.x];
+        const int t = (int)threadIdx.x - 64;
+        if (a.mask && a.fs) {
+            if (t >= 0 && t < 4) mk_s[t] = a.mask[t];
+            if (t >= 8 && t < 8 + 2 * a.degree) row_s[t - 8] = a.mask[4 + 2 * (size_t)a.round * a.degree + (t - 8)];
+            if (t >= 32 && t < 34) hs_s[t - 32] = a.mask_half_suffix[2 * (size_t)a.round + (t - 32)];
+        }
+        if (t >= 40 && t < 40 + a.degree + 1) invden_s[t - 40] = a.inv_den[t - 40];
+        const int ne = a.extrap ? (a.degree - a.eval_degree) * (a.eval_degree + 1) : 0;
+        if (t >= 64 && t < 64 + ne) extrap_s[t - 64] = a.extrap[t - 64];
+    }
     const int W = 2 * (a.degree + 1);              // <= 16 words per partial row
     const int w = threadIdx.x & 15, grp = threadIdx.x >> 4;  // STEP_T / 16 groups stride over the rows
     u64 s = 0;
@@ -246,7 +265,17 @@ __global__ void __launch_bounds__(STEP_T) k_sc_step(ScStep a) {
     }
     if (threadIdx.x < W) sm.sums[threadIdx.x] = red[threadIdx.x];
     __syncthreads();
-    if (threadIdx.x < 32) step_body(a, sm, threadIdx.x);
+    if (threadIdx.x < 32) {
+        if (a.mask && a.fs) { a.mask = mk_s; a.mask_row = row_s; a.hs_row = hs_s; }
+        a.inv_den = invden_s;
+        if (a.extrap) a.extrap = extrap_s;
+        a.state = &st_s;
+        step_body(a, sm, threadIdx.x);
+        __syncwarp();
+        const u32* src = reinterpret_cast<const u32*>(&st_s);
+        u32* dst = reinterpret_cast<u32*>(st_global);
+        for (u32 i = threadIdx.x; i < sizeof(hlk::ScState) / 4; i += 32) dst[i] = src[i];
+    }
 }
 
 // The tail of a sumcheck in ONE CTA: once a round has at most TAIL_HALF pairs, the remaining rounds (round sums,
@@ -352,6 +381,63 @@ __global__ void __launch_bounds__(256) k_sc_nonbase(const u64* __restrict__ tabl
     u64 any = 0;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < len; i += (size_t)gridDim.x * blockDim.x) any |= tb[2 * i + 1];
     if (__syncthreads_or(any != 0) && threadIdx.x == 0) atomicOr(mask, 1ull << t);
+}
+
+// The fold with the previous challenge and the sums of the next round in ONE pass (the closed-form families): the tables are
+// stored at length 2 n, unfolded; a thread reads T[i], T[i + n], T[i + half], T[i + half + n] (half = n / 2), writes the two
+// folded entries T[i], T[i + half] - no other thread reads or writes those four places - and evaluates the round polynomial
+// on them.  A table word is read once and written once per round, and a round is two launches (this one and the step).
+template <int POLY, int K, int D>
+__global__ void __launch_bounds__(RT) k_sc_fold_round(u64* __restrict__ tables, size_t stride, u32 n, const u64* __restrict__ coefs,
+                                                      const hlk::ScState* __restrict__ st, int eval_one, u64* __restrict__ partials) {
+    fp2 acc[D + 1];
+#pragma unroll
+    for (int d = 0; d <= D; d++) acc[d] = f2(0, 0);
+    const fp2* cf = reinterpret_cast<const fp2*>(coefs);
+    const fp2 r = st->r;
+    const u32 half = n >> 1;
+    for (u32 i = blockIdx.x * RT + threadIdx.x; i < half; i += gridDim.x * RT) {
+        fp2 cur[K], dif[K];
+#pragma unroll
+        for (int t = 0; t < K; t++) {
+            u64* tb = tables + 2 * (size_t)t * stride;
+            const fp2 a0 = ld2(tb + 2 * (size_t)i), a1 = ld2(tb + 2 * ((size_t)i + n));
+            const fp2 b0 = ld2(tb + 2 * ((size_t)i + half)), b1 = ld2(tb + 2 * ((size_t)i + half + n));
+            const fp2 lo = f2_add(a0, f2_mul(r, f2_sub(a1, a0))), hi = f2_add(b0, f2_mul(r, f2_sub(b1, b0)));
+            st2(tb + 2 * (size_t)i, lo);
+            st2(tb + 2 * ((size_t)i + half), hi);
+            cur[t] = lo;
+            dif[t] = f2_sub(hi, lo);
+        }
+        acc[0] = f2_add(acc[0], poly_eval<POLY, K>(cur, cf));
+#pragma unroll
+        for (int d = 1; d <= D; d++) {
+#pragma unroll
+            for (int t = 0; t < K; t++) cur[t] = f2_add(cur[t], dif[t]);
+            if (d != 1 || eval_one) acc[d] = f2_add(acc[d], poly_eval<POLY, K>(cur, cf));
+        }
+    }
+#pragma unroll
+    for (int d = 0; d <= D; d++) {
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+            acc[d].c0 = gl_add(acc[d].c0, shfl_down64(acc[d].c0, off));
+            acc[d].c1 = gl_add(acc[d].c1, shfl_down64(acc[d].c1, off));
+        }
+    }
+    __shared__ u64 wsum[RT / 32][2 * (D + 1)];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) {
+#pragma unroll
+        for (int d = 0; d <= D; d++) { wsum[warp][2 * d] = acc[d].c0; wsum[warp][2 * d + 1] = acc[d].c1; }
+    }
+    __syncthreads();
+    if (threadIdx.x < 2 * (D + 1)) {
+        u64 s = 0;
+#pragma unroll
+        for (int w = 0; w < RT / 32; w++) s = gl_add(s, wsum[w][threadIdx.x]);
+        partials[(size_t)blockIdx.x * 2 * (D + 1) + threadIdx.x] = s;
+    }
 }
 
 __global__ void __launch_bounds__(256) k_sc_fold(u64* __restrict__ tables, size_t stride, u32 half, u32 k, const hlk::ScState* __restrict__ st) {
@@ -838,6 +924,36 @@ bool sc_supported(int poly, int k, int degree) {
 cudaError_t sc_round(int poly, int k, const u64* tables, size_t stride, u32 half, const u64* coefs, int eval_one, u64* partials,
                      u32 nblocks, cudaStream_t s) {
 #define R(P, K, D) return launch_round<P, K, D>(tables, stride, half, coefs, eval_one, partials, nblocks, s)
+    switch (poly) {
+        case POLY_PROD:
+            switch (k) {
+                case 1: R(POLY_PROD, 1, 1);
+                case 2: R(POLY_PROD, 2, 2);
+                case 3: R(POLY_PROD, 3, 3);
+                case 4: R(POLY_PROD, 4, 4);
+                case 5: R(POLY_PROD, 5, 5);
+                case 6: R(POLY_PROD, 6, 6);
+            }
+            break;
+        case POLY_ZC: R(POLY_ZC, 4, 3);
+        case POLY_LOGUP_Q: R(POLY_LOGUP_Q, 3, 3);
+        case POLY_LOGUP_T: R(POLY_LOGUP_T, 4, 3);
+    }
+#undef R
+    return cudaErrorInvalidValue;
+}
+
+template <int POLY, int K, int D>
+static cudaError_t launch_fold_round(u64* tables, size_t stride, u32 n, const u64* coefs, const ScState* st, int eval_one, u64* partials, u32 nblocks,
+                                     cudaStream_t s) {
+    k_sc_fold_round<POLY, K, D><<<nblocks, RT, 0, s>>>(tables, stride, n, coefs, st, eval_one, partials);
+    return cudaGetLastError();
+}
+
+// fold with the challenge in `st` and the sums of the next round (table length n after the fold) in one pass
+cudaError_t sc_fold_round(int poly, int k, u64* tables, size_t stride, u32 n, const u64* coefs, const ScState* st, int eval_one, u64* partials,
+                          u32 nblocks, cudaStream_t s) {
+#define R(P, K, D) return launch_fold_round<P, K, D>(tables, stride, n, coefs, st, eval_one, partials, nblocks, s)
     switch (poly) {
         case POLY_PROD:
             switch (k) {

@@ -33,6 +33,8 @@ struct ScStep {
     int fs;                     // 0: only reduce and write the sums (host-driven round())
     const u64* mask;            // CFS coefficients [a0, a', a_{j,e}] or NULL
     const u64* mask_half_suffix;  // per round j: sum_{i>j} u_i(1)/2
+    const u64* mask_row = nullptr;  // when set: this round's `degree` coefficients a_{j,e} and (hs_row) its suffix term, already picked out
+    const u64* hs_row = nullptr;
     int mask_vars;
     const u64* inv_den;         // degree+1 inverse Lagrange denominators
     int eval_degree;            // the sums arrive at the points 0..eval_degree; the points above are extrapolated
@@ -64,6 +66,9 @@ bool sc_supported(int poly, int k, int degree);
 cudaError_t sc_round(int poly, int k, const u64* tables, size_t stride, u32 half, const u64* coefs, int eval_one, u64* partials,
                      u32 nblocks, cudaStream_t s);
 cudaError_t sc_step(const ScStep& a, cudaStream_t s);
+// closed-form families: fold with the challenge in `st` and sum the next round (length n after the fold) in one pass
+cudaError_t sc_fold_round(int poly, int k, u64* tables, size_t stride, u32 n, const u64* coefs, const ScState* st, int eval_one, u64* partials,
+                          u32 nblocks, cudaStream_t s);
 constexpr u32 SC_TAIL_LEN = 1024;  // table length from which the remaining rounds run in one CTA (one SM: above it a round's arithmetic costs more than three launches)
 cudaError_t sc_tail(int poly, int k, u64* tables, size_t stride, u32 len, const u64* coefs, const ScStep& a, int nrounds,
                     int first_has_claim, u64* scratch, cudaStream_t s);

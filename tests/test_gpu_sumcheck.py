@@ -147,11 +147,15 @@ def test_l6_corpus_sumchecks_on_the_device(ctx, oracle, golden_dir):
     assert done >= 14
 
 
-@pytest.mark.parametrize("poly_name,k,deg,n", [("prod", 2, 2, 12), ("zc", 4, 3, 16), ("prod", 3, 3, 14), ("logup_q", 3, 3, 15), ("logup_t", 4, 3, 13)])
+@pytest.mark.parametrize("poly_name,k,deg,n", [("prod", 2, 2, 12), ("zc", 4, 3, 16), ("prod", 3, 3, 14), ("logup_q", 3, 3, 15), ("logup_t", 4, 3, 13),
+                                               ("prod", 6, 6, 11), ("prod", 1, 1, 17), ("zc", 4, 3, 20), ("logup_q", 3, 3, 19)])
 def test_random_cubes_masked_batches_match_the_oracle(ctx, oracle, poly_name, k, deg, n):
-    """Larger cubes (many CTAs per round, partial-sum trees) against the oracle's prover, masked, keyed, with recovery."""
+    """Larger cubes (many CTAs per round, partial-sum trees) against the oracle's prover, masked, keyed, with the running claim
+    from the first round on, and (second run) without claim recovery in two batches, where the point 1 is evaluated in every round
+    and the second batch starts in the middle of the long rounds."""
     o = oracle
     from intelligenceregulation_b200 import backend
+
 
     poly = {"prod": 0, "zc": 1, "logup_q": 2, "logup_t": 3}[poly_name]
     rng = o.ZkRng(1000 + n, b"b200-sumcheck-test")
@@ -174,6 +178,16 @@ def test_random_cubes_masked_batches_match_the_oracle(ctx, oracle, poly_name, k,
     assert (ev.finals() == want.finals).all()
     assert claim == o.interpolate_eval(want.rounds[-1], tuple(map(int, want.challenges[-1])))
     ev.free()
+    if n <= 17:  # no recovery, no mask, in two batches: the second one starts in the middle of the long rounds
+        t2 = tr.clone()
+        want = o.sc_prove(poly, tables, deg, t2, coefs=coefs)
+        ev = backend.B200Rounds(ctx, poly, tables, deg, coefs)
+        first = max(1, n - 11)
+        a_ = ev.batched(first, tr.state, tr.counter, key)
+        b_ = ev.batched(n - first, a_[3], a_[4], key)
+        assert (np.concatenate([a_[0], b_[0]]) == want.rounds).all() and b_[3] == t2.state
+        assert (ev.finals() == want.finals).all()
+        ev.free()
 
 
 def test_round_order_is_enforced(ctx, oracle):
