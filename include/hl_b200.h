@@ -165,6 +165,23 @@ const uint64_t* hl_b200_store_encoded_dev(hl_store* store);
 const uint8_t* hl_b200_store_leaves_dev(hl_store* store);
 void hl_b200_store_free(hl_store* store);
 
+/* ---- the verifier's per-column checks of a hiding opening (pcs.rs:1303-1331, the parallel map of `verify_zk_tagged`;
+ * merkle.rs:120-127 `verify_path_keyed`; pcs.rs:696-715 `salt_leaf_keyed`) ----
+ * cols: ncols runs of `rows` words (OpeningZk::columns in order); idx: the sampled position of each; salts32: ncols x 32;
+ * paths32: ncols x depth x 32, the sibling next to the leaf first (the caller has checked every path's length against the
+ * tree's depth, pcs.rs:1258-1263); the three keys are NULL for the untagged profile.
+ * rhos: k x rows Fp2, the combined row weights of the groups followed by the proximity weights.  What each combination
+ * rho_g^T col must equal is given either as `wants` (k x ncols Fp2: the encoded clear vector g at idx[c]) or as
+ * `vec_store`, a hiding commitment of the 2k rows (re of vector 0, im of vector 0, re of vector 1, ..) made on this
+ * context with store != 0, whose encoding is then read in place.  Exactly one of the two when k > 0.
+ * verdict[c]: 0 every check holds; 1 the Merkle path of column c fails; 2 + g column c disagrees with clear vector g
+ * (the first such g; the path is checked first, as in the reference).  first_bad (may be NULL): the first c with a
+ * non-zero verdict, or -1. */
+int hl_b200_verify_columns(hl_ctx* ctx, const uint64_t* cols, size_t rows, size_t ncols, const uint64_t* idx, const uint8_t* salts32,
+                           const uint8_t* paths32, uint32_t depth, const uint8_t* root32, const uint8_t* column_key32,
+                           const uint8_t* leaf_key32, const uint8_t* node_key32, const uint64_t* rhos, size_t k, const uint64_t* wants,
+                           const hl_store* vec_store, int32_t* verdict, int64_t* first_bad);
+
 /* ---- SumcheckRounds (sumcheck/rounds.rs:22-28; CPU evaluator ClosureRounds :52-167) ----
  * k tables of 2^n_vars Fp2 (table-major, variable 0 = most significant index bit) and a slot polynomial
  * from a fixed family; round j returns the UNMASKED values at 0..=degree of

@@ -229,6 +229,31 @@ class Context:
         self.check(self.lib.hl_b200_fold_cols_i8(self.h, _ptr(m), m.shape[0], m.shape[1], _ptr(c), _ptr(out)))
         return out
 
+    def verify_columns(self, cols, idx, salts, paths, root: bytes, column_key: Optional[bytes], leaf_key: Optional[bytes], node_key: Optional[bytes],
+                       rhos=None, wants=None, vec_store: Optional["B200Commit"] = None) -> np.ndarray:
+        """The verifier's per-column checks (pcs.rs:1303-1331): cols (ncols, rows), idx (ncols,), salts (ncols, 32), paths (ncols, depth, 32).
+        Returns one verdict per column: 0 accepted, 1 Merkle path fails, 2 + g disagrees with clear vector g.  What the combinations must equal
+        comes as `wants` (k, ncols, 2) or as `vec_store`, the device commitment of the clear vectors' re / im rows."""
+        cols, idx = _u64(cols), _u64(idx)
+        ncols = idx.size
+        rows = cols.size // ncols
+        salts = np.ascontiguousarray(salts, dtype=np.uint8).reshape(ncols, 32)
+        paths = np.ascontiguousarray(paths, dtype=np.uint8).reshape(ncols, -1, 32)
+        depth = paths.shape[1]
+        k = 0
+        if rhos is not None:
+            rhos = _u64(rhos).reshape(-1, rows, 2)
+            k = rhos.shape[0]
+        if wants is not None:
+            wants = _u64(wants).reshape(k, ncols, 2)
+        verdict = np.empty(ncols, dtype=np.int32)
+        first = C.c_int64()
+        self.check(self.lib.hl_b200_verify_columns(self.h, _ptr(cols), rows, ncols, _ptr(idx), _ptr(salts), _ptr(paths) if depth else None, depth, _ptr(root),
+                                                   _ptr(column_key), _ptr(leaf_key), _ptr(node_key), _ptr(rhos) if k else None, k,
+                                                   _ptr(wants) if wants is not None else None, vec_store.h if vec_store is not None else None,
+                                                   _ptr(verdict), C.byref(first)))
+        return verdict
+
     def merkle(self, leaves: np.ndarray, salts: Optional[np.ndarray], leaf_key: Optional[bytes], node_key: Optional[bytes]) -> np.ndarray:
         """salt_leaf_keyed + MerkleTree::build_keyed: all levels, (2 nn - 1, 32) bytes, root last."""
         leaves = np.ascontiguousarray(leaves, dtype=np.uint8)
@@ -395,6 +420,24 @@ class B200Backend:
             return None
         st = B200Commit(self.ctx, h)
         return (st, leaves, levels) if tree else (st, leaves)
+
+    def check_opening_columns(self, log_cols: int, inv_rate: int, pows, max_log: int, cols, idx, salts, paths, root: bytes, column_key: Optional[bytes],
+                              leaf_key: Optional[bytes], node_key: Optional[bytes], rhos, vecs) -> Optional[np.ndarray]:
+        """The data-parallel part of `verify_zk_tagged` (pcs.rs:1282-1331) on the device: the clear vectors (G + 1, n + q, 2) are encoded as
+        2 (G + 1) base rows (re and im apart, pcs.rs:1287-1296) by the commitment's own encoder, and every opened column is hashed, walked to the
+        root and compared with them.  None when the device declines the shape (the caller then runs its host body)."""
+        vecs = _u64(vecs)
+        n = 1 << log_cols
+        g1 = vecs.shape[0]
+        planes = np.ascontiguousarray(np.moveaxis(vecs, 2, 1)).reshape(2 * g1, -1)  # row 2 g + c = component c of vector g
+        got = self.try_commit_zk_keyed(log_cols, inv_rate, np.ascontiguousarray(planes[:, :n]), np.ascontiguousarray(planes[:, n:]), pows, max_log, None)
+        if got is None:
+            return None
+        store, _ = got
+        try:
+            return self.ctx.verify_columns(cols, idx, salts, paths, root, column_key, leaf_key, node_key, rhos=rhos, vec_store=store)
+        finally:
+            store.free()
 
     def commit_zk_dev(self, log_cols: int, inv_rate: int, d_data: int, rows: int, d_pads: int, q: int, d_pows: int,
                       key: Optional[bytes], d_leaves: int = 0) -> B200Commit:

@@ -15,7 +15,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libhl_b200.so")
-SOURCES = ["api.cu", "commit_api.cu", "encode.cu", "hash.cu", "store.cu", "misc.cu", "sumcheck.cu", "rounds_api.cu", "hash_noalloc.cu", "logup.cu", "aux_api.cu", "tables.cu", "rng.cu", "lookup.cu", "mask.cu", "witness.cu", "act.cu"]
+SOURCES = ["api.cu", "commit_api.cu", "encode.cu", "hash.cu", "store.cu", "misc.cu", "sumcheck.cu", "rounds_api.cu", "hash_noalloc.cu", "logup.cu", "aux_api.cu", "tables.cu", "rng.cu", "lookup.cu", "mask.cu", "witness.cu", "act.cu", "verify.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

@@ -828,6 +828,121 @@ def open_zk(cmz: CommittedZk, claims: Sequence[ZClaim], tr: Transcript, fold=Non
     return OpeningZk(vecs[:-1], vecs[-1], out)
 
 
+def zkey_weights(key, log_cols: int) -> np.ndarray:
+    """pcs.rs:908-920: the column weights of a group key (tail bytes, c0, len), (n, 2)."""
+    tail, c0, ln = key
+    out = np.zeros((1 << log_cols, 2), dtype=np.uint64)
+    if len(tail) == 0:
+        out[c0:c0 + ln, 0] = 1
+    else:
+        out[c0:c0 + ln] = eq_table_msb(np.frombuffer(tail, dtype=np.uint64).reshape(-1, 2))
+    return out
+
+
+def check_columns_host(cols, idx, salts, paths, root, tag, rhos, encoded_vecs) -> List[int]:
+    """The body of the verifier's map over the opened columns (pcs.rs:1303-1331): per column 0 when every check holds,
+    1 when the Merkle path fails, 2 + g when the column disagrees with clear vector g.  encoded_vecs: (G+1, 2, nn)."""
+    out = []
+    for c, j in enumerate(idx):
+        col = _u64(cols[c])
+        leaf = salt_leaves(hash_columns(col, col.size, 1, tag.column), np.frombuffer(salts[c], np.uint8).reshape(1, 32), tag.leaf)
+        if not merkle_verify_path(root, int(j), bytes(leaf[0]), paths[c], tag.node):
+            out.append(1)
+            continue
+        acc = fold_rows(col, col.size, 1, 1, 1, rhos)  # a26_combine, one column
+        v = 0
+        for g in range(rhos.shape[0]):
+            if (int(acc[g, 0, 0]), int(acc[g, 0, 1])) != (int(encoded_vecs[g][0][int(j)]), int(encoded_vecs[g][1][int(j)])):
+                v = 2 + g
+                break
+        out.append(v)
+    return out
+
+
+def verify_zk(params: PcsParams, q: int, root: bytes, rows: int, claims: Sequence[ZClaim], opening: OpeningZk, tr: Transcript, tag: HashTag,
+              max_log: int, coset: int = 7, check_columns=None) -> Optional[str]:
+    """pcs.rs:1235-1336 (`verify_zk_tagged`): None when the opening is accepted, else the reference's refusal text.
+    `check_columns(cols, idx, salts, paths, root, tag, rhos, vecs, encoded_vecs) -> verdicts` defaults to the host body;
+    a device verifier under test is plugged in through it (vecs: the clear vectors (G+1, n+q, 2))."""
+    n, nn = params.cols, params.enc_cols
+    if q < params.num_col_checks:
+        return "pcs zk: fewer pads than column checks"
+    depth = nn.bit_length() - 1
+    for at, (_, _, _, path) in enumerate(opening.columns):
+        if len(path) != depth:
+            return f"pcs zk: opened column {at} carries a Merkle path of {len(path)} entries; this commitment's tree is {depth} deep"
+    groups = group_zclaims(claims, rows, params.log_cols)
+    if len(opening.group_vecs) != len(groups):
+        return f"pcs zk: {len(opening.group_vecs)} group vectors for {len(groups)} groups"
+    # zk_rhos (pcs.rs:952-973) with the combined claims
+    rhos = np.zeros((len(groups) + 1, rows, 2), dtype=np.uint64)
+    wants = []
+    for g, (_, members) in enumerate(groups):
+        lambdas = tr.challenge_fp2_vec(len(members))
+        rho, want = [(0, 0)] * rows, (0, 0)
+        for (rw, val), lam in zip(members, lambdas):
+            lam = (int(lam[0]), int(lam[1]))
+            for i in range(rows):
+                if not fp2_is_zero(rw[i]):
+                    rho[i] = fp2_add(rho[i], fp2_mul(lam, rw[i]))
+            want = fp2_add(want, fp2_mul(lam, val))
+        rhos[g] = np.array(rho, dtype=np.uint64)
+        wants.append(want)
+    rhos[-1] = tr.challenge_fp2_vec(rows)
+    for g, (key, _) in enumerate(groups):
+        v = _u64(opening.group_vecs[g]).reshape(-1, 2)
+        if v.shape[0] != n + q:
+            return f"pcs zk: group vector {g} has length {v.shape[0]}"
+        cw = zkey_weights(key, params.log_cols)
+        got = (0, 0)
+        for x, y in zip(v[:n], cw):
+            if int(y[0]) | int(y[1]):
+                got = fp2_add(got, fp2_mul((int(x[0]), int(x[1])), (int(y[0]), int(y[1]))))
+        if got != wants[g]:
+            return f"pcs zk: group {g}: <v, c> != combined claim"
+    for v in opening.group_vecs:
+        tr.absorb_fp2(b"pcs-vec", v)
+    if _u64(opening.prox_vec).reshape(-1, 2).shape[0] != n + q:
+        return "pcs zk: prox vector length"
+    tr.absorb_fp2(b"pcs-prox", opening.prox_vec)
+    idx = tr.challenge_indices(params.num_col_checks, nn)
+    if len(opening.columns) != len(idx):
+        return "pcs zk: wrong number of columns"
+    pows = coset_powers(coset, nn)
+    vecs = np.concatenate([_u64(opening.group_vecs).reshape(-1, n + q, 2), _u64(opening.prox_vec).reshape(1, n + q, 2)], axis=0)
+    encoded_vecs = [(encode_row_zk(v[:n, 0], v[n:, 0], pows, max_log), encode_row_zk(v[:n, 1], v[n:, 1], pows, max_log)) for v in vecs]
+    # the map over the columns reports the first failing column, whatever its failure (pcs.rs:1303-1335)
+    early = []
+    for (j, col, _, _), want_j in zip(opening.columns, idx):
+        if int(j) != int(want_j):
+            early.append(f"pcs zk: column index {j} != sampled {int(want_j)}")
+        elif len(col) != rows:
+            early.append("pcs zk: column length")
+        else:
+            early.append(None)
+    live = [c for c, e in enumerate(early) if e is None]
+    cols = [opening.columns[c][1] for c in live]
+    salts = [opening.columns[c][2] for c in live]
+    paths = [opening.columns[c][3] for c in live]
+    lidx = np.array([int(idx[c]) for c in live], dtype=np.uint64)
+    if not live:
+        verdicts = []
+    elif check_columns is None:
+        verdicts = check_columns_host(cols, lidx, salts, paths, root, tag, rhos, encoded_vecs)
+    else:
+        verdicts = check_columns(cols, lidx, salts, paths, root, tag, rhos, vecs, encoded_vecs)
+    by_col = dict(zip(live, verdicts))
+    for c, (j, _, _, _) in enumerate(opening.columns):
+        if early[c] is not None:
+            return early[c]
+        v = by_col[c]
+        if v == 1:
+            return f"pcs zk: Merkle path for column {j} fails"
+        if v >= 2:
+            return f"pcs zk: column {j} disagrees with clear vector {v - 2}"
+    return None
+
+
 # ----------------------------------------------------------------------------- the masking commitment M (hashline/src/zk.rs)
 # Parity of this part is UNPINNED: the reference tree holds no golden vector of an M commitment or opening (its L10 corpus is
 # present only as a checksum).  Every primitive below IS pinned (transforms by the encode conformance vectors, hashing and

@@ -284,6 +284,78 @@ def test_l5_whole_pcs_openings(oracle, l5):
     assert done == 3
 
 
+# --------------------------------------------------------------------------- L5: the verifier on the recorded openings
+def test_l5_verifier_accepts_the_recorded_openings_and_ends_in_the_recorded_state(oracle, l5):
+    """lean_l5_export.rs:383-386: `verify_zk_tagged` accepts what `open_zk` wrote and leaves the transcript where the prover's is."""
+    import l5_util
+    for case in l5_util.pcs_cases(oracle, l5):
+        tr = l5_util.start_transcript(oracle, case)
+        err = oracle.verify_zk(case["params"], case["q"], case["root"], case["rows"], case["claims"], case["opening"], tr, case["tag"], case["max_log"])
+        assert err is None, (case["name"], err)
+        assert tr.state == case["end_state"]
+
+
+def test_l5_verifier_refuses_tampered_openings_with_the_reference_messages(oracle, l5):
+    """pcs.rs:1258-1335: each refusal in the order the reference makes them (lean_l5_export.rs:419-423 tampers a salt)."""
+    import copy
+    import l5_util
+    o = oracle
+    case = l5_util.pcs_cases(o, l5)[0]
+    depth = (case["params"].enc_cols).bit_length() - 1
+
+    def run(op):
+        return o.verify_zk(case["params"], case["q"], case["root"], case["rows"], case["claims"], op, l5_util.start_transcript(o, case), case["tag"], case["max_log"])
+
+    def tampered(f):
+        op = copy.deepcopy(case["opening"])
+        op.columns = [list(c) for c in op.columns]
+        f(op)
+        op.columns = [tuple(c) for c in op.columns]
+        return op
+
+    j0, j1 = case["opening"].columns[0][0], case["opening"].columns[1][0]
+
+    def salt(op):
+        b = bytearray(op.columns[0][2]); b[0] ^= 1; op.columns[0][2] = bytes(b)
+    assert run(tampered(salt)) == f"pcs zk: Merkle path for column {j0} fails"
+
+    def short_path(op):
+        op.columns[2][3] = op.columns[2][3][:-1]
+    assert run(tampered(short_path)) == f"pcs zk: opened column 2 carries a Merkle path of {depth - 1} entries; this commitment's tree is {depth} deep"
+
+    def vec(op):
+        op.group_vecs[0][0][0] = (int(op.group_vecs[0][0][0]) + 1) % P
+    assert run(tampered(vec)) == "pcs zk: group 0: <v, c> != combined claim"
+
+    def pad(op):  # a pad entry is outside <v, c>: the transcript moves, so the sampled columns no longer match
+        op.prox_vec[-1][1] = (int(op.prox_vec[-1][1]) + 1) % P
+    assert run(tampered(pad)).startswith("pcs zk: column index ")
+
+    def col(op):  # the second column disagrees, the first column's failure would come first
+        op.columns[1][1] = op.columns[1][1].copy(); op.columns[1][1][0] = (int(op.columns[1][1][0]) + 1) % P
+    assert run(tampered(col)) == f"pcs zk: Merkle path for column {j1} fails"
+
+    def drop(op):
+        op.columns = op.columns[:-1]
+    assert run(tampered(drop)) == "pcs zk: wrong number of columns"
+
+
+def test_l5_single_column_verdicts(oracle, l5):
+    """lean_l5_export.rs:399-417: 84 columns, honest and tampered, with the crate's verdict (path length and column length first)."""
+    import l5_util
+    o = oracle
+    tags = {"rungg": o.HashTag.for_profile(l5_util.CASES["rungg"][0]), "m125": o.HashTag.for_profile(l5_util.CASES["m125"][0]), "legacy": o.HashTag.legacy()}
+    seen = [0, 0]
+    for name, depth, rows, root, j, col, salt, path, want in l5_util.column_records(l5):
+        ok = len(path) == depth and col.size == rows
+        if ok:
+            none = np.zeros((0, rows, 2), dtype=np.uint64)
+            ok = o.check_columns_host([col], [j], [salt], [path], root, tags[name], none, []) == [0]
+        assert int(ok) == want
+        seen[want] += 1
+    assert seen == [72, 12]
+
+
 # --------------------------------------------------------------------------- encode conformance vectors
 def splitmix_fp(seed, n):
     out, s = [], seed
