@@ -453,8 +453,41 @@ def device_extras(dev, backend, np_data, np_pads, np_pows, col_key, only: str = 
         torch.cuda.synchronize()
         out["commit_H_2606x2^14_to_root_ms"] = ea.elapsed_time(eb) / 3
         del dd, dp, dw, dsalt, dlev
+    if want("verify"):
+        # the verifier's data-parallel part for one opening of `A` (pcs.rs:1282-1331): 39 clear vectors encoded (78 rows), 280 opened
+        # columns hashed, walked to the root and combined with 39 row weights; host buffers in, verdicts out, wall time of the call
+        vin = verifier_inputs(dev, np_data, np_pads, np_pows, col_key, rhos)
+        for rep in range(4):
+            if rep == 1:
+                t0 = time.perf_counter()
+            v = dev.check_opening_columns(log_cols, ir, np_pows, log_cols + 1, *vin["args"])
+        out["verify_280_columns_39_vectors_wall_ms"] = (time.perf_counter() - t0) * 1e3 / 3
+        assert v is not None and (v == 0).all(), "the verifier refused an honest opening"
     ctx.timing_enable(False)
     return out
+
+
+def verifier_inputs(dev, np_data, np_pads, np_pows, col_key, rhos38) -> dict:
+    """An honest opening of the bench's `A` commitment as the verifier receives it: 39 clear vectors, 280 opened columns with salts and paths."""
+    w = WORK
+    log_cols, ir, q, rows = w["log_cols"], w["inv_rate"], w["q"], w["rows"]
+    nn = (1 << log_cols) * ir
+    salts = (splitmix_fp(0xB2000700, nn * 4).view(np.uint8)).reshape(nn, 32)
+    st, _, levels = dev.try_commit_zk_tree(log_cols, ir, np_data, np_pads, np_pows, log_cols + 1, col_key, salts, col_key, col_key, want_leaves=False)
+    rhos = np.concatenate([structured_rhos(rhos38), splitmix_fp(0xB2000701, rows * 2).reshape(1, rows, 2)])
+    vecs = st.fold_rows_with_pads(rhos)
+    idx = (splitmix_fp(78, 280) % np.uint64(nn)).astype(np.uint64)
+    cols = st.columns(idx)
+    st.free()
+    depth = log_cols + (ir.bit_length() - 1)
+    paths = np.empty((280, depth, 32), dtype=np.uint8)
+    for c, j in enumerate(idx):  # merkle.rs:92-100: the sibling at every level below the root
+        off, width, i = 0, nn, int(j)
+        for l in range(depth):
+            paths[c, l] = levels[off + (i ^ 1)]
+            off, width, i = off + width, width // 2, i >> 1
+    return {"args": (cols, idx, np.ascontiguousarray(salts[idx.astype(np.int64)]), paths, bytes(levels[-1]), col_key, col_key, col_key, rhos, vecs),
+            "levels": levels}
 
 
 def _m125_slots():
@@ -662,6 +695,21 @@ def cpu_extras(o, backend, np_data) -> dict:
                                                                                           mask=mask, mask_c=(3, 5), mask_vars=nv + 1, recover_one=True, claim=(0, 0)))
     out["notes"] = notes
     return out
+
+
+def cpu_verify(o, dev, np_data, np_pads, np_pows, col_key) -> float:
+    """The same verifier work on the host through the restatement: 78 row encodings, then hash, path and 39 combinations per column."""
+    w = WORK
+    n, nn = 1 << w["log_cols"], (1 << w["log_cols"]) * w["inv_rate"]
+    rhos38 = splitmix_fp(77, 38 * w["rows"] * 2).reshape(38, w["rows"], 2)
+    cols, idx, salts, paths, root, ck, lk, nk, rhos, vecs = verifier_inputs(dev, np_data, np_pads, np_pows, col_key, rhos38)["args"]
+    tag = o.HashTag(transcript=None, column=ck, leaf=lk, node=nk)
+    t0 = time.perf_counter()
+    enc = [(o.encode_row_zk(v[:n, 0], v[n:, 0], np_pows, w["log_cols"] + 1), o.encode_row_zk(v[:n, 1], v[n:, 1], np_pows, w["log_cols"] + 1)) for v in vecs]
+    verdicts = o.check_columns_host(list(cols), idx, [bytes(x) for x in salts], [[bytes(x) for x in p] for p in paths], root, tag, rhos, enc)
+    ms = (time.perf_counter() - t0) * 1e3
+    assert verdicts == [0] * len(idx)
+    return ms
 
 
 def extras_rooflines(extras: dict, peak_gbs: float) -> dict:
@@ -1071,6 +1119,9 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     d55_out = d55_leg(dev, backend, rank, world, col_key, leaf_key, node_key)
     extras = device_extras(dev, backend, np_data, np_pads, np_pows, col_key) if (world == 1 and rank == 0 and not args.no_extras) else None
     extras_cpu = cpu_extras(o, backend, np_data) if extras is not None else None
+    if extras_cpu is not None:
+        extras_cpu["verify_280_columns_39_vectors_wall_ms"] = cpu_verify(o, dev, np_data, np_pads, np_pows, col_key)
+        extras_cpu["notes"]["verify_280_columns_39_vectors_wall_ms"] = "the restated verifier's column part, one thread (the reference runs the columns on rayon)"
     ref_cuda_ms = reference_cuda_extras(dev, backend, d_data, d_pads, d_pows, col_key) if extras is not None else None
 
     if rank == 0:
@@ -1128,7 +1179,7 @@ def main() -> None:
     ap.add_argument("--profile", action="store_true", help="resident-input leg only (for a run under a profiler)")
     ap.add_argument("--profile-extras", action="store_true", help="opening, sumcheck and LogUp kernels only (for a run under a profiler)")
     ap.add_argument("--only", default="", help="with --profile-extras: comma-separated families to run (open, sumcheck, helpers, i8folds, rng, lookup, slots, "
-                                               "slot_program, mask, witness, long_rows, commit_h)")
+                                               "slot_program, mask, witness, long_rows, commit_h, verify)")
     args = ap.parse_args()
     rank, local_rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     if args.impl == "reference":
