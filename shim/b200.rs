@@ -42,6 +42,10 @@ extern "C" {
                                 pads: *const u64, q: usize, pows: *const u64, max_log: u32, key32: *const u8, salts32: *const u8,
                                 leaf_key32: *const u8, node_key32: *const u8, store: *mut *mut HlStore, leaves32: *mut u8,
                                 levels_out: *mut u8) -> c_int;
+    fn hl_b200_verify_columns(ctx: *mut HlCtx, cols: *const u64, rows: usize, ncols: usize, idx: *const u64, salts32: *const u8,
+                              paths32: *const u8, depth: u32, root32: *const u8, column_key32: *const u8, leaf_key32: *const u8,
+                              node_key32: *const u8, rhos: *const u64, k: usize, wants: *const u64, vec_store: *const HlStore,
+                              verdict: *mut i32, first_bad: *mut i64) -> c_int;
     fn hl_b200_store_fold(s: *mut HlStore, rhos: *const u64, k: usize, with_pads: c_int, out: *mut u64) -> c_int;
     fn hl_b200_store_columns(s: *mut HlStore, idx: *const u64, nidx: usize, out: *mut u64) -> c_int;
     fn hl_b200_store_free(s: *mut HlStore);
@@ -226,6 +230,65 @@ impl B200Backend {
         }
         Some((B200Commit { h, rows, n, q }, leaves))
     }
+}
+
+/// What the device found wrong with an opened column (pcs.rs:1313-1327).
+pub enum ColumnVerdict {
+    MerklePath(usize),
+    Disagrees { column: usize, vector: usize },
+}
+
+/// The map over the opened columns of `verify_zk_tagged` (pcs.rs:1282-1331) on the device.  `vecs`: the group vectors then the
+/// proximity vector, `n + q` entries each; `rhos`: their combined row weights in the same order; the caller has already checked
+/// path lengths, column lengths and `j == want_j`.  `Ok(None)`: every column passes; `Ok(Some(v))`: the first failing column;
+/// `Err`: the device declined and the host body runs.
+#[allow(clippy::too_many_arguments)]
+pub fn verify_columns(p: &PcsParams, q: usize, pows: &[Fp], ntt: &NttTables, root: &Digest, keys: [Option<&[u8; 32]>; 3], rhos: &[Vec<Fp2>],
+                      vecs: &[&Vec<Fp2>], columns: &[(usize, Vec<Fp>, [u8; 32], Vec<Digest>)]) -> Result<Option<ColumnVerdict>, String> {
+    let n = p.cols();
+    let rows = columns.first().map(|c| c.1.len()).unwrap_or(0);
+    if rows == 0 || vecs.len() != rhos.len() {
+        return Err("b200 verify: empty opening".into());
+    }
+    // 2 (G + 1) base rows: re and im of every clear vector apart (pcs.rs:1287-1296)
+    let mut data = Vec::with_capacity(2 * vecs.len() * n);
+    let mut pads = Vec::with_capacity(2 * vecs.len() * q);
+    for v in vecs {
+        for part in 0..2 {
+            data.extend(v[..n].iter().map(|x| if part == 0 { x.c0 } else { x.c1 }));
+            pads.extend(v[n..].iter().map(|x| if part == 0 { x.c0 } else { x.c1 }));
+        }
+    }
+    let (store, _) = B200Backend.zk(p, &data, &pads, pows, ntt, None).ok_or_else(|| "b200 verify: the vectors' encoding was declined".to_string())?;
+    let depth = columns[0].3.len();
+    let mut cols = Vec::with_capacity(columns.len() * rows);
+    let mut idx = Vec::with_capacity(columns.len());
+    let mut salts = Vec::with_capacity(columns.len() * 32);
+    let mut paths = Vec::with_capacity(columns.len() * depth * 32);
+    for (j, col, salt, path) in columns {
+        idx.push(*j as u64);
+        cols.extend_from_slice(col);
+        salts.extend_from_slice(salt);
+        for d in path {
+            paths.extend_from_slice(d);
+        }
+    }
+    let flat: Vec<Fp2> = rhos.iter().flat_map(|r| r.iter().copied()).collect();
+    let kp = |k: Option<&[u8; 32]>| k.map(|x| x.as_ptr()).unwrap_or(std::ptr::null());
+    let mut verdict = vec![0i32; columns.len()];
+    let mut first: i64 = -1;
+    status(unsafe {
+        hl_b200_verify_columns(ctx(), words(&cols), rows, columns.len(), idx.as_ptr(), salts.as_ptr(), paths.as_ptr(), depth as u32, root.as_ptr(),
+                               kp(keys[0]), kp(keys[1]), kp(keys[2]), flat.as_ptr() as *const u64, rhos.len(), std::ptr::null(), store.h,
+                               verdict.as_mut_ptr(), &mut first)
+    })?;
+    Ok(if first < 0 {
+        None
+    } else if verdict[first as usize] == 1 {
+        Some(ColumnVerdict::MerklePath(columns[first as usize].0))
+    } else {
+        Some(ColumnVerdict::Disagrees { column: columns[first as usize].0, vector: (verdict[first as usize] - 2) as usize })
+    })
 }
 
 impl Backend for B200Backend {

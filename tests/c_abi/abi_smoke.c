@@ -26,6 +26,8 @@ typedef int (*columns_fn)(hl_store*, const uint64_t*, size_t, uint64_t*);
 typedef int (*rounds_new_ir_fn)(hl_ctx*, size_t, uint32_t, uint32_t, const uint64_t*, const uint32_t*, size_t, uint32_t, uint32_t, const uint64_t*,
                                 size_t, hl_rounds**);
 typedef int (*static_hash_fn)(const uint64_t*, size_t, size_t, const uint8_t*, uint8_t*, void*);
+typedef int (*verify_fn)(hl_ctx*, const uint64_t*, size_t, size_t, const uint64_t*, const uint8_t*, const uint8_t*, uint32_t, const uint8_t*, const uint8_t*,
+                         const uint8_t*, const uint8_t*, const uint64_t*, size_t, const uint64_t*, const hl_store*, int32_t*, int64_t*);
 
 static uint64_t addmod(uint64_t a, uint64_t b) { /* a, b < p */
     uint64_t s = a + b;
@@ -50,7 +52,9 @@ int main(int argc, char** argv) {
     columns_fn f4 = hl_b200_store_columns;
     rounds_new_ir_fn f5 = hl_b200_rounds_new_ir;
     static_hash_fn f6 = hl_b200_hash_columns_static;
-    if (!f1 || !f2 || !f3 || !f4 || !f5 || !f6) return 1;
+    verify_fn f7 = hl_b200_verify_columns;
+    if (!f1 || !f2 || !f3 || !f4 || !f5 || !f6 || !f7) return 1;
+    if (hl_b200_verify_columns(NULL, NULL, 0, 0, NULL, NULL, NULL, 0, NULL, NULL, NULL, NULL, NULL, 0, NULL, NULL, NULL, NULL) != HL_B200_ERR_ARG) return 5;
     /* refusals that need no device */
     if (hl_b200_store_fold(NULL, NULL, 0, 0, NULL) != HL_B200_ERR_ARG) return 2;
     if (hl_b200_hash_columns_static(NULL, 1, 1, NULL, NULL, NULL) != HL_B200_ERR_ARG) return 3;

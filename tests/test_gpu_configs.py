@@ -1,4 +1,4 @@
-"""Configs 2 and 3 of BASELINE.json on the device against the CPU oracle (bit-exact).
+"""The matmul-claim and LogUp benchmark configurations (called config 2 and config 3 below) on the device against the CPU oracle (bit-exact).
 
 Config 2: masked sumcheck of one integer matmul C = A B (A int8 128 x 4096, B int8 4096 x 4096): the two
 weight folds, the 12-round product sumcheck under a CFS mask, one extension round, transcript end state.
