@@ -57,11 +57,11 @@ void free_rounds(hl_rounds* r) {
 }
 
 // the reduce + Fiat-Shamir step of round r->next over `nb` partial rows
-int launch_step(hl_rounds* r, u32 nb, int fs, int use_claim, int recover, const u64* d_mask, const u64* d_hs, int mask_vars) {
+int launch_step(hl_rounds* r, u32 nb, int fs, int use_claim, int recover, const u64* d_mask, const u64* d_mtab, int mask_vars) {
     hl_ctx* c = r->ctx;
     hlk::ScStep a;
     a.partials = r->d_partials; a.nblocks = nb; a.degree = (int)r->degree; a.round = (int)r->next;
-    a.use_claim = use_claim; a.recover = recover; a.fs = fs; a.mask = d_mask; a.mask_half_suffix = d_hs; a.mask_vars = mask_vars;
+    a.use_claim = use_claim; a.recover = recover; a.fs = fs; a.mask = d_mask; a.mask_tab = d_mtab; a.mask_vars = mask_vars;
     a.inv_den = r->d_inv_den; a.state = r->d_state; a.out = r->d_out;
     a.eval_degree = (int)r->eval_degree; a.extrap = r->d_extrap;
     cudaError_t e = hlk::sc_step(a, c->stream);
@@ -71,7 +71,7 @@ int launch_step(hl_rounds* r, u32 nb, int fs, int use_claim, int recover, const 
 }
 
 // launches round j's kernels; the caller holds the context lock
-int launch_round(hl_rounds* r, int eval_one, int fs, int use_claim, int recover, const u64* d_mask, const u64* d_hs, int mask_vars) {
+int launch_round(hl_rounds* r, int eval_one, int fs, int use_claim, int recover, const u64* d_mask, const u64* d_mtab, int mask_vars) {
     hl_ctx* c = r->ctx;
     const u32 half = (u32)(r->len / 2);
     const bool is_ir = r->poly == hlk::POLY_IR;
@@ -95,7 +95,7 @@ int launch_round(hl_rounds* r, int eval_one, int fs, int use_claim, int recover,
     }
     c->stats.kernel_launches++;
     if (e != cudaSuccess) return fail(c, HL_B200_ERR_DEVICE, "round launch", e);
-    return launch_step(r, nb, fs, use_claim, recover, d_mask, d_hs, mask_vars);
+    return launch_step(r, nb, fs, use_claim, recover, d_mask, d_mtab, mask_vars);
 }
 
 int launch_fold(hl_rounds* r) {
@@ -352,28 +352,37 @@ int hl_b200_rounds_batched(hl_rounds* r, uint32_t nd, hl_fs_state* fs, const uin
     st.counter = fs->counter;
     st.keyed = fs->keyed;
     st.claim = f2(fs->claim[0], fs->claim[1]);
-    st.prod_prev = f2(1, 0);
-    u64 *d_mask = nullptr, *d_hs = nullptr;
+    u64 *d_mask = nullptr, *d_mtab = nullptr;
     const size_t mlen = mask_coeffs ? (size_t)mask_vars * r->degree + 2 : 0;
-    std::vector<u64> hs;
+    const size_t tab_words = (size_t)mask_vars * (r->degree + 1) * 2;
+    std::vector<u64> mtab;
     int rc = HL_B200_OK;
     if (mask_coeffs) {
         st.mask_c = f2(mask_c[0], mask_c[1]);
-        // per round j: sum_{i>j} u_i(1) / 2 (sumcheck.rs:266-268)
         const fp2* co = reinterpret_cast<const fp2*>(mask_coeffs);
+        st.ap = co[1];  // a' times the empty product
+        // per round j and point x: 2^(N-1-j) (a0 + sum_{i>j} u_i(1)/2 + u_j(x)) (sumcheck.rs:260-295): the part of g_j(x) no challenge enters
         const u64 half = gl_inv(2);
-        hs.assign((size_t)mask_vars * 2, 0);
+        mtab.assign(tab_words, 0);
         fp2 run = f2(0, 0);
         for (int i = (int)mask_vars - 1; i >= 0; i--) {
-            hs[2 * i] = run.c0; hs[2 * i + 1] = run.c1;
+            const fp2* ai = co + 2 + (size_t)i * r->degree;
+            const u64 scale = 1ull << (mask_vars - 1 - (u32)i);  // mask_vars <= 63: the power of two is its own canonical word
+            for (u32 x = 0; x <= r->degree; x++) {
+                fp2 u = f2(0, 0);
+                u64 xp = 1;
+                for (u32 e = 1; e <= r->degree; e++) { xp = gl_mul(xp, (u64)x); u = f2_add(u, f2_mul_base(ai[e - 1], xp)); }
+                const fp2 v = f2_mul_base(f2_add(f2_add(co[0], run), u), scale);
+                mtab[((size_t)i * (r->degree + 1) + x) * 2] = v.c0; mtab[((size_t)i * (r->degree + 1) + x) * 2 + 1] = v.c1;
+            }
             fp2 u1 = f2(0, 0);
-            for (u32 e = 0; e < r->degree; e++) u1 = f2_add(u1, co[2 + (size_t)i * r->degree + e]);
+            for (u32 e = 0; e < r->degree; e++) u1 = f2_add(u1, ai[e]);
             run = f2_add(run, f2_mul_base(u1, half));
         }
         rc = dev_alloc(c, (void**)&d_mask, mlen * 16);
-        if (!rc) rc = dev_alloc(c, (void**)&d_hs, (size_t)mask_vars * 16);
+        if (!rc) rc = dev_alloc(c, (void**)&d_mtab, tab_words * 8);
         if (!rc) rc = h2d(c, d_mask, mask_coeffs, mlen * 16);
-        if (!rc) rc = h2d(c, d_hs, hs.data(), (size_t)mask_vars * 16);
+        if (!rc) rc = h2d(c, d_mtab, mtab.data(), tab_words * 8);
     }
     if (!rc) rc = h2d(c, r->d_state, &st, sizeof st);
     const u32 first = r->next;
@@ -383,7 +392,7 @@ int hl_b200_rounds_batched(hl_rounds* r, uint32_t nd, hl_fs_state* fs, const uin
         u32 i = 0;
         if (r->poly == hlk::POLY_IR) {
             for (; i < nd && !rc && r->len > r->tail_len; i++) {
-                rc = launch_round(r, have_claim ? 0 : 1, 1, have_claim ? 1 : 0, fs->recover_one ? 1 : 0, d_mask, d_hs, (int)mask_vars);
+                rc = launch_round(r, have_claim ? 0 : 1, 1, have_claim ? 1 : 0, fs->recover_one ? 1 : 0, d_mask, d_mtab, (int)mask_vars);
                 if (!rc) rc = launch_fold(r);
                 have_claim = fs->recover_one != 0;
             }
@@ -404,14 +413,14 @@ int hl_b200_rounds_batched(hl_rounds* r, uint32_t nd, hl_fs_state* fs, const uin
                     pending = false;
                 }
                 if (!pending) {
-                    rc = launch_round(r, eval_one, 1, have_claim ? 1 : 0, fs->recover_one ? 1 : 0, d_mask, d_hs, (int)mask_vars);
+                    rc = launch_round(r, eval_one, 1, have_claim ? 1 : 0, fs->recover_one ? 1 : 0, d_mask, d_mtab, (int)mask_vars);
                 } else {
                     const u32 nb = hlk::sc_round_blocks((u32)(r->len / 2), c->sm_count);
                     cudaError_t e = hlk::sc_fold_round(r->poly, (int)r->k, r->d_tables, r->stride, (u32)r->len, r->d_coefs, r->d_state, eval_one, r->d_partials,
                                                        nb, c->stream);
                     c->stats.kernel_launches++;
                     if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "fold + round launch", e);
-                    if (!rc) rc = launch_step(r, nb, 1, have_claim ? 1 : 0, fs->recover_one ? 1 : 0, d_mask, d_hs, (int)mask_vars);
+                    if (!rc) rc = launch_step(r, nb, 1, have_claim ? 1 : 0, fs->recover_one ? 1 : 0, d_mask, d_mtab, (int)mask_vars);
                 }
                 r->len /= 2;
                 r->next++;
@@ -427,7 +436,7 @@ int hl_b200_rounds_batched(hl_rounds* r, uint32_t nd, hl_fs_state* fs, const uin
         if (!rc && i < nd) {  // the short rounds: one CTA, no launches in between
             hlk::ScStep a;
             a.partials = r->d_partials; a.nblocks = 1; a.degree = (int)r->degree; a.round = (int)r->next;
-            a.use_claim = 0; a.recover = fs->recover_one ? 1 : 0; a.fs = 1; a.mask = d_mask; a.mask_half_suffix = d_hs; a.mask_vars = (int)mask_vars;
+            a.use_claim = 0; a.recover = fs->recover_one ? 1 : 0; a.fs = 1; a.mask = d_mask; a.mask_tab = d_mtab; a.mask_vars = (int)mask_vars;
             a.inv_den = r->d_inv_den; a.state = r->d_state; a.out = r->d_out;
             a.eval_degree = (int)r->eval_degree; a.extrap = r->d_extrap;
             const u32 left = nd - i;
@@ -445,7 +454,7 @@ int hl_b200_rounds_batched(hl_rounds* r, uint32_t nd, hl_fs_state* fs, const uin
     if (!rc) rc = d2h(c, &st, r->d_state, sizeof st);
     if (!rc) rc = sync(c, "rounds_batched");
     if (d_mask) dev_free(c, d_mask, mlen * 16);
-    if (d_hs) dev_free(c, d_hs, (size_t)mask_vars * 16);
+    if (d_mtab) dev_free(c, d_mtab, tab_words * 8);
     if (rc) return rc;
     memcpy(fs->state, st.state, 32);
     fs->counter = st.counter;

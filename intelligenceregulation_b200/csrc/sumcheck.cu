@@ -118,7 +118,6 @@ __device__ __forceinline__ u64 reduce_le16(const uint32_t* w) {  // 128-bit litt
     return gl_reduce128(((u64)w[1] << 32) | w[0], ((u64)w[3] << 32) | w[2]);
 }
 
-__device__ __forceinline__ fp2 shfl_down_f2(fp2 v, int d) { return f2(shfl_down64(v.c0, d), shfl_down64(v.c1, d)); }
 
 // One warp.  The field work is spread over the lanes (one evaluation point per lane); only the two transcript
 // hashes run on lane 0.
@@ -129,8 +128,45 @@ struct StepSmem {
     __align__(16) uint32_t msg[64];  // 256 bytes
 };
 
-// One warp; sm.sums already holds the round's D+1 sums.
-__device__ void step_body(const ScStep& a, StepSmem& sm, int lane) {
+// v 2^k mod p, 0 <= k <= 62
+__device__ __forceinline__ u64 gl_mul_pow2(u64 v, int k) { return gl_reduce128(v << k, k ? v >> (64 - k) : 0ull); }
+
+__device__ __forceinline__ fp2 shfl_down8_f2(fp2 v, int d) {  // within groups of eight lanes
+    u32 a0 = __shfl_down_sync(0xffffffffu, (u32)v.c0, d, 8), a1 = __shfl_down_sync(0xffffffffu, (u32)(v.c0 >> 32), d, 8);
+    u32 b0 = __shfl_down_sync(0xffffffffu, (u32)v.c1, d, 8), b1 = __shfl_down_sync(0xffffffffu, (u32)(v.c1 >> 32), d, 8);
+    return f2(((u64)a1 << 32) | a0, ((u64)b1 << 32) | b0);
+}
+
+// One warp; sm.sums already holds the round's D+1 sums.  The step is a serial chain (sums -> masked message -> two hashes ->
+// challenge -> next claim and the mask's running terms), so it is written for depth, not for work:
+//   before the hashes  one multiplication level: the mask's round polynomial is a host-made table entry plus 2^k acc_prev plus
+//                      x a' prod r_i, and s_i / den_i is taken here, off the path that follows the challenge;
+//   after the hashes   every lane runs the SAME product tree over eight (or four) factors and one multiplier: lanes 0..7 a
+//                      Lagrange numerator prod_{j != i} (r - j) times s_i / den_i, lanes 8..15 a power r^e times the mask
+//                      coefficient a_{j,e}, lane 16 the product r (a' prod r_i); sums over groups of eight lanes give the next
+//                      claim (rounds.rs:145-147, mle.rs:338-351) and u_j(r_j).
+// What one step reads, resolved to this round's rows and handed over by value: the step's operands then sit in registers,
+// where a reference to the launch arguments would make every field a load from the local copy of the argument block.
+struct StepArgs {
+    int degree, round, use_claim, recover, fs, mask_vars, eval_degree;
+    const fp2* aj;      // this round's `degree` mask coefficients a_{j,e}; NULL: no mask
+    const fp2* tab;     // this round's degree + 1 entries of ScStep::mask_tab
+    const u64* inv_den;
+    const u64* extrap;  // or NULL
+    hlk::ScState* state;
+    u64* out;
+};
+__device__ __forceinline__ StepArgs step_args(const ScStep& a, int round, int use_claim, int fs, const u64* mask, const u64* mask_tab, const u64* inv_den,
+                                              const u64* extrap, hlk::ScState* state) {
+    StepArgs x;
+    x.degree = a.degree; x.round = round; x.use_claim = use_claim; x.recover = a.recover; x.fs = fs; x.mask_vars = a.mask_vars; x.eval_degree = a.eval_degree;
+    x.aj = mask ? reinterpret_cast<const fp2*>(mask) + 2 + (size_t)round * a.degree : nullptr;
+    x.tab = mask ? reinterpret_cast<const fp2*>(mask_tab) + (size_t)round * (a.degree + 1) : nullptr;
+    x.inv_den = inv_den; x.extrap = extrap; x.state = state; x.out = a.out;
+    return x;
+}
+
+__device__ __forceinline__ void step_body(const StepArgs a, StepSmem& sm, int lane) {
     u64* sums = sm.sums;
     u64* mskd = sm.mskd;
     u64* chal = sm.chal;
@@ -154,30 +190,30 @@ __device__ void step_body(const ScStep& a, StepSmem& sm, int lane) {
     u64* orow = a.out + (size_t)j * (2 * (size_t)np + 1) * 2;
     if (lane < np) st2(orow + 2 * lane, s[lane]);
     if (!a.fs) return;  // plain round(): the host drives the transcript
-    const fp2* mk = reinterpret_cast<const fp2*>(a.mask);
+    const bool masked = a.aj != nullptr;
+    const fp2* aj = a.aj;
     // masked message s + c g_j, one point x per lane (sumcheck.rs:260-295):
     //   g_j(x) = 2^(N-1-j) (a0 + sum_{i<j} u_i(r_i) + sum_{i>j} u_i(1)/2 + u_j(x)) + a' (prod_{i<j} r_i) x
+    fp2 sd = f2(0, 0);
     if (lane < np) {
         fp2 m = s[lane];
-        if (mk) {
-            const fp2* aj = a.mask_row ? reinterpret_cast<const fp2*>(a.mask_row) : mk + 2 + (size_t)j * a.degree;
-            const fp2 base = f2_add(f2_add(mk[0], st->acc_prev), a.hs_row ? reinterpret_cast<const fp2*>(a.hs_row)[0] : reinterpret_cast<const fp2*>(a.mask_half_suffix)[j]);
-            const u64 scale = 1ull << (a.mask_vars - 1 - j);  // mask_vars <= 63: the power of two is its own canonical word
-            const u64 x = (u64)lane;
-            fp2 u = f2(0, 0);
-            u64 xp = 1;
-            for (int e = 1; e <= a.degree; e++) { xp = gl_mul(xp, x); u = f2_add(u, f2_mul_base(aj[e - 1], xp)); }
-            const fp2 g = f2_add(f2_mul_base(f2_add(base, u), scale), f2_mul_base(f2_mul(mk[1], st->prod_prev), x));
+        if (masked) {
+            const fp2* tab = a.tab;
+            const int sh = a.mask_vars - 1 - j;  // mask_vars <= 63
+            fp2 g = f2_add(tab[lane], f2(gl_mul_pow2(st->acc_prev.c0, sh), gl_mul_pow2(st->acc_prev.c1, sh)));
+            g = f2_add(g, f2_mul_base(st->ap, (u64)lane));
             m = f2_add(m, f2_mul(st->mask_c, g));
         }
         st2(mskd + 2 * lane, m);
         st2(orow + 2 * (np + lane), m);
+        if (a.recover) sd = f2_mul_base(s[lane], a.inv_den[lane]);
     }
     __syncwarp();
     if (lane == 0) {
         // absorb: state' = H(state || LE64(8) || "sc-round" || LE64(16 np) || bytes) (transcript.rs:67-74)
         const uint32_t* key = st->keyed ? st->key : nullptr;
-        for (int i = 0; i < 64; i++) msg[i] = 0;
+        const int nw = 14 + 2 * W;  // message words
+        for (int i = nw; i < ((nw + 15) & ~15); i++) msg[i] = 0;
         for (int i = 0; i < 8; i++) msg[i] = st->state[i];
         msg[8] = 8; msg[9] = 0;
         msg[10] = 0x722d6373u; msg[11] = 0x646e756fu;  // "sc-r" "ound", little-endian words
@@ -186,7 +222,7 @@ __device__ void step_body(const ScStep& a, StepSmem& sm, int lane) {
         uint32_t h[8];
         hash_small(key, msg, 56 + 16 * np, h);
         // squeeze: out = H(state || "squeeze" || LE64(counter)); counter++; state = out (transcript.rs:120-130)
-        for (int i = 0; i < 16; i++) msg[i] = 0;
+        for (int i = 12; i < 16; i++) msg[i] = 0;
         for (int i = 0; i < 8; i++) msg[i] = h[i];
         const u64 ctr = st->counter;
         msg[8] = 0x65757173u;                                   // "sque"
@@ -202,27 +238,42 @@ __device__ void step_body(const ScStep& a, StepSmem& sm, int lane) {
         st->r = r;
     }
     __syncwarp();
+    if (!a.recover && !masked) return;
     const fp2 r = f2(chal[0], chal[1]);
-    // next claim = the UNMASKED round polynomial at r, one Lagrange term per lane (rounds.rs:145-147; mle.rs:338-351)
-    if (a.recover) {
-        fp2 term = f2(0, 0);
-        if (lane < np) {
-            fp2 num = f2_one();
-            for (int jj = 0; jj < np; jj++)
-                if (jj != lane) num = f2_mul(num, f2(gl_sub(r.c0, (u64)jj), r.c1));
-            term = f2_mul_base(f2_mul(s[lane], num), a.inv_den[lane]);
-        }
+    const int grp = lane >> 3, li = lane & 7;
+    fp2 f[8], mult = f2(0, 0);
 #pragma unroll
-        for (int off = 4; off >= 1; off >>= 1) term = f2_add(term, shfl_down_f2(term, off));  // np <= 8
-        if (lane == 0) st->claim = term;
+    for (int t = 0; t < 8; t++) f[t] = f2_one();
+    if (grp == 0) {
+        if (a.recover && li < np) {
+#pragma unroll
+            for (int t = 0; t < 7; t++) {  // the points other than li, in order
+                const int jj = t < li ? t : t + 1;
+                if (jj < np) f[t] = f2(gl_sub(r.c0, (u64)jj), r.c1);
+            }
+            mult = sd;
+        }
+    } else if (grp == 1) {
+        if (masked && li < a.degree) {  // r^(li + 1) a_{j, li + 1}
+#pragma unroll
+            for (int t = 0; t < 7; t++)
+                if (t <= li) f[t] = r;
+            mult = aj[li];
+        }
+    } else if (lane == 16 && masked) {
+        f[0] = r;
+        f[1] = st->ap;
+        mult = f2_one();
     }
-    if (mk && lane == 8) {  // the mask's running terms: sum_i u_i(r_i) and prod r_i
-        const fp2* aj = a.mask_row ? reinterpret_cast<const fp2*>(a.mask_row) : mk + 2 + (size_t)j * a.degree;
-        fp2 u = f2(0, 0), xp = f2_one();
-        for (int e = 1; e <= a.degree; e++) { xp = f2_mul(xp, r); u = f2_add(u, f2_mul(aj[e - 1], xp)); }
-        st->acc_prev = f2_add(st->acc_prev, u);
-        st->prod_prev = f2_mul(st->prod_prev, r);
-    }
+    fp2 prod = f2_mul(f2_mul(f[0], f[1]), f2_mul(f[2], f[3]));
+    if (a.degree > 4) prod = f2_mul(prod, f2_mul(f2_mul(f[4], f[5]), f2_mul(f[6], f[7])));
+    fp2 term = f2_mul(prod, mult);
+    const fp2 own = term;
+#pragma unroll
+    for (int off = 4; off >= 1; off >>= 1) term = f2_add(term, shfl_down8_f2(term, off));
+    if (lane == 0 && a.recover) st->claim = term;
+    if (lane == 8 && masked) st->acc_prev = f2_add(st->acc_prev, term);
+    if (lane == 16 && masked) st->ap = own;
 }
 
 // The CTA partials of a round are summed by all STEP_T threads (independent loads, shared-memory tree);
@@ -234,7 +285,7 @@ __global__ void __launch_bounds__(STEP_T) k_sc_step(ScStep a) {
     // everything the serial step reads is fetched by the whole CTA while the partials are summed: the step itself then waits on
     // no global load (each one is most of a microsecond for a single warp)
     __shared__ hlk::ScState st_s;
-    __shared__ u64 mk_s[4], row_s[2 * hlk::SC_MAX_POINTS], hs_s[2], invden_s[hlk::SC_MAX_POINTS], extrap_s[hlk::SC_MAX_POINTS * hlk::SC_MAX_POINTS];
+    __shared__ u64 row_s[2 * hlk::SC_MAX_POINTS], tab_s[2 * hlk::SC_MAX_POINTS], invden_s[hlk::SC_MAX_POINTS], extrap_s[hlk::SC_MAX_POINTS * hlk::SC_MAX_POINTS];
     hlk::ScState* const st_global = a.state;
     {
         const u32* src = reinterpret_cast<const u32*>(a.state);
@@ -242,9 +293,8 @@ __global__ void __launch_bounds__(STEP_T) k_sc_step(ScStep a) {
         if (threadIdx.x < sizeof(hlk::ScState) / 4) dst[threadIdx.x] = src[threadIdx.x];
         const int t = (int)threadIdx.x - 64;
         if (a.mask && a.fs) {
-            if (t >= 0 && t < 4) mk_s[t] = a.mask[t];
-            if (t >= 8 && t < 8 + 2 * a.degree) row_s[t - 8] = a.mask[4 + 2 * (size_t)a.round * a.degree + (t - 8)];
-            if (t >= 32 && t < 34) hs_s[t - 32] = a.mask_half_suffix[2 * (size_t)a.round + (t - 32)];
+            if (t >= 0 && t < 2 * a.degree) row_s[t] = a.mask[4 + 2 * (size_t)a.round * a.degree + t];
+            if (t >= 16 && t < 16 + 2 * (a.degree + 1)) tab_s[t - 16] = a.mask_tab[2 * (size_t)a.round * (a.degree + 1) + (t - 16)];
         }
         if (t >= 40 && t < 40 + a.degree + 1) invden_s[t - 40] = a.inv_den[t - 40];
         const int ne = a.extrap ? (a.degree - a.eval_degree) * (a.eval_degree + 1) : 0;
@@ -266,11 +316,9 @@ __global__ void __launch_bounds__(STEP_T) k_sc_step(ScStep a) {
     if (threadIdx.x < W) sm.sums[threadIdx.x] = red[threadIdx.x];
     __syncthreads();
     if (threadIdx.x < 32) {
-        if (a.mask && a.fs) { a.mask = mk_s; a.mask_row = row_s; a.hs_row = hs_s; }
-        a.inv_den = invden_s;
-        if (a.extrap) a.extrap = extrap_s;
-        a.state = &st_s;
-        step_body(a, sm, threadIdx.x);
+        StepArgs x = step_args(a, a.round, a.use_claim, a.fs, nullptr, nullptr, invden_s, a.extrap ? extrap_s : nullptr, &st_s);
+        if (a.mask && a.fs) { x.aj = reinterpret_cast<const fp2*>(row_s); x.tab = reinterpret_cast<const fp2*>(tab_s); }
+        step_body(x, sm, threadIdx.x);
         __syncwarp();
         const u32* src = reinterpret_cast<const u32*>(&st_s);
         u32* dst = reinterpret_cast<u32*>(st_global);
@@ -290,7 +338,7 @@ __global__ void __launch_bounds__(TAIL_T) k_sc_tail(u64* __restrict__ tables, si
     // the serial step then waits on no global load
     __shared__ hlk::ScState st_s;
     __shared__ u64 mask_s[2 * (63 * D + 2)];
-    __shared__ u64 hs_s[2 * 63];
+    __shared__ u64 tab_s[2 * 63 * (D + 1)];
     __shared__ u64 invden_s[hlk::SC_MAX_POINTS];
     const fp2* cf = reinterpret_cast<const fp2*>(coefs);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -300,64 +348,62 @@ __global__ void __launch_bounds__(TAIL_T) k_sc_tail(u64* __restrict__ tables, si
         for (u32 i = threadIdx.x; i < sizeof(hlk::ScState) / 4; i += TAIL_T) dst[i] = src[i];
         if (a.mask) {
             for (u32 i = threadIdx.x; i < 2u * (a.mask_vars * D + 2); i += TAIL_T) mask_s[i] = a.mask[i];
-            for (u32 i = threadIdx.x; i < 2u * a.mask_vars; i += TAIL_T) hs_s[i] = a.mask_half_suffix[i];
+            for (u32 i = threadIdx.x; i < 2u * a.mask_vars * (D + 1); i += TAIL_T) tab_s[i] = a.mask_tab[i];
         }
         if (threadIdx.x <= D) invden_s[threadIdx.x] = a.inv_den[threadIdx.x];
     }
     hlk::ScState* const st_global = a.state;
-    if (a.mask) { a.mask = mask_s; a.mask_half_suffix = hs_s; }
-    a.inv_den = invden_s;
-    a.state = &st_s;
+    const u64* const mask_p = a.mask ? mask_s : nullptr;
     __syncthreads();
     for (int rd = 0; rd < nrounds; rd++) {
         const u32 half = len >> 1;
         const bool have_claim = a.recover && (rd > 0 || first_has_claim);
-        fp2 acc[D + 1];
+        // warps beyond the round's pairs hold nothing: they skip the sums and their reduction (32 warps reducing zeros cost more
+        // than the round's arithmetic once a round is down to a few pairs)
+        const u32 live_warps = (half + 31u) >> 5 < (u32)(TAIL_T / 32) ? (half + 31u) >> 5 : (u32)(TAIL_T / 32);
+        if ((u32)warp < live_warps) {
+            fp2 acc[D + 1];
 #pragma unroll
-        for (int d = 0; d <= D; d++) acc[d] = f2(0, 0);
-        for (u32 i = threadIdx.x; i < half; i += TAIL_T) {
-            fp2 cur[K], dif[K];
+            for (int d = 0; d <= D; d++) acc[d] = f2(0, 0);
+            for (u32 i = threadIdx.x; i < half; i += TAIL_T) {
+                fp2 cur[K], dif[K];
 #pragma unroll
-            for (int t = 0; t < K; t++) {
-                const u64* tb = tables + 2 * (size_t)t * stride;
-                cur[t] = ld2(tb + 2 * (size_t)i);
-                dif[t] = f2_sub(ld2(tb + 2 * ((size_t)i + half)), cur[t]);
+                for (int t = 0; t < K; t++) {
+                    const u64* tb = tables + 2 * (size_t)t * stride;
+                    cur[t] = ld2(tb + 2 * (size_t)i);
+                    dif[t] = f2_sub(ld2(tb + 2 * ((size_t)i + half)), cur[t]);
+                }
+                acc[0] = f2_add(acc[0], poly_eval<POLY, K>(cur, cf));
+#pragma unroll
+                for (int d = 1; d <= D; d++) {
+#pragma unroll
+                    for (int t = 0; t < K; t++) cur[t] = f2_add(cur[t], dif[t]);
+                    if (d != 1 || !have_claim) acc[d] = f2_add(acc[d], poly_eval<POLY, K>(cur, cf));
+                }
             }
-            acc[0] = f2_add(acc[0], poly_eval<POLY, K>(cur, cf));
 #pragma unroll
-            for (int d = 1; d <= D; d++) {
+            for (int d = 0; d <= D; d++) {
 #pragma unroll
-                for (int t = 0; t < K; t++) cur[t] = f2_add(cur[t], dif[t]);
-                if (d != 1 || !have_claim) acc[d] = f2_add(acc[d], poly_eval<POLY, K>(cur, cf));
+                for (int off = 16; off >= 1; off >>= 1) {
+                    acc[d].c0 = gl_add(acc[d].c0, shfl_down64(acc[d].c0, off));
+                    acc[d].c1 = gl_add(acc[d].c1, shfl_down64(acc[d].c1, off));
+                }
             }
-        }
+            if (lane == 0) {
 #pragma unroll
-        for (int d = 0; d <= D; d++) {
-#pragma unroll
-            for (int off = 16; off >= 1; off >>= 1) {
-                acc[d].c0 = gl_add(acc[d].c0, shfl_down64(acc[d].c0, off));
-                acc[d].c1 = gl_add(acc[d].c1, shfl_down64(acc[d].c1, off));
+                for (int d = 0; d <= D; d++) { wsum[warp][2 * d] = acc[d].c0; wsum[warp][2 * d + 1] = acc[d].c1; }
             }
-        }
-        if (lane == 0) {
-#pragma unroll
-            for (int d = 0; d <= D; d++) { wsum[warp][2 * d] = acc[d].c0; wsum[warp][2 * d + 1] = acc[d].c1; }
         }
         __syncthreads();
         if (threadIdx.x < 2 * (D + 1)) {
             u64 s = 0;
-#pragma unroll
-            for (int w = 0; w < TAIL_T / 32; w++) s = gl_add(s, wsum[w][threadIdx.x]);
+            for (u32 w = 0; w < live_warps; w++) s = gl_add(s, wsum[w][threadIdx.x]);
             sm.sums[threadIdx.x] = s;
         }
         __syncthreads();
-        if (warp == 0) {
-            ScStep b = a;
-            b.round = a.round + rd; b.use_claim = have_claim ? 1 : 0; b.fs = 1;
-            step_body(b, sm, lane);
-        }
+        if (warp == 0) step_body(step_args(a, a.round + rd, have_claim ? 1 : 0, 1, mask_p, tab_s, invden_s, a.extrap, &st_s), sm, lane);
         __syncthreads();
-        const fp2 r = a.state->r;
+        const fp2 r = st_s.r;
         for (u32 x = threadIdx.x; x < half * K; x += TAIL_T) {
             const u32 t = x / half, i = x - t * half;
             u64* tb = tables + 2 * (size_t)t * stride;
@@ -699,7 +745,7 @@ __global__ void __launch_bounds__(IR_TAIL_T) k_sc_tail_ir(u64* __restrict__ tabl
     __shared__ u64 wsum[IR_TAIL_T / 32][2 * hlk::SC_MAX_POINTS];
     __shared__ hlk::ScState st_s;
     __shared__ u64 mask_s[2 * (63 * (hlk::SC_MAX_POINTS - 1) + 2)];
-    __shared__ u64 hs_s[2 * 63];
+    __shared__ u64 tab_s[2 * 63 * hlk::SC_MAX_POINTS];
     __shared__ u64 invden_s[hlk::SC_MAX_POINTS];
     __shared__ u64 extrap_s[hlk::SC_MAX_POINTS * hlk::SC_MAX_POINTS];
     fp2* cf_s;
@@ -713,16 +759,14 @@ __global__ void __launch_bounds__(IR_TAIL_T) k_sc_tail_ir(u64* __restrict__ tabl
         for (u32 i = threadIdx.x; i < sizeof(hlk::ScState) / 4; i += nthreads) dst[i] = src[i];
         if (a.mask) {
             for (u32 i = threadIdx.x; i < 2u * (a.mask_vars * degree + 2); i += nthreads) mask_s[i] = a.mask[i];
-            for (u32 i = threadIdx.x; i < 2u * a.mask_vars; i += nthreads) hs_s[i] = a.mask_half_suffix[i];
+            for (u32 i = threadIdx.x; i < 2u * a.mask_vars * np; i += nthreads) tab_s[i] = a.mask_tab[i];
         }
         if ((int)threadIdx.x < np) invden_s[threadIdx.x] = a.inv_den[threadIdx.x];
         if (a.extrap && (int)threadIdx.x < (a.degree - a.eval_degree) * (a.eval_degree + 1)) extrap_s[threadIdx.x] = a.extrap[threadIdx.x];
     }
     hlk::ScState* const st_global = a.state;
-    if (a.mask) { a.mask = mask_s; a.mask_half_suffix = hs_s; }
-    a.inv_den = invden_s;
-    if (a.extrap) a.extrap = extrap_s;
-    a.state = &st_s;
+    const u64* const mask_p = a.mask ? mask_s : nullptr;
+    const u64* const extrap_p = a.extrap ? extrap_s : nullptr;
     __syncthreads();
     for (int rd = 0; rd < nrounds; rd++) {
         const u32 half = len >> 1;  // a power of two
@@ -772,13 +816,9 @@ __global__ void __launch_bounds__(IR_TAIL_T) k_sc_tail_ir(u64* __restrict__ tabl
             sm.sums[threadIdx.x] = s;
         }
         __syncthreads();
-        if (warp == 0) {
-            ScStep b = a;
-            b.round = a.round + rd; b.use_claim = have_claim ? 1 : 0; b.fs = 1;
-            step_body(b, sm, (int)lane);
-        }
+        if (warp == 0) step_body(step_args(a, a.round + rd, have_claim ? 1 : 0, 1, mask_p, tab_s, invden_s, extrap_p, &st_s), sm, (int)lane);
         __syncthreads();
-        const fp2 r = a.state->r;
+        const fp2 r = st_s.r;
         for (u32 x = threadIdx.x; x < half * (u32)k; x += nthreads) {
             const u32 t = x / half, i = x - t * half;
             u64* tb = tables + 2 * (size_t)t * stride;

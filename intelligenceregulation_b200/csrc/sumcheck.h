@@ -21,7 +21,7 @@ struct ScState {
     fp2 r;
     fp2 mask_c;
     fp2 acc_prev;   // sum_{i<j} u_i(r_i)
-    fp2 prod_prev;  // prod_{i<j} r_i
+    fp2 ap;         // a' prod_{i<j} r_i (the mask's linear term, sumcheck.rs:260-295)
 };
 
 struct ScStep {
@@ -32,9 +32,11 @@ struct ScStep {
     int recover;                // keep the running claim (rounds.rs recover_one)
     int fs;                     // 0: only reduce and write the sums (host-driven round())
     const u64* mask;            // CFS coefficients [a0, a', a_{j,e}] or NULL
-    const u64* mask_half_suffix;  // per round j: sum_{i>j} u_i(1)/2
-    const u64* mask_row = nullptr;  // when set: this round's `degree` coefficients a_{j,e} and (hs_row) its suffix term, already picked out
-    const u64* hs_row = nullptr;
+    // per round j and point x = 0..degree: 2^(N-1-j) (a0 + sum_{i>j} u_i(1)/2 + u_j(x)), the part of the mask's round
+    // polynomial g_j(x) that no challenge enters (made by the host once per batch)
+    const u64* mask_tab;
+    const u64* mask_row = nullptr;  // when set: this round's `degree` coefficients a_{j,e} and (tab_row) its degree+1 table entries, already picked out
+    const u64* tab_row = nullptr;
     int mask_vars;
     const u64* inv_den;         // degree+1 inverse Lagrange denominators
     int eval_degree;            // the sums arrive at the points 0..eval_degree; the points above are extrapolated
