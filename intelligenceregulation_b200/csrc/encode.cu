@@ -1,4 +1,5 @@
 // Row-encoder kernels: persistent CTAs, one row at a time per CTA (see encode_core.cuh).
+#define GL_PLAIN_CANONICAL_FORMS 1  // see gl_field.cuh: this file is tuned around the 64-bit C forms
 #include "encode_core.cuh"
 #include "kernels.h"
 
