@@ -260,6 +260,15 @@ def device_extras(dev, backend, np_data, np_pads, np_pows, col_key, only: str = 
             ev.free()
         t = ctx.timing_read(reset=True)
         out["sumcheck_logup_q_2^21_deg3_21rounds_ms"] = t["rounds"][0] / 2
+        ctx.set_dependent_launch(False)  # the same batch with every kernel an ordinary stream launch
+        for rep in range(3):
+            ev = backend.B200Rounds(ctx, backend.POLY_LOGUP_Q, tables, 3, alpha)
+            if rep == 1:
+                ctx.timing_read(reset=True)
+            ev.batched(n, bytes(32), 0, None, mask=mask, mask_vars=n + 1, mask_c=(3, 5), recover_one=True, claim=(0, 0))
+            ev.free()
+        out["sumcheck_logup_q_2^21_deg3_21rounds_plain_launches_ms"] = ctx.timing_read(reset=True)["rounds"][0] / 2
+        ctx.set_dependent_launch(True)
     if want("helpers"):
         nq = 1 << 21
         qidx = (splitmix_fp(82, nq) % np.uint64(1 << 16)).astype(np.int32)

@@ -17,6 +17,9 @@ extern "C" {
 int hl_b200_butterfly_peak(hl_ctx* ctx, uint32_t iters, double* butterflies_per_second);
 /* the same for the column hash: register-resident BLAKE3 compressions per second, all SMs */
 int hl_b200_compress_peak(hl_ctx* ctx, uint32_t iters, double* compressions_per_second);
+/* A/B switch of the sumcheck kernels' programmatic dependent launch (process-wide, on by default): with 0 every kernel of a
+ * sumcheck is an ordinary stream launch again.  For measuring what the chained launch saves. */
+int hl_b200_set_dependent_launch(int on);
 
 #ifdef __cplusplus
 }

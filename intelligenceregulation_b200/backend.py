@@ -89,6 +89,10 @@ class Context:
         """the generated per-graph round kernels, or (default) the interpreter, for slot programs with a known graph"""
         self.check(self.lib.hl_b200_set_slot_kernels(self.h, 1 if on else 0))
 
+    def set_dependent_launch(self, on: bool) -> None:
+        """measurement aid (process-wide): the sumcheck kernels as a programmatic dependent-launch chain (default) or as ordinary launches"""
+        self.check(self.lib.hl_b200_set_dependent_launch(1 if on else 0))
+
     def set_alloc_cap(self, nbytes: int) -> None:
         """Host-side allocation-failure injection (0 = no cap)."""
         self.check(self.lib.hl_b200_set_alloc_cap(self.h, nbytes))

@@ -4,6 +4,7 @@
 #include <cstring>
 
 #include "api_internal.h"
+#include "../../include/hl_b200_bench.h"
 #include "slot_gen.cuh"
 #include "sumcheck.h"
 
@@ -332,6 +333,11 @@ int hl_b200_rounds_finals(hl_rounds* r, uint64_t* out) {
     for (u32 t = 0; t < r->k && !rc; t++) rc = d2h(c, out + 2 * t, r->d_tables + 2 * (size_t)t * r->stride, 16);
     if (!rc) rc = sync(c, "rounds_finals");
     return rc;
+}
+
+int hl_b200_set_dependent_launch(int on) {
+    hlk::sc_set_dependent_launch(on != 0);
+    return HL_B200_OK;
 }
 
 int hl_b200_rounds_batched(hl_rounds* r, uint32_t nd, hl_fs_state* fs, const uint64_t* mask_coeffs, uint32_t mask_vars,

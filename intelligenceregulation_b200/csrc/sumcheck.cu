@@ -17,7 +17,37 @@
 #include "kernels.h"
 #include "sumcheck.h"
 
+namespace hlk {
+bool g_sc_dependent_launch = true;
+void sc_set_dependent_launch(bool on) { g_sc_dependent_launch = on; }
+}  // namespace hlk
+
 namespace {
+
+// Programmatic dependent launch: every kernel of a sumcheck is a link of one dependency chain in one stream.  A kernel opens with
+// `chain_enter()`: it lets the next link be scheduled at once (its CTAs take the SM slots this grid leaves free and stop at their own
+// wait) and then waits until the previous link has completed and its writes are visible.  Launched without the attribute the two
+// instructions do nothing.  What the chain saves is the launch latency between dependent kernels, a few microseconds per link.
+__device__ __forceinline__ void chain_enter() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+template <class... P, class... A>
+cudaError_t chain_launch(void (*kern)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, A... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = hlk::g_sc_dependent_launch ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, P(args)...);
+}
+
 
 using hlk::ScStep;
 
@@ -56,6 +86,7 @@ constexpr int RT = 256;  // threads of a round CTA
 template <int POLY, int K, int D>
 __global__ void __launch_bounds__(RT) k_sc_round(const u64* __restrict__ tables, size_t stride, u32 half, const u64* __restrict__ coefs,
                                                  int eval_one, u64* __restrict__ partials) {
+    chain_enter();
     fp2 acc[D + 1];
 #pragma unroll
     for (int d = 0; d <= D; d++) acc[d] = f2(0, 0);
@@ -280,6 +311,7 @@ __device__ __forceinline__ void step_body(const StepArgs a, StepSmem& sm, int la
 // warp 0 then runs the Fiat-Shamir step.
 constexpr int STEP_T = 512;
 __global__ void __launch_bounds__(STEP_T) k_sc_step(ScStep a) {
+    chain_enter();
     __shared__ StepSmem sm;
     __shared__ u64 red[STEP_T];
     // everything the serial step reads is fetched by the whole CTA while the partials are summed: the step itself then waits on
@@ -332,6 +364,7 @@ constexpr int TAIL_T = 1024;
 template <int POLY, int K, int D>
 __global__ void __launch_bounds__(TAIL_T) k_sc_tail(u64* __restrict__ tables, size_t stride, u32 len, const u64* __restrict__ coefs,
                                                     ScStep a, int nrounds, int first_has_claim, u64* __restrict__ scratch) {
+    chain_enter();
     __shared__ StepSmem sm;
     __shared__ u64 wsum[TAIL_T / 32][2 * (D + 1)];
     // the evaluator state, the mask and the Lagrange denominators stay in shared memory for the whole tail:
@@ -436,6 +469,7 @@ __global__ void __launch_bounds__(256) k_sc_nonbase(const u64* __restrict__ tabl
 template <int POLY, int K, int D>
 __global__ void __launch_bounds__(RT) k_sc_fold_round(u64* __restrict__ tables, size_t stride, u32 n, const u64* __restrict__ coefs,
                                                       const hlk::ScState* __restrict__ st, int eval_one, u64* __restrict__ partials) {
+    chain_enter();
     fp2 acc[D + 1];
 #pragma unroll
     for (int d = 0; d <= D; d++) acc[d] = f2(0, 0);
@@ -487,6 +521,7 @@ __global__ void __launch_bounds__(RT) k_sc_fold_round(u64* __restrict__ tables, 
 }
 
 __global__ void __launch_bounds__(256) k_sc_fold(u64* __restrict__ tables, size_t stride, u32 half, u32 k, const hlk::ScState* __restrict__ st) {
+    chain_enter();
     const u32 i = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
     if (i >= half || t >= k) return;
     const fp2 r = st->r;
@@ -527,6 +562,7 @@ __device__ __forceinline__ fp2 ir_table_value(const u64* __restrict__ tb, u32 i,
 // thread form: grid (blocks, degree + 1), row y evaluates point y; partials[block][point] as in k_sc_round
 __global__ void __launch_bounds__(IRT) k_sc_round_ir(const u64* __restrict__ tables, size_t stride, u32 half, hlk::IrDev p, int degree,
                                                      int eval_one, u64* __restrict__ partials) {
+    chain_enter();
     extern __shared__ __align__(16) u32 ir_smem[];
     __shared__ u64 wsum[IRT / 32][2];
     fp2* cf_s;
@@ -565,6 +601,7 @@ __global__ void __launch_bounds__(IRT) k_sc_round_ir(const u64* __restrict__ tab
 constexpr u32 IRP_VALUES = ir::MAX_TABLES + ir::MAX_NODES + 1;
 __global__ void __launch_bounds__(IRT, 8) k_sc_round_irp(const u64* __restrict__ tables, size_t stride, u32 half, hlk::IrDev p, int degree,
                                                       int eval_one, u64* __restrict__ partials) {
+    chain_enter();
     extern __shared__ __align__(16) u32 ir_smem[];
     __shared__ u64 wsum[IRT / 32][2 * hlk::SC_MAX_POINTS];
     fp2* cf_s;
@@ -623,6 +660,7 @@ __global__ void __launch_bounds__(IRT, 8) k_sc_round_irp(const u64* __restrict__
 template <u32 NPW, bool SKIP>
 __global__ void __launch_bounds__(IRT, 4) k_sc_round_irq(const u64* __restrict__ tables, size_t stride, u32 half, hlk::IrDev p, int degree,
                                                          u64* __restrict__ partials) {
+    chain_enter();
     extern __shared__ __align__(16) u32 ir_smem[];
     __shared__ u64 wsum[IRT / 32][2 * hlk::SC_MAX_POINTS];
     fp2* cf_s;
@@ -712,6 +750,7 @@ __device__ __forceinline__ ir::Pair ir_pair_setup(const hlk::IrDev& p, const u32
 
 __global__ void __launch_bounds__(IRC_MAX_WARPS * 32) k_sc_round_irc(const u64* __restrict__ tables, size_t stride, u32 half, hlk::IrDev p,
                                                                      int degree, int eval_one, u64* __restrict__ partials) {
+    chain_enter();
     extern __shared__ __align__(16) u32 ir_smem[];
     __shared__ u64 wsum[IRC_MAX_WARPS][2 * hlk::SC_MAX_POINTS];
     fp2* cf_s;
@@ -740,6 +779,7 @@ __global__ void __launch_bounds__(IRC_MAX_WARPS * 32) k_sc_round_irc(const u64* 
 template <bool PAIR_FORM>
 __global__ void __launch_bounds__(IR_TAIL_T) k_sc_tail_ir(u64* __restrict__ tables, size_t stride, u32 len, hlk::IrDev p, int degree, int k,
                                                           ScStep a, int nrounds, int first_has_claim) {
+    chain_enter();
     extern __shared__ __align__(16) u32 ir_smem[];
     __shared__ StepSmem sm;
     __shared__ u64 wsum[IR_TAIL_T / 32][2 * hlk::SC_MAX_POINTS];
@@ -857,7 +897,7 @@ int ir_pair_warps(const hlk::IrDev& p, int degree, int want) {
 
 template <int POLY, int K, int D>
 cudaError_t launch_round(const u64* tables, size_t stride, u32 half, const u64* coefs, int eval_one, u64* partials, u32 nblocks, cudaStream_t s) {
-    k_sc_round<POLY, K, D><<<nblocks, RT, 0, s>>>(tables, stride, half, coefs, eval_one, partials);
+    chain_launch(k_sc_round<POLY, K, D>, dim3(nblocks), dim3(RT), 0, s, tables, stride, half, coefs, eval_one, partials);
     return cudaGetLastError();
 }
 
@@ -913,7 +953,7 @@ cudaError_t sc_round_ir(const IrDev& p, int k, const u64* tables, size_t stride,
             cudaError_t e = cudaFuncSetAttribute(k_sc_round_irc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return e;
         }
-        k_sc_round_irc<<<nblocks, w * 32, smem, s>>>(tables, stride, half, p, degree, eval_one, partials);
+        chain_launch(k_sc_round_irc, dim3(nblocks), dim3(w * 32), smem, s, tables, stride, half, p, degree, eval_one, partials);
         return cudaGetLastError();
     }
     if (ir_thread_pair_form(p, half)) {
@@ -921,18 +961,18 @@ cudaError_t sc_round_ir(const IrDev& p, int k, const u64* tables, size_t stride,
             const bool skip = !eval_one && p.eval_degree >= 1;
 #define IRQ(N)                                                                                                             \
     case N:                                                                                                                \
-        if (skip) k_sc_round_irq<N, true><<<nblocks, IRT, ir_fixed_bytes(p), s>>>(tables, stride, half, p, degree, partials); \
-        else k_sc_round_irq<N, false><<<nblocks, IRT, ir_fixed_bytes(p), s>>>(tables, stride, half, p, degree, partials);     \
+        if (skip) chain_launch(k_sc_round_irq<N, true>, dim3(nblocks), dim3(IRT), ir_fixed_bytes(p), s, tables, stride, half, p, degree, partials); \
+        else chain_launch(k_sc_round_irq<N, false>, dim3(nblocks), dim3(IRT), ir_fixed_bytes(p), s, tables, stride, half, p, degree, partials);     \
         break;
             switch (p.eval_degree + 1) { IRQ(1) IRQ(2) IRQ(3) IRQ(4) IRQ(5) IRQ(6) default: return cudaErrorInvalidValue; }
 #undef IRQ
             return cudaGetLastError();
         }
-        k_sc_round_irp<<<nblocks, IRT, ir_fixed_bytes(p), s>>>(tables, stride, half, p, degree, eval_one, partials);
+        chain_launch(k_sc_round_irp, dim3(nblocks), dim3(IRT), ir_fixed_bytes(p), s, tables, stride, half, p, degree, eval_one, partials);
         return cudaGetLastError();
     }
     dim3 grid(nblocks, p.eval_degree + 1);  // the rows above are extrapolated by the step
-    k_sc_round_ir<<<grid, IRT, ir_fixed_bytes(p), s>>>(tables, stride, half, p, degree, eval_one, partials);
+    chain_launch(k_sc_round_ir, dim3(grid), dim3(IRT), ir_fixed_bytes(p), s, tables, stride, half, p, degree, eval_one, partials);
     return cudaGetLastError();
 }
 
@@ -946,9 +986,9 @@ cudaError_t sc_tail_ir(const IrDev& p, int k, u64* tables, size_t stride, u32 le
             cudaError_t e = cudaFuncSetAttribute(k_sc_tail_ir<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return e;
         }
-        k_sc_tail_ir<true><<<1, w * 32, smem, s>>>(tables, stride, len, p, degree, k, a, nrounds, first_has_claim);
+        chain_launch(k_sc_tail_ir<true>, dim3(1), dim3(w * 32), smem, s, tables, stride, len, p, degree, k, a, nrounds, first_has_claim);
     } else {
-        k_sc_tail_ir<false><<<1, IR_TAIL_T, ir_fixed_bytes(p), s>>>(tables, stride, len, p, degree, k, a, nrounds, first_has_claim);
+        chain_launch(k_sc_tail_ir<false>, dim3(1), dim3(IR_TAIL_T), ir_fixed_bytes(p), s, tables, stride, len, p, degree, k, a, nrounds, first_has_claim);
     }
     return cudaGetLastError();
 }
@@ -986,7 +1026,7 @@ cudaError_t sc_round(int poly, int k, const u64* tables, size_t stride, u32 half
 template <int POLY, int K, int D>
 static cudaError_t launch_fold_round(u64* tables, size_t stride, u32 n, const u64* coefs, const ScState* st, int eval_one, u64* partials, u32 nblocks,
                                      cudaStream_t s) {
-    k_sc_fold_round<POLY, K, D><<<nblocks, RT, 0, s>>>(tables, stride, n, coefs, st, eval_one, partials);
+    chain_launch(k_sc_fold_round<POLY, K, D>, dim3(nblocks), dim3(RT), 0, s, tables, stride, n, coefs, st, eval_one, partials);
     return cudaGetLastError();
 }
 
@@ -1016,7 +1056,7 @@ cudaError_t sc_fold_round(int poly, int k, u64* tables, size_t stride, u32 n, co
 template <int POLY, int K, int D>
 static cudaError_t launch_tail(u64* tables, size_t stride, u32 len, const u64* coefs, const ScStep& a, int nrounds, int first_has_claim,
                                u64* scratch, cudaStream_t s) {
-    k_sc_tail<POLY, K, D><<<1, TAIL_T, 0, s>>>(tables, stride, len, coefs, a, nrounds, first_has_claim, scratch);
+    chain_launch(k_sc_tail<POLY, K, D>, dim3(1), dim3(TAIL_T), 0, s, tables, stride, len, coefs, a, nrounds, first_has_claim, scratch);
     return cudaGetLastError();
 }
 
@@ -1043,7 +1083,7 @@ cudaError_t sc_tail(int poly, int k, u64* tables, size_t stride, u32 len, const 
 }
 
 cudaError_t sc_step(const ScStep& a, cudaStream_t s) {
-    k_sc_step<<<1, STEP_T, 0, s>>>(a);
+    chain_launch(k_sc_step, dim3(1), dim3(STEP_T), 0, s, a);
     return cudaGetLastError();
 }
 
@@ -1056,7 +1096,7 @@ cudaError_t sc_nonbase_mask(const u64* tables, size_t stride, size_t len, u32 k,
 
 cudaError_t sc_fold(u64* tables, size_t stride, u32 half, u32 k, const ScState* st, cudaStream_t s) {
     dim3 grid((half + 255) / 256, k);
-    k_sc_fold<<<grid, 256, 0, s>>>(tables, stride, half, k, st);
+    chain_launch(k_sc_fold, dim3(grid), dim3(256), 0, s, tables, stride, half, k, st);
     return cudaGetLastError();
 }
 

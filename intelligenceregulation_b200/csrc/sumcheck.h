@@ -54,6 +54,7 @@ struct IrDev {
     int all_points;    // the plan fits the thread pair form that evaluates a unit at every point at once
 };
 
+void sc_set_dependent_launch(bool on);
 u32 sc_round_blocks(u32 half, int sm_count);
 // the data-driven evaluator: one CTA row per evaluation point, `sc_ir_blocks` CTAs per row
 u32 sc_ir_blocks(const IrDev& p, u32 half, int degree, int sm_count);
@@ -71,7 +72,7 @@ cudaError_t sc_step(const ScStep& a, cudaStream_t s);
 // closed-form families: fold with the challenge in `st` and sum the next round (length n after the fold) in one pass
 cudaError_t sc_fold_round(int poly, int k, u64* tables, size_t stride, u32 n, const u64* coefs, const ScState* st, int eval_one, u64* partials,
                           u32 nblocks, cudaStream_t s);
-constexpr u32 SC_TAIL_LEN = 1024;  // table length from which the remaining rounds run in one CTA (one SM: above it a round's arithmetic costs more than three launches)
+constexpr u32 SC_TAIL_LEN = 2048;  // table length from which the remaining rounds run in one CTA (measured on the 3-table degree-3 family: 1024 -> 0.467 ms, 2048 -> 0.450, 4096 -> 0.480, 8192 -> 0.517 for 21 rounds; above it the arithmetic of one SM costs more than the launches it saves)
 cudaError_t sc_tail(int poly, int k, u64* tables, size_t stride, u32 len, const u64* coefs, const ScStep& a, int nrounds,
                     int first_has_claim, u64* scratch, cudaStream_t s);
 // bit t of *d_mask is set when table t holds a non-zero second word anywhere in its first `len` entries (*d_mask zeroed by the caller)
