@@ -36,6 +36,13 @@ struct HostRows {
     const void* base = nullptr;
     const uint8_t* row_w = nullptr;
     std::vector<u64> off;  // packed form only: rows + 1 byte offsets
+    // what else the call brings from the host.  When the rows go up in pieces these ride with them instead of ahead of them: the
+    // pads of a piece's rows behind the piece (st->d_pads is their place), `tail` (the salts: nothing reads them before the
+    // tree) behind the last piece.  Otherwise both are copied before the rows.
+    const u64* pads = nullptr;
+    const void* tail_src = nullptr;
+    void* tail_dst = nullptr;
+    size_t tail_bytes = 0;
 };
 
 // Encode + column-hash.  With no host rows the data rows are already in st->d_data; otherwise they are
@@ -74,15 +81,34 @@ int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* 
     if (!rc && packed) rc = h2d_owned(c, d_row_w, hr.row_w, st->rows);
     // Row pieces: a piece is encoded and its complete 1 KiB hash chunks (128 rows) are hashed while the next piece is still on
     // the bus.  Piece sizes are whole waves of the encoder (one row per SM per wave).  When the bytes per row make the bus the
-    // slower side (64-bit words) the pieces are two waves and the last one a single wave, so that little follows the upload;
-    // when the device is the slower side (narrow rows) the first piece is one wave, so that the encoder starts early, and the
-    // rest are four waves, which keeps the number of partly filled waves at one.
+    // slower side (64-bit words) the pieces are two waves and the last one a single wave, so that little follows the upload.
+    // When the device is the slower side (narrow rows) the pieces grow 1, 2, 3, 5, 8, 8, .. waves: the encoder starts after one
+    // wave's bytes, and each next piece is on the device before the encoder has finished the one before it (a wave takes the
+    // encoder and the chunk hash about 1.7 times what its narrow bytes take on the bus, and no piece is more than 1.7 times
+    // its predecessor but the second); with a first piece of one wave followed by four-wave pieces the encoder idled through
+    // most of the second piece's upload.
     auto byte_at = [&](u32 r) { return packed ? (size_t)hr.off[r] : (size_t)r * n * 8; };
     const u32 wave = (u32)c->sm_count;
     const bool split = h_data && total_bytes >= ((size_t)32 << 20) && st->rows > 4u * wave;
     const bool bus_bound = total_bytes / st->rows >= n * 6;  // bytes per row near the 64-bit form
-    const u32 chunk = split ? (bus_bound ? 2u * wave : 4u * wave) : st->rows;
     const bool pieces = split;
+    std::vector<u32> piece_rows;
+    if (!pieces) {
+        piece_rows.push_back(st->rows);
+    } else if (bus_bound) {
+        for (u32 r0 = 0; r0 < st->rows;) {
+            u32 nr = st->rows - r0 < 2u * wave ? st->rows - r0 : 2u * wave;
+            if (r0 + nr == st->rows && nr > wave) nr -= wave;  // leave one wave or less for the end
+            piece_rows.push_back(nr);
+            r0 += nr;
+        }
+    } else {
+        for (u32 r0 = 0, w = 1; r0 < st->rows; w = (w * 3 + 1) / 2 > 8 ? 8 : (w * 3 + 1) / 2) {
+            const u32 nr = st->rows - r0 < w * wave ? st->rows - r0 : w * wave;
+            piece_rows.push_back(nr);
+            r0 += nr;
+        }
+    }
     if (!rc && pieces) {
         // the copy stream may touch the fresh allocations only after the main stream has made them
         cudaError_t e = cudaEventRecord(c->ev_main, c->stream);
@@ -96,10 +122,10 @@ int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* 
         cudaPointerAttributes attr;
         const bool pageable = cudaPointerGetAttributes(&attr, h_data) != cudaSuccess || attr.type == cudaMemoryTypeUnregistered;
         cudaGetLastError();  // an unregistered pointer is not an error here
-        size_t need = 0;  // the largest piece, whatever its start
-        for (u32 r0 = 0; r0 < st->rows; r0 += wave) {
-            const u32 r1 = r0 + chunk < st->rows ? r0 + chunk : st->rows;
-            need = byte_at(r1) - byte_at(r0) > need ? byte_at(r1) - byte_at(r0) : need;
+        size_t need = 0;  // the largest piece
+        for (u32 r0 = 0, k = 0; k < piece_rows.size(); r0 += piece_rows[k++]) {
+            const size_t b = byte_at(r0 + piece_rows[k]) - byte_at(r0);
+            need = b > need ? b : need;
         }
         if (pageable) {
             staged = true;
@@ -114,15 +140,16 @@ int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* 
             }
         }
     }
+    if (!rc && !pieces && hr.pads) rc = h2d(c, st->d_pads, hr.pads, (size_t)st->rows * st->q * 8);
+    if (!rc && !pieces && hr.tail_bytes) rc = h2d(c, hr.tail_dst, hr.tail_src, hr.tail_bytes);
     size_t piece_i = 0;
     if (!rc) {
         Timed t(c, HL_T_ENCODE);
         size_t ev_i = 0;
         u32 nr = 0, chunks_done = 0;
+        size_t pk = 0;
         for (u32 r0 = 0; r0 < st->rows && !rc; r0 += nr) {
-            nr = st->rows - r0 < chunk ? st->rows - r0 : chunk;
-            if (pieces && !bus_bound && r0 == 0) nr = wave;                                            // start the encoder early
-            if (pieces && bus_bound && r0 + nr == st->rows && nr > wave) nr -= wave;                   // leave one wave or less for the end
+            nr = piece_rows[pk++];
             if (h_data) {
                 cudaStream_t cs = pieces ? c->copy_stream : c->stream;
                 const size_t b0 = byte_at(r0), bytes = byte_at(r0 + nr) - b0;
@@ -143,6 +170,15 @@ int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* 
                 cudaError_t e = cudaMemcpyAsync(to, from, bytes, cudaMemcpyHostToDevice, cs);
                 if (staged && e == cudaSuccess) e = cudaEventRecord(c->stage_ev[(piece_i - 1) & 1], cs);
                 c->stats.bytes_h2d += bytes;
+                if (pieces && hr.pads && e == cudaSuccess) {
+                    const size_t pb = (size_t)nr * st->q * 8;
+                    e = cudaMemcpyAsync(st->d_pads + (size_t)r0 * st->q, hr.pads + (size_t)r0 * st->q, pb, cudaMemcpyHostToDevice, cs);
+                    c->stats.bytes_h2d += pb;
+                }
+                if (pieces && hr.tail_bytes && r0 + nr == st->rows && e == cudaSuccess) {
+                    e = cudaMemcpyAsync(hr.tail_dst, hr.tail_src, hr.tail_bytes, cudaMemcpyHostToDevice, cs);
+                    c->stats.bytes_h2d += hr.tail_bytes;
+                }
                 if (e == cudaSuccess && cs != c->stream) {
                     if (ev_i == c->ev_chunks.size()) {
                         cudaEvent_t ev = nullptr;
@@ -172,7 +208,10 @@ int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* 
             cudaError_t e = hlk::encode_rows(a, logb, c->fast_encoder || loga, c->sm_count, scratch_words, c->stream, &st->encoder_path);
             c->stats.kernel_launches += 1;
             if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "row encoder launch", e);
-            if (!rc && pieces) {  // the 128-row hash chunks that are complete now
+            // the 128-row hash chunks that are complete now: only where the bus is the slower side and the device would idle otherwise.
+            // Where the device is the slower side every kernel's time adds up, and chunk launches of a few chunks each fill the
+            // machine badly (five launches 430 us against 350 us for all twenty chunks in one).
+            if (!rc && pieces && bus_bound) {
                 const u32 c1 = r0 + nr == st->rows ? nchunks : (r0 + nr) / 128u;
                 if (c1 > chunks_done) {
                     e = hlk::hash_column_chunks(st->d_enc, st->rows, (u32)nn, d_key, chunks_done, c1 - chunks_done, cvs, st->d_leaves, c->stream);
@@ -183,13 +222,13 @@ int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* 
             }
         }
     }
-    if (!rc && pieces) {
+    if (!rc && pieces && bus_bound) {
         Timed t(c, HL_T_HASH);
         cudaError_t e = hlk::hash_column_merge(st->rows, (u32)nn, d_key, cvs, st->d_leaves, c->stream);
         c->stats.kernel_launches += 1;
         if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "column hash merge launch", e);
     }
-    if (!rc && !pieces) {
+    if (!rc && !(pieces && bus_bound)) {
         Timed t(c, HL_T_HASH);
         cudaError_t e = hlk::hash_columns(st->d_enc, st->rows, (u32)nn, d_key, cvs, st->d_leaves, c->stream);
         c->stats.kernel_launches += nchunks > 1 ? 2 : 1;
@@ -244,14 +283,15 @@ int commit_host(hl_ctx* c, const Shape& s, const HostRows& data, const uint64_t*
     int rc = dev_alloc(c, (void**)&st->d_data, (size_t)s.rows * n * 8);
     if (!rc && tree) rc = dev_alloc(c, (void**)&d_salts, nn * 32);
     if (!rc && tree) rc = dev_alloc(c, (void**)&d_levels, (2 * nn - 1) * 32);
-    if (!rc && tree) rc = h2d(c, d_salts, tree->salts32, nn * 32);
     if (!rc && s.zk) rc = dev_alloc(c, (void**)&st->d_pads, (size_t)s.rows * s.q * 8);
     if (!rc && s.zk) rc = dev_alloc(c, (void**)&d_pows, nn * 8);
     if (!rc) rc = dev_alloc(c, (void**)&st->d_enc, (size_t)s.rows * nn * 8);
     if (!rc) rc = dev_alloc(c, (void**)&st->d_leaves, nn * 32);
-    if (!rc && s.zk) rc = h2d(c, st->d_pads, pads, (size_t)s.rows * s.q * 8);
     if (!rc && s.zk) rc = h2d(c, d_pows, pows, nn * 8);
-    if (!rc) rc = commit_on_device(c, st, d_pows, key32, data);
+    HostRows hr = data;  // the pads and the salts travel with the rows (commit_on_device)
+    if (s.zk) hr.pads = reinterpret_cast<const u64*>(pads);
+    if (tree) { hr.tail_src = tree->salts32; hr.tail_dst = d_salts; hr.tail_bytes = nn * 32; }
+    if (!rc) rc = commit_on_device(c, st, d_pows, key32, hr);
     if (!rc && tree) rc = merkle_on_device(c, st->d_leaves, d_salts, nn, tree->leaf_key32, tree->node_key32, d_levels);
     if (!rc && leaves32) rc = d2h(c, leaves32, st->d_leaves, nn * 32);
     if (!rc && tree) rc = d2h(c, tree->levels_out, d_levels, (2 * nn - 1) * 32);
