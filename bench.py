@@ -1186,10 +1186,13 @@ def main() -> None:
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the device times of the opening, sumcheck and LogUp kernels")
     ap.add_argument("--profile", action="store_true", help="resident-input leg only (for a run under a profiler)")
+    ap.add_argument("--profile-rows", type=int, default=0, help="with --profile: commit this many rows instead of the workload's (a capture small enough for multi-pass counters)")
     ap.add_argument("--profile-extras", action="store_true", help="opening, sumcheck and LogUp kernels only (for a run under a profiler)")
     ap.add_argument("--only", default="", help="with --profile-extras: comma-separated families to run (open, sumcheck, helpers, i8folds, rng, lookup, slots, "
                                                "slot_program, mask, witness, long_rows, commit_h, verify)")
     args = ap.parse_args()
+    if args.profile and args.profile_rows > 0:
+        WORK["rows"] = args.profile_rows
     rank, local_rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     if args.impl == "reference":
         run_reference(args, rank)

@@ -182,6 +182,15 @@ int hl_b200_verify_columns(hl_ctx* ctx, const uint64_t* cols, size_t rows, size_
                            const uint8_t* leaf_key32, const uint8_t* node_key32, const uint64_t* rhos, size_t k, const uint64_t* wants,
                            const hl_store* vec_store, int32_t* verdict, int64_t* first_bad);
 
+/* The same with the clear vectors handed over as the opening holds them (pcs.rs:1282-1331 in one call): vecs = k vectors of
+ * n + q Fp2 (the group vectors, then the proximity vector); they are split into their 2k real / imaginary rows and encoded on
+ * the device by the commitment's encoder (pows = the coset powers of the commitment, nn words), and every column's combinations are
+ * compared with that encoding at idx[c].  rhos: k x rows Fp2.  The other arguments and the verdicts are hl_b200_verify_columns'. */
+int hl_b200_verify_opening(hl_ctx* ctx, uint32_t log_cols, uint32_t inv_rate, size_t q, const uint64_t* pows, const uint64_t* vecs, size_t k,
+                           const uint64_t* cols, size_t rows, size_t ncols, const uint64_t* idx, const uint8_t* salts32,
+                           const uint8_t* paths32, uint32_t depth, const uint8_t* root32, const uint8_t* column_key32,
+                           const uint8_t* leaf_key32, const uint8_t* node_key32, const uint64_t* rhos, int32_t* verdict, int64_t* first_bad);
+
 /* ---- SumcheckRounds (sumcheck/rounds.rs:22-28; CPU evaluator ClosureRounds :52-167) ----
  * k tables of 2^n_vars Fp2 (table-major, variable 0 = most significant index bit) and a slot polynomial
  * from a fixed family; round j returns the UNMASKED values at 0..=degree of

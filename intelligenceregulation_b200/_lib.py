@@ -64,6 +64,7 @@ SIGNATURES.update({
     "hl_b200_commit_zk_tree": (_int, [_vp, _u32, _u32, _vp, _sz, _vp, _sz, _vp, _u32, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "hl_b200_commit_zk_packed": (_int, [_vp, _u32, _u32, _vp, _vp, _sz, _vp, _sz, _vp, _u32, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "hl_b200_set_dependent_launch": (_int, [_int]),
+    "hl_b200_verify_opening": (_int, [_vp, _u32, _u32, _sz, _vp, _vp, _sz, _vp, _sz, _sz, _vp, _vp, _vp, _u32, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "hl_b200_verify_columns": (_int, [_vp, _vp, _sz, _sz, _vp, _vp, _vp, _u32, _vp, _vp, _vp, _vp, _vp, _sz, _vp, _vp, _vp, _vp]),
     "hl_b200_mask_commit": (_int, [_vp, _u32, _u32, _vp, _sz, _vp, _sz, _vp, _vp, _vp, _vp, _vp]),
     "hl_b200_mask_open_q": (_int, [_vp, _sz, _vp, _vp]),

@@ -426,13 +426,30 @@ class B200Backend:
         return (st, leaves, levels) if tree else (st, leaves)
 
     def check_opening_columns(self, log_cols: int, inv_rate: int, pows, max_log: int, cols, idx, salts, paths, root: bytes, column_key: Optional[bytes],
-                              leaf_key: Optional[bytes], node_key: Optional[bytes], rhos, vecs) -> Optional[np.ndarray]:
+                              leaf_key: Optional[bytes], node_key: Optional[bytes], rhos, vecs, one_call: bool = True) -> Optional[np.ndarray]:
         """The data-parallel part of `verify_zk_tagged` (pcs.rs:1282-1331) on the device: the clear vectors (G + 1, n + q, 2) are encoded as
         2 (G + 1) base rows (re and im apart, pcs.rs:1287-1296) by the commitment's own encoder, and every opened column is hashed, walked to the
-        root and compared with them.  None when the device declines the shape (the caller then runs its host body)."""
+        root and compared with them.  `one_call`: through `hl_b200_verify_opening`; otherwise as the two calls a caller who keeps the vectors'
+        commitment would make.  None when the device declines the shape (the caller then runs its host body)."""
         vecs = _u64(vecs)
         n = 1 << log_cols
         g1 = vecs.shape[0]
+        if one_call:
+            cols, idx, rhos, pows = _u64(cols), _u64(idx), _u64(rhos), _u64(pows)
+            ncols = idx.size
+            rows = cols.size // ncols
+            salts = np.ascontiguousarray(salts, dtype=np.uint8).reshape(ncols, 32)
+            paths = np.ascontiguousarray(paths, dtype=np.uint8).reshape(ncols, -1, 32)
+            depth = paths.shape[1]
+            verdict = np.empty(ncols, dtype=np.int32)
+            first = C.c_int64()
+            rc = self.ctx.lib.hl_b200_verify_opening(self.ctx.h, log_cols, inv_rate, vecs.shape[1] - n, _ptr(pows), _ptr(vecs), g1, _ptr(cols), rows, ncols, _ptr(idx),
+                                                     _ptr(salts), _ptr(paths) if depth else None, depth, _ptr(root), _ptr(column_key), _ptr(leaf_key),
+                                                     _ptr(node_key), _ptr(rhos), _ptr(verdict), C.byref(first))
+            if rc != 0:
+                self.ctx.declined("b200 verify opening", rc)
+                return None
+            return verdict
         planes = np.ascontiguousarray(np.moveaxis(vecs, 2, 1)).reshape(2 * g1, -1)  # row 2 g + c = component c of vector g
         got = self.try_commit_zk_keyed(log_cols, inv_rate, np.ascontiguousarray(planes[:, :n]), np.ascontiguousarray(planes[:, n:]), pows, max_log, None)
         if got is None:

@@ -69,6 +69,9 @@ int root_powers(hl_ctx* c, u32 lognn, const u64** out);
 int upload_key(hl_ctx* c, const uint8_t* key32, uint32_t** d_key);
 int log2_exact(size_t v);
 void store_release(hl_store* st);  // frees a store; the caller holds the context's lock
+// a hiding commitment of rows that are on the device already (hl_b200_commit_zk_dev); the caller holds the context's lock
+int commit_resident(hl_ctx* c, u32 log_cols, u32 inv_rate, const u64* d_data, size_t rows, const u64* d_pads, size_t q, const u64* d_pows,
+                    const uint8_t* key32, hl_store** store, uint8_t* d_leaves32);
 
 // Brackets the launches of one kernel family with two events when the context's timing is on.
 struct Timed {

@@ -82,11 +82,12 @@ int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* 
     // Row pieces: a piece is encoded and its complete 1 KiB hash chunks (128 rows) are hashed while the next piece is still on
     // the bus.  Piece sizes are whole waves of the encoder (one row per SM per wave).  When the bytes per row make the bus the
     // slower side (64-bit words) the pieces are two waves and the last one a single wave, so that little follows the upload.
-    // When the device is the slower side (narrow rows) the pieces grow 1, 2, 3, 5, 8, 8, .. waves: the encoder starts after one
-    // wave's bytes, and each next piece is on the device before the encoder has finished the one before it (a wave takes the
-    // encoder and the chunk hash about 1.7 times what its narrow bytes take on the bus, and no piece is more than 1.7 times
-    // its predecessor but the second); with a first piece of one wave followed by four-wave pieces the encoder idled through
-    // most of the second piece's upload.
+    // With narrow rows the device is the slower side when a GPU has the host's bus to itself, and the bus is the slower side again
+    // when eight ranks upload at once (measured: the same 90 MB take 1.6 ms alone and 2.5-3.7 ms beside seven other ranks).  The
+    // pieces are made for both: 1, 2, 3, 3, .. waves - the encoder starts after one wave's bytes, and no piece is more than 1.7
+    // times its predecessor but the second, which is what keeps every next piece on the device before the encoder has finished the
+    // one before it when the device is the slower side - and the last two waves as pieces of their own, so that one wave's
+    // encoding, not five, follows the last byte when the bus is the slower side.
     auto byte_at = [&](u32 r) { return packed ? (size_t)hr.off[r] : (size_t)r * n * 8; };
     const u32 wave = (u32)c->sm_count;
     const bool split = h_data && total_bytes >= ((size_t)32 << 20) && st->rows > 4u * wave;
@@ -103,11 +104,16 @@ int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* 
             r0 += nr;
         }
     } else {
-        for (u32 r0 = 0, w = 1; r0 < st->rows; w = (w * 3 + 1) / 2 > 8 ? 8 : (w * 3 + 1) / 2) {
+        u32 rem = (st->rows + wave - 1) / wave, r0 = 0;  // waves left, the last one possibly short
+        auto take = [&](u32 w) {
             const u32 nr = st->rows - r0 < w * wave ? st->rows - r0 : w * wave;
             piece_rows.push_back(nr);
             r0 += nr;
-        }
+            rem -= w;
+        };
+        for (u32 w = 1; w <= 2 && rem > 2; w++) take(w < rem - 2 ? w : rem - 2);
+        while (rem > 2) take(rem - 2 < 3 ? rem - 2 : 3);
+        while (rem > 0) take(1);
     }
     if (!rc && pieces) {
         // the copy stream may touch the fresh allocations only after the main stream has made them
@@ -208,12 +214,12 @@ int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* 
             cudaError_t e = hlk::encode_rows(a, logb, c->fast_encoder || loga, c->sm_count, scratch_words, c->stream, &st->encoder_path);
             c->stats.kernel_launches += 1;
             if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "row encoder launch", e);
-            // the 128-row hash chunks that are complete now: only where the bus is the slower side and the device would idle otherwise.
-            // Where the device is the slower side every kernel's time adds up, and chunk launches of a few chunks each fill the
-            // machine badly (five launches 430 us against 350 us for all twenty chunks in one).
-            if (!rc && pieces && bus_bound) {
+            // the 128-row hash chunks that are complete now.  Launches of one or two chunks fill the machine badly (five such
+            // launches took 430 us against 350 us for all twenty chunks in one), so narrow rows wait until four chunks are
+            // ready; the last launch takes what is left.
+            if (!rc && pieces) {
                 const u32 c1 = r0 + nr == st->rows ? nchunks : (r0 + nr) / 128u;
-                if (c1 > chunks_done) {
+                if (c1 > chunks_done && (bus_bound || c1 - chunks_done >= 4 || r0 + nr == st->rows)) {
                     e = hlk::hash_column_chunks(st->d_enc, st->rows, (u32)nn, d_key, chunks_done, c1 - chunks_done, cvs, st->d_leaves, c->stream);
                     c->stats.kernel_launches += 1;
                     if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "column hash launch", e);
@@ -222,13 +228,13 @@ int commit_on_device(hl_ctx* c, hl_store* st, const u64* d_pows, const uint8_t* 
             }
         }
     }
-    if (!rc && pieces && bus_bound) {
+    if (!rc && pieces) {
         Timed t(c, HL_T_HASH);
         cudaError_t e = hlk::hash_column_merge(st->rows, (u32)nn, d_key, cvs, st->d_leaves, c->stream);
         c->stats.kernel_launches += 1;
         if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "column hash merge launch", e);
     }
-    if (!rc && !(pieces && bus_bound)) {
+    if (!rc && !pieces) {
         Timed t(c, HL_T_HASH);
         cudaError_t e = hlk::hash_columns(st->d_enc, st->rows, (u32)nn, d_key, cvs, st->d_leaves, c->stream);
         c->stats.kernel_launches += nchunks > 1 ? 2 : 1;
@@ -310,6 +316,31 @@ int commit_host(hl_ctx* c, const Shape& s, const HostRows& data, const uint64_t*
 
 void hlapi::store_release(hl_store* st) { free_store(st); }
 
+// hl_b200_commit_zk_dev without the lock: for entry points that hold it already
+int hlapi::commit_resident(hl_ctx* c, u32 log_cols, u32 inv_rate, const u64* d_data, size_t rows, const u64* d_pads, size_t q, const u64* d_pows,
+                           const uint8_t* key32, hl_store** store, uint8_t* d_leaves32) {
+    Shape s;
+    int rc = check_shape(c, log_cols, inv_rate, rows, q, true, 0, &s);
+    if (rc) return rc;
+    hl_store* st = new hl_store();
+    st->ctx = c; st->rows = s.rows; st->logn = s.logn; st->logr = s.logr; st->q = s.q; st->zk = true;
+    st->owns_inputs = false;
+    st->d_data = const_cast<u64*>(d_data);
+    st->d_pads = const_cast<u64*>(d_pads);
+    const size_t nn = st->nn();
+    rc = dev_alloc(c, (void**)&st->d_enc, (size_t)s.rows * nn * 8);
+    if (!rc) rc = dev_alloc(c, (void**)&st->d_leaves, nn * 32);
+    if (!rc) rc = commit_on_device(c, st, d_pows, key32, HostRows());
+    if (!rc && d_leaves32) {
+        cudaError_t e = cudaMemcpyAsync(d_leaves32, st->d_leaves, nn * 32, cudaMemcpyDeviceToDevice, c->stream);
+        if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "leaf copy", e);
+    }
+    if (rc) { cudaStreamSynchronize(c->stream); free_store(st); return rc; }
+    c->stats.commits++;
+    *store = st;
+    return HL_B200_OK;
+}
+
 extern "C" {
 
 int hl_b200_commit(hl_ctx* c, uint32_t log_cols, uint32_t inv_rate, const uint64_t* data, size_t rows, uint32_t max_log,
@@ -389,26 +420,7 @@ int hl_b200_commit_zk_dev(hl_ctx* c, uint32_t log_cols, uint32_t inv_rate, const
     if (!c || !d_data || !d_pads || !d_pows || !store) return fail(c, HL_B200_ERR_ARG, "commit_zk_dev: null argument");
     std::lock_guard<std::mutex> g(c->mu);
     cudaSetDevice(c->device);
-    Shape s;
-    int rc = check_shape(c, log_cols, inv_rate, rows, q, true, 0, &s);
-    if (rc) return rc;
-    hl_store* st = new hl_store();
-    st->ctx = c; st->rows = s.rows; st->logn = s.logn; st->logr = s.logr; st->q = s.q; st->zk = true;
-    st->owns_inputs = false;
-    st->d_data = const_cast<u64*>((const u64*)d_data);
-    st->d_pads = const_cast<u64*>((const u64*)d_pads);
-    const size_t nn = st->nn();
-    rc = dev_alloc(c, (void**)&st->d_enc, (size_t)s.rows * nn * 8);
-    if (!rc) rc = dev_alloc(c, (void**)&st->d_leaves, nn * 32);
-    if (!rc) rc = commit_on_device(c, st, (const u64*)d_pows, key32, HostRows());
-    if (!rc && d_leaves32) {
-        cudaError_t e = cudaMemcpyAsync(d_leaves32, st->d_leaves, nn * 32, cudaMemcpyDeviceToDevice, c->stream);
-        if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "leaf copy", e);
-    }
-    if (rc) { cudaStreamSynchronize(c->stream); free_store(st); return rc; }
-    c->stats.commits++;
-    *store = st;
-    return HL_B200_OK;
+    return commit_resident(c, log_cols, inv_rate, (const u64*)d_data, rows, (const u64*)d_pads, q, (const u64*)d_pows, key32, store, d_leaves32);
 }
 
 int hl_b200_store_shape(hl_store* st, size_t* rows, size_t* n, size_t* nn, size_t* q) {

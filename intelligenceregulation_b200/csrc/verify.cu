@@ -75,13 +75,30 @@ __global__ void __launch_bounds__(128) k_verify_columns(const uint32_t* __restri
     verdict[c] = v;
 }
 
+// vecs: k vectors of n + q Fp2 -> 2k base rows (re of vector 0, im of vector 0, re of vector 1, ..): the first n words of each into
+// `data` (2k x n), the last q into `pads` (2k x q), the rows a hiding commitment takes (pcs.rs:1287-1296)
+__global__ void __launch_bounds__(256) k_split_vectors(const u64* __restrict__ vecs, u32 k, u32 n, u32 q, u64* __restrict__ data, u64* __restrict__ pads) {
+    const u32 g = blockIdx.y, w = n + q;
+    for (u32 j = blockIdx.x * blockDim.x + threadIdx.x; j < w; j += gridDim.x * blockDim.x) {
+        const u64 re = vecs[((size_t)g * w + j) * 2], im = vecs[((size_t)g * w + j) * 2 + 1];
+        if (j < n) {
+            data[(size_t)(2 * g) * n + j] = re;
+            data[(size_t)(2 * g + 1) * n + j] = im;
+        } else {
+            pads[(size_t)(2 * g) * q + (j - n)] = re;
+            pads[(size_t)(2 * g + 1) * q + (j - n)] = im;
+        }
+    }
+    (void)k;
+}
+
 }  // namespace
 
-extern "C" int hl_b200_verify_columns(hl_ctx* c, const uint64_t* cols, size_t rows, size_t ncols, const uint64_t* idx, const uint8_t* salts32,
-                                      const uint8_t* paths32, uint32_t depth, const uint8_t* root32, const uint8_t* column_key32,
-                                      const uint8_t* leaf_key32, const uint8_t* node_key32, const uint64_t* rhos, size_t k, const uint64_t* wants,
-                                      const hl_store* vec_store, int32_t* verdict, int64_t* first_bad) {
-    if (!c) return HL_B200_ERR_ARG;
+// the body of hl_b200_verify_columns; the caller holds the context's lock
+static int verify_columns_locked(hl_ctx* c, const uint64_t* cols, size_t rows, size_t ncols, const uint64_t* idx, const uint8_t* salts32,
+                                 const uint8_t* paths32, uint32_t depth, const uint8_t* root32, const uint8_t* column_key32,
+                                 const uint8_t* leaf_key32, const uint8_t* node_key32, const uint64_t* rhos, size_t k, const uint64_t* wants,
+                                 const hl_store* vec_store, int32_t* verdict, int64_t* first_bad) {
     if (!cols || !idx || !salts32 || !root32 || !verdict || rows == 0 || ncols == 0) return fail(c, HL_B200_ERR_ARG, "verify_columns: null or empty argument");
     if (depth && !paths32) return fail(c, HL_B200_ERR_ARG, "verify_columns: paths missing");
     if (depth > 40) return fail(c, HL_B200_ERR_ARG, "verify_columns: a path of more than 40 entries");
@@ -95,8 +112,6 @@ extern "C" int hl_b200_verify_columns(hl_ctx* c, const uint64_t* cols, size_t ro
         for (size_t i = 0; i < ncols; i++)
             if (idx[i] >= vec_store->nn()) return fail(c, HL_B200_ERR_ARG, "verify_columns: a column index beyond the encoding");
     }
-    std::lock_guard<std::mutex> g(c->mu);
-    cudaSetDevice(c->device);
     const size_t cb = rows * ncols * 8, pb = (size_t)(depth ? depth : 1) * ncols * 32, ab = (k ? k : 1) * ncols * 16;
     const u32 nchunks = hlk::hash_chunks((u32)rows);
     const size_t cvs_bytes = nchunks > 1 ? (size_t)nchunks * ncols * 32 : 0;
@@ -162,5 +177,56 @@ extern "C" int hl_b200_verify_columns(hl_ctx* c, const uint64_t* cols, size_t ro
     if (d_ck) dev_free(c, d_ck, 32);
     if (d_lk) dev_free(c, d_lk, 32);
     if (d_nk) dev_free(c, d_nk, 32);
+    return rc;
+}
+
+extern "C" int hl_b200_verify_columns(hl_ctx* c, const uint64_t* cols, size_t rows, size_t ncols, const uint64_t* idx, const uint8_t* salts32,
+                                      const uint8_t* paths32, uint32_t depth, const uint8_t* root32, const uint8_t* column_key32,
+                                      const uint8_t* leaf_key32, const uint8_t* node_key32, const uint64_t* rhos, size_t k, const uint64_t* wants,
+                                      const hl_store* vec_store, int32_t* verdict, int64_t* first_bad) {
+    if (!c) return HL_B200_ERR_ARG;
+    std::lock_guard<std::mutex> g(c->mu);
+    cudaSetDevice(c->device);
+    return verify_columns_locked(c, cols, rows, ncols, idx, salts32, paths32, depth, root32, column_key32, leaf_key32, node_key32, rhos, k, wants, vec_store,
+                                 verdict, first_bad);
+}
+
+extern "C" int hl_b200_verify_opening(hl_ctx* c, uint32_t log_cols, uint32_t inv_rate, size_t q, const uint64_t* pows, const uint64_t* vecs, size_t k,
+                                      const uint64_t* cols, size_t rows, size_t ncols, const uint64_t* idx, const uint8_t* salts32,
+                                      const uint8_t* paths32, uint32_t depth, const uint8_t* root32, const uint8_t* column_key32,
+                                      const uint8_t* leaf_key32, const uint8_t* node_key32, const uint64_t* rhos, int32_t* verdict, int64_t* first_bad) {
+    if (!c) return HL_B200_ERR_ARG;
+    if (!pows || !vecs || k == 0 || q == 0) return fail(c, HL_B200_ERR_ARG, "verify_opening: null or empty argument");
+    if (log_cols < 1 || log_cols > 16 || k > 0x7FFFu) return fail(c, HL_B200_ERR_ARG, "verify_opening: shape");
+    std::lock_guard<std::mutex> g(c->mu);
+    cudaSetDevice(c->device);
+    const size_t n = (size_t)1 << log_cols, nn = n * inv_rate, w = n + q;
+    u64 *d_vecs = nullptr, *d_data = nullptr, *d_pads = nullptr, *d_pows = nullptr;
+    hl_store* st = nullptr;
+    int rc = dev_alloc(c, (void**)&d_vecs, k * w * 16);
+    if (!rc) rc = dev_alloc(c, (void**)&d_data, 2 * k * n * 8);
+    if (!rc) rc = dev_alloc(c, (void**)&d_pads, 2 * k * q * 8);
+    if (!rc) rc = dev_alloc(c, (void**)&d_pows, nn * 8);
+    if (!rc) rc = h2d(c, d_vecs, vecs, k * w * 16);
+    if (!rc) rc = h2d(c, d_pows, pows, nn * 8);
+    if (!rc) {
+        const unsigned bx = (unsigned)((w + 255) / 256 < 64 ? (w + 255) / 256 : 64);
+        k_split_vectors<<<dim3(bx, (unsigned)k), 256, 0, c->stream>>>(d_vecs, (u32)k, (u32)n, (u32)q, d_data, d_pads);
+        c->stats.kernel_launches++;
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "verify_opening launch", e);
+    }
+    // the commitment's own encoder on the 2k rows; the shape checks (inv_rate a power of two, n + q <= nn) are its
+    if (!rc) rc = commit_resident(c, log_cols, inv_rate, d_data, 2 * k, d_pads, q, d_pows, nullptr, &st, nullptr);
+    if (!rc)
+        rc = verify_columns_locked(c, cols, rows, ncols, idx, salts32, paths32, depth, root32, column_key32, leaf_key32, node_key32, rhos, k, nullptr, st,
+                                   verdict, first_bad);
+    else if (st == nullptr)
+        cudaStreamSynchronize(c->stream);  // the copies above read the caller's memory
+    if (st) store_release(st);
+    dev_free(c, d_vecs, k * w * 16);
+    dev_free(c, d_data, 2 * k * n * 8);
+    dev_free(c, d_pads, 2 * k * q * 8);
+    dev_free(c, d_pows, nn * 8);
     return rc;
 }

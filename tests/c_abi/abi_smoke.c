@@ -54,6 +54,7 @@ int main(int argc, char** argv) {
     static_hash_fn f6 = hl_b200_hash_columns_static;
     verify_fn f7 = hl_b200_verify_columns;
     if (!f1 || !f2 || !f3 || !f4 || !f5 || !f6 || !f7) return 1;
+    if (hl_b200_verify_opening(NULL, 4, 2, 4, NULL, NULL, 0, NULL, 0, 0, NULL, NULL, NULL, 0, NULL, NULL, NULL, NULL, NULL, NULL, NULL) != HL_B200_ERR_ARG) return 6;
     if (hl_b200_verify_columns(NULL, NULL, 0, 0, NULL, NULL, NULL, 0, NULL, NULL, NULL, NULL, NULL, 0, NULL, NULL, NULL, NULL) != HL_B200_ERR_ARG) return 5;
     /* refusals that need no device */
     if (hl_b200_store_fold(NULL, NULL, 0, 0, NULL) != HL_B200_ERR_ARG) return 2;

@@ -104,7 +104,7 @@ def test_packed_rows_commit_to_the_same_leaves_tree_and_opening(dev, oracle, sha
 
 def test_block_shape_from_pageable_and_page_locked_packed_rows(dev, oracle):
     """2,504 rows of 2^14 words (the Llama-3-8B block `A` shape), int16-valued except eight full-width rows: the upload goes in
-    256-row pieces (82 MB of narrow bytes instead of 328 MB), from pageable memory through the context's staging buffers and from
+    wave-sized pieces (82 MB of narrow bytes instead of 328 MB), from pageable memory through the context's staging buffers and from
     page-locked memory directly; leaves and tree equal the wide call's."""
     import torch
     from intelligenceregulation_b200 import backend
@@ -135,6 +135,53 @@ def test_block_shape_from_pageable_and_page_locked_packed_rows(dev, oracle):
     assert (st_q.fold_rows_with_pads(rhos) == st_w.fold_rows_with_pads(rhos)).all()
     for s in (st_w, st_p, st_q):
         s.free()
+
+
+@pytest.mark.parametrize("rows", [593, 1185, 1777, 2369])
+def test_piecewise_upload_at_row_counts_around_the_piece_boundaries(dev, oracle, rows):
+    """The narrow upload goes in pieces of 1, 2, 3, 5, 8 waves (a wave = one row per SM), the pads of each piece and the salts with
+    them.  Row counts one above a piece boundary on a 148-SM device (4 x 148 + 1, 8 x 148 + 1, ..), where the last piece is a single
+    row: the packed call from page-locked and from pageable memory, the wide call, and a commitment of the same rows already on the
+    device (no pieces at all) give one tree, and the pads and widened rows left resident give the same opening combination."""
+    import torch
+
+    from intelligenceregulation_b200 import backend
+
+    o = oracle
+    log_cols, ir, q = 14, 2, 280
+    n, nn = 1 << log_cols, ir << log_cols
+    rng = np.random.default_rng(rows)
+    data = to_fp(rng.integers(-32768, 32768, rows * n)).reshape(rows, n)
+    data[::97] = rng.integers(0, P, (len(range(0, rows, 97)), n), dtype=np.uint64)
+    data = data.reshape(-1)
+    pads = rng.integers(0, P, rows * q, dtype=np.uint64)
+    pows, salts = o.coset_powers(7, nn), rng.integers(0, 256, (nn, 32), dtype=np.uint8)
+    tag = o.HashTag.for_profile("hashline-zk-mr1/b200-packed/1")
+    packed, widths = backend.pack_rows(data, rows)
+    # resident rows: one encoder launch, no pieces
+    dd, dp = torch.from_numpy(data.view(np.int64)).cuda(), torch.from_numpy(pads.view(np.int64)).cuda()
+    dw, ds = torch.from_numpy(pows.view(np.int64)).cuda(), torch.from_numpy(salts).cuda()
+    dl = torch.empty((2 * nn - 1) * 32, dtype=torch.uint8, device="cuda")
+    st_r = dev.commit_zk_dev(log_cols, ir, dd.data_ptr(), rows, dp.data_ptr(), q, dw.data_ptr(), tag.column)
+    st_r.merkle_dev(ds.data_ptr(), tag.leaf, tag.node, dl.data_ptr())
+    dev.ctx.sync()
+    want = dl.cpu().numpy().reshape(2 * nn - 1, 32)
+    st_w, _, levels_w = dev.try_commit_zk_tree(log_cols, ir, data, pads, pows, 15, tag.column, salts, tag.leaf, tag.node, want_leaves=False)
+    assert (levels_w == want).all()
+    st_p, _, levels_p = dev.try_commit_zk_packed(log_cols, ir, packed, widths, pads, pows, 15, tag.column, salts, tag.leaf, tag.node, want_leaves=False)
+    assert (levels_p == want).all()
+    pin = torch.empty(packed.size, dtype=torch.uint8, pin_memory=True)
+    pin.numpy()[...] = packed
+    pin_pads = torch.from_numpy(pads.view(np.int64)).pin_memory()
+    st_q, _, levels_q = dev.try_commit_zk_packed(log_cols, ir, pin.numpy(), widths, pin_pads.numpy().view(np.uint64), pows, 15, tag.column, salts, tag.leaf, tag.node,
+                                                  want_leaves=False)
+    assert (levels_q == want).all()
+    rhos = rng.integers(0, P, (2, rows, 2), dtype=np.uint64)
+    ref = st_r.fold_rows_with_pads(rhos)
+    for s in (st_w, st_p, st_q):
+        assert (s.fold_rows_with_pads(rhos) == ref).all()
+        s.free()
+    st_r.free()
 
 
 def test_refusals(dev, oracle):

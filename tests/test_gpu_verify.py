@@ -35,9 +35,9 @@ def device_checker(dev, case_params, max_log, o, form):
         cols = np.stack([np.asarray(c, dtype=np.uint64) for c in cols])
         salts = np.frombuffer(b"".join(salts), dtype=np.uint8).reshape(len(idx), 32)
         paths = np.frombuffer(b"".join(b"".join(p) for p in paths), dtype=np.uint8).reshape(len(idx), -1, 32)
-        if form == "store":
+        if form in ("store", "one_call"):
             v = dev.check_opening_columns(case_params.log_cols, case_params.inv_rate, o.coset_powers(7, case_params.enc_cols), max_log, cols, idx, salts, paths,
-                                          root, tag.column, tag.leaf, tag.node, rhos, vecs)
+                                          root, tag.column, tag.leaf, tag.node, rhos, vecs, one_call=form == "one_call")
             assert v is not None, dev.ctx.declines
             return [int(x) for x in v]
         wants = np.array([[[int(e[0][int(j)]), int(e[1][int(j)])] for j in idx] for e in encoded_vecs], dtype=np.uint64)
@@ -71,7 +71,7 @@ def test_l5_single_column_verdicts_on_the_device(dev, oracle, l5):
     assert seen == [72, 12]
 
 
-@pytest.mark.parametrize("form", ["wants", "store"])
+@pytest.mark.parametrize("form", ["wants", "store", "one_call"])
 def test_l5_recorded_openings_verify_with_the_device_as_column_checker(dev, oracle, l5, form):
     o = oracle
     for case in l5_util.pcs_cases(o, l5):
@@ -126,6 +126,8 @@ def test_block_sized_opening_with_every_kind_of_tampered_column(dev, oracle):
     paths = np.stack([np.stack([np.frombuffer(x, dtype=np.uint8) for x in o.merkle_path(levels, nn, int(j))]) for j in idx])
     sl = np.stack([salts[int(j)] for j in idx])
     v = dev.check_opening_columns(log_cols, ir, pows, 18, cols, idx, sl, paths, root, tag.column, tag.leaf, tag.node, rhos, vecs)
+    assert v is not None and (v == 0).all()
+    v = dev.check_opening_columns(log_cols, ir, pows, 18, cols, idx, sl, paths, root, tag.column, tag.leaf, tag.node, rhos, vecs, one_call=False)
     assert v is not None and (v == 0).all()
     # the host body on a sample of the honest columns (the whole of it takes a pure-Python minute)
     enc_vecs = [(o.encode_row_zk(x[:n, 0], x[n:, 0], pows, 18), o.encode_row_zk(x[:n, 1], x[n:, 1], pows, 18)) for x in vecs]
