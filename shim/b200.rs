@@ -42,6 +42,10 @@ extern "C" {
                                 pads: *const u64, q: usize, pows: *const u64, max_log: u32, key32: *const u8, salts32: *const u8,
                                 leaf_key32: *const u8, node_key32: *const u8, store: *mut *mut HlStore, leaves32: *mut u8,
                                 levels_out: *mut u8) -> c_int;
+    fn hl_b200_verify_opening(ctx: *mut HlCtx, log_cols: u32, inv_rate: u32, q: usize, pows: *const u64, vecs: *const u64, k: usize, cols: *const u64,
+                              rows: usize, ncols: usize, idx: *const u64, salts32: *const u8, paths32: *const u8, depth: u32, root32: *const u8,
+                              column_key32: *const u8, leaf_key32: *const u8, node_key32: *const u8, rhos: *const u64, verdict: *mut i32,
+                              first_bad: *mut i64) -> c_int;
     fn hl_b200_verify_columns(ctx: *mut HlCtx, cols: *const u64, rows: usize, ncols: usize, idx: *const u64, salts32: *const u8,
                               paths32: *const u8, depth: u32, root32: *const u8, column_key32: *const u8, leaf_key32: *const u8,
                               node_key32: *const u8, rhos: *const u64, k: usize, wants: *const u64, vec_store: *const HlStore,
@@ -238,28 +242,18 @@ pub enum ColumnVerdict {
     Disagrees { column: usize, vector: usize },
 }
 
-/// The map over the opened columns of `verify_zk_tagged` (pcs.rs:1282-1331) on the device.  `vecs`: the group vectors then the
-/// proximity vector, `n + q` entries each; `rhos`: their combined row weights in the same order; the caller has already checked
-/// path lengths, column lengths and `j == want_j`.  `Ok(None)`: every column passes; `Ok(Some(v))`: the first failing column;
-/// `Err`: the device declined and the host body runs.
+/// The map over the opened columns of `verify_zk_tagged` (pcs.rs:1282-1331) on the device, the encoding of the clear vectors
+/// included.  `vecs`: the group vectors then the proximity vector, `n + q` entries each; `rhos`: their combined row weights in the
+/// same order; the caller has already checked path lengths, column lengths and `j == want_j`.  `Ok(None)`: every column passes;
+/// `Ok(Some(v))`: the first failing column; `Err`: the device declined and the host body runs.
+/// (A caller that keeps a device commitment of the vectors' rows uses `hl_b200_verify_columns` with that store instead.)
 #[allow(clippy::too_many_arguments)]
-pub fn verify_columns(p: &PcsParams, q: usize, pows: &[Fp], ntt: &NttTables, root: &Digest, keys: [Option<&[u8; 32]>; 3], rhos: &[Vec<Fp2>],
-                      vecs: &[&Vec<Fp2>], columns: &[(usize, Vec<Fp>, [u8; 32], Vec<Digest>)]) -> Result<Option<ColumnVerdict>, String> {
-    let n = p.cols();
+pub fn verify_columns(p: &PcsParams, q: usize, pows: &[Fp], root: &Digest, keys: [Option<&[u8; 32]>; 3], rhos: &[Vec<Fp2>], vecs: &[&Vec<Fp2>],
+                      columns: &[(usize, Vec<Fp>, [u8; 32], Vec<Digest>)]) -> Result<Option<ColumnVerdict>, String> {
     let rows = columns.first().map(|c| c.1.len()).unwrap_or(0);
-    if rows == 0 || vecs.len() != rhos.len() {
-        return Err("b200 verify: empty opening".into());
+    if !enabled() || rows == 0 || vecs.len() != rhos.len() {
+        return Err("b200 verify: nothing to do on the device".into());
     }
-    // 2 (G + 1) base rows: re and im of every clear vector apart (pcs.rs:1287-1296)
-    let mut data = Vec::with_capacity(2 * vecs.len() * n);
-    let mut pads = Vec::with_capacity(2 * vecs.len() * q);
-    for v in vecs {
-        for part in 0..2 {
-            data.extend(v[..n].iter().map(|x| if part == 0 { x.c0 } else { x.c1 }));
-            pads.extend(v[n..].iter().map(|x| if part == 0 { x.c0 } else { x.c1 }));
-        }
-    }
-    let (store, _) = B200Backend.zk(p, &data, &pads, pows, ntt, None).ok_or_else(|| "b200 verify: the vectors' encoding was declined".to_string())?;
     let depth = columns[0].3.len();
     let mut cols = Vec::with_capacity(columns.len() * rows);
     let mut idx = Vec::with_capacity(columns.len());
@@ -273,14 +267,15 @@ pub fn verify_columns(p: &PcsParams, q: usize, pows: &[Fp], ntt: &NttTables, roo
             paths.extend_from_slice(d);
         }
     }
-    let flat: Vec<Fp2> = rhos.iter().flat_map(|r| r.iter().copied()).collect();
+    let flat_v: Vec<Fp2> = vecs.iter().flat_map(|v| v.iter().copied()).collect();
+    let flat_r: Vec<Fp2> = rhos.iter().flat_map(|r| r.iter().copied()).collect();
     let kp = |k: Option<&[u8; 32]>| k.map(|x| x.as_ptr()).unwrap_or(std::ptr::null());
     let mut verdict = vec![0i32; columns.len()];
     let mut first: i64 = -1;
     status(unsafe {
-        hl_b200_verify_columns(ctx(), words(&cols), rows, columns.len(), idx.as_ptr(), salts.as_ptr(), paths.as_ptr(), depth as u32, root.as_ptr(),
-                               kp(keys[0]), kp(keys[1]), kp(keys[2]), flat.as_ptr() as *const u64, rhos.len(), std::ptr::null(), store.h,
-                               verdict.as_mut_ptr(), &mut first)
+        hl_b200_verify_opening(ctx(), p.log_cols, p.inv_rate as u32, q, words(pows), flat_v.as_ptr() as *const u64, vecs.len(), words(&cols), rows,
+                               columns.len(), idx.as_ptr(), salts.as_ptr(), paths.as_ptr(), depth as u32, root.as_ptr(), kp(keys[0]), kp(keys[1]),
+                               kp(keys[2]), flat_r.as_ptr() as *const u64, verdict.as_mut_ptr(), &mut first)
     })?;
     Ok(if first < 0 {
         None
