@@ -168,6 +168,7 @@ static int verify_columns_locked(hl_ctx* c, const uint64_t* cols, size_t rows, s
         for (size_t i = 0; i < ncols; i++)
             if (verdict[i]) { *first_bad = (int64_t)i; break; }
     }
+    if (rc) cudaStreamSynchronize(c->stream);  // copies already queued read the caller's memory: none outlives the call
     dev_free(c, d_cols, cb); dev_free(c, d_mat, cb); dev_free(c, d_idx, ncols * 8); dev_free(c, d_salts, ncols * 32);
     dev_free(c, d_paths, pb); dev_free(c, d_root, 32); dev_free(c, d_leaves, ncols * 32);
     if (d_cvs) dev_free(c, d_cvs, cvs_bytes);
@@ -221,8 +222,7 @@ extern "C" int hl_b200_verify_opening(hl_ctx* c, uint32_t log_cols, uint32_t inv
     if (!rc)
         rc = verify_columns_locked(c, cols, rows, ncols, idx, salts32, paths32, depth, root32, column_key32, leaf_key32, node_key32, rhos, k, nullptr, st,
                                    verdict, first_bad);
-    else if (st == nullptr)
-        cudaStreamSynchronize(c->stream);  // the copies above read the caller's memory
+    if (rc) cudaStreamSynchronize(c->stream);  // a refusal on the way: the copies above may still be reading the caller's memory
     if (st) store_release(st);
     dev_free(c, d_vecs, k * w * 16);
     dev_free(c, d_data, 2 * k * n * 8);
