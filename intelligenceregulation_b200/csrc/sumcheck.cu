@@ -936,10 +936,13 @@ u32 sc_ir_blocks(const IrDev& p, u32 half, int degree, int sm_count) {
     return b > cap ? cap : b;
 }
 
-// The single-CTA tail pays off only while a round's pairs fit its warps a few times over.
+// The single-CTA tail pays off only while a round's pairs fit its warps a few times over.  Thread form (polynomials of a few units):
+// a round as three launches costs about 20 us whatever its size, a tail round about 12 us plus 3.4 us per (pair, point) item
+// and thread; measured over a block's 23 slot sumchecks, tail from 4,096 entries: 15.97 ms, 1,024: 15.16, 512: 15.06, 256: 14.97,
+// 128: 15.21.  Pair form: 16 / 32 / 64 / 128 entries gave 15.77 / 15.97 / 15.85 / 16.28 ms (inside the run-to-run spread but the last).
 u32 sc_ir_tail_len(const IrDev& p, int degree) {
     (void)degree;
-    return ir_pair_capable(p) ? 32u : p.n_units >= 4 ? 1024u : 4096u;
+    return ir_pair_capable(p) ? 32u : 256u;
 }
 
 cudaError_t sc_round_ir(const IrDev& p, int k, const u64* tables, size_t stride, u32 half, int degree, int eval_one, u64* partials,
