@@ -193,8 +193,9 @@ int rounds_build(hl_ctx* c, int poly, size_t k, uint32_t n_vars, uint32_t degree
         cudaError_t e = cudaMemsetAsync(r->d_state, 0, sizeof(hlk::ScState), c->stream);
         if (e != cudaSuccess) rc = fail(c, HL_B200_ERR_DEVICE, "state clear", e);
     }
-    if (!rc && gen && gen->entry && gen->entry->n_tables == k && gen->entry->n_cfo == gen->cfo.size()) {
-        // the graph has a generated kernel: its coefficients by occurrence, and which tables are base-valued right now
+    if (!rc && c->slot_kernels && gen && gen->entry && gen->entry->n_tables == k && gen->entry->n_cfo == gen->cfo.size()) {
+        // the generated kernels are switched on and the graph has one: its coefficients by occurrence, and which tables are base-valued
+        // right now (a scan of every table: not paid while the switch is off)
         r->gen = gen->entry;
         rc = dev_alloc(c, (void**)&r->d_cfo, (size_t)(gen->cfo.size() ? gen->cfo.size() : 1) * 16);
         if (!rc) rc = dev_alloc(c, (void**)&r->d_nonbase, 8);
