@@ -245,7 +245,9 @@ int hl_b200_rng_fill_dev(hl_ctx* ctx, const uint8_t* key32, uint64_t first_word,
  *                  Every address the maps can form is checked against the rows before the launch.
  * base_check != 0 declares the table base-valued; tables_flush (and rounds_from_tables) answer
  * HL_B200_ERR_MISMATCH if a word of such a table has a non-zero imaginary part (metal.rs:2649-2665).
- * The map arrays are read during the call when they are ordinary (pageable) host memory.
+ * tables_eq and tables_plane PLAN a table (MetalTables::plan_eq / plan_plane): the maps are copied during the call, and every planned
+ * table is written by one launch when the set is flushed, read or handed to an evaluator.  The commitment (or the device rows) a
+ * planned plane reads must still be there then; a freed store is refused at that point (HL_B200_ERR_ARG), nothing is launched.
  * rounds_from_tables[_ir] takes the set over on success (the handle stays valid but empty; free it). */
 typedef struct hl_tables hl_tables;
 int hl_b200_tables_new(hl_ctx* ctx, size_t k, uint32_t n_vars, hl_tables** out);

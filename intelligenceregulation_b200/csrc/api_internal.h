@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 
 #include <map>
+#include <set>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -37,6 +38,7 @@ struct hl_ctx {
     size_t arena_off = 0;
     int* d_wp_flag = nullptr;  // the witness products' status word: zero between calls
     bool wp_attr = false;      // the product kernel's shared-memory size has been raised on this device
+    std::set<const struct hl_store*> stores;  // the live commitment stores (a planned slot table that reads one checks it is still there when it is built)
     size_t alloc_live = 0;   // bytes handed out and not yet returned
     size_t alloc_cap = 0;    // 0 = none; a host-side failure-injection cap (mod.rs:121 set_alloc_cap_for_test)
 };

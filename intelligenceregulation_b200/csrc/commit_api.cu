@@ -264,6 +264,7 @@ int check_shape(hl_ctx* c, uint32_t log_cols, uint32_t inv_rate, size_t rows, si
 
 void free_store(hl_store* st) {
     hl_ctx* c = st->ctx;
+    c->stores.erase(st);
     if (st->owns_inputs) {
         dev_free(c, st->d_data, (size_t)st->rows * st->n() * 8);
         dev_free(c, st->d_pads, (size_t)st->rows * st->q * 8);
@@ -308,6 +309,7 @@ int commit_host(hl_ctx* c, const Shape& s, const HostRows& data, const uint64_t*
     if (d_levels) dev_free(c, d_levels, (2 * nn - 1) * 32);
     if (rc) { cudaStreamSynchronize(c->copy_stream); cudaStreamSynchronize(c->stream); free_store(st); return rc; }
     c->stats.commits++;
+    c->stores.insert(st);
     *store = st;
     return HL_B200_OK;
 }
@@ -337,6 +339,7 @@ int hlapi::commit_resident(hl_ctx* c, u32 log_cols, u32 inv_rate, const u64* d_d
     }
     if (rc) { cudaStreamSynchronize(c->stream); free_store(st); return rc; }
     c->stats.commits++;
+    c->stores.insert(st);
     *store = st;
     return HL_B200_OK;
 }

@@ -189,6 +189,7 @@ int hl_b200_mask_commit(hl_ctx* c, uint32_t log_msg, uint32_t log_dom, const uin
     if (cvs) dev_free(c, cvs, cvs_bytes);
     if (rc) { store_release(st); return rc; }
     c->stats.commits++;
+    c->stores.insert(st);
     *store = st;
     return HL_B200_OK;
 }

@@ -32,6 +32,7 @@ struct TabDesc {
     u64 off_a, off_b;          // 64-bit pool: eq hi / lo, or plane eqf / slices
     u64 off_lo, off_hi, off_zb;  // 32-bit pool: plane inv_lo / inv_hi / zbits
     const u64* rows;           // plane: the committed data, flat
+    const hl_store* store;     // plane: the commitment those rows belong to, or NULL for caller-owned device rows (host use only)
 };
 
 // The eq and plane calls only PLAN a table (MetalTables::plan_eq / plan_plane do the same, gpu/metal.rs): the maps are copied
@@ -156,6 +157,11 @@ void hl_tables_shape(hl_tables* t, hl_ctx** c, size_t* k, uint32_t* n_vars) {
 static int launch_planned(hl_tables* t) {
     if (t->plan.empty()) return HL_B200_OK;
     hl_ctx* c = t->ctx;
+    for (const TabDesc& d : t->plan)
+        if (d.kind == 1 && d.store && !c->stores.count(d.store)) {  // the rows are gone: nothing is launched over them
+            t->plan.clear(); t->pool64.clear(); t->pool32.clear();
+            return fail(c, HL_B200_ERR_ARG, "tables: a planned plane's commitment was freed before the set was built");
+        }
     TabDesc* d_desc = nullptr;
     u64* d_p64 = nullptr;
     u32* d_p32 = nullptr;
@@ -282,6 +288,7 @@ int hl_b200_tables_plane(hl_tables* t, size_t i, const hl_store* store, const ui
     d.kind = 1; d.table = (u32)i; d.xlo = xlo; d.nz = nz; d.ns = ns; d.used = used; d.base_check = base_check;
     d.one_slice = ns == 1 && slices[1] == 1 && slices[2] == 0;
     d.rows = reinterpret_cast<const u64*>(d_rows);
+    d.store = store;
     d.off_lo = t->pool32.size();
     t->pool32.insert(t->pool32.end(), inv_lo, inv_lo + nlo);
     d.off_hi = t->pool32.size();

@@ -124,6 +124,34 @@ def test_refusals(dev, oracle, committed):
     t.free()
 
 
+def test_a_planned_plane_whose_commitment_was_freed_is_refused_not_launched(dev, oracle):
+    """The eq and plane calls only plan a table; the launch comes when the set is flushed.  A commitment freed in between is found
+    on the host: the flush is refused, nothing is launched over the freed rows, and the set takes new plans afterwards."""
+    from intelligenceregulation_b200 import backend
+
+    data = np.random.default_rng(7).integers(0, T.P, size=64 << 8, dtype=np.uint64)
+    store, _ = dev.try_commit(8, 2, data, 10)
+    coords, slices = T.random_plane(43, 10, 0, 0, 1, data.size)
+    t = backend.B200Tables(dev.ctx, 2, 10)
+    t.plan_plane(0, store, coords, slices)
+    point = oracle.ZkRng(2, b"e").fp2_vec(10)
+    t.plan_eq(1, point, 0)
+    store.free()
+    launches = dev.ctx.stats()["kernel_launches"]
+    with pytest.raises(backend.DeviceError):
+        t.flush()
+    assert dev.ctx.stats()["kernel_launches"] == launches
+    # the refused plan is gone: the set builds what is planned next
+    store2, _ = dev.try_commit(8, 2, data, 10)
+    t.plan_plane(0, store2, coords, slices)
+    t.plan_eq(1, point, 0)
+    t.flush()
+    assert (t.read(0) == oracle.priv_table(coords, slices, data, 10)).all()
+    assert (t.read(1) == oracle.eq_cube(point, 10, 0)).all()
+    t.free()
+    store2.free()
+
+
 def test_page_locked_inputs_may_be_overwritten_when_the_call_returns(dev, oracle):
     """`tables_put`, `tables_eq` and `tables_plane` return before their copies run.  From page-locked caller memory such a
     copy reads its source when the DMA engine gets to it, so the library must have taken the bytes by then: every input
