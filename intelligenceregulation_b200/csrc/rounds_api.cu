@@ -77,6 +77,7 @@ int launch_round(hl_rounds* r, int eval_one, int fs, int use_claim, int recover,
     const u32 half = (u32)(r->len / 2);
     const bool is_ir = r->poly == hlk::POLY_IR;
     u32 nb = is_ir ? hlk::sc_ir_blocks(r->ir, half, (int)r->degree, c->sm_count) : hlk::sc_round_blocks(half, c->sm_count);
+    if (nb > r->max_blocks) return fail(c, HL_B200_ERR_DEVICE, "round launch: more partial rows than the buffer holds");  // the two grid rules agree by construction
     cudaError_t e;
     if (is_ir && r->gen && c->slot_kernels) {
         // the generated kernel of this graph: the first-round typing while the tables it reads as base words are base-valued
