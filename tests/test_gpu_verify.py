@@ -178,3 +178,18 @@ def test_refusals(dev):
     # no weights at all: the hash and path part alone
     v = dev.ctx.verify_columns(cols, idx, salts, paths, bytes(32), None, None, None)
     assert (v == 1).all()
+    # the one-call form: a position beyond the encoding, and a pad count the encoder cannot take, are declines (None), nothing is compared
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle"))
+    import hl_oracle as o
+    pows = o.coset_powers(7, 32)
+    vecs = np.zeros((1, 16 + 4, 2), dtype=np.uint64)
+    declines = len(dev.ctx.declines)
+    far = np.array([5, 32], dtype=np.uint64)
+    assert dev.check_opening_columns(4, 2, pows, 6, cols, far, salts, paths[:, :1], bytes(32), None, None, None, rhos, vecs) is None
+    wide = np.zeros((1, 16 + 17, 2), dtype=np.uint64)  # n + q > nn
+    assert dev.check_opening_columns(4, 2, pows, 6, cols, idx, salts, paths[:, :1], bytes(32), None, None, None, rhos, wide) is None
+    assert len(dev.ctx.declines) == declines + 2
+    # and the same shapes accepted: every column fails its (all-zero) path, verdict 1
+    v = dev.check_opening_columns(4, 2, pows, 6, cols, idx, salts, paths[:, :1], bytes(32), None, None, None, rhos, vecs)
+    assert v is not None and (v == 1).all()
