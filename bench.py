@@ -879,11 +879,12 @@ def block_device_trace(line: dict, extras: dict, commit_h_ms: float) -> dict:
 
 D55_BLOCKS = 8
 # S1 of the bench's D55 run (below) proved by ONE process; every world size must join to the same state (run_fork.rs:1819-1827)
-D55_EXPECTED_S1 = "580eed19e1f6e23ffa6abdebff52bb1c09155fc84876e64d894e43aed53008cf"
+D55_EXPECTED_S1 = "5af4ea9224dd48e403b182d2267a79b80245dd0e8ce75e10d7a9a64ccfc3e848"
 
 
 def d55_leg(dev, backend, rank: int, world: int, col_key, leaf_key, node_key) -> dict:
-    """A D55 commit-fork-join run with the forks' work on the device: D55_BLOCKS blocks, block k proved by rank k mod world (a
+    """A D55 commit-fork-join run with its work on the device: rank 0 commits the boundary planes and broadcasts their roots;
+    D55_BLOCKS blocks, block k proved by rank k mod world (a
     hiding commitment with its tree, an opening and a masked sumcheck with the device Fiat-Shamir step per fork:
     d55.device_fork), the fixed-size join records all-gathered over NCCL, the join replayed on every rank.  Returns S1 and the
     wall time; S1 does not depend on the world size."""
@@ -896,8 +897,21 @@ def d55_leg(dev, backend, rank: int, world: int, col_key, leaf_key, node_key) ->
     pows = coset_powers(nn)
     header = d55.RunHeader(WORK["profile"].encode(), col_key, D55_BLOCKS, (128, 4096, 14336, 32, 8, 128), b"\x01" * 64, b"\x02" * 32, b"bench", b"\x03" * 16,
                            b"\x04" * 32)
-    roots = [bytes([16 + k]) * 32 for k in range(D55_BLOCKS - 1)]  # boundary roots: rank 0 commits them in a real run; public here
     digs = [bytes([64 + k]) * 32 for k in range(D55_BLOCKS)]
+    brows = 32 + 2 * 2 + 2  # a boundary plane: 32 data rows, a reserved row pair per claim site, a proximity pair (boundary.rs:184-188)
+
+    def commit_plane(b):  # rank 0 only: a few rows, so the encoder's one-CTA-per-(row, residue) form
+        salts = (splitmix_fp(0xD5C00 + b, nn * 4).view(np.uint8)).reshape(nn, 32)
+        st, _, levels = dev.try_commit_zk_tree(lc, ir, witness_words(0xD5A00 + b, brows, 1 << lc), splitmix_fp(0xD5B00 + b, brows * q), pows, lc + 1, col_key, salts,
+                                               leaf_key, node_key, want_leaves=False)
+        st.free()
+        return bytes(levels[-1])
+
+    def bcast(buf):
+        nbytes = 1 + 32 * (D55_BLOCKS - 1)
+        t = torch.frombuffer(bytearray(buf), dtype=torch.uint8).cuda() if rank == 0 else torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+        dist.broadcast(t, src=0)
+        return t.cpu().numpy().tobytes()
 
     def block(k):
         return dict(log_cols=lc, inv_rate=ir, data=witness_words(0xD5500 + k, rows, 1 << lc), pads=splitmix_fp(0xD5600 + k, rows * q),
@@ -915,12 +929,14 @@ def d55_leg(dev, backend, rank: int, world: int, col_key, leaf_key, node_key) ->
         dist.barrier()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
-    s1 = d55.run_forks(header, roots, [40] * (D55_BLOCKS - 1), [14] * (D55_BLOCKS - 1), digs,
+    roots = d55.commit_boundaries(commit_plane, D55_BLOCKS, rank, world, bcast if world > 1 else None)
+    s1 = d55.run_forks(header, roots, [brows] * (D55_BLOCKS - 1), [lc] * (D55_BLOCKS - 1), digs,
                        lambda k, tr: d55.device_fork(dev, backend, k, tr, block(k)), rank, world, gather if world > 1 else None)
     wall = time.perf_counter() - t0
     out = {"blocks": D55_BLOCKS, "s1": s1.state.hex(), "counter": s1.counter, "wall_ms": wall * 1e3,
            "fork": f"commit {rows} x 2^{lc} -> 2^{lc + 1} with tree, opening (1 combination, 8 columns), masked zero-check sumcheck of 2^{nv} points",
-           "exchange": "one all-gather of fixed-size join records over NCCL" if world > 1 else "none (one process)"}
+           "boundaries": f"{D55_BLOCKS - 1} planes of {brows} x 2^{lc} committed on rank 0, their roots in one broadcast",
+           "exchange": "one broadcast of the boundary roots, one all-gather of fixed-size join records, over NCCL" if world > 1 else "none (one process)"}
     if D55_EXPECTED_S1 is not None:
         assert out["s1"] == D55_EXPECTED_S1, "the D55 join state differs from the one-process value"
         out["s1_equals_one_process_value"] = True

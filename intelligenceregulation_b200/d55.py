@@ -198,6 +198,28 @@ def _failure_record(k: int, text: str, claim_cap: int) -> bytes:
     return struct.pack("<QQQQ", FAILED_K, k, len(msg), 0) + msg.ljust(32 + 2 * claim_cap, b"\0")
 
 
+def commit_boundaries(commit_plane: Callable[[int], bytes], blocks: int, rank: int = 0, world: int = 1,
+                      broadcast: Optional[Callable[[Optional[bytes]], bytes]] = None) -> List[bytes]:
+    """Phase 1 of a fork run (run_fork.rs:1636-1676): rank 0 commits the L - 1 boundary planes - `commit_plane(b)` returns the
+    32-byte root of the plane between blocks b and b + 1 - and the roots reach every rank as ONE broadcast of 32 (L - 1) bytes
+    (`broadcast(buffer on rank 0 | None elsewhere) -> buffer`).  Every rank then derives the same S0 from the header and the roots.
+    A commitment that fails on rank 0 still takes part in the broadcast, as all-ones roots with a marker, and every rank raises."""
+    n = blocks - 1
+    buf = None
+    if rank == 0:
+        try:
+            roots = [commit_plane(b) for b in range(n)]
+            assert all(len(r) == 32 for r in roots)
+            buf = b"\x00" + b"".join(roots)
+        except Exception as e:  # noqa: BLE001  (reported to every rank below)
+            buf = (b"\x01" + f"{type(e).__name__}: {e}".encode("utf-8", "replace")).ljust(1 + 32 * n, b"\0")[: 1 + 32 * n]
+    if world > 1 and broadcast is not None:
+        buf = broadcast(buf)
+    if buf[0] != 0:
+        raise ForkFailed([(0, -1, bytes(buf[1:]).rstrip(b"\0").decode("utf-8", "replace"))])
+    return [bytes(buf[1 + 32 * b: 33 + 32 * b]) for b in range(n)]
+
+
 def run_forks(header: RunHeader, roots: Sequence[bytes], rows: Sequence[int], log_cols: Sequence[int], block_digests: Sequence[bytes],
               prove_fork: Callable[[int, HostTranscript], JoinRecord], rank: int = 0, world: int = 1,
               all_gather: Optional[Callable[[bytes], List[bytes]]] = None, claim_cap: int = 4096) -> HostTranscript:

@@ -121,10 +121,22 @@ dist.init_process_group("gloo")
 rank, world = dist.get_rank(), dist.get_world_size()
 h = T._header(d55, bytes(range(32)))
 roots, rows, logs, digs = T._inputs()
-# rank 0 "commits" and broadcasts the roots (32 bytes each)
-rt = torch.tensor(list(b"".join(roots)) if rank == 0 else [0] * (32 * len(roots)), dtype=torch.uint8)
-dist.broadcast(rt, 0)
-roots = [bytes(rt[32 * i:32 * i + 32].tolist()) for i in range(len(roots))]
+# rank 0 "commits" the boundary planes; the roots reach the other rank in one broadcast (d55.commit_boundaries)
+def commit_plane(b):
+    if os.environ.get("HL_FAIL_BOUNDARY") == str(b):
+        raise RuntimeError("injected boundary failure")
+    return roots[b]
+def bcast(buf):
+    n = 1 + 32 * (h.blocks - 1)
+    t = torch.tensor(list(buf) if rank == 0 else [0] * n, dtype=torch.uint8)
+    dist.broadcast(t, 0)
+    return bytes(t.tolist())
+try:
+    roots = d55.commit_boundaries(commit_plane, h.blocks, rank, world, bcast)
+except d55.ForkFailed as e:
+    open(os.path.join(os.environ["HL_OUT"], "rank%d.txt" % rank), "w").write("FAILED " + str(e))
+    dist.destroy_process_group()
+    sys.exit(0)
 def gather(buf):
     mine = torch.tensor(list(buf), dtype=torch.uint8)
     out = [torch.empty_like(mine) for _ in range(world)]
@@ -206,3 +218,20 @@ def test_a_failed_fork_in_one_process_raises_fork_failed():
     with pytest.raises(d55.ForkFailed) as ei:
         d55.run_forks(h, roots, rows, logs, digs, prove)
     assert ei.value.failures[0][:2] == (0, 2) and "zero LogUp denominator" in ei.value.failures[0][2]
+
+
+def test_a_boundary_commitment_that_fails_on_rank_0_ends_every_rank(tmp_path):
+    """Phase 1: rank 0 commits the boundary planes and broadcasts the roots.  A commitment that raises (a host-side failure) still
+    takes part in the broadcast, so rank 1 does not wait for roots that never come; both ranks end with the same text."""
+    texts = _run_two_ranks(tmp_path, {"HL_FAIL_BOUNDARY": "1"})
+    assert texts[0] == texts[1] and texts[0].startswith("FAILED D55: block -1 on rank 0: RuntimeError: injected boundary failure")
+
+
+def test_boundary_roots_in_one_process():
+    from intelligenceregulation_b200 import d55
+
+    roots = [bytes([b]) * 32 for b in range(4)]
+    assert d55.commit_boundaries(lambda b: roots[b], 5) == roots
+    assert d55.commit_boundaries(lambda b: roots[b], 1) == []
+    with pytest.raises(d55.ForkFailed):
+        d55.commit_boundaries(lambda b: (_ for _ in ()).throw(ValueError("no plane")), 3)

@@ -1,6 +1,6 @@
-"""D55 commit-fork-join with the forks' work on the device (run_fork.rs:1617-1860): S1 after the join is the same whether one
-process proves every block or the blocks are spread over ranks, one GPU each, with the join records exchanged by an NCCL
-all-gather.  The one-process case runs on any GPU box; the multi-rank case needs at least two GPUs and is skipped otherwise."""
+"""D55 commit-fork-join with its work on the device (run_fork.rs:1617-1860): rank 0 commits the boundary planes and the roots
+reach the other ranks in one broadcast; S1 after the join is the same whether one process proves every block or the blocks are
+spread over ranks, one GPU each, with the join records exchanged by an NCCL all-gather.  The one-process case runs on any GPU box; the multi-rank case needs at least two GPUs and is skipped otherwise."""
 import os
 import subprocess
 import sys
@@ -32,11 +32,22 @@ def block_inputs(k):
                 tables=rng.integers(0, P, (4, 1 << n, 2), dtype=np.uint64), mask=rng.integers(0, P, ((n + 1) * 3 + 2, 2), dtype=np.uint64))
 
 
-def run(rank=0, world=1, all_gather=None, fail_block=None):
+def boundary_plane(dev, b):
+    """the commitment of the plane between blocks b and b + 1: 38 rows of 2^10 words (32 data rows, two reserved row pairs, a
+    proximity pair: boundary.rs:184-188), its salted root"""
+    blk = block_inputs(100 + b)
+    rows = 38
+    st, _, levels = dev.try_commit_zk_tree(blk["log_cols"], blk["inv_rate"], blk["data"][: rows << blk["log_cols"]], blk["pads"][: rows * 16], blk["pows"], 11,
+                                           blk["keys"][0], blk["salts"], blk["keys"][1], blk["keys"][2], want_leaves=False)
+    st.free()
+    return bytes(levels[-1])
+
+
+def run(rank=0, world=1, all_gather=None, fail_block=None, broadcast=None):
     from intelligenceregulation_b200 import backend, d55
 
     dev = backend.B200Backend(device=rank if world > 1 else 0)
-    roots = [bytes([10 + k]) * 32 for k in range(BLOCKS - 1)]
+    roots = d55.commit_boundaries(lambda b: boundary_plane(dev, b), BLOCKS, rank, world, broadcast)
     digs = [bytes([50 + k]) * 32 for k in range(BLOCKS)]
 
     def prove(k, tr):
@@ -45,7 +56,7 @@ def run(rank=0, world=1, all_gather=None, fail_block=None):
         return d55.device_fork(dev, backend, k, tr, block_inputs(k))
 
     try:
-        return d55.run_forks(header(d55), roots, [40] * (BLOCKS - 1), [14] * (BLOCKS - 1), digs, prove, rank, world, all_gather)
+        return d55.run_forks(header(d55), roots, [38] * (BLOCKS - 1), [10] * (BLOCKS - 1), digs, prove, rank, world, all_gather)
     finally:
         dev.ctx.close()
 
@@ -74,7 +85,12 @@ def gather(buf):
     dist.all_gather_into_tensor(out, mine)
     host = bytes(out.cpu().tolist())
     return [host[i * len(buf):(i + 1) * len(buf)] for i in range(world)]
-s1 = T.run(rank, world, gather)
+def bcast(buf):
+    n = 1 + 32 * (T.BLOCKS - 1)
+    t = torch.tensor(list(buf), dtype=torch.uint8, device="cuda") if rank == 0 else torch.empty(n, dtype=torch.uint8, device="cuda")
+    dist.broadcast(t, 0)
+    return bytes(t.cpu().tolist())
+s1 = T.run(rank, world, gather, broadcast=bcast)
 open(os.path.join(os.environ["HL_OUT"], "rank%d.txt" % rank), "w").write("%s %d" % (s1.state.hex(), s1.counter))
 dist.barrier()
 dist.destroy_process_group()
