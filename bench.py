@@ -1083,6 +1083,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
         leaves, levels = step_e2e()
     barrier()
     e2e_own = time.perf_counter() - t0
+    parts_timed = list(e2e_parts)  # this leg's parts only: the 64-bit comparison below runs through the same function
     e2e_s = max_over_ranks(e2e_own)
     clocks = sampler.stop()
     s1 = dev.ctx.stats()
@@ -1114,7 +1115,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     del d_packed
     per_rank = None
     if world > 1:  # every rank's own wall time and upload time: the ranks share the host's memory and PCIe root complexes
-        t = torch.tensor([e2e_own * 1e3 / args.steps, h2d_only_ms] + [x * 1e3 / args.steps for x in e2e_parts], dtype=torch.float64, device="cuda")
+        t = torch.tensor([e2e_own * 1e3 / args.steps, h2d_only_ms] + [x * 1e3 / args.steps for x in parts_timed], dtype=torch.float64, device="cuda")
         allt = torch.empty(5 * world, dtype=torch.float64, device="cuda")
         dist.all_gather_into_tensor(allt, t)
         per_rank = [[round(x, 3) for x in row] for row in allt.view(world, 5).tolist()]
