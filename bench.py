@@ -1103,7 +1103,7 @@ def run_b200(args, rank: int, local_rank: int, world: int) -> None:
     c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     d_packed = torch.empty_like(h_packed, device="cuda")
     d_packed.copy_(h_packed, non_blocking=True)
-    torch.cuda.synchronize()
+    barrier()  # every rank copies at the same time, as in the leg above: the ranks share the host's upload path
     c0.record(stream)
     for _ in range(5):
         d_packed.copy_(h_packed, non_blocking=True)
